@@ -1,0 +1,64 @@
+"""ctypes binding of libgarnet_b200.so (the C ABI declared in include/garnet_b200.h).
+
+There is no fallback: if the library is missing or a call fails, an exception
+is raised."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import _build
+
+OK, INVALID_VALUE, NOT_SUPPORTED, CUDA_ERROR, DEVICE_FAULT, OUT_OF_MEMORY = range(6)
+FP16, BF16, FP32 = 0, 1, 2
+
+_lib = None
+
+
+class GarnetB200Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"garnet_b200 status {code}: {message}")
+        self.code = code
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    c = ctypes
+    vp, i, u, sz = c.c_void_p, c.c_int, c.c_uint, c.c_size_t
+    L.garnet_b200_last_error.restype = c.c_char_p
+    L.garnet_b200_abi_version.restype = i
+    L.garnet_b200_manifest_json.restype = c.c_char_p
+    L.garnet_b200_resolve.restype = vp
+    L.garnet_b200_resolve.argtypes = [c.c_char_p]
+    L.garnet_b200_binary_path.restype = c.c_char_p
+    L.garnet_b200_int4_quantize.argtypes = [vp, i, c.c_int64, c.c_int64, i, i, vp, vp, vp]
+    L.garnet_b200_w4a16_packed_bytes.argtypes = [i, i, i, c.POINTER(sz)]
+    L.garnet_b200_w4a16_pack_host.argtypes = [vp, vp, i, i, i, i, vp]
+    L.garnet_b200_w4a16_create.argtypes = [vp, vp, i, i, i, i, i, i, vp, c.POINTER(vp)]
+    L.garnet_b200_w4a16_create_prepacked.argtypes = [vp, i, i, i, i, c.POINTER(vp)]
+    L.garnet_b200_w4a16_shape.argtypes = [vp, c.POINTER(i), c.POINTER(i)]
+    L.garnet_b200_w4a16_workspace.argtypes = [vp, i, c.POINTER(sz)]
+    L.garnet_b200_w4a16_run.argtypes = [vp, vp, vp, i, vp, sz, u, vp]
+    L.garnet_b200_w4a16_run_host.argtypes = [vp, vp, vp, i, vp]
+    L.garnet_b200_w4a16_dequant.argtypes = [vp, vp, vp]
+    L.garnet_b200_w4a16_fault.argtypes = [vp]
+    L.garnet_b200_w4a16_destroy.argtypes = [vp]
+    L.garnet_b200_w4a16_destroy.restype = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = _build.LIB_PATH
+        if not os.path.exists(path):
+            path = _build.build()
+        L = ctypes.CDLL(path)
+        _declare(L)
+        if L.garnet_b200_abi_version() != 1:
+            raise RuntimeError("libgarnet_b200.so reports an unexpected ABI version")
+        _lib = L
+    return _lib
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise GarnetB200Error(code, lib().garnet_b200_last_error().decode())

@@ -1,0 +1,691 @@
+// Weight-only int4 linear for sm_100a: repackers, dequant check kernel, the
+// small-batch streaming kernel (M <= 16 per launch) and the C ABI around them.
+//
+// Numerics: y[m,n] = bf16( sum_k x[m,k] * q[n,k] * s[n,k/group] ) with fp32
+// accumulation.  In the streaming kernel q is expanded to an exact bf16 integer,
+// each group's partial sum is accumulated by the tensor core in fp32 and the
+// group scale is applied to that partial sum in fp32, so no product is rounded
+// before the final bf16 store.
+#include <algorithm>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "layout.h"
+#include "w4a16.h"
+
+namespace gb200 {
+
+// ------------------------------------------------------------------ repack
+
+// One thread per packed 32-bit word (8 codes of one row).
+__global__ void w4_repack_codes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, PackGeom geo,
+                                       long long src_row0)
+{
+    const size_t words_per_chunk = geo.chunk_data / 4;
+    const size_t total = size_t(geo.panels) * geo.chunks * words_per_chunk;
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t chunk_lin = idx / words_per_chunk;
+    const int w = int(idx % words_per_chunk);
+    const int panel = int(chunk_lin / geo.chunks), chunk = int(chunk_lin % geo.chunks);
+    // invert locate(): word index -> (row, first column)
+    const int tile = w >> 10, wt = w & 1023;          // 1024 words per 4 KiB tile
+    const int sub = wt >> 7, unit = (wt >> 2) & 31, word = wt & 3;
+    const int g = unit >> 2, t = unit & 3, h = word & 1, j = word >> 1;
+    const int n = panel * 128 + sub * 16 + row_of_g(g) + 8 * h;
+    const int k0 = chunk * geo.chunk_k + tile * 64 + (t + 4 * j) * 8;
+    uint32_t out = 0;
+    if (n < geo.rows && k0 < geo.cols) {
+        // K is a multiple of 8, so the 8 codes are 4 aligned source bytes.
+        const size_t sb = ((size_t(src_row0) + n) * size_t(geo.cols) + k0) / 2;
+        const uint32_t in = *reinterpret_cast<const uint32_t*>(src + sb);
+        if (geo.format == kFormatInt4) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) out |= ((in >> (4 * e)) & 15u) << (4 * ((e >> 1) + 4 * (e & 1)));
+        } else {
+            out = in;
+        }
+    }
+    const size_t ob = size_t(panel) * geo.panel_bytes() + size_t(chunk) * geo.chunk_bytes + size_t(w) * 4;
+    *reinterpret_cast<uint32_t*>(dst + ob) = out;
+}
+
+// int4 scales: one thread per (padded row, chunk).  The 16 scale bits are kept as
+// they are (fp16 or bf16); the kernels widen them to fp32 according to the
+// handle's scale_dtype.
+__global__ void w4_repack_scales_int4_kernel(const uint16_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                             PackGeom geo, long long src_row0)
+{
+    const size_t total = size_t(geo.panels) * 128 * geo.chunks;
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int n = int(idx / geo.chunks), chunk = int(idx % geo.chunks);
+    uint16_t bits = 0;
+    if (n < geo.rows) {
+        const int groups = geo.cols / geo.group;
+        bits = src[(size_t(src_row0) + n) * groups + (chunk * geo.chunk_k) / geo.group];
+    }
+    *reinterpret_cast<uint16_t*>(dst + locate_scale(geo, n, chunk * geo.chunk_k)) = bits;
+}
+
+// ------------------------------------------------------------------ dequant
+
+// fp32 q*s of every logical element, decoded from the packed tiles with the same
+// device function the GEMM kernels use.
+__device__ __forceinline__ float scale16_to_float(uint32_t bits16, int scale_dtype)
+{
+    return scale_dtype == GARNET_B200_BF16 ? __uint_as_float(bits16 << 16)
+                                           : __half2float(__ushort_as_half(uint16_t(bits16)));
+}
+
+__global__ void w4_dequant_kernel(const uint8_t* __restrict__ packed, float* __restrict__ out, PackGeom geo,
+                                  int scale_dtype)
+{
+    const size_t total = size_t(geo.rows) * geo.cols / 2;
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int n = int(idx / (geo.cols / 2)), k = int(idx % (geo.cols / 2)) * 2;   // elements k, k+1
+    const PackPos p = locate(geo, n, k);
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(packed + p.word_byte);
+    const int pair = (k & 7) >> 1;
+    const uint32_t v = int4x2_to_bf16x2(w >> (4 * pair));
+    const float s = scale16_to_float(*reinterpret_cast<const uint16_t*>(packed + locate_scale(geo, n, k)), scale_dtype);
+    out[size_t(n) * geo.cols + k] = __bfloat162float(__ushort_as_bfloat16(uint16_t(v & 0xffff))) * s;
+    out[size_t(n) * geo.cols + k + 1] = __bfloat162float(__ushort_as_bfloat16(uint16_t(v >> 16))) * s;
+}
+
+// --------------------------------------------------------------- quantizer
+
+// One warp per (row, group).  weight_quantization.cpp:220-266.
+template <typename T>
+__device__ __forceinline__ float load_as_float(const T* p, size_t i);
+template <>
+__device__ __forceinline__ float load_as_float<float>(const float* p, size_t i) { return p[i]; }
+template <>
+__device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16* p, size_t i)
+{
+    return __bfloat162float(p[i]);
+}
+template <>
+__device__ __forceinline__ float load_as_float<__half>(const __half* p, size_t i) { return __half2float(p[i]); }
+
+template <typename T>
+__global__ void int4_quantize_kernel(const T* __restrict__ src, long long rows, long long cols, int group,
+                                     int scale_dtype, uint8_t* __restrict__ nibbles, uint16_t* __restrict__ scales)
+{
+    const long long groups = cols / group;
+    const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= rows * groups) return;
+    const long long row = wid / groups, grp = wid % groups;
+    const size_t start = size_t(row) * cols + size_t(grp) * group;
+    float lo = 0.f, hi = 0.f;
+    for (int o = lane; o < group; o += 32) {
+        const float v = load_as_float(src, start + o);
+        lo = fminf(lo, v);
+        hi = fmaxf(hi, v);
+    }
+    for (int off = 16; off; off >>= 1) {
+        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+    }
+    float scale = fmaxf(__fdiv_rn(-lo, 8.0f), __fdiv_rn(hi, 7.0f));
+    if (!isfinite(scale) || scale <= 0.f) scale = 1.0f;
+    uint16_t bits;
+    float stored;
+    if (scale_dtype == GARNET_B200_FP16) {
+        const __half hs = __float2half_rn(scale);
+        bits = __half_as_ushort(hs);
+        stored = __half2float(hs);
+    } else {
+        const __nv_bfloat16 bs = __float2bfloat16_rn(scale);
+        bits = __bfloat16_as_ushort(bs);
+        stored = __bfloat162float(bs);
+    }
+    if (lane == 0) scales[row * groups + grp] = bits;
+    // each lane packs pairs of elements: byte index (start + 2i) / 2
+    for (int o = 2 * lane; o < group; o += 64) {
+        int q0 = __float2int_rn(__fdiv_rn(load_as_float(src, start + o), stored));
+        int q1 = __float2int_rn(__fdiv_rn(load_as_float(src, start + o + 1), stored));
+        q0 = max(-8, min(7, q0));
+        q1 = max(-8, min(7, q1));
+        nibbles[(start + o) >> 1] = uint8_t((q0 & 15) | ((q1 & 15) << 4));
+    }
+}
+
+// ------------------------------------------------------- streaming kernel
+
+constexpr int kGemvStages = 6;
+constexpr int kGemvConsumerWarps = 8;
+constexpr int kGemvThreads = (kGemvConsumerWarps + 1) * 32;
+constexpr int kInt4ChunkBytes = 8192 + 256;
+
+struct GemvParams {
+    const uint8_t* packed;
+    const __nv_bfloat16* x;
+    __nv_bfloat16* y;
+    float* partial;      // [gk][m][padded rows] fp32, only when gk > 1
+    int* counters;       // [panels], self-resetting, only when gk > 1
+    int* fault;          // mapped host word; non-zero = a bounded wait gave up
+    int m, n, k;         // batch rows, logical weight rows, logical K
+    int ldy;             // row stride of y in elements
+    int panels, chunks, gk;
+    int kspan_max;       // K columns per CTA, upper bound (sizes the x tile)
+    int scale_dtype;     // GARNET_B200_FP16 / GARNET_B200_BF16
+    size_t panel_bytes;
+};
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// CTA = 8 consumer warps (one 16-row sub-tile each) + 1 producer warp.  The
+// producer streams the panel's chunks (codes + scales, 8448 bytes each) through a
+// ring of bulk copies; consumers expand int4 -> bf16 in registers and feed
+// m16n8k16 MMAs whose N dimension is the (padded) batch.
+template <int MB>
+__global__ void __launch_bounds__(kGemvThreads) w4a16_stream_kernel(const GemvParams p)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* stages = smem;                                               // kGemvStages * chunk
+    uint8_t* xs = smem + kGemvStages * kInt4ChunkBytes;                   // x tile, padded rows
+    const int x_stride = p.kspan_max * 2 + 64;                            // bytes; 64 mod 128 => conflict-free
+    uint64_t* full = reinterpret_cast<uint64_t*>(xs + size_t(8 * MB) * x_stride);
+    uint64_t* empty = full + kGemvStages;
+    __shared__ int s_last;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int panel = blockIdx.x / p.gk, ks = blockIdx.x % p.gk;
+    const int c0 = int((long long)ks * p.chunks / p.gk), c1 = int((long long)(ks + 1) * p.chunks / p.gk);
+    const int nchunks = c1 - c0;
+    const uint8_t* src = p.packed + size_t(panel) * p.panel_bytes + size_t(c0) * kInt4ChunkBytes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGemvStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kGemvConsumerWarps);
+        }
+        fence_barrier_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == kGemvConsumerWarps) {
+        // ---- producer: weights are constants, so streaming starts before the
+        // previous kernel in the stream has finished.
+        if (lane == 0) {
+            for (int i = 0; i < nchunks; ++i) {
+                const int s = i % kGemvStages;
+                if (i >= kGemvStages && !mbar_wait(&empty[s], ((i / kGemvStages) - 1) & 1)) {
+                    atomicExch(p.fault, 1);
+                    break;
+                }
+                mbar_expect_tx(&full[s], kInt4ChunkBytes);
+                bulk_g2s(stages + size_t(s) * kInt4ChunkBytes, src + size_t(i) * kInt4ChunkBytes, kInt4ChunkBytes,
+                         &full[s]);
+            }
+        }
+        return;
+    }
+
+    // ---- consumers
+    pdl_wait();   // x is produced by the previous kernel; y / partial may still be read by it
+    {
+        const int kbeg = c0 * 128, kspan = nchunks * 128;
+        const int vec_per_row = kspan / 8;
+        for (int i = threadIdx.x; i < 8 * MB * vec_per_row; i += kGemvConsumerWarps * 32) {
+            const int m = i / vec_per_row, v = i % vec_per_row;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (m < p.m) val = *reinterpret_cast<const uint4*>(p.x + size_t(m) * p.k + kbeg + v * 8);
+            *reinterpret_cast<uint4*>(xs + size_t(m) * x_stride + v * 16) = val;
+        }
+    }
+    named_barrier_sync(1, kGemvConsumerWarps * 32);
+
+    const int g = lane >> 2, t = lane & 3;
+    float acc[MB][4];
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mb][i] = 0.f;
+    const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+
+    bool ok = true;
+    for (int i = 0; i < nchunks && ok; ++i) {
+        const int s = i % kGemvStages;
+        if (!mbar_wait(&full[s], (i / kGemvStages) & 1)) {
+            atomicExch(p.fault, 2);
+            ok = false;
+            break;
+        }
+        const uint8_t* st = stages + size_t(s) * kInt4ChunkBytes;
+        const uint32_t sc = *reinterpret_cast<const uint32_t*>(st + 8192 + (warp * 8 + g) * 4);
+        const float s_lo = scale16_to_float(sc & 0xffffu, p.scale_dtype), s_hi = scale16_to_float(sc >> 16, p.scale_dtype);
+        float tmp[MB][4];
+#pragma unroll
+        for (int tile = 0; tile < 2; ++tile) {
+            const uint4 u = *reinterpret_cast<const uint4*>(st + tile * 4096 + warp * 512 + lane * 16);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint32_t wlo = half ? u.z : u.x, whi = half ? u.w : u.y;
+                const int kloc = i * 128 + tile * 64 + (t + 4 * half) * 8;
+                uint32_t a0[4] = {int4x2_to_bf16x2(wlo), int4x2_to_bf16x2(whi), int4x2_to_bf16x2(wlo >> 4),
+                                  int4x2_to_bf16x2(whi >> 4)};
+                uint32_t a1[4] = {int4x2_to_bf16x2(wlo >> 8), int4x2_to_bf16x2(whi >> 8),
+                                  int4x2_to_bf16x2(wlo >> 12), int4x2_to_bf16x2(whi >> 12)};
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) {
+                    const uint4 xb =
+                        *reinterpret_cast<const uint4*>(xs + size_t(mb * 8 + g) * x_stride + size_t(kloc) * 2);
+                    if (tile == 0 && half == 0)
+                        mma_bf16_16816(tmp[mb], a0, xb.x, xb.y, zero4);
+                    else
+                        mma_bf16_16816(tmp[mb], a0, xb.x, xb.y, tmp[mb]);
+                    mma_bf16_16816(tmp[mb], a1, xb.z, xb.w, tmp[mb]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+            acc[mb][0] = fmaf(tmp[mb][0], s_lo, acc[mb][0]);
+            acc[mb][1] = fmaf(tmp[mb][1], s_lo, acc[mb][1]);
+            acc[mb][2] = fmaf(tmp[mb][2], s_hi, acc[mb][2]);
+            acc[mb][3] = fmaf(tmp[mb][3], s_hi, acc[mb][3]);
+        }
+    }
+
+    if (!ok) {
+        // A wait gave up: give the copies still in flight a bounded chance to land
+        // before this CTA's shared memory is released.
+        for (int i = 0; i < nchunks; ++i) (void)mbar_wait(&full[i % kGemvStages], (i / kGemvStages) & 1);
+    }
+
+    // ---- epilogue.  acc[mb][0..1]: row R(g), batch columns 2t, 2t+1; [2..3]: row R(g)+8.
+    const int n_lo = panel * 128 + warp * 16 + row_of_g(g);
+    if (p.gk == 1) {
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int m = mb * 8 + 2 * t + (i & 1), n = n_lo + 8 * (i >> 1);
+                if (m < p.m && n < p.n) p.y[size_t(m) * p.ldy + n] = __float2bfloat16_rn(acc[mb][i]);
+            }
+        return;
+    }
+    const int np = p.panels * 128;
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int m = mb * 8 + 2 * t + (i & 1), n = n_lo + 8 * (i >> 1);
+            if (m < p.m) p.partial[(size_t(ks) * p.m + m) * np + n] = acc[mb][i];
+        }
+    __threadfence();
+    named_barrier_sync(1, kGemvConsumerWarps * 32);
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(&p.counters[panel], 1);
+        s_last = (old == p.gk - 1);
+        if (s_last) p.counters[panel] = 0;   // ready for the next call on this handle
+    }
+    named_barrier_sync(1, kGemvConsumerWarps * 32);
+    if (!s_last) return;
+    __threadfence();
+    // The last CTA of the panel adds the slices in slice order: the result does
+    // not depend on which CTA finished last.
+    for (int i = threadIdx.x; i < p.m * 128; i += kGemvConsumerWarps * 32) {
+        const int m = i >> 7, n = panel * 128 + (i & 127);
+        if (n >= p.n) continue;
+        float v = 0.f;
+        for (int q = 0; q < p.gk; ++q) v += __ldcg(&p.partial[(size_t(q) * p.m + m) * np + n]);
+        p.y[size_t(m) * p.ldy + n] = __float2bfloat16_rn(v);
+    }
+}
+
+// ------------------------------------------------------------------ handle
+
+static int pick_split(const PackGeom& geo)
+{
+    // Enough CTAs to cover the machine about twice, never more K columns per CTA
+    // than the x tile can hold, never less than one chunk.
+    const int min_gk = (geo.chunks * 128 + kW4MaxKSpan - 1) / kW4MaxKSpan;
+    int gk = (2 * kSmCount + geo.panels - 1) / geo.panels;
+    gk = std::max(gk, min_gk);
+    gk = std::min(gk, geo.chunks);
+    return std::max(gk, 1);
+}
+
+static size_t gemv_smem_bytes(int mb, int kspan_max)
+{
+    return size_t(kGemvStages) * kInt4ChunkBytes + size_t(8 * mb) * (size_t(kspan_max) * 2 + 64) +
+           2 * kGemvStages * sizeof(uint64_t);
+}
+
+int W4A16::init_common()
+{
+    gk = pick_split(geo);
+    kspan_max = ((geo.chunks + gk - 1) / gk) * 128;
+    GB_CUDA(cudaGetDevice(&device));
+    GB_CUDA(cudaMalloc(&counters, sizeof(int) * size_t(geo.panels)));
+    GB_CUDA(cudaMemset(counters, 0, sizeof(int) * size_t(geo.panels)));
+    GB_CUDA(cudaHostAlloc(&fault_host, sizeof(int), cudaHostAllocMapped));
+    *fault_host = 0;
+    GB_CUDA(cudaHostGetDevicePointer(&fault_dev, fault_host, 0));
+    GB_CUDA(cudaFuncSetAttribute(w4a16_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(gemv_smem_bytes(1, kW4MaxKSpan))));
+    GB_CUDA(cudaFuncSetAttribute(w4a16_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(gemv_smem_bytes(2, kW4MaxKSpan))));
+    return GARNET_B200_OK;
+}
+
+W4A16::~W4A16()
+{
+    if (owns_packed && packed) cudaFree(packed);
+    if (counters) cudaFree(counters);
+    if (fault_host) cudaFreeHost(fault_host);
+    if (stage_x) cudaFree(stage_x);
+    if (stage_y) cudaFree(stage_y);
+    if (stage_ws) cudaFree(stage_ws);
+    if (pin_x) cudaFreeHost(pin_x);
+    if (pin_y) cudaFreeHost(pin_y);
+}
+
+size_t W4A16::workspace_bytes(int m) const
+{
+    if (gk <= 1) return 0;
+    const int rows = std::min(m, 16);
+    return size_t(gk) * rows * geo.padded_rows() * sizeof(float);
+}
+
+int W4A16::launch_stream(const __nv_bfloat16* x, __nv_bfloat16* y, int m, int ldy, void* ws, unsigned flags,
+                         cudaStream_t stream)
+{
+    GemvParams p;
+    p.packed = packed;
+    p.x = x;
+    p.y = y;
+    p.partial = static_cast<float*>(ws);
+    p.counters = counters;
+    p.fault = fault_dev;
+    p.m = m;
+    p.n = geo.rows;
+    p.k = geo.cols;
+    p.ldy = ldy;
+    p.panels = geo.panels;
+    p.chunks = geo.chunks;
+    p.gk = gk;
+    p.kspan_max = kspan_max;
+    p.panel_bytes = geo.panel_bytes();
+    p.scale_dtype = scale_dtype;
+
+    const int mb = m <= 8 ? 1 : 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(geo.panels * gk));
+    cfg.blockDim = dim3(kGemvThreads);
+    cfg.dynamicSmemBytes = gemv_smem_bytes(mb, kspan_max);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & 1u) ? 1 : 0;
+    if (mb == 1)
+        GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_stream_kernel<1>, p));
+    else
+        GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_stream_kernel<2>, p));
+    return GARNET_B200_OK;
+}
+
+int W4A16::run(const void* d_x, void* d_y, int m, void* ws, size_t ws_bytes, unsigned flags, cudaStream_t stream)
+{
+    if (m <= 0) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run: m must be positive (got %d)", m);
+    if (!d_x || !d_y) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run: null x or y");
+    if ((reinterpret_cast<uintptr_t>(d_x) & 15) || (reinterpret_cast<uintptr_t>(d_y) & 1))
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_run: x must be 16-byte aligned");
+    if (ws_bytes < workspace_bytes(m) || (workspace_bytes(m) && !ws))
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_run: workspace too small (%zu < %zu)", ws_bytes,
+                    workspace_bytes(m));
+    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(d_x);
+    __nv_bfloat16* y = static_cast<__nv_bfloat16*>(d_y);
+    for (int m0 = 0; m0 < m; m0 += 16) {
+        const int rows = std::min(16, m - m0);
+        const int rc = launch_stream(x + size_t(m0) * geo.cols, y + size_t(m0) * geo.rows, rows, geo.rows, ws,
+                                     flags, stream);
+        if (rc) return rc;
+    }
+    return GARNET_B200_OK;
+}
+
+static int validate_shape(int n, int k, int group)
+{
+    if (n <= 0 || k <= 0 || group <= 0) return fail(GARNET_B200_INVALID_VALUE, "w4a16: n, k, group must be positive");
+    if (k % group) return fail(GARNET_B200_INVALID_VALUE, "w4a16: k (%d) is not a multiple of group (%d)", k, group);
+    if (group % 128)
+        return fail(GARNET_B200_NOT_SUPPORTED, "w4a16: group %d is not a multiple of 128", group);
+    return GARNET_B200_OK;
+}
+
+int w4a16_repack_device(const uint8_t* d_nibbles, const uint16_t* d_scales, const PackGeom& geo, long long row0,
+                        uint8_t* d_packed, cudaStream_t stream)
+{
+    const size_t words = size_t(geo.panels) * geo.chunks * (geo.chunk_data / 4);
+    w4_repack_codes_kernel<<<unsigned((words + 255) / 256), 256, 0, stream>>>(d_nibbles, d_packed, geo, row0);
+    const size_t sc = size_t(geo.panels) * 128 * geo.chunks;
+    w4_repack_scales_int4_kernel<<<unsigned((sc + 255) / 256), 256, 0, stream>>>(d_scales, d_packed, geo, row0);
+    GB_CUDA(cudaGetLastError());
+    return GARNET_B200_OK;
+}
+
+}  // namespace gb200
+
+using namespace gb200;
+
+extern "C" {
+
+int garnet_b200_int4_quantize(const void* d_src, int src_dtype, int64_t rows, int64_t cols, int group,
+                              int scale_dtype, uint8_t* d_nibbles, uint16_t* d_scales, void* stream)
+{
+    if (!d_src || !d_nibbles || !d_scales) return fail(GARNET_B200_INVALID_VALUE, "int4_quantize: null pointer");
+    if (rows <= 0 || cols <= 0 || group <= 0 || cols % group || (group & 1))
+        return fail(GARNET_B200_INVALID_VALUE, "int4_quantize: bad shape rows=%lld cols=%lld group=%d",
+                    (long long)rows, (long long)cols, group);
+    if (scale_dtype != GARNET_B200_FP16 && scale_dtype != GARNET_B200_BF16)
+        return fail(GARNET_B200_INVALID_VALUE, "int4_quantize: scale dtype must be fp16 or bf16");
+    const long long warps = rows * (cols / group);
+    const unsigned blocks = unsigned((warps * 32 + 255) / 256);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (src_dtype) {
+        case GARNET_B200_FP32:
+            int4_quantize_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(d_src), rows, cols, group,
+                                                              scale_dtype, d_nibbles, d_scales);
+            break;
+        case GARNET_B200_BF16:
+            int4_quantize_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(d_src),
+                                                                      rows, cols, group, scale_dtype, d_nibbles,
+                                                                      d_scales);
+            break;
+        case GARNET_B200_FP16:
+            int4_quantize_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const __half*>(d_src), rows, cols,
+                                                               group, scale_dtype, d_nibbles, d_scales);
+            break;
+        default:
+            return fail(GARNET_B200_INVALID_VALUE, "int4_quantize: unknown source dtype %d", src_dtype);
+    }
+    GB_CUDA(cudaGetLastError());
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_packed_bytes(int n, int k, int group, size_t* bytes)
+{
+    if (!bytes) return fail(GARNET_B200_INVALID_VALUE, "w4a16_packed_bytes: null output");
+    if (int rc = validate_shape(n, k, group)) return rc;
+    *bytes = make_geom(kFormatInt4, n, k, group).matrix_bytes();
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_pack_host(const uint8_t* nibbles, const uint16_t* scales, int scale_dtype, int n, int k,
+                                int group, uint8_t* packed)
+{
+    if (!nibbles || !scales || !packed) return fail(GARNET_B200_INVALID_VALUE, "w4a16_pack_host: null pointer");
+    if (int rc = validate_shape(n, k, group)) return rc;
+    if (scale_dtype != GARNET_B200_FP16 && scale_dtype != GARNET_B200_BF16)
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_pack_host: scale dtype must be fp16 or bf16");
+    const PackGeom geo = make_geom(kFormatInt4, n, k, group);
+    std::memset(packed, 0, geo.matrix_bytes());
+    const int groups = k / group;
+    for (int row = 0; row < n; ++row) {
+        for (int col = 0; col < k; col += 8) {
+            uint32_t in;
+            std::memcpy(&in, nibbles + (size_t(row) * k + col) / 2, 4);
+            uint32_t out = 0;
+            for (int e = 0; e < 8; ++e) out |= ((in >> (4 * e)) & 15u) << (4 * ((e >> 1) + 4 * (e & 1)));
+            std::memcpy(packed + locate(geo, row, col).word_byte, &out, 4);
+        }
+        for (int chunk = 0; chunk < geo.chunks; ++chunk) {
+            const uint16_t s = scales[size_t(row) * groups + (chunk * 128) / group];
+            std::memcpy(packed + locate_scale(geo, row, chunk * 128), &s, 2);
+        }
+    }
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_create(const uint8_t* d_nibbles, const void* d_scales, int scale_dtype, int n, int k,
+                             int group, int shard_rank, int shard_world, void* stream,
+                             garnet_b200_w4a16_t* out)
+{
+    if (!out) return fail(GARNET_B200_INVALID_VALUE, "w4a16_create: null output handle");
+    *out = nullptr;
+    if (!d_nibbles || !d_scales) return fail(GARNET_B200_INVALID_VALUE, "w4a16_create: null weight pointer");
+    if (int rc = validate_shape(n, k, group)) return rc;
+    if (scale_dtype != GARNET_B200_FP16 && scale_dtype != GARNET_B200_BF16)
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_create: scale dtype must be fp16 or bf16");
+    if (shard_world < 1) shard_world = 1;
+    if (shard_rank < 0 || shard_rank >= shard_world || n % shard_world)
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_create: bad shard %d of %d for n=%d", shard_rank, shard_world, n);
+    const int n_local = n / shard_world;
+    W4A16* h = new (std::nothrow) W4A16();
+    if (!h) return fail(GARNET_B200_OUT_OF_MEMORY, "w4a16_create: host allocation failed");
+    h->geo = make_geom(kFormatInt4, n_local, k, group);
+    h->scale_dtype = scale_dtype;
+    h->owns_packed = true;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc = GARNET_B200_OK;
+    do {
+        if (cudaMalloc(&h->packed, h->geo.matrix_bytes()) != cudaSuccess) {
+            rc = fail(GARNET_B200_OUT_OF_MEMORY, "w4a16_create: cudaMalloc of %zu bytes failed", h->geo.matrix_bytes());
+            cudaGetLastError();
+            break;
+        }
+        if ((rc = w4a16_repack_device(d_nibbles, static_cast<const uint16_t*>(d_scales), h->geo,
+                                      (long long)shard_rank * n_local, h->packed, s)))
+            break;
+        if ((rc = h->init_common())) break;
+        if (cudaStreamSynchronize(s) != cudaSuccess) {
+            rc = cuda_fail(cudaGetLastError(), "w4a16_create: synchronize");
+            break;
+        }
+    } while (false);
+    if (rc) {
+        delete h;
+        return rc;
+    }
+    *out = reinterpret_cast<garnet_b200_w4a16_t>(h);
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_create_prepacked(const uint8_t* d_packed, int scale_dtype, int n, int k, int group,
+                                       garnet_b200_w4a16_t* out)
+{
+    if (!out) return fail(GARNET_B200_INVALID_VALUE, "w4a16_create_prepacked: null output handle");
+    *out = nullptr;
+    if (!d_packed || (reinterpret_cast<uintptr_t>(d_packed) & 127))
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_create_prepacked: packed pointer must be 128-byte aligned");
+    if (int rc = validate_shape(n, k, group)) return rc;
+    W4A16* h = new (std::nothrow) W4A16();
+    if (!h) return fail(GARNET_B200_OUT_OF_MEMORY, "w4a16_create_prepacked: host allocation failed");
+    h->geo = make_geom(kFormatInt4, n, k, group);
+    h->packed = const_cast<uint8_t*>(d_packed);
+    h->scale_dtype = scale_dtype;
+    h->owns_packed = false;
+    if (int rc = h->init_common()) {
+        delete h;
+        return rc;
+    }
+    *out = reinterpret_cast<garnet_b200_w4a16_t>(h);
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_shape(garnet_b200_w4a16_t hh, int* n_local, int* k)
+{
+    W4A16* h = reinterpret_cast<W4A16*>(hh);
+    if (!h) return fail(GARNET_B200_INVALID_VALUE, "w4a16_shape: null handle");
+    if (n_local) *n_local = h->geo.rows;
+    if (k) *k = h->geo.cols;
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_workspace(garnet_b200_w4a16_t hh, int m, size_t* bytes)
+{
+    W4A16* h = reinterpret_cast<W4A16*>(hh);
+    if (!h || !bytes || m <= 0) return fail(GARNET_B200_INVALID_VALUE, "w4a16_workspace: bad argument");
+    *bytes = h->workspace_bytes(m);
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_run(garnet_b200_w4a16_t hh, const void* d_x, void* d_y, int m, void* d_workspace,
+                          size_t workspace_bytes, unsigned flags, void* stream)
+{
+    W4A16* h = reinterpret_cast<W4A16*>(hh);
+    if (!h) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run: null handle");
+    return h->run(d_x, d_y, m, d_workspace, workspace_bytes, flags, static_cast<cudaStream_t>(stream));
+}
+
+int garnet_b200_w4a16_run_host(garnet_b200_w4a16_t hh, const void* h_x, void* h_y, int m, void* stream)
+{
+    W4A16* h = reinterpret_cast<W4A16*>(hh);
+    if (!h || !h_x || !h_y || m <= 0) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run_host: bad argument");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t xb = size_t(m) * h->geo.cols * 2, yb = size_t(m) * h->geo.rows * 2, wb = h->workspace_bytes(m);
+    if (m > h->stage_rows) {
+        if (h->stage_x) cudaFree(h->stage_x);
+        if (h->stage_y) cudaFree(h->stage_y);
+        if (h->stage_ws) cudaFree(h->stage_ws);
+        h->stage_x = h->stage_y = h->stage_ws = nullptr;
+        h->stage_rows = 0;
+        GB_CUDA(cudaMalloc(&h->stage_x, xb));
+        GB_CUDA(cudaMalloc(&h->stage_y, yb));
+        if (wb) GB_CUDA(cudaMalloc(&h->stage_ws, wb));
+        h->stage_rows = m;
+    }
+    GB_CUDA(cudaMemcpyAsync(h->stage_x, h_x, xb, cudaMemcpyHostToDevice, s));
+    if (int rc = h->run(h->stage_x, h->stage_y, m, h->stage_ws, wb, 0, s)) return rc;
+    GB_CUDA(cudaMemcpyAsync(h_y, h->stage_y, yb, cudaMemcpyDeviceToHost, s));
+    GB_CUDA(cudaStreamSynchronize(s));
+    if (*h->fault_host) return fail(GARNET_B200_DEVICE_FAULT, "w4a16: device wait gave up (code %d)", *h->fault_host);
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_dequant(garnet_b200_w4a16_t hh, float* d_out, void* stream)
+{
+    W4A16* h = reinterpret_cast<W4A16*>(hh);
+    if (!h || !d_out) return fail(GARNET_B200_INVALID_VALUE, "w4a16_dequant: bad argument");
+    const size_t total = size_t(h->geo.rows) * h->geo.cols / 2;
+    w4_dequant_kernel<<<unsigned((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        h->packed, d_out, h->geo, h->scale_dtype);
+    GB_CUDA(cudaGetLastError());
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_fault(garnet_b200_w4a16_t hh)
+{
+    W4A16* h = reinterpret_cast<W4A16*>(hh);
+    return h && h->fault_host ? *h->fault_host : -1;
+}
+
+void garnet_b200_w4a16_destroy(garnet_b200_w4a16_t hh) { delete reinterpret_cast<W4A16*>(hh); }
+
+}  // extern "C"

@@ -1,0 +1,135 @@
+/*
+ * garnet_b200.h - C ABI of the B200 (sm_100a) quantized-matmul library.
+ *
+ * Drop-in boundary for the two quantized operators of Garnet:
+ *   - the weight-only int4 linear (every Qwen3 decoder projection and lm_head);
+ *   - the gpt-oss MXFP4 mixture-of-experts operator `gpt_oss_moe_mxfp4`.
+ * Every entry point takes plain pointers, sizes and a CUDA stream (passed as
+ * void*), returns an int status and never throws.  Each declaration cites the
+ * reference interface it replaces (path inside the Garnet checkout : line).
+ *
+ * Ownership: the caller owns inputs, outputs, workspaces and the stream.  A
+ * handle owns only its repacked weight copy and a few counters.  `*_run`
+ * functions do not allocate, free or synchronise.  A handle is not thread-safe:
+ * use one handle per (device, stream), as the reference requires of its plugin
+ * objects (plugins/gpt_oss/include/gpt_oss_marlin.h:14-16).
+ */
+#ifndef GARNET_B200_H
+#define GARNET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GARNET_B200_ABI 1
+
+/* Status codes.  The reference returns cudaError_t from its free functions and
+ * int (0 = ok) from its C exports (src/include/garnet_serving.h:22-36); here
+ * cudaErrorInvalidValue maps to INVALID_VALUE and cudaErrorNotSupported ("use
+ * the fallback", plugins/gpt_oss/tensorrt/gpt_oss_plugin.cpp:405) to
+ * NOT_SUPPORTED. */
+enum {
+    GARNET_B200_OK = 0,
+    GARNET_B200_INVALID_VALUE = 1,
+    GARNET_B200_NOT_SUPPORTED = 2,
+    GARNET_B200_CUDA_ERROR = 3,
+    GARNET_B200_DEVICE_FAULT = 4,   /* a bounded device-side wait gave up */
+    GARNET_B200_OUT_OF_MEMORY = 5
+};
+
+enum { GARNET_B200_FP16 = 0, GARNET_B200_BF16 = 1, GARNET_B200_FP32 = 2 };
+
+/* Thread-local text of the last failure on the calling thread. */
+const char* garnet_b200_last_error(void);
+
+/* ---- plugin discovery -------------------------------------------------------
+ * Replaces the four callbacks of GarnetOperatorModuleBridge
+ * (src/model/operator_module_bridge.h:6-14): abi, manifest(), resolve_callback(name),
+ * binary_path().  The manifest has the keys of the reference's manifest
+ * (plugins/gpt_oss/tensorrt/gpt_oss_plugin.cpp:497-503): id, module, abi, version,
+ * backend, operators. */
+int garnet_b200_abi_version(void);
+const char* garnet_b200_manifest_json(void);
+void* garnet_b200_resolve(const char* symbol_name);
+const char* garnet_b200_binary_path(void);
+
+/* ---- int4 quantizer ---------------------------------------------------------
+ * Replaces Garnet::QuantizeSymmetricINT4 (src/model/weight_quantization.cpp:188-270)
+ * for a device-resident weight: per (row, K-group) scale = max(-min/8, max/7),
+ * stored rounded to `scale_dtype` (the reference stores fp16; the B200 path is
+ * specified with bf16), q = clamp(nearbyint(v / stored_scale), -8, 7), canonical
+ * nibble packing.  `d_src` is [rows, cols] of `src_dtype`; `d_nibbles` receives
+ * rows*cols/2 bytes, `d_scales` rows*cols/group 16-bit values. */
+int garnet_b200_int4_quantize(const void* d_src, int src_dtype, int64_t rows, int64_t cols, int group,
+                              int scale_dtype, uint8_t* d_nibbles, uint16_t* d_scales, void* stream);
+
+/* ---- W4A16 linear -----------------------------------------------------------
+ * y[M,N] = x[M,K] * W^T with W int4 (group scales), x and y bf16, fp32
+ * accumulation.  Replaces, for the CUDA backend, the int4 branch of
+ * GetOrCreateTRTWeight + MatMul (src/backends/tensorrt/trt_builder.cpp:3285-3344,
+ * :7398-7408) and mirrors the life cycle of the CPU operator Garnet::Q4Q8Linear
+ * (src/backends/cpu/q4q8_linear.h:21-35): Prepare -> create, Forward -> run. */
+typedef struct garnet_b200_w4a16* garnet_b200_w4a16_t;
+
+/* Bytes of the packed form of an [N,K] matrix (codes and scales together). */
+int garnet_b200_w4a16_packed_bytes(int n, int k, int group, size_t* bytes);
+
+/* Host repacker: canonical nibbles + 16-bit scales -> packed bytes, identical to
+ * what the device repacker writes.  Counterpart of the reference's host packers
+ * that let an engine hold prepacked constants (Q4Q8Linear::Prepare,
+ * q4q8_linear.cpp:227-283; PackGptOssMarlinWeight, gpt_oss_marlin_pack.h:74-193). */
+int garnet_b200_w4a16_pack_host(const uint8_t* nibbles, const uint16_t* scales, int scale_dtype, int n, int k,
+                                int group, uint8_t* packed);
+
+/* Creates the operator from device-resident canonical weights.  With
+ * shard_world > 1 the handle keeps only rows [rank*N/world, (rank+1)*N/world)
+ * (tensor-parallel split along N; the reference's vocab-parallel lm_head,
+ * trt_builder.cpp:7360-7371).  Repacks on `stream` and synchronises it once.
+ * Q4Q8Linear::Prepare (q4q8_linear.cpp:227). */
+int garnet_b200_w4a16_create(const uint8_t* d_nibbles, const void* d_scales, int scale_dtype, int n, int k,
+                             int group, int shard_rank, int shard_world, void* stream,
+                             garnet_b200_w4a16_t* out);
+
+/* Creates the operator over already packed device bytes, which are borrowed, not
+ * copied (Q4Q8Linear::BindPackedView, q4q8_linear.cpp:285-313). */
+int garnet_b200_w4a16_create_prepacked(const uint8_t* d_packed, int scale_dtype, int n, int k, int group,
+                                       garnet_b200_w4a16_t* out);
+
+/* Logical rows held by this handle (N / shard_world) and K. */
+int garnet_b200_w4a16_shape(garnet_b200_w4a16_t h, int* n_local, int* k);
+
+/* Workspace bytes `run` needs for a batch of m rows (0 is possible). */
+int garnet_b200_w4a16_workspace(garnet_b200_w4a16_t h, int m, size_t* bytes);
+
+/* y[m, n_local] = x[m, k] W^T.  x, y bf16 device pointers, row-major, 16-byte
+ * aligned.  Q4Q8Linear::Forward (q4q8_linear.cpp:315-389).  `flags`: bit 0 asks
+ * for a programmatic dependent launch, so that this kernel's weight prefetch
+ * overlaps the tail of the previous kernel in the stream. */
+int garnet_b200_w4a16_run(garnet_b200_w4a16_t h, const void* d_x, void* d_y, int m, void* d_workspace,
+                          size_t workspace_bytes, unsigned flags, void* stream);
+
+/* Same call for host-resident x and y (the plugin-facing form: host -> device
+ * copy, kernel, device -> host copy on `stream`, then a stream synchronise).
+ * Staging buffers belong to the handle and grow on first use. */
+int garnet_b200_w4a16_run_host(garnet_b200_w4a16_t h, const void* h_x, void* h_y, int m, void* stream);
+
+/* Writes the dequantised weights q*s as fp32 [n_local, k], reading the packed
+ * tiles with the same device decode the GEMM kernels use (bit-exactness check;
+ * cf. TestGptOssMxfp4Decode, plugins/gpt_oss/include/gpt_oss_kernels.h:65). */
+int garnet_b200_w4a16_dequant(garnet_b200_w4a16_t h, float* d_out, void* stream);
+
+/* Non-zero when a bounded device-side wait of this handle's kernels gave up
+ * (read from mapped host memory; meaningful after the stream has been
+ * synchronised).  The reference reports such faults through a fault word as
+ * well (plugins/gpt_oss/cuda/tp_peer_owner.cuh:40-46,308-315). */
+int garnet_b200_w4a16_fault(garnet_b200_w4a16_t h);
+
+void garnet_b200_w4a16_destroy(garnet_b200_w4a16_t h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GARNET_B200_H */

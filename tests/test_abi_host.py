@@ -1,0 +1,110 @@
+"""CPU-side checks of the C ABI: the library loads, exports every symbol the
+header declares, validates arguments before touching pointers, and its host
+repacker writes the documented layout (checked by an independent
+inverse-coordinate restatement, in the manner of the reference's
+test2026/gpt_oss/marlin_weight_pack.cpp:54-78)."""
+import ctypes
+import json
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import garnet_b200
+from garnet_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "garnet_b200.h")).read()
+    return sorted(set(re.findall(r"\b(garnet_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported():
+    L = garnet_b200.lib()
+    names = declared_symbols()
+    assert len(names) >= 15
+    for name in names:
+        assert hasattr(L, name), name
+        assert L.garnet_b200_resolve(name.encode()), name
+    assert L.garnet_b200_resolve(b"printf") is None
+
+
+def test_manifest_keys_match_reference_contract():
+    L = garnet_b200.lib()
+    m = json.loads(L.garnet_b200_manifest_json().decode())
+    for key in ("id", "module", "abi", "version", "backend", "operators"):
+        assert key in m
+    assert m["abi"] == L.garnet_b200_abi_version() == 1
+    assert "gpt_oss_moe_mxfp4" in m["operators"] and "lm_head" in m["operators"]
+    assert os.path.exists(L.garnet_b200_binary_path().decode())
+    reg = json.load(open(os.path.join(ROOT, "garnet_b200", "registry.json")))
+    assert reg["plugins"][m["id"]]["module"] == m["module"]
+
+
+def test_invalid_arguments_are_rejected_before_pointer_access():
+    L = garnet_b200.lib()
+    out = ctypes.c_void_p(None)
+    sz = ctypes.c_size_t(0)
+    assert L.garnet_b200_w4a16_create(None, None, 1, 128, 128, 128, 0, 1, None, ctypes.byref(out)) == _lib.INVALID_VALUE
+    assert b"null" in L.garnet_b200_last_error()
+    assert L.garnet_b200_w4a16_packed_bytes(128, 100, 128, ctypes.byref(sz)) == _lib.INVALID_VALUE
+    assert L.garnet_b200_w4a16_packed_bytes(128, 128, 64, ctypes.byref(sz)) == _lib.NOT_SUPPORTED
+    assert L.garnet_b200_w4a16_run(None, None, None, 1, None, 0, 0, None) == _lib.INVALID_VALUE
+    assert L.garnet_b200_w4a16_workspace(None, 1, ctypes.byref(sz)) == _lib.INVALID_VALUE
+    assert L.garnet_b200_int4_quantize(None, 2, 1, 128, 128, 1, None, None, None) == _lib.INVALID_VALUE
+
+
+def row_of_g(g):
+    return (g >> 1) + 4 * (g & 1)
+
+
+def expected_position(n, k, chunks):
+    """Independent statement of the packed int4 layout: byte offset of the word
+    and nibble index that hold element (n, k)."""
+    panel, nl = divmod(n, 128)
+    chunk, kl = divmod(k, 128)
+    tile, kk = divmod(kl, 64)
+    sub, r16 = divmod(nl, 16)
+    h, r8 = divmod(r16, 8)
+    g = next(g for g in range(8) if row_of_g(g) == r8)
+    octet, e = divmod(kk, 8)
+    j, t = divmod(octet, 4)
+    byte = (panel * chunks + chunk) * (8192 + 256) + tile * 4096 + sub * 512 + (4 * g + t) * 16 + (h + 2 * j) * 4
+    return byte, (e >> 1) + 4 * (e & 1)
+
+
+@pytest.mark.parametrize("n,k,group", [(128, 128, 128), (200, 256, 128), (384, 512, 256), (16, 384, 128)])
+def test_host_packer_layout(n, k, group):
+    rng = np.random.default_rng(n + k)
+    codes = rng.integers(-8, 8, size=(n, k)).astype(np.int8)
+    flat = (codes.reshape(-1) & 15).astype(np.uint8)
+    nibbles = (flat[0::2] | (flat[1::2] << 4)).astype(np.uint8)
+    scales = rng.integers(0, 65536, size=(n, k // group)).astype(np.uint16)
+    packed = garnet_b200.pack_host(torch.from_numpy(nibbles), torch.from_numpy(scales.view(np.int16)).view(torch.bfloat16),
+                                   n, k, group).numpy()
+    chunks = k // 128
+    panels = (n + 127) // 128
+    assert packed.size == panels * chunks * (8192 + 256) == garnet_b200.packed_bytes(n, k, group)
+    words = packed.view(np.uint32)
+    for nn in range(0, n, 7):
+        for kk in range(0, k, 5):
+            byte, nib = expected_position(nn, kk, chunks)
+            got = (int(words[byte // 4]) >> (4 * nib)) & 15
+            assert got == (int(codes[nn, kk]) & 15), (nn, kk)
+    # scales: [sub][g][h] 16-bit words after the 8192 code bytes of each chunk
+    for nn in range(0, n, 3):
+        for c in range(chunks):
+            panel, nl = divmod(nn, 128)
+            sub, r16 = divmod(nl, 16)
+            h, r8 = divmod(r16, 8)
+            g = next(g for g in range(8) if row_of_g(g) == r8)
+            off = (panel * chunks + c) * 8448 + 8192 + (sub * 8 + g) * 4 + h * 2
+            assert packed[off:off + 2].view(np.uint16)[0] == scales[nn, (c * 128) // group]
+    # padding rows hold zero codes
+    if n % 128:
+        byte, _ = expected_position(panels * 128 - 1, 0, chunks)
+        assert words[byte // 4] == 0

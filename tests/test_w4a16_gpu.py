@@ -1,0 +1,175 @@
+"""Parity of the int4 linear on the GPU, through the C ABI, against the CPU
+oracle: bit-exact repack and dequantisation, GEMM outputs within 1e-2 in the
+reference's error form |a - e| <= tol * (1 + |e|) (test2026/gpt_oss/kernel_parity.cpp:46-57)
+of the fp64-accumulated exact product (the tolerance the specification names),
+and far tighter in practice (checked too)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import garnet_b200
+import oracle
+from garnet_b200 import synth
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+TOL = 1e-2
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.view(dtype)
+
+
+def bf16_tensor(bits):
+    return dev(bits.view(np.int16), torch.bfloat16)
+
+
+def make_linear(case, n, k, group=128, **kw):
+    lin = garnet_b200.W4A16Linear()
+    scales = bf16_tensor(case["scales_bits"]).reshape(n, k // group)
+    return lin.prepare(dev(case["nibbles"]), scales, n, k, group, **kw)
+
+
+def check_close(y_dev, y64, tol=TOL):
+    y = y_dev.float().cpu().numpy().astype(np.float64)
+    err = np.abs(y - y64)
+    assert np.isfinite(y).all()
+    assert (err <= tol * (1 + np.abs(y64))).all(), float((err / (1 + np.abs(y64))).max())
+    # in practice the result is the correctly rounded bf16 of the exact sum, give or take one ulp
+    ref = oracle.bf16_round(y64.astype(np.float32)).astype(np.float64)
+    ulp = np.maximum(np.abs(ref), 2.0 ** -120) * 2.0 ** -7
+    assert (np.abs(y - ref) <= 1.01 * ulp + 1e-6).all()
+
+
+@pytest.mark.parametrize("n,k,group", [(128, 128, 128), (200, 256, 128), (1024, 2048, 128), (256, 512, 256)])
+def test_device_repack_equals_host_packer_and_dequant_is_bit_exact(n, k, group):
+    case = synth.int4_linear(n, k, 1, group, seed=n + k)
+    lin = make_linear(case, n, k, group)
+    deq = lin.dequantized().cpu().numpy()
+    expect = oracle.int4_dequant(case["nibbles"], case["scales_f32"], n, k, group)
+    assert np.array_equal(deq.view(np.uint32), expect.view(np.uint32))
+    # host-packed bytes, bound without copying, decode to the same matrix
+    packed = garnet_b200.pack_host(torch.from_numpy(case["nibbles"]),
+                                   torch.from_numpy(case["scales_bits"].view(np.int16)).view(torch.bfloat16).reshape(n, -1),
+                                   n, k, group).cuda()
+    view = garnet_b200.W4A16Linear().bind_packed(packed, torch.bfloat16, n, k, group)
+    assert torch.equal(view.dequantized(), lin.dequantized())
+    x = bf16_tensor(case["x_bits"])
+    assert torch.equal(view.forward(x), lin.forward(x))
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 9, 16, 17, 40])
+@pytest.mark.parametrize("n,k", [(256, 256), (200, 512), (2048, 2048), (2048, 6144), (1024, 2048)])
+def test_linear_matches_exact_oracle(n, k, m):
+    case = synth.int4_linear(n, k, m, seed=17 * m + n)
+    lin = make_linear(case, n, k)
+    y = lin.forward(bf16_tensor(case["x_bits"]).reshape(m, k))
+    torch.cuda.synchronize()
+    assert lin.fault() == 0
+    _, y64 = oracle.w4a16_exact(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"])
+    check_close(y, y64)
+
+
+def test_baseline_config_gate_proj_m1():
+    """x[1,2048] ~ N(0,1), W [6144,2048] codes U[-8,7], scales |N(0,.02)|/7, seed 0."""
+    n, k = 6144, 2048
+    case = synth.int4_linear(n, k, 1, seed=0)
+    lin = make_linear(case, n, k)
+    x = bf16_tensor(case["x_bits"]).reshape(1, k)
+    y1 = lin.forward(x)
+    y2 = lin.forward(x)
+    assert torch.equal(y1, y2)          # deterministic: K slices are reduced in a fixed order
+    _, y64 = oracle.w4a16_exact(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"])
+    check_close(y1, y64)
+    # the reference CPU operator (int8 activations) lands within the same bound
+    q4q8 = oracle.q4q8_forward(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"][0])
+    assert (np.abs(q4q8 - y64[0]) <= TOL * (1 + np.abs(y64[0]))).all()
+
+
+def test_lm_head_slice_and_n_sharding():
+    n, k, m = 151936 // 8, 2048, 4    # one eighth of the vocabulary: 18992 rows, not a multiple of 128
+    case = synth.int4_linear(n, k, m, seed=5)
+    x = bf16_tensor(case["x_bits"]).reshape(m, k)
+    full = make_linear(case, n, k).forward(x)
+    y64 = oracle.w4a16_blas(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"])
+    check_close(full, y64)
+    for world in (2, 4):
+        parts = [make_linear(case, n, k, shard_rank=r, shard_world=world).forward(x) for r in range(world)]
+        assert torch.equal(torch.cat(parts, dim=1), full)
+
+
+def test_fp16_scales_are_used_unrounded():
+    n, k = 256, 256
+    case = synth.int4_linear(n, k, 2, seed=3)
+    s16 = (case["scales_f32"] * np.float32(1.0009765625)).astype(np.float16)   # not bf16-representable
+    lin = garnet_b200.W4A16Linear().prepare(dev(case["nibbles"]), dev(s16), n, k)
+    expect = oracle.int4_dequant(case["nibbles"], s16.astype(np.float32), n, k, 128)
+    assert np.array_equal(lin.dequantized().cpu().numpy(), expect)
+    y = lin.forward(bf16_tensor(case["x_bits"]).reshape(2, k))
+    _, y64 = oracle.w4a16_exact(case["nibbles"], s16.astype(np.float32), n, k, 128, case["x_f32"])
+    check_close(y, y64)
+
+
+def test_edge_values():
+    n, k = 128, 256
+    case = synth.int4_linear(n, k, 3, seed=9)
+    x = case["x_f32"].copy()
+    x[0] = 0.0                                   # all-zero row
+    x[1, :] = np.float32(2.0) ** 100              # large magnitudes stay finite in fp32
+    case["scales_f32"][:] = oracle.bf16_round(np.float32(2.0) ** -110 * np.ones_like(case["scales_f32"]))
+    case["scales_bits"] = oracle.bf16_bits(case["scales_f32"])
+    lin = make_linear(case, n, k)
+    y = lin.forward(bf16_tensor(oracle.bf16_bits(x)).reshape(3, k))
+    _, y64 = oracle.w4a16_exact(case["nibbles"], case["scales_f32"], n, k, 128, x)
+    assert (y[0] == 0).all()
+    check_close(y, y64)
+
+
+@pytest.mark.parametrize("scale_dtype,kind", [(torch.bfloat16, "bf16"), (torch.float16, "fp16")])
+@pytest.mark.parametrize("src_dtype", [torch.float32, torch.bfloat16])
+def test_device_quantizer_matches_reference_arithmetic(scale_dtype, kind, src_dtype):
+    rng = np.random.default_rng(11)
+    w = oracle.bf16_round(rng.normal(0, 0.05, size=(96, 512)).astype(np.float32))
+    w[3, :128] = 0.0                              # degenerate group -> scale 1
+    nib, sc = garnet_b200.quantize_int4(dev(w).to(src_dtype), 128, scale_dtype)
+    p, s, _ = oracle.int4_quantize(w, 128, kind)
+    assert np.array_equal(nib.cpu().numpy(), p)
+    assert np.array_equal(sc.cpu().view(torch.int16).numpy().view(np.uint16), s)
+
+
+def test_golden_reference_artifact():
+    """The reference's own quantized artifact and its CPU operator output
+    (tests/golden/int4_ref.npz, produced by the compiled reference sources)."""
+    g = np.load(os.path.join(GOLD, "int4_ref.npz"))
+    n, k = 48, 512
+    s16 = g["rand_scales_fp16"].view(np.float16)
+    lin = garnet_b200.W4A16Linear().prepare(dev(g["rand_packed"]), dev(s16), n, k)
+    x = g["rand_x"]
+    y = lin.forward(bf16_tensor(oracle.bf16_bits(x)).reshape(1, k)).float().cpu().numpy()[0]
+    _, y64 = oracle.w4a16_exact(g["rand_packed"], s16.astype(np.float32), n, k, 128, x)
+    check_close(torch.from_numpy(y)[None], y64)
+    ref_cpu = g["rand_y_q4q8"]                    # Q4Q8Linear with bf16-rounded scales
+    assert (np.abs(y - ref_cpu) <= TOL * (1 + np.abs(ref_cpu))).all()
+
+
+def test_host_buffer_entry_point():
+    n, k, m = 2048, 2048, 5
+    case = synth.int4_linear(n, k, m, seed=21)
+    lin = make_linear(case, n, k)
+    xh = torch.from_numpy(case["x_bits"].view(np.int16)).view(torch.bfloat16).reshape(m, k).pin_memory()
+    yh = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+    lin.forward_host(xh, yh)
+    assert torch.equal(yh, lin.forward(xh.cuda()).cpu())
+
+
+def test_run_rejects_bad_arguments():
+    case = synth.int4_linear(128, 128, 1, seed=1)
+    lin = make_linear(case, 128, 128)
+    x = bf16_tensor(case["x_bits"])
+    with pytest.raises(garnet_b200.GarnetB200Error):
+        lin.forward(x, workspace=torch.empty(0, dtype=torch.uint8, device="cuda")) if lin.workspace_bytes(1) else (_ for _ in ()).throw(garnet_b200.GarnetB200Error(1, "no workspace needed"))
+    with pytest.raises(garnet_b200.GarnetB200Error):
+        garnet_b200.W4A16Linear().prepare(dev(case["nibbles"]), bf16_tensor(case["scales_bits"]), 128, 128, 64)
