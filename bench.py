@@ -1,0 +1,411 @@
+"""Benchmark of the quantized-matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): the W4A16 shape sweep over every Qwen3-1.7B projection.  One
+step = one decode pass (batch M = 1) over the full random-init weight set: 28
+layers x {q,k,v,o,gate,up,down}_proj + lm_head = 197 int4 linears, 887 MB of
+packed weights, i.e. several times the 126 MB L2, so every weight byte of a step
+comes from HBM.  `value` is algorithmic bytes / step time with activations
+resident in HBM; `e2e` is the same pass through the host-buffer entry point
+(pinned host x -> device, kernel, device -> host y, per linear).  `sweep` holds
+the per-shape, per-batch (M in 1,4,16,64,256) numbers measured on rotating weight
+copies larger than twice the L2.  With N > 1 the lm_head is sharded along N
+across the ranks and the logits are all-gathered over NVLink; the decoder
+layers are replicated (the configuration's definition), so scaling is strong.
+
+--impl reference times the reference's own CPU operator (Q4Q8Linear compiled
+from the reference sources when available, otherwise its restatement) on the
+host cores for the same metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+GROUP = 128
+LAYERS = 28
+PROJ = [("q_proj", 2048, 2048), ("k_proj", 2048, 1024), ("v_proj", 2048, 1024), ("o_proj", 2048, 2048),
+        ("gate_proj", 2048, 6144), ("up_proj", 2048, 6144), ("down_proj", 6144, 2048)]
+LM_HEAD = ("lm_head", 2048, 151936)
+SWEEP_M = [1, 4, 16, 64, 256]
+
+
+def weight_bytes(k, n):
+    return n * k // 2 + n * (k // GROUP) * 2
+
+
+def algo_bytes(k, n, m):
+    return weight_bytes(k, n) + m * k * 2 + m * n * 2
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm=float(d["hbm_gbs"]), tf=float(d["bf16_tflops"]), tf_sus=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), src="measured")
+    return dict(hbm=6650.0, tf=1590.0, tf_sus=1400.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ GPU arm
+
+def make_linear(torch, gb, k, n, gen, shard=(0, 1)):
+    nib = torch.randint(0, 256, (n * k // 2,), dtype=torch.uint8, device="cuda", generator=gen)
+    sc = (torch.randn(n, k // GROUP, device="cuda", generator=gen).abs() * (0.02 / 7.0)).to(torch.bfloat16)
+    lin = gb.W4A16Linear().prepare(nib, sc, n, k, GROUP, shard_rank=shard[0], shard_world=shard[1])
+    del nib, sc
+    return lin
+
+
+def time_graph(torch, fn, steps, warmup, flush=None):
+    """Captures fn() once into a CUDA graph and times `steps` replays with CUDA
+    events on the launching stream (after `warmup` replays)."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        fn()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            fn()
+        for _ in range(warmup):
+            graph.replay()
+        stream.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        stop.record(stream)
+        stream.synchronize()
+    return start.elapsed_time(stop) / steps   # ms per replay
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    import garnet_b200 as gb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks = measured_peaks()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234 + rank)
+
+    # ---- the decode pass: 28 layers + lm_head (sharded along N when world > 1)
+    m = 1
+    layers = []
+    for _ in range(LAYERS):
+        layers.append([(make_linear(torch, gb, k, n, gen), k, n) for (_, k, n) in PROJ])
+    _, hk, hn = LM_HEAD
+    head = make_linear(torch, gb, hk, hn, gen, shard=(rank, world))
+    hn_local = hn // world
+    xs = {k: torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16) for k in (2048, 6144)}
+    ys = {n: torch.empty(m, n, device="cuda", dtype=torch.bfloat16) for n in (1024, 2048, 6144)}
+    y_head = torch.empty(m, hn_local, device="cuda", dtype=torch.bfloat16)
+    logits = torch.empty(world, m, hn_local, device="cuda", dtype=torch.bfloat16) if world > 1 else None
+    ws_bytes = max([lin.workspace_bytes(m) for layer in layers for (lin, _, _) in layer] + [head.workspace_bytes(m)])
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
+    launches_per_step = LAYERS * len(PROJ) + 1
+
+    def decode_pass():
+        for layer in layers:
+            for lin, k, n in layer:
+                lin.forward(xs[k], out=ys[n], workspace=ws)
+        head.forward(xs[hk], out=y_head, workspace=ws)
+        if world > 1:
+            dist.all_gather_into_tensor(logits.view(-1), y_head.view(-1))
+
+    step_bytes = LAYERS * sum(algo_bytes(k, n, m) for (_, k, n) in PROJ) + algo_bytes(hk, hn, m)
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = time_graph(torch, decode_pass, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = step_bytes / (ms * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer entry point
+    xh = {k: v.cpu().pin_memory() for k, v in xs.items()}
+    yh = {n: torch.empty(m, n, dtype=torch.bfloat16).pin_memory() for n in (1024, 2048, 6144)}
+    yh_head = torch.empty(m, hn_local, dtype=torch.bfloat16).pin_memory()
+
+    def host_pass():
+        for layer in layers:
+            for lin, k, n in layer:
+                lin.forward_host(xh[k], yh[n])
+        head.forward_host(xh[hk], yh_head)
+        if world > 1:
+            y_head.copy_(yh_head, non_blocking=True)
+            dist.all_gather_into_tensor(logits.view(-1), y_head.view(-1))
+            torch.cuda.current_stream().synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        host_pass()
+    e2e_steps = max(3, min(args.steps, 10))
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        host_pass()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+    if world > 1:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    h2d = LAYERS * sum(m * k * 2 for (_, k, n) in PROJ) + m * hk * 2
+    d2h = LAYERS * sum(m * n * 2 for (_, k, n) in PROJ) + m * hn_local * 2
+
+    out = None
+    if rank == 0:
+        out = {
+            "metric": "w4a16_weight_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16 x int4 -> fp32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": "qwen3_1p7b_w4a16_sweep: decode pass M=1 over 28x7 projections + lm_head (197 int4 group-128 linears)",
+                       "bytes_per_step": step_bytes, "l2": "887 MB of weights per step > 126 MB L2; no flush needed",
+                       "parallelism": f"lm_head N-sharded x{world} + all-gather" if world > 1 else "single GPU",
+                       "launch": "one CUDA graph of 197 programmatic-dependent launches"},
+            "clocks": clocks,
+            "e2e": {"value": round(step_bytes / (e2e_ms * 1e-3) / 1e9, 3), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "achieved": round(value, 2), "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": round(value / peaks["hbm"], 4), "peak_source": peaks["src"], "traffic": None,
+                         "kernel": "w4a16_stream_kernel<1>", "bytes_per_launch": round(step_bytes / launches_per_step),
+                         "us_per_launch": round(ms * 1e3 / launches_per_step, 3)},
+        }
+
+    # ---- per-shape sweep on rotating copies (single GPU only)
+    if world == 1 and not args.no_sweep:
+        del layers, head
+        torch.cuda.empty_cache()
+        sweep = []
+        shapes = [("q_proj/o_proj", 2048, 2048), ("k_proj/v_proj", 2048, 1024), ("gate_proj/up_proj", 2048, 6144),
+                  ("down_proj", 6144, 2048), ("lm_head", 2048, 151936)]
+        for name, k, n in shapes:
+            copies = max(2, int(np.ceil(2.2 * 126e6 / weight_bytes(k, n))))
+            lins = [make_linear(torch, gb, k, n, gen) for _ in range(copies)]
+            for mm in SWEEP_M:
+                x = torch.randn(mm, k, device="cuda", generator=gen).to(torch.bfloat16)
+                y = torch.empty(mm, n, device="cuda", dtype=torch.bfloat16)
+                w = torch.empty(max(16, lins[0].workspace_bytes(mm)), dtype=torch.uint8, device="cuda")
+
+                def body():
+                    for lin in lins:
+                        lin.forward(x, out=y, workspace=w)
+
+                t_ms = time_graph(torch, body, max(3, args.steps // 4), 3) / copies
+                gbs = algo_bytes(k, n, mm) / (t_ms * 1e-3) / 1e9
+                tfl = 2.0 * mm * n * k / (t_ms * 1e-3) / 1e12
+                sweep.append({"shape": name, "K": k, "N": n, "M": mm, "us": round(t_ms * 1e3, 3), "GBps": round(gbs, 1),
+                              "hbm_frac": round(gbs / peaks["hbm"], 4), "TFLOPs": round(tfl, 2),
+                              "tensor_frac": round(tfl / peaks["tf"], 4), "copies": copies})
+            del lins
+            torch.cuda.empty_cache()
+        out["sweep"] = sweep
+
+    if rank == 0:
+        if world == 1:
+            out["cpu_baseline"] = cpu_baseline(sample_seconds=12.0)
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------- CPU baseline
+
+def cpu_linears():
+    """One layer's seven projections plus the lm_head, as CPU operators.  Uses the
+    reference's own compiled operator when oracle/_ref is present, else the
+    restatement in oracle/oracle.c."""
+    import oracle
+    import oracle.ref as ref
+    rng = np.random.default_rng(0)
+    threads = min(16, os.cpu_count() or 1)      # the reference's pool is capped at 16 threads
+    kind = "reference" if ref.available() else "port"
+    ops = []
+    for name, k, n in PROJ + [LM_HEAD]:
+        nib = rng.integers(0, 256, size=n * k // 2, dtype=np.uint8)
+        sc = (np.abs(rng.normal(0, 0.02, size=(n, k // GROUP))) / 7.0).astype(np.float32)
+        x = rng.normal(0, 1, size=k).astype(np.float32)
+        if kind == "reference":
+            op = ref.Q4Q8Linear(nib, sc, n, k, GROUP)
+            y = np.empty(n, np.float32)
+            ops.append((name, k, n, (lambda op=op, x=x, y=y: op.forward(x, threads, out=y))))
+        else:
+            ops.append((name, k, n, (lambda nib=nib, sc=sc, n=n, k=k, x=x: oracle.q4q8_forward(nib, sc, n, k, GROUP, x, threads))))
+    return ops, kind, threads
+
+
+def cpu_baseline(sample_seconds=12.0):
+    ops, kind, threads = cpu_linears()
+    bytes_pass = sum(algo_bytes(k, n, 1) for (_, k, n, _) in ops)
+    for (_, _, _, fn) in ops:
+        fn()
+    t0 = time.perf_counter()
+    passes = 0
+    while time.perf_counter() - t0 < sample_seconds or passes < 3:
+        for (_, _, _, fn) in ops:
+            fn()
+        passes += 1
+    dt = time.perf_counter() - t0
+    return {"value": round(bytes_pass * passes / dt / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": f"{passes} passes over one layer's 7 projections + lm_head at M=1 ({bytes_pass} B each), "
+                      f"Q4Q8Linear::Forward (int8 activations), {dt:.1f} s"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ops, kind, threads = cpu_linears()
+    bytes_pass = sum(algo_bytes(k, n, 1) for (_, k, n, _) in ops)
+    for _ in range(max(1, args.warmup)):
+        for (_, _, _, fn) in ops:
+            fn()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for (_, _, _, fn) in ops:
+            fn()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = bytes_pass / dt / 1e9
+    sample = (f"each step = one layer's 7 projections + lm_head at M=1 ({bytes_pass} B of the 887 MB pass), "
+              f"Q4Q8Linear::Forward on host cores")
+    print(json.dumps({
+        "impl": "reference", "metric": "w4a16_weight_GBps", "value": round(value, 3), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4 -> int32 (W4A8)",
+        "data": "synthetic",
+        "config": {"workload": "qwen3_1p7b_w4a16_sweep: decode pass M=1 (bounded sample: one layer + lm_head per step)"},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def run_profile_case(spec):
+    """Small fixed case for profiler captures: `w4a16:K:N:M` runs one linear a few
+    times without a graph (3 warm-up launches, 3 measured ones) and prints the
+    CUDA-event time per launch."""
+    import torch
+
+    import garnet_b200 as gb
+
+    kind, k, n, m = spec.split(":")
+    k, n, m = int(k), int(n), int(m)
+    assert kind == "w4a16"
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0)
+    lins = [make_linear(torch, gb, k, n, gen) for _ in range(2)]
+    x = torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16)
+    y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    for i in range(3):
+        lins[i % 2].forward(x, out=y)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(3):
+        lins[i % 2].forward(x, out=y)
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) / 3 * 1e3
+    print(json.dumps({"case": spec, "us_per_launch": round(us, 3),
+                      "GBps": round(algo_bytes(k, n, m) / us / 1e3, 1)}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--profile", default=None, help="w4a16:K:N:M - run one small case for a profiler capture")
+    args = ap.parse_args()
+    if args.profile:
+        run_profile_case(args.profile)
+        return
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

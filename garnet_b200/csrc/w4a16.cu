@@ -24,17 +24,16 @@ __global__ void w4_repack_codes_kernel(const uint8_t* __restrict__ src, uint8_t*
                                        long long src_row0)
 {
     const size_t words_per_chunk = geo.chunk_data / 4;
-    const size_t total = size_t(geo.panels) * geo.chunks * words_per_chunk;
+    const size_t total = size_t(geo.strips_padded) * geo.chunks * words_per_chunk;
     const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t chunk_lin = idx / words_per_chunk;
     const int w = int(idx % words_per_chunk);
-    const int panel = int(chunk_lin / geo.chunks), chunk = int(chunk_lin % geo.chunks);
+    const int strip = int(chunk_lin / geo.chunks), chunk = int(chunk_lin % geo.chunks);
     // invert locate(): word index -> (row, first column)
-    const int tile = w >> 10, wt = w & 1023;          // 1024 words per 4 KiB tile
-    const int sub = wt >> 7, unit = (wt >> 2) & 31, word = wt & 3;
+    const int tile = w >> 7, unit = (w >> 2) & 31, word = w & 3;      // 128 words per 512-byte tile
     const int g = unit >> 2, t = unit & 3, h = word & 1, j = word >> 1;
-    const int n = panel * 128 + sub * 16 + row_of_g(g) + 8 * h;
+    const int n = strip * 16 + row_of_g(g) + 8 * h;
     const int k0 = chunk * geo.chunk_k + tile * 64 + (t + 4 * j) * 8;
     uint32_t out = 0;
     if (n < geo.rows && k0 < geo.cols) {
@@ -48,7 +47,7 @@ __global__ void w4_repack_codes_kernel(const uint8_t* __restrict__ src, uint8_t*
             out = in;
         }
     }
-    const size_t ob = size_t(panel) * geo.panel_bytes() + size_t(chunk) * geo.chunk_bytes + size_t(w) * 4;
+    const size_t ob = (size_t(strip) * geo.chunks + chunk) * geo.chunk_bytes + size_t(w) * 4;
     *reinterpret_cast<uint32_t*>(dst + ob) = out;
 }
 
@@ -58,7 +57,7 @@ __global__ void w4_repack_codes_kernel(const uint8_t* __restrict__ src, uint8_t*
 __global__ void w4_repack_scales_int4_kernel(const uint16_t* __restrict__ src, uint8_t* __restrict__ dst,
                                              PackGeom geo, long long src_row0)
 {
-    const size_t total = size_t(geo.panels) * 128 * geo.chunks;
+    const size_t total = size_t(geo.strips_padded) * 16 * geo.chunks;
     const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const int n = int(idx / geo.chunks), chunk = int(idx % geo.chunks);
@@ -157,24 +156,21 @@ __global__ void int4_quantize_kernel(const T* __restrict__ src, long long rows, 
 
 // ------------------------------------------------------- streaming kernel
 
-constexpr int kGemvStages = 6;
-constexpr int kGemvConsumerWarps = 8;
-constexpr int kGemvThreads = (kGemvConsumerWarps + 1) * 32;
-constexpr int kInt4ChunkBytes = 8192 + 256;
+constexpr int kStreamStages = 3;            // segment buffers in flight per CTA
+constexpr int kStreamWarps = 8;             // consumer warps; one extra warp produces
+constexpr int kStreamThreads = (kStreamWarps + 1) * 32;
+constexpr int kSegChunks = 2 * kStreamWarps;   // chunks per segment: two per consumer warp
+constexpr int kInt4ChunkBytes = 1024 + 32;
 
-struct GemvParams {
+struct StreamParams {
     const uint8_t* packed;
     const __nv_bfloat16* x;
     __nv_bfloat16* y;
-    float* partial;      // [gk][m][padded rows] fp32, only when gk > 1
-    int* counters;       // [panels], self-resetting, only when gk > 1
     int* fault;          // mapped host word; non-zero = a bounded wait gave up
     int m, n, k;         // batch rows, logical weight rows, logical K
     int ldy;             // row stride of y in elements
-    int panels, chunks, gk;
-    int kspan_max;       // K columns per CTA, upper bound (sizes the x tile)
+    int strips, chunks;  // real strips (ceil(n/16)) and chunks per strip
     int scale_dtype;     // GARNET_B200_FP16 / GARNET_B200_BF16
-    size_t panel_bytes;
 };
 
 __device__ __forceinline__ void named_barrier_sync(int id, int threads)
@@ -182,68 +178,76 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads)
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// CTA = 8 consumer warps (one 16-row sub-tile each) + 1 producer warp.  The
-// producer streams the panel's chunks (codes + scales, 8448 bytes each) through a
-// ring of bulk copies; consumers expand int4 -> bf16 in registers and feed
-// m16n8k16 MMAs whose N dimension is the (padded) batch.
+// Persistent CTAs; each owns a contiguous range of 16-row strips.  A strip is one
+// linear byte range of the packed matrix; the producer warp streams it in
+// segments of up to 16 chunks (16.5 KiB) through a ring of bulk copies.  The 8
+// consumer warps split each segment along K (two chunks each), expand int4 ->
+// bf16 in registers and feed m16n8k16 MMAs whose N dimension is the (padded)
+// batch; at the end of a strip their partial sums meet in shared memory.  No
+// global scratch, no atomics: the summation order is fixed.
 template <int MB>
-__global__ void __launch_bounds__(kGemvThreads) w4a16_stream_kernel(const GemvParams p)
+__global__ void __launch_bounds__(kStreamThreads) w4a16_stream_kernel(const StreamParams p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* stages = smem;                                               // kGemvStages * chunk
-    uint8_t* xs = smem + kGemvStages * kInt4ChunkBytes;                   // x tile, padded rows
-    const int x_stride = p.kspan_max * 2 + 64;                            // bytes; 64 mod 128 => conflict-free
-    uint64_t* full = reinterpret_cast<uint64_t*>(xs + size_t(8 * MB) * x_stride);
-    uint64_t* empty = full + kGemvStages;
-    __shared__ int s_last;
+    constexpr int kSegBytes = kSegChunks * kInt4ChunkBytes;
+    uint8_t* ring = smem;                                                 // kStreamStages * kSegBytes
+    float* red = reinterpret_cast<float*>(smem + kStreamStages * kSegBytes);   // [2][warps][MB*4][32]
+    uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * kStreamWarps * MB * 128);
+    uint64_t* empty = full + kStreamStages;
+    uint8_t* xs = reinterpret_cast<uint8_t*>(empty + kStreamStages) + 16;      // x tile, 8*MB padded rows
+    xs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(xs) + 127) & ~uintptr_t(127));
+    const int x_stride = p.k * 2 + 64;                                    // bytes; 64 mod 128 => conflict-free
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int panel = blockIdx.x / p.gk, ks = blockIdx.x % p.gk;
-    const int c0 = int((long long)ks * p.chunks / p.gk), c1 = int((long long)(ks + 1) * p.chunks / p.gk);
-    const int nchunks = c1 - c0;
-    const uint8_t* src = p.packed + size_t(panel) * p.panel_bytes + size_t(c0) * kInt4ChunkBytes;
+    const int s0 = int((long long)blockIdx.x * p.strips / gridDim.x);
+    const int s1 = int((long long)(blockIdx.x + 1) * p.strips / gridDim.x);
+    const int nseg = (p.chunks + kSegChunks - 1) / kSegChunks;
+    const int items = (s1 - s0) * nseg;
+    const size_t strip_bytes = size_t(p.chunks) * kInt4ChunkBytes;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kGemvStages; ++s) {
+        for (int s = 0; s < kStreamStages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kGemvConsumerWarps);
+            mbar_init(&empty[s], kStreamWarps);
         }
         fence_barrier_init();
     }
     __syncthreads();
     pdl_launch_dependents();
 
-    if (warp == kGemvConsumerWarps) {
+    if (warp == kStreamWarps) {
         // ---- producer: weights are constants, so streaming starts before the
         // previous kernel in the stream has finished.
         if (lane == 0) {
-            for (int i = 0; i < nchunks; ++i) {
-                const int s = i % kGemvStages;
-                if (i >= kGemvStages && !mbar_wait(&empty[s], ((i / kGemvStages) - 1) & 1)) {
+            for (int i = 0; i < items; ++i) {
+                const int s = i % kStreamStages;
+                if (i >= kStreamStages && !mbar_wait(&empty[s], ((i / kStreamStages) - 1) & 1)) {
                     atomicExch(p.fault, 1);
                     break;
                 }
-                mbar_expect_tx(&full[s], kInt4ChunkBytes);
-                bulk_g2s(stages + size_t(s) * kInt4ChunkBytes, src + size_t(i) * kInt4ChunkBytes, kInt4ChunkBytes,
-                         &full[s]);
+                const int strip = s0 + i / nseg, seg = i % nseg;
+                const int nch = min(kSegChunks, p.chunks - seg * kSegChunks);
+                const uint32_t bytes = uint32_t(nch) * kInt4ChunkBytes;
+                mbar_expect_tx(&full[s], bytes);
+                bulk_g2s(ring + size_t(s) * kSegBytes,
+                         p.packed + size_t(strip) * strip_bytes + size_t(seg) * kSegBytes, bytes, &full[s]);
             }
         }
         return;
     }
 
     // ---- consumers
-    pdl_wait();   // x is produced by the previous kernel; y / partial may still be read by it
+    pdl_wait();   // x is produced by the previous kernel; y may still be read by it
     {
-        const int kbeg = c0 * 128, kspan = nchunks * 128;
-        const int vec_per_row = kspan / 8;
-        for (int i = threadIdx.x; i < 8 * MB * vec_per_row; i += kGemvConsumerWarps * 32) {
+        const int vec_per_row = p.k / 8;
+        for (int i = threadIdx.x; i < 8 * MB * vec_per_row; i += kStreamWarps * 32) {
             const int m = i / vec_per_row, v = i % vec_per_row;
             uint4 val = make_uint4(0, 0, 0, 0);
-            if (m < p.m) val = *reinterpret_cast<const uint4*>(p.x + size_t(m) * p.k + kbeg + v * 8);
+            if (m < p.m) val = *reinterpret_cast<const uint4*>(p.x + size_t(m) * p.k + v * 8);
             *reinterpret_cast<uint4*>(xs + size_t(m) * x_stride + v * 16) = val;
         }
     }
-    named_barrier_sync(1, kGemvConsumerWarps * 32);
+    named_barrier_sync(1, kStreamWarps * 32);
 
     const int g = lane >> 2, t = lane & 3;
     float acc[MB][4];
@@ -254,179 +258,150 @@ __global__ void __launch_bounds__(kGemvThreads) w4a16_stream_kernel(const GemvPa
     const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
 
     bool ok = true;
-    for (int i = 0; i < nchunks && ok; ++i) {
-        const int s = i % kGemvStages;
-        if (!mbar_wait(&full[s], (i / kGemvStages) & 1)) {
+    for (int i = 0; i < items; ++i) {
+        const int s = i % kStreamStages;
+        const int strip = s0 + i / nseg, seg = i % nseg;
+        if (ok && !mbar_wait(&full[s], (i / kStreamStages) & 1)) {
             atomicExch(p.fault, 2);
             ok = false;
-            break;
         }
-        const uint8_t* st = stages + size_t(s) * kInt4ChunkBytes;
-        const uint32_t sc = *reinterpret_cast<const uint32_t*>(st + 8192 + (warp * 8 + g) * 4);
-        const float s_lo = scale16_to_float(sc & 0xffffu, p.scale_dtype), s_hi = scale16_to_float(sc >> 16, p.scale_dtype);
-        float tmp[MB][4];
+        const int nch = min(kSegChunks, p.chunks - seg * kSegChunks);
+        if (ok) {
 #pragma unroll
-        for (int tile = 0; tile < 2; ++tile) {
-            const uint4 u = *reinterpret_cast<const uint4*>(st + tile * 4096 + warp * 512 + lane * 16);
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = 2 * warp + cc;
+                if (c >= nch) break;
+                const uint8_t* st = ring + size_t(s) * kSegBytes + size_t(c) * kInt4ChunkBytes;
+                const uint32_t sc = *reinterpret_cast<const uint32_t*>(st + 1024 + g * 4);
+                const float s_lo = scale16_to_float(sc & 0xffffu, p.scale_dtype);
+                const float s_hi = scale16_to_float(sc >> 16, p.scale_dtype);
+                const int kchunk = (seg * kSegChunks + c) * 128;
+                float tmp[MB][4];
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const uint32_t wlo = half ? u.z : u.x, whi = half ? u.w : u.y;
-                const int kloc = i * 128 + tile * 64 + (t + 4 * half) * 8;
-                uint32_t a0[4] = {int4x2_to_bf16x2(wlo), int4x2_to_bf16x2(whi), int4x2_to_bf16x2(wlo >> 4),
-                                  int4x2_to_bf16x2(whi >> 4)};
-                uint32_t a1[4] = {int4x2_to_bf16x2(wlo >> 8), int4x2_to_bf16x2(whi >> 8),
-                                  int4x2_to_bf16x2(wlo >> 12), int4x2_to_bf16x2(whi >> 12)};
+                for (int tile = 0; tile < 2; ++tile) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(st + tile * 512 + lane * 16);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const uint32_t wlo = half ? u.z : u.x, whi = half ? u.w : u.y;
+                        const int kloc = kchunk + tile * 64 + (t + 4 * half) * 8;
+                        const uint32_t a0[4] = {int4x2_to_bf16x2(wlo), int4x2_to_bf16x2(whi),
+                                                int4x2_to_bf16x2(wlo >> 4), int4x2_to_bf16x2(whi >> 4)};
+                        const uint32_t a1[4] = {int4x2_to_bf16x2(wlo >> 8), int4x2_to_bf16x2(whi >> 8),
+                                                int4x2_to_bf16x2(wlo >> 12), int4x2_to_bf16x2(whi >> 12)};
+#pragma unroll
+                        for (int mb = 0; mb < MB; ++mb) {
+                            const uint4 xb = *reinterpret_cast<const uint4*>(xs + size_t(mb * 8 + g) * x_stride +
+                                                                             size_t(kloc) * 2);
+                            if (tile == 0 && half == 0)
+                                mma_bf16_16816(tmp[mb], a0, xb.x, xb.y, zero4);
+                            else
+                                mma_bf16_16816(tmp[mb], a0, xb.x, xb.y, tmp[mb]);
+                            mma_bf16_16816(tmp[mb], a1, xb.z, xb.w, tmp[mb]);
+                        }
+                    }
+                }
 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb) {
-                    const uint4 xb =
-                        *reinterpret_cast<const uint4*>(xs + size_t(mb * 8 + g) * x_stride + size_t(kloc) * 2);
-                    if (tile == 0 && half == 0)
-                        mma_bf16_16816(tmp[mb], a0, xb.x, xb.y, zero4);
-                    else
-                        mma_bf16_16816(tmp[mb], a0, xb.x, xb.y, tmp[mb]);
-                    mma_bf16_16816(tmp[mb], a1, xb.z, xb.w, tmp[mb]);
+                    acc[mb][0] = fmaf(tmp[mb][0], s_lo, acc[mb][0]);
+                    acc[mb][1] = fmaf(tmp[mb][1], s_lo, acc[mb][1]);
+                    acc[mb][2] = fmaf(tmp[mb][2], s_hi, acc[mb][2]);
+                    acc[mb][3] = fmaf(tmp[mb][3], s_hi, acc[mb][3]);
                 }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
-#pragma unroll
-        for (int mb = 0; mb < MB; ++mb) {
-            acc[mb][0] = fmaf(tmp[mb][0], s_lo, acc[mb][0]);
-            acc[mb][1] = fmaf(tmp[mb][1], s_lo, acc[mb][1]);
-            acc[mb][2] = fmaf(tmp[mb][2], s_hi, acc[mb][2]);
-            acc[mb][3] = fmaf(tmp[mb][3], s_hi, acc[mb][3]);
-        }
-    }
+        if (seg != nseg - 1) continue;
 
-    if (!ok) {
-        // A wait gave up: give the copies still in flight a bounded chance to land
-        // before this CTA's shared memory is released.
-        for (int i = 0; i < nchunks; ++i) (void)mbar_wait(&full[i % kGemvStages], (i / kGemvStages) & 1);
-    }
-
-    // ---- epilogue.  acc[mb][0..1]: row R(g), batch columns 2t, 2t+1; [2..3]: row R(g)+8.
-    const int n_lo = panel * 128 + warp * 16 + row_of_g(g);
-    if (p.gk == 1) {
+        // ---- end of a strip: the 8 warps' partial sums meet in shared memory.
+        // acc[mb][0..1]: row R(g), batch columns 2t, 2t+1; [2..3]: row R(g)+8.
+        float* slot = red + size_t((strip - s0) & 1) * (kStreamWarps * MB * 128);
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int m = mb * 8 + 2 * t + (i & 1), n = n_lo + 8 * (i >> 1);
-                if (m < p.m && n < p.n) p.y[size_t(m) * p.ldy + n] = __float2bfloat16_rn(acc[mb][i]);
+            for (int q = 0; q < 4; ++q) {
+                slot[(warp * MB * 4 + mb * 4 + q) * 32 + lane] = acc[mb][q];
+                acc[mb][q] = 0.f;
             }
-        return;
-    }
-    const int np = p.panels * 128;
+        named_barrier_sync(1, kStreamWarps * 32);
+        for (int idx = threadIdx.x; idx < MB * 128; idx += kStreamWarps * 32) {
+            const int l = idx & 31, q = (idx >> 5) & 3, mb = idx >> 7;
+            float v = 0.f;
 #pragma unroll
-    for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int m = mb * 8 + 2 * t + (i & 1), n = n_lo + 8 * (i >> 1);
-            if (m < p.m) p.partial[(size_t(ks) * p.m + m) * np + n] = acc[mb][i];
+            for (int w = 0; w < kStreamWarps; ++w) v += slot[(w * MB * 4 + mb * 4 + q) * 32 + l];
+            const int m = mb * 8 + 2 * (l & 3) + (q & 1);
+            const int n = strip * 16 + row_of_g(l >> 2) + 8 * (q >> 1);
+            if (m < p.m && n < p.n) p.y[size_t(m) * p.ldy + n] = __float2bfloat16_rn(v);
         }
-    __threadfence();
-    named_barrier_sync(1, kGemvConsumerWarps * 32);
-    if (threadIdx.x == 0) {
-        const int old = atomicAdd(&p.counters[panel], 1);
-        s_last = (old == p.gk - 1);
-        if (s_last) p.counters[panel] = 0;   // ready for the next call on this handle
     }
-    named_barrier_sync(1, kGemvConsumerWarps * 32);
-    if (!s_last) return;
-    __threadfence();
-    // The last CTA of the panel adds the slices in slice order: the result does
-    // not depend on which CTA finished last.
-    for (int i = threadIdx.x; i < p.m * 128; i += kGemvConsumerWarps * 32) {
-        const int m = i >> 7, n = panel * 128 + (i & 127);
-        if (n >= p.n) continue;
-        float v = 0.f;
-        for (int q = 0; q < p.gk; ++q) v += __ldcg(&p.partial[(size_t(q) * p.m + m) * np + n]);
-        p.y[size_t(m) * p.ldy + n] = __float2bfloat16_rn(v);
+    if (!ok) {
+        // A wait gave up: give the copies still in flight a bounded chance to land
+        // before this CTA's shared memory is released.
+        for (int i = 0; i < min(items, kStreamStages); ++i) (void)mbar_wait(&full[i], 0);
     }
 }
 
 // ------------------------------------------------------------------ handle
 
-static int pick_split(const PackGeom& geo)
+static size_t stream_smem_bytes(int mb, int k)
 {
-    // Enough CTAs to cover the machine about twice, never more K columns per CTA
-    // than the x tile can hold, never less than one chunk.
-    const int min_gk = (geo.chunks * 128 + kW4MaxKSpan - 1) / kW4MaxKSpan;
-    int gk = (2 * kSmCount + geo.panels - 1) / geo.panels;
-    gk = std::max(gk, min_gk);
-    gk = std::min(gk, geo.chunks);
-    return std::max(gk, 1);
+    return size_t(kStreamStages) * kSegChunks * kInt4ChunkBytes + size_t(2) * kStreamWarps * mb * 128 * sizeof(float) +
+           2 * kStreamStages * sizeof(uint64_t) + 16 + 128 + size_t(8 * mb) * (size_t(k) * 2 + 64);
 }
 
-static size_t gemv_smem_bytes(int mb, int kspan_max)
-{
-    return size_t(kGemvStages) * kInt4ChunkBytes + size_t(8 * mb) * (size_t(kspan_max) * 2 + 64) +
-           2 * kGemvStages * sizeof(uint64_t);
-}
+constexpr size_t kMaxDynamicSmem = 227 * 1024;
 
 int W4A16::init_common()
 {
-    gk = pick_split(geo);
-    kspan_max = ((geo.chunks + gk - 1) / gk) * 128;
     GB_CUDA(cudaGetDevice(&device));
-    GB_CUDA(cudaMalloc(&counters, sizeof(int) * size_t(geo.panels)));
-    GB_CUDA(cudaMemset(counters, 0, sizeof(int) * size_t(geo.panels)));
     GB_CUDA(cudaHostAlloc(&fault_host, sizeof(int), cudaHostAllocMapped));
     *fault_host = 0;
     GB_CUDA(cudaHostGetDevicePointer(&fault_dev, fault_host, 0));
+    if (stream_smem_bytes(1, geo.cols) > kMaxDynamicSmem)
+        return fail(GARNET_B200_NOT_SUPPORTED, "w4a16: k=%d is too large for the streaming kernel", geo.cols);
+    max_rows_per_launch = stream_smem_bytes(2, geo.cols) <= kMaxDynamicSmem ? 16 : 8;
+    // The attribute is per kernel and per device, not per handle: always ask for the maximum.
     GB_CUDA(cudaFuncSetAttribute(w4a16_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(gemv_smem_bytes(1, kW4MaxKSpan))));
+                                 int(kMaxDynamicSmem)));
     GB_CUDA(cudaFuncSetAttribute(w4a16_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(gemv_smem_bytes(2, kW4MaxKSpan))));
+                                 int(kMaxDynamicSmem)));
     return GARNET_B200_OK;
 }
 
 W4A16::~W4A16()
 {
     if (owns_packed && packed) cudaFree(packed);
-    if (counters) cudaFree(counters);
     if (fault_host) cudaFreeHost(fault_host);
     if (stage_x) cudaFree(stage_x);
     if (stage_y) cudaFree(stage_y);
     if (stage_ws) cudaFree(stage_ws);
-    if (pin_x) cudaFreeHost(pin_x);
-    if (pin_y) cudaFreeHost(pin_y);
 }
 
-size_t W4A16::workspace_bytes(int m) const
-{
-    if (gk <= 1) return 0;
-    const int rows = std::min(m, 16);
-    return size_t(gk) * rows * geo.padded_rows() * sizeof(float);
-}
+size_t W4A16::workspace_bytes(int) const { return 0; }
 
-int W4A16::launch_stream(const __nv_bfloat16* x, __nv_bfloat16* y, int m, int ldy, void* ws, unsigned flags,
+int W4A16::launch_stream(const __nv_bfloat16* x, __nv_bfloat16* y, int m, int ldy, unsigned flags,
                          cudaStream_t stream)
 {
-    GemvParams p;
+    StreamParams p;
     p.packed = packed;
     p.x = x;
     p.y = y;
-    p.partial = static_cast<float*>(ws);
-    p.counters = counters;
     p.fault = fault_dev;
     p.m = m;
     p.n = geo.rows;
     p.k = geo.cols;
     p.ldy = ldy;
-    p.panels = geo.panels;
+    p.strips = geo.strips;
     p.chunks = geo.chunks;
-    p.gk = gk;
-    p.kspan_max = kspan_max;
-    p.panel_bytes = geo.panel_bytes();
     p.scale_dtype = scale_dtype;
 
     const int mb = m <= 8 ? 1 : 2;
+    const size_t smem = stream_smem_bytes(mb, geo.cols);
+    const int ctas_per_sm = std::max(1, int(kMaxDynamicSmem / (smem + 1024)));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(unsigned(geo.panels * gk));
-    cfg.blockDim = dim3(kGemvThreads);
-    cfg.dynamicSmemBytes = gemv_smem_bytes(mb, kspan_max);
+    cfg.gridDim = dim3(unsigned(std::min(geo.strips, kSmCount * std::min(ctas_per_sm, 2))));
+    cfg.blockDim = dim3(kStreamThreads);
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -451,10 +426,10 @@ int W4A16::run(const void* d_x, void* d_y, int m, void* ws, size_t ws_bytes, uns
                     workspace_bytes(m));
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(d_x);
     __nv_bfloat16* y = static_cast<__nv_bfloat16*>(d_y);
-    for (int m0 = 0; m0 < m; m0 += 16) {
-        const int rows = std::min(16, m - m0);
-        const int rc = launch_stream(x + size_t(m0) * geo.cols, y + size_t(m0) * geo.rows, rows, geo.rows, ws,
-                                     flags, stream);
+    for (int m0 = 0; m0 < m; m0 += max_rows_per_launch) {
+        const int rows = std::min(max_rows_per_launch, m - m0);
+        const int rc = launch_stream(x + size_t(m0) * geo.cols, y + size_t(m0) * geo.rows, rows, geo.rows, flags,
+                                     stream);
         if (rc) return rc;
     }
     return GARNET_B200_OK;
@@ -472,9 +447,9 @@ static int validate_shape(int n, int k, int group)
 int w4a16_repack_device(const uint8_t* d_nibbles, const uint16_t* d_scales, const PackGeom& geo, long long row0,
                         uint8_t* d_packed, cudaStream_t stream)
 {
-    const size_t words = size_t(geo.panels) * geo.chunks * (geo.chunk_data / 4);
+    const size_t words = size_t(geo.strips_padded) * geo.chunks * (geo.chunk_data / 4);
     w4_repack_codes_kernel<<<unsigned((words + 255) / 256), 256, 0, stream>>>(d_nibbles, d_packed, geo, row0);
-    const size_t sc = size_t(geo.panels) * 128 * geo.chunks;
+    const size_t sc = size_t(geo.strips_padded) * 16 * geo.chunks;
     w4_repack_scales_int4_kernel<<<unsigned((sc + 255) / 256), 256, 0, stream>>>(d_scales, d_packed, geo, row0);
     GB_CUDA(cudaGetLastError());
     return GARNET_B200_OK;

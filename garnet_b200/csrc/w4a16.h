@@ -11,31 +11,25 @@
 
 namespace gb200 {
 
-constexpr int kW4MaxKSpan = 2048;   // K columns one CTA of the streaming kernel covers at most
-
 struct W4A16 {
     PackGeom geo{};
     int scale_dtype = 1;             // GARNET_B200_FP16 or GARNET_B200_BF16: how the 16-bit scales are read
     uint8_t* packed = nullptr;       // packed tiles (device)
     bool owns_packed = false;
     int device = 0;
-    int gk = 1;                      // K slices per panel in the streaming kernel
-    int kspan_max = 0;
-    int* counters = nullptr;         // [panels] arrival counters for the K-slice reduction (device)
+    int max_rows_per_launch = 16;    // batch rows one launch of the streaming kernel takes
     int* fault_host = nullptr;       // mapped host word written by bounded device waits
     int* fault_dev = nullptr;
     // staging for the host-buffer entry point
     void* stage_x = nullptr;
     void* stage_y = nullptr;
     void* stage_ws = nullptr;
-    void* pin_x = nullptr;
-    void* pin_y = nullptr;
     int stage_rows = 0;
 
     ~W4A16();
     int init_common();
     size_t workspace_bytes(int m) const;
-    int launch_stream(const __nv_bfloat16* x, __nv_bfloat16* y, int m, int ldy, void* ws, unsigned flags,
+    int launch_stream(const __nv_bfloat16* x, __nv_bfloat16* y, int m, int ldy, unsigned flags,
                       cudaStream_t stream);
     int run(const void* d_x, void* d_y, int m, void* ws, size_t ws_bytes, unsigned flags, cudaStream_t stream);
 };

@@ -64,16 +64,17 @@ def row_of_g(g):
 
 def expected_position(n, k, chunks):
     """Independent statement of the packed int4 layout: byte offset of the word
-    and nibble index that hold element (n, k)."""
-    panel, nl = divmod(n, 128)
+    and nibble index that hold element (n, k).  Strips of 16 rows, chunks of 128
+    columns (1024 code bytes + 32 scale bytes), 512-byte tiles of 64 columns,
+    16-byte units 4*g + t, words h + 2*j."""
+    strip, r16 = divmod(n, 16)
     chunk, kl = divmod(k, 128)
     tile, kk = divmod(kl, 64)
-    sub, r16 = divmod(nl, 16)
     h, r8 = divmod(r16, 8)
     g = next(g for g in range(8) if row_of_g(g) == r8)
     octet, e = divmod(kk, 8)
     j, t = divmod(octet, 4)
-    byte = (panel * chunks + chunk) * (8192 + 256) + tile * 4096 + sub * 512 + (4 * g + t) * 16 + (h + 2 * j) * 4
+    byte = (strip * chunks + chunk) * 1056 + tile * 512 + (4 * g + t) * 16 + (h + 2 * j) * 4
     return byte, (e >> 1) + 4 * (e & 1)
 
 
@@ -87,24 +88,23 @@ def test_host_packer_layout(n, k, group):
     packed = garnet_b200.pack_host(torch.from_numpy(nibbles), torch.from_numpy(scales.view(np.int16)).view(torch.bfloat16),
                                    n, k, group).numpy()
     chunks = k // 128
-    panels = (n + 127) // 128
-    assert packed.size == panels * chunks * (8192 + 256) == garnet_b200.packed_bytes(n, k, group)
+    strips_padded = ((n + 15) // 16 + 7) // 8 * 8
+    assert packed.size == strips_padded * chunks * 1056 == garnet_b200.packed_bytes(n, k, group)
     words = packed.view(np.uint32)
     for nn in range(0, n, 7):
         for kk in range(0, k, 5):
             byte, nib = expected_position(nn, kk, chunks)
             got = (int(words[byte // 4]) >> (4 * nib)) & 15
             assert got == (int(codes[nn, kk]) & 15), (nn, kk)
-    # scales: [sub][g][h] 16-bit words after the 8192 code bytes of each chunk
+    # scales: [g][h] 16-bit words after the 1024 code bytes of each strip-chunk
     for nn in range(0, n, 3):
         for c in range(chunks):
-            panel, nl = divmod(nn, 128)
-            sub, r16 = divmod(nl, 16)
+            strip, r16 = divmod(nn, 16)
             h, r8 = divmod(r16, 8)
             g = next(g for g in range(8) if row_of_g(g) == r8)
-            off = (panel * chunks + c) * 8448 + 8192 + (sub * 8 + g) * 4 + h * 2
+            off = (strip * chunks + c) * 1056 + 1024 + g * 4 + h * 2
             assert packed[off:off + 2].view(np.uint16)[0] == scales[nn, (c * 128) // group]
     # padding rows hold zero codes
     if n % 128:
-        byte, _ = expected_position(panels * 128 - 1, 0, chunks)
+        byte, _ = expected_position(strips_padded * 16 - 1, 0, chunks)
         assert words[byte // 4] == 0

@@ -84,9 +84,11 @@ def test_baseline_config_gate_proj_m1():
     assert torch.equal(y1, y2)          # deterministic: K slices are reduced in a fixed order
     _, y64 = oracle.w4a16_exact(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"])
     check_close(y1, y64)
-    # the reference CPU operator (int8 activations) lands within the same bound
+    # the reference CPU operator quantises activations to int8 per group, so it is
+    # itself only an approximation of this product; it must still land close by
     q4q8 = oracle.q4q8_forward(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"][0])
-    assert (np.abs(q4q8 - y64[0]) <= TOL * (1 + np.abs(y64[0]))).all()
+    assert (np.abs(q4q8 - y64[0]) <= 5e-2 * (1 + np.abs(y64[0]))).all()
+    assert (np.abs(q4q8 - y1.float().cpu().numpy()[0]) <= 5e-2 * (1 + np.abs(q4q8))).all()
 
 
 def test_lm_head_slice_and_n_sharding():
