@@ -7,6 +7,7 @@
 // group scale is applied to that partial sum in fp32, so no product is rounded
 // before the final bf16 store.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -156,11 +157,13 @@ __global__ void int4_quantize_kernel(const T* __restrict__ src, long long rows, 
 
 // ------------------------------------------------------- streaming kernel
 
-constexpr int kStreamStages = 3;            // segment buffers in flight per CTA
-constexpr int kStreamWarps = 8;             // consumer warps; one extra warp produces
-constexpr int kStreamThreads = (kStreamWarps + 1) * 32;
-constexpr int kSegChunks = 2 * kStreamWarps;   // chunks per segment: two per consumer warp
+// Two shapes of CTA: 4 consumer warps with 8-chunk segments (many strips per CTA:
+// more CTAs per SM, cheaper per-strip reduction) and 8 consumer warps with
+// 16-chunk segments (few strips: more warps share one strip, lower latency).
 constexpr int kInt4ChunkBytes = 1024 + 32;
+__host__ __device__ constexpr int stream_stages(int warps) { return warps == 4 ? 4 : 3; }
+__host__ __device__ constexpr int seg_chunks(int warps) { return 2 * warps; }   // two chunks per consumer warp
+__host__ __device__ constexpr int seg_bytes(int warps) { return seg_chunks(warps) * kInt4ChunkBytes; }
 
 struct StreamParams {
     const uint8_t* packed;
@@ -178,25 +181,61 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads)
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Two int4 codes -> bf16x2 {128 + (q+8), ...}: the biased form, without the
+// subtraction.  The bias is removed once per (batch row, chunk) from the
+// accumulated sum: sum_k (136 + q_k) x_k - 136 * sum_k x_k.
+__device__ __forceinline__ uint32_t int4x2_to_bf16x2_biased(uint32_t word_shifted)
+{
+    return lop3_and_xor(word_shifted, 0x000F000Fu, 0x43084308u);
+}
+
+template <bool kBiased>
+__device__ __forceinline__ uint32_t int4x2_expand(uint32_t word_shifted)
+{
+    return kBiased ? int4x2_to_bf16x2_biased(word_shifted) : int4x2_to_bf16x2(word_shifted);
+}
+
+// Shared-memory plan of the streaming kernel (bytes).
+struct StreamSmem {
+    int ring, red, bars, sx, xs, total;
+    int x_rows, x_stride;
+};
+__host__ __device__ inline StreamSmem stream_smem_plan(int warps, int mb, int m, int k, int chunks)
+{
+    const int kStreamStages = stream_stages(warps), kSegBytes = seg_bytes(warps), kStreamWarps = warps;
+    StreamSmem p;
+    p.x_rows = min(m, 8 * mb) + 1;                 // one shared all-zero row for the padded batch columns
+    p.x_stride = k * 2 + 64;                       // 64 mod 128: conflict-free 16-byte reads across rows
+    p.ring = 0;
+    p.red = p.ring + kStreamStages * kSegBytes;    // [2][warps][mb*4][32] fp32
+    p.bars = p.red + 2 * kStreamWarps * mb * 128 * 4;
+    p.sx = p.bars + 2 * kStreamStages * 8;         // [chunks][8*mb] fp32: -136 * sum of x over the chunk
+    p.xs = (p.sx + chunks * 8 * mb * 4 + 127) & ~127;
+    p.total = p.xs + p.x_rows * p.x_stride;
+    return p;
+}
+
 // Persistent CTAs; each owns a contiguous range of 16-row strips.  A strip is one
 // linear byte range of the packed matrix; the producer warp streams it in
-// segments of up to 16 chunks (16.5 KiB) through a ring of bulk copies.  The 8
-// consumer warps split each segment along K (two chunks each), expand int4 ->
-// bf16 in registers and feed m16n8k16 MMAs whose N dimension is the (padded)
-// batch; at the end of a strip their partial sums meet in shared memory.  No
-// global scratch, no atomics: the summation order is fixed.
-template <int MB>
-__global__ void __launch_bounds__(kStreamThreads) w4a16_stream_kernel(const StreamParams p)
+// segments of 8 chunks (8.25 KiB) through a ring of bulk copies.  The 4 consumer
+// warps split each segment along K (two chunks each), expand int4 -> bf16 in
+// registers and feed m16n8k16 MMAs whose N dimension is the (padded) batch; at
+// the end of a strip their partial sums meet in shared memory.  No global
+// scratch, no atomics: the summation order is fixed.
+template <int MB, bool kBiased, int kStreamWarps>
+__global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(const StreamParams p)
 {
+    constexpr int kStreamStages = stream_stages(kStreamWarps);
+    constexpr int kSegChunks = seg_chunks(kStreamWarps);
+    constexpr int kSegBytes = seg_bytes(kStreamWarps);
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int kSegBytes = kSegChunks * kInt4ChunkBytes;
-    uint8_t* ring = smem;                                                 // kStreamStages * kSegBytes
-    float* red = reinterpret_cast<float*>(smem + kStreamStages * kSegBytes);   // [2][warps][MB*4][32]
-    uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * kStreamWarps * MB * 128);
+    const StreamSmem plan = stream_smem_plan(kStreamWarps, MB, p.m, p.k, p.chunks);
+    uint8_t* ring = smem + plan.ring;
+    float* red = reinterpret_cast<float*>(smem + plan.red);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + plan.bars);
     uint64_t* empty = full + kStreamStages;
-    uint8_t* xs = reinterpret_cast<uint8_t*>(empty + kStreamStages) + 16;      // x tile, 8*MB padded rows
-    xs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(xs) + 127) & ~uintptr_t(127));
-    const int x_stride = p.k * 2 + 64;                                    // bytes; 64 mod 128 => conflict-free
+    float* sx = reinterpret_cast<float*>(smem + plan.sx);
+    uint8_t* xs = smem + plan.xs;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int s0 = int((long long)blockIdx.x * p.strips / gridDim.x);
@@ -239,17 +278,47 @@ __global__ void __launch_bounds__(kStreamThreads) w4a16_stream_kernel(const Stre
     // ---- consumers
     pdl_wait();   // x is produced by the previous kernel; y may still be read by it
     {
+        // Stage the batch rows (bf16) and, per (row, chunk), -136 * sum of the row's
+        // 128 values (the bias term of the int4 expansion).  16 consecutive threads
+        // cover one chunk of one row.
+        const int rows = plan.x_rows - 1;
         const int vec_per_row = p.k / 8;
-        for (int i = threadIdx.x; i < 8 * MB * vec_per_row; i += kStreamWarps * 32) {
+        const int total = rows * vec_per_row;
+        for (int i0 = 0; i0 < total; i0 += kStreamWarps * 32) {
+            const int i = i0 + threadIdx.x;
             const int m = i / vec_per_row, v = i % vec_per_row;
             uint4 val = make_uint4(0, 0, 0, 0);
-            if (m < p.m) val = *reinterpret_cast<const uint4*>(p.x + size_t(m) * p.k + v * 8);
-            *reinterpret_cast<uint4*>(xs + size_t(m) * x_stride + v * 16) = val;
+            if (i < total) {
+                val = *reinterpret_cast<const uint4*>(p.x + size_t(m) * p.k + v * 8);
+                *reinterpret_cast<uint4*>(xs + size_t(m) * plan.x_stride + v * 16) = val;
+            }
+            if (kBiased) {
+                float part = 0.f;
+                const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    part += __uint_as_float(w4[q] << 16) + __uint_as_float(w4[q] & 0xffff0000u);
+#pragma unroll
+                for (int off = 8; off; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+                if ((lane & 15) == 0 && i < total) sx[(v >> 4) * (8 * MB) + m] = -136.f * part;
+            }
         }
+        for (int i = threadIdx.x; i < vec_per_row; i += kStreamWarps * 32)
+            *reinterpret_cast<uint4*>(xs + size_t(rows) * plan.x_stride + i * 16) = make_uint4(0, 0, 0, 0);
+        if (kBiased)
+            for (int i = threadIdx.x; i < p.chunks * 8 * MB; i += kStreamWarps * 32)
+                if ((i % (8 * MB)) >= rows) sx[i] = 0.f;
     }
     named_barrier_sync(1, kStreamWarps * 32);
 
     const int g = lane >> 2, t = lane & 3;
+    // Per-lane x row pointers: batch row g (and 8+g), or the zero row.
+    const uint8_t* xrow[MB];
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb) {
+        const int r = mb * 8 + g;
+        xrow[mb] = xs + size_t(r < p.m ? r : plan.x_rows - 1) * plan.x_stride + t * 16;
+    }
     float acc[MB][4];
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
@@ -258,10 +327,9 @@ __global__ void __launch_bounds__(kStreamThreads) w4a16_stream_kernel(const Stre
     const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
 
     bool ok = true;
+    int s = 0, phase = 0, strip = s0, seg = 0;
     for (int i = 0; i < items; ++i) {
-        const int s = i % kStreamStages;
-        const int strip = s0 + i / nseg, seg = i % nseg;
-        if (ok && !mbar_wait(&full[s], (i / kStreamStages) & 1)) {
+        if (ok && !mbar_wait(&full[s], phase)) {
             atomicExch(p.fault, 2);
             ok = false;
         }
@@ -271,37 +339,41 @@ __global__ void __launch_bounds__(kStreamThreads) w4a16_stream_kernel(const Stre
             for (int cc = 0; cc < 2; ++cc) {
                 const int c = 2 * warp + cc;
                 if (c >= nch) break;
-                const uint8_t* st = ring + size_t(s) * kSegBytes + size_t(c) * kInt4ChunkBytes;
+                const uint8_t* st = ring + s * kSegBytes + c * kInt4ChunkBytes;
                 const uint32_t sc = *reinterpret_cast<const uint32_t*>(st + 1024 + g * 4);
-                const float s_lo = scale16_to_float(sc & 0xffffu, p.scale_dtype);
-                const float s_hi = scale16_to_float(sc >> 16, p.scale_dtype);
-                const int kchunk = (seg * kSegChunks + c) * 128;
+                const int chunk = seg * kSegChunks + c;
+                const uint4 u0 = *reinterpret_cast<const uint4*>(st + lane * 16);
+                const uint4 u1 = *reinterpret_cast<const uint4*>(st + 512 + lane * 16);
                 float tmp[MB][4];
 #pragma unroll
-                for (int tile = 0; tile < 2; ++tile) {
-                    const uint4 u = *reinterpret_cast<const uint4*>(st + tile * 512 + lane * 16);
+                for (int q = 0; q < 4; ++q) {   // q = 2*tile + half: octets t, t+4 of tile 0, then of tile 1
+                    const uint32_t wlo = q == 0 ? u0.x : q == 1 ? u0.z : q == 2 ? u1.x : u1.z;
+                    const uint32_t whi = q == 0 ? u0.y : q == 1 ? u0.w : q == 2 ? u1.y : u1.w;
+                    const uint32_t a0[4] = {int4x2_expand<kBiased>(wlo), int4x2_expand<kBiased>(whi),
+                                            int4x2_expand<kBiased>(wlo >> 4), int4x2_expand<kBiased>(whi >> 4)};
+                    const uint32_t a1[4] = {int4x2_expand<kBiased>(wlo >> 8), int4x2_expand<kBiased>(whi >> 8),
+                                            int4x2_expand<kBiased>(wlo >> 12), int4x2_expand<kBiased>(whi >> 12)};
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const uint32_t wlo = half ? u.z : u.x, whi = half ? u.w : u.y;
-                        const int kloc = kchunk + tile * 64 + (t + 4 * half) * 8;
-                        const uint32_t a0[4] = {int4x2_to_bf16x2(wlo), int4x2_to_bf16x2(whi),
-                                                int4x2_to_bf16x2(wlo >> 4), int4x2_to_bf16x2(whi >> 4)};
-                        const uint32_t a1[4] = {int4x2_to_bf16x2(wlo >> 8), int4x2_to_bf16x2(whi >> 8),
-                                                int4x2_to_bf16x2(wlo >> 12), int4x2_to_bf16x2(whi >> 12)};
-#pragma unroll
-                        for (int mb = 0; mb < MB; ++mb) {
-                            const uint4 xb = *reinterpret_cast<const uint4*>(xs + size_t(mb * 8 + g) * x_stride +
-                                                                             size_t(kloc) * 2);
-                            if (tile == 0 && half == 0)
-                                mma_bf16_16816(tmp[mb], a0, xb.x, xb.y, zero4);
-                            else
-                                mma_bf16_16816(tmp[mb], a0, xb.x, xb.y, tmp[mb]);
-                            mma_bf16_16816(tmp[mb], a1, xb.z, xb.w, tmp[mb]);
-                        }
+                    for (int mb = 0; mb < MB; ++mb) {
+                        const uint4 xb = *reinterpret_cast<const uint4*>(xrow[mb] + chunk * 256 + q * 64);
+                        if (q == 0)
+                            mma_bf16_16816(tmp[mb], a0, xb.x, xb.y, zero4);
+                        else
+                            mma_bf16_16816(tmp[mb], a0, xb.x, xb.y, tmp[mb]);
+                        mma_bf16_16816(tmp[mb], a1, xb.z, xb.w, tmp[mb]);
                     }
                 }
+                const float s_lo = scale16_to_float(sc & 0xffffu, p.scale_dtype);
+                const float s_hi = scale16_to_float(sc >> 16, p.scale_dtype);
 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb) {
+                    if (kBiased) {
+                        const float2 b = *reinterpret_cast<const float2*>(sx + chunk * (8 * MB) + mb * 8 + 2 * t);
+                        tmp[mb][0] += b.x;
+                        tmp[mb][1] += b.y;
+                        tmp[mb][2] += b.x;
+                        tmp[mb][3] += b.y;
+                    }
                     acc[mb][0] = fmaf(tmp[mb][0], s_lo, acc[mb][0]);
                     acc[mb][1] = fmaf(tmp[mb][1], s_lo, acc[mb][1]);
                     acc[mb][2] = fmaf(tmp[mb][2], s_hi, acc[mb][2]);
@@ -311,11 +383,16 @@ __global__ void __launch_bounds__(kStreamThreads) w4a16_stream_kernel(const Stre
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
-        if (seg != nseg - 1) continue;
+        if (++s == kStreamStages) {
+            s = 0;
+            phase ^= 1;
+        }
+        if (++seg != nseg) continue;
+        seg = 0;
 
-        // ---- end of a strip: the 8 warps' partial sums meet in shared memory.
+        // ---- end of a strip: the warps' partial sums meet in shared memory.
         // acc[mb][0..1]: row R(g), batch columns 2t, 2t+1; [2..3]: row R(g)+8.
-        float* slot = red + size_t((strip - s0) & 1) * (kStreamWarps * MB * 128);
+        float* slot = red + ((strip - s0) & 1) * (kStreamWarps * MB * 128);
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
@@ -324,7 +401,7 @@ __global__ void __launch_bounds__(kStreamThreads) w4a16_stream_kernel(const Stre
                 acc[mb][q] = 0.f;
             }
         named_barrier_sync(1, kStreamWarps * 32);
-        for (int idx = threadIdx.x; idx < MB * 128; idx += kStreamWarps * 32) {
+        for (int idx = threadIdx.x; idx < MB * 128; idx += kStreamWarps * 32) {   // 128 outputs per 8 batch columns
             const int l = idx & 31, q = (idx >> 5) & 3, mb = idx >> 7;
             float v = 0.f;
 #pragma unroll
@@ -333,6 +410,7 @@ __global__ void __launch_bounds__(kStreamThreads) w4a16_stream_kernel(const Stre
             const int n = strip * 16 + row_of_g(l >> 2) + 8 * (q >> 1);
             if (m < p.m && n < p.n) p.y[size_t(m) * p.ldy + n] = __float2bfloat16_rn(v);
         }
+        ++strip;
     }
     if (!ok) {
         // A wait gave up: give the copies still in flight a bounded chance to land
@@ -343,13 +421,25 @@ __global__ void __launch_bounds__(kStreamThreads) w4a16_stream_kernel(const Stre
 
 // ------------------------------------------------------------------ handle
 
-static size_t stream_smem_bytes(int mb, int k)
+constexpr size_t kMaxDynamicSmem = 227 * 1024;
+
+static bool use_biased_expansion()
 {
-    return size_t(kStreamStages) * kSegChunks * kInt4ChunkBytes + size_t(2) * kStreamWarps * mb * 128 * sizeof(float) +
-           2 * kStreamStages * sizeof(uint64_t) + 16 + 128 + size_t(8 * mb) * (size_t(k) * 2 + 64);
+    // GARNET_B200_W4_EXACT_EXPAND=1 selects the variant that subtracts the int4
+    // bias per element instead of once per chunk (A/B switch, read once).
+    static const bool biased = [] {
+        const char* e = getenv("GARNET_B200_W4_EXACT_EXPAND");
+        return !(e && e[0] == '1');
+    }();
+    return biased;
 }
 
-constexpr size_t kMaxDynamicSmem = 227 * 1024;
+template <int MB, bool B, int W>
+static cudaError_t set_stream_attr()
+{
+    return cudaFuncSetAttribute(w4a16_stream_kernel<MB, B, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                int(kMaxDynamicSmem));
+}
 
 int W4A16::init_common()
 {
@@ -357,14 +447,18 @@ int W4A16::init_common()
     GB_CUDA(cudaHostAlloc(&fault_host, sizeof(int), cudaHostAllocMapped));
     *fault_host = 0;
     GB_CUDA(cudaHostGetDevicePointer(&fault_dev, fault_host, 0));
-    if (stream_smem_bytes(1, geo.cols) > kMaxDynamicSmem)
+    if (size_t(stream_smem_plan(4, 1, 8, geo.cols, geo.chunks).total) > kMaxDynamicSmem)
         return fail(GARNET_B200_NOT_SUPPORTED, "w4a16: k=%d is too large for the streaming kernel", geo.cols);
-    max_rows_per_launch = stream_smem_bytes(2, geo.cols) <= kMaxDynamicSmem ? 16 : 8;
+    max_rows_per_launch = size_t(stream_smem_plan(8, 2, 16, geo.cols, geo.chunks).total) <= kMaxDynamicSmem ? 16 : 8;
     // The attribute is per kernel and per device, not per handle: always ask for the maximum.
-    GB_CUDA(cudaFuncSetAttribute(w4a16_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(kMaxDynamicSmem)));
-    GB_CUDA(cudaFuncSetAttribute(w4a16_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(kMaxDynamicSmem)));
+    GB_CUDA((set_stream_attr<1, true, 4>()));
+    GB_CUDA((set_stream_attr<2, true, 4>()));
+    GB_CUDA((set_stream_attr<1, false, 4>()));
+    GB_CUDA((set_stream_attr<2, false, 4>()));
+    GB_CUDA((set_stream_attr<1, true, 8>()));
+    GB_CUDA((set_stream_attr<2, true, 8>()));
+    GB_CUDA((set_stream_attr<1, false, 8>()));
+    GB_CUDA((set_stream_attr<2, false, 8>()));
     return GARNET_B200_OK;
 }
 
@@ -396,11 +490,18 @@ int W4A16::launch_stream(const __nv_bfloat16* x, __nv_bfloat16* y, int m, int ld
     p.scale_dtype = scale_dtype;
 
     const int mb = m <= 8 ? 1 : 2;
-    const size_t smem = stream_smem_bytes(mb, geo.cols);
-    const int ctas_per_sm = std::max(1, int(kMaxDynamicSmem / (smem + 1024)));
+    // Many strips per SM: narrow CTAs (4 consumer warps, up to 4 per SM).  Few strips:
+    // wide CTAs (8 consumer warps) so that more warps share each strip.
+    const bool narrow = geo.strips >= 8 * kSmCount * 4 &&
+                        size_t(stream_smem_plan(4, mb, m, geo.cols, geo.chunks).total) * 2 + 2048 <= kMaxDynamicSmem;
+    const int warps = narrow ? 4 : 8;
+    const size_t smem = size_t(stream_smem_plan(warps, mb, m, geo.cols, geo.chunks).total);
+    if (smem > kMaxDynamicSmem)
+        return fail(GARNET_B200_NOT_SUPPORTED, "w4a16: batch %d with k=%d does not fit shared memory", m, geo.cols);
+    const int ctas_per_sm = std::max(1, std::min(narrow ? 4 : 2, int(kMaxDynamicSmem / (smem + 1024))));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(unsigned(std::min(geo.strips, kSmCount * std::min(ctas_per_sm, 2))));
-    cfg.blockDim = dim3(kStreamThreads);
+    cfg.gridDim = dim3(unsigned(std::min(geo.strips, kSmCount * ctas_per_sm)));
+    cfg.blockDim = dim3((warps + 1) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -408,10 +509,20 @@ int W4A16::launch_stream(const __nv_bfloat16* x, __nv_bfloat16* y, int m, int ld
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & 1u) ? 1 : 0;
-    if (mb == 1)
-        GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_stream_kernel<1>, p));
-    else
-        GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_stream_kernel<2>, p));
+    const bool biased = use_biased_expansion();
+#define GB_LAUNCH_STREAM(MB_, B_, W_) GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_stream_kernel<MB_, B_, W_>, p))
+    if (warps == 4) {
+        if (mb == 1 && biased) GB_LAUNCH_STREAM(1, true, 4);
+        else if (mb == 1) GB_LAUNCH_STREAM(1, false, 4);
+        else if (biased) GB_LAUNCH_STREAM(2, true, 4);
+        else GB_LAUNCH_STREAM(2, false, 4);
+    } else {
+        if (mb == 1 && biased) GB_LAUNCH_STREAM(1, true, 8);
+        else if (mb == 1) GB_LAUNCH_STREAM(1, false, 8);
+        else if (biased) GB_LAUNCH_STREAM(2, true, 8);
+        else GB_LAUNCH_STREAM(2, false, 8);
+    }
+#undef GB_LAUNCH_STREAM
     return GARNET_B200_OK;
 }
 

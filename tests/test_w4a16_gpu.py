@@ -38,10 +38,14 @@ def check_close(y_dev, y64, tol=TOL):
     err = np.abs(y - y64)
     assert np.isfinite(y).all()
     assert (err <= tol * (1 + np.abs(y64))).all(), float((err / (1 + np.abs(y64))).max())
-    # in practice the result is the correctly rounded bf16 of the exact sum, give or take one ulp
+    # in practice the result is the correctly rounded bf16 of the exact sum, give or
+    # take one ulp, plus an absolute term far below the row's output scale (the
+    # int4 bias is removed once per 128 columns in fp32, which leaves a few 1e-6 of
+    # the typical output magnitude on results that nearly cancel)
     ref = oracle.bf16_round(y64.astype(np.float32)).astype(np.float64)
     ulp = np.maximum(np.abs(ref), 2.0 ** -120) * 2.0 ** -7
-    assert (np.abs(y - ref) <= 1.01 * ulp + 1e-6).all()
+    rms = np.sqrt((y64 ** 2).mean(axis=1, keepdims=True))
+    assert (np.abs(y - ref) <= 1.01 * ulp + 2e-5 * rms + 1e-30).all()
 
 
 @pytest.mark.parametrize("n,k,group", [(128, 128, 128), (200, 256, 128), (1024, 2048, 128), (256, 512, 256)])
