@@ -43,6 +43,15 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_w4a16_fault.argtypes = [vp]
     L.garnet_b200_w4a16_destroy.argtypes = [vp]
     L.garnet_b200_w4a16_destroy.restype = None
+    L.garnet_b200_moe_workspace.argtypes = [vp, i, c.POINTER(sz)]
+    L.garnet_b200_moe_create.argtypes = [vp, vp, vp, c.POINTER(vp)]
+    L.garnet_b200_moe_run.argtypes = [vp, vp, vp, vp, sz, i, vp]
+    L.garnet_b200_moe_route.argtypes = [vp, vp, vp, vp, vp, i, vp]
+    L.garnet_b200_mxfp4_decode.argtypes = [vp, vp, vp, i, vp]
+    L.garnet_b200_moe_dequant.argtypes = [vp, i, i, vp, vp]
+    L.garnet_b200_moe_fault.argtypes = [vp]
+    L.garnet_b200_moe_destroy.argtypes = [vp]
+    L.garnet_b200_moe_destroy.restype = None
 
 
 def lib() -> ctypes.CDLL:

@@ -23,11 +23,6 @@ int cuda_fail(cudaError_t e, const char* where);
 
 constexpr int kSmCount = 148;
 
-// ---- packed tile geometry (see layout.h) ----
-constexpr int kPanelRows = 128;   // weight rows per panel (one tcgen05 A tile)
-constexpr int kTileK = 64;        // K elements per 4 KiB tile
-constexpr int kTileBytes = kPanelRows * kTileK / 2;
-
 #if defined(__CUDACC__)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -119,7 +114,9 @@ __device__ __forceinline__ uint32_t int4x2_to_bf16x2(uint32_t word_shifted)
 }
 
 // One byte holding two e2m1 codes (low nibble first) -> f16x2, by the sm_100a
-// conversion instruction; all 16 codes are exact in fp16.
+// conversion instruction; all 16 codes are exact in fp16.  `word` must come from
+// a 32-bit (or wider) load: when the operand is a zero-extended byte load, the
+// byte unpack below was observed to yield zero with nvcc 12.9.
 __device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t word, int byte_index)
 {
     uint32_t r;
@@ -151,6 +148,11 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]),
           "f"(c[3]));
+}
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 __device__ __forceinline__ float bf16_round_f(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }

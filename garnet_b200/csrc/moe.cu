@@ -1,0 +1,992 @@
+// gpt-oss MXFP4 mixture-of-experts operator (`gpt_oss_moe_mxfp4`) for sm_100a:
+// repackers, router, top-k, slot bucketing, the streaming expert kernel used for
+// small per-expert batches, the weighted combine, and the C ABI around them.
+//
+// Numerics follow the reference operator step by step
+// (plugins/gpt_oss/cuda/gpt_oss_kernels.cu:537-587, :681-726, :762-811, :907-921):
+//   logit = bf(x . Wr + br); k rounds of arg-max, ties to the lowest index;
+//   p_j = bf(exp(l_j - l_0) / sum_i exp(l_i - l_0));
+//   g = min(bf(bf(x . w_gate) + b), limit); u = clamp(bf(bf(x . w_up) + b), +-limit);
+//   h = bf(bf(g * bf(sigmoid(bf(1.702 g)))) * bf(u + 1));
+//   y = bf(sum_j bf(bf(h . w_down) + bd) * p_j)   (router order j).
+// Dot products accumulate in fp32.  MXFP4 codes are expanded by the hardware
+// conversion cvt.rn.f16x2.e2m1x2 (exact) and the e8m0 group scale multiplies the
+// fp32 partial sum of each 32-column group (exact power of two), so no weight
+// value is ever rounded.  Activations enter the tensor core as fp16 after an
+// exact per-token power-of-two normalisation (bf16 inputs have 8 significant
+// bits, fp16 carries 11).
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+#include "layout.h"
+#include "moe.h"
+
+namespace gb200 {
+
+constexpr int kMxChunkBytes = 512 + 32;
+
+// ------------------------------------------------------------------ repack
+
+// One thread per packed 32-bit word.  `interleaved` = 1 for the gate/up matrix:
+// original row 2i is gate_i and row 2i+1 is up_i (gpt_oss_kernels.cu:776); the
+// packed matrix stores gate_i at strip row r and up_i at strip row r + 8
+// (i = 8*strip + r), so that one MMA accumulator lane holds the gate and the up
+// value of the same intermediate channel.
+__global__ void mx_repack_codes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, PackGeom geo,
+                                       int interleaved)
+{
+    const int expert = blockIdx.y;
+    const size_t words_per_chunk = geo.chunk_data / 4;
+    const size_t total = size_t(geo.strips_padded) * geo.chunks * words_per_chunk;
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t chunk_lin = idx / words_per_chunk;
+    const int w = int(idx % words_per_chunk);
+    const int strip = int(chunk_lin / geo.chunks), chunk = int(chunk_lin % geo.chunks);
+    const int unit = (w >> 2) & 31, word = w & 3;          // one 512-byte tile per chunk
+    const int g = unit >> 2, t = unit & 3, h = word & 1, j = word >> 1;
+    const int r16 = row_of_g(g) + 8 * h;
+    const int n = strip * 16 + r16;                          // packed row
+    const int k0 = chunk * 64 + (t + 4 * j) * 8;
+    uint32_t out = 0;
+    if (n < geo.rows && k0 < geo.cols) {
+        const int src_row = interleaved ? 2 * (strip * 8 + (r16 & 7)) + (r16 >> 3) : n;
+        const size_t sb = (size_t(expert) * geo.rows + src_row) * size_t(geo.cols / 2) + k0 / 2;
+        out = *reinterpret_cast<const uint32_t*>(src + sb);
+    }
+    const size_t ob = size_t(expert) * geo.matrix_bytes() + (size_t(strip) * geo.chunks + chunk) * geo.chunk_bytes +
+                      size_t(w) * 4;
+    *reinterpret_cast<uint32_t*>(dst + ob) = out;
+}
+
+// One thread per (packed row, 32-column group).  Padding gets scale 127 (1.0).
+__global__ void mx_repack_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, PackGeom geo,
+                                        int interleaved)
+{
+    const int expert = blockIdx.y;
+    const int groups = geo.chunks * 2;
+    const size_t total = size_t(geo.strips_padded) * 16 * groups;
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int n = int(idx / groups), grp = int(idx % groups);
+    uint8_t e = 127;
+    if (n < geo.rows && grp * 32 < geo.cols) {
+        const int strip = n >> 4, r16 = n & 15;
+        const int src_row = interleaved ? 2 * (strip * 8 + (r16 & 7)) + (r16 >> 3) : n;
+        e = src[(size_t(expert) * geo.rows + src_row) * size_t(geo.cols / 32) + grp];
+    }
+    dst[size_t(expert) * geo.matrix_bytes() + locate_scale(geo, n, grp * 32)] = e;
+}
+
+// Flags e8m0 bytes 0 (2^-127, an fp32 subnormal) and 255 (NaN), which need the
+// careful scale decode.
+__global__ void mx_scan_scales_kernel(const uint8_t* __restrict__ scales, size_t count, int* flag)
+{
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx < count && (scales[idx] == 0 || scales[idx] == 255)) atomicOr(flag, 1);
+}
+
+// 2^(e-127) as fp32.  The plain form is a shift; the careful form also covers
+// e = 0 (subnormal 2^-127) and e = 255 (NaN), gpt_oss_kernels.cu:55-56.
+template <bool kCareful>
+__device__ __forceinline__ float e8m0_to_float(uint32_t e)
+{
+    if (kCareful) {
+        if (e == 0) return __uint_as_float(0x00400000u);
+        if (e == 255) return __uint_as_float(0x7fc00000u);
+    }
+    return __uint_as_float(e << 23);
+}
+
+// ------------------------------------------------------------ decode checks
+
+// rows x 32 columns, one scale per row: the shape of the reference's exhaustive
+// decode test (TestGptOssMxfp4Decode, gpt_oss_kernels.cu:71-76).  Uses the same
+// conversion instruction and scale decode as the expert kernels.
+__global__ void mx_decode_rows_kernel(const uint8_t* __restrict__ blocks, const uint8_t* __restrict__ scales,
+                                      float* __restrict__ out, int rows)
+{
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;   // one 32-bit word = eight codes
+    if (idx >= rows * 4) return;
+    const int row = idx >> 2;
+    // The conversion is fed from a full 32-bit word, as in the expert kernels.
+    const uint32_t w = reinterpret_cast<const uint32_t*>(blocks)[idx];
+    const float s = e8m0_to_float<true>(scales[row]);
+    const uint32_t pairs[4] = {e2m1x2_to_f16x2(w, 0), e2m1x2_to_f16x2(w, 1), e2m1x2_to_f16x2(w, 2),
+                               e2m1x2_to_f16x2(w, 3)};
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const __half2 hv = *reinterpret_cast<const __half2*>(&pairs[b]);
+        out[8 * idx + 2 * b] = __half2float(__low2half(hv)) * s;
+        out[8 * idx + 2 * b + 1] = __half2float(__high2half(hv)) * s;
+    }
+}
+
+// fp32 value of every logical element of one packed expert matrix (row order of
+// the ORIGINAL matrix), decoded from the packed tiles.
+__global__ void mx_dequant_kernel(const uint8_t* __restrict__ packed, float* __restrict__ out, PackGeom geo,
+                                  int interleaved, int expert)
+{
+    const size_t total = size_t(geo.rows) * geo.cols / 2;
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int src_row = int(idx / (geo.cols / 2)), k = int(idx % (geo.cols / 2)) * 2;
+    int n = src_row;
+    if (interleaved) {
+        const int i = src_row >> 1, up = src_row & 1;
+        n = (i >> 3) * 16 + (i & 7) + 8 * up;
+    }
+    const uint8_t* base = packed + size_t(expert) * geo.matrix_bytes();
+    const PackPos p = locate(geo, n, k);
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(base + p.word_byte);
+    const uint32_t pair = e2m1x2_to_f16x2(w >> (8 * ((k & 7) >> 1)), 0);
+    const float s = e8m0_to_float<true>(base[locate_scale(geo, n, k)]);
+    const __half2 hv = *reinterpret_cast<const __half2*>(&pair);
+    out[size_t(src_row) * geo.cols + k] = __half2float(__low2half(hv)) * s;
+    out[size_t(src_row) * geo.cols + k + 1] = __half2float(__high2half(hv)) * s;
+}
+
+// ------------------------------------------------------------------ router
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+constexpr int kRouteTokens = 8;     // tokens per CTA
+constexpr int kRouteWarps = 8;      // one expert per warp at a time
+
+// logits[t,e] = bf(sum_d x[t,d] * W[e,d] + b[e]) with fp32 accumulation
+// (gpt_oss_kernels.cu:537-587).  A CTA stages 8 tokens in shared memory; each warp
+// walks experts, its lanes striding the hidden dimension.  The CTA of expert
+// group 0 also writes, per token, the fp16 copy of x used by the expert kernels
+// (x rounded to bf16, then scaled by an exact power of two so that the largest
+// magnitude lands in [2^13, 2^14)), and that exponent.
+template <typename XT>
+__global__ void __launch_bounds__(kRouteWarps * 32)
+moe_route_scores_kernel(const XT* __restrict__ x, const float* __restrict__ rw, const float* __restrict__ rb,
+                        float* __restrict__ logits, __half* __restrict__ xh, int* __restrict__ xshift, int tokens,
+                        int hidden, int experts, int experts_per_cta)
+{
+    extern __shared__ float xs[];   // [kRouteTokens][hidden]
+    __shared__ float s_amax[kRouteTokens];
+    const int t0 = blockIdx.x * kRouteTokens;
+    const int nt = min(kRouteTokens, tokens - t0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < kRouteTokens * hidden; i += blockDim.x) {
+        const int t = i / hidden, d = i % hidden;
+        xs[i] = t < nt ? to_float(x[size_t(t0 + t) * hidden + d]) : 0.f;
+    }
+    __syncthreads();
+    const int e0 = blockIdx.y * experts_per_cta, e1 = min(experts, e0 + experts_per_cta);
+    for (int e = e0 + warp; e < e1; e += kRouteWarps) {
+        float acc[kRouteTokens];
+#pragma unroll
+        for (int t = 0; t < kRouteTokens; ++t) acc[t] = 0.f;
+        const float* w = rw + size_t(e) * hidden;
+        for (int d = lane; d < hidden; d += 32) {
+            const float wv = w[d];
+#pragma unroll
+            for (int t = 0; t < kRouteTokens; ++t) acc[t] = fmaf(xs[t * hidden + d], wv, acc[t]);
+        }
+        const float b = rb[e];
+#pragma unroll
+        for (int t = 0; t < kRouteTokens; ++t) {
+            const float v = warp_sum(acc[t]);
+            if (lane == 0 && t < nt) logits[size_t(t0 + t) * experts + e] = bf16_round_f(v + b);
+        }
+    }
+    if (blockIdx.y != 0 || !xh) return;
+    // fp16 copy of x: one warp per token
+    for (int t = warp; t < nt; t += kRouteWarps) {
+        float amax = 0.f;
+        for (int d = lane; d < hidden; d += 32) amax = fmaxf(amax, fabsf(bf16_round_f(xs[t * hidden + d])));
+#pragma unroll
+        for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (lane == 0) s_amax[t] = amax;
+    }
+    __syncthreads();
+    for (int t = warp; t < nt; t += kRouteWarps) {
+        const float amax = s_amax[t];
+        int shift = 0;   // x = xh * 2^shift
+        if (amax > 0.f && isfinite(amax)) shift = int((__float_as_uint(amax) >> 23) & 0xff) - 127 - 13;
+        shift = max(-100, min(100, shift));
+        const float scale = __uint_as_float(uint32_t(127 - shift) << 23);   // 2^-shift
+        for (int d = lane; d < hidden; d += 32)
+            xh[size_t(t0 + t) * hidden + d] = __float2half_rn(bf16_round_f(xs[t * hidden + d]) * scale);
+        if (lane == 0) xshift[t0 + t] = shift;
+    }
+}
+
+// k rounds of arg-max (ties to the lowest expert index), then the softmax over the
+// selected logits only (gpt_oss_kernels.cu:681-726).  One warp per token.
+__global__ void moe_topk_kernel(const float* __restrict__ logits, int* __restrict__ selected,
+                                float* __restrict__ probs, int tokens, int experts, int topk)
+{
+    const int token = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (token >= tokens) return;
+    const float* l = logits + size_t(token) * experts;
+    float top[8];
+    int chosen[8];
+    for (int j = 0; j < topk; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;   // "none yet"
+        for (int e = lane; e < experts; e += 32) {
+            bool used = false;
+            for (int q = 0; q < j; ++q) used |= chosen[q] == e;
+            const float v = l[e];
+            if (!used && (arg == 0x7fffffff || v > best || (v == best && e < arg))) {
+                best = v;
+                arg = e;
+            }
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
+            if (oa != 0x7fffffff && (arg == 0x7fffffff || ov > best || (ov == best && oa < arg))) {
+                best = ov;
+                arg = oa;
+            }
+        }
+        chosen[j] = arg;
+        top[j] = best;
+    }
+    if (lane == 0) {
+        float total = 0.f;
+        for (int j = 0; j < topk; ++j) total += expf(top[j] - top[0]);
+        for (int j = 0; j < topk; ++j) {
+            selected[token * topk + j] = chosen[j];
+            probs[token * topk + j] = bf16_round_f(expf(top[j] - top[0]) / total);
+        }
+    }
+}
+
+// ------------------------------------------------------------ slot bucketing
+
+__device__ __forceinline__ bool expert_is_local(int e, const MoeShard& sh)
+{
+    if (sh.world <= 1) return true;
+    return sh.interleaved ? (e % sh.world) == sh.rank : (e >= sh.lo && e < sh.hi);
+}
+
+// counts[e] = number of routed slots of expert e (0 for experts of other ranks).
+__global__ void moe_count_kernel(const int* __restrict__ selected, int slots, int* __restrict__ counts, MoeShard sh)
+{
+    const int e = blockIdx.x;
+    __shared__ int s_part[32];
+    int c = 0;
+    if (expert_is_local(e, sh))
+        for (int i = threadIdx.x; i < slots; i += blockDim.x) c += selected[i] == e;
+    for (int off = 16; off; off >>= 1) c += __shfl_xor_sync(0xffffffffu, c, off);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int w = 0; w < int(blockDim.x >> 5); ++w) total += s_part[w];
+        counts[e] = total;
+    }
+}
+
+// Stable counting sort of the slots by expert (slot order preserved inside an
+// expert, like gpt_oss_marlin.cu:239-277) plus the task list: one task per block
+// of up to `rows_per_task` slots of one expert.  One CTA per expert.
+__global__ void __launch_bounds__(1024)
+moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restrict__ counts,
+                int* __restrict__ offsets, int* __restrict__ sorted, int4* __restrict__ tasks,
+                int* __restrict__ ntasks, int experts, int rows_per_task, MoeShard sh)
+{
+    const int e = blockIdx.x;
+    __shared__ int s_offset, s_task, s_warp[32], s_running;
+    if (threadIdx.x == 0) {
+        int off = 0, tk = 0;
+        for (int q = 0; q < e; ++q) {
+            off += counts[q];
+            tk += (counts[q] + rows_per_task - 1) / rows_per_task;
+        }
+        s_offset = off;
+        s_task = tk;
+        s_running = 0;
+        offsets[e] = off;
+        const int mine = counts[e];
+        for (int b = 0; b * rows_per_task < mine; ++b)
+            tasks[tk + b] = make_int4(e, off + b * rows_per_task, min(rows_per_task, mine - b * rows_per_task), 0);
+        if (e == experts - 1) {
+            offsets[experts] = off + mine;
+            *ntasks = tk + (mine + rows_per_task - 1) / rows_per_task;
+        }
+    }
+    __syncthreads();
+    if (counts[e] == 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int base = 0; base < slots; base += blockDim.x) {
+        const int i = base + threadIdx.x;
+        const bool hit = i < slots && selected[i] == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) s_warp[warp] = __popc(ballot);
+        __syncthreads();
+        int before = s_running;
+        for (int w = 0; w < warp; ++w) before += s_warp[w];
+        if (hit) sorted[s_offset + before + __popc(ballot & ((1u << lane) - 1u))] = i;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int total = 0;
+            for (int w = 0; w < int(blockDim.x >> 5); ++w) total += s_warp[w];
+            s_running += total;
+        }
+        __syncthreads();
+    }
+}
+
+// ------------------------------------------------- streaming expert kernel
+
+constexpr int kMoeWarps = 8;                       // consumer warps; one extra warp produces
+constexpr int kMoeStages = 4;
+constexpr int kMoeSegChunks = 2 * kMoeWarps;       // 16 chunks = 1024 columns per segment
+constexpr int kMoeSegBytes = kMoeSegChunks * kMxChunkBytes;
+constexpr int kMoeRows = 8;                        // slots per task (one MMA N-tile)
+
+struct MoeStreamParams {
+    const uint8_t* packed;      // [experts_local][matrix]
+    const __half* act_in;       // up: xh [tokens, K]; down: act [slots, K]
+    const int* xshift;          // up: per-token exponent of the fp16 copy; down: null
+    const int4* tasks;
+    const int* ntasks;
+    const int* sorted;
+    const float* bias;          // [experts_local, rows] fp32, original row order
+    __half* act_out;            // up: [slots, inter]
+    float* vals_out;            // down: [slots, hidden]
+    int* fault;
+    int k, rows;                // K columns, logical rows of one expert matrix
+    int strips, chunks;
+    int topk;
+    int expert_base, expert_div;   // stored expert = (e - expert_base) / expert_div
+    int bias_by_global;            // bias rows are indexed by the global expert id
+    float limit;
+    size_t matrix_bytes;
+};
+
+struct MoeSmem {
+    int ring, red, bars, meta, xs, total, x_stride;
+};
+__host__ __device__ inline MoeSmem moe_smem_plan(int k)
+{
+    MoeSmem p;
+    p.x_stride = k * 2 + 64 + ((k * 2) % 128 == 0 ? 0 : 64);   // keep (stride mod 128) == 64
+    p.ring = 0;
+    p.red = p.ring + kMoeStages * kMoeSegBytes;
+    p.bars = p.red + 2 * kMoeWarps * 128 * 4;
+    p.meta = p.bars + 2 * kMoeStages * 8;            // row slot ids and shifts
+    p.xs = (p.meta + 2 * kMoeRows * 4 + 127) & ~127;
+    p.total = p.xs + (kMoeRows + 1) * p.x_stride;
+    return p;
+}
+
+// Persistent CTAs over the flattened list of (task, strip) items; a task is up to
+// 8 routed slots of one expert.  The producer warp streams each strip of that
+// expert's matrix (codes and scales together) in 16-chunk segments; the 8
+// consumer warps split a segment along K, convert e2m1 pairs to fp16 pairs with
+// one instruction each, and run m16n8k16 fp16 MMAs whose N dimension is the
+// task's slots.  Each 32-column group's fp32 partial sum is scaled by its e8m0
+// factor.  kUp: epilogue = bias + clamped SwiGLU -> activation (bf16-valued,
+// stored as fp16); else bias -> per-slot values for the combine.
+template <bool kUp, bool kCareful>
+__global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const MoeStreamParams p)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    const MoeSmem plan = moe_smem_plan(p.k);
+    uint8_t* ring = smem + plan.ring;
+    float* red = reinterpret_cast<float*>(smem + plan.red);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + plan.bars);
+    uint64_t* empty = full + kMoeStages;
+    int* row_slot = reinterpret_cast<int*>(smem + plan.meta);
+    int* row_shift = row_slot + kMoeRows;
+    uint8_t* xs = smem + plan.xs;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMoeStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kMoeWarps);
+        }
+        fence_barrier_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();   // the task list and activations come from earlier kernels of this call
+
+    const int ntasks = *p.ntasks;
+    const long long total = (long long)ntasks * p.strips;
+    const long long i0 = total * blockIdx.x / gridDim.x, i1 = total * (blockIdx.x + 1) / gridDim.x;
+    const int nseg = (p.chunks + kMoeSegChunks - 1) / kMoeSegChunks;
+    const size_t strip_bytes = size_t(p.chunks) * kMxChunkBytes;
+
+    if (warp == kMoeWarps) {
+        if (lane == 0) {
+            long long n = 0;
+            for (long long it = i0; it < i1; ++it) {
+                const int task = int(it / p.strips), strip = int(it % p.strips);
+                const int e = (p.tasks[task].x - p.expert_base) / p.expert_div;
+                const uint8_t* src = p.packed + size_t(e) * p.matrix_bytes + size_t(strip) * strip_bytes;
+                for (int seg = 0; seg < nseg; ++seg, ++n) {
+                    const int s = int(n % kMoeStages);
+                    if (n >= kMoeStages && !mbar_wait(&empty[s], uint32_t((n / kMoeStages) - 1) & 1)) {
+                        atomicExch(p.fault, 1);
+                        return;
+                    }
+                    const int nch = min(kMoeSegChunks, p.chunks - seg * kMoeSegChunks);
+                    const uint32_t bytes = uint32_t(nch) * kMxChunkBytes;
+                    mbar_expect_tx(&full[s], bytes);
+                    bulk_g2s(ring + size_t(s) * kMoeSegBytes, src + size_t(seg) * kMoeSegBytes, bytes, &full[s]);
+                }
+            }
+        }
+        return;
+    }
+
+    const int g = lane >> 2, t = lane & 3;
+    const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int cur_task = -1, task_rows = 0, task_expert = 0;
+    const uint8_t* xrow = xs;
+    bool ok = true;
+    int s = 0, phase = 0, parity = 0;
+
+    for (long long it = i0; it < i1; ++it) {
+        const int task = int(it / p.strips), strip = int(it % p.strips);
+        if (task != cur_task) {
+            // ---- new task: stage its rows.  All consumers have left the previous x tile.
+            named_barrier_sync(1, kMoeWarps * 32);
+            const int4 tk = p.tasks[task];
+            task_expert = tk.x;
+            task_rows = tk.z;
+            if (threadIdx.x < kMoeRows) {
+                int slot = -1, shift = 0;
+                if (int(threadIdx.x) < task_rows) {
+                    slot = p.sorted[tk.y + threadIdx.x];
+                    if (kUp) shift = p.xshift[slot / p.topk];
+                }
+                row_slot[threadIdx.x] = slot;
+                row_shift[threadIdx.x] = shift;
+            }
+            const int vec_per_row = (p.k * 2 + 15) / 16;       // K*2 bytes is a multiple of 16 (K % 8 == 0)
+            for (int i = threadIdx.x; i < (kMoeRows + 1) * (plan.x_stride / 16); i += kMoeWarps * 32) {
+                const int m = i / (plan.x_stride / 16), v = i % (plan.x_stride / 16);
+                uint4 val = make_uint4(0, 0, 0, 0);
+                if (m < task_rows && v < vec_per_row) {
+                    const int slot = p.sorted[tk.y + m];
+                    const size_t src_row = kUp ? size_t(slot / p.topk) : size_t(slot);
+                    val = *reinterpret_cast<const uint4*>(p.act_in + src_row * p.k + v * 8);
+                }
+                *reinterpret_cast<uint4*>(xs + size_t(m) * plan.x_stride + v * 16) = val;
+            }
+            named_barrier_sync(1, kMoeWarps * 32);
+            cur_task = task;
+            xrow = xs + size_t(g < task_rows ? g : kMoeRows) * plan.x_stride + t * 16;
+        }
+        for (int seg = 0; seg < nseg; ++seg) {
+            if (ok && !mbar_wait(&full[s], phase)) {
+                atomicExch(p.fault, 2);
+                ok = false;
+            }
+            const int nch = min(kMoeSegChunks, p.chunks - seg * kMoeSegChunks);
+            if (ok) {
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int c = 2 * warp + cc;
+                    if (c >= nch) break;
+                    const uint8_t* st = ring + s * kMoeSegBytes + c * kMxChunkBytes;
+                    const uint4 u = *reinterpret_cast<const uint4*>(st + lane * 16);
+                    const uint32_t sc = *reinterpret_cast<const uint32_t*>(st + 512 + g * 4);
+                    const int kbyte = (seg * kMoeSegChunks + c) * 128;      // 64 columns = 128 bytes of x
+                    const uint4 xa = *reinterpret_cast<const uint4*>(xrow + kbyte);
+                    const uint4 xb = *reinterpret_cast<const uint4*>(xrow + kbyte + 64);
+                    float tmp[4];
+                    // group 0: octets 0..3 (words x = row R, y = row R+8)
+                    {
+                        const uint32_t a0[4] = {e2m1x2_to_f16x2(u.x, 0), e2m1x2_to_f16x2(u.y, 0),
+                                                e2m1x2_to_f16x2(u.x, 1), e2m1x2_to_f16x2(u.y, 1)};
+                        const uint32_t a1[4] = {e2m1x2_to_f16x2(u.x, 2), e2m1x2_to_f16x2(u.y, 2),
+                                                e2m1x2_to_f16x2(u.x, 3), e2m1x2_to_f16x2(u.y, 3)};
+                        mma_f16_16816(tmp, a0, xa.x, xa.y, zero4);
+                        mma_f16_16816(tmp, a1, xa.z, xa.w, tmp);
+                        const float f_lo = e8m0_to_float<kCareful>(sc & 0xff);
+                        const float f_hi = e8m0_to_float<kCareful>((sc >> 8) & 0xff);
+                        acc[0] = fmaf(tmp[0], f_lo, acc[0]);
+                        acc[1] = fmaf(tmp[1], f_lo, acc[1]);
+                        acc[2] = fmaf(tmp[2], f_hi, acc[2]);
+                        acc[3] = fmaf(tmp[3], f_hi, acc[3]);
+                    }
+                    // group 1: octets 4..7 (words z = row R, w = row R+8)
+                    {
+                        const uint32_t a0[4] = {e2m1x2_to_f16x2(u.z, 0), e2m1x2_to_f16x2(u.w, 0),
+                                                e2m1x2_to_f16x2(u.z, 1), e2m1x2_to_f16x2(u.w, 1)};
+                        const uint32_t a1[4] = {e2m1x2_to_f16x2(u.z, 2), e2m1x2_to_f16x2(u.w, 2),
+                                                e2m1x2_to_f16x2(u.z, 3), e2m1x2_to_f16x2(u.w, 3)};
+                        mma_f16_16816(tmp, a0, xb.x, xb.y, zero4);
+                        mma_f16_16816(tmp, a1, xb.z, xb.w, tmp);
+                        const float f_lo = e8m0_to_float<kCareful>((sc >> 16) & 0xff);
+                        const float f_hi = e8m0_to_float<kCareful>(sc >> 24);
+                        acc[0] = fmaf(tmp[0], f_lo, acc[0]);
+                        acc[1] = fmaf(tmp[1], f_lo, acc[1]);
+                        acc[2] = fmaf(tmp[2], f_hi, acc[2]);
+                        acc[3] = fmaf(tmp[3], f_hi, acc[3]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            if (++s == kMoeStages) {
+                s = 0;
+                phase ^= 1;
+            }
+        }
+
+        // ---- end of a strip: reduce the warps' partial sums, then the epilogue.
+        // acc[0..1]: strip row R(g), slots 2t, 2t+1; acc[2..3]: strip row R(g)+8.
+        float* slotbuf = red + parity * (kMoeWarps * 128);
+        parity ^= 1;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            slotbuf[(warp * 4 + q) * 32 + lane] = acc[q];
+            acc[q] = 0.f;
+        }
+        named_barrier_sync(2, kMoeWarps * 32);
+        const int ebias = p.bias_by_global ? task_expert : (task_expert - p.expert_base) / p.expert_div;
+        if (kUp) {
+            // 64 outputs: (lane l, slot parity): gate from q = par, up from q = par + 2
+            if (threadIdx.x < 64) {
+                const int l = threadIdx.x & 31, par = threadIdx.x >> 5;
+                float gate = 0.f, up = 0.f;
+#pragma unroll
+                for (int w = 0; w < kMoeWarps; ++w) {
+                    gate += slotbuf[(w * 4 + par) * 32 + l];
+                    up += slotbuf[(w * 4 + par + 2) * 32 + l];
+                }
+                const int m = 2 * (l & 3) + par;
+                const int i = strip * 8 + row_of_g(l >> 2);          // intermediate channel
+                if (m < task_rows && 2 * i + 1 < p.rows) {
+                    const float sc2 = __uint_as_float(uint32_t(127 + row_shift[m]) << 23);   // 2^shift
+                    const float* b = p.bias + size_t(ebias) * p.rows + 2 * i;
+                    gate = fminf(bf16_round_f(bf16_round_f(gate * sc2) + b[0]), p.limit);
+                    up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(up * sc2) + b[1])));
+                    const float sig = bf16_round_f(1.f / (1.f + expf(-bf16_round_f(1.702f * gate))));
+                    const float glu = bf16_round_f(gate * sig);
+                    p.act_out[size_t(row_slot[m]) * (p.rows / 2) + i] = __float2half_rn(bf16_round_f(glu * bf16_round_f(up + 1.f)));
+                }
+            }
+        } else {
+            if (threadIdx.x < 128) {
+                const int l = threadIdx.x & 31, q = threadIdx.x >> 5;
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < kMoeWarps; ++w) v += slotbuf[(w * 4 + q) * 32 + l];
+                const int m = 2 * (l & 3) + (q & 1);
+                const int d = strip * 16 + row_of_g(l >> 2) + 8 * (q >> 1);
+                if (m < task_rows && d < p.rows)
+                    p.vals_out[size_t(row_slot[m]) * p.rows + d] =
+                        bf16_round_f(bf16_round_f(v) + p.bias[size_t(ebias) * p.rows + d]);
+            }
+        }
+    }
+    if (!ok)
+        for (int i = 0; i < kMoeStages; ++i) (void)mbar_wait(&full[i], 0);
+}
+
+// y[t,d] = bf(sum_j vals[t*k+j, d] * p[t,j]) over the local experts in router order
+// (gpt_oss_kernels.cu:907-921); the partial of an expert-sharded rank is left
+// unrounded (:920).
+template <typename YT>
+__global__ void moe_combine_kernel(const float* __restrict__ vals, const float* __restrict__ probs,
+                                   const int* __restrict__ selected, YT* __restrict__ y, int tokens, int hidden,
+                                   int topk, MoeShard sh, int round_output)
+{
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= size_t(tokens) * hidden) return;
+    const int token = int(idx / hidden), d = int(idx % hidden);
+    float r = 0.f;
+    for (int j = 0; j < topk; ++j) {
+        const int slot = token * topk + j;
+        if (!expert_is_local(selected[slot], sh)) continue;
+        r += vals[size_t(slot) * hidden + d] * probs[slot];
+    }
+    if (round_output) r = bf16_round_f(r);
+    if constexpr (sizeof(YT) == 4)
+        y[idx] = r;
+    else
+        y[idx] = __float2bfloat16_rn(r);
+}
+
+// ------------------------------------------------------------------ handle
+
+constexpr size_t kMaxDynamicSmem = 227 * 1024;
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens)
+{
+    MoeWorkspace w;
+    const size_t slots = size_t(tokens) * o.top_k;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t at = off;
+        off = align_up(off + bytes, 256);
+        return at;
+    };
+    w.logits = take(size_t(tokens) * o.experts * 4);
+    w.selected = take(slots * 4);
+    w.probs = take(slots * 4);
+    w.xshift = take(size_t(tokens) * 4);
+    w.xh = take(size_t(tokens) * o.hidden * 2);
+    w.counts = take(size_t(o.experts) * 4);
+    w.offsets = take(size_t(o.experts + 1) * 4);
+    w.sorted = take(slots * 4);
+    w.ntasks = take(4);
+    w.tasks = take((slots / kMoeRows + o.experts + 1) * 16);
+    w.act = take(slots * o.intermediate * 2);
+    w.vals = take(slots * o.hidden * 4);
+    w.total = off;
+    return w;
+}
+
+static int validate_options(const garnet_b200_moe_options* o)
+{
+    if (!o) return fail(GARNET_B200_INVALID_VALUE, "moe: null options");
+    if (o->abi != GARNET_B200_ABI || o->struct_size != int(sizeof(garnet_b200_moe_options)))
+        return fail(GARNET_B200_INVALID_VALUE, "moe: options abi/size mismatch (abi %d, size %d)", o->abi, o->struct_size);
+    if (o->hidden <= 0 || o->intermediate <= 0 || o->experts <= 0 || o->top_k <= 0)
+        return fail(GARNET_B200_INVALID_VALUE, "moe: hidden, intermediate, experts, top_k must be positive");
+    if (o->hidden % 32 || o->intermediate % 32)
+        return fail(GARNET_B200_INVALID_VALUE, "moe: hidden and intermediate must be multiples of 32");
+    if (o->top_k > 8 || o->top_k > o->experts)
+        return fail(GARNET_B200_INVALID_VALUE, "moe: top_k must be <= 8 and <= experts");
+    if (o->experts > 1024) return fail(GARNET_B200_NOT_SUPPORTED, "moe: more than 1024 experts");
+    if (o->io_dtype != GARNET_B200_FP32 && o->io_dtype != GARNET_B200_BF16)
+        return fail(GARNET_B200_INVALID_VALUE, "moe: io dtype must be fp32 or bf16");
+    if (!(o->limit > 0.f) || o->limit * (o->limit + 1.f) > 60000.f)
+        return fail(GARNET_B200_NOT_SUPPORTED, "moe: swiglu limit %g is outside the fp16 activation range", o->limit);
+    if (o->ep_world > 1) {
+        if (o->ep_rank < 0 || o->ep_rank >= o->ep_world)
+            return fail(GARNET_B200_INVALID_VALUE, "moe: ep_rank %d outside ep_world %d", o->ep_rank, o->ep_world);
+        if (!o->ep_interleaved && o->experts % o->ep_world)
+            return fail(GARNET_B200_INVALID_VALUE, "moe: experts not divisible by ep_world");
+    }
+    if (size_t(moe_smem_plan(std::max(o->hidden, o->intermediate)).total) > kMaxDynamicSmem)
+        return fail(GARNET_B200_NOT_SUPPORTED, "moe: hidden/intermediate too large for the streaming kernel");
+    return GARNET_B200_OK;
+}
+
+MoeShard Moe::shard() const
+{
+    MoeShard s{};
+    s.world = opt.ep_world > 1 ? opt.ep_world : 1;
+    s.rank = s.world > 1 ? opt.ep_rank : 0;
+    s.interleaved = opt.ep_interleaved;
+    const int per = opt.experts / s.world;
+    s.lo = s.interleaved ? 0 : s.rank * per;
+    s.hi = s.interleaved ? opt.experts : s.lo + per;
+    return s;
+}
+
+int Moe::local_experts() const
+{
+    const MoeShard s = shard();
+    if (s.world <= 1) return opt.experts;
+    return s.interleaved ? (opt.experts - s.rank + s.world - 1) / s.world : opt.experts / s.world;
+}
+
+Moe::~Moe()
+{
+    if (packed_up) cudaFree(packed_up);
+    if (packed_down) cudaFree(packed_down);
+    if (flag_dev) cudaFree(flag_dev);
+    if (fault_host) cudaFreeHost(fault_host);
+}
+
+template <bool U, bool C>
+static cudaError_t set_moe_attr()
+{
+    return cudaFuncSetAttribute(moe_stream_kernel<U, C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                int(kMaxDynamicSmem));
+}
+
+// weights[0..7] = in[1..8] of the reference operand list (gpt_oss_lowering.cpp:309-312):
+// router W, router b, gate_up blocks, gate_up scales, gate_up bias, down blocks,
+// down scales, down bias.  Expert tensors hold all experts, or only this rank's
+// when expert_weights_sharded is set (gpt_oss_weight_shard.h:76-92).
+int Moe::prepare(const void* const* weights, cudaStream_t stream)
+{
+    const int el = opt.expert_weights_sharded ? local_experts() : opt.experts;
+    geo_up = make_geom(kFormatMxfp4, 2 * opt.intermediate, opt.hidden, 32);
+    geo_down = make_geom(kFormatMxfp4, opt.hidden, opt.intermediate, 32);
+    stored_experts = local_experts();
+    GB_CUDA(cudaMalloc(&packed_up, geo_up.matrix_bytes() * stored_experts));
+    GB_CUDA(cudaMalloc(&packed_down, geo_down.matrix_bytes() * stored_experts));
+    GB_CUDA(cudaMalloc(&flag_dev, sizeof(int)));
+    GB_CUDA(cudaMemsetAsync(flag_dev, 0, sizeof(int), stream));
+    GB_CUDA(cudaHostAlloc(&fault_host, sizeof(int), cudaHostAllocMapped));
+    *fault_host = 0;
+    GB_CUDA(cudaHostGetDevicePointer(&fault_dev, fault_host, 0));
+
+    const MoeShard sh = shard();
+    // source expert index of stored expert s
+    auto src_expert = [&](int s) {
+        if (opt.expert_weights_sharded || sh.world <= 1) return s;
+        return sh.interleaved ? s * sh.world + sh.rank : sh.lo + s;
+    };
+    (void)el;
+    for (int pass = 0; pass < 2; ++pass) {
+        const PackGeom& geo = pass == 0 ? geo_up : geo_down;
+        const uint8_t* blocks = static_cast<const uint8_t*>(weights[pass == 0 ? 2 : 5]);
+        const uint8_t* scales = static_cast<const uint8_t*>(weights[pass == 0 ? 3 : 6]);
+        uint8_t* dst = pass == 0 ? packed_up : packed_down;
+        const size_t words = size_t(geo.strips_padded) * geo.chunks * (geo.chunk_data / 4);
+        const size_t nsc = size_t(geo.strips_padded) * 16 * geo.chunks * 2;
+        const size_t blk_per_expert = size_t(geo.rows) * geo.cols / 2, sc_per_expert = size_t(geo.rows) * geo.cols / 32;
+        // contiguous runs of source experts are repacked with one launch each
+        int s = 0;
+        while (s < stored_experts) {
+            int run = 1;
+            while (s + run < stored_experts && src_expert(s + run) == src_expert(s) + run) ++run;
+            const size_t e0 = size_t(src_expert(s));
+            mx_repack_codes_kernel<<<dim3(unsigned((words + 255) / 256), run), 256, 0, stream>>>(
+                blocks + e0 * blk_per_expert, dst + size_t(s) * geo.matrix_bytes(), geo, pass == 0);
+            mx_repack_scales_kernel<<<dim3(unsigned((nsc + 255) / 256), run), 256, 0, stream>>>(
+                scales + e0 * sc_per_expert, dst + size_t(s) * geo.matrix_bytes(), geo, pass == 0);
+            const size_t cnt = size_t(run) * sc_per_expert;
+            mx_scan_scales_kernel<<<unsigned((cnt + 255) / 256), 256, 0, stream>>>(scales + e0 * sc_per_expert, cnt,
+                                                                                 flag_dev);
+            s += run;
+        }
+    }
+    GB_CUDA(cudaGetLastError());
+    int flag = 0;
+    GB_CUDA(cudaMemcpyAsync(&flag, flag_dev, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    GB_CUDA(cudaStreamSynchronize(stream));
+    careful_scales = flag != 0;
+    // router and biases are borrowed from the caller (engine-owned constants)
+    router_w_ptr = static_cast<const float*>(weights[0]);
+    router_b_ptr = static_cast<const float*>(weights[1]);
+    up_bias_ptr = static_cast<const float*>(weights[4]);
+    down_bias_ptr = static_cast<const float*>(weights[7]);
+    GB_CUDA((set_moe_attr<true, true>()));
+    GB_CUDA((set_moe_attr<true, false>()));
+    GB_CUDA((set_moe_attr<false, true>()));
+    GB_CUDA((set_moe_attr<false, false>()));
+    return GARNET_B200_OK;
+}
+
+int Moe::route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
+               cudaStream_t stream)
+{
+    const size_t smem = size_t(kRouteTokens) * opt.hidden * sizeof(float);
+    if (smem > kMaxDynamicSmem) return fail(GARNET_B200_NOT_SUPPORTED, "moe_route: hidden too large");
+    // spread the experts over enough CTAs to fill the machine at small token counts
+    const int token_ctas = (tokens + kRouteTokens - 1) / kRouteTokens;
+    int per_cta = opt.experts;
+    while (per_cta > kRouteWarps && token_ctas * ((opt.experts + per_cta - 1) / per_cta) < 2 * kSmCount) per_cta = (per_cta + 1) / 2;
+    per_cta = std::max(per_cta, std::min(opt.experts, kRouteWarps));
+    const dim3 grid(token_ctas, (opt.experts + per_cta - 1) / per_cta);
+    if (opt.io_dtype == GARNET_B200_FP32) {
+        GB_CUDA(cudaFuncSetAttribute(moe_route_scores_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        moe_route_scores_kernel<float><<<grid, kRouteWarps * 32, smem, stream>>>(
+            static_cast<const float*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens, opt.hidden,
+            opt.experts, per_cta);
+    } else {
+        GB_CUDA(cudaFuncSetAttribute(moe_route_scores_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        moe_route_scores_kernel<__nv_bfloat16><<<grid, kRouteWarps * 32, smem, stream>>>(
+            static_cast<const __nv_bfloat16*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens,
+            opt.hidden, opt.experts, per_cta);
+    }
+    moe_topk_kernel<<<(tokens * 32 + 255) / 256, 256, 0, stream>>>(logits, selected, probs, tokens, opt.experts,
+                                                                 opt.top_k);
+    GB_CUDA(cudaGetLastError());
+    return GARNET_B200_OK;
+}
+
+int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream)
+{
+    const PackGeom& geo = up ? geo_up : geo_down;
+    const MoeShard sh = shard();
+    MoeStreamParams p;
+    p.packed = up ? packed_up : packed_down;
+    p.act_in = up ? w.xh : w.act;
+    p.xshift = up ? w.xshift : nullptr;
+    p.tasks = w.tasks;
+    p.ntasks = w.ntasks;
+    p.sorted = w.sorted;
+    p.bias = up ? up_bias_ptr : down_bias_ptr;
+    p.act_out = w.act;
+    p.vals_out = w.vals;
+    p.fault = fault_dev;
+    p.k = geo.cols;
+    p.rows = geo.rows;
+    p.strips = geo.strips;
+    p.chunks = geo.chunks;
+    p.topk = opt.top_k;
+    // stored expert index of global expert e; biases follow the same indexing as
+    // the expert tensors the caller handed over
+    p.expert_base = (sh.world > 1 && !sh.interleaved) ? sh.lo : (sh.world > 1 ? sh.rank : 0);
+    p.expert_div = (sh.world > 1 && sh.interleaved) ? sh.world : 1;
+    p.limit = opt.limit;
+    p.matrix_bytes = geo.matrix_bytes();
+    p.bias_by_global = (!opt.expert_weights_sharded && sh.world > 1) ? 1 : 0;
+
+    const size_t smem = size_t(moe_smem_plan(geo.cols).total);
+    const int ctas_per_sm = std::max(1, std::min(2, int(kMaxDynamicSmem / (smem + 1024))));
+    // upper bound of (task, strip) items: every slot its own task
+    const long long max_items = (long long)tokens * opt.top_k * geo.strips;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(std::max<long long>(1, std::min<long long>(max_items, (long long)kSmCount * ctas_per_sm))));
+    cfg.blockDim = dim3((kMoeWarps + 1) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+    if (up && careful_scales) GB_CUDA(cudaLaunchKernelEx(&cfg, moe_stream_kernel<true, true>, p));
+    else if (up) GB_CUDA(cudaLaunchKernelEx(&cfg, moe_stream_kernel<true, false>, p));
+    else if (careful_scales) GB_CUDA(cudaLaunchKernelEx(&cfg, moe_stream_kernel<false, true>, p));
+    else GB_CUDA(cudaLaunchKernelEx(&cfg, moe_stream_kernel<false, false>, p));
+    return GARNET_B200_OK;
+}
+
+int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cudaStream_t stream)
+{
+    if (tokens <= 0) return fail(GARNET_B200_INVALID_VALUE, "moe_run: tokens must be positive");
+    if (!x || !y || !ws) return fail(GARNET_B200_INVALID_VALUE, "moe_run: null pointer");
+    const MoeWorkspace plan = moe_workspace_plan(opt, tokens);
+    if (ws_bytes < plan.total) return fail(GARNET_B200_INVALID_VALUE, "moe_run: workspace too small (%zu < %zu)", ws_bytes, plan.total);
+    if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(GARNET_B200_INVALID_VALUE, "moe_run: workspace must be 256-byte aligned");
+    uint8_t* b = static_cast<uint8_t*>(ws);
+    MoeWorkspacePtrs w;
+    w.logits = reinterpret_cast<float*>(b + plan.logits);
+    w.selected = reinterpret_cast<int*>(b + plan.selected);
+    w.probs = reinterpret_cast<float*>(b + plan.probs);
+    w.xshift = reinterpret_cast<int*>(b + plan.xshift);
+    w.xh = reinterpret_cast<__half*>(b + plan.xh);
+    w.counts = reinterpret_cast<int*>(b + plan.counts);
+    w.offsets = reinterpret_cast<int*>(b + plan.offsets);
+    w.sorted = reinterpret_cast<int*>(b + plan.sorted);
+    w.ntasks = reinterpret_cast<int*>(b + plan.ntasks);
+    w.tasks = reinterpret_cast<int4*>(b + plan.tasks);
+    w.act = reinterpret_cast<__half*>(b + plan.act);
+    w.vals = reinterpret_cast<float*>(b + plan.vals);
+
+    if (int rc = route(x, w.logits, w.selected, w.probs, w.xh, w.xshift, tokens, stream)) return rc;
+    const int slots = tokens * opt.top_k;
+    const MoeShard sh = shard();
+    moe_count_kernel<<<opt.experts, 256, 0, stream>>>(w.selected, slots, w.counts, sh);
+    moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(w.selected, slots, w.counts, w.offsets, w.sorted, w.tasks,
+                                                     w.ntasks, opt.experts, kMoeRows, sh);
+    GB_CUDA(cudaGetLastError());
+    if (int rc = launch_stream(true, w, tokens, stream)) return rc;
+    if (int rc = launch_stream(false, w, tokens, stream)) return rc;
+    const size_t n = size_t(tokens) * opt.hidden;
+    const int round_output = sh.world > 1 ? 0 : 1;
+    if (opt.io_dtype == GARNET_B200_FP32)
+        moe_combine_kernel<float><<<unsigned((n + 255) / 256), 256, 0, stream>>>(
+            w.vals, w.probs, w.selected, static_cast<float*>(y), tokens, opt.hidden, opt.top_k, sh, round_output);
+    else
+        moe_combine_kernel<__nv_bfloat16><<<unsigned((n + 255) / 256), 256, 0, stream>>>(
+            w.vals, w.probs, w.selected, static_cast<__nv_bfloat16*>(y), tokens, opt.hidden, opt.top_k, sh,
+            round_output);
+    GB_CUDA(cudaGetLastError());
+    return GARNET_B200_OK;
+}
+
+}  // namespace gb200
+
+using namespace gb200;
+
+extern "C" {
+
+int garnet_b200_mxfp4_decode(const uint8_t* d_blocks, const uint8_t* d_scales, float* d_out, int rows, void* stream)
+{
+    if (!d_blocks || !d_scales || !d_out || rows <= 0) return fail(GARNET_B200_INVALID_VALUE, "mxfp4_decode: bad argument");
+    mx_decode_rows_kernel<<<(rows * 4 + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(d_blocks, d_scales,
+                                                                                                d_out, rows);
+    GB_CUDA(cudaGetLastError());
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_moe_workspace(const garnet_b200_moe_options* o, int tokens, size_t* bytes)
+{
+    if (int rc = validate_options(o)) return rc;
+    if (!bytes || tokens <= 0) return fail(GARNET_B200_INVALID_VALUE, "moe_workspace: bad argument");
+    *bytes = moe_workspace_plan(*o, tokens).total;
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_moe_create(const garnet_b200_moe_options* o, const void* const* weights, void* stream,
+                           garnet_b200_moe_t* out)
+{
+    if (!out) return fail(GARNET_B200_INVALID_VALUE, "moe_create: null output handle");
+    *out = nullptr;
+    if (int rc = validate_options(o)) return rc;
+    if (!weights) return fail(GARNET_B200_INVALID_VALUE, "moe_create: null weight list");
+    for (int i = 0; i < 8; ++i)
+        if (!weights[i]) return fail(GARNET_B200_INVALID_VALUE, "moe_create: weight operand %d is null", i + 1);
+    Moe* h = new (std::nothrow) Moe();
+    if (!h) return fail(GARNET_B200_OUT_OF_MEMORY, "moe_create: host allocation failed");
+    h->opt = *o;
+    if (int rc = h->prepare(weights, static_cast<cudaStream_t>(stream))) {
+        delete h;
+        return rc;
+    }
+    *out = reinterpret_cast<garnet_b200_moe_t>(h);
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_moe_run(garnet_b200_moe_t hh, const void* d_x, void* d_y, void* d_workspace, size_t workspace_bytes,
+                        int tokens, void* stream)
+{
+    Moe* h = reinterpret_cast<Moe*>(hh);
+    if (!h) return fail(GARNET_B200_INVALID_VALUE, "moe_run: null handle");
+    return h->run(d_x, d_y, d_workspace, workspace_bytes, tokens, static_cast<cudaStream_t>(stream));
+}
+
+int garnet_b200_moe_route(garnet_b200_moe_t hh, const void* d_x, int* d_selected, float* d_probs, float* d_logits,
+                          int tokens, void* stream)
+{
+    Moe* h = reinterpret_cast<Moe*>(hh);
+    if (!h) return fail(GARNET_B200_INVALID_VALUE, "moe_route: null handle");
+    if (!d_x || !d_selected || !d_probs || !d_logits || tokens <= 0)
+        return fail(GARNET_B200_INVALID_VALUE, "moe_route: bad argument");
+    return h->route(d_x, d_logits, d_selected, d_probs, nullptr, nullptr, tokens, static_cast<cudaStream_t>(stream));
+}
+
+int garnet_b200_moe_dequant(garnet_b200_moe_t hh, int which, int stored_expert, float* d_out, void* stream)
+{
+    Moe* h = reinterpret_cast<Moe*>(hh);
+    if (!h || !d_out || stored_expert < 0 || stored_expert >= h->stored_experts || (which != 0 && which != 1))
+        return fail(GARNET_B200_INVALID_VALUE, "moe_dequant: bad argument");
+    const PackGeom& geo = which == 0 ? h->geo_up : h->geo_down;
+    const size_t total = size_t(geo.rows) * geo.cols / 2;
+    mx_dequant_kernel<<<unsigned((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        which == 0 ? h->packed_up : h->packed_down, d_out, geo, which == 0, stored_expert);
+    GB_CUDA(cudaGetLastError());
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_moe_fault(garnet_b200_moe_t hh)
+{
+    Moe* h = reinterpret_cast<Moe*>(hh);
+    return h && h->fault_host ? *h->fault_host : -1;
+}
+
+void garnet_b200_moe_destroy(garnet_b200_moe_t hh) { delete reinterpret_cast<Moe*>(hh); }
+
+}  // extern "C"

@@ -1,0 +1,69 @@
+// Host-side state of one gpt_oss_moe_mxfp4 operator (the object behind
+// garnet_b200_moe_t).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/garnet_b200.h"
+#include "layout.h"
+
+namespace gb200 {
+
+// Which experts this rank computes: all (world <= 1), a contiguous block
+// [lo, hi), or every world-th expert (the reference's 2-way rule
+// expert % 2 == rank, gpt_oss_kernels.cu:771).
+struct MoeShard {
+    int world, rank, interleaved, lo, hi;
+};
+
+// Byte offsets of the regions of the caller's workspace.
+struct MoeWorkspace {
+    size_t logits, selected, probs, xshift, xh, counts, offsets, sorted, ntasks, tasks, act, vals, total;
+};
+
+struct MoeWorkspacePtrs {
+    float* logits;
+    int* selected;
+    float* probs;
+    int* xshift;
+    __half* xh;
+    int* counts;
+    int* offsets;
+    int* sorted;
+    int* ntasks;
+    int4* tasks;
+    __half* act;
+    float* vals;
+};
+
+MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens);
+
+struct Moe {
+    garnet_b200_moe_options opt{};
+    PackGeom geo_up{}, geo_down{};
+    int stored_experts = 0;            // experts whose packed weights this handle holds
+    uint8_t* packed_up = nullptr;      // [stored_experts][geo_up.matrix_bytes()]
+    uint8_t* packed_down = nullptr;
+    const float* router_w_ptr = nullptr;   // borrowed constants
+    const float* router_b_ptr = nullptr;
+    const float* up_bias_ptr = nullptr;
+    const float* down_bias_ptr = nullptr;
+    bool careful_scales = false;       // some e8m0 byte is 0 or 255
+    int* flag_dev = nullptr;
+    int* fault_host = nullptr;
+    int* fault_dev = nullptr;
+
+    ~Moe();
+    MoeShard shard() const;
+    int local_experts() const;
+    int prepare(const void* const* weights, cudaStream_t stream);
+    int route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
+              cudaStream_t stream);
+    int launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream);
+    int run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cudaStream_t stream);
+};
+
+}  // namespace gb200

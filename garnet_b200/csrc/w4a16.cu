@@ -176,11 +176,6 @@ struct StreamParams {
     int scale_dtype;     // GARNET_B200_FP16 / GARNET_B200_BF16
 };
 
-__device__ __forceinline__ void named_barrier_sync(int id, int threads)
-{
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
 // Two int4 codes -> bf16x2 {128 + (q+8), ...}: the biased form, without the
 // subtraction.  The bias is removed once per (batch row, chunk) from the
 // accumulated sum: sum_k (136 + q_k) x_k - 136 * sum_k x_k.

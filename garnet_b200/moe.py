@@ -1,0 +1,120 @@
+"""Host-side mirror of the reference's gpt-oss MoE operator for the CUDA path.
+
+`GptOssMoe` follows Garnet::GptOssMarlin (plugins/gpt_oss/include/gpt_oss_marlin.h:17-30):
+construct with the options, query `workspace_bytes(tokens)`, `run(x)`.  Operands
+keep the order and original checkpoint layout of the reference operator
+`gpt_oss_moe_mxfp4` (src/backends/tensorrt/gpt_oss_lowering.cpp:309-312).  All
+compute happens in libgarnet_b200.so through the C ABI."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ._lib import BF16, FP32, check, lib
+
+
+class MoeOptions(ctypes.Structure):
+    _fields_ = [("abi", ctypes.c_int), ("struct_size", ctypes.c_int), ("hidden", ctypes.c_int),
+                ("intermediate", ctypes.c_int), ("experts", ctypes.c_int), ("top_k", ctypes.c_int),
+                ("prefill", ctypes.c_int), ("ep_rank", ctypes.c_int), ("ep_world", ctypes.c_int),
+                ("ep_interleaved", ctypes.c_int), ("expert_weights_sharded", ctypes.c_int),
+                ("io_dtype", ctypes.c_int), ("limit", ctypes.c_float)]
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class GptOssMoe:
+    def __init__(self, hidden: int, intermediate: int, experts: int, top_k: int, limit: float = 7.0,
+                 io_dtype: torch.dtype = torch.float32, ep_rank: int = 0, ep_world: int = 1,
+                 ep_interleaved: bool = False, expert_weights_sharded: bool = False, prefill: int = 0):
+        self.opt = MoeOptions(abi=1, struct_size=ctypes.sizeof(MoeOptions), hidden=hidden,
+                              intermediate=intermediate, experts=experts, top_k=top_k, prefill=prefill,
+                              ep_rank=ep_rank, ep_world=ep_world, ep_interleaved=int(ep_interleaved),
+                              expert_weights_sharded=int(expert_weights_sharded),
+                              io_dtype=FP32 if io_dtype == torch.float32 else BF16, limit=limit)
+        self.io_dtype = io_dtype
+        self._h = ctypes.c_void_p(None)
+        self._keep = None
+        self._ws = None
+
+    # GptOssMarlin::Workspace (gpt_oss_marlin.h:25)
+    def workspace_bytes(self, tokens: int) -> int:
+        out = ctypes.c_size_t(0)
+        check(lib().garnet_b200_moe_workspace(ctypes.byref(self.opt), tokens, ctypes.byref(out)))
+        return out.value
+
+    def prepare(self, router_w, router_b, gu_blocks, gu_scales, gu_bias, dn_blocks, dn_scales, dn_bias) -> "GptOssMoe":
+        self.close()
+        tensors = [router_w.float(), router_b.float(), gu_blocks, gu_scales, gu_bias.float(), dn_blocks, dn_scales,
+                   dn_bias.float()]
+        tensors = [t.contiguous() for t in tensors]
+        if not all(t.is_cuda for t in tensors):
+            raise ValueError("prepare needs device-resident operands")
+        arr = (ctypes.c_void_p * 8)(*[t.data_ptr() for t in tensors])
+        h = ctypes.c_void_p(None)
+        check(lib().garnet_b200_moe_create(ctypes.byref(self.opt), arr, _stream_ptr(), ctypes.byref(h)))
+        self._h = h
+        self._keep = tensors            # router weights and biases are borrowed by the handle
+        return self
+
+    def _workspace(self, tokens: int, device) -> torch.Tensor:
+        need = self.workspace_bytes(tokens)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=device)
+        return self._ws
+
+    # GptOssMarlin::Run (gpt_oss_marlin.h:28-29)
+    def run(self, x: torch.Tensor, out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+        if x.dtype != self.io_dtype or not x.is_cuda:
+            raise ValueError("run needs a CUDA tensor of the operator's io dtype")
+        x2 = x.reshape(-1, self.opt.hidden).contiguous()
+        tokens = x2.shape[0]
+        y = out if out is not None else torch.empty_like(x2)
+        ws = workspace if workspace is not None else self._workspace(tokens, x.device)
+        check(lib().garnet_b200_moe_run(self._h, x2.data_ptr(), y.data_ptr(), ws.data_ptr(), ws.numel(), tokens,
+                                        _stream_ptr()))
+        return y
+
+    # RunGptOssMoeRoute (gpt_oss_kernels.h:54-56)
+    def route(self, x: torch.Tensor):
+        x2 = x.reshape(-1, self.opt.hidden).contiguous()
+        tokens = x2.shape[0]
+        logits = torch.empty(tokens, self.opt.experts, dtype=torch.float32, device=x.device)
+        selected = torch.empty(tokens, self.opt.top_k, dtype=torch.int32, device=x.device)
+        probs = torch.empty(tokens, self.opt.top_k, dtype=torch.float32, device=x.device)
+        check(lib().garnet_b200_moe_route(self._h, x2.data_ptr(), selected.data_ptr(), probs.data_ptr(),
+                                          logits.data_ptr(), tokens, _stream_ptr()))
+        return logits, selected, probs
+
+    def dequantized(self, which: int, stored_expert: int) -> torch.Tensor:
+        rows, cols = (2 * self.opt.intermediate, self.opt.hidden) if which == 0 else (self.opt.hidden, self.opt.intermediate)
+        out = torch.empty(rows, cols, dtype=torch.float32, device="cuda")
+        check(lib().garnet_b200_moe_dequant(self._h, which, stored_expert, out.data_ptr(), _stream_ptr()))
+        return out
+
+    def fault(self) -> int:
+        return lib().garnet_b200_moe_fault(self._h)
+
+    def close(self) -> None:
+        if self._h:
+            lib().garnet_b200_moe_destroy(self._h)
+            self._h = ctypes.c_void_p(None)
+        self._keep = None
+        self._ws = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def mxfp4_decode(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """rows x 32 MXFP4 values -> fp32 (TestGptOssMxfp4Decode)."""
+    rows = scales.numel()
+    out = torch.empty(rows, 32, dtype=torch.float32, device=blocks.device)
+    check(lib().garnet_b200_mxfp4_decode(blocks.data_ptr(), scales.data_ptr(), out.data_ptr(), rows, _stream_ptr()))
+    return out

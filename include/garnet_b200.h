@@ -129,6 +129,80 @@ int garnet_b200_w4a16_fault(garnet_b200_w4a16_t h);
 
 void garnet_b200_w4a16_destroy(garnet_b200_w4a16_t h);
 
+/* ---- gpt-oss MXFP4 mixture of experts (`gpt_oss_moe_mxfp4`) -------------------
+ * Replaces the free functions below the TensorRT plugin:
+ *   size_t GptOssMoeWorkspace(int tokens, const GptOssOptions&) and
+ *   cudaError_t RunGptOssMoe(const void* const* in, float* y, void* workspace, int tokens,
+ *                            const GptOssOptions&, cudaStream_t)
+ * (plugins/gpt_oss/include/gpt_oss_kernels.h:41-43), and the stateful
+ * GptOssMarlin{ctor, Workspace, Run} (plugins/gpt_oss/include/gpt_oss_marlin.h:17-30).
+ *
+ * Options mirror the GptOssOptions fields the MoE uses
+ * (plugins/gpt_oss/include/gpt_oss_kernels.h:8-20): hidden, intermediate, experts,
+ * topK, prefill, limit, tpRank (-> ep_rank with ep_world = 2, ep_interleaved = 1),
+ * expertWeightsSharded.  `abi` and `struct_size` version the struct the way the
+ * reference versions its module bridge (src/model/operator_module_bridge.h:6-14). */
+typedef struct garnet_b200_moe_options {
+    int abi;                    /* GARNET_B200_ABI */
+    int struct_size;            /* sizeof(garnet_b200_moe_options) */
+    int hidden;
+    int intermediate;
+    int experts;
+    int top_k;
+    int prefill;                /* informational; the kernel choice follows the token count */
+    int ep_rank;                /* expert-parallel rank; ignored when ep_world <= 1 */
+    int ep_world;               /* 0 or 1 = unsharded */
+    int ep_interleaved;         /* 1: expert e belongs to rank e % ep_world (reference rule);
+                                   0: contiguous blocks of experts / ep_world */
+    int expert_weights_sharded; /* expert tensors (and biases) hold only this rank's experts */
+    int io_dtype;               /* GARNET_B200_FP32 (reference carrier: fp32 holding bf16 values) or GARNET_B200_BF16 */
+    float limit;                /* swiglu clamp, 7 for gpt-oss */
+} garnet_b200_moe_options;
+
+typedef struct garnet_b200_moe* garnet_b200_moe_t;
+
+/* Caller-provided workspace size for `tokens` tokens.  GptOssMoeWorkspace
+ * (gpt_oss_kernels.h:41). */
+int garnet_b200_moe_workspace(const garnet_b200_moe_options* options, int tokens, size_t* bytes);
+
+/* Creates the operator.  `weights[0..7]` are operands in[1..8] of the reference
+ * operand list (src/backends/tensorrt/gpt_oss_lowering.cpp:309-312), device
+ * resident, original checkpoint layout: router W [E,H] f32, router b [E] f32,
+ * gate_up blocks u8 [E,2I,H/32,16], gate_up scales u8 [E,2I,H/32], gate_up bias
+ * [E,2I] f32, down blocks [E,H,I/32,16], down scales [E,H,I/32], down bias [E,H]
+ * f32.  Expert blocks and scales are repacked into handle-owned memory (one
+ * stream synchronise); router weights and biases are borrowed and must outlive
+ * the handle.  GptOssMarlin constructor + first-run prepare
+ * (plugins/gpt_oss/cuda/gpt_oss_marlin.cu:415-499). */
+int garnet_b200_moe_create(const garnet_b200_moe_options* options, const void* const* weights, void* stream,
+                           garnet_b200_moe_t* out);
+
+/* y[tokens, hidden] = MoE(x[tokens, hidden]); x and y are of io_dtype.  No
+ * allocation, no synchronisation.  RunGptOssMoe / GptOssMarlin::Run
+ * (gpt_oss_kernels.h:42-43, gpt_oss_marlin.h:28-29).  With ep_world > 1 the output
+ * is this rank's unrounded partial sum (gpt_oss_kernels.cu:810). */
+int garnet_b200_moe_run(garnet_b200_moe_t h, const void* d_x, void* d_y, void* d_workspace, size_t workspace_bytes,
+                        int tokens, void* stream);
+
+/* Router only: bf16-rounded logits [tokens, experts], top-k expert ids
+ * [tokens, top_k] and bf16-rounded probabilities.  RunGptOssMoeRoute
+ * (gpt_oss_kernels.h:54-56). */
+int garnet_b200_moe_route(garnet_b200_moe_t h, const void* d_x, int* d_selected, float* d_probs, float* d_logits,
+                          int tokens, void* stream);
+
+/* Decodes rows x 32 MXFP4 values (16 bytes and one e8m0 byte per row) to fp32.
+ * TestGptOssMxfp4Decode (gpt_oss_kernels.h:65). */
+int garnet_b200_mxfp4_decode(const uint8_t* d_blocks, const uint8_t* d_scales, float* d_out, int rows, void* stream);
+
+/* Writes one stored expert matrix (which = 0: gate_up [2I,H], 1: down [H,I]) as
+ * fp32 in the original row order, decoded from the packed tiles. */
+int garnet_b200_moe_dequant(garnet_b200_moe_t h, int which, int stored_expert, float* d_out, void* stream);
+
+/* Non-zero when a bounded device-side wait gave up (see garnet_b200_w4a16_fault). */
+int garnet_b200_moe_fault(garnet_b200_moe_t h);
+
+void garnet_b200_moe_destroy(garnet_b200_moe_t h);
+
 #ifdef __cplusplus
 }
 #endif

@@ -75,7 +75,7 @@ def lib() -> ctypes.CDLL:
         L.orc_moe_experts.argtypes = [_f32p, _i32p, _f32p, _u8p, _u8p, _f32p, _u8p, _u8p, _f32p,
                                       ctypes.c_long, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                       ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int,
-                                      ctypes.c_int, ctypes.c_int, ctypes.c_int, _f32p]
+                                      ctypes.c_int, ctypes.c_int, ctypes.c_int, _f32p, _f32p]
         _lib = L
     return _lib
 
@@ -215,7 +215,9 @@ def moe_route(x, router_w, router_b, experts, topk):
 
 def moe_experts(x, selected, probs, gu_blocks, gu_scales, gu_bias, dn_blocks, dn_scales, dn_bias,
                 hidden, inter, experts, topk, limit=7.0, expert_lo=0, expert_hi=None,
-                modulo=0, residue=0, round_output=True) -> np.ndarray:
+                modulo=0, residue=0, round_output=True, want_mass=False):
+    """Experts for a given routing.  With want_mass, also returns
+    sum_j |per-slot value| * p_j, the scale of the summands of each output."""
     x = _c(x, np.float32).reshape(-1, hidden)
     T = x.shape[0]
     sel = _c(selected, np.int32)
@@ -223,12 +225,13 @@ def moe_experts(x, selected, probs, gu_blocks, gu_scales, gu_bias, dn_blocks, dn
     gb, gs, gbi = _c(gu_blocks, np.uint8), _c(gu_scales, np.uint8), _c(gu_bias, np.float32)
     db, ds, dbi = _c(dn_blocks, np.uint8), _c(dn_scales, np.uint8), _c(dn_bias, np.float32)
     y = np.empty((T, hidden), dtype=np.float32)
+    mass = np.empty((T, hidden), dtype=np.float32) if want_mass else None
     lib().orc_moe_experts(_p(x, _f32p), _p(sel, _i32p), _p(pr, _f32p), _p(gb, _u8p), _p(gs, _u8p),
                           _p(gbi, _f32p), _p(db, _u8p), _p(ds, _u8p), _p(dbi, _f32p), T, hidden,
                           inter, experts, topk, limit, expert_lo,
                           experts if expert_hi is None else expert_hi, modulo, residue,
-                          1 if round_output else 0, _p(y, _f32p))
-    return y
+                          1 if round_output else 0, _p(y, _f32p), _p(mass, _f32p) if want_mass else None)
+    return (y, mass) if want_mass else y
 
 
 def moe_forward(x, router_w, router_b, gu_blocks, gu_scales, gu_bias, dn_blocks, dn_scales, dn_bias,
@@ -238,20 +241,3 @@ def moe_forward(x, router_w, router_b, gu_blocks, gu_scales, gu_bias, dn_blocks,
     y = moe_experts(x, sel, pr, gu_blocks, gu_scales, gu_bias, dn_blocks, dn_scales, dn_bias,
                     hidden, inter, experts, topk, limit)
     return y, logits, sel, pr
-
-
-def route_fragile_tokens(x, router_w, router_b, topk, rel=1e-5) -> np.ndarray:
-    """Boolean [T]: tokens whose routing could legitimately differ between two
-    correct fp32 implementations.  A logit is fragile when its float64 value lies
-    within `rel * sum_d |x_d w_d|` of a bf16 rounding midpoint, so that a
-    different fp32 summation order may round it the other way.  Only tokens free
-    of fragile logits are compared exactly in routing tests."""
-    x64 = np.asarray(x, np.float64)
-    w64 = np.asarray(router_w, np.float64)
-    l64 = x64 @ w64.T + np.asarray(router_b, np.float64)
-    mass = np.abs(x64) @ np.abs(w64).T + np.abs(np.asarray(router_b, np.float64))
-    down = bf16_round(l64.astype(np.float32))
-    bits = down.view(np.uint32)
-    ulp = np.abs(((bits + 0x10000).view(np.float32) - down).astype(np.float64))
-    mid_dist = np.abs(np.abs(l64 - down.astype(np.float64)) - 0.5 * ulp)
-    return (mid_dist <= rel * mass).any(axis=1)

@@ -362,20 +362,23 @@ ORC_API void orc_moe_route(const float* x, const float* router_w, const float* r
  * kernel_parity.cpp:634-647; gpt_oss_kernels.cu:762-811.
  * An expert e is computed only when expert_lo <= e < expert_hi and, if
  * `modulo` > 0, e % modulo == residue (the reference's 2-way rule is modulo 2,
- * gpt_oss_kernels.cu:771). */
+ * gpt_oss_kernels.cu:771).
+ * `mass` (may be NULL) receives sum_j |bf(bf(v)+bd)| * p_j, the scale of the
+ * summands, against which errors of outputs that nearly cancel are judged. */
 ORC_API void orc_moe_experts(const float* x, const int32_t* selected, const float* probs,
                              const uint8_t* gu_blocks, const uint8_t* gu_scales,
                              const float* gu_bias, const uint8_t* dn_blocks,
                              const uint8_t* dn_scales, const float* dn_bias, long tokens,
                              int hidden, int inter, int experts, int topk, float limit,
                              int expert_lo, int expert_hi, int modulo, int residue,
-                             int round_output, float* y)
+                             int round_output, float* y, float* mass)
 {
     (void)experts;
 #pragma omp parallel for schedule(dynamic, 1)
     for (long t = 0; t < tokens; ++t) {
         float* h = (float*)malloc(sizeof(float) * (size_t)inter);
         float* o = (float*)calloc((size_t)hidden, sizeof(float));
+        float* ms = (float*)calloc((size_t)hidden, sizeof(float));
         const float* xt = x + t * hidden;
         for (int j = 0; j < topk; ++j) {
             const int e = selected[t * topk + j];
@@ -398,11 +401,16 @@ ORC_API void orc_moe_experts(const float* x, const int32_t* selected, const floa
                 const size_t row = (size_t)e * hidden + (size_t)d;
                 float v = 0.f;
                 for (int i = 0; i < inter; ++i) v += h[i] * mxfp4_at(dn_blocks, dn_scales, row, i, inter);
-                o[d] += bf(bf(v) + dn_bias[row]) * p;
+                const float val = bf(bf(v) + dn_bias[row]);
+                o[d] += val * p;
+                ms[d] += fabsf(val) * p;
             }
         }
         for (int d = 0; d < hidden; ++d) y[t * hidden + d] = round_output ? bf(o[d]) : o[d];
+        if (mass)
+            for (int d = 0; d < hidden; ++d) mass[t * hidden + d] = ms[d];
         free(h);
         free(o);
+        free(ms);
     }
 }
