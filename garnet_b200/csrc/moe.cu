@@ -18,6 +18,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <mutex>
 #include <new>
 
 #include "common.cuh"
@@ -310,7 +311,7 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
                 int* __restrict__ ntasks, int experts, int rows_per_task, MoeShard sh)
 {
     const int e = blockIdx.x;
-    __shared__ int s_offset, s_task, s_warp[32], s_running;
+    __shared__ int s_offset, s_warp[32], s_running;
     if (threadIdx.x == 0) {
         int off = 0, tk = 0;
         for (int q = 0; q < e; ++q) {
@@ -318,7 +319,6 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
             tk += (counts[q] + rows_per_task - 1) / rows_per_task;
         }
         s_offset = off;
-        s_task = tk;
         s_running = 0;
         offsets[e] = off;
         const int mine = counts[e];
@@ -907,11 +907,65 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     return GARNET_B200_OK;
 }
 
+// ------------------------------------------- built-in scratch (no allocation)
+
+// Scratch for garnet_b200_moe_run_static().  It lives in the library image: every
+// GPU that loads the library holds these 2 MiB until the process exits.  The
+// name below is only a host-side stand-in for the array; the device address is
+// looked up once per device with cudaGetSymbolAddress and handed to the kernels.
+constexpr size_t kMoeStaticScratchBytes = size_t(2) << 20;
+static __device__ __align__(256) unsigned char g_moe_static_scratch[kMoeStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+
+// Device address of the built-in scratch on the current device.  The first call
+// on a device performs the symbol lookup (with that device current).
+static int moe_static_scratch(void** out)
+{
+    static std::mutex mu;
+    static void* address[kMaxDevices] = {};
+    int dev = 0;
+    GB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(GARNET_B200_NOT_SUPPORTED, "moe_run_static: device index %d", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!address[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_moe_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "moe_run_static: cudaGetSymbolAddress");
+        if (!p) return fail(GARNET_B200_CUDA_ERROR, "moe_run_static: scratch symbol has no device address");
+        address[dev] = p;
+    }
+    *out = address[dev];
+    return GARNET_B200_OK;
+}
+
 }  // namespace gb200
 
 using namespace gb200;
 
 extern "C" {
+
+int garnet_b200_moe_run_static(garnet_b200_moe_t hh, const void* d_x, void* d_y, int tokens, void* stream)
+{
+    Moe* h = reinterpret_cast<Moe*>(hh);
+    if (!h) return fail(GARNET_B200_INVALID_VALUE, "moe_run_static: null handle");
+    if (tokens <= 0) return fail(GARNET_B200_INVALID_VALUE, "moe_run_static: tokens must be positive");
+    const size_t need = moe_workspace_plan(h->opt, tokens).total;
+    if (need > kMoeStaticScratchBytes) {
+        int fit = tokens;
+        while (fit > 0 && moe_workspace_plan(h->opt, fit).total > kMoeStaticScratchBytes) --fit;
+        return fail(GARNET_B200_INVALID_VALUE,
+                    "moe_run_static: %d tokens need %zu bytes of scratch but the built-in array holds %zu "
+                    "(at most %d tokens for this layer); use garnet_b200_moe_run with a caller workspace",
+                    tokens, need, kMoeStaticScratchBytes, fit);
+    }
+    void* scratch = nullptr;
+    if (int rc = moe_static_scratch(&scratch)) return rc;
+    // Nothing in the scratch has to start at zero: every region the kernels read
+    // (logits, routing, counts, slot lists, activations, per-slot values) is fully
+    // written earlier in the same call for the slots that are read.
+    return h->run(d_x, d_y, scratch, kMoeStaticScratchBytes, tokens, static_cast<cudaStream_t>(stream));
+}
 
 int garnet_b200_mxfp4_decode(const uint8_t* d_blocks, const uint8_t* d_scales, float* d_out, int rows, void* stream)
 {

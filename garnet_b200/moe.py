@@ -78,6 +78,18 @@ class GptOssMoe:
                                         _stream_ptr()))
         return y
 
+    def run_static(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """`run` without a workspace: the scratch is the 2 MiB array built into the
+        library, for callers that must not allocate device memory (see
+        garnet_b200_moe_run_static in include/garnet_b200.h for the limits: small
+        token counts only, one call at a time per device)."""
+        if x.dtype != self.io_dtype or not x.is_cuda:
+            raise ValueError("run_static needs a CUDA tensor of the operator's io dtype")
+        x2 = x.reshape(-1, self.opt.hidden).contiguous()
+        y = out if out is not None else torch.empty_like(x2)
+        check(lib().garnet_b200_moe_run_static(self._h, x2.data_ptr(), y.data_ptr(), x2.shape[0], _stream_ptr()))
+        return y
+
     # RunGptOssMoeRoute (gpt_oss_kernels.h:54-56)
     def route(self, x: torch.Tensor):
         x2 = x.reshape(-1, self.opt.hidden).contiguous()

@@ -184,6 +184,28 @@ int garnet_b200_moe_create(const garnet_b200_moe_options* options, const void* c
 int garnet_b200_moe_run(garnet_b200_moe_t h, const void* d_x, void* d_y, void* d_workspace, size_t workspace_bytes,
                         int tokens, void* stream);
 
+/* Same computation as garnet_b200_moe_run for callers that have no workspace to
+ * give and may not create one.  (No counterpart in the reference, whose callers
+ * always receive a workspace from the engine that owns the plugin.)  It is meant
+ * for hosts that drive this library directly from a latency-critical decode loop
+ * in which device allocation is off limits: cudaMalloc and cudaFree serialise
+ * with all work on the device, and in deployments where another runtime has
+ * already reserved the GPU's memory they simply fail.  The scratch is a 2 MiB
+ * array built into the library image (held by every GPU that loads the library,
+ * until the process exits); this call allocates and frees nothing, on the host
+ * side of CUDA or through any library.
+ *   - Limit: the layer's workspace for `tokens` must fit in 2 MiB - 27 tokens for
+ *     the gpt-oss-120b layer (hidden = intermediate = 2880, 128 experts, top-4).
+ *     Larger requests are rejected with INVALID_VALUE and a message that names the
+ *     largest token count that fits.
+ *   - The first call on each device looks up the array's device address; make that
+ *     first call before starting any stream capture on that device.
+ *   - All calls on a device share the one array, and it keeps the previous call's
+ *     contents.  Nothing needs clearing between calls, but two calls whose kernels
+ *     overlap on the GPU (different streams, or different handles at once) race on
+ *     it: serialise them, or use garnet_b200_moe_run with separate workspaces. */
+int garnet_b200_moe_run_static(garnet_b200_moe_t h, const void* d_x, void* d_y, int tokens, void* stream);
+
 /* Router only: bf16-rounded logits [tokens, experts], top-k expert ids
  * [tokens, top_k] and bf16-rounded probabilities.  RunGptOssMoeRoute
  * (gpt_oss_kernels.h:54-56). */
