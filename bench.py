@@ -278,6 +278,10 @@ def run_gpu(args):
             torch.cuda.empty_cache()
         out["sweep"] = sweep
 
+    if world == 1 and not args.no_moe:
+        torch.cuda.empty_cache()
+        out["moe"] = bench_moe(torch, gb, peaks, args)
+
     if rank == 0:
         if world == 1:
             out["cpu_baseline"] = cpu_baseline(sample_seconds=12.0)
@@ -285,6 +289,49 @@ def run_gpu(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def bench_moe(torch, gb, peaks, args, token_counts=(1, 32, 512, 4096)):
+    """gpt-oss-120b MoE layer (hidden = intermediate = 2880, 128 experts, top-4, MXFP4), one GPU.
+    tok/s per token count; a step = one call of the operator.  To keep weight reads
+    out of L2 at small T, a graph holds several calls on different token sets
+    (different experts) and the time is divided by their number."""
+    H = I = 2880
+    E, K = 128, 4
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(99)
+    u8 = lambda *shape, lo=0, hi=256: torch.randint(lo, hi, shape, dtype=torch.uint8, device="cuda", generator=gen)
+    router_w = (torch.randn(E, H, device="cuda", generator=gen) / H ** 0.5).to(torch.bfloat16).float()
+    router_b = torch.zeros(E, device="cuda")
+    moe = gb.GptOssMoe(H, I, E, K, io_dtype=torch.bfloat16).prepare(
+        router_w, router_b, u8(E, 2 * I, H // 32, 16), u8(E, 2 * I, H // 32, lo=117, hi=124),
+        torch.zeros(E, 2 * I, device="cuda"), u8(E, H, I // 32, 16), u8(E, H, I // 32, lo=117, hi=124),
+        torch.zeros(E, H, device="cuda"))
+    per_expert = 5760 * 2880 // 2 + 5760 * 90 + 2880 * 2880 // 2 + 2880 * 90
+    rows = []
+    for T in token_counts:
+        rot = 16 if T == 1 else (4 if T <= 32 else 1)
+        xs = [torch.randn(T, H, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(rot)]
+        y = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+        ws = torch.empty(moe.workspace_bytes(T), dtype=torch.uint8, device="cuda")
+        distinct = float(np.mean([len(torch.unique(moe.route(x)[1])) for x in xs]))
+
+        def body():
+            for x in xs:
+                moe.run(x, out=y, workspace=ws)
+
+        steps = max(3, min(args.steps, 20 if T <= 512 else 5))
+        ms = time_graph(torch, body, steps, 3) / rot
+        bytes_ = distinct * per_expert + T * H * 2 * 2
+        flops = 199065600.0 * T
+        rows.append({"tokens": T, "ms": round(ms, 4), "tok_per_s": round(T / (ms * 1e-3), 1),
+                     "distinct_experts": round(distinct, 1), "GBps": round(bytes_ / (ms * 1e-3) / 1e9, 1),
+                     "hbm_frac": round(bytes_ / (ms * 1e-3) / 1e9 / peaks["hbm"], 4),
+                     "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 2),
+                     "tensor_frac": round(flops / (ms * 1e-3) / 1e12 / peaks["tf_sus"], 4), "calls_per_graph": rot})
+    del moe
+    torch.cuda.empty_cache()
+    return rows
 
 
 # ------------------------------------------------------------- CPU baseline
@@ -395,6 +442,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-moe", action="store_true")
     ap.add_argument("--profile", default=None, help="w4a16:K:N:M - run one small case for a profiler capture")
     args = ap.parse_args()
     if args.profile:

@@ -782,6 +782,11 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
     router_b_ptr = static_cast<const float*>(weights[1]);
     up_bias_ptr = static_cast<const float*>(weights[4]);
     down_bias_ptr = static_cast<const float*>(weights[7]);
+    // the router kernel also has a little static shared memory: leave room for it
+    GB_CUDA(cudaFuncSetAttribute(moe_route_scores_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(kMaxDynamicSmem - 1024)));
+    GB_CUDA(cudaFuncSetAttribute(moe_route_scores_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(kMaxDynamicSmem - 1024)));
     GB_CUDA((set_moe_attr<true, true>()));
     GB_CUDA((set_moe_attr<true, false>()));
     GB_CUDA((set_moe_attr<false, true>()));
@@ -793,7 +798,7 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
                cudaStream_t stream)
 {
     const size_t smem = size_t(kRouteTokens) * opt.hidden * sizeof(float);
-    if (smem > kMaxDynamicSmem) return fail(GARNET_B200_NOT_SUPPORTED, "moe_route: hidden too large");
+    if (smem > kMaxDynamicSmem - 1024) return fail(GARNET_B200_NOT_SUPPORTED, "moe_route: hidden too large");
     // spread the experts over enough CTAs to fill the machine at small token counts
     const int token_ctas = (tokens + kRouteTokens - 1) / kRouteTokens;
     int per_cta = opt.experts;
@@ -801,12 +806,10 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
     per_cta = std::max(per_cta, std::min(opt.experts, kRouteWarps));
     const dim3 grid(token_ctas, (opt.experts + per_cta - 1) / per_cta);
     if (opt.io_dtype == GARNET_B200_FP32) {
-        GB_CUDA(cudaFuncSetAttribute(moe_route_scores_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         moe_route_scores_kernel<float><<<grid, kRouteWarps * 32, smem, stream>>>(
             static_cast<const float*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens, opt.hidden,
             opt.experts, per_cta);
     } else {
-        GB_CUDA(cudaFuncSetAttribute(moe_route_scores_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         moe_route_scores_kernel<__nv_bfloat16><<<grid, kRouteWarps * 32, smem, stream>>>(
             static_cast<const __nv_bfloat16*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens,
             opt.hidden, opt.experts, per_cta);
