@@ -1,0 +1,414 @@
+// Tensor-core (tcgen05 / TMEM) tile kernel of the int4 linear, for batches above
+// the streaming kernel's 16 rows.
+//
+// The weights are the A operand: a CTA owns kATiles x 128 weight rows (8 strips per
+// A tile) and up to 128 batch rows (the UMMA N dimension).  Per 64 columns of K:
+//   producer warp   bulk-copies the packed strip-chunks (codes + scales) and issues
+//                   the TMA load of the activation tile (128-byte swizzle);
+//   8 dequant warps expand int4 -> bf16, multiply by the group scale and store the
+//                   16-byte rows into the 128-byte-swizzled K-major A tile
+//                   (the row interleave of the packed layout makes those stores
+//                   bank-conflict free);
+//   MMA warp        one thread issues 4 x kATiles tcgen05.mma (M=128, N=batch tile,
+//                   K=16) into the TMEM accumulator and commits to the stage barrier;
+//   4 epilogue warps read the accumulator with tcgen05.ld, round to bf16 and store
+//                   y[m, n]; accumulators are double buffered so the next tile's
+//                   main loop overlaps the epilogue.
+// Numerics: w = bf16(q * s) (one rounding of the dequantised weight), products
+// exact, fp32 accumulation in TMEM, bf16 output.
+#include <algorithm>
+
+#include "layout.h"
+#include "tc_common.cuh"
+#include "w4a16.h"
+
+namespace gb200 {
+
+constexpr int kTcTokens = 128;            // batch rows per tile (UMMA N, multiple of 16)
+constexpr int kTcStages = 3;              // A/B ring depth, in 64-column tiles
+constexpr int kTcPackStages = 3;          // packed ring depth, in 128-column chunks
+constexpr int kTcDequantWarps = 8;
+constexpr int kTcEpilogueWarps = 4;
+constexpr int kTcThreads = (2 + kTcDequantWarps + kTcEpilogueWarps) * 32;
+constexpr int kTcChunkBytes = 1024 + 32;  // int4 strip-chunk
+constexpr int kTcTileBytes = 128 * 128;   // one 128-row x 64-column 16-bit tile
+
+struct TcParams {
+    const uint8_t* packed;
+    __nv_bfloat16* y;
+    int* fault;
+    int m, n, k;
+    int ldy;
+    int strips_padded, chunks;
+    int panels, token_tiles;
+    int scale_dtype;
+};
+
+template <int kATiles>
+struct TcSmem {
+    static constexpr int a = 0;
+    static constexpr int b = a + kTcStages * kATiles * kTcTileBytes;
+    static constexpr int pk = b + kTcStages * kTcTileBytes;
+    static constexpr int bars = pk + kTcPackStages * kATiles * 8 * kTcChunkBytes;
+    static constexpr int total = bars + 256 + 1024;   // barriers + slack for 1024-byte alignment
+};
+
+// One int4 word (8 codes of one row, pair-interleaved) times a scale -> 8 bf16.
+__device__ __forceinline__ uint4 int4_word_to_bf16x8(uint32_t w, uint32_t scale_bf16x2)
+{
+    uint4 r;
+    const uint32_t p0 = int4x2_to_bf16x2(w), p1 = int4x2_to_bf16x2(w >> 4), p2 = int4x2_to_bf16x2(w >> 8),
+                   p3 = int4x2_to_bf16x2(w >> 12);
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r.x) : "r"(p0), "r"(scale_bf16x2));
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r.y) : "r"(p1), "r"(scale_bf16x2));
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r.z) : "r"(p2), "r"(scale_bf16x2));
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r.w) : "r"(p3), "r"(scale_bf16x2));
+    return r;
+}
+// Same with an fp32 scale (fp16-scaled artifacts): q * s rounded once to bf16.
+__device__ __forceinline__ uint4 int4_word_to_bf16x8_f32(uint32_t w, float s)
+{
+    uint32_t out[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t p = int4x2_to_bf16x2(w >> (4 * j));
+        const float lo = __uint_as_float(p << 16) * s, hi = __uint_as_float(p & 0xffff0000u) * s;
+        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        out[j] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+template <int kATiles>
+__global__ void __launch_bounds__(kTcThreads, 1)
+w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
+{
+    using S = TcSmem<kATiles>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* a_ring = smem + S::a;
+    uint8_t* b_ring = smem + S::b;
+    uint8_t* pk_ring = smem + S::pk;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::bars);
+    uint64_t* pk_full = bars;                          // [kTcPackStages]
+    uint64_t* pk_empty = pk_full + kTcPackStages;      // [kTcPackStages]
+    uint64_t* a_full = pk_empty + kTcPackStages;       // [kTcStages]
+    uint64_t* b_full = a_full + kTcStages;             // [kTcStages]
+    uint64_t* ab_empty = b_full + kTcStages;           // [kTcStages]
+    uint64_t* acc_full = ab_empty + kTcStages;         // [2]
+    uint64_t* acc_empty = acc_full + 2;                // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    constexpr int kStripsPerPanel = 8 * kATiles;
+    constexpr int kPackStageBytes = kStripsPerPanel * kTcChunkBytes;
+    constexpr uint32_t kTmemCols = 2 * kATiles * 128;   // two accumulator buffers
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTcPackStages; ++s) {
+            mbar_init(&pk_full[s], 1);
+            mbar_init(&pk_empty[s], kTcDequantWarps);
+        }
+        for (int s = 0; s < kTcStages; ++s) {
+            mbar_init(&a_full[s], kTcDequantWarps);
+            mbar_init(&b_full[s], 1);
+            mbar_init(&ab_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], kTcEpilogueWarps);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+
+    const int items = p.panels * p.token_tiles;
+    const int ktiles = p.chunks * 2;
+    const size_t strip_bytes = size_t(p.chunks) * kTcChunkBytes;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t pk_n = 0, ab_n = 0;
+            bool first_b = true;
+            for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
+                const int panel = item % p.panels, tt = item / p.panels;
+                const int strip0 = panel * kStripsPerPanel;
+                const int valid = min(kStripsPerPanel, p.strips_padded - strip0);
+                for (int c = 0; c < p.chunks; ++c) {
+                    const uint32_t ps = pk_n % kTcPackStages;
+                    if (pk_n >= kTcPackStages && !mbar_wait_bounded(&pk_empty[ps], ((pk_n / kTcPackStages) - 1) & 1)) {
+                        atomicExch(p.fault, 11);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    mbar_expect_tx(&pk_full[ps], uint32_t(valid) * kTcChunkBytes);
+                    for (int s = 0; s < valid; ++s)
+                        bulk_g2s(pk_ring + ps * kPackStageBytes + s * kTcChunkBytes,
+                                 p.packed + size_t(strip0 + s) * strip_bytes + size_t(c) * kTcChunkBytes,
+                                 kTcChunkBytes, &pk_full[ps]);
+                    ++pk_n;
+                    for (int half = 0; half < 2; ++half) {
+                        const uint32_t s = ab_n % kTcStages;
+                        if (ab_n >= kTcStages && !mbar_wait_bounded(&ab_empty[s], ((ab_n / kTcStages) - 1) & 1)) {
+                            atomicExch(p.fault, 12);
+                            *abort_flag = 1;
+                            break;
+                        }
+                        if (first_b) {
+                            pdl_wait();   // activations come from the previous kernel in the stream
+                            first_b = false;
+                        }
+                        mbar_expect_tx(&b_full[s], kTcTileBytes);
+                        tma_load_2d(b_ring + s * kTcTileBytes, &x_map, (2 * c + half) * 64, tt * kTcTokens, &b_full[s]);
+                        ++ab_n;
+                    }
+                    if (*abort_flag) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ----------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t ab_n = 0, it_n = 0;
+            for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
+                const int tt = item / p.panels;
+                const int rows = min(kTcTokens, p.m - tt * kTcTokens);
+                const int nt = (rows + 15) & ~15;
+                const uint32_t idesc = umma_idesc_f16(1, 128, nt);
+                const uint32_t buf = it_n & 1;
+                if (it_n >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((it_n >> 1) - 1) & 1)) {
+                    atomicExch(p.fault, 13);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                for (int kt = 0; kt < ktiles; ++kt) {
+                    const uint32_t s = ab_n % kTcStages, ph = (ab_n / kTcStages) & 1;
+                    if (!mbar_wait_bounded(&a_full[s], ph) || !mbar_wait_bounded(&b_full[s], ph)) {
+                        atomicExch(p.fault, 14);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t b_addr = smem_u32(b_ring + s * kTcTileBytes);
+#pragma unroll
+                    for (int k16 = 0; k16 < 4; ++k16) {
+                        const uint64_t bd = umma_desc_k_sw128(b_addr + k16 * 32);
+#pragma unroll
+                        for (int at = 0; at < kATiles; ++at) {
+                            const uint32_t a_addr = smem_u32(a_ring + (s * kATiles + at) * kTcTileBytes);
+                            umma_f16(tmem_base + buf * (kATiles * 128) + at * 128, umma_desc_k_sw128(a_addr + k16 * 32),
+                                     bd, idesc, kt > 0 || k16 > 0);
+                        }
+                    }
+                    umma_commit(&ab_empty[s]);   // stage reusable once these MMAs have read it
+                    ++ab_n;
+                }
+                if (*abort_flag) break;
+                umma_commit(&acc_full[buf]);
+            }
+        }
+    } else if (warp < 2 + kTcDequantWarps) {
+        // -------------------------------------------------------------- dequant
+        const int dq = warp - 2;
+        const int g = lane >> 2, t = lane & 3;
+        uint32_t pk_n = 0, ab_n = 0;
+        for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
+            const int panel = item % p.panels;
+            const int valid = min(kStripsPerPanel, p.strips_padded - panel * kStripsPerPanel);
+            for (int c = 0; c < p.chunks && !*abort_flag; ++c) {
+                const uint32_t ps = pk_n % kTcPackStages;
+                if (!mbar_wait_bounded(&pk_full[ps], (pk_n / kTcPackStages) & 1)) {
+                    atomicExch(p.fault, 15);
+                    *abort_flag = 1;
+                    break;
+                }
+                const uint8_t* pk = pk_ring + ps * kPackStageBytes;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t s = ab_n % kTcStages;
+                    if (ab_n >= kTcStages && !mbar_wait_bounded(&ab_empty[s], ((ab_n / kTcStages) - 1) & 1)) {
+                        atomicExch(p.fault, 16);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int at = 0; at < kATiles; ++at) {
+                        const int sidx = at * 8 + dq;   // this warp's strip in A tile `at`
+                        if (sidx < valid) {
+                            const uint8_t* sc = pk + sidx * kTcChunkBytes;
+                            const uint4 u = *reinterpret_cast<const uint4*>(sc + half * 512 + lane * 16);
+                            const uint32_t sw = *reinterpret_cast<const uint32_t*>(sc + 1024 + g * 4);
+                            uint4 v0, v1, v2, v3;
+                            if (p.scale_dtype == GARNET_B200_BF16) {
+                                const uint32_t s_lo = (sw & 0xffffu) * 0x10001u, s_hi = (sw >> 16) * 0x10001u;
+                                v0 = int4_word_to_bf16x8(u.x, s_lo);
+                                v1 = int4_word_to_bf16x8(u.y, s_hi);
+                                v2 = int4_word_to_bf16x8(u.z, s_lo);
+                                v3 = int4_word_to_bf16x8(u.w, s_hi);
+                            } else {
+                                const float f_lo = __half2float(__ushort_as_half(uint16_t(sw & 0xffffu)));
+                                const float f_hi = __half2float(__ushort_as_half(uint16_t(sw >> 16)));
+                                v0 = int4_word_to_bf16x8_f32(u.x, f_lo);
+                                v1 = int4_word_to_bf16x8_f32(u.y, f_hi);
+                                v2 = int4_word_to_bf16x8_f32(u.z, f_lo);
+                                v3 = int4_word_to_bf16x8_f32(u.w, f_hi);
+                            }
+                            // rows R(g), R(g)+8 of strip dq; 16-byte chunks t and t+4, XOR-swizzled by row % 8
+                            uint8_t* tile = a_ring + (s * kATiles + at) * kTcTileBytes;
+                            const int r0 = dq * 16 + row_of_g(g), r1 = r0 + 8;
+                            const int x0 = r0 & 7;   // == r1 & 7
+                            *reinterpret_cast<uint4*>(tile + r0 * 128 + ((t ^ x0) << 4)) = v0;
+                            *reinterpret_cast<uint4*>(tile + r1 * 128 + ((t ^ x0) << 4)) = v1;
+                            *reinterpret_cast<uint4*>(tile + r0 * 128 + (((t + 4) ^ x0) << 4)) = v2;
+                            *reinterpret_cast<uint4*>(tile + r1 * 128 + (((t + 4) ^ x0) << 4)) = v3;
+                        }
+                    }
+                    fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&a_full[s]);
+                    ++ab_n;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&pk_empty[ps]);
+                ++pk_n;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------- epilogue
+        const int quarter = warp & 3;   // TMEM lanes 32*quarter .. +31 belong to this warp
+        uint32_t it_n = 0;
+        bool waited = false;
+        for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
+            const int panel = item % p.panels, tt = item / p.panels;
+            const uint32_t buf = it_n & 1;
+            if (!mbar_wait_bounded(&acc_full[buf], (it_n >> 1) & 1)) {
+                atomicExch(p.fault, 17);
+                *abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            if (!waited) {
+                pdl_wait();   // y may still be read by the previous kernel in the stream
+                waited = true;
+            }
+            const int m0 = tt * kTcTokens;
+            const int rows = min(kTcTokens, p.m - m0);
+#pragma unroll
+            for (int at = 0; at < kATiles; ++at) {
+                const int n = panel * (kATiles * 128) + at * 128 + quarter * 32 + lane;
+                for (int c0 = 0; c0 < rows; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * (kATiles * 128) + at * 128 + c0, r);
+                    tmem_ld_wait();
+                    if (n < p.n) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (c0 + j < rows)
+                                p.y[size_t(m0 + c0 + j) * p.ldy + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+
+    // ---- teardown: every role arrives here, also after a wait that gave up
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+TensorMapEncodeFn tensor_map_encoder()
+{
+    static TensorMapEncodeFn fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return reinterpret_cast<TensorMapEncodeFn>(ptr);
+    }();
+    return fn;
+}
+
+int make_tensor_map_2d_16bit(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows)
+{
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (!enc) return fail(GARNET_B200_NOT_SUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(GARNET_B200_CUDA_ERROR, "cuTensorMapEncodeTiled failed with code %d", int(r));
+    return GARNET_B200_OK;
+}
+
+int W4A16::init_tc()
+{
+    GB_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<1>::total));
+    GB_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<2>::total));
+    return GARNET_B200_OK;
+}
+
+int W4A16::launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, unsigned flags, cudaStream_t stream)
+{
+    CUtensorMap map;
+    if (int rc = make_tensor_map_2d_16bit(&map, x, uint64_t(m), uint64_t(geo.cols), kTcTokens)) return rc;
+    TcParams p;
+    p.packed = packed;
+    p.y = y;
+    p.fault = fault_dev;
+    p.m = m;
+    p.n = geo.rows;
+    p.k = geo.cols;
+    p.ldy = geo.rows;
+    p.strips_padded = geo.strips_padded;
+    p.chunks = geo.chunks;
+    p.token_tiles = (m + kTcTokens - 1) / kTcTokens;
+    p.scale_dtype = scale_dtype;
+    // 256-row CTA tiles halve the activation traffic per weight row; use them when
+    // there are enough tiles to fill the machine, else 128-row tiles.
+    const int panels256 = (geo.strips_padded + 15) / 16;
+    const int atiles = panels256 * p.token_tiles >= 2 * kSmCount ? 2 : 1;
+    p.panels = atiles == 2 ? panels256 : geo.strips_padded / 8;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(std::min(p.panels * p.token_tiles, kSmCount)));
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = atiles == 2 ? TcSmem<2>::total : TcSmem<1>::total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & 1u) ? 1 : 0;
+    if (atiles == 2)
+        GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<2>, p, map));
+    else
+        GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<1>, p, map));
+    return GARNET_B200_OK;
+}
+
+}  // namespace gb200

@@ -33,7 +33,7 @@ def make_linear(case, n, k, group=128, **kw):
     return lin.prepare(dev(case["nibbles"]), scales, n, k, group, **kw)
 
 
-def check_close(y_dev, y64, tol=TOL):
+def check_close(y_dev, y64, tol=TOL, rounded_weights=False):
     y = y_dev.float().cpu().numpy().astype(np.float64)
     err = np.abs(y - y64)
     assert np.isfinite(y).all()
@@ -45,7 +45,12 @@ def check_close(y_dev, y64, tol=TOL):
     ref = oracle.bf16_round(y64.astype(np.float32)).astype(np.float64)
     ulp = np.maximum(np.abs(ref), 2.0 ** -120) * 2.0 ** -7
     rms = np.sqrt((y64 ** 2).mean(axis=1, keepdims=True))
-    assert (np.abs(y - ref) <= 1.01 * ulp + 2e-5 * rms + 1e-30).all()
+    # Above 16 rows the tensor-core tile kernel multiplies by w = bf16(q * s): each
+    # weight carries one bf16 rounding (up to 2^-9 relative), which shows as up to
+    # ~1e-2 of the row's output scale on individual outputs (the kernel reproduces
+    # x . bf16(q*s) to the last bit; checked below where that model is passed in).
+    slack = 2.5e-2 if rounded_weights else 2e-5
+    assert (np.abs(y - ref) <= 1.01 * ulp + slack * rms + 1e-30).all()
 
 
 @pytest.mark.parametrize("n,k,group", [(128, 128, 128), (200, 256, 128), (1024, 2048, 128), (256, 512, 256)])
@@ -74,7 +79,25 @@ def test_linear_matches_exact_oracle(n, k, m):
     torch.cuda.synchronize()
     assert lin.fault() == 0
     _, y64 = oracle.w4a16_exact(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"])
-    check_close(y, y64)
+    check_close(y, y64, rounded_weights=m > 16)
+
+
+@pytest.mark.parametrize("m", [33, 64, 130, 256, 300])
+@pytest.mark.parametrize("n,k", [(384, 256), (6144, 2048), (2048, 6144), (200, 512)])
+def test_linear_tensor_core_tiles(n, k, m):
+    """Batches above 16 rows: 128- and 256-row weight tiles, partial batch tiles,
+    several batch tiles, rows that are not a multiple of 128."""
+    case = synth.int4_linear(n, k, m, seed=m + n + k)
+    lin = make_linear(case, n, k)
+    y = lin.forward(bf16_tensor(case["x_bits"]).reshape(m, k))
+    torch.cuda.synchronize()
+    assert lin.fault() == 0
+    y64 = oracle.w4a16_blas(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"])
+    check_close(y, y64, rounded_weights=True)
+    # against the same product with weights rounded once to bf16, the result is the
+    # correctly rounded bf16 value up to fp32 accumulation noise
+    wq = oracle.bf16_round(oracle.int4_dequant(case["nibbles"], case["scales_f32"], n, k, 128)).astype(np.float64)
+    check_close(y, case["x_f32"].astype(np.float64) @ wq.T)
 
 
 def test_baseline_config_gate_proj_m1():
