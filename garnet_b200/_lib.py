@@ -47,6 +47,9 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_moe_create.argtypes = [vp, vp, vp, c.POINTER(vp)]
     L.garnet_b200_moe_run.argtypes = [vp, vp, vp, vp, sz, i, vp]
     L.garnet_b200_moe_run_static.argtypes = [vp, vp, vp, i, vp]
+    L.garnet_b200_moe_rows_workspace.argtypes = [vp, i, c.POINTER(sz)]
+    L.garnet_b200_moe_run_rows.argtypes = [vp, vp, vp, i, vp, vp, sz, vp]
+    L.garnet_b200_moe_combine.argtypes = [vp, vp, vp, vp, i, vp]
     L.garnet_b200_moe_route.argtypes = [vp, vp, vp, vp, vp, i, vp]
     L.garnet_b200_mxfp4_decode.argtypes = [vp, vp, vp, i, vp]
     L.garnet_b200_moe_dequant.argtypes = [vp, i, i, vp, vp]

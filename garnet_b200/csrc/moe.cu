@@ -276,6 +276,30 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int* __restric
     }
 }
 
+// fp16 copy of activation rows for the expert kernels, one warp per row: the row
+// is rounded to bf16 and scaled by an exact power of two so that its largest
+// magnitude lands in [2^13, 2^14); `xshift` keeps the exponent (x = xh * 2^shift).
+// Same arithmetic as the tail of moe_route_scores_kernel.
+template <typename XT>
+__global__ void moe_prep_rows_kernel(const XT* __restrict__ x, __half* __restrict__ xh, int* __restrict__ xshift,
+                                     int rows, int hidden)
+{
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const XT* src = x + size_t(row) * hidden;
+    float amax = 0.f;
+    for (int d = lane; d < hidden; d += 32) amax = fmaxf(amax, fabsf(bf16_round_f(to_float(src[d]))));
+#pragma unroll
+    for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    int shift = 0;
+    if (amax > 0.f && isfinite(amax)) shift = int((__float_as_uint(amax) >> 23) & 0xff) - 127 - 13;
+    shift = max(-100, min(100, shift));
+    const float scale = __uint_as_float(uint32_t(127 - shift) << 23);
+    for (int d = lane; d < hidden; d += 32)
+        xh[size_t(row) * hidden + d] = __float2half_rn(bf16_round_f(to_float(src[d])) * scale);
+    if (lane == 0) xshift[row] = shift;
+}
+
 // ------------------------------------------------------------ slot bucketing
 
 __device__ __forceinline__ bool expert_is_local(int e, const MoeShard& sh)
@@ -620,7 +644,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ vals, const float* 
     float r = 0.f;
     for (int j = 0; j < topk; ++j) {
         const int slot = token * topk + j;
-        if (!expert_is_local(selected[slot], sh)) continue;
+        if (sh.world > 1 && !expert_is_local(selected[slot], sh)) continue;
         r += vals[size_t(slot) * hidden + d] * probs[slot];
     }
     if (round_output) r = bf16_round_f(r);
@@ -820,8 +844,9 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
     return GARNET_B200_OK;
 }
 
-int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream)
+int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream, int topk)
 {
+    if (topk <= 0) topk = opt.top_k;
     const PackGeom& geo = up ? geo_up : geo_down;
     const MoeShard sh = shard();
     MoeStreamParams p;
@@ -839,7 +864,7 @@ int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStrea
     p.rows = geo.rows;
     p.strips = geo.strips;
     p.chunks = geo.chunks;
-    p.topk = opt.top_k;
+    p.topk = topk;
     // stored expert index of global expert e; biases follow the same indexing as
     // the expert tensors the caller handed over
     p.expert_base = (sh.world > 1 && !sh.interleaved) ? sh.lo : (sh.world > 1 ? sh.rank : 0);
@@ -851,7 +876,7 @@ int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStrea
     const size_t smem = size_t(moe_smem_plan(geo.cols).total);
     const int ctas_per_sm = std::max(1, std::min(2, int(kMaxDynamicSmem / (smem + 1024))));
     // upper bound of (task, strip) items: every slot its own task
-    const long long max_items = (long long)tokens * opt.top_k * geo.strips;
+    const long long max_items = (long long)tokens * topk * geo.strips;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(std::max<long long>(1, std::min<long long>(max_items, (long long)kSmCount * ctas_per_sm))));
     cfg.blockDim = dim3((kMoeWarps + 1) * 32);
@@ -906,6 +931,82 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
         moe_combine_kernel<__nv_bfloat16><<<unsigned((n + 255) / 256), 256, 0, stream>>>(
             w.vals, w.probs, w.selected, static_cast<__nv_bfloat16*>(y), tokens, opt.hidden, opt.top_k, sh,
             round_output);
+    GB_CUDA(cudaGetLastError());
+    return GARNET_B200_OK;
+}
+
+static MoeWorkspacePtrs bind_workspace(void* ws, const MoeWorkspace& plan)
+{
+    uint8_t* b = static_cast<uint8_t*>(ws);
+    MoeWorkspacePtrs w;
+    w.logits = reinterpret_cast<float*>(b + plan.logits);
+    w.selected = reinterpret_cast<int*>(b + plan.selected);
+    w.probs = reinterpret_cast<float*>(b + plan.probs);
+    w.xshift = reinterpret_cast<int*>(b + plan.xshift);
+    w.xh = reinterpret_cast<__half*>(b + plan.xh);
+    w.counts = reinterpret_cast<int*>(b + plan.counts);
+    w.offsets = reinterpret_cast<int*>(b + plan.offsets);
+    w.sorted = reinterpret_cast<int*>(b + plan.sorted);
+    w.ntasks = reinterpret_cast<int*>(b + plan.ntasks);
+    w.tasks = reinterpret_cast<int4*>(b + plan.tasks);
+    w.act = reinterpret_cast<__half*>(b + plan.act);
+    w.vals = reinterpret_cast<float*>(b + plan.vals);
+    return w;
+}
+
+// Workspace plan of run_rows: every row is one routed slot (top_k = 1); the
+// per-slot values go straight to the caller's buffer, so that region is empty.
+MoeWorkspace moe_rows_workspace_plan(const garnet_b200_moe_options& o, int rows)
+{
+    garnet_b200_moe_options one = o;
+    one.top_k = 1;
+    one.experts = o.experts;
+    MoeWorkspace plan = moe_workspace_plan(one, rows);
+    plan.total = plan.vals;   // vals is the last region
+    return plan;
+}
+
+// Experts only, on rows that have already been routed (and, in an expert-parallel
+// run, already exchanged): row r goes through expert row_expert[r];
+// vals[r, :] = bf(bf(h . w_down) + bd), unweighted.  Rows of experts that this
+// handle does not hold are skipped (their vals are left untouched).
+int Moe::run_rows(const void* x_rows, const int* row_expert, int rows, float* vals, void* ws, size_t ws_bytes,
+                  cudaStream_t stream)
+{
+    if (rows <= 0) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: rows must be positive");
+    if (!x_rows || !row_expert || !vals || !ws) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: null pointer");
+    const MoeWorkspace plan = moe_rows_workspace_plan(opt, rows);
+    if (ws_bytes < plan.total) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: workspace too small (%zu < %zu)", ws_bytes, plan.total);
+    if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: workspace must be 256-byte aligned");
+    MoeWorkspacePtrs w = bind_workspace(ws, plan);
+    w.vals = vals;
+    const unsigned blocks = unsigned((size_t(rows) * 32 + 255) / 256);
+    if (opt.io_dtype == GARNET_B200_FP32)
+        moe_prep_rows_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x_rows), w.xh, w.xshift, rows, opt.hidden);
+    else
+        moe_prep_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x_rows), w.xh, w.xshift, rows, opt.hidden);
+    const MoeShard sh = shard();
+    moe_count_kernel<<<opt.experts, 256, 0, stream>>>(row_expert, rows, w.counts, sh);
+    moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(row_expert, rows, w.counts, w.offsets, w.sorted, w.tasks, w.ntasks,
+                                                     opt.experts, kMoeRows, sh);
+    GB_CUDA(cudaGetLastError());
+    if (int rc = launch_stream(true, w, rows, stream, 1)) return rc;
+    return launch_stream(false, w, rows, stream, 1);
+}
+
+// y[t, :] = bf(sum_j vals[t*k + j, :] * probs[t, j]) in router order, all slots.
+int Moe::combine(const float* vals, const float* probs, void* y, int tokens, cudaStream_t stream)
+{
+    if (tokens <= 0 || !vals || !probs || !y) return fail(GARNET_B200_INVALID_VALUE, "moe_combine: bad argument");
+    MoeShard all{};
+    all.world = 1;
+    const size_t n = size_t(tokens) * opt.hidden;
+    if (opt.io_dtype == GARNET_B200_FP32)
+        moe_combine_kernel<float><<<unsigned((n + 255) / 256), 256, 0, stream>>>(vals, probs, nullptr, static_cast<float*>(y),
+                                                                               tokens, opt.hidden, opt.top_k, all, 1);
+    else
+        moe_combine_kernel<__nv_bfloat16><<<unsigned((n + 255) / 256), 256, 0, stream>>>(
+            vals, probs, nullptr, static_cast<__nv_bfloat16*>(y), tokens, opt.hidden, opt.top_k, all, 1);
     GB_CUDA(cudaGetLastError());
     return GARNET_B200_OK;
 }
@@ -1013,6 +1114,30 @@ int garnet_b200_moe_run(garnet_b200_moe_t hh, const void* d_x, void* d_y, void* 
     Moe* h = reinterpret_cast<Moe*>(hh);
     if (!h) return fail(GARNET_B200_INVALID_VALUE, "moe_run: null handle");
     return h->run(d_x, d_y, d_workspace, workspace_bytes, tokens, static_cast<cudaStream_t>(stream));
+}
+
+int garnet_b200_moe_rows_workspace(const garnet_b200_moe_options* o, int rows, size_t* bytes)
+{
+    if (int rc = validate_options(o)) return rc;
+    if (!bytes || rows <= 0) return fail(GARNET_B200_INVALID_VALUE, "moe_rows_workspace: bad argument");
+    *bytes = moe_rows_workspace_plan(*o, rows).total;
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_moe_run_rows(garnet_b200_moe_t hh, const void* d_rows, const int* d_row_expert, int rows,
+                             float* d_vals, void* d_workspace, size_t workspace_bytes, void* stream)
+{
+    Moe* h = reinterpret_cast<Moe*>(hh);
+    if (!h) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: null handle");
+    return h->run_rows(d_rows, d_row_expert, rows, d_vals, d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int garnet_b200_moe_combine(garnet_b200_moe_t hh, const float* d_vals, const float* d_probs, void* d_y, int tokens,
+                            void* stream)
+{
+    Moe* h = reinterpret_cast<Moe*>(hh);
+    if (!h) return fail(GARNET_B200_INVALID_VALUE, "moe_combine: null handle");
+    return h->combine(d_vals, d_probs, d_y, tokens, static_cast<cudaStream_t>(stream));
 }
 
 int garnet_b200_moe_route(garnet_b200_moe_t hh, const void* d_x, int* d_selected, float* d_probs, float* d_logits,

@@ -40,6 +40,7 @@ struct MoeWorkspacePtrs {
 };
 
 MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens);
+MoeWorkspace moe_rows_workspace_plan(const garnet_b200_moe_options& o, int rows);
 
 struct Moe {
     garnet_b200_moe_options opt{};
@@ -62,7 +63,10 @@ struct Moe {
     int prepare(const void* const* weights, cudaStream_t stream);
     int route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
               cudaStream_t stream);
-    int launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream);
+    int launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream, int topk = -1);
+    int run_rows(const void* x_rows, const int* row_expert, int rows, float* vals, void* ws, size_t ws_bytes,
+                 cudaStream_t stream);
+    int combine(const float* vals, const float* probs, void* y, int tokens, cudaStream_t stream);
     int run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cudaStream_t stream);
 };
 

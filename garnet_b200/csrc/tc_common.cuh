@@ -17,6 +17,12 @@ TensorMapEncodeFn tensor_map_encoder();
 // rows, 128-byte swizzle (the K-major operand layout of tcgen05.mma).
 int make_tensor_map_2d_16bit(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
+// Rows of `row_bytes` bytes (a multiple of 16), `rows` of them `stride_bytes` apart,
+// viewed as 8-byte elements without swizzle; box = box_bytes x box_rows.  Used to
+// fetch the same chunk of several consecutive strips with one TMA operation.
+int make_tensor_map_2d_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                             uint64_t stride_bytes, uint32_t box_bytes, uint32_t box_rows);
+
 #if defined(__CUDACC__)
 
 constexpr uint32_t kTcWaitSpins = 1u << 24;
@@ -48,6 +54,14 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
             smem_u32(dst)),
         "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
         : "memory");
+}
+
+// Prefetch of the same box into L2 only (no shared-memory destination, no barrier).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+                 "r"(c0), "r"(c1)
+                 : "memory");
 }
 
 // ---- tensor memory

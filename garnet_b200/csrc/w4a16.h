@@ -17,6 +17,8 @@ struct W4A16 {
     uint8_t* packed = nullptr;       // packed tiles (device)
     bool owns_packed = false;
     int device = 0;
+    struct alignas(64) TensorMapStorage { unsigned char bytes[128]; };
+    TensorMapStorage tc_packed_map[2];   // TMA views of the packed matrix: 8 and 16 strips per box
     int max_rows_per_launch = 16;    // batch rows one launch of the streaming kernel takes
     int* fault_host = nullptr;       // mapped host word written by bounded device waits
     int* fault_dev = nullptr;

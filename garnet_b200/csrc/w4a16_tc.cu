@@ -17,6 +17,7 @@
 // Numerics: w = bf16(q * s) (one rounding of the dequantised weight), products
 // exact, fp32 accumulation in TMEM, bf16 output.
 #include <algorithm>
+#include <cstdlib>
 
 #include "layout.h"
 #include "tc_common.cuh"
@@ -25,11 +26,26 @@
 namespace gb200 {
 
 constexpr int kTcTokens = 128;            // batch rows per tile (UMMA N, multiple of 16)
-constexpr int kTcStages = 3;              // A/B ring depth, in 64-column tiles
-constexpr int kTcPackStages = 3;          // packed ring depth, in 128-column chunks
-constexpr int kTcDequantWarps = 8;
+// Ring depths.  A (expanded weights) only has to cover the dequant -> MMA hand-off;
+// B (activations, from L2 through TMA) has to cover about a microsecond of L2
+// latency at ~0.4 us per 64-column tile; the packed ring is fed from L2 as well,
+// because the producer prefetches packed chunks into L2 well ahead of their use.
+__host__ __device__ constexpr int tc_a_stages(int atiles) { return atiles == 2 ? 3 : 4; }
+__host__ __device__ constexpr int tc_b_stages(int atiles) { return atiles == 2 ? 4 : 6; }
+constexpr int kTcPrefetchChunks = 8;      // packed chunks prefetched into L2 ahead of the ring
+// Packed ring depth, in 128-column chunks.  The codes come from HBM (microseconds
+// of latency against ~0.3 us per 64-column tile), so this ring is the deep one.
+__host__ __device__ constexpr int tc_pack_stages(int atiles) { return atiles == 2 ? 3 : 4; }
+// One dequant warp per strip of the CTA tile (8 per 128-row A tile): the expansion
+// of a 64-column tile is then one 16-byte unit per lane, and the 16 warps of a
+// 256-row tile keep all four schedulers busy.
+__host__ __device__ constexpr int tc_dequant_warps(int atiles) { return 8 * atiles; }
 constexpr int kTcEpilogueWarps = 4;
-constexpr int kTcThreads = (2 + kTcDequantWarps + kTcEpilogueWarps) * 32;
+constexpr int kTcFirstDequantWarp = 3;    // warp 0: packed producer, 1: MMA, 2: activation producer
+__host__ __device__ constexpr int tc_threads(int atiles)
+{
+    return (kTcFirstDequantWarp + tc_dequant_warps(atiles) + kTcEpilogueWarps) * 32;
+}
 constexpr int kTcChunkBytes = 1024 + 32;  // int4 strip-chunk
 constexpr int kTcTileBytes = 128 * 128;   // one 128-row x 64-column 16-bit tile
 
@@ -42,14 +58,15 @@ struct TcParams {
     int strips_padded, chunks;
     int panels, token_tiles;
     int scale_dtype;
+    int debug;
 };
 
 template <int kATiles>
 struct TcSmem {
     static constexpr int a = 0;
-    static constexpr int b = a + kTcStages * kATiles * kTcTileBytes;
-    static constexpr int pk = b + kTcStages * kTcTileBytes;
-    static constexpr int bars = pk + kTcPackStages * kATiles * 8 * kTcChunkBytes;
+    static constexpr int b = a + tc_a_stages(kATiles) * kATiles * kTcTileBytes;
+    static constexpr int pk = b + tc_b_stages(kATiles) * kTcTileBytes;
+    static constexpr int bars = pk + tc_pack_stages(kATiles) * kATiles * 8 * kTcChunkBytes;
     static constexpr int total = bars + 256 + 1024;   // barriers + slack for 1024-byte alignment
 };
 
@@ -80,8 +97,9 @@ __device__ __forceinline__ uint4 int4_word_to_bf16x8_f32(uint32_t w, float s)
 }
 
 template <int kATiles>
-__global__ void __launch_bounds__(kTcThreads, 1)
-w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
+__global__ void __launch_bounds__(tc_threads(kATiles), 1)
+w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
+                const __grid_constant__ CUtensorMap w_map)
 {
     using S = TcSmem<kATiles>;
     extern __shared__ uint8_t smem_raw[];
@@ -89,13 +107,18 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
     uint8_t* a_ring = smem + S::a;
     uint8_t* b_ring = smem + S::b;
     uint8_t* pk_ring = smem + S::pk;
+    constexpr int kTcPackStages = tc_pack_stages(kATiles);
+    constexpr int kAStages = tc_a_stages(kATiles);
+    constexpr int kBStages = tc_b_stages(kATiles);
+    constexpr int kTcDequantWarps = tc_dequant_warps(kATiles);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::bars);
     uint64_t* pk_full = bars;                          // [kTcPackStages]
     uint64_t* pk_empty = pk_full + kTcPackStages;      // [kTcPackStages]
-    uint64_t* a_full = pk_empty + kTcPackStages;       // [kTcStages]
-    uint64_t* b_full = a_full + kTcStages;             // [kTcStages]
-    uint64_t* ab_empty = b_full + kTcStages;           // [kTcStages]
-    uint64_t* acc_full = ab_empty + kTcStages;         // [2]
+    uint64_t* a_full = pk_empty + kTcPackStages;       // [kAStages]
+    uint64_t* a_empty = a_full + kAStages;             // [kAStages]
+    uint64_t* b_full = a_empty + kAStages;             // [kBStages]
+    uint64_t* b_empty = b_full + kBStages;             // [kBStages]
+    uint64_t* acc_full = b_empty + kBStages;           // [2]
     uint64_t* acc_empty = acc_full + 2;                // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -110,10 +133,13 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
             mbar_init(&pk_full[s], 1);
             mbar_init(&pk_empty[s], kTcDequantWarps);
         }
-        for (int s = 0; s < kTcStages; ++s) {
+        for (int s = 0; s < kAStages; ++s) {
             mbar_init(&a_full[s], kTcDequantWarps);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int s = 0; s < kBStages; ++s) {
             mbar_init(&b_full[s], 1);
-            mbar_init(&ab_empty[s], 1);
+            mbar_init(&b_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&acc_full[s], 1);
@@ -134,46 +160,60 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
 
     const int items = p.panels * p.token_tiles;
     const int ktiles = p.chunks * 2;
-    const size_t strip_bytes = size_t(p.chunks) * kTcChunkBytes;
 
     if (warp == 0) {
-        // ------------------------------------------------------------ producer
+        // ------------------------------------- producer of packed codes + scales
+        // Weights are constants: this stream starts before the previous kernel in the
+        // stream has finished, and runs as far ahead as its ring allows.
         if (lane == 0) {
-            uint32_t pk_n = 0, ab_n = 0;
-            bool first_b = true;
+            uint32_t pk_n = 0, pf_n = 0;   // chunks issued to the ring / prefetched into L2, in this CTA's order
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
-                const int panel = item % p.panels, tt = item / p.panels;
+                const int panel = item / p.token_tiles;
                 const int strip0 = panel * kStripsPerPanel;
-                const int valid = min(kStripsPerPanel, p.strips_padded - strip0);
                 for (int c = 0; c < p.chunks; ++c) {
+                    // keep the L2 prefetch kTcPrefetchChunks ahead of the ring, across items
+                    while (pf_n < pk_n + kTcPrefetchChunks) {
+                        const int pf_item = blockIdx.x + int(pf_n / p.chunks) * gridDim.x;
+                        if (pf_item >= items) break;
+                        tma_prefetch_2d(&w_map, int(pf_n % p.chunks) * (kTcChunkBytes / 8),
+                                        (pf_item / p.token_tiles) * kStripsPerPanel);
+                        ++pf_n;
+                    }
                     const uint32_t ps = pk_n % kTcPackStages;
                     if (pk_n >= kTcPackStages && !mbar_wait_bounded(&pk_empty[ps], ((pk_n / kTcPackStages) - 1) & 1)) {
                         atomicExch(p.fault, 11);
                         *abort_flag = 1;
                         break;
                     }
-                    mbar_expect_tx(&pk_full[ps], uint32_t(valid) * kTcChunkBytes);
-                    for (int s = 0; s < valid; ++s)
-                        bulk_g2s(pk_ring + ps * kPackStageBytes + s * kTcChunkBytes,
-                                 p.packed + size_t(strip0 + s) * strip_bytes + size_t(c) * kTcChunkBytes,
-                                 kTcChunkBytes, &pk_full[ps]);
+                    // one TMA operation fetches chunk c of all the panel's strips (rows
+                    // past the last strip are filled with zeros and count as bytes)
+                    mbar_expect_tx(&pk_full[ps], kPackStageBytes);
+                    tma_load_2d(pk_ring + ps * kPackStageBytes, &w_map, c * (kTcChunkBytes / 8), strip0, &pk_full[ps]);
                     ++pk_n;
-                    for (int half = 0; half < 2; ++half) {
-                        const uint32_t s = ab_n % kTcStages;
-                        if (ab_n >= kTcStages && !mbar_wait_bounded(&ab_empty[s], ((ab_n / kTcStages) - 1) & 1)) {
-                            atomicExch(p.fault, 12);
-                            *abort_flag = 1;
-                            break;
-                        }
-                        if (first_b) {
-                            pdl_wait();   // activations come from the previous kernel in the stream
-                            first_b = false;
-                        }
-                        mbar_expect_tx(&b_full[s], kTcTileBytes);
-                        tma_load_2d(b_ring + s * kTcTileBytes, &x_map, (2 * c + half) * 64, tt * kTcTokens, &b_full[s]);
-                        ++ab_n;
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------ producer of activation tiles
+        if (lane == 0) {
+            uint32_t ab_n = 0;
+            pdl_wait();   // activations come from the previous kernel in the stream
+            for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
+                const int tt = item % p.token_tiles;
+                for (int kt = 0; kt < ktiles; ++kt) {
+                    const uint32_t s = ab_n % kBStages;
+                    if (ab_n >= kBStages && !mbar_wait_bounded(&b_empty[s], ((ab_n / kBStages) - 1) & 1)) {
+                        atomicExch(p.fault, 12);
+                        *abort_flag = 1;
+                        break;
                     }
-                    if (*abort_flag) break;
+                    if (p.debug & 4) {
+                        mbar_arrive(&b_full[s]);
+                    } else {
+                        mbar_expect_tx(&b_full[s], kTcTileBytes);
+                        tma_load_2d(b_ring + s * kTcTileBytes, &x_map, kt * 64, tt * kTcTokens, &b_full[s]);
+                    }
+                    ++ab_n;
                 }
             }
         }
@@ -182,7 +222,7 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
         if (lane == 0) {
             uint32_t ab_n = 0, it_n = 0;
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
-                const int tt = item / p.panels;
+                const int tt = item % p.token_tiles;
                 const int rows = min(kTcTokens, p.m - tt * kTcTokens);
                 const int nt = (rows + 15) & ~15;
                 const uint32_t idesc = umma_idesc_f16(1, 128, nt);
@@ -194,14 +234,16 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
                 }
                 tc_fence_after();
                 for (int kt = 0; kt < ktiles; ++kt) {
-                    const uint32_t s = ab_n % kTcStages, ph = (ab_n / kTcStages) & 1;
-                    if (!mbar_wait_bounded(&a_full[s], ph) || !mbar_wait_bounded(&b_full[s], ph)) {
+                    const uint32_t s = ab_n % kAStages, sb = ab_n % kBStages;
+                    if (!mbar_wait_bounded(&a_full[s], (ab_n / kAStages) & 1) ||
+                        !mbar_wait_bounded(&b_full[sb], (ab_n / kBStages) & 1)) {
                         atomicExch(p.fault, 14);
                         *abort_flag = 1;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t b_addr = smem_u32(b_ring + s * kTcTileBytes);
+                    const uint32_t b_addr = smem_u32(b_ring + sb * kTcTileBytes);
+                    if (!(p.debug & 2))
 #pragma unroll
                     for (int k16 = 0; k16 < 4; ++k16) {
                         const uint64_t bd = umma_desc_k_sw128(b_addr + k16 * 32);
@@ -212,20 +254,21 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
                                      bd, idesc, kt > 0 || k16 > 0);
                         }
                     }
-                    umma_commit(&ab_empty[s]);   // stage reusable once these MMAs have read it
+                    umma_commit(&a_empty[s]);    // stages reusable once these MMAs have read them
+                    umma_commit(&b_empty[sb]);
                     ++ab_n;
                 }
                 if (*abort_flag) break;
                 umma_commit(&acc_full[buf]);
             }
         }
-    } else if (warp < 2 + kTcDequantWarps) {
+    } else if (warp < kTcFirstDequantWarp + kTcDequantWarps) {
         // -------------------------------------------------------------- dequant
-        const int dq = warp - 2;
+        const int dq = warp - kTcFirstDequantWarp;
         const int g = lane >> 2, t = lane & 3;
         uint32_t pk_n = 0, ab_n = 0;
         for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
-            const int panel = item % p.panels;
+            const int panel = item / p.token_tiles;
             const int valid = min(kStripsPerPanel, p.strips_padded - panel * kStripsPerPanel);
             for (int c = 0; c < p.chunks && !*abort_flag; ++c) {
                 const uint32_t ps = pk_n % kTcPackStages;
@@ -237,17 +280,16 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
                 const uint8_t* pk = pk_ring + ps * kPackStageBytes;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    const uint32_t s = ab_n % kTcStages;
-                    if (ab_n >= kTcStages && !mbar_wait_bounded(&ab_empty[s], ((ab_n / kTcStages) - 1) & 1)) {
+                    const uint32_t s = ab_n % kAStages;
+                    if (ab_n >= kAStages && !mbar_wait_bounded(&a_empty[s], ((ab_n / kAStages) - 1) & 1)) {
                         atomicExch(p.fault, 16);
                         *abort_flag = 1;
                         break;
                     }
                     tc_fence_after();
-#pragma unroll
-                    for (int at = 0; at < kATiles; ++at) {
-                        const int sidx = at * 8 + dq;   // this warp's strip in A tile `at`
-                        if (sidx < valid) {
+                    {
+                        const int sidx = dq, at = dq >> 3;   // this warp's strip, and the A tile it belongs to
+                        if (sidx < valid && !(p.debug & 1)) {
                             const uint8_t* sc = pk + sidx * kTcChunkBytes;
                             const uint4 u = *reinterpret_cast<const uint4*>(sc + half * 512 + lane * 16);
                             const uint32_t sw = *reinterpret_cast<const uint32_t*>(sc + 1024 + g * 4);
@@ -268,7 +310,7 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
                             }
                             // rows R(g), R(g)+8 of strip dq; 16-byte chunks t and t+4, XOR-swizzled by row % 8
                             uint8_t* tile = a_ring + (s * kATiles + at) * kTcTileBytes;
-                            const int r0 = dq * 16 + row_of_g(g), r1 = r0 + 8;
+                            const int r0 = (dq & 7) * 16 + row_of_g(g), r1 = r0 + 8;
                             const int x0 = r0 & 7;   // == r1 & 7
                             *reinterpret_cast<uint4*>(tile + r0 * 128 + ((t ^ x0) << 4)) = v0;
                             *reinterpret_cast<uint4*>(tile + r1 * 128 + ((t ^ x0) << 4)) = v1;
@@ -276,7 +318,7 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
                             *reinterpret_cast<uint4*>(tile + r1 * 128 + (((t + 4) ^ x0) << 4)) = v3;
                         }
                     }
-                    fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core
+                    if (!(p.debug & 16)) fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&a_full[s]);
                     ++ab_n;
@@ -292,7 +334,7 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
         uint32_t it_n = 0;
         bool waited = false;
         for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
-            const int panel = item % p.panels, tt = item / p.panels;
+            const int panel = item / p.token_tiles, tt = item % p.token_tiles;
             const uint32_t buf = it_n & 1;
             if (!mbar_wait_bounded(&acc_full[buf], (it_n >> 1) & 1)) {
                 atomicExch(p.fault, 17);
@@ -313,7 +355,7 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map)
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * (kATiles * 128) + at * 128 + c0, r);
                     tmem_ld_wait();
-                    if (n < p.n) {
+                    if (n < p.n && !(p.debug & 8)) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (c0 + j < rows)
@@ -366,8 +408,30 @@ int make_tensor_map_2d_16bit(CUtensorMap* map, const void* base, uint64_t rows, 
     return GARNET_B200_OK;
 }
 
+int make_tensor_map_2d_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                             uint64_t stride_bytes, uint32_t box_bytes, uint32_t box_rows)
+{
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (!enc) return fail(GARNET_B200_NOT_SUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {row_bytes / 8, rows};
+    const cuuint64_t strides[1] = {stride_bytes};
+    const cuuint32_t box[2] = {box_bytes / 8, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(GARNET_B200_CUDA_ERROR, "cuTensorMapEncodeTiled (bytes) failed with code %d", int(r));
+    return GARNET_B200_OK;
+}
+
 int W4A16::init_tc()
 {
+    static_assert(sizeof(tc_packed_map[0]) == sizeof(CUtensorMap), "tensor map storage size");
+    for (int at = 1; at <= 2; ++at)
+        if (int rc = make_tensor_map_2d_bytes(reinterpret_cast<CUtensorMap*>(&tc_packed_map[at - 1]), packed,
+                                              uint64_t(geo.strips_padded), geo.strip_bytes(), geo.strip_bytes(),
+                                              kTcChunkBytes, 8 * at))
+            return rc;
     GB_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<1>::total));
     GB_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<2>::total));
     return GARNET_B200_OK;
@@ -389,14 +453,16 @@ int W4A16::launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, unsigned f
     p.chunks = geo.chunks;
     p.token_tiles = (m + kTcTokens - 1) / kTcTokens;
     p.scale_dtype = scale_dtype;
+    p.debug = getenv("GARNET_B200_TC_DEBUG") ? atoi(getenv("GARNET_B200_TC_DEBUG")) : 0;
     // 256-row CTA tiles halve the activation traffic per weight row; use them when
     // there are enough tiles to fill the machine, else 128-row tiles.
     const int panels256 = (geo.strips_padded + 15) / 16;
-    const int atiles = panels256 * p.token_tiles >= 2 * kSmCount ? 2 : 1;
+    int atiles = panels256 * p.token_tiles >= 2 * kSmCount ? 2 : 1;
+    if (const char* e = getenv("GARNET_B200_TC_ATILES")) atiles = e[0] == '1' ? 1 : 2;   // A/B switch
     p.panels = atiles == 2 ? panels256 : geo.strips_padded / 8;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(std::min(p.panels * p.token_tiles, kSmCount)));
-    cfg.blockDim = dim3(kTcThreads);
+    cfg.blockDim = dim3(tc_threads(atiles));
     cfg.dynamicSmemBytes = atiles == 2 ? TcSmem<2>::total : TcSmem<1>::total;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -405,9 +471,9 @@ int W4A16::launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, unsigned f
     cfg.attrs = attr;
     cfg.numAttrs = (flags & 1u) ? 1 : 0;
     if (atiles == 2)
-        GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<2>, p, map));
+        GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<2>, p, map, *reinterpret_cast<const CUtensorMap*>(&tc_packed_map[1])));
     else
-        GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<1>, p, map));
+        GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<1>, p, map, *reinterpret_cast<const CUtensorMap*>(&tc_packed_map[0])));
     return GARNET_B200_OK;
 }
 

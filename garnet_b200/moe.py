@@ -101,6 +101,33 @@ class GptOssMoe:
                                           logits.data_ptr(), tokens, _stream_ptr()))
         return logits, selected, probs
 
+    def rows_workspace_bytes(self, rows: int) -> int:
+        out = ctypes.c_size_t(0)
+        check(lib().garnet_b200_moe_rows_workspace(ctypes.byref(self.opt), rows, ctypes.byref(out)))
+        return out.value
+
+    def run_rows(self, rows_x: torch.Tensor, row_expert: torch.Tensor, out: torch.Tensor | None = None,
+                 workspace: torch.Tensor | None = None) -> torch.Tensor:
+        """Experts only, on already routed rows: returns unweighted per-row values
+        [rows, hidden] fp32 (bf16-valued)."""
+        x2 = rows_x.reshape(-1, self.opt.hidden).contiguous()
+        rows = x2.shape[0]
+        vals = out if out is not None else torch.empty(rows, self.opt.hidden, dtype=torch.float32, device=x2.device)
+        need = self.rows_workspace_bytes(rows)
+        ws = workspace if workspace is not None else torch.empty(need, dtype=torch.uint8, device=x2.device)
+        ex = row_expert.to(torch.int32).contiguous()
+        check(lib().garnet_b200_moe_run_rows(self._h, x2.data_ptr(), ex.data_ptr(), rows, vals.data_ptr(),
+                                             ws.data_ptr(), ws.numel(), _stream_ptr()))
+        return vals
+
+    def combine(self, vals: torch.Tensor, probs: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """y[t] = bf(sum_j vals[t*k+j] * probs[t, j]) in router order."""
+        tokens = probs.shape[0]
+        y = out if out is not None else torch.empty(tokens, self.opt.hidden, dtype=self.io_dtype, device=vals.device)
+        v, p = vals.contiguous(), probs.contiguous()
+        check(lib().garnet_b200_moe_combine(self._h, v.data_ptr(), p.data_ptr(), y.data_ptr(), tokens, _stream_ptr()))
+        return y
+
     def dequantized(self, which: int, stored_expert: int) -> torch.Tensor:
         rows, cols = (2 * self.opt.intermediate, self.opt.hidden) if which == 0 else (self.opt.hidden, self.opt.intermediate)
         out = torch.empty(rows, cols, dtype=torch.float32, device="cuda")

@@ -206,6 +206,33 @@ int garnet_b200_moe_run(garnet_b200_moe_t h, const void* d_x, void* d_y, void* d
  *     it: serialise them, or use garnet_b200_moe_run with separate workspaces. */
 int garnet_b200_moe_run_static(garnet_b200_moe_t h, const void* d_x, void* d_y, int tokens, void* stream);
 
+/* ---- expert-parallel building blocks --------------------------------------------
+ * The reference shards experts two ways with replicated tokens and an all-reduce
+ * of partial sums (expert % 2 == rank, plugins/gpt_oss/cuda/gpt_oss_kernels.cu:771,
+ * :818; xModel/gpt_oss/120b/gpt_oss_llm.py:119-123) - garnet_b200_moe_run with
+ * ep_world > 1 reproduces that.  For wider expert parallelism over NVLink the
+ * tokens are instead exchanged: each rank routes its own tokens
+ * (garnet_b200_moe_route), rows travel to the rank that owns their expert, that
+ * rank runs the experts on the rows it received (garnet_b200_moe_run_rows), the
+ * per-row values travel back and the source rank applies the router weights in
+ * router order (garnet_b200_moe_combine, gpt_oss_kernels.cu:907-921).  The
+ * exchange itself is the caller's (NCCL all-to-all in garnet_b200/dist.py). */
+
+/* Workspace bytes of garnet_b200_moe_run_rows for `rows` rows. */
+int garnet_b200_moe_rows_workspace(const garnet_b200_moe_options* options, int rows, size_t* bytes);
+
+/* d_vals[r, :] (fp32, bf16-valued) = bf(bf(h_r . w_down[e]) + bd[e]) with
+ * h_r = SwiGLU(d_rows[r, :] . w_gate_up[e] + b) and e = d_row_expert[r] (global
+ * expert id; must be one of this handle's experts, other rows are skipped).
+ * d_rows is [rows, hidden] of io_dtype. */
+int garnet_b200_moe_run_rows(garnet_b200_moe_t h, const void* d_rows, const int* d_row_expert, int rows,
+                             float* d_vals, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* y[t, :] = bf(sum_j d_vals[t * top_k + j, :] * d_probs[t, j]), j in router order
+ * (combineExperts, gpt_oss_kernels.cu:907-921). */
+int garnet_b200_moe_combine(garnet_b200_moe_t h, const float* d_vals, const float* d_probs, void* d_y, int tokens,
+                            void* stream);
+
 /* Router only: bf16-rounded logits [tokens, experts], top-k expert ids
  * [tokens, top_k] and bf16-rounded probabilities.  RunGptOssMoeRoute
  * (gpt_oss_kernels.h:54-56). */
