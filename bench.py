@@ -281,6 +281,12 @@ def run_gpu(args):
     if world == 1 and not args.no_moe:
         torch.cuda.empty_cache()
         out["moe"] = bench_moe(torch, gb, peaks, args)
+    if world > 1 and not args.no_moe:
+        del layers, head
+        torch.cuda.empty_cache()
+        ep = bench_moe_ep(torch, dist, gb, args, rank, world)
+        if rank == 0:
+            out["moe_ep"] = ep
 
     if rank == 0:
         if world == 1:
@@ -332,6 +338,66 @@ def bench_moe(torch, gb, peaks, args, token_counts=(1, 32, 512, 4096)):
     del moe
     torch.cuda.empty_cache()
     return rows
+
+
+def bench_moe_ep(torch, dist, gb, args, rank, world, tokens_total=8192):
+    """gpt-oss-120b MoE layer, expert parallel over `world` GPUs: 128/world experts per
+    GPU (contiguous blocks), tokens_total tokens split evenly, Zipf(1.1)-skewed expert
+    popularity, NCCL all-to-all dispatch and combine.  tok/s = tokens_total / time
+    (device time, max over ranks)."""
+    from garnet_b200.dist import ExpertParallelMoe
+    H = I = 2880
+    E, K = 128, 4
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)                       # same weights on every rank; each keeps its block
+    u8 = lambda *shape, lo=0, hi=256: torch.randint(lo, hi, shape, dtype=torch.uint8, device="cuda", generator=gen)
+    router_w = (torch.randn(E, H, device="cuda", generator=gen) / H ** 0.5).to(torch.bfloat16).float()
+    perm = torch.randperm(E, device="cuda", generator=gen).float() + 1.0
+    pop = perm ** -1.1
+    router_b = torch.log(pop / pop.sum() * E).to(torch.bfloat16).float()
+    per = E // world
+    lo = rank * per
+    gu_b, gu_s = u8(E, 2 * I, H // 32, 16), u8(E, 2 * I, H // 32, lo=117, hi=124)
+    dn_b, dn_s = u8(E, H, I // 32, 16), u8(E, H, I // 32, lo=117, hi=124)
+    moe = gb.GptOssMoe(H, I, E, K, io_dtype=torch.bfloat16, ep_rank=rank, ep_world=world,
+                       expert_weights_sharded=True).prepare(
+        router_w, router_b, gu_b[lo:lo + per].contiguous(), gu_s[lo:lo + per].contiguous(),
+        torch.zeros(per, 2 * I, device="cuda"), dn_b[lo:lo + per].contiguous(), dn_s[lo:lo + per].contiguous(),
+        torch.zeros(per, H, device="cuda"))
+    del gu_b, gu_s, dn_b, dn_s
+    torch.cuda.empty_cache()
+    t_local = tokens_total // world
+    gx = torch.Generator(device="cuda")
+    gx.manual_seed(1000 + rank)
+    x = torch.randn(t_local, H, device="cuda", generator=gx).to(torch.bfloat16)
+
+    def route(a):
+        _, sel, pr = moe.route(a)
+        return sel, pr
+
+    ep = ExpertParallelMoe(route, moe.run_rows, moe.combine, E, K)
+    for _ in range(3):
+        y = ep.forward(x)
+    dist.barrier()
+    torch.cuda.synchronize()
+    steps = max(3, min(args.steps, 10))
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        y = ep.forward(x)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    t = torch.tensor([ms, float(ep.last_recv_rows)], device="cuda")
+    tmax = t.clone()
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    tsum = t.clone()
+    dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+    ms = float(tmax[0].item())
+    return {"tokens": tokens_total, "ms": round(ms, 4), "tok_per_s": round(tokens_total / (ms * 1e-3), 1),
+            "experts_per_gpu": per, "routing": "zipf(1.1) popularity over a seeded permutation",
+            "max_rows_on_one_gpu": int(tmax[1].item()), "mean_rows_per_gpu": round(float(tsum[1].item()) / world, 1),
+            "TFLOPs": round(199065600.0 * tokens_total / (ms * 1e-3) / 1e12, 2), "finite": bool(torch.isfinite(y).all().item())}
 
 
 # ------------------------------------------------------------- CPU baseline

@@ -17,6 +17,7 @@
 // bits, fp16 carries 11).
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -656,6 +657,18 @@ __global__ void moe_combine_kernel(const float* __restrict__ vals, const float* 
 
 // ------------------------------------------------------------------ handle
 
+__global__ void mx_scale_range_kernel(const uint8_t* __restrict__ scales, size_t count, int* lo, int* hi);   // moe_tc.cu
+
+bool Moe::use_tc(int slots) const
+{
+    // GARNET_B200_MOE_NO_TC=1 keeps every size on the streaming kernel (A/B switch).
+    static const bool enabled = [] {
+        const char* e = getenv("GARNET_B200_MOE_NO_TC");
+        return !(e && e[0] == '1');
+    }();
+    return enabled && tc_ok && (long long)slots >= 16LL * local_experts() && opt.experts <= 1024;
+}
+
 constexpr size_t kMaxDynamicSmem = 227 * 1024;
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -680,6 +693,10 @@ MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens)
     w.sorted = take(slots * 4);
     w.ntasks = take(4);
     w.tasks = take((slots / kMoeRows + o.experts + 1) * 16);
+    // rows gathered into expert order: only the tensor-core path uses them
+    const bool tc = moe_tc_eligible(o, tokens);
+    w.xg = take(tc ? slots * o.hidden * 2 : 0);
+    w.xshift_g = take(tc ? slots * 4 : 0);
     w.act = take(slots * o.intermediate * 2);
     w.vals = take(slots * o.hidden * 4);
     w.total = off;
@@ -737,6 +754,7 @@ Moe::~Moe()
     if (packed_up) cudaFree(packed_up);
     if (packed_down) cudaFree(packed_down);
     if (flag_dev) cudaFree(flag_dev);
+    if (range_dev) cudaFree(range_dev);
     if (fault_host) cudaFreeHost(fault_host);
 }
 
@@ -761,6 +779,9 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
     GB_CUDA(cudaMalloc(&packed_down, geo_down.matrix_bytes() * stored_experts));
     GB_CUDA(cudaMalloc(&flag_dev, sizeof(int)));
     GB_CUDA(cudaMemsetAsync(flag_dev, 0, sizeof(int), stream));
+    GB_CUDA(cudaMalloc(&range_dev, 4 * sizeof(int)));
+    const int range_init[4] = {255, 0, 255, 0};   // {min, max} of the gate_up scales, then of the down scales
+    GB_CUDA(cudaMemcpyAsync(range_dev, range_init, sizeof(range_init), cudaMemcpyHostToDevice, stream));
     GB_CUDA(cudaHostAlloc(&fault_host, sizeof(int), cudaHostAllocMapped));
     *fault_host = 0;
     GB_CUDA(cudaHostGetDevicePointer(&fault_dev, fault_host, 0));
@@ -793,14 +814,18 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
             const size_t cnt = size_t(run) * sc_per_expert;
             mx_scan_scales_kernel<<<unsigned((cnt + 255) / 256), 256, 0, stream>>>(scales + e0 * sc_per_expert, cnt,
                                                                                  flag_dev);
+            mx_scale_range_kernel<<<256, 256, 0, stream>>>(scales + e0 * sc_per_expert, cnt, range_dev + 2 * pass,
+                                                          range_dev + 2 * pass + 1);
             s += run;
         }
     }
     GB_CUDA(cudaGetLastError());
-    int flag = 0;
+    int flag = 0, range[4] = {255, 0, 255, 0};
     GB_CUDA(cudaMemcpyAsync(&flag, flag_dev, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    GB_CUDA(cudaMemcpyAsync(range, range_dev, sizeof(range), cudaMemcpyDeviceToHost, stream));
     GB_CUDA(cudaStreamSynchronize(stream));
     careful_scales = flag != 0;
+    if (int rc = init_tc(range[0], range[1], range[2], range[3])) return rc;
     // router and biases are borrowed from the caller (engine-owned constants)
     router_w_ptr = static_cast<const float*>(weights[0]);
     router_b_ptr = static_cast<const float*>(weights[1]);
@@ -910,6 +935,8 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     w.sorted = reinterpret_cast<int*>(b + plan.sorted);
     w.ntasks = reinterpret_cast<int*>(b + plan.ntasks);
     w.tasks = reinterpret_cast<int4*>(b + plan.tasks);
+    w.xg = reinterpret_cast<__half*>(b + plan.xg);
+    w.xshift_g = reinterpret_cast<int*>(b + plan.xshift_g);
     w.act = reinterpret_cast<__half*>(b + plan.act);
     w.vals = reinterpret_cast<float*>(b + plan.vals);
 
@@ -920,8 +947,14 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(w.selected, slots, w.counts, w.offsets, w.sorted, w.tasks,
                                                      w.ntasks, opt.experts, kMoeRows, sh);
     GB_CUDA(cudaGetLastError());
-    if (int rc = launch_stream(true, w, tokens, stream)) return rc;
-    if (int rc = launch_stream(false, w, tokens, stream)) return rc;
+    if (use_tc(slots) && moe_tc_eligible(opt, tokens)) {
+        if (int rc = gather_rows(w, slots, opt.top_k, stream)) return rc;
+        if (int rc = launch_tc(true, w, slots, stream)) return rc;
+        if (int rc = launch_tc(false, w, slots, stream)) return rc;
+    } else {
+        if (int rc = launch_stream(true, w, tokens, stream)) return rc;
+        if (int rc = launch_stream(false, w, tokens, stream)) return rc;
+    }
     const size_t n = size_t(tokens) * opt.hidden;
     const int round_output = sh.world > 1 ? 0 : 1;
     if (opt.io_dtype == GARNET_B200_FP32)
@@ -949,6 +982,8 @@ static MoeWorkspacePtrs bind_workspace(void* ws, const MoeWorkspace& plan)
     w.sorted = reinterpret_cast<int*>(b + plan.sorted);
     w.ntasks = reinterpret_cast<int*>(b + plan.ntasks);
     w.tasks = reinterpret_cast<int4*>(b + plan.tasks);
+    w.xg = reinterpret_cast<__half*>(b + plan.xg);
+    w.xshift_g = reinterpret_cast<int*>(b + plan.xshift_g);
     w.act = reinterpret_cast<__half*>(b + plan.act);
     w.vals = reinterpret_cast<float*>(b + plan.vals);
     return w;
@@ -990,6 +1025,13 @@ int Moe::run_rows(const void* x_rows, const int* row_expert, int rows, float* va
     moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(row_expert, rows, w.counts, w.offsets, w.sorted, w.tasks, w.ntasks,
                                                      opt.experts, kMoeRows, sh);
     GB_CUDA(cudaGetLastError());
+    garnet_b200_moe_options one = opt;
+    one.top_k = 1;
+    if (use_tc(rows) && moe_tc_eligible(one, rows)) {
+        if (int rc = gather_rows(w, rows, 1, stream)) return rc;
+        if (int rc = launch_tc(true, w, rows, stream)) return rc;
+        return launch_tc(false, w, rows, stream);
+    }
     if (int rc = launch_stream(true, w, rows, stream, 1)) return rc;
     return launch_stream(false, w, rows, stream, 1);
 }

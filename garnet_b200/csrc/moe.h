@@ -21,7 +21,7 @@ struct MoeShard {
 
 // Byte offsets of the regions of the caller's workspace.
 struct MoeWorkspace {
-    size_t logits, selected, probs, xshift, xh, counts, offsets, sorted, ntasks, tasks, act, vals, total;
+    size_t logits, selected, probs, xshift, xh, counts, offsets, sorted, ntasks, tasks, xg, xshift_g, act, vals, total;
 };
 
 struct MoeWorkspacePtrs {
@@ -35,12 +35,16 @@ struct MoeWorkspacePtrs {
     int* sorted;
     int* ntasks;
     int4* tasks;
+    __half* xg;        // rows gathered into expert order (tensor-core path)
+    int* xshift_g;
     __half* act;
     float* vals;
 };
 
 MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens);
 MoeWorkspace moe_rows_workspace_plan(const garnet_b200_moe_options& o, int rows);
+// True when the per-expert row counts are large enough for the tensor-core tile kernel.
+bool moe_tc_eligible(const garnet_b200_moe_options& o, int tokens);
 
 struct Moe {
     garnet_b200_moe_options opt{};
@@ -53,6 +57,11 @@ struct Moe {
     const float* up_bias_ptr = nullptr;
     const float* down_bias_ptr = nullptr;
     bool careful_scales = false;       // some e8m0 byte is 0 or 255
+    struct alignas(64) TensorMapStorage { unsigned char bytes[128]; };
+    TensorMapStorage tc_w_map[2];      // TMA views of the packed gate_up / down matrices
+    bool tc_ok = false;                // scale bytes fit the fp16 window of the tensor-core path
+    int ref_up = 0, ref_down = 0;      // exponent references of that path
+    int* range_dev = nullptr;
     int* flag_dev = nullptr;
     int* fault_host = nullptr;
     int* fault_dev = nullptr;
@@ -66,6 +75,10 @@ struct Moe {
     int launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream, int topk = -1);
     int run_rows(const void* x_rows, const int* row_expert, int rows, float* vals, void* ws, size_t ws_bytes,
                  cudaStream_t stream);
+    int init_tc(int lo_up, int hi_up, int lo_dn, int hi_dn);
+    int gather_rows(const MoeWorkspacePtrs& w, int slots, int topk, cudaStream_t stream);
+    int launch_tc(bool up, const MoeWorkspacePtrs& w, int slots, cudaStream_t stream);
+    bool use_tc(int slots) const;
     int combine(const float* vals, const float* probs, void* y, int tokens, cudaStream_t stream);
     int run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cudaStream_t stream);
 };

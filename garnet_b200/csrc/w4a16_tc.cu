@@ -58,7 +58,6 @@ struct TcParams {
     int strips_padded, chunks;
     int panels, token_tiles;
     int scale_dtype;
-    int debug;
 };
 
 template <int kATiles>
@@ -207,12 +206,8 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                         *abort_flag = 1;
                         break;
                     }
-                    if (p.debug & 4) {
-                        mbar_arrive(&b_full[s]);
-                    } else {
-                        mbar_expect_tx(&b_full[s], kTcTileBytes);
-                        tma_load_2d(b_ring + s * kTcTileBytes, &x_map, kt * 64, tt * kTcTokens, &b_full[s]);
-                    }
+                    mbar_expect_tx(&b_full[s], kTcTileBytes);
+                    tma_load_2d(b_ring + s * kTcTileBytes, &x_map, kt * 64, tt * kTcTokens, &b_full[s]);
                     ++ab_n;
                 }
             }
@@ -243,7 +238,6 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                     }
                     tc_fence_after();
                     const uint32_t b_addr = smem_u32(b_ring + sb * kTcTileBytes);
-                    if (!(p.debug & 2))
 #pragma unroll
                     for (int k16 = 0; k16 < 4; ++k16) {
                         const uint64_t bd = umma_desc_k_sw128(b_addr + k16 * 32);
@@ -289,7 +283,7 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                     tc_fence_after();
                     {
                         const int sidx = dq, at = dq >> 3;   // this warp's strip, and the A tile it belongs to
-                        if (sidx < valid && !(p.debug & 1)) {
+                        if (sidx < valid) {
                             const uint8_t* sc = pk + sidx * kTcChunkBytes;
                             const uint4 u = *reinterpret_cast<const uint4*>(sc + half * 512 + lane * 16);
                             const uint32_t sw = *reinterpret_cast<const uint32_t*>(sc + 1024 + g * 4);
@@ -318,7 +312,7 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                             *reinterpret_cast<uint4*>(tile + r1 * 128 + (((t + 4) ^ x0) << 4)) = v3;
                         }
                     }
-                    if (!(p.debug & 16)) fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core
+                    fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&a_full[s]);
                     ++ab_n;
@@ -355,7 +349,7 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * (kATiles * 128) + at * 128 + c0, r);
                     tmem_ld_wait();
-                    if (n < p.n && !(p.debug & 8)) {
+                    if (n < p.n) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (c0 + j < rows)
@@ -453,12 +447,10 @@ int W4A16::launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, unsigned f
     p.chunks = geo.chunks;
     p.token_tiles = (m + kTcTokens - 1) / kTcTokens;
     p.scale_dtype = scale_dtype;
-    p.debug = getenv("GARNET_B200_TC_DEBUG") ? atoi(getenv("GARNET_B200_TC_DEBUG")) : 0;
     // 256-row CTA tiles halve the activation traffic per weight row; use them when
     // there are enough tiles to fill the machine, else 128-row tiles.
     const int panels256 = (geo.strips_padded + 15) / 16;
-    int atiles = panels256 * p.token_tiles >= 2 * kSmCount ? 2 : 1;
-    if (const char* e = getenv("GARNET_B200_TC_ATILES")) atiles = e[0] == '1' ? 1 : 2;   // A/B switch
+    const int atiles = panels256 * p.token_tiles >= 2 * kSmCount ? 2 : 1;
     p.panels = atiles == 2 ? panels256 : geo.strips_padded / 8;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(std::min(p.panels * p.token_tiles, kSmCount)));
