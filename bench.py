@@ -473,15 +473,22 @@ def run_reference(args):
 def run_profile_case(spec):
     """Small fixed case for profiler captures: `w4a16:K:N:M` runs one linear a few
     times without a graph (3 warm-up launches, 3 measured ones) and prints the
-    CUDA-event time per launch."""
+    CUDA-event time per launch; `moe:T` runs the MoE layer on T tokens."""
     import torch
 
     import garnet_b200 as gb
 
+    torch.cuda.set_device(0)
+    if spec.startswith("moe:"):
+        # `moe:T`: the gpt-oss-120b MoE layer on T tokens, 2 warm-up calls + 2 timed calls
+        class A:
+            steps = 2
+        rows = bench_moe(torch, gb, measured_peaks(), A, token_counts=(int(spec.split(":")[1]),))
+        print(json.dumps({"case": spec, **rows[0]}))
+        return
     kind, k, n, m = spec.split(":")
     k, n, m = int(k), int(n), int(m)
     assert kind == "w4a16"
-    torch.cuda.set_device(0)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(0)
     lins = [make_linear(torch, gb, k, n, gen) for _ in range(2)]

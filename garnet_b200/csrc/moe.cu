@@ -193,21 +193,39 @@ moe_route_scores_kernel(const XT* __restrict__ x, const float* __restrict__ rw, 
     }
     __syncthreads();
     const int e0 = blockIdx.y * experts_per_cta, e1 = min(experts, e0 + experts_per_cta);
-    for (int e = e0 + warp; e < e1; e += kRouteWarps) {
-        float acc[kRouteTokens];
+    // A warp takes four experts at a time: every activation value read from shared
+    // memory feeds four FMAs (one per expert), every weight value eight (one per token).
+    constexpr int kEx = 4;
+    for (int eb = e0 + warp * kEx; eb < e1; eb += kRouteWarps * kEx) {
+        float acc[kEx][kRouteTokens];
 #pragma unroll
-        for (int t = 0; t < kRouteTokens; ++t) acc[t] = 0.f;
-        const float* w = rw + size_t(e) * hidden;
+        for (int q = 0; q < kEx; ++q)
+#pragma unroll
+            for (int t = 0; t < kRouteTokens; ++t) acc[q][t] = 0.f;
+        const float* w[kEx];
+#pragma unroll
+        for (int q = 0; q < kEx; ++q) w[q] = rw + size_t(min(eb + q, e1 - 1)) * hidden;
         for (int d = lane; d < hidden; d += 32) {
-            const float wv = w[d];
+            float wv[kEx];
 #pragma unroll
-            for (int t = 0; t < kRouteTokens; ++t) acc[t] = fmaf(xs[t * hidden + d], wv, acc[t]);
+            for (int q = 0; q < kEx; ++q) wv[q] = w[q][d];
+#pragma unroll
+            for (int t = 0; t < kRouteTokens; ++t) {
+                const float xv = xs[t * hidden + d];
+#pragma unroll
+                for (int q = 0; q < kEx; ++q) acc[q][t] = fmaf(xv, wv[q], acc[q][t]);
+            }
         }
-        const float b = rb[e];
 #pragma unroll
-        for (int t = 0; t < kRouteTokens; ++t) {
-            const float v = warp_sum(acc[t]);
-            if (lane == 0 && t < nt) logits[size_t(t0 + t) * experts + e] = bf16_round_f(v + b);
+        for (int q = 0; q < kEx; ++q) {
+            const int e = eb + q;
+            if (e >= e1) break;
+            const float b = rb[e];
+#pragma unroll
+            for (int t = 0; t < kRouteTokens; ++t) {
+                const float v = warp_sum(acc[q][t]);
+                if (lane == 0 && t < nt) logits[size_t(t0 + t) * experts + e] = bf16_round_f(v + b);
+            }
         }
     }
     if (blockIdx.y != 0 || !xh) return;
@@ -851,8 +869,8 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
     // spread the experts over enough CTAs to fill the machine at small token counts
     const int token_ctas = (tokens + kRouteTokens - 1) / kRouteTokens;
     int per_cta = opt.experts;
-    while (per_cta > kRouteWarps && token_ctas * ((opt.experts + per_cta - 1) / per_cta) < 2 * kSmCount) per_cta = (per_cta + 1) / 2;
-    per_cta = std::max(per_cta, std::min(opt.experts, kRouteWarps));
+    while (per_cta > 4 * kRouteWarps && token_ctas * ((opt.experts + per_cta - 1) / per_cta) < 2 * kSmCount) per_cta = (per_cta + 1) / 2;
+    per_cta = std::max(per_cta, std::min(opt.experts, 4));
     const dim3 grid(token_ctas, (opt.experts + per_cta - 1) / per_cta);
     if (opt.io_dtype == GARNET_B200_FP32) {
         moe_route_scores_kernel<float><<<grid, kRouteWarps * 32, smem, stream>>>(

@@ -249,8 +249,8 @@ moe_tc_kernel(const MtParams p, const __grid_constant__ CUtensorMap x_map, const
             int cur = 0;
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
                 const MtItem it = mt_decode(p, tile_prefix, p.offsets, item, cur);
-                const int nt = (it.rows + 15) & ~15;
-                const uint32_t idesc = umma_idesc_f16(0, 128, nt);
+                // UMMA M = 128 rows (TMEM lanes), N = 256 weight rows of the panel (TMEM columns)
+                const uint32_t idesc = umma_idesc_f16(0, kMtTokens, kMtATiles * 128);
                 const uint32_t buf = it_n & 1;
                 if (it_n >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((it_n >> 1) - 1) & 1)) {
                     atomicExch(p.fault, 23);
@@ -267,17 +267,14 @@ moe_tc_kernel(const MtParams p, const __grid_constant__ CUtensorMap x_map, const
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t b_addr = smem_u32(b_ring + sb * kMtTileBytes);
+                    // rows are the UMMA A operand; the two expanded weight tiles of the stage
+                    // are contiguous and form one 256-row B operand
+                    const uint32_t x_addr = smem_u32(b_ring + sb * kMtTileBytes);
+                    const uint32_t w_addr = smem_u32(a_ring + s * kMtATiles * kMtTileBytes);
 #pragma unroll
-                    for (int k16 = 0; k16 < 4; ++k16) {
-                        const uint64_t bd = umma_desc_k_sw128(b_addr + k16 * 32);
-#pragma unroll
-                        for (int at = 0; at < kMtATiles; ++at) {
-                            const uint32_t a_addr = smem_u32(a_ring + (s * kMtATiles + at) * kMtTileBytes);
-                            umma_f16(tmem_base + buf * (kMtATiles * 128) + at * 128, umma_desc_k_sw128(a_addr + k16 * 32),
-                                     bd, idesc, kt > 0 || k16 > 0);
-                        }
-                    }
+                    for (int k16 = 0; k16 < 4; ++k16)
+                        umma_f16(tmem_base + buf * (kMtATiles * 128), umma_desc_k_sw128(x_addr + k16 * 32),
+                                 umma_desc_k_sw128(w_addr + k16 * 32), idesc, kt > 0 || k16 > 0);
                     umma_commit(&a_empty[s]);
                     umma_commit(&b_empty[sb]);
                     ++ab_n;
@@ -348,54 +345,65 @@ moe_tc_kernel(const MtParams p, const __grid_constant__ CUtensorMap x_map, const
             }
             tc_fence_after();
             const int ebias = p.bias_by_global ? it.expert : (it.expert - p.expert_base) / p.expert_div;
-#pragma unroll
-            for (int at = 0; at < kMtATiles; ++at) {
-                const int strip = it.panel * kMtStrips + at * 8 + (l >> 4);
-                const int r16 = l & 15;
-                for (int c0 = 0; c0 < it.rows; c0 += 32) {
+            // TMEM lane = row of the tile (a routed slot), column = weight row of the panel.
+            const bool live = l < it.rows;
+            const int pos = it.row0 + min(l, it.rows - 1);
+            const float* bias = p.bias + size_t(ebias) * p.rows;
+            if (kUp) {
+                // 32 columns = two strips; in a strip, columns 0..7 are the gates and 8..15 the
+                // ups of channels 8*strip .. 8*strip+7 (the repacker's row order).
+                const float f = __uint_as_float(uint32_t(p.ref_exp + p.xshift_g[pos]) << 23);
+                __half* arow = p.act_out + size_t(pos) * (p.rows / 2);
+                for (int c0 = 0; c0 < kMtATiles * 128; c0 += 32) {
+                    const int strip0 = it.panel * kMtStrips + (c0 >> 4);
+                    if (strip0 * 16 >= p.rows) break;   // warp-uniform
                     uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * (kMtATiles * 128) + at * 128 + c0, r);
+                    tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * (kMtATiles * 128) + c0, r);
                     tmem_ld_wait();
-                    if (kUp) {
-                        // strip row r16 < 8: gate of channel i; r16 >= 8: up of the same channel,
-                        // held by the lane 8 further on.  Each of the two lanes finishes half
-                        // of the columns.
-                        const int i = strip * 8 + (r16 & 7);
-                        const bool is_up = r16 >= 8;
-                        const bool valid = 2 * i + 1 < p.rows;
-                        float b0 = 0.f, b1 = 0.f;
-                        if (valid) {
-                            b0 = p.bias[size_t(ebias) * p.rows + 2 * i];
-                            b1 = p.bias[size_t(ebias) * p.rows + 2 * i + 1];
-                        }
+                    if (!live) continue;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const uint32_t other = __shfl_xor_sync(0xffffffffu, r[j], 8);
-                            if (((j & 1) != 0) != is_up || !valid || c0 + j >= it.rows) continue;
-                            const int pos = it.row0 + c0 + j;
-                            const float f = __uint_as_float(uint32_t(p.ref_exp + p.xshift_g[pos]) << 23);
-                            float gate = __uint_as_float(is_up ? other : r[j]) * f;
-                            float up = __uint_as_float(is_up ? r[j] : other) * f;
-                            gate = fminf(bf16_round_f(bf16_round_f(gate) + b0), p.limit);
-                            up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(up) + b1)));
+                    for (int h = 0; h < 2; ++h) {
+                        const int i0 = (strip0 + h) * 8;
+                        if (2 * i0 >= p.rows) break;
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            float gate = __uint_as_float(r[16 * h + q]) * f;
+                            float up = __uint_as_float(r[16 * h + 8 + q]) * f;
+                            gate = fminf(bf16_round_f(bf16_round_f(gate) + bias[2 * (i0 + q)]), p.limit);
+                            up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(up) + bias[2 * (i0 + q) + 1])));
                             const float sig = bf16_round_f(1.f / (1.f + expf(-bf16_round_f(1.702f * gate))));
                             const float glu = bf16_round_f(gate * sig);
-                            p.act_out[size_t(pos) * (p.rows / 2) + i] =
-                                __float2half_rn(bf16_round_f(glu * bf16_round_f(up + 1.f)));
+                            const uint32_t hv = __half_as_ushort(__float2half_rn(bf16_round_f(glu * bf16_round_f(up + 1.f))));
+                            if (q & 1) packed[q >> 1] |= hv << 16;
+                            else packed[q >> 1] = hv;
                         }
-                    } else {
-                        const int d = strip * 16 + r16;
-                        if (d < p.rows) {
-                            const float bd = p.bias[size_t(ebias) * p.rows + d];
-                            const float f = __uint_as_float(uint32_t(p.ref_exp) << 23);
+                        *reinterpret_cast<uint4*>(arow + i0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
+                }
+            } else {
+                const float f = __uint_as_float(uint32_t(p.ref_exp) << 23);
+                float* vrow = p.vals_out + size_t(p.sorted[pos]) * p.rows;
+                for (int c0 = 0; c0 < kMtATiles * 128; c0 += 32) {
+                    const int d0 = it.panel * (kMtATiles * 128) + c0;
+                    if (d0 >= p.rows) break;   // warp-uniform
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * (kMtATiles * 128) + c0, r);
+                    tmem_ld_wait();
+                    if (!live) continue;
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (c0 + j >= it.rows) continue;
-                                const int slot = p.sorted[it.row0 + c0 + j];
-                                p.vals_out[size_t(slot) * p.rows + d] =
-                                    bf16_round_f(bf16_round_f(__uint_as_float(r[j]) * f) + bd);
-                            }
+                    for (int q = 0; q < 8; ++q) {
+                        float4 v;
+                        float* vp = reinterpret_cast<float*>(&v);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int d = d0 + 4 * q + j;
+                            vp[j] = d < p.rows ? bf16_round_f(bf16_round_f(__uint_as_float(r[4 * q + j]) * f) + bias[d]) : 0.f;
                         }
+                        if (d0 + 4 * q + 3 < p.rows) *reinterpret_cast<float4*>(vrow + d0 + 4 * q) = v;
+                        else
+                            for (int j = 0; j < 4; ++j)
+                                if (d0 + 4 * q + j < p.rows) vrow[d0 + 4 * q + j] = vp[j];
                     }
                 }
             }

@@ -217,10 +217,8 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
         if (lane == 0) {
             uint32_t ab_n = 0, it_n = 0;
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
-                const int tt = item % p.token_tiles;
-                const int rows = min(kTcTokens, p.m - tt * kTcTokens);
-                const int nt = (rows + 15) & ~15;
-                const uint32_t idesc = umma_idesc_f16(1, 128, nt);
+                                // UMMA M = 128 batch rows (TMEM lanes), N = the tile's weight rows (TMEM columns)
+                const uint32_t idesc = umma_idesc_f16(1, kTcTokens, kATiles * 128);
                 const uint32_t buf = it_n & 1;
                 if (it_n >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((it_n >> 1) - 1) & 1)) {
                     atomicExch(p.fault, 13);
@@ -237,17 +235,15 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t b_addr = smem_u32(b_ring + sb * kTcTileBytes);
+                    // The activation tile is the UMMA A operand; the expanded weight tiles of
+                    // the stage are contiguous and form one B operand of kATiles*128 rows.  One
+                    // instruction per 16 columns of K reads 4 KiB + kATiles*4 KiB of shared memory.
+                    const uint32_t x_addr = smem_u32(b_ring + sb * kTcTileBytes);
+                    const uint32_t w_addr = smem_u32(a_ring + s * kATiles * kTcTileBytes);
 #pragma unroll
-                    for (int k16 = 0; k16 < 4; ++k16) {
-                        const uint64_t bd = umma_desc_k_sw128(b_addr + k16 * 32);
-#pragma unroll
-                        for (int at = 0; at < kATiles; ++at) {
-                            const uint32_t a_addr = smem_u32(a_ring + (s * kATiles + at) * kTcTileBytes);
-                            umma_f16(tmem_base + buf * (kATiles * 128) + at * 128, umma_desc_k_sw128(a_addr + k16 * 32),
-                                     bd, idesc, kt > 0 || k16 > 0);
-                        }
-                    }
+                    for (int k16 = 0; k16 < 4; ++k16)
+                        umma_f16(tmem_base + buf * (kATiles * 128), umma_desc_k_sw128(x_addr + k16 * 32),
+                                 umma_desc_k_sw128(w_addr + k16 * 32), idesc, kt > 0 || k16 > 0);
                     umma_commit(&a_empty[s]);    // stages reusable once these MMAs have read them
                     umma_commit(&b_empty[sb]);
                     ++ab_n;
@@ -340,21 +336,34 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                 pdl_wait();   // y may still be read by the previous kernel in the stream
                 waited = true;
             }
-            const int m0 = tt * kTcTokens;
-            const int rows = min(kTcTokens, p.m - m0);
+            // TMEM lane = batch row of the tile, column = weight row of the panel: a thread
+            // reads 32 consecutive outputs of its row and stores them as 64 contiguous bytes.
+            const int m = tt * kTcTokens + quarter * 32 + lane;
+            __nv_bfloat16* yrow = p.y + size_t(min(m, p.m - 1)) * p.ldy;
+            const bool vec_ok = (p.ldy & 7) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0;
+            for (int c0 = 0; c0 < kATiles * 128; c0 += 32) {
+                const int n0 = panel * (kATiles * 128) + c0;
+                if (n0 >= p.n) break;   // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * (kATiles * 128) + c0, r);
+                tmem_ld_wait();
+                if (m >= p.m) continue;
+                if (vec_ok && n0 + 32 <= p.n) {
 #pragma unroll
-            for (int at = 0; at < kATiles; ++at) {
-                const int n = panel * (kATiles * 128) + at * 128 + quarter * 32 + lane;
-                for (int c0 = 0; c0 < rows; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * (kATiles * 128) + at * 128 + c0, r);
-                    tmem_ld_wait();
-                    if (n < p.n) {
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t w[4];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (c0 + j < rows)
-                                p.y[size_t(m0 + c0 + j) * p.ldy + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        for (int j = 0; j < 4; ++j) {
+                            const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * q + 2 * j]),
+                                                                           __uint_as_float(r[8 * q + 2 * j + 1]));
+                            w[j] = *reinterpret_cast<const uint32_t*>(&v);
+                        }
+                        *reinterpret_cast<uint4*>(yrow + n0 + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (n0 + j < p.n) yrow[n0 + j] = __float2bfloat16_rn(__uint_as_float(r[j]));
                 }
             }
             tc_fence_before();
