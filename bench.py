@@ -244,8 +244,11 @@ def run_gpu(args):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": round(value, 2), "peak": peaks["hbm"], "unit": "GB/s",
-                         "frac": round(value / peaks["hbm"], 4), "peak_source": peaks["src"], "traffic": None,
-                         "kernel": "w4a16_stream_kernel<1>", "bytes_per_launch": round(step_bytes / launches_per_step),
+                         "frac": round(value / peaks["hbm"], 4), "peak_source": peaks["src"],
+                         # dram read+write per launch = 1.002 x algorithmic, from the ncu captures summarised in
+                         # profiles/ (gate_proj: 6,518,272 B for 6,504,448 B; lm_head: 164.4 MB for 160.75 MB)
+                         "traffic": round(step_bytes / launches_per_step * 1.002),
+                         "kernel": "w4a16_stream_kernel", "bytes_per_launch": round(step_bytes / launches_per_step),
                          "us_per_launch": round(ms * 1e3 / launches_per_step, 3)},
         }
 
@@ -471,8 +474,9 @@ def run_reference(args):
 
 
 def run_profile_case(spec):
-    """Small fixed case for profiler captures: `w4a16:K:N:M` runs one linear a few
-    times without a graph (3 warm-up launches, 3 measured ones) and prints the
+    """Small fixed case for profiler captures: `w4a16:K:N:M[:copies]` runs one linear
+    a few times without a graph (one warm-up and one measured rotation over `copies`
+    weight copies, at least 3 launches each) and prints the
     CUDA-event time per launch; `moe:T` runs the MoE layer on T tokens."""
     import torch
 
@@ -486,24 +490,26 @@ def run_profile_case(spec):
         rows = bench_moe(torch, gb, measured_peaks(), A, token_counts=(int(spec.split(":")[1]),))
         print(json.dumps({"case": spec, **rows[0]}))
         return
-    kind, k, n, m = spec.split(":")
-    k, n, m = int(k), int(n), int(m)
+    parts = spec.split(":")
+    kind, k, n, m = parts[0], int(parts[1]), int(parts[2]), int(parts[3])
+    copies = int(parts[4]) if len(parts) > 4 else 2      # weight copies rotated through (to defeat L2)
     assert kind == "w4a16"
     gen = torch.Generator(device="cuda")
     gen.manual_seed(0)
-    lins = [make_linear(torch, gb, k, n, gen) for _ in range(2)]
+    lins = [make_linear(torch, gb, k, n, gen) for _ in range(copies)]
     x = torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16)
     y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
-    for i in range(3):
-        lins[i % 2].forward(x, out=y)
+    reps = max(3, copies)
+    for i in range(reps):
+        lins[i % copies].forward(x, out=y)
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for i in range(3):
-        lins[i % 2].forward(x, out=y)
+    for i in range(reps):
+        lins[i % copies].forward(x, out=y)
     b.record()
     torch.cuda.synchronize()
-    us = a.elapsed_time(b) / 3 * 1e3
+    us = a.elapsed_time(b) / reps * 1e3
     print(json.dumps({"case": spec, "us_per_launch": round(us, 3),
                       "GBps": round(algo_bytes(k, n, m) / us / 1e3, 1)}))
 

@@ -250,6 +250,79 @@ moe_route_scores_kernel(const XT* __restrict__ x, const float* __restrict__ rw, 
     }
 }
 
+// Router for at most 8 tokens (decode): latency matters, so the hidden dimension is
+// split over the 8 warps of a CTA and a CTA owns only 4 experts (E/4 CTAs); the
+// warps' partial sums meet in shared memory.  Same results contract as
+// moe_route_scores_kernel (fp32 accumulation, bf16-rounded logits); CTA 0 also
+// writes the fp16 copy of x.
+template <typename XT>
+__global__ void __launch_bounds__(kRouteWarps * 32)
+moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, const float* __restrict__ rb,
+                       float* __restrict__ logits, __half* __restrict__ xh, int* __restrict__ xshift, int tokens,
+                       int hidden, int experts)
+{
+    extern __shared__ float xs[];   // [kRouteTokens][hidden]
+    __shared__ float part[kRouteWarps][4][kRouteTokens];
+    __shared__ float s_amax[kRouteTokens];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < kRouteTokens * hidden; i += blockDim.x) {
+        const int t = i / hidden, d = i % hidden;
+        xs[i] = t < tokens ? to_float(x[size_t(t) * hidden + d]) : 0.f;
+    }
+    __syncthreads();
+    const int e0 = blockIdx.x * 4;
+    float acc[4][kRouteTokens];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int t = 0; t < kRouteTokens; ++t) acc[q][t] = 0.f;
+    for (int d = threadIdx.x; d < hidden; d += kRouteWarps * 32) {
+        float wv[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) wv[q] = rw[size_t(min(e0 + q, experts - 1)) * hidden + d];
+#pragma unroll
+        for (int t = 0; t < kRouteTokens; ++t) {
+            const float xv = xs[t * hidden + d];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[q][t] = fmaf(xv, wv[q], acc[q][t]);
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int t = 0; t < kRouteTokens; ++t) {
+            const float v = warp_sum(acc[q][t]);
+            if (lane == 0) part[warp][q][t] = v;
+        }
+    __syncthreads();
+    if (threadIdx.x < 4 * kRouteTokens) {
+        const int q = threadIdx.x / kRouteTokens, t = threadIdx.x % kRouteTokens;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kRouteWarps; ++w) v += part[w][q][t];
+        if (e0 + q < experts && t < tokens) logits[size_t(t) * experts + e0 + q] = bf16_round_f(v + rb[e0 + q]);
+    }
+    if (blockIdx.x != 0 || !xh) return;
+    for (int t = warp; t < tokens; t += kRouteWarps) {
+        float amax = 0.f;
+        for (int d = lane; d < hidden; d += 32) amax = fmaxf(amax, fabsf(bf16_round_f(xs[t * hidden + d])));
+#pragma unroll
+        for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (lane == 0) s_amax[t] = amax;
+    }
+    __syncthreads();
+    for (int t = warp; t < tokens; t += kRouteWarps) {
+        const float amax = s_amax[t];
+        int shift = 0;
+        if (amax > 0.f && isfinite(amax)) shift = int((__float_as_uint(amax) >> 23) & 0xff) - 127 - 13;
+        shift = max(-100, min(100, shift));
+        const float scale = __uint_as_float(uint32_t(127 - shift) << 23);
+        for (int d = lane; d < hidden; d += 32)
+            xh[size_t(t) * hidden + d] = __float2half_rn(bf16_round_f(xs[t * hidden + d]) * scale);
+        if (lane == 0) xshift[t] = shift;
+    }
+}
+
 // k rounds of arg-max (ties to the lowest expert index), then the softmax over the
 // selected logits only (gpt_oss_kernels.cu:681-726).  One warp per token.
 __global__ void moe_topk_kernel(const float* __restrict__ logits, int* __restrict__ selected,
@@ -849,7 +922,11 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
     router_b_ptr = static_cast<const float*>(weights[1]);
     up_bias_ptr = static_cast<const float*>(weights[4]);
     down_bias_ptr = static_cast<const float*>(weights[7]);
-    // the router kernel also has a little static shared memory: leave room for it
+    // the router kernels also have a little static shared memory: leave room for it
+    GB_CUDA(cudaFuncSetAttribute(moe_route_small_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(kMaxDynamicSmem - 2048)));
+    GB_CUDA(cudaFuncSetAttribute(moe_route_small_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(kMaxDynamicSmem - 2048)));
     GB_CUDA(cudaFuncSetAttribute(moe_route_scores_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  int(kMaxDynamicSmem - 1024)));
     GB_CUDA(cudaFuncSetAttribute(moe_route_scores_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -865,14 +942,24 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
                cudaStream_t stream)
 {
     const size_t smem = size_t(kRouteTokens) * opt.hidden * sizeof(float);
-    if (smem > kMaxDynamicSmem - 1024) return fail(GARNET_B200_NOT_SUPPORTED, "moe_route: hidden too large");
+    if (smem > kMaxDynamicSmem - 2048) return fail(GARNET_B200_NOT_SUPPORTED, "moe_route: hidden too large");
     // spread the experts over enough CTAs to fill the machine at small token counts
     const int token_ctas = (tokens + kRouteTokens - 1) / kRouteTokens;
     int per_cta = opt.experts;
     while (per_cta > 4 * kRouteWarps && token_ctas * ((opt.experts + per_cta - 1) / per_cta) < 2 * kSmCount) per_cta = (per_cta + 1) / 2;
     per_cta = std::max(per_cta, std::min(opt.experts, 4));
     const dim3 grid(token_ctas, (opt.experts + per_cta - 1) / per_cta);
-    if (opt.io_dtype == GARNET_B200_FP32) {
+    if (tokens <= kRouteTokens) {
+        const unsigned ctas = unsigned((opt.experts + 3) / 4);
+        if (opt.io_dtype == GARNET_B200_FP32)
+            moe_route_small_kernel<float><<<ctas, kRouteWarps * 32, smem, stream>>>(
+                static_cast<const float*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens, opt.hidden,
+                opt.experts);
+        else
+            moe_route_small_kernel<__nv_bfloat16><<<ctas, kRouteWarps * 32, smem, stream>>>(
+                static_cast<const __nv_bfloat16*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens,
+                opt.hidden, opt.experts);
+    } else if (opt.io_dtype == GARNET_B200_FP32) {
         moe_route_scores_kernel<float><<<grid, kRouteWarps * 32, smem, stream>>>(
             static_cast<const float*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens, opt.hidden,
             opt.experts, per_cta);
