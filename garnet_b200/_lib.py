@@ -38,6 +38,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_w4a16_shape.argtypes = [vp, c.POINTER(i), c.POINTER(i)]
     L.garnet_b200_w4a16_workspace.argtypes = [vp, i, c.POINTER(sz)]
     L.garnet_b200_w4a16_run.argtypes = [vp, vp, vp, i, vp, sz, u, vp]
+    L.garnet_b200_w4a16_run_group.argtypes = [vp, i, vp, vp, i, u, vp]
     L.garnet_b200_w4a16_run_host.argtypes = [vp, vp, vp, i, vp]
     L.garnet_b200_w4a16_dequant.argtypes = [vp, vp, vp]
     L.garnet_b200_w4a16_fault.argtypes = [vp]

@@ -467,6 +467,90 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
     }
 }
 
+// Decode-sized batches (at most 8 tokens, at most 256 experts): top-k, counts,
+// stable slot order and the task list in ONE single-CTA launch instead of three.
+// Same results as moe_topk_kernel + moe_count_kernel + moe_fill_kernel.
+__global__ void __launch_bounds__(256)
+moe_small_meta_kernel(const float* __restrict__ logits, int* __restrict__ selected, float* __restrict__ probs,
+                      int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ sorted,
+                      int4* __restrict__ tasks, int* __restrict__ ntasks, int tokens, int experts, int topk,
+                      int rows_per_task, MoeShard sh)
+{
+    __shared__ int s_sel[8 * 8];
+    __shared__ int s_count[256], s_offset[257], s_task[257];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // ---- top-k: one warp per token (8 warps)
+    if (warp < tokens) {
+        const float* l = logits + size_t(warp) * experts;
+        float top[8];
+        int chosen[8];
+        for (int j = 0; j < topk; ++j) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int e = lane; e < experts; e += 32) {
+                bool used = false;
+                for (int q = 0; q < j; ++q) used |= chosen[q] == e;
+                const float v = l[e];
+                if (!used && (arg == 0x7fffffff || v > best || (v == best && e < arg))) {
+                    best = v;
+                    arg = e;
+                }
+            }
+#pragma unroll
+            for (int off = 16; off; off >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
+                if (oa != 0x7fffffff && (arg == 0x7fffffff || ov > best || (ov == best && oa < arg))) {
+                    best = ov;
+                    arg = oa;
+                }
+            }
+            chosen[j] = arg;
+            top[j] = best;
+        }
+        if (lane == 0) {
+            float total = 0.f;
+            for (int j = 0; j < topk; ++j) total += expf(top[j] - top[0]);
+            for (int j = 0; j < topk; ++j) {
+                selected[warp * topk + j] = chosen[j];
+                s_sel[warp * topk + j] = chosen[j];
+                probs[warp * topk + j] = bf16_round_f(expf(top[j] - top[0]) / total);
+            }
+        }
+    }
+    __syncthreads();
+    // ---- counts per expert (thread e), then prefix sums by thread 0
+    const int slots = tokens * topk;
+    const int e = threadIdx.x;
+    int mine = 0;
+    if (e < experts && expert_is_local(e, sh))
+        for (int i = 0; i < slots; ++i) mine += s_sel[i] == e;
+    s_count[e] = e < experts ? mine : 0;
+    if (e < experts) counts[e] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, tk = 0;
+        for (int q = 0; q < experts; ++q) {
+            s_offset[q] = off;
+            s_task[q] = tk;
+            off += s_count[q];
+            tk += (s_count[q] + rows_per_task - 1) / rows_per_task;
+        }
+        s_offset[experts] = off;
+        *ntasks = tk;
+    }
+    __syncthreads();
+    if (e < experts) offsets[e] = s_offset[e];
+    if (e == 0) offsets[experts] = s_offset[experts];
+    if (e < experts && mine) {
+        int n = 0;
+        for (int i = 0; i < slots; ++i)
+            if (s_sel[i] == e) sorted[s_offset[e] + n++] = i;   // slot order kept: stable
+        for (int b = 0; b * rows_per_task < mine; ++b)
+            tasks[s_task[e] + b] = make_int4(e, s_offset[e] + b * rows_per_task, min(rows_per_task, mine - b * rows_per_task), 0);
+    }
+}
+
 // ------------------------------------------------- streaming expert kernel
 
 constexpr int kMoeWarps = 8;                       // consumer warps; one extra warp produces
@@ -939,7 +1023,7 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
 }
 
 int Moe::route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
-               cudaStream_t stream)
+               cudaStream_t stream, bool skip_topk)
 {
     const size_t smem = size_t(kRouteTokens) * opt.hidden * sizeof(float);
     if (smem > kMaxDynamicSmem - 2048) return fail(GARNET_B200_NOT_SUPPORTED, "moe_route: hidden too large");
@@ -968,8 +1052,9 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
             static_cast<const __nv_bfloat16*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens,
             opt.hidden, opt.experts, per_cta);
     }
-    moe_topk_kernel<<<(tokens * 32 + 255) / 256, 256, 0, stream>>>(logits, selected, probs, tokens, opt.experts,
-                                                                 opt.top_k);
+    if (!skip_topk)
+        moe_topk_kernel<<<(tokens * 32 + 255) / 256, 256, 0, stream>>>(logits, selected, probs, tokens, opt.experts,
+                                                                     opt.top_k);
     GB_CUDA(cudaGetLastError());
     return GARNET_B200_OK;
 }
@@ -1045,12 +1130,18 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     w.act = reinterpret_cast<__half*>(b + plan.act);
     w.vals = reinterpret_cast<float*>(b + plan.vals);
 
-    if (int rc = route(x, w.logits, w.selected, w.probs, w.xh, w.xshift, tokens, stream)) return rc;
     const int slots = tokens * opt.top_k;
     const MoeShard sh = shard();
-    moe_count_kernel<<<opt.experts, 256, 0, stream>>>(w.selected, slots, w.counts, sh);
-    moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(w.selected, slots, w.counts, w.offsets, w.sorted, w.tasks,
-                                                     w.ntasks, opt.experts, kMoeRows, sh);
+    const bool small = tokens <= 8 && opt.experts <= 256;
+    if (int rc = route(x, w.logits, w.selected, w.probs, w.xh, w.xshift, tokens, stream, small)) return rc;
+    if (small) {
+        moe_small_meta_kernel<<<1, 256, 0, stream>>>(w.logits, w.selected, w.probs, w.counts, w.offsets, w.sorted,
+                                                     w.tasks, w.ntasks, tokens, opt.experts, opt.top_k, kMoeRows, sh);
+    } else {
+        moe_count_kernel<<<opt.experts, 256, 0, stream>>>(w.selected, slots, w.counts, sh);
+        moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(w.selected, slots, w.counts, w.offsets, w.sorted, w.tasks,
+                                                         w.ntasks, opt.experts, kMoeRows, sh);
+    }
     GB_CUDA(cudaGetLastError());
     if (use_tc(slots) && moe_tc_eligible(opt, tokens)) {
         if (int rc = gather_rows(w, slots, opt.top_k, stream)) return rc;

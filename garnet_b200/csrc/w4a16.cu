@@ -165,16 +165,32 @@ __host__ __device__ constexpr int stream_stages(int warps) { return warps == 4 ?
 __host__ __device__ constexpr int seg_chunks(int warps) { return 2 * warps; }   // two chunks per consumer warp
 __host__ __device__ constexpr int seg_bytes(int warps) { return seg_chunks(warps) * kInt4ChunkBytes; }
 
+constexpr int kMaxGroup = 4;   // linears that share one input and one launch (q/k/v, gate/up)
+
 struct StreamParams {
-    const uint8_t* packed;
+    const uint8_t* packed[kMaxGroup];
+    __nv_bfloat16* y[kMaxGroup];
+    int n[kMaxGroup];         // logical weight rows of each matrix
+    int ldy[kMaxGroup];       // row stride of each y in elements
+    int strip_end[kMaxGroup]; // cumulative strip count: matrix g owns strips [strip_end[g-1], strip_end[g])
+    int group;                // matrices in this launch
     const __nv_bfloat16* x;
-    __nv_bfloat16* y;
-    int* fault;          // mapped host word; non-zero = a bounded wait gave up
-    int m, n, k;         // batch rows, logical weight rows, logical K
-    int ldy;             // row stride of y in elements
-    int strips, chunks;  // real strips (ceil(n/16)) and chunks per strip
-    int scale_dtype;     // GARNET_B200_FP16 / GARNET_B200_BF16
+    int* fault;               // mapped host word; non-zero = a bounded wait gave up
+    int m, k;                 // batch rows, logical K
+    int strips, chunks;       // total real strips over the group, chunks per strip
+    int scale_dtype;          // GARNET_B200_FP16 / GARNET_B200_BF16
 };
+
+// Strip of the concatenated list -> (matrix, strip inside it).
+__device__ __forceinline__ int stream_matrix_of(const StreamParams& p, int strip, int& local)
+{
+    int g = 0;
+#pragma unroll
+    for (int q = 0; q < kMaxGroup - 1; ++q)
+        if (q + 1 < p.group && strip >= p.strip_end[q]) g = q + 1;
+    local = strip - (g ? p.strip_end[g - 1] : 0);
+    return g;
+}
 
 // Two int4 codes -> bf16x2 {128 + (q+8), ...}: the biased form, without the
 // subtraction.  The bias is removed once per (batch row, chunk) from the
@@ -263,8 +279,10 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(c
                 const int nch = min(kSegChunks, p.chunks - seg * kSegChunks);
                 const uint32_t bytes = uint32_t(nch) * kInt4ChunkBytes;
                 mbar_expect_tx(&full[s], bytes);
+                int local;
+                const int g = stream_matrix_of(p, strip, local);
                 bulk_g2s(ring + size_t(s) * kSegBytes,
-                         p.packed + size_t(strip) * strip_bytes + size_t(seg) * kSegBytes, bytes, &full[s]);
+                         p.packed[g] + size_t(local) * strip_bytes + size_t(seg) * kSegBytes, bytes, &full[s]);
             }
         }
         return;
@@ -396,14 +414,16 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(c
                 acc[mb][q] = 0.f;
             }
         named_barrier_sync(1, kStreamWarps * 32);
+        int local;
+        const int grp = stream_matrix_of(p, strip, local);
         for (int idx = threadIdx.x; idx < MB * 128; idx += kStreamWarps * 32) {   // 128 outputs per 8 batch columns
             const int l = idx & 31, q = (idx >> 5) & 3, mb = idx >> 7;
             float v = 0.f;
 #pragma unroll
             for (int w = 0; w < kStreamWarps; ++w) v += slot[(w * MB * 4 + mb * 4 + q) * 32 + l];
             const int m = mb * 8 + 2 * (l & 3) + (q & 1);
-            const int n = strip * 16 + row_of_g(l >> 2) + 8 * (q >> 1);
-            if (m < p.m && n < p.n) p.y[size_t(m) * p.ldy + n] = __float2bfloat16_rn(v);
+            const int n = local * 16 + row_of_g(l >> 2) + 8 * (q >> 1);
+            if (m < p.m && n < p.n[grp]) p.y[grp][size_t(m) * p.ldy[grp] + n] = __float2bfloat16_rn(v);
         }
         ++strip;
     }
@@ -481,18 +501,39 @@ size_t W4A16::workspace_bytes(int) const { return 0; }
 int W4A16::launch_stream(const __nv_bfloat16* x, __nv_bfloat16* y, int m, int ldy, unsigned flags,
                          cudaStream_t stream)
 {
+    W4A16* one[1] = {this};
+    __nv_bfloat16* ys[1] = {y};
+    const int ldys[1] = {ldy};
+    return launch_stream_group(one, 1, x, ys, ldys, m, flags, stream);
+}
+
+// One launch for up to kMaxGroup linears that read the same x (same K, same scale
+// type): their strips are concatenated, so the small projections of a decoder layer
+// share one kernel's launch latency.
+int W4A16::launch_stream_group(W4A16* const* hs, int count, const __nv_bfloat16* x, __nv_bfloat16* const* ys,
+                               const int* ldys, int m, unsigned flags, cudaStream_t stream)
+{
+    const PackGeom& geo0 = hs[0]->geo;
     StreamParams p;
-    p.packed = packed;
+    int total = 0;
+    for (int g = 0; g < kMaxGroup; ++g) {
+        const int src = g < count ? g : 0;
+        p.packed[g] = hs[src]->packed;
+        p.y[g] = ys[src];
+        p.n[g] = hs[src]->geo.rows;
+        p.ldy[g] = ldys[src];
+        if (g < count) total += hs[g]->geo.strips;
+        p.strip_end[g] = total;
+    }
+    p.group = count;
     p.x = x;
-    p.y = y;
-    p.fault = fault_dev;
+    p.fault = hs[0]->fault_dev;
     p.m = m;
-    p.n = geo.rows;
-    p.k = geo.cols;
-    p.ldy = ldy;
-    p.strips = geo.strips;
-    p.chunks = geo.chunks;
-    p.scale_dtype = scale_dtype;
+    p.k = geo0.cols;
+    p.strips = total;
+    p.chunks = geo0.chunks;
+    p.scale_dtype = hs[0]->scale_dtype;
+    struct { int strips, cols, chunks; } geo = {total, geo0.cols, geo0.chunks};
 
     const int mb = m <= 8 ? 1 : 2;
     // Many strips per SM: narrow CTAs (4 consumer warps, up to 4 per SM).  Few strips:
@@ -735,6 +776,35 @@ int garnet_b200_w4a16_run(garnet_b200_w4a16_t hh, const void* d_x, void* d_y, in
     W4A16* h = reinterpret_cast<W4A16*>(hh);
     if (!h) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run: null handle");
     return h->run(d_x, d_y, m, d_workspace, workspace_bytes, flags, static_cast<cudaStream_t>(stream));
+}
+
+int garnet_b200_w4a16_run_group(const garnet_b200_w4a16_t* handles, int count, const void* d_x, void* const* d_ys,
+                                int m, unsigned flags, void* stream)
+{
+    if (!handles || !d_ys || !d_x || count <= 0 || m <= 0)
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_run_group: bad argument");
+    if (count > kMaxGroup) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run_group: at most %d linears per group", kMaxGroup);
+    if (reinterpret_cast<uintptr_t>(d_x) & 15) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run_group: x must be 16-byte aligned");
+    W4A16* hs[kMaxGroup];
+    __nv_bfloat16* ys[kMaxGroup];
+    int ldys[kMaxGroup];
+    int max_rows = 16;
+    for (int g = 0; g < count; ++g) {
+        hs[g] = reinterpret_cast<W4A16*>(handles[g]);
+        ys[g] = static_cast<__nv_bfloat16*>(d_ys[g]);
+        if (!hs[g] || !ys[g]) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run_group: null handle or output %d", g);
+        if (hs[g]->geo.cols != hs[0]->geo.cols || hs[g]->scale_dtype != hs[0]->scale_dtype)
+            return fail(GARNET_B200_INVALID_VALUE, "w4a16_run_group: linears of a group must share K and the scale type");
+        ldys[g] = hs[g]->geo.rows;
+        max_rows = std::min(max_rows, hs[g]->max_rows_per_launch);
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (m > max_rows) {   // larger batches: one launch per linear (tile kernel or row blocks)
+        for (int g = 0; g < count; ++g)
+            if (int rc = hs[g]->run(d_x, ys[g], m, nullptr, 0, flags, s)) return rc;
+        return GARNET_B200_OK;
+    }
+    return W4A16::launch_stream_group(hs, count, static_cast<const __nv_bfloat16*>(d_x), ys, ldys, m, flags, s);
 }
 
 int garnet_b200_w4a16_run_host(garnet_b200_w4a16_t hh, const void* h_x, void* h_y, int m, void* stream)

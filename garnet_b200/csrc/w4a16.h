@@ -33,6 +33,8 @@ struct W4A16 {
     size_t workspace_bytes(int m) const;
     int launch_stream(const __nv_bfloat16* x, __nv_bfloat16* y, int m, int ldy, unsigned flags,
                       cudaStream_t stream);
+    static int launch_stream_group(W4A16* const* hs, int count, const __nv_bfloat16* x, __nv_bfloat16* const* ys,
+                                   const int* ldys, int m, unsigned flags, cudaStream_t stream);
     int init_tc();
     int launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, unsigned flags, cudaStream_t stream);
     int run(const void* d_x, void* d_y, int m, void* ws, size_t ws_bytes, unsigned flags, cudaStream_t stream);

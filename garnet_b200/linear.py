@@ -54,6 +54,18 @@ def pack_host(nibbles, scales, n: int, k: int, group: int = 128) -> torch.Tensor
     return out
 
 
+def forward_group(linears, x: torch.Tensor, outs=None, pdl: bool = True):
+    """One launch for up to 4 linears that share the input x (q/k/v, gate/up)."""
+    x2 = x.reshape(-1, linears[0].k).contiguous()
+    m = x2.shape[0]
+    if outs is None:
+        outs = [torch.empty(m, lin.n, dtype=torch.bfloat16, device=x.device) for lin in linears]
+    hs = (ctypes.c_void_p * len(linears))(*[lin._h for lin in linears])
+    ys = (ctypes.c_void_p * len(linears))(*[o.data_ptr() for o in outs])
+    check(lib().garnet_b200_w4a16_run_group(hs, len(linears), x2.data_ptr(), ys, m, 1 if pdl else 0, _stream_ptr()))
+    return outs
+
+
 class W4A16Linear:
     """y[M, N] = x[M, K] W^T, W int4 with one scale per (row, `group` columns)."""
 

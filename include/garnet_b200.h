@@ -111,6 +111,14 @@ int garnet_b200_w4a16_workspace(garnet_b200_w4a16_t h, int m, size_t* bytes);
 int garnet_b200_w4a16_run(garnet_b200_w4a16_t h, const void* d_x, void* d_y, int m, void* d_workspace,
                           size_t workspace_bytes, unsigned flags, void* stream);
 
+/* Up to 4 linears that read the same x (same K), one launch: y_g[m, n_g] = x W_g^T.
+ * The device form of the reference's packed projections, which concatenate q/k/v and
+ * gate/up along N because they share their input (qwen3_text_qkv_packed,
+ * qwen3_mlp_gate_up_swiglu_packed: src/backends/tensorrt/trt_builder.cpp:7565-7577,
+ * :7727-7738), without requiring the weights to be stored concatenated. */
+int garnet_b200_w4a16_run_group(const garnet_b200_w4a16_t* handles, int count, const void* d_x, void* const* d_ys,
+                                int m, unsigned flags, void* stream);
+
 /* Same call for host-resident x and y (the plugin-facing form: host -> device
  * copy, kernel, device -> host copy on `stream`, then a stream synchronise).
  * Staging buffers belong to the handle and grow on first use. */

@@ -202,3 +202,18 @@ def test_run_rejects_bad_arguments():
         lin.forward(x, workspace=torch.empty(0, dtype=torch.uint8, device="cuda")) if lin.workspace_bytes(1) else (_ for _ in ()).throw(garnet_b200.GarnetB200Error(1, "no workspace needed"))
     with pytest.raises(garnet_b200.GarnetB200Error):
         garnet_b200.W4A16Linear().prepare(dev(case["nibbles"]), bf16_tensor(case["scales_bits"]), 128, 128, 64)
+
+
+@pytest.mark.parametrize("m", [1, 5, 16, 40])
+def test_grouped_launch_equals_separate_launches(m):
+    """q/k/v-style group: three linears of different N sharing one x in one launch."""
+    k = 2048
+    shapes = [2048, 1024, 1000]
+    cases = [synth.int4_linear(n, k, m, seed=100 + i) for i, n in enumerate(shapes)]
+    lins = [make_linear(c, n, k) for c, n in zip(cases, shapes)]
+    x = bf16_tensor(cases[0]["x_bits"]).reshape(m, k)
+    separate = [lin.forward(x) for lin in lins]
+    grouped = garnet_b200.forward_group(lins, x)
+    for a, b in zip(separate, grouped):
+        assert torch.equal(a, b)
+    assert all(lin.fault() == 0 for lin in lins)
