@@ -157,12 +157,20 @@ __global__ void int4_quantize_kernel(const T* __restrict__ src, long long rows, 
 
 // ------------------------------------------------------- streaming kernel
 
-// Two shapes of CTA: 4 consumer warps with 8-chunk segments (many strips per CTA:
-// more CTAs per SM, cheaper per-strip reduction) and 8 consumer warps with
-// 16-chunk segments (few strips: more warps share one strip, lower latency).
+// Two shapes of CTA, both with 16-chunk segments: 8 consumer warps with two chunks
+// each (many strips per CTA) and 16 consumer warps with one chunk each (few strips,
+// e.g. a 2048-row projection: more warps share one strip, lower latency).
 constexpr int kInt4ChunkBytes = 1024 + 32;
-__host__ __device__ constexpr int stream_stages(int warps) { return warps == 4 ? 4 : 3; }
-__host__ __device__ constexpr int seg_chunks(int warps) { return 2 * warps; }   // two chunks per consumer warp
+constexpr int kWideMaxStripsPerSm = 1;    // at most this many strips per SM: 16-warp CTAs
+constexpr int kStreamCtasPerSm = 3;       // 8-warp CTAs per SM (shared memory allows 3 at K = 2048)
+// A 16-warp CTA asks for more than half of the SM's shared memory so that it has the
+// SM to itself: with programmatic dependent launch the next launch's CTAs otherwise
+// move in beside it, two of them land on some SMs, and the launch takes as long as
+// those (down_proj at batch 1: 5.0 us with sharing, 3.8 us without).
+constexpr size_t kWideSmemFloor = 120000;
+__host__ __device__ constexpr int stream_stages(int) { return 3; }
+__host__ __device__ constexpr int chunks_per_warp(int warps) { return warps == 16 ? 1 : 2; }
+__host__ __device__ constexpr int seg_chunks(int warps) { return chunks_per_warp(warps) * warps; }
 __host__ __device__ constexpr int seg_bytes(int warps) { return seg_chunks(warps) * kInt4ChunkBytes; }
 
 constexpr int kMaxGroup = 4;   // linears that share one input and one launch (q/k/v, gate/up)
@@ -220,7 +228,7 @@ __host__ __device__ inline StreamSmem stream_smem_plan(int warps, int mb, int m,
     p.ring = 0;
     p.red = p.ring + kStreamStages * kSegBytes;    // [2][warps][mb*4][32] fp32
     p.bars = p.red + 2 * kStreamWarps * mb * 128 * 4;
-    p.sx = p.bars + 2 * kStreamStages * 8;         // [chunks][8*mb] fp32: -136 * sum of x over the chunk
+    p.sx = p.bars + 2 * kStreamStages * 8 + 8;         // [chunks][8*mb] fp32: -136 * sum of x over the chunk
     p.xs = (p.sx + chunks * 8 * mb * 4 + 127) & ~127;
     p.total = p.xs + p.x_rows * p.x_stride;
     return p;
@@ -228,8 +236,8 @@ __host__ __device__ inline StreamSmem stream_smem_plan(int warps, int mb, int m,
 
 // Persistent CTAs; each owns a contiguous range of 16-row strips.  A strip is one
 // linear byte range of the packed matrix; the producer warp streams it in
-// segments of 8 chunks (8.25 KiB) through a ring of bulk copies.  The 4 consumer
-// warps split each segment along K (two chunks each), expand int4 -> bf16 in
+// segments of 16 chunks (16.5 KiB) through a ring of bulk copies.  The consumer
+// warps split each segment along K (two chunks or one each), expand int4 -> bf16 in
 // registers and feed m16n8k16 MMAs whose N dimension is the (padded) batch; at
 // the end of a strip their partial sums meet in shared memory.  No global
 // scratch, no atomics: the summation order is fixed.
@@ -245,6 +253,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(c
     float* red = reinterpret_cast<float*>(smem + plan.red);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + plan.bars);
     uint64_t* empty = full + kStreamStages;
+    uint64_t* xbar = empty + kStreamStages;   // completion of the batch-row copies
     float* sx = reinterpret_cast<float*>(smem + plan.sx);
     uint8_t* xs = smem + plan.xs;
 
@@ -260,6 +269,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(c
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kStreamWarps);
         }
+        mbar_init(xbar, 1);
         fence_barrier_init();
     }
     __syncthreads();
@@ -290,22 +300,35 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(c
 
     // ---- consumers
     pdl_wait();   // x is produced by the previous kernel; y may still be read by it
+    bool ok = true;
     {
-        // Stage the batch rows (bf16) and, per (row, chunk), -136 * sum of the row's
-        // 128 values (the bias term of the int4 expansion).  16 consecutive threads
-        // cover one chunk of one row.
+        // Stage the batch rows (bf16) with one bulk copy per row - a single round trip
+        // to L2 however long the rows are - and then, per (row, chunk), -136 * the sum of
+        // the row's 128 values (the bias term of the int4 expansion).  16 consecutive
+        // threads cover one chunk of one row.
         const int rows = plan.x_rows - 1;
         const int vec_per_row = p.k / 8;
         const int total = rows * vec_per_row;
-        for (int i0 = 0; i0 < total; i0 += kStreamWarps * 32) {
-            const int i = i0 + threadIdx.x;
-            const int m = i / vec_per_row, v = i % vec_per_row;
-            uint4 val = make_uint4(0, 0, 0, 0);
-            if (i < total) {
-                val = *reinterpret_cast<const uint4*>(p.x + size_t(m) * p.k + v * 8);
-                *reinterpret_cast<uint4*>(xs + size_t(m) * plan.x_stride + v * 16) = val;
-            }
-            if (kBiased) {
+        if (threadIdx.x == 0) {
+            mbar_expect_tx(xbar, uint32_t(rows) * uint32_t(p.k) * 2u);
+            for (int m = 0; m < rows; ++m)
+                bulk_g2s(xs + size_t(m) * plan.x_stride, p.x + size_t(m) * p.k, uint32_t(p.k) * 2u, xbar);
+        }
+        for (int i = threadIdx.x; i < vec_per_row; i += kStreamWarps * 32)
+            *reinterpret_cast<uint4*>(xs + size_t(rows) * plan.x_stride + i * 16) = make_uint4(0, 0, 0, 0);
+        if (kBiased)
+            for (int i = threadIdx.x; i < p.chunks * 8 * MB; i += kStreamWarps * 32)
+                if ((i % (8 * MB)) >= rows) sx[i] = 0.f;
+        if (!mbar_wait(xbar, 0)) {
+            atomicExch(p.fault, 3);
+            ok = false;
+        }
+        if (kBiased) {
+            for (int i0 = 0; i0 < total; i0 += kStreamWarps * 32) {
+                const int i = i0 + threadIdx.x;
+                const int m = i / vec_per_row, v = i % vec_per_row;
+                uint4 val = make_uint4(0, 0, 0, 0);
+                if (i < total) val = *reinterpret_cast<const uint4*>(xs + size_t(m) * plan.x_stride + v * 16);
                 float part = 0.f;
                 const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
 #pragma unroll
@@ -316,11 +339,6 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(c
                 if ((lane & 15) == 0 && i < total) sx[(v >> 4) * (8 * MB) + m] = -136.f * part;
             }
         }
-        for (int i = threadIdx.x; i < vec_per_row; i += kStreamWarps * 32)
-            *reinterpret_cast<uint4*>(xs + size_t(rows) * plan.x_stride + i * 16) = make_uint4(0, 0, 0, 0);
-        if (kBiased)
-            for (int i = threadIdx.x; i < p.chunks * 8 * MB; i += kStreamWarps * 32)
-                if ((i % (8 * MB)) >= rows) sx[i] = 0.f;
     }
     named_barrier_sync(1, kStreamWarps * 32);
 
@@ -339,7 +357,6 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(c
         for (int i = 0; i < 4; ++i) acc[mb][i] = 0.f;
     const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
 
-    bool ok = true;
     int s = 0, phase = 0, strip = s0, seg = 0;
     for (int i = 0; i < items; ++i) {
         if (ok && !mbar_wait(&full[s], phase)) {
@@ -349,8 +366,8 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(c
         const int nch = min(kSegChunks, p.chunks - seg * kSegChunks);
         if (ok) {
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                const int c = 2 * warp + cc;
+            for (int cc = 0; cc < chunks_per_warp(kStreamWarps); ++cc) {
+                const int c = chunks_per_warp(kStreamWarps) * warp + cc;
                 if (c >= nch) break;
                 const uint8_t* st = ring + s * kSegBytes + c * kInt4ChunkBytes;
                 const uint32_t sc = *reinterpret_cast<const uint32_t*>(st + 1024 + g * 4);
@@ -376,6 +393,7 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(c
                         mma_bf16_16816(tmp[mb], a1, xb.z, xb.w, tmp[mb]);
                     }
                 }
+
                 const float s_lo = scale16_to_float(sc & 0xffffu, p.scale_dtype);
                 const float s_hi = scale16_to_float(sc >> 16, p.scale_dtype);
 #pragma unroll
@@ -403,7 +421,9 @@ __global__ void __launch_bounds__((kStreamWarps + 1) * 32) w4a16_stream_kernel(c
         if (++seg != nseg) continue;
         seg = 0;
 
-        // ---- end of a strip: the warps' partial sums meet in shared memory.
+        // ---- end of a strip: the warps' partial sums meet in shared memory (all
+        // threads take part: leaving the sum to the few threads that batch 1 needs made
+        // their warp the straggler and was measured slower).
         // acc[mb][0..1]: row R(g), batch columns 2t, 2t+1; [2..3]: row R(g)+8.
         float* slot = red + ((strip - s0) & 1) * (kStreamWarps * MB * 128);
 #pragma unroll
@@ -462,14 +482,14 @@ int W4A16::init_common()
     GB_CUDA(cudaHostAlloc(&fault_host, sizeof(int), cudaHostAllocMapped));
     *fault_host = 0;
     GB_CUDA(cudaHostGetDevicePointer(&fault_dev, fault_host, 0));
-    if (size_t(stream_smem_plan(4, 1, 8, geo.cols, geo.chunks).total) > kMaxDynamicSmem)
+    if (size_t(stream_smem_plan(8, 1, 8, geo.cols, geo.chunks).total) > kMaxDynamicSmem)
         return fail(GARNET_B200_NOT_SUPPORTED, "w4a16: k=%d is too large for the streaming kernel", geo.cols);
     max_rows_per_launch = size_t(stream_smem_plan(8, 2, 16, geo.cols, geo.chunks).total) <= kMaxDynamicSmem ? 16 : 8;
     // The attribute is per kernel and per device, not per handle: always ask for the maximum.
-    GB_CUDA((set_stream_attr<1, true, 4>()));
-    GB_CUDA((set_stream_attr<2, true, 4>()));
-    GB_CUDA((set_stream_attr<1, false, 4>()));
-    GB_CUDA((set_stream_attr<2, false, 4>()));
+    GB_CUDA((set_stream_attr<1, true, 16>()));
+    GB_CUDA((set_stream_attr<2, true, 16>()));
+    GB_CUDA((set_stream_attr<1, false, 16>()));
+    GB_CUDA((set_stream_attr<2, false, 16>()));
     GB_CUDA((set_stream_attr<1, true, 8>()));
     GB_CUDA((set_stream_attr<2, true, 8>()));
     GB_CUDA((set_stream_attr<1, false, 8>()));
@@ -536,19 +556,22 @@ int W4A16::launch_stream_group(W4A16* const* hs, int count, const __nv_bfloat16*
     struct { int strips, cols, chunks; } geo = {total, geo0.cols, geo0.chunks};
 
     const int mb = m <= 8 ? 1 : 2;
-    // Many strips per SM: narrow CTAs (4 consumer warps, up to 4 per SM).  Few strips:
-    // wide CTAs (8 consumer warps) so that more warps share each strip.
-    const bool narrow = geo.strips >= 8 * kSmCount * 4 &&
-                        size_t(stream_smem_plan(4, mb, m, geo.cols, geo.chunks).total) * 2 + 2048 <= kMaxDynamicSmem;
-    const int warps = narrow ? 4 : 8;
+    // Few strips per SM: 16 consumer warps per CTA so that more warps share each strip.
+    const bool wide = geo.strips <= kWideMaxStripsPerSm * kSmCount &&
+                      size_t(stream_smem_plan(16, mb, m, geo.cols, geo.chunks).total) <= kMaxDynamicSmem;
+    const int warps = wide ? 16 : 8;
     const size_t smem = size_t(stream_smem_plan(warps, mb, m, geo.cols, geo.chunks).total);
     if (smem > kMaxDynamicSmem)
         return fail(GARNET_B200_NOT_SUPPORTED, "w4a16: batch %d with k=%d does not fit shared memory", m, geo.cols);
-    const int ctas_per_sm = std::max(1, std::min(narrow ? 4 : 2, int(kMaxDynamicSmem / (smem + 1024))));
+    const int ctas_per_sm = std::max(1, std::min(kStreamCtasPerSm, int(kMaxDynamicSmem / (smem + 1024))));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(std::min(geo.strips, kSmCount * ctas_per_sm)));
     cfg.blockDim = dim3((warps + 1) * 32);
     cfg.dynamicSmemBytes = smem;
+    if (wide) {
+        cfg.dynamicSmemBytes = std::max(smem, kWideSmemFloor);
+        cfg.gridDim = dim3(unsigned(std::min(geo.strips, kSmCount)));
+    }
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -557,11 +580,11 @@ int W4A16::launch_stream_group(W4A16* const* hs, int count, const __nv_bfloat16*
     cfg.numAttrs = (flags & 1u) ? 1 : 0;
     const bool biased = use_biased_expansion();
 #define GB_LAUNCH_STREAM(MB_, B_, W_) GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_stream_kernel<MB_, B_, W_>, p))
-    if (warps == 4) {
-        if (mb == 1 && biased) GB_LAUNCH_STREAM(1, true, 4);
-        else if (mb == 1) GB_LAUNCH_STREAM(1, false, 4);
-        else if (biased) GB_LAUNCH_STREAM(2, true, 4);
-        else GB_LAUNCH_STREAM(2, false, 4);
+    if (warps == 16) {
+        if (mb == 1 && biased) GB_LAUNCH_STREAM(1, true, 16);
+        else if (mb == 1) GB_LAUNCH_STREAM(1, false, 16);
+        else if (biased) GB_LAUNCH_STREAM(2, true, 16);
+        else GB_LAUNCH_STREAM(2, false, 16);
     } else {
         if (mb == 1 && biased) GB_LAUNCH_STREAM(1, true, 8);
         else if (mb == 1) GB_LAUNCH_STREAM(1, false, 8);

@@ -214,6 +214,12 @@ def test_grouped_launch_equals_separate_launches(m):
     x = bf16_tensor(cases[0]["x_bits"]).reshape(m, k)
     separate = [lin.forward(x) for lin in lins]
     grouped = garnet_b200.forward_group(lins, x)
+    # The group runs as one wider launch, whose CTAs may split K over a different
+    # number of warps than the separate launches do: the fp32 partial sums associate
+    # differently, so the bf16 results may differ by one rounding step.
     for a, b in zip(separate, grouped):
-        assert torch.equal(a, b)
+        a32, b32 = a.float(), b.float()
+        step = torch.maximum(a32.abs(), b32.abs()) * 2.0 ** -7 + 1e-4 * a32.pow(2).mean().sqrt()
+        assert bool(((a32 - b32).abs() <= step).all())
+        assert float((a32 != b32).float().mean()) < 0.02
     assert all(lin.fault() == 0 for lin in lins)
