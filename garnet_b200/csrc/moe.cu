@@ -261,14 +261,15 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
                        float* __restrict__ logits, __half* __restrict__ xh, int* __restrict__ xshift, int tokens,
                        int hidden, int experts)
 {
-    extern __shared__ float xs[];   // [kRouteTokens][hidden]
+    extern __shared__ float xs[];   // [kRouteTokens][hidden]; rows >= tokens are not used
     __shared__ float part[kRouteWarps][4][kRouteTokens];
-    __shared__ float s_amax[kRouteTokens];
+    __shared__ float s_amax[kRouteWarps];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = threadIdx.x; i < kRouteTokens * hidden; i += blockDim.x) {
-        const int t = i / hidden, d = i % hidden;
-        xs[i] = t < tokens ? to_float(x[size_t(t) * hidden + d]) : 0.f;
-    }
+    pdl_launch_dependents();
+    pdl_wait();   // x comes from the kernel before this one
+    for (int t = 0; t < tokens; ++t)
+        for (int d = threadIdx.x; d < hidden; d += kRouteWarps * 32)
+            xs[t * hidden + d] = to_float(x[size_t(t) * hidden + d]);
     __syncthreads();
     const int e0 = blockIdx.x * 4;
     float acc[4][kRouteTokens];
@@ -282,44 +283,52 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
         for (int q = 0; q < 4; ++q) wv[q] = rw[size_t(min(e0 + q, experts - 1)) * hidden + d];
 #pragma unroll
         for (int t = 0; t < kRouteTokens; ++t) {
-            const float xv = xs[t * hidden + d];
+            if (t < tokens) {
+                const float xv = xs[t * hidden + d];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) acc[q][t] = fmaf(xv, wv[q], acc[q][t]);
+                for (int q = 0; q < 4; ++q) acc[q][t] = fmaf(xv, wv[q], acc[q][t]);
+            }
         }
     }
 #pragma unroll
     for (int q = 0; q < 4; ++q)
 #pragma unroll
         for (int t = 0; t < kRouteTokens; ++t) {
-            const float v = warp_sum(acc[q][t]);
-            if (lane == 0) part[warp][q][t] = v;
+            if (t < tokens) {
+                const float v = warp_sum(acc[q][t]);
+                if (lane == 0) part[warp][q][t] = v;
+            }
         }
     __syncthreads();
     if (threadIdx.x < 4 * kRouteTokens) {
         const int q = threadIdx.x / kRouteTokens, t = threadIdx.x % kRouteTokens;
-        float v = 0.f;
+        if (e0 + q < experts && t < tokens) {
+            float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < kRouteWarps; ++w) v += part[w][q][t];
-        if (e0 + q < experts && t < tokens) logits[size_t(t) * experts + e0 + q] = bf16_round_f(v + rb[e0 + q]);
+            for (int w = 0; w < kRouteWarps; ++w) v += part[w][q][t];
+            logits[size_t(t) * experts + e0 + q] = bf16_round_f(v + rb[e0 + q]);
+        }
     }
-    if (blockIdx.x != 0 || !xh) return;
-    for (int t = warp; t < tokens; t += kRouteWarps) {
+    if (!xh) return;
+    // fp16 copy of token t by CTA t (mod the grid)
+    for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
         float amax = 0.f;
-        for (int d = lane; d < hidden; d += 32) amax = fmaxf(amax, fabsf(bf16_round_f(xs[t * hidden + d])));
+        for (int d = threadIdx.x; d < hidden; d += kRouteWarps * 32)
+            amax = fmaxf(amax, fabsf(bf16_round_f(xs[t * hidden + d])));
 #pragma unroll
         for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        if (lane == 0) s_amax[t] = amax;
-    }
-    __syncthreads();
-    for (int t = warp; t < tokens; t += kRouteWarps) {
-        const float amax = s_amax[t];
+        __syncthreads();
+        if (lane == 0) s_amax[warp] = amax;
+        __syncthreads();
+#pragma unroll
+        for (int w = 0; w < kRouteWarps; ++w) amax = fmaxf(amax, s_amax[w]);
         int shift = 0;
         if (amax > 0.f && isfinite(amax)) shift = int((__float_as_uint(amax) >> 23) & 0xff) - 127 - 13;
         shift = max(-100, min(100, shift));
         const float scale = __uint_as_float(uint32_t(127 - shift) << 23);
-        for (int d = lane; d < hidden; d += 32)
+        for (int d = threadIdx.x; d < hidden; d += kRouteWarps * 32)
             xh[size_t(t) * hidden + d] = __float2half_rn(bf16_round_f(xs[t * hidden + d]) * scale);
-        if (lane == 0) xshift[t] = shift;
+        if (threadIdx.x == 0) xshift[t] = shift;
     }
 }
 
@@ -479,6 +488,8 @@ moe_small_meta_kernel(const float* __restrict__ logits, int* __restrict__ select
     __shared__ int s_sel[8 * 8];
     __shared__ int s_count[256], s_offset[257], s_task[257];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();   // the logits come from the kernel before this one
     // ---- top-k: one warp per token (8 warps)
     if (warp < tokens) {
         const float* l = logits + size_t(warp) * experts;
@@ -575,6 +586,7 @@ struct MoeStreamParams {
     int topk;
     int expert_base, expert_div;   // stored expert = (e - expert_base) / expert_div
     int bias_by_global;            // bias rows are indexed by the global expert id
+    int tasks_early;               // the task list was complete before this grid could start (see kernel)
     float limit;
     size_t matrix_bytes;
 };
@@ -589,7 +601,7 @@ __host__ __device__ inline MoeSmem moe_smem_plan(int k)
     p.ring = 0;
     p.red = p.ring + kMoeStages * kMoeSegBytes;
     p.bars = p.red + 2 * kMoeWarps * 128 * 4;
-    p.meta = p.bars + 2 * kMoeStages * 8;            // row slot ids and shifts
+    p.meta = p.bars + 2 * kMoeStages * 8 + 8;        // row slot ids and shifts
     p.xs = (p.meta + 2 * kMoeRows * 4 + 127) & ~127;
     p.total = p.xs + (kMoeRows + 1) * p.x_stride;
     return p;
@@ -616,19 +628,26 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
     int* row_shift = row_slot + kMoeRows;
     uint8_t* xs = smem + plan.xs;
 
+    uint64_t* xbar = empty + kMoeStages;   // completion of a task's row copies
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMoeStages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kMoeWarps);
         }
+        mbar_init(xbar, 1);
         fence_barrier_init();
     }
     __syncthreads();
+    // Programmatic dependent launch.  The gate/up launch lets its dependent (the down
+    // launch) start only after its own wait has returned, i.e. once the kernels that
+    // wrote the task list have completed: the down launch can therefore read the task
+    // list and stream its expert weights before its own wait, while gate/up still runs.
+    // Only its consumers, which read gate/up's activations, wait.
+    if (!p.tasks_early) pdl_wait();
     pdl_launch_dependents();
-    pdl_wait();   // the task list and activations come from earlier kernels of this call
 
-    const int ntasks = *p.ntasks;
+    const int ntasks = __ldcg(p.ntasks);
     const long long total = (long long)ntasks * p.strips;
     const long long i0 = total * blockIdx.x / gridDim.x, i1 = total * (blockIdx.x + 1) / gridDim.x;
     const int nseg = (p.chunks + kMoeSegChunks - 1) / kMoeSegChunks;
@@ -639,7 +658,7 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
             long long n = 0;
             for (long long it = i0; it < i1; ++it) {
                 const int task = int(it / p.strips), strip = int(it % p.strips);
-                const int e = (p.tasks[task].x - p.expert_base) / p.expert_div;
+                const int e = (__ldcg(&p.tasks[task]).x - p.expert_base) / p.expert_div;
                 const uint8_t* src = p.packed + size_t(e) * p.matrix_bytes + size_t(strip) * strip_bytes;
                 for (int seg = 0; seg < nseg; ++seg, ++n) {
                     const int s = int(n % kMoeStages);
@@ -657,42 +676,48 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
         return;
     }
 
+    // The row tile starts all-zero: row kMoeRows stays zero for the padded slots, and the
+    // row copies never write the padding behind column K.
+    for (int i = threadIdx.x; i < (kMoeRows + 1) * (plan.x_stride / 16); i += kMoeWarps * 32)
+        *reinterpret_cast<uint4*>(xs + size_t(i) * 16) = make_uint4(0, 0, 0, 0);
+    if (p.tasks_early) pdl_wait();   // the activations come from the launch before this one
+
     const int g = lane >> 2, t = lane & 3;
     const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int cur_task = -1, task_rows = 0, task_expert = 0;
     const uint8_t* xrow = xs;
     bool ok = true;
-    int s = 0, phase = 0, parity = 0;
+    int s = 0, phase = 0, parity = 0, xphase = 0;
 
     for (long long it = i0; it < i1; ++it) {
         const int task = int(it / p.strips), strip = int(it % p.strips);
         if (task != cur_task) {
-            // ---- new task: stage its rows.  All consumers have left the previous x tile.
+            // ---- new task: stage its rows, one bulk copy per row (one round trip to L2
+            // however long the rows are).  All consumers have left the previous x tile.
+            fence_proxy_async_smem();
             named_barrier_sync(1, kMoeWarps * 32);
-            const int4 tk = p.tasks[task];
+            const int4 tk = __ldcg(&p.tasks[task]);
             task_expert = tk.x;
             task_rows = tk.z;
+            if (threadIdx.x == 0) mbar_expect_tx(xbar, uint32_t(task_rows) * uint32_t(p.k) * 2u);
             if (threadIdx.x < kMoeRows) {
                 int slot = -1, shift = 0;
                 if (int(threadIdx.x) < task_rows) {
-                    slot = p.sorted[tk.y + threadIdx.x];
+                    slot = __ldcg(&p.sorted[tk.y + threadIdx.x]);
+                    const size_t src_row = kUp ? size_t(slot / p.topk) : size_t(slot);
+                    bulk_g2s(xs + size_t(threadIdx.x) * plan.x_stride, p.act_in + src_row * p.k, uint32_t(p.k) * 2u,
+                             xbar);
                     if (kUp) shift = p.xshift[slot / p.topk];
                 }
                 row_slot[threadIdx.x] = slot;
                 row_shift[threadIdx.x] = shift;
             }
-            const int vec_per_row = (p.k * 2 + 15) / 16;       // K*2 bytes is a multiple of 16 (K % 8 == 0)
-            for (int i = threadIdx.x; i < (kMoeRows + 1) * (plan.x_stride / 16); i += kMoeWarps * 32) {
-                const int m = i / (plan.x_stride / 16), v = i % (plan.x_stride / 16);
-                uint4 val = make_uint4(0, 0, 0, 0);
-                if (m < task_rows && v < vec_per_row) {
-                    const int slot = p.sorted[tk.y + m];
-                    const size_t src_row = kUp ? size_t(slot / p.topk) : size_t(slot);
-                    val = *reinterpret_cast<const uint4*>(p.act_in + src_row * p.k + v * 8);
-                }
-                *reinterpret_cast<uint4*>(xs + size_t(m) * plan.x_stride + v * 16) = val;
+            if (ok && !mbar_wait(xbar, xphase)) {
+                atomicExch(p.fault, 3);
+                ok = false;
             }
+            xphase ^= 1;
             named_barrier_sync(1, kMoeWarps * 32);
             cur_task = task;
             xrow = xs + size_t(g < task_rows ? g : kMoeRows) * plan.x_stride + t * 16;
@@ -814,6 +839,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ vals, const float* 
                                    const int* __restrict__ selected, YT* __restrict__ y, int tokens, int hidden,
                                    int topk, MoeShard sh, int round_output)
 {
+    pdl_launch_dependents();
+    pdl_wait();   // the per-slot values come from the kernel before this one
     const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= size_t(tokens) * hidden) return;
     const int token = int(idx / hidden), d = int(idx % hidden);
@@ -1022,6 +1049,26 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
     return GARNET_B200_OK;
 }
 
+// Launch with (or without) the programmatic-dependent-launch attribute.  Kernels
+// launched with it execute griddepcontrol.wait before they touch anything an
+// earlier kernel produced.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              bool pdl, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 int Moe::route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
                cudaStream_t stream, bool skip_topk)
 {
@@ -1035,14 +1082,15 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
     const dim3 grid(token_ctas, (opt.experts + per_cta - 1) / per_cta);
     if (tokens <= kRouteTokens) {
         const unsigned ctas = unsigned((opt.experts + 3) / 4);
+        const size_t small_smem = size_t(tokens) * opt.hidden * sizeof(float);
         if (opt.io_dtype == GARNET_B200_FP32)
-            moe_route_small_kernel<float><<<ctas, kRouteWarps * 32, smem, stream>>>(
-                static_cast<const float*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens, opt.hidden,
-                opt.experts);
+            GB_CUDA(launch_pdl(moe_route_small_kernel<float>, dim3(ctas), dim3(kRouteWarps * 32), small_smem, stream, true,
+                               static_cast<const float*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens,
+                               opt.hidden, opt.experts));
         else
-            moe_route_small_kernel<__nv_bfloat16><<<ctas, kRouteWarps * 32, smem, stream>>>(
-                static_cast<const __nv_bfloat16*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens,
-                opt.hidden, opt.experts);
+            GB_CUDA(launch_pdl(moe_route_small_kernel<__nv_bfloat16>, dim3(ctas), dim3(kRouteWarps * 32), small_smem, stream,
+                               true, static_cast<const __nv_bfloat16*>(x), router_w_ptr, router_b_ptr, logits, xh,
+                               xshift, tokens, opt.hidden, opt.experts));
     } else if (opt.io_dtype == GARNET_B200_FP32) {
         moe_route_scores_kernel<float><<<grid, kRouteWarps * 32, smem, stream>>>(
             static_cast<const float*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens, opt.hidden,
@@ -1087,6 +1135,8 @@ int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStrea
     p.limit = opt.limit;
     p.matrix_bytes = geo.matrix_bytes();
     p.bias_by_global = (!opt.expert_weights_sharded && sh.world > 1) ? 1 : 0;
+    // The down launch always follows the gate/up launch of the same call directly.
+    p.tasks_early = up ? 0 : 1;
 
     const size_t smem = size_t(moe_smem_plan(geo.cols).total);
     const int ctas_per_sm = std::max(1, std::min(2, int(kMaxDynamicSmem / (smem + 1024))));
@@ -1097,8 +1147,11 @@ int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStrea
     cfg.blockDim = dim3((kMoeWarps + 1) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cfg.attrs = nullptr;
-    cfg.numAttrs = 0;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     if (up && careful_scales) GB_CUDA(cudaLaunchKernelEx(&cfg, moe_stream_kernel<true, true>, p));
     else if (up) GB_CUDA(cudaLaunchKernelEx(&cfg, moe_stream_kernel<true, false>, p));
     else if (careful_scales) GB_CUDA(cudaLaunchKernelEx(&cfg, moe_stream_kernel<false, true>, p));
@@ -1135,8 +1188,9 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     const bool small = tokens <= 8 && opt.experts <= 256;
     if (int rc = route(x, w.logits, w.selected, w.probs, w.xh, w.xshift, tokens, stream, small)) return rc;
     if (small) {
-        moe_small_meta_kernel<<<1, 256, 0, stream>>>(w.logits, w.selected, w.probs, w.counts, w.offsets, w.sorted,
-                                                     w.tasks, w.ntasks, tokens, opt.experts, opt.top_k, kMoeRows, sh);
+        GB_CUDA(launch_pdl(moe_small_meta_kernel, dim3(1), dim3(256), 0, stream, true, w.logits, w.selected, w.probs,
+                           w.counts, w.offsets, w.sorted, w.tasks, w.ntasks, tokens, opt.experts, opt.top_k, kMoeRows,
+                           sh));
     } else {
         moe_count_kernel<<<opt.experts, 256, 0, stream>>>(w.selected, slots, w.counts, sh);
         moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(w.selected, slots, w.counts, w.offsets, w.sorted, w.tasks,
@@ -1153,13 +1207,15 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     }
     const size_t n = size_t(tokens) * opt.hidden;
     const int round_output = sh.world > 1 ? 0 : 1;
+    const bool streamed = !(use_tc(slots) && moe_tc_eligible(opt, tokens));
     if (opt.io_dtype == GARNET_B200_FP32)
-        moe_combine_kernel<float><<<unsigned((n + 255) / 256), 256, 0, stream>>>(
-            w.vals, w.probs, w.selected, static_cast<float*>(y), tokens, opt.hidden, opt.top_k, sh, round_output);
+        GB_CUDA(launch_pdl(moe_combine_kernel<float>, dim3(unsigned((n + 255) / 256)), dim3(256), 0, stream, streamed,
+                           (const float*)w.vals, (const float*)w.probs, (const int*)w.selected, static_cast<float*>(y),
+                           tokens, opt.hidden, opt.top_k, sh, round_output));
     else
-        moe_combine_kernel<__nv_bfloat16><<<unsigned((n + 255) / 256), 256, 0, stream>>>(
-            w.vals, w.probs, w.selected, static_cast<__nv_bfloat16*>(y), tokens, opt.hidden, opt.top_k, sh,
-            round_output);
+        GB_CUDA(launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(unsigned((n + 255) / 256)), dim3(256), 0, stream,
+                           streamed, (const float*)w.vals, (const float*)w.probs, (const int*)w.selected,
+                           static_cast<__nv_bfloat16*>(y), tokens, opt.hidden, opt.top_k, sh, round_output));
     GB_CUDA(cudaGetLastError());
     return GARNET_B200_OK;
 }
