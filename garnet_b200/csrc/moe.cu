@@ -899,6 +899,11 @@ MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens)
     const bool tc = moe_tc_eligible(o, tokens);
     w.xg = take(tc ? slots * o.hidden * 2 : 0);
     w.xshift_g = take(tc ? slots * 4 : 0);
+    const bool mx = moe_mx_enabled();
+    const MoeMxPlan mxp = moe_mx_plan(o, tokens, int(slots));
+    w.mx_tp = take(mx ? size_t(o.experts + 1) * 4 : 0);
+    w.mx_q = take(mx ? mxp.q_bytes : 0);
+    w.mx_sf = take(mx ? mxp.sf_bytes : 0);
     w.act = take(slots * o.intermediate * 2);
     w.vals = take(slots * o.hidden * 4);
     w.total = off;
@@ -953,6 +958,10 @@ int Moe::local_experts() const
 
 Moe::~Moe()
 {
+    for (int i = 0; i < 2; ++i) {
+        if (mx_w[i]) cudaFree(mx_w[i]);
+        if (mx_sfa[i]) cudaFree(mx_sfa[i]);
+    }
     if (packed_up) cudaFree(packed_up);
     if (packed_down) cudaFree(packed_down);
     if (flag_dev) cudaFree(flag_dev);
@@ -1018,6 +1027,9 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
                                                                                  flag_dev);
             mx_scale_range_kernel<<<256, 256, 0, stream>>>(scales + e0 * sc_per_expert, cnt, range_dev + 2 * pass,
                                                           range_dev + 2 * pass + 1);
+            if (moe_mx_enabled())
+                if (int rc = init_mx(pass, blocks + e0 * blk_per_expert, scales + e0 * sc_per_expert, s, run, stream))
+                    return rc;
             s += run;
         }
     }
@@ -1028,6 +1040,8 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
     GB_CUDA(cudaStreamSynchronize(stream));
     careful_scales = flag != 0;
     if (int rc = init_tc(range[0], range[1], range[2], range[3])) return rc;
+    if (moe_mx_enabled())
+        if (int rc = finish_mx()) return rc;
     // router and biases are borrowed from the caller (engine-owned constants)
     router_w_ptr = static_cast<const float*>(weights[0]);
     router_b_ptr = static_cast<const float*>(weights[1]);
@@ -1180,6 +1194,9 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     w.tasks = reinterpret_cast<int4*>(b + plan.tasks);
     w.xg = reinterpret_cast<__half*>(b + plan.xg);
     w.xshift_g = reinterpret_cast<int*>(b + plan.xshift_g);
+    w.mx_tp = reinterpret_cast<int*>(b + plan.mx_tp);
+    w.mx_q = b + plan.mx_q;
+    w.mx_sf = b + plan.mx_sf;
     w.act = reinterpret_cast<__half*>(b + plan.act);
     w.vals = reinterpret_cast<float*>(b + plan.vals);
 
@@ -1197,7 +1214,10 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
                                                          w.ntasks, opt.experts, kMoeRows, sh);
     }
     GB_CUDA(cudaGetLastError());
-    if (use_tc(slots) && moe_tc_eligible(opt, tokens)) {
+    if (use_mx()) {
+        if (int rc = launch_mx(true, w, x, 0, tokens, slots, opt.top_k, stream)) return rc;
+        if (int rc = launch_mx(false, w, x, 0, tokens, slots, opt.top_k, stream)) return rc;
+    } else if (use_tc(slots) && moe_tc_eligible(opt, tokens)) {
         if (int rc = gather_rows(w, slots, opt.top_k, stream)) return rc;
         if (int rc = launch_tc(true, w, slots, stream)) return rc;
         if (int rc = launch_tc(false, w, slots, stream)) return rc;
@@ -1207,7 +1227,7 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     }
     const size_t n = size_t(tokens) * opt.hidden;
     const int round_output = sh.world > 1 ? 0 : 1;
-    const bool streamed = !(use_tc(slots) && moe_tc_eligible(opt, tokens));
+    const bool streamed = use_mx() || !(use_tc(slots) && moe_tc_eligible(opt, tokens));
     if (opt.io_dtype == GARNET_B200_FP32)
         GB_CUDA(launch_pdl(moe_combine_kernel<float>, dim3(unsigned((n + 255) / 256)), dim3(256), 0, stream, streamed,
                            (const float*)w.vals, (const float*)w.probs, (const int*)w.selected, static_cast<float*>(y),
@@ -1236,6 +1256,9 @@ static MoeWorkspacePtrs bind_workspace(void* ws, const MoeWorkspace& plan)
     w.tasks = reinterpret_cast<int4*>(b + plan.tasks);
     w.xg = reinterpret_cast<__half*>(b + plan.xg);
     w.xshift_g = reinterpret_cast<int*>(b + plan.xshift_g);
+    w.mx_tp = reinterpret_cast<int*>(b + plan.mx_tp);
+    w.mx_q = b + plan.mx_q;
+    w.mx_sf = b + plan.mx_sf;
     w.act = reinterpret_cast<__half*>(b + plan.act);
     w.vals = reinterpret_cast<float*>(b + plan.vals);
     return w;
@@ -1279,6 +1302,10 @@ int Moe::run_rows(const void* x_rows, const int* row_expert, int rows, float* va
     GB_CUDA(cudaGetLastError());
     garnet_b200_moe_options one = opt;
     one.top_k = 1;
+    if (use_mx()) {
+        if (int rc = launch_mx(true, w, x_rows, 0, rows, rows, 1, stream)) return rc;
+        return launch_mx(false, w, x_rows, 0, rows, rows, 1, stream);
+    }
     if (use_tc(rows) && moe_tc_eligible(one, rows)) {
         if (int rc = gather_rows(w, rows, 1, stream)) return rc;
         if (int rc = launch_tc(true, w, rows, stream)) return rc;

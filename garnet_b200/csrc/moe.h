@@ -21,7 +21,8 @@ struct MoeShard {
 
 // Byte offsets of the regions of the caller's workspace.
 struct MoeWorkspace {
-    size_t logits, selected, probs, xshift, xh, counts, offsets, sorted, ntasks, tasks, xg, xshift_g, act, vals, total;
+    size_t logits, selected, probs, xshift, xh, counts, offsets, sorted, ntasks, tasks, xg, xshift_g, mx_tp, mx_q, mx_sf,
+        act, vals, total;
 };
 
 struct MoeWorkspacePtrs {
@@ -37,12 +38,25 @@ struct MoeWorkspacePtrs {
     int4* tasks;
     __half* xg;        // rows gathered into expert order (tensor-core path)
     int* xshift_g;
+    int* mx_tp;        // row tiles before each expert (block-scaled path)
+    uint8_t* mx_q;     // e4m3 row pieces at tile-aligned positions: [2][q_rows][kp]
+    uint8_t* mx_sf;    // their scale atoms: [tiles][kslabs][512]
     __half* act;
     float* vals;
 };
 
 MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens);
 MoeWorkspace moe_rows_workspace_plan(const garnet_b200_moe_options& o, int rows);
+// Sizes of the block-scaled path's per-call buffers.
+struct MoeMxPlan {
+    int nt;            // rows per tile (UMMA N)
+    int tiles_max;     // upper bound of the row tiles of one call
+    int q_rows;        // tiles_max * nt
+    int kp_max;        // max(hidden, intermediate) padded to 128
+    size_t q_bytes, sf_bytes;
+};
+MoeMxPlan moe_mx_plan(const garnet_b200_moe_options& o, int tokens, int slots);
+bool moe_mx_enabled();
 // True when the per-expert row counts are large enough for the tensor-core tile kernel.
 bool moe_tc_eligible(const garnet_b200_moe_options& o, int tokens);
 
@@ -59,6 +73,11 @@ struct Moe {
     bool careful_scales = false;       // some e8m0 byte is 0 or 255
     struct alignas(64) TensorMapStorage { unsigned char bytes[128]; };
     TensorMapStorage tc_w_map[2];      // TMA views of the packed gate_up / down matrices
+    uint8_t* mx_w[2] = {nullptr, nullptr};     // block-scaled path: row-major e2m1, K padded to 128
+    uint8_t* mx_sfa[2] = {nullptr, nullptr};   // and the weights' scale atoms
+    TensorMapStorage mx_w_map[2];
+    int mx_kp[2] = {0, 0}, mx_mtiles[2] = {0, 0}, mx_kslabs[2] = {0, 0};
+    bool mx_ok = false;
     bool tc_ok = false;                // scale bytes fit the fp16 window of the tensor-core path
     int ref_up = 0, ref_down = 0;      // exponent references of that path
     int* range_dev = nullptr;
@@ -79,6 +98,11 @@ struct Moe {
     int gather_rows(const MoeWorkspacePtrs& w, int slots, int topk, cudaStream_t stream);
     int launch_tc(bool up, const MoeWorkspacePtrs& w, int slots, cudaStream_t stream);
     bool use_tc(int slots) const;
+    int init_mx(int pass, const uint8_t* blocks, const uint8_t* scales, int first_stored, int count, cudaStream_t stream);
+    int finish_mx();
+    int launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_sorted, int tokens, int slots, int topk,
+                  cudaStream_t stream);
+    bool use_mx() const { return mx_ok && moe_mx_enabled(); }
     int combine(const float* vals, const float* probs, void* y, int tokens, cudaStream_t stream);
     int run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cudaStream_t stream);
 };
