@@ -433,15 +433,22 @@ __global__ void moe_count_kernel(const int* __restrict__ selected, int slots, in
 __global__ void __launch_bounds__(1024)
 moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restrict__ counts,
                 int* __restrict__ offsets, int* __restrict__ sorted, int4* __restrict__ tasks,
-                int* __restrict__ ntasks, int experts, int rows_per_task, MoeShard sh)
+                int* __restrict__ ntasks, int experts, int rows_per_task, MoeShard sh, int tile_rows,
+                int* __restrict__ tile_prefix)
 {
     const int e = blockIdx.x;
     __shared__ int s_offset, s_warp[32], s_running;
     if (threadIdx.x == 0) {
-        int off = 0, tk = 0;
+        int off = 0, tk = 0, tp = 0;
         for (int q = 0; q < e; ++q) {
             off += counts[q];
             tk += (counts[q] + rows_per_task - 1) / rows_per_task;
+            if (tile_rows) tp += (counts[q] + tile_rows - 1) / tile_rows;
+        }
+        if (tile_rows) {
+            // row tiles before each expert (block-scaled path)
+            tile_prefix[e] = tp;
+            if (e == experts - 1) tile_prefix[experts] = tp + (counts[e] + tile_rows - 1) / tile_rows;
         }
         s_offset = off;
         s_running = 0;
@@ -483,7 +490,7 @@ __global__ void __launch_bounds__(256)
 moe_small_meta_kernel(const float* __restrict__ logits, int* __restrict__ selected, float* __restrict__ probs,
                       int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ sorted,
                       int4* __restrict__ tasks, int* __restrict__ ntasks, int tokens, int experts, int topk,
-                      int rows_per_task, MoeShard sh)
+                      int rows_per_task, MoeShard sh, int tile_rows, int* __restrict__ tile_prefix)
 {
     __shared__ int s_sel[8 * 8];
     __shared__ int s_count[256], s_offset[257], s_task[257];
@@ -540,15 +547,18 @@ moe_small_meta_kernel(const float* __restrict__ logits, int* __restrict__ select
     if (e < experts) counts[e] = mine;
     __syncthreads();
     if (threadIdx.x == 0) {
-        int off = 0, tk = 0;
+        int off = 0, tk = 0, tp = 0;
         for (int q = 0; q < experts; ++q) {
             s_offset[q] = off;
             s_task[q] = tk;
+            if (tile_rows) tile_prefix[q] = tp;
             off += s_count[q];
             tk += (s_count[q] + rows_per_task - 1) / rows_per_task;
+            if (tile_rows) tp += (s_count[q] + tile_rows - 1) / tile_rows;
         }
         s_offset[experts] = off;
         *ntasks = tk;
+        if (tile_rows) tile_prefix[experts] = tp;
     }
     __syncthreads();
     if (e < experts) offsets[e] = s_offset[e];
@@ -904,6 +914,7 @@ MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens)
     w.mx_tp = take(mx ? size_t(o.experts + 1) * 4 : 0);
     w.mx_q = take(mx ? mxp.q_bytes : 0);
     w.mx_sf = take(mx ? mxp.sf_bytes : 0);
+    w.route_partial = take(mx ? moe_route_partial_bytes(tokens, o.experts) : 0);
     w.act = take(slots * o.intermediate * 2);
     w.vals = take(slots * o.hidden * 4);
     w.total = off;
@@ -958,6 +969,7 @@ int Moe::local_experts() const
 
 Moe::~Moe()
 {
+    if (router_w3) cudaFree(router_w3);
     for (int i = 0; i < 2; ++i) {
         if (mx_w[i]) cudaFree(mx_w[i]);
         if (mx_sfa[i]) cudaFree(mx_sfa[i]);
@@ -1040,8 +1052,12 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
     GB_CUDA(cudaStreamSynchronize(stream));
     careful_scales = flag != 0;
     if (int rc = init_tc(range[0], range[1], range[2], range[3])) return rc;
-    if (moe_mx_enabled())
+    router_w_ptr = static_cast<const float*>(weights[0]);
+    if (moe_mx_enabled()) {
         if (int rc = finish_mx()) return rc;
+        if (int rc = init_route_mma(stream)) return rc;
+        GB_CUDA(cudaStreamSynchronize(stream));
+    }
     // router and biases are borrowed from the caller (engine-owned constants)
     router_w_ptr = static_cast<const float*>(weights[0]);
     router_b_ptr = static_cast<const float*>(weights[1]);
@@ -1084,7 +1100,7 @@ static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 }
 
 int Moe::route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
-               cudaStream_t stream, bool skip_topk)
+               cudaStream_t stream, bool skip_topk, float* route_partial)
 {
     const size_t smem = size_t(kRouteTokens) * opt.hidden * sizeof(float);
     if (smem > kMaxDynamicSmem - 2048) return fail(GARNET_B200_NOT_SUPPORTED, "moe_route: hidden too large");
@@ -1094,7 +1110,10 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
     while (per_cta > 4 * kRouteWarps && token_ctas * ((opt.experts + per_cta - 1) / per_cta) < 2 * kSmCount) per_cta = (per_cta + 1) / 2;
     per_cta = std::max(per_cta, std::min(opt.experts, 4));
     const dim3 grid(token_ctas, (opt.experts + per_cta - 1) / per_cta);
-    if (tokens <= kRouteTokens) {
+    if (route_partial && route_mma_ok && use_mx(tokens * opt.top_k) && tokens > 4 * kRouteTokens) {
+        // many tokens, and no consumer of the fp16 row copies: tensor-core router
+        if (int rc = route_mma(x, logits, route_partial, tokens, stream)) return rc;
+    } else if (tokens <= kRouteTokens) {
         const unsigned ctas = unsigned((opt.experts + 3) / 4);
         const size_t small_smem = size_t(tokens) * opt.hidden * sizeof(float);
         if (opt.io_dtype == GARNET_B200_FP32)
@@ -1197,24 +1216,26 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     w.mx_tp = reinterpret_cast<int*>(b + plan.mx_tp);
     w.mx_q = b + plan.mx_q;
     w.mx_sf = b + plan.mx_sf;
+    w.route_partial = reinterpret_cast<float*>(b + plan.route_partial);
     w.act = reinterpret_cast<__half*>(b + plan.act);
     w.vals = reinterpret_cast<float*>(b + plan.vals);
 
     const int slots = tokens * opt.top_k;
     const MoeShard sh = shard();
     const bool small = tokens <= 8 && opt.experts <= 256;
-    if (int rc = route(x, w.logits, w.selected, w.probs, w.xh, w.xshift, tokens, stream, small)) return rc;
+    const int tile_rows = use_mx(slots) ? moe_mx_plan(opt, tokens, slots).nt : 0;
+    if (int rc = route(x, w.logits, w.selected, w.probs, w.xh, w.xshift, tokens, stream, small, w.route_partial)) return rc;
     if (small) {
         GB_CUDA(launch_pdl(moe_small_meta_kernel, dim3(1), dim3(256), 0, stream, true, w.logits, w.selected, w.probs,
                            w.counts, w.offsets, w.sorted, w.tasks, w.ntasks, tokens, opt.experts, opt.top_k, kMoeRows,
-                           sh));
+                           sh, tile_rows, w.mx_tp));
     } else {
         moe_count_kernel<<<opt.experts, 256, 0, stream>>>(w.selected, slots, w.counts, sh);
         moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(w.selected, slots, w.counts, w.offsets, w.sorted, w.tasks,
-                                                         w.ntasks, opt.experts, kMoeRows, sh);
+                                                         w.ntasks, opt.experts, kMoeRows, sh, tile_rows, w.mx_tp);
     }
     GB_CUDA(cudaGetLastError());
-    if (use_mx()) {
+    if (use_mx(slots)) {
         if (int rc = launch_mx(true, w, x, 0, tokens, slots, opt.top_k, stream)) return rc;
         if (int rc = launch_mx(false, w, x, 0, tokens, slots, opt.top_k, stream)) return rc;
     } else if (use_tc(slots) && moe_tc_eligible(opt, tokens)) {
@@ -1227,7 +1248,7 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     }
     const size_t n = size_t(tokens) * opt.hidden;
     const int round_output = sh.world > 1 ? 0 : 1;
-    const bool streamed = use_mx() || !(use_tc(slots) && moe_tc_eligible(opt, tokens));
+    const bool streamed = use_mx(slots) || !(use_tc(slots) && moe_tc_eligible(opt, tokens));
     if (opt.io_dtype == GARNET_B200_FP32)
         GB_CUDA(launch_pdl(moe_combine_kernel<float>, dim3(unsigned((n + 255) / 256)), dim3(256), 0, stream, streamed,
                            (const float*)w.vals, (const float*)w.probs, (const int*)w.selected, static_cast<float*>(y),
@@ -1259,6 +1280,7 @@ static MoeWorkspacePtrs bind_workspace(void* ws, const MoeWorkspace& plan)
     w.mx_tp = reinterpret_cast<int*>(b + plan.mx_tp);
     w.mx_q = b + plan.mx_q;
     w.mx_sf = b + plan.mx_sf;
+    w.route_partial = reinterpret_cast<float*>(b + plan.route_partial);
     w.act = reinterpret_cast<__half*>(b + plan.act);
     w.vals = reinterpret_cast<float*>(b + plan.vals);
     return w;
@@ -1298,11 +1320,12 @@ int Moe::run_rows(const void* x_rows, const int* row_expert, int rows, float* va
     const MoeShard sh = shard();
     moe_count_kernel<<<opt.experts, 256, 0, stream>>>(row_expert, rows, w.counts, sh);
     moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(row_expert, rows, w.counts, w.offsets, w.sorted, w.tasks, w.ntasks,
-                                                     opt.experts, kMoeRows, sh);
+                                                     opt.experts, kMoeRows, sh,
+                                                     use_mx(rows) ? moe_mx_plan(opt, rows, rows).nt : 0, w.mx_tp);
     GB_CUDA(cudaGetLastError());
     garnet_b200_moe_options one = opt;
     one.top_k = 1;
-    if (use_mx()) {
+    if (use_mx(rows)) {
         if (int rc = launch_mx(true, w, x_rows, 0, rows, rows, 1, stream)) return rc;
         return launch_mx(false, w, x_rows, 0, rows, rows, 1, stream);
     }
@@ -1335,10 +1358,10 @@ int Moe::combine(const float* vals, const float* probs, void* y, int tokens, cud
 // ------------------------------------------- built-in scratch (no allocation)
 
 // Scratch for garnet_b200_moe_run_static().  It lives in the library image: every
-// GPU that loads the library holds these 2 MiB until the process exits.  The
+// GPU that loads the library holds these 8 MiB until the process exits.  The
 // name below is only a host-side stand-in for the array; the device address is
 // looked up once per device with cudaGetSymbolAddress and handed to the kernels.
-constexpr size_t kMoeStaticScratchBytes = size_t(2) << 20;
+constexpr size_t kMoeStaticScratchBytes = size_t(8) << 20;
 static __device__ __align__(256) unsigned char g_moe_static_scratch[kMoeStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;

@@ -1,6 +1,7 @@
 // Host-side state of one gpt_oss_moe_mxfp4 operator (the object behind
 // garnet_b200_moe_t).
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -21,7 +22,7 @@ struct MoeShard {
 
 // Byte offsets of the regions of the caller's workspace.
 struct MoeWorkspace {
-    size_t logits, selected, probs, xshift, xh, counts, offsets, sorted, ntasks, tasks, xg, xshift_g, mx_tp, mx_q, mx_sf,
+    size_t logits, selected, probs, xshift, xh, counts, offsets, sorted, ntasks, tasks, xg, xshift_g, mx_tp, mx_q, mx_sf, route_partial,
         act, vals, total;
 };
 
@@ -41,6 +42,7 @@ struct MoeWorkspacePtrs {
     int* mx_tp;        // row tiles before each expert (block-scaled path)
     uint8_t* mx_q;     // e4m3 row pieces at tile-aligned positions: [2][q_rows][kp]
     uint8_t* mx_sf;    // their scale atoms: [tiles][kslabs][512]
+    float* route_partial;   // [3][tokens][experts] partial router sums (tensor-core router)
     __half* act;
     float* vals;
 };
@@ -57,6 +59,8 @@ struct MoeMxPlan {
 };
 MoeMxPlan moe_mx_plan(const garnet_b200_moe_options& o, int tokens, int slots);
 bool moe_mx_enabled();
+bool moe_mx_forced();
+size_t moe_route_partial_bytes(int tokens, int experts);
 // True when the per-expert row counts are large enough for the tensor-core tile kernel.
 bool moe_tc_eligible(const garnet_b200_moe_options& o, int tokens);
 
@@ -78,6 +82,8 @@ struct Moe {
     TensorMapStorage mx_w_map[2];
     int mx_kp[2] = {0, 0}, mx_mtiles[2] = {0, 0}, mx_kslabs[2] = {0, 0};
     bool mx_ok = false;
+    __nv_bfloat16* router_w3 = nullptr;        // router weight split into three bf16 terms (tensor-core router)
+    bool route_mma_ok = false;
     bool tc_ok = false;                // scale bytes fit the fp16 window of the tensor-core path
     int ref_up = 0, ref_down = 0;      // exponent references of that path
     int* range_dev = nullptr;
@@ -90,7 +96,7 @@ struct Moe {
     int local_experts() const;
     int prepare(const void* const* weights, cudaStream_t stream);
     int route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
-              cudaStream_t stream, bool skip_topk = false);
+              cudaStream_t stream, bool skip_topk = false, float* route_partial = nullptr);
     int launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream, int topk = -1);
     int run_rows(const void* x_rows, const int* row_expert, int rows, float* vals, void* ws, size_t ws_bytes,
                  cudaStream_t stream);
@@ -102,7 +108,12 @@ struct Moe {
     int finish_mx();
     int launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_sorted, int tokens, int slots, int topk,
                   cudaStream_t stream);
-    bool use_mx() const { return mx_ok && moe_mx_enabled(); }
+    // The block-scaled path pays off once experts get several rows each (measured
+    // crossover on the gpt-oss-120b layer: about 8 rows per expert); below that the
+    // streaming kernel moves the weights faster.
+    bool use_mx(int slots) const { return mx_ok && moe_mx_enabled() && (moe_mx_forced() || slots > 8 * local_experts()); }
+    int init_route_mma(cudaStream_t stream);
+    int route_mma(const void* x, float* logits, float* partial, int tokens, cudaStream_t stream);
     int combine(const float* vals, const float* probs, void* y, int tokens, cudaStream_t stream);
     int run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cudaStream_t stream);
 };

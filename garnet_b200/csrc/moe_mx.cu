@@ -6,11 +6,14 @@
 // (plugins/gpt_oss/cuda/gpt_oss_marlin.cu:586-648).
 //
 // Operands.
-//   A (UMMA M side, 128 rows per tile): expert weights, row-major e2m1 with K padded
-//     to a multiple of 128, fetched by TMA with the 16U4_ALIGN16B element type (16
-//     codes land in the low 8 bytes of every 16-byte slot, the layout the MMA reads
-//     4-bit operands in).  Scales: 512-byte atoms of 128 rows x 4 blocks, copied to
-//     tensor memory with tcgen05.cp (32x128b, replicated to the four lane quarters).
+//   A (UMMA M side, 128 rows per tile): expert weights as contiguous 8 KiB tiles of
+//     128 rows x 128 columns of e2m1 codes (K padded to a multiple of 128).  The MMA reads 4-bit operands from 16-byte slots whose low
+//     8 bytes hold 16 codes.  TMA can write that format itself (element type
+//     16U4_ALIGN16B), but was measured at 8 packed bytes per cycle per SM (2.3 TB/s
+//     over the GPU), so the packed bytes are fetched as plain bytes and four warps
+//     spread them into the slots - a copy, no arithmetic.  Scales: 512-byte atoms of
+//     128 rows x 4 blocks, copied to tensor memory with tcgen05.cp (32x128b,
+//     replicated to the four lane quarters).
 //   B (UMMA N side, 16..128 routed rows per tile): activations.  The MMA takes
 //     8-bit floats there, so every bf16 activation is split into two e4m3 numbers
 //     that share the e8m0 scale of their 32-block: hi = e4m3(v), lo = e4m3(v - hi),
@@ -34,26 +37,43 @@ namespace gb200 {
 constexpr int kMxM = 128;            // weight rows per tile
 constexpr int kMxSlab = 128;         // K elements per pipeline stage (4 MMAs of K = 32 per piece)
 constexpr int kMxAtom = 512;         // bytes of one scale atom: 128 rows x 4 blocks
-constexpr int kMxThreads = 6 * 32;   // producer, MMA issuer, 4 epilogue warps
+constexpr int kMxEpiWarps = 8;       // two per 32-lane quarter of tensor memory
+constexpr int kMxUnpackWarps = 4;
+constexpr int kMxFirstUnpack = 3, kMxFirstEpi = kMxFirstUnpack + kMxUnpackWarps;
+constexpr int kMxThreads = (kMxFirstEpi + kMxEpiWarps) * 32;   // 2 producers, MMA issuer, unpack and epilogue warps
+constexpr int kMxPkStages = 4;       // ring of packed weight tiles (8 KiB each)
+constexpr int kMxPkBytes = kMxM * kMxSlab / 2;
 constexpr int kMxMaxExperts = 1024;
 constexpr uint32_t kMxATileBytes = kMxM * 128;       // shared-memory footprint of a weight tile
-constexpr uint32_t kMxATxBytes = kMxM * kMxSlab / 2;   // bytes the weight tile's TMA transfers
 
-__host__ __device__ constexpr int mx_stage_bytes(int nt) { return int(kMxATileBytes) + 2 * nt * 128 + 2 * kMxAtom; }
+// Two ways to feed the two e4m3 pieces of a tile's rows:
+//   joined (tiles of up to 120 rows): one N = 2 nt operand, accumulator columns [0, nt)
+//     and [nt, 2 nt) added in the epilogue - one MMA per K block;
+//   split (tiles of 160 rows): two MMAs per K block, N = the live rows in sixteens, into
+//     the same accumulator.
+__host__ __device__ constexpr bool mx_joined(int nt) { return nt <= 120; }
+__host__ __device__ constexpr int mx_sfb_atoms(int nt) { return ((mx_joined(nt) ? 2 : 1) * nt + 127) / 128; }
+// An MMA of this kind was measured to occupy the tensor pipe for about 100 cycles
+// however small its N, and in proportion to N only above N of about 190: the
+// instruction count, not the math, sets the pace of small tiles, hence the joined form.
+__host__ __device__ constexpr int mx_stage_bytes(int nt)
+{
+    return int(kMxATileBytes) + 2 * nt * 128 + 1024 * ((kMxAtom * (1 + mx_sfb_atoms(nt)) + 1023) / 1024);
+}
 __host__ __device__ constexpr int mx_stages(int nt)
 {
-    const int s = (200 * 1024) / mx_stage_bytes(nt);
+    const int s = (188 * 1024) / mx_stage_bytes(nt);
     return s > 8 ? 8 : s;
 }
 __host__ __device__ constexpr int mx_tmem_cols(int nt)
 {
-    const int need = 2 * nt + 8;
+    const int need = (mx_joined(nt) ? 4 : 2) * nt + 4 + 4 * mx_sfb_atoms(nt);
     return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
 }
 // dynamic shared memory: 1 KiB alignment slack, the stages, tile prefix, barriers
 __host__ __device__ constexpr int mx_smem_total(int nt)
 {
-    return 1024 + mx_stages(nt) * mx_stage_bytes(nt) + (kMxMaxExperts + 1) * 4 + 256;
+    return 1024 + mx_stages(nt) * mx_stage_bytes(nt) + kMxPkStages * kMxPkBytes + (kMxMaxExperts + 1) * 4 + 512;
 }
 
 struct MxParams {
@@ -61,8 +81,9 @@ struct MxParams {
     const int* sorted;         // [slots] slot ids in expert order
     const int* tile_prefix;    // [experts + 1] row tiles before each expert
     const float* bias;         // [experts(local or global), rows] original row order
+    const uint8_t* w;          // [stored experts][mtiles][kslabs][8 KiB] weight tiles
     const uint8_t* sfa;        // [stored experts][mtiles][kslabs][512] weight scale atoms
-    const uint8_t* sfb;        // [row tiles][kslabs][512] activation scale atoms
+    const uint8_t* sfb;        // [row tiles][kslabs][atoms per tile][512] activation scale atoms
     __half* act_out;           // up: [sorted position, intermediate]
     float* vals_out;           // down: [slot id, hidden]
     int* fault;
@@ -106,8 +127,7 @@ __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t 
 // scales; `sf` selects which of the four blocks of the scale atoms this MMA uses.
 __device__ __forceinline__ uint32_t mx_idesc(int m, int n, uint32_t sf)
 {
-    return (sf << 4) | (5u << 7) | (0u << 10) | (uint32_t(n >> 3) << 17) | (1u << 23) | (uint32_t(m >> 4) << 24) |
-           (sf << 29);
+    return (sf << 4) | (5u << 7) | (0u << 10) | (uint32_t(n >> 3) << 17) | (1u << 23) | (uint32_t(m >> 4) << 24) | (sf << 29);
 }
 
 __device__ __forceinline__ void umma_mx(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa,
@@ -132,6 +152,32 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
         : "memory");
 }
 
+// 16 accumulator columns of this thread's lane; in the joined form the two pieces'
+// columns, kN apart, are added.
+template <int kN>
+__device__ __forceinline__ void mx_load_acc(uint32_t taddr, uint32_t (&r)[16])
+{
+    tmem_ld_32x16(taddr, r);
+    if (mx_joined(kN)) {
+        uint32_t r2[16];
+        tmem_ld_32x16(taddr + kN, r2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+    } else {
+        tmem_ld_wait();
+    }
+}
+
+#if defined(GB_TUNE_PROF)
+__device__ unsigned long long g_mx_prof[16];
+#define MXP_T0() const long long _t0 = clock64()
+#define MXP_ADD(i) atomicAdd(&g_mx_prof[i], (unsigned long long)(clock64() - _t0))
+#else
+#define MXP_T0()
+#define MXP_ADD(i)
+#endif
+
 struct MxItem {
     int expert, tile, mtile, rows;   // tile: global row-tile index; rows: live rows of it
     int row0;                        // sorted position of the tile's first row
@@ -153,20 +199,25 @@ __device__ __forceinline__ MxItem mx_decode(const MxParams& p, const int* tile_p
 
 template <bool kUp, int kN>
 __global__ void __launch_bounds__(kMxThreads, 1)
-moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap q_map,
-              const int q_rows)
+moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap q_map, const int q_rows)
 {
     constexpr int kStages = mx_stages(kN);
     constexpr int kStageBytes = mx_stage_bytes(kN);
     constexpr uint32_t kTmemCols = mx_tmem_cols(kN);
-    constexpr uint32_t kStageTx = kMxATxBytes + 2 * kN * 128 + 2 * kMxAtom;
+    constexpr int kSfbAtoms = mx_sfb_atoms(kN);
+    constexpr bool kJoined = mx_joined(kN);
+    constexpr uint32_t kAccCols = kJoined ? 2 * kN : kN;   // accumulator columns per buffer
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;
-    int* tile_prefix = reinterpret_cast<int*>(smem + kStages * kStageBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + (kMxMaxExperts + 1) * 4 + 4);
-    uint64_t* full = bars;
-    uint64_t* empty = full + kStages;
+    uint8_t* pk_ring = smem + kStages * kStageBytes;
+    int* tile_prefix = reinterpret_cast<int*>(pk_ring + kMxPkStages * kMxPkBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(tile_prefix) + (kMxMaxExperts + 1) * 4 + 4);
+    uint64_t* pk_full = bars;
+    uint64_t* pk_empty = pk_full + kMxPkStages;
+    uint64_t* full = pk_empty + kMxPkStages;      // activation tiles and scale atoms have landed
+    uint64_t* a_ready = full + kStages;           // the weight tile has been spread into its slots
+    uint64_t* empty = a_ready + kStages;
     uint64_t* acc_full = empty + kStages;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
@@ -174,18 +225,23 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap w_map, const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
+        for (int s = 0; s < kMxPkStages; ++s) {
+            mbar_init(&pk_full[s], 1);
+            mbar_init(&pk_empty[s], kMxUnpackWarps);
+        }
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 1);
+            mbar_init(&a_ready[s], kMxUnpackWarps);
             mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&acc_full[s], 1);
-            mbar_init(&acc_empty[s], 4);
+            mbar_init(&acc_empty[s], kMxEpiWarps);
         }
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 1) {
+    if (warp == 2) {
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
@@ -196,11 +252,35 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap w_map, const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_sfa = tmem_base + 2 * kN, tmem_sfb = tmem_sfa + 4;
+    const uint32_t tmem_sfa = tmem_base + 2 * kAccCols, tmem_sfb = tmem_sfa + 4;
     const int items = tile_prefix[p.experts] * p.mtiles;
 
     if (warp == 0) {
-        // ------------------------------------------------------------ producer
+        // ------------------------------------- producer of packed weight tiles
+        if (lane == 0) {
+            uint32_t n = 0;
+            int cur = 0;
+            for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
+                const MxItem it = mx_decode<kN>(p, tile_prefix, item, cur);
+                const int se = (it.expert - p.expert_base) / p.expert_div;
+                const uint8_t* wt = p.w + (size_t(se) * p.mtiles + it.mtile) * p.kslabs * kMxPkBytes;
+                for (int ks = 0; ks < p.kslabs; ++ks, ++n) {
+                    const uint32_t s = n % kMxPkStages;
+                    MXP_T0();
+                    const bool okw = !(n >= kMxPkStages && !mbar_wait_bounded(&pk_empty[s], ((n / kMxPkStages) - 1) & 1));
+                    MXP_ADD(5);
+                    if (!okw) {
+                        atomicExch(p.fault, 30);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    mbar_expect_tx(&pk_full[s], kMxPkBytes);
+                    bulk_g2s(pk_ring + s * kMxPkBytes, wt + size_t(ks) * kMxPkBytes, kMxPkBytes, &pk_full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------- producer of activation tiles and scale atoms
         if (lane == 0) {
             uint32_t n = 0;
             int cur = 0;
@@ -208,112 +288,188 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap w_map, const
                 const MxItem it = mx_decode<kN>(p, tile_prefix, item, cur);
                 const int se = (it.expert - p.expert_base) / p.expert_div;
                 const uint8_t* sfa = p.sfa + (size_t(se) * p.mtiles + it.mtile) * p.kslabs * kMxAtom;
-                const uint8_t* sfb = p.sfb + size_t(it.tile) * p.kslabs * kMxAtom;
+                const uint8_t* sfb = p.sfb + size_t(it.tile) * p.kslabs * (kSfbAtoms * kMxAtom);
+                constexpr uint32_t tx = uint32_t(2 * kN * 128) + uint32_t((1 + kSfbAtoms) * kMxAtom);
                 for (int ks = 0; ks < p.kslabs; ++ks, ++n) {
                     const uint32_t s = n % kStages;
-                    if (n >= kStages && !mbar_wait_bounded(&empty[s], ((n / kStages) - 1) & 1)) {
+                    MXP_T0();
+                    const bool okw = !(n >= kStages && !mbar_wait_bounded(&empty[s], ((n / kStages) - 1) & 1));
+                    MXP_ADD(4);
+                    if (!okw) {
                         atomicExch(p.fault, 31);
                         *abort_flag = 1;
                         break;
                     }
                     uint8_t* st = ring + s * kStageBytes;
-                    mbar_expect_tx(&full[s], kStageTx);
-                    tma_load_3d(st, &w_map, ks * kMxSlab, it.mtile * kMxM, se, &full[s]);
+                    uint8_t* sf_s = st + kMxATileBytes + 2 * kN * 128;
+                    mbar_expect_tx(&full[s], tx);
                     tma_load_2d(st + kMxATileBytes, &q_map, ks * kMxSlab, it.tile * kN, &full[s]);
                     tma_load_2d(st + kMxATileBytes + kN * 128, &q_map, ks * kMxSlab, q_rows + it.tile * kN, &full[s]);
-                    bulk_g2s(st + kMxATileBytes + 2 * kN * 128, sfa + size_t(ks) * kMxAtom, kMxAtom, &full[s]);
-                    bulk_g2s(st + kMxATileBytes + 2 * kN * 128 + kMxAtom, sfb + size_t(ks) * kMxAtom, kMxAtom, &full[s]);
+                    bulk_g2s(sf_s, sfa + size_t(ks) * kMxAtom, kMxAtom, &full[s]);
+                    bulk_g2s(sf_s + kMxAtom, sfb + size_t(ks) * (kSfbAtoms * kMxAtom), kSfbAtoms * kMxAtom, &full[s]);
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp >= kMxFirstUnpack && warp < kMxFirstEpi) {
+        // ------------------------------------------------------------- unpack
+        // Packed tile: 128 rows x 64 bytes.  Operand tile: 128 rows x 128 bytes with the
+        // 128-byte swizzle, 16 codes in the low 8 bytes of every 16-byte slot.  Lane l of
+        // a pass handles 16 bytes (two slots) of row l / 4: loads are conflict-free.
+        const int uw = warp - kMxFirstUnpack;
+        uint32_t n = 0;
+        for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
+            for (int ks = 0; ks < p.kslabs && !*abort_flag; ++ks, ++n) {
+                const uint32_t ps = n % kMxPkStages, s = n % kStages;
+                if (!mbar_wait_bounded(&pk_full[ps], (n / kMxPkStages) & 1) ||
+                    (n >= kStages && !mbar_wait_bounded(&empty[s], ((n / kStages) - 1) & 1))) {
+                    atomicExch(p.fault, 35);
+                    *abort_flag = 1;
+                    break;
+                }
+                const uint8_t* src = pk_ring + ps * kMxPkBytes;
+                uint8_t* dst = ring + s * kStageBytes;
+#pragma unroll
+                for (int pass = 0; pass < 4; ++pass) {
+                    const int row = uw * 32 + pass * 8 + (lane >> 2), c16 = lane & 3;
+                    const uint4 v = *reinterpret_cast<const uint4*>(src + row * 64 + c16 * 16);
+                    uint8_t* drow = dst + row * 128;
+                    *reinterpret_cast<uint2*>(drow + (((2 * c16) ^ (row & 7)) << 4)) = make_uint2(v.x, v.y);
+                    *reinterpret_cast<uint2*>(drow + (((2 * c16 + 1) ^ (row & 7)) << 4)) = make_uint2(v.z, v.w);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&a_ready[s]);
+                    mbar_arrive(&pk_empty[ps]);
+                }
+            }
+        }
+    } else if (warp == 2) {
         // ---------------------------------------------------------- MMA issuer
         if (lane == 0) {
             uint32_t n = 0, it_n = 0;
+            int cur = 0;
+            const uint32_t ring_addr = smem_u32(ring);
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
+                const MxItem it = mx_decode<kN>(p, tile_prefix, item, cur);
+                const int n16 = (it.rows + 15) & ~15;   // split form: UMMA N = the live rows, in sixteens
+                const uint32_t idesc0 = mx_idesc(kMxM, kJoined ? 2 * kN : n16, 0);
                 const uint32_t buf = it_n & 1;
+                {
+                    MXP_T0();
                 if (it_n >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((it_n >> 1) - 1) & 1)) {
                     atomicExch(p.fault, 32);
                     *abort_flag = 1;
                     break;
                 }
+                    MXP_ADD(0);
+                }
                 tc_fence_after();
+                MXP_T0();
                 for (int ks = 0; ks < p.kslabs; ++ks, ++n) {
                     const uint32_t s = n % kStages;
-                    if (!mbar_wait_bounded(&full[s], (n / kStages) & 1)) {
+                    bool okw;
+                    {
+                        MXP_T0();
+                        okw = mbar_wait_bounded(&full[s], (n / kStages) & 1);
+                        MXP_ADD(1);
+                    }
+                    {
+                        MXP_T0();
+                        okw = okw && mbar_wait_bounded(&a_ready[s], (n / kStages) & 1);
+                        MXP_ADD(2);
+                    }
+                    if (!okw) {
                         atomicExch(p.fault, 33);
                         *abort_flag = 1;
                         break;
                     }
-                    tc_fence_after();
-                    const uint32_t a_addr = smem_u32(ring + s * kStageBytes);
-                    const uint32_t hi_addr = a_addr + kMxATileBytes, lo_addr = hi_addr + kN * 128;
-                    const uint32_t sfa_addr = lo_addr + kN * 128, sfb_addr = sfa_addr + kMxAtom;
+                    // One thread issues everything, so the loop is kept to a few instructions per
+                    // MMA: descriptors advance by adding to the start-address field (32 bytes =
+                    // 2 units per K block), the scale selectors by adding to the two id fields.
+                    const uint32_t a_addr = ring_addr + s * kStageBytes;
+                    const uint64_t a_d = umma_desc_k_sw128(a_addr), b_d = umma_desc_k_sw128(a_addr + kMxATileBytes);
+                    const uint32_t sfa_addr = a_addr + kMxATileBytes + 2 * kN * 128;
                     tmem_cp_32x128b_warpx4(tmem_sfa, umma_desc_k_plain(sfa_addr, 128));
-                    tmem_cp_32x128b_warpx4(tmem_sfb, umma_desc_k_plain(sfb_addr, 128));
+#pragma unroll
+                    for (int at = 0; at < kSfbAtoms; ++at)
+                        tmem_cp_32x128b_warpx4(tmem_sfb + 4 * at, umma_desc_k_plain(sfa_addr + (1 + at) * kMxAtom, 128));
+
+                    const uint32_t d_addr = tmem_base + buf * kAccCols;
 #pragma unroll
                     for (uint32_t kb = 0; kb < 4; ++kb) {
-                        const uint32_t idesc = mx_idesc(kMxM, kN, kb);
-                        const uint64_t a_desc = umma_desc_k_sw128(a_addr + kb * 32);
-                        umma_mx(tmem_base + buf * kN, a_desc, umma_desc_k_sw128(hi_addr + kb * 32), idesc, tmem_sfa,
-                                tmem_sfb, ks > 0 || kb > 0);
-                        umma_mx(tmem_base + buf * kN, a_desc, umma_desc_k_sw128(lo_addr + kb * 32), idesc, tmem_sfa,
-                                tmem_sfb, true);
+                        const uint32_t idesc = idesc0 + kb * ((1u << 4) | (1u << 29));
+                        umma_mx(d_addr, a_d + 2 * kb, b_d + 2 * kb, idesc, tmem_sfa, tmem_sfb, ks > 0 || kb > 0);
+                        if (!kJoined)
+                            umma_mx(d_addr, a_d + 2 * kb, b_d + (kN * 128 >> 4) + 2 * kb, idesc, tmem_sfa, tmem_sfb, true);
                     }
                     umma_commit(&empty[s]);
                 }
+                MXP_ADD(3);
                 if (*abort_flag) break;
                 umma_commit(&acc_full[buf]);
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        const int quarter = warp & 3;
+        // Warp w serves the 32-lane quarter w % 4 (a warp may only read its own quarter of
+        // tensor memory); the two warps of a quarter take alternate 16-column groups.
+        const int quarter = warp & 3, half = (warp - kMxFirstEpi) >> 2;
         const int l = quarter * 32 + lane;   // TMEM lane = weight row of the tile
         uint32_t it_n = 0;
         int cur = 0;
         for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
             const MxItem it = mx_decode<kN>(p, tile_prefix, item, cur);
             const uint32_t buf = it_n & 1;
+            {
+                MXP_T0();
             if (!mbar_wait_bounded(&acc_full[buf], (it_n >> 1) & 1)) {
                 atomicExch(p.fault, 34);
                 *abort_flag = 1;
                 break;
             }
+                if (threadIdx.x == kMxFirstEpi * 32) MXP_ADD(6);
+            }
             tc_fence_after();
+            MXP_T0();
             const int ebias = p.bias_by_global ? it.expert : (it.expert - p.expert_base) / p.expert_div;
             const int row = it.mtile * kMxM + l;
             const bool row_ok = row < p.rows;
             const float b_mine = row_ok ? p.bias[size_t(ebias) * p.rows + row] : 0.f;
-            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kN;
+            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * kAccCols;
             if (kUp) {
-                // rows 2i (gate) and 2i+1 (up) sit in neighbouring lanes
+                // Weight rows 2i (gate) and 2i+1 (up) sit in neighbouring lanes.  Per pair of
+                // columns the lanes swap one value, after which the even lane holds gate and
+                // up of column j and the odd lane those of column j + 1: every lane finishes
+                // one output.
                 const float b_other = __shfl_xor_sync(0xffffffffu, b_mine, 1);
+                const float b_gate = (lane & 1) ? b_other : b_mine, b_up = (lane & 1) ? b_mine : b_other;
                 const int ch = row >> 1;
                 const int inter = p.rows >> 1;
-                for (int c0 = 0; c0 < kN && c0 < it.rows; c0 += 16) {
+                for (int c0 = half * 16; c0 < it.rows; c0 += 32) {
                     uint32_t r[16];
-                    tmem_ld_32x16(taddr + c0, r);
-                    tmem_ld_wait();
+                    mx_load_acc<kN>(taddr + c0, r);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float mine = __uint_as_float(r[j]);
-                        const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-                        if (!(lane & 1) && row_ok && c0 + j < it.rows) {
-                            const float gate = fminf(bf16_round_f(bf16_round_f(mine) + b_mine), p.limit);
-                            const float up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(other) + b_other)));
+                    for (int j = 0; j < 16; j += 2) {
+                        const float send = __uint_as_float((lane & 1) ? r[j] : r[j + 1]);
+                        const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                        const float g_raw = (lane & 1) ? recv : __uint_as_float(r[j]);
+                        const float u_raw = (lane & 1) ? __uint_as_float(r[j + 1]) : recv;
+                        const int col = c0 + j + (lane & 1);
+                        if (row_ok && col < it.rows) {
+                            const float gate = fminf(bf16_round_f(bf16_round_f(g_raw) + b_gate), p.limit);
+                            const float up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(u_raw) + b_up)));
                             const float sig = bf16_round_f(1.f / (1.f + expf(-bf16_round_f(1.702f * gate))));
                             const float glu = bf16_round_f(gate * sig);
-                            p.act_out[size_t(it.row0 + c0 + j) * inter + ch] =
+                            p.act_out[size_t(it.row0 + col) * inter + ch] =
                                 __float2half_rn(bf16_round_f(glu * bf16_round_f(up + 1.f)));
                         }
                     }
                 }
             } else {
-                for (int c0 = 0; c0 < kN && c0 < it.rows; c0 += 16) {
+                for (int c0 = half * 16; c0 < it.rows; c0 += 32) {
                     uint32_t r[16];
-                    tmem_ld_32x16(taddr + c0, r);
-                    tmem_ld_wait();
+                    mx_load_acc<kN>(taddr + c0, r);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         if (row_ok && c0 + j < it.rows) {
@@ -327,12 +483,13 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap w_map, const
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (threadIdx.x == kMxFirstEpi * 32) MXP_ADD(7);
         }
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 2) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
@@ -340,18 +497,26 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap w_map, const
 
 // ------------------------------------------------------------ create-time kernels
 
-// Row-major e2m1 rows padded with zero codes to `kp` columns: dst[e][row][kp / 2].
-__global__ void mx_pad_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, long long rows_total,
-                                   int k, int kp)
+// Weight tiles: dst[e][mtile][kslab][128 rows][64 bytes], i.e. every (128 rows x 128
+// columns) tile of an expert matrix is one contiguous 8 KiB block (a k-slab of a
+// row-major matrix would be 128 separate 64-byte pieces, which DRAM serves at a
+// fraction of its bandwidth).  Rows and columns beyond the matrix hold zero codes.
+__global__ void mx_tile_weights_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int experts, int rows,
+                                       int k, int mtiles, int kslabs)
 {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one 16-byte piece of a padded row
-    const int per_row = kp / 32;
-    if (idx >= rows_total * per_row) return;
-    const long long row = idx / per_row;
-    const int piece = int(idx % per_row);
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one 16-byte piece of the output
+    const long long total = (long long)experts * mtiles * kslabs * (kMxPkBytes / 16);
+    if (idx >= total) return;
+    const int piece = int(idx % 4);
+    const int r = int((idx / 4) % kMxM);
+    const long long tile = idx / (4 * kMxM);
+    const int ks = int(tile % kslabs);
+    const int mt = int((tile / kslabs) % mtiles);
+    const int e = int(tile / ((long long)kslabs * mtiles));
+    const int row = mt * kMxM + r, col = ks * kMxSlab + piece * 32;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (piece * 32 < k) v = *reinterpret_cast<const uint4*>(src + row * (k / 2) + piece * 16);
-    *reinterpret_cast<uint4*>(dst + row * (kp / 2) + piece * 16) = v;
+    if (row < rows && col < k) v = *reinterpret_cast<const uint4*>(src + (size_t(e) * rows + row) * (k / 2) + col / 2);
+    *reinterpret_cast<uint4*>(dst + idx * 16) = v;
 }
 
 // Scale atoms of the weights: dst[e][mtile][kslab][512], byte (r % 32) * 16 + (r / 32) * 4 + kb
@@ -377,29 +542,6 @@ __global__ void mx_weight_atoms_kernel(const uint8_t* __restrict__ scales, uint8
 
 // ------------------------------------------------------------- per-call kernels
 
-// tile_prefix[e] = number of nt-row tiles of the experts before e; one warp.
-__global__ void mx_tile_prefix_kernel(const int* __restrict__ offsets, int experts, int nt, int* __restrict__ tile_prefix)
-{
-    pdl_launch_dependents();
-    pdl_wait();
-    const int lane = threadIdx.x;
-    int run = 0;
-    for (int e0 = 0; e0 < experts; e0 += 32) {
-        const int e = e0 + lane;
-        int tiles = 0;
-        if (e < experts) tiles = (offsets[e + 1] - offsets[e] + nt - 1) / nt;
-        int incl = tiles;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, incl, off);
-            if (lane >= off) incl += v;
-        }
-        if (e < experts) tile_prefix[e] = run + incl - tiles;
-        run += __shfl_sync(0xffffffffu, incl, 31);
-    }
-    if (lane == 0) tile_prefix[experts] = run;
-}
-
 __device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi)
 {
     uint16_t r;
@@ -414,14 +556,45 @@ __device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t v)
     return make_float2(__low2float(h), __high2float(h));
 }
 
-template <typename T>
-__device__ __forceinline__ float mx_load(const T* p);
-template <>
-__device__ __forceinline__ float mx_load<float>(const float* p) { return bf16_round_f(*p); }
-template <>
-__device__ __forceinline__ float mx_load<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-template <>
-__device__ __forceinline__ float mx_load<__half>(const __half* p) { return __half2float(*p); }
+// 32 consecutive elements of a row as bf16-valued floats.
+__device__ __forceinline__ void mx_load32(const float* p, float (&v)[32])
+{
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float4 f = *reinterpret_cast<const float4*>(p + 4 * i);
+        v[4 * i] = bf16_round_f(f.x);
+        v[4 * i + 1] = bf16_round_f(f.y);
+        v[4 * i + 2] = bf16_round_f(f.z);
+        v[4 * i + 3] = bf16_round_f(f.w);
+    }
+}
+__device__ __forceinline__ void mx_load32(const __nv_bfloat16* p, float (&v)[32])
+{
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p + 8 * i);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            v[8 * i + 2 * q] = __uint_as_float(w[q] << 16);
+            v[8 * i + 2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u);
+        }
+    }
+}
+__device__ __forceinline__ void mx_load32(const __half* p, float (&v)[32])
+{
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p + 8 * i);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[q]));
+            v[8 * i + 2 * q] = f.x;
+            v[8 * i + 2 * q + 1] = f.y;
+        }
+    }
+}
 
 // One routed row per CTA, one 32-block per thread: the row (bf16-valued) becomes two
 // e4m3 rows sharing one e8m0 scale per block, written at the row's tile-aligned
@@ -453,16 +626,14 @@ __global__ void mx_quant_rows_kernel(const T* __restrict__ src, const int* __res
     const int idx = pos - offsets[e];
     const int tile = tile_prefix[e] + idx / nt, r = idx % nt;
     const T* row = src + size_t(sorted ? sorted[pos] / div : pos) * k;
-    const int kslabs = kp / kMxSlab;
+    const int kslabs = kp / kMxSlab, atoms = mx_sfb_atoms(nt);
     for (int b = threadIdx.x; b < kp / 32; b += blockDim.x) {
         float v[32];
         float amax = 0.f;
         if (b * 32 < k) {
+            mx_load32(row + b * 32, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                v[i] = mx_load<T>(row + b * 32 + i);
-                amax = fmaxf(amax, fabsf(v[i]));
-            }
+            for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
         } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0.f;
@@ -493,49 +664,65 @@ __global__ void mx_quant_rows_kernel(const T* __restrict__ src, const int* __res
         *reinterpret_cast<uint4*>(dst_hi + 16) = make_uint4(hi_w[4], hi_w[5], hi_w[6], hi_w[7]);
         *reinterpret_cast<uint4*>(dst_lo) = make_uint4(lo_w[0], lo_w[1], lo_w[2], lo_w[3]);
         *reinterpret_cast<uint4*>(dst_lo + 16) = make_uint4(lo_w[4], lo_w[5], lo_w[6], lo_w[7]);
-        sf[(size_t(tile) * kslabs + (b >> 2)) * kMxAtom + (r & 31) * 16 + (r >> 5) * 4 + (b & 3)] = uint8_t(sbyte);
+        // operand rows r (first piece) and nt + r (second piece) carry the same scale
+        uint8_t* atom0 = sf + (size_t(tile) * kslabs + (b >> 2)) * atoms * kMxAtom;
+#pragma unroll
+        for (int piece = 0; piece < (mx_joined(nt) ? 2 : 1); ++piece) {
+            const int rr = r + piece * nt;
+            atom0[(rr >> 7) * kMxAtom + (rr & 31) * 16 + ((rr >> 5) & 3) * 4 + (b & 3)] = uint8_t(sbyte);
+        }
     }
 }
 
 // ------------------------------------------------------------------ host side
 
-bool moe_mx_enabled()
+// GARNET_B200_MOE_MX: 0 keeps the expert GEMMs on the kernels that expand the weights
+// in registers, 2 uses the block-scaled path at every size (for tests), anything else
+// lets the row count per expert decide.  Read once.
+static int moe_mx_mode()
 {
-    // GARNET_B200_MOE_MX=0 keeps the expert GEMMs on the kernels that expand the
-    // weights in registers (A/B switch, read once).
-    static const bool on = [] {
+    static const int mode = [] {
         const char* e = getenv("GARNET_B200_MOE_MX");
-        return !(e && e[0] == '0');
+        return (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : 1;
     }();
-    return on;
+    return mode;
 }
+bool moe_mx_enabled() { return moe_mx_mode() != 0; }
+bool moe_mx_forced() { return moe_mx_mode() == 2; }
 
-int moe_mx_nt(int rows_per_expert_max)
+// Rows per tile: no expert can get more rows than there are tokens; beyond 64 the
+// average decides between 120-row joined tiles and 160-row split tiles.
+int moe_mx_nt(int tokens, int slots, int local_experts)
 {
-    return rows_per_expert_max <= 16 ? 16 : rows_per_expert_max <= 32 ? 32 : rows_per_expert_max <= 64 ? 64 : 128;
+    if (tokens <= 16) return 16;
+    if (tokens <= 32) return 32;
+    if (tokens <= 64) return 64;
+    return slots / std::max(1, local_experts) <= 100 ? 120 : 160;
 }
 
 MoeMxPlan moe_mx_plan(const garnet_b200_moe_options& o, int tokens, int slots)
 {
     MoeMxPlan m;
-    m.nt = moe_mx_nt(tokens);
+    const int world = o.ep_world > 1 ? o.ep_world : 1;
+    m.nt = moe_mx_nt(tokens, slots, std::max(1, o.experts / world));
     m.tiles_max = slots / m.nt + std::min(slots, o.experts) + 1;   // full tiles + one partial tile per expert that has rows
     m.q_rows = m.tiles_max * m.nt;
     const int kmax = std::max(o.hidden, o.intermediate);
     m.kp_max = (kmax + kMxSlab - 1) / kMxSlab * kMxSlab;
     m.q_bytes = size_t(2) * m.q_rows * m.kp_max;
-    m.sf_bytes = size_t(m.tiles_max) * (m.kp_max / kMxSlab) * kMxAtom;
+    m.sf_bytes = size_t(m.tiles_max) * (m.kp_max / kMxSlab) * mx_sfb_atoms(m.nt) * kMxAtom;
     return m;
 }
 
 static int mx_encode(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, const void* base, const cuuint64_t* dims,
-                     const cuuint64_t* strides, const cuuint32_t* box)
+                     const cuuint64_t* strides, const cuuint32_t* box,
+                     CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B)
 {
     TensorMapEncodeFn enc = tensor_map_encoder();
     if (!enc) return fail(GARNET_B200_NOT_SUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     const CUresult r = enc(map, dt, rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(GARNET_B200_CUDA_ERROR, "cuTensorMapEncodeTiled (block-scaled path) failed with code %d", int(r));
     return GARNET_B200_OK;
@@ -556,17 +743,15 @@ int Moe::init_mx(int pass, const uint8_t* blocks, const uint8_t* scales, int fir
     const int kp = (k + kMxSlab - 1) / kMxSlab * kMxSlab;
     const int mtiles = (rows + kMxM - 1) / kMxM, kslabs = kp / kMxSlab;
     if (!mx_w[pass]) {
-        // one spare row: the last tile's TMA box may start inside the matrix and is clipped, never read past it
-        GB_CUDA(cudaMalloc(&mx_w[pass], size_t(stored_experts) * rows * (kp / 2)));
+        GB_CUDA(cudaMalloc(&mx_w[pass], size_t(stored_experts) * mtiles * kslabs * kMxPkBytes));
         GB_CUDA(cudaMalloc(&mx_sfa[pass], size_t(stored_experts) * mtiles * kslabs * kMxAtom));
         mx_kp[pass] = kp;
         mx_mtiles[pass] = mtiles;
         mx_kslabs[pass] = kslabs;
     }
-    const long long rows_total = (long long)count * rows;
-    const long long pieces = rows_total * (kp / 32);
-    mx_pad_rows_kernel<<<unsigned((pieces + 255) / 256), 256, 0, stream>>>(
-        blocks, mx_w[pass] + size_t(first_stored) * rows * (kp / 2), rows_total, k, kp);
+    const long long pieces = (long long)count * mtiles * kslabs * (kMxPkBytes / 16);
+    mx_tile_weights_kernel<<<unsigned((pieces + 255) / 256), 256, 0, stream>>>(
+        blocks, mx_w[pass] + size_t(first_stored) * mtiles * kslabs * kMxPkBytes, count, rows, k, mtiles, kslabs);
     const long long bytes = (long long)count * mtiles * kslabs * kMxAtom;
     mx_weight_atoms_kernel<<<unsigned((bytes + 255) / 256), 256, 0, stream>>>(
         scales, mx_sfa[pass] + size_t(first_stored) * mtiles * kslabs * kMxAtom, count, rows, k / 32, mtiles, kslabs);
@@ -579,31 +764,22 @@ int Moe::finish_mx()
     mx_ok = false;
     if (!tensor_map_encoder() || opt.experts > kMxMaxExperts) return GARNET_B200_OK;
     if ((opt.hidden % 32) || (opt.intermediate % 32)) return GARNET_B200_OK;
-    static_assert(sizeof(TensorMapStorage) == sizeof(CUtensorMap), "tensor map storage size");
-    for (int pass = 0; pass < 2; ++pass) {
-        const PackGeom& geo = pass == 0 ? geo_up : geo_down;
-        const cuuint64_t dims[3] = {cuuint64_t(mx_kp[pass]), cuuint64_t(geo.rows), cuuint64_t(stored_experts)};
-        const cuuint64_t strides[2] = {cuuint64_t(mx_kp[pass] / 2), cuuint64_t(geo.rows) * (mx_kp[pass] / 2)};
-        const cuuint32_t box[3] = {kMxSlab, kMxM, 1};
-        if (int rc = mx_encode(reinterpret_cast<CUtensorMap*>(&mx_w_map[pass]), CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3,
-                               mx_w[pass], dims, strides, box))
-            return rc;
-    }
     GB_CUDA((mx_set_attr<true, 16>()));
     GB_CUDA((mx_set_attr<true, 32>()));
     GB_CUDA((mx_set_attr<true, 64>()));
-    GB_CUDA((mx_set_attr<true, 128>()));
+    GB_CUDA((mx_set_attr<true, 120>()));
+    GB_CUDA((mx_set_attr<true, 160>()));
+    GB_CUDA((mx_set_attr<false, 160>()));
     GB_CUDA((mx_set_attr<false, 16>()));
     GB_CUDA((mx_set_attr<false, 32>()));
     GB_CUDA((mx_set_attr<false, 64>()));
-    GB_CUDA((mx_set_attr<false, 128>()));
+    GB_CUDA((mx_set_attr<false, 120>()));
     mx_ok = true;
     return GARNET_B200_OK;
 }
 
 template <bool kUp, int kN>
-static cudaError_t mx_launch(const MxParams& p, const CUtensorMap& wm, const CUtensorMap& qm, int q_rows, int grid,
-                             cudaStream_t stream)
+static cudaError_t mx_launch(const MxParams& p, const CUtensorMap& qm, int q_rows, int grid, cudaStream_t stream)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(grid));
@@ -615,7 +791,7 @@ static cudaError_t mx_launch(const MxParams& p, const CUtensorMap& wm, const CUt
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, moe_mx_kernel<kUp, kN>, p, wm, qm, q_rows);
+    return cudaLaunchKernelEx(&cfg, moe_mx_kernel<kUp, kN>, p, qm, q_rows);
 }
 
 // Quantises the rows (layer input for the gate/up projection, activations for the
@@ -636,11 +812,6 @@ int Moe::launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_s
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cfg.stream = stream;
-    if (up) {
-        cfg.gridDim = dim3(1);
-        cfg.blockDim = dim3(32);
-        GB_CUDA(cudaLaunchKernelEx(&cfg, mx_tile_prefix_kernel, (const int*)w.offsets, opt.experts, nt, w.mx_tp));
-    }
     cfg.gridDim = dim3(unsigned(slots));
     cfg.blockDim = dim3(96);
     const int* sorted = (up && !x_is_sorted) ? w.sorted : nullptr;
@@ -669,6 +840,7 @@ int Moe::launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_s
     p.sorted = w.sorted;
     p.tile_prefix = w.mx_tp;
     p.bias = up ? up_bias_ptr : down_bias_ptr;
+    p.w = mx_w[pass];
     p.sfa = mx_sfa[pass];
     p.sfb = w.mx_sf;
     p.act_out = w.act;
@@ -682,19 +854,32 @@ int Moe::launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_s
     p.expert_div = (sh.world > 1 && sh.interleaved) ? sh.world : 1;
     p.bias_by_global = (!opt.expert_weights_sharded && sh.world > 1) ? 1 : 0;
     p.limit = opt.limit;
-    const CUtensorMap& wm = *reinterpret_cast<const CUtensorMap*>(&mx_w_map[pass]);
     // upper bound of the item count: every tile of every expert
     const long long max_items = (long long)plan.tiles_max * p.mtiles;
     const int grid = int(std::min<long long>(kSmCount, max_items));
 #define GB_MX_LAUNCH(N_)                                                                       \
-    GB_CUDA(up ? (mx_launch<true, N_>(p, wm, q_map, plan.q_rows, grid, stream))                \
-               : (mx_launch<false, N_>(p, wm, q_map, plan.q_rows, grid, stream)))
+    GB_CUDA(up ? (mx_launch<true, N_>(p, q_map, plan.q_rows, grid, stream))                \
+               : (mx_launch<false, N_>(p, q_map, plan.q_rows, grid, stream)))
     if (nt == 16) GB_MX_LAUNCH(16);
     else if (nt == 32) GB_MX_LAUNCH(32);
     else if (nt == 64) GB_MX_LAUNCH(64);
-    else GB_MX_LAUNCH(128);
+    else if (nt == 120) GB_MX_LAUNCH(120);
+    else GB_MX_LAUNCH(160);
 #undef GB_MX_LAUNCH
     return GARNET_B200_OK;
 }
 
 }  // namespace gb200
+
+#if defined(GB_TUNE_PROF)
+extern "C" int garnet_b200_mx_prof(unsigned long long* out, int reset)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, gb200::g_mx_prof, sizeof(unsigned long long) * 16);
+    if (reset) {
+        unsigned long long z[16] = {0};
+        cudaMemcpyToSymbol(gb200::g_mx_prof, z, sizeof(z));
+    }
+    return 0;
+}
+#endif

@@ -79,7 +79,7 @@ class GptOssMoe:
         return y
 
     def run_static(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """`run` without a workspace: the scratch is the 2 MiB array built into the
+        """`run` without a workspace: the scratch is the 8 MiB array built into the
         library, for callers that must not allocate device memory (see
         garnet_b200_moe_run_static in include/garnet_b200.h for the limits: small
         token counts only, one call at a time per device)."""

@@ -198,11 +198,11 @@ int garnet_b200_moe_run(garnet_b200_moe_t h, const void* d_x, void* d_y, void* d
  * for hosts that drive this library directly from a latency-critical decode loop
  * in which device allocation is off limits: cudaMalloc and cudaFree serialise
  * with all work on the device, and in deployments where another runtime has
- * already reserved the GPU's memory they simply fail.  The scratch is a 2 MiB
+ * already reserved the GPU's memory they simply fail.  The scratch is a 8 MiB
  * array built into the library image (held by every GPU that loads the library,
  * until the process exits); this call allocates and frees nothing, on the host
  * side of CUDA or through any library.
- *   - Limit: the layer's workspace for `tokens` must fit in 2 MiB - 27 tokens for
+ *   - Limit: the layer's workspace for `tokens` must fit in 8 MiB - 15 tokens for
  *     the gpt-oss-120b layer (hidden = intermediate = 2880, 128 experts, top-4).
  *     Larger requests are rejected with INVALID_VALUE and a message that names the
  *     largest token count that fits.

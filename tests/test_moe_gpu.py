@@ -256,3 +256,20 @@ def test_rows_entry_point_and_combine_match_full_operator():
     assert torch.equal(full.combine(merged, pr), y)
     # bf16 wire format is exact for the per-row values
     assert torch.equal(vals.bfloat16().float(), vals)
+
+
+def test_block_scaled_path_at_every_size():
+    """Small batches normally take the streaming kernel; GARNET_B200_MOE_MX=2 sends every
+    size through the block-scaled tensor-core path.  The switch is read once per process,
+    so the fixture and golden parity tests are re-run in a child process with it set."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("GARNET_B200_MOE_MX") == "2":
+        pytest.skip("already running with the block-scaled path forced")
+    env = dict(os.environ, GARNET_B200_MOE_MX="2")
+    here = os.path.dirname(os.path.abspath(__file__))
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_moe_gpu.py"), "-m", "gpu", "-q", "-x",
+                        "-k", "fixtures or golden or bf16_io or rows"], env=env, capture_output=True, text=True,
+                       timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

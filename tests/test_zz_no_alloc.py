@@ -4,7 +4,7 @@ Some hosts cannot hand the operator a workspace because they may not allocate
 device memory where they call it - a decode loop that must never hit the CUDA
 allocator (allocation and free serialise the whole device), or a process in
 which another runtime already owns all of the GPU's memory.  For them the
-library carries a 2 MiB scratch array of its own.  This file checks, through the
+library carries a 8 MiB scratch array of its own.  This file checks, through the
 C ABI, that the entry point gives exactly what the ordinary entry point gives,
 twice in a row (the array is shared and keeps its old contents between calls),
 and that requests beyond the array's size are refused with a clear message.
