@@ -498,6 +498,35 @@ def run_profile_case(spec):
         rows = bench_moe(torch, gb, measured_peaks(), A, token_counts=(int(spec.split(":")[1]),))
         print(json.dumps({"case": spec, **rows[0]}))
         return
+    if spec == "pass":
+        # the headline decode pass (28 layers + lm_head, M = 1): 2 warm-up + 2 timed passes, no graph
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(1234)
+        layers = [[make_linear(torch, gb, k, n, gen) for (_, k, n) in PROJ] for _ in range(LAYERS)]
+        head = make_linear(torch, gb, LM_HEAD[1], LM_HEAD[2], gen)
+        xs = {k: torch.randn(1, k, device="cuda", generator=gen).to(torch.bfloat16) for k in (2048, 6144)}
+        mk = lambda n: torch.empty(1, n, device="cuda", dtype=torch.bfloat16)
+        yq, yk, yv, yo, yg, yu, yd, yh = mk(2048), mk(1024), mk(1024), mk(2048), mk(6144), mk(6144), mk(2048), mk(LM_HEAD[2])
+
+        def decode_pass():
+            for q, kk, v, o, gate, up, down in layers:
+                gb.forward_group([q, kk, v], xs[2048], outs=[yq, yk, yv])
+                o.forward(xs[2048], out=yo)
+                gb.forward_group([gate, up], xs[2048], outs=[yg, yu])
+                down.forward(xs[6144], out=yd)
+            head.forward(xs[2048], out=yh)
+
+        for _ in range(2):
+            decode_pass()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(2):
+            decode_pass()
+        b.record()
+        torch.cuda.synchronize()
+        print(json.dumps({"case": spec, "ms_per_pass_no_graph": round(a.elapsed_time(b) / 2, 4)}))
+        return
     parts = spec.split(":")
     kind, k, n, m = parts[0], int(parts[1]), int(parts[2]), int(parts[3])
     copies = int(parts[4]) if len(parts) > 4 else 2      # weight copies rotated through (to defeat L2)
@@ -530,7 +559,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-moe", action="store_true")
-    ap.add_argument("--profile", default=None, help="w4a16:K:N:M - run one small case for a profiler capture")
+    ap.add_argument("--profile", default=None,
+                    help="w4a16:K:N:M[:copies] | moe:T | pass - run one small case for a profiler capture")
     args = ap.parse_args()
     if args.profile:
         run_profile_case(args.profile)

@@ -53,9 +53,10 @@ constexpr uint32_t kMxATileBytes = kMxM * 128;       // shared-memory footprint 
 //     the same accumulator.
 __host__ __device__ constexpr bool mx_joined(int nt) { return nt <= 120; }
 __host__ __device__ constexpr int mx_sfb_atoms(int nt) { return ((mx_joined(nt) ? 2 : 1) * nt + 127) / 128; }
-// An MMA of this kind was measured to occupy the tensor pipe for about 100 cycles
-// however small its N, and in proportion to N only above N of about 190: the
-// instruction count, not the math, sets the pace of small tiles, hence the joined form.
+// An MMA of this kind (M = 128, K = 32) was measured to occupy the tensor pipe for about
+// 130 cycles however small its N - the time to stream its 4 KiB A tile - and only an
+// N near 256 has that much math: the instruction count, not the math, sets the pace of
+// small tiles, hence the joined form wherever the tile is short enough.
 __host__ __device__ constexpr int mx_stage_bytes(int nt)
 {
     return int(kMxATileBytes) + 2 * nt * 128 + 1024 * ((kMxAtom * (1 + mx_sfb_atoms(nt)) + 1023) / 1024);
@@ -94,16 +95,6 @@ struct MxParams {
     int expert_base, expert_div, bias_by_global;
     float limit;
 };
-
-// 3-D tiled TMA load (innermost coordinate first).
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
-            smem_u32(dst)),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
-        : "memory");
-}
 
 // K-major operand without swizzle: 8-row core matrices of 128 contiguous bytes,
 // `sbo` bytes apart (the source format of the scale-atom copies).
@@ -168,15 +159,6 @@ __device__ __forceinline__ void mx_load_acc(uint32_t taddr, uint32_t (&r)[16])
         tmem_ld_wait();
     }
 }
-
-#if defined(GB_TUNE_PROF)
-__device__ unsigned long long g_mx_prof[16];
-#define MXP_T0() const long long _t0 = clock64()
-#define MXP_ADD(i) atomicAdd(&g_mx_prof[i], (unsigned long long)(clock64() - _t0))
-#else
-#define MXP_T0()
-#define MXP_ADD(i)
-#endif
 
 struct MxItem {
     int expert, tile, mtile, rows;   // tile: global row-tile index; rows: live rows of it
@@ -266,9 +248,7 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap q_map, const
                 const uint8_t* wt = p.w + (size_t(se) * p.mtiles + it.mtile) * p.kslabs * kMxPkBytes;
                 for (int ks = 0; ks < p.kslabs; ++ks, ++n) {
                     const uint32_t s = n % kMxPkStages;
-                    MXP_T0();
                     const bool okw = !(n >= kMxPkStages && !mbar_wait_bounded(&pk_empty[s], ((n / kMxPkStages) - 1) & 1));
-                    MXP_ADD(5);
                     if (!okw) {
                         atomicExch(p.fault, 30);
                         *abort_flag = 1;
@@ -292,9 +272,7 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap q_map, const
                 constexpr uint32_t tx = uint32_t(2 * kN * 128) + uint32_t((1 + kSfbAtoms) * kMxAtom);
                 for (int ks = 0; ks < p.kslabs; ++ks, ++n) {
                     const uint32_t s = n % kStages;
-                    MXP_T0();
                     const bool okw = !(n >= kStages && !mbar_wait_bounded(&empty[s], ((n / kStages) - 1) & 1));
-                    MXP_ADD(4);
                     if (!okw) {
                         atomicExch(p.fault, 31);
                         *abort_flag = 1;
@@ -355,31 +333,16 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap q_map, const
                 const int n16 = (it.rows + 15) & ~15;   // split form: UMMA N = the live rows, in sixteens
                 const uint32_t idesc0 = mx_idesc(kMxM, kJoined ? 2 * kN : n16, 0);
                 const uint32_t buf = it_n & 1;
-                {
-                    MXP_T0();
                 if (it_n >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((it_n >> 1) - 1) & 1)) {
                     atomicExch(p.fault, 32);
                     *abort_flag = 1;
                     break;
                 }
-                    MXP_ADD(0);
-                }
                 tc_fence_after();
-                MXP_T0();
                 for (int ks = 0; ks < p.kslabs; ++ks, ++n) {
                     const uint32_t s = n % kStages;
-                    bool okw;
-                    {
-                        MXP_T0();
-                        okw = mbar_wait_bounded(&full[s], (n / kStages) & 1);
-                        MXP_ADD(1);
-                    }
-                    {
-                        MXP_T0();
-                        okw = okw && mbar_wait_bounded(&a_ready[s], (n / kStages) & 1);
-                        MXP_ADD(2);
-                    }
-                    if (!okw) {
+                    if (!mbar_wait_bounded(&full[s], (n / kStages) & 1) ||
+                        !mbar_wait_bounded(&a_ready[s], (n / kStages) & 1)) {
                         atomicExch(p.fault, 33);
                         *abort_flag = 1;
                         break;
@@ -405,7 +368,6 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap q_map, const
                     }
                     umma_commit(&empty[s]);
                 }
-                MXP_ADD(3);
                 if (*abort_flag) break;
                 umma_commit(&acc_full[buf]);
             }
@@ -421,17 +383,12 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap q_map, const
         for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
             const MxItem it = mx_decode<kN>(p, tile_prefix, item, cur);
             const uint32_t buf = it_n & 1;
-            {
-                MXP_T0();
             if (!mbar_wait_bounded(&acc_full[buf], (it_n >> 1) & 1)) {
                 atomicExch(p.fault, 34);
                 *abort_flag = 1;
                 break;
             }
-                if (threadIdx.x == kMxFirstEpi * 32) MXP_ADD(6);
-            }
             tc_fence_after();
-            MXP_T0();
             const int ebias = p.bias_by_global ? it.expert : (it.expert - p.expert_base) / p.expert_div;
             const int row = it.mtile * kMxM + l;
             const bool row_ok = row < p.rows;
@@ -483,7 +440,6 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap q_map, const
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
-            if (threadIdx.x == kMxFirstEpi * 32) MXP_ADD(7);
         }
     }
 
@@ -870,16 +826,3 @@ int Moe::launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_s
 }
 
 }  // namespace gb200
-
-#if defined(GB_TUNE_PROF)
-extern "C" int garnet_b200_mx_prof(unsigned long long* out, int reset)
-{
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, gb200::g_mx_prof, sizeof(unsigned long long) * 16);
-    if (reset) {
-        unsigned long long z[16] = {0};
-        cudaMemcpyToSymbol(gb200::g_mx_prof, z, sizeof(z));
-    }
-    return 0;
-}
-#endif
