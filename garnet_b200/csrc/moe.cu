@@ -909,7 +909,11 @@ MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens)
     const bool tc = moe_tc_eligible(o, tokens);
     w.xg = take(tc ? slots * o.hidden * 2 : 0);
     w.xshift_g = take(tc ? slots * 4 : 0);
-    const bool mx = moe_mx_enabled();
+    // the block-scaled path's buffers exist only at sizes that use it (see Moe::use_mx)
+    const int mx_world = o.ep_world > 1 ? o.ep_world : 1;
+    const int mx_local = mx_world <= 1 ? o.experts   // the same count as Moe::local_experts()
+                         : o.ep_interleaved ? (o.experts - o.ep_rank + mx_world - 1) / mx_world : o.experts / mx_world;
+    const bool mx = moe_mx_enabled() && (moe_mx_forced() || slots > size_t(8) * mx_local);
     const MoeMxPlan mxp = moe_mx_plan(o, tokens, int(slots));
     w.mx_tp = take(mx ? size_t(o.experts + 1) * 4 : 0);
     w.mx_q = take(mx ? mxp.q_bytes : 0);
@@ -973,6 +977,8 @@ Moe::~Moe()
     for (int i = 0; i < 2; ++i) {
         if (mx_w[i]) cudaFree(mx_w[i]);
         if (mx_sfa[i]) cudaFree(mx_sfa[i]);
+        if (mxr_w[i]) cudaFree(mxr_w[i]);
+        if (mxr_sf[i]) cudaFree(mxr_sf[i]);
     }
     if (packed_up) cudaFree(packed_up);
     if (packed_down) cudaFree(packed_down);

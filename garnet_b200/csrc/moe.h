@@ -60,6 +60,7 @@ struct MoeMxPlan {
 MoeMxPlan moe_mx_plan(const garnet_b200_moe_options& o, int tokens, int slots);
 bool moe_mx_enabled();
 bool moe_mx_forced();
+bool moe_mx_weights_as_m();   // the earlier orientation (GARNET_B200_MOE_MX=3), kept for comparison
 size_t moe_route_partial_bytes(int tokens, int experts);
 // True when the per-expert row counts are large enough for the tensor-core tile kernel.
 bool moe_tc_eligible(const garnet_b200_moe_options& o, int tokens);
@@ -82,6 +83,10 @@ struct Moe {
     TensorMapStorage mx_w_map[2];
     int mx_kp[2] = {0, 0}, mx_mtiles[2] = {0, 0}, mx_kslabs[2] = {0, 0};
     bool mx_ok = false;
+    uint8_t* mxr_w[2] = {nullptr, nullptr};    // rows-as-M form: 15 KiB blocks of 240 weight rows
+    uint8_t* mxr_sf[2] = {nullptr, nullptr};   // and their scale atoms
+    int mxr_ntiles[2] = {0, 0};
+    TensorMapStorage mxr_w_map[2];
     __nv_bfloat16* router_w3 = nullptr;        // router weight split into three bf16 terms (tensor-core router)
     bool route_mma_ok = false;
     bool tc_ok = false;                // scale bytes fit the fp16 window of the tensor-core path
@@ -106,6 +111,10 @@ struct Moe {
     bool use_tc(int slots) const;
     int init_mx(int pass, const uint8_t* blocks, const uint8_t* scales, int first_stored, int count, cudaStream_t stream);
     int finish_mx();
+    int init_mxr(int pass, const uint8_t* blocks, const uint8_t* scales, int first_stored, int count, cudaStream_t stream);
+    int finish_mxr();
+    int launch_mxr_gemm(bool up, const MoeWorkspacePtrs& w, const void* q_map, int q_rows, int tiles_max,
+                        cudaStream_t stream);
     int launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_sorted, int tokens, int slots, int topk,
                   cudaStream_t stream);
     // The block-scaled path pays off once experts get several rows each (measured

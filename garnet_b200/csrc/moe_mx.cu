@@ -31,19 +31,17 @@
 #include "layout.h"
 #include "moe.h"
 #include "tc_common.cuh"
+#include "mx_common.cuh"
 
 namespace gb200 {
 
 constexpr int kMxM = 128;            // weight rows per tile
-constexpr int kMxSlab = 128;         // K elements per pipeline stage (4 MMAs of K = 32 per piece)
-constexpr int kMxAtom = 512;         // bytes of one scale atom: 128 rows x 4 blocks
 constexpr int kMxEpiWarps = 8;       // two per 32-lane quarter of tensor memory
 constexpr int kMxUnpackWarps = 4;
 constexpr int kMxFirstUnpack = 3, kMxFirstEpi = kMxFirstUnpack + kMxUnpackWarps;
 constexpr int kMxThreads = (kMxFirstEpi + kMxEpiWarps) * 32;   // 2 producers, MMA issuer, unpack and epilogue warps
 constexpr int kMxPkStages = 4;       // ring of packed weight tiles (8 KiB each)
 constexpr int kMxPkBytes = kMxM * kMxSlab / 2;
-constexpr int kMxMaxExperts = 1024;
 constexpr uint32_t kMxATileBytes = kMxM * 128;       // shared-memory footprint of a weight tile
 
 // Two ways to feed the two e4m3 pieces of a tile's rows:
@@ -95,53 +93,6 @@ struct MxParams {
     int expert_base, expert_div, bias_by_global;
     float limit;
 };
-
-// K-major operand without swizzle: 8-row core matrices of 128 contiguous bytes,
-// `sbo` bytes apart (the source format of the scale-atom copies).
-__device__ __forceinline__ uint64_t umma_desc_k_plain(uint32_t smem_addr, uint32_t sbo)
-{
-    uint64_t d = 0;
-    d |= uint64_t((smem_addr & 0x3FFFFu) >> 4);
-    d |= uint64_t(sbo >> 4) << 32;
-    d |= uint64_t(1) << 46;   // version
-    return d;
-}
-
-// 32 rows x 16 bytes of shared memory -> 4 columns of tensor memory, replicated to
-// the four 32-lane quarters.
-__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc)
-{
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
-// Instruction descriptor of kind::mxf8f6f4: A = e2m1, B = e4m3, both K-major, e8m0
-// scales; `sf` selects which of the four blocks of the scale atoms this MMA uses.
-__device__ __forceinline__ uint32_t mx_idesc(int m, int n, uint32_t sf)
-{
-    return (sf << 4) | (5u << 7) | (0u << 10) | (uint32_t(n >> 3) << 17) | (1u << 23) | (uint32_t(m >> 4) << 24) | (sf << 29);
-}
-
-__device__ __forceinline__ void umma_mx(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa,
-                                        uint32_t sfb, bool accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate)), "r"(sfa), "r"(sfb)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
 
 // 16 accumulator columns of this thread's lane; in the joined form the two pieces'
 // columns, kN apart, are added.
@@ -331,7 +282,7 @@ moe_mx_kernel(const MxParams p, const __grid_constant__ CUtensorMap q_map, const
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
                 const MxItem it = mx_decode<kN>(p, tile_prefix, item, cur);
                 const int n16 = (it.rows + 15) & ~15;   // split form: UMMA N = the live rows, in sixteens
-                const uint32_t idesc0 = mx_idesc(kMxM, kJoined ? 2 * kN : n16, 0);
+                const uint32_t idesc0 = mx_idesc_fmt(kMxFmtE2M1, kMxFmtE4M3, kMxM, kJoined ? 2 * kN : n16, 0);
                 const uint32_t buf = it_n & 1;
                 if (it_n >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((it_n >> 1) - 1) & 1)) {
                     atomicExch(p.fault, 32);
@@ -633,23 +584,27 @@ __global__ void mx_quant_rows_kernel(const T* __restrict__ src, const int* __res
 // ------------------------------------------------------------------ host side
 
 // GARNET_B200_MOE_MX: 0 keeps the expert GEMMs on the kernels that expand the weights
-// in registers, 2 uses the block-scaled path at every size (for tests), anything else
-// lets the row count per expert decide.  Read once.
+// in registers, 2 uses the block-scaled path at every size (for tests), 3 selects the
+// orientation with the weights as the M operand (this file's kernel; the default is the
+// rows-as-M kernel of moe_mxr.cu), anything else lets the row count per expert decide.
+// Read once.
 static int moe_mx_mode()
 {
     static const int mode = [] {
         const char* e = getenv("GARNET_B200_MOE_MX");
-        return (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : 1;
+        return (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : (e && e[0] == '3') ? 3 : 1;
     }();
     return mode;
 }
 bool moe_mx_enabled() { return moe_mx_mode() != 0; }
 bool moe_mx_forced() { return moe_mx_mode() == 2; }
+bool moe_mx_weights_as_m() { return moe_mx_mode() == 3; }
 
 // Rows per tile: no expert can get more rows than there are tokens; beyond 64 the
 // average decides between 120-row joined tiles and 160-row split tiles.
 int moe_mx_nt(int tokens, int slots, int local_experts)
 {
+    if (!moe_mx_weights_as_m()) return 128;   // rows-as-M kernel: 128-row tiles
     if (tokens <= 16) return 16;
     if (tokens <= 32) return 32;
     if (tokens <= 64) return 64;
@@ -698,6 +653,10 @@ int Moe::init_mx(int pass, const uint8_t* blocks, const uint8_t* scales, int fir
     const int k = geo.cols, rows = geo.rows;
     const int kp = (k + kMxSlab - 1) / kMxSlab * kMxSlab;
     const int mtiles = (rows + kMxM - 1) / kMxM, kslabs = kp / kMxSlab;
+    mx_kp[pass] = kp;
+    mx_mtiles[pass] = mtiles;
+    mx_kslabs[pass] = kslabs;
+    if (!moe_mx_weights_as_m()) return init_mxr(pass, blocks, scales, first_stored, count, stream);
     if (!mx_w[pass]) {
         GB_CUDA(cudaMalloc(&mx_w[pass], size_t(stored_experts) * mtiles * kslabs * kMxPkBytes));
         GB_CUDA(cudaMalloc(&mx_sfa[pass], size_t(stored_experts) * mtiles * kslabs * kMxAtom));
@@ -720,6 +679,7 @@ int Moe::finish_mx()
     mx_ok = false;
     if (!tensor_map_encoder() || opt.experts > kMxMaxExperts) return GARNET_B200_OK;
     if ((opt.hidden % 32) || (opt.intermediate % 32)) return GARNET_B200_OK;
+    if (int rc = finish_mxr()) return rc;
     GB_CUDA((mx_set_attr<true, 16>()));
     GB_CUDA((mx_set_attr<true, 32>()));
     GB_CUDA((mx_set_attr<true, 64>()));
@@ -791,6 +751,7 @@ int Moe::launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_s
         const cuuint32_t box[2] = {kMxSlab, cuuint32_t(nt)};
         if (int rc = mx_encode(&q_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w.mx_q, dims, strides, box)) return rc;
     }
+    if (!moe_mx_weights_as_m()) return launch_mxr_gemm(up, w, &q_map, plan.q_rows, plan.tiles_max, stream);
     MxParams p;
     p.offsets = w.offsets;
     p.sorted = w.sorted;

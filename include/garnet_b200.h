@@ -202,7 +202,7 @@ int garnet_b200_moe_run(garnet_b200_moe_t h, const void* d_x, void* d_y, void* d
  * array built into the library image (held by every GPU that loads the library,
  * until the process exits); this call allocates and frees nothing, on the host
  * side of CUDA or through any library.
- *   - Limit: the layer's workspace for `tokens` must fit in 8 MiB - 15 tokens for
+ *   - Limit: the layer's workspace for `tokens` must fit in 8 MiB - 111 tokens for
  *     the gpt-oss-120b layer (hidden = intermediate = 2880, 128 experts, top-4).
  *     Larger requests are rejected with INVALID_VALUE and a message that names the
  *     largest token count that fits.
