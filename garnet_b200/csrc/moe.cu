@@ -332,10 +332,17 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
     }
 }
 
+__device__ __forceinline__ bool expert_is_local(int e, const MoeShard& sh)
+{
+    if (sh.world <= 1) return true;
+    return sh.interleaved ? (e % sh.world) == sh.rank : (e >= sh.lo && e < sh.hi);
+}
+
 // k rounds of arg-max (ties to the lowest expert index), then the softmax over the
 // selected logits only (gpt_oss_kernels.cu:681-726).  One warp per token.
 __global__ void moe_topk_kernel(const float* __restrict__ logits, int* __restrict__ selected,
-                                float* __restrict__ probs, int tokens, int experts, int topk)
+                                float* __restrict__ probs, int tokens, int experts, int topk, int* __restrict__ counts,
+                                MoeShard sh)
 {
     const int token = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -373,6 +380,8 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int* __restric
         for (int j = 0; j < topk; ++j) {
             selected[token * topk + j] = chosen[j];
             probs[token * topk + j] = bf16_round_f(expf(top[j] - top[0]) / total);
+            // rows per local expert (zeroed by the caller): integer adds, any order
+            if (counts && expert_is_local(chosen[j], sh)) atomicAdd(&counts[chosen[j]], 1);
         }
     }
 }
@@ -403,11 +412,6 @@ __global__ void moe_prep_rows_kernel(const XT* __restrict__ x, __half* __restric
 
 // ------------------------------------------------------------ slot bucketing
 
-__device__ __forceinline__ bool expert_is_local(int e, const MoeShard& sh)
-{
-    if (sh.world <= 1) return true;
-    return sh.interleaved ? (e % sh.world) == sh.rank : (e >= sh.lo && e < sh.hi);
-}
 
 // counts[e] = number of routed slots of expert e (0 for experts of other ranks).
 __global__ void moe_count_kernel(const int* __restrict__ selected, int slots, int* __restrict__ counts, MoeShard sh)
@@ -1106,7 +1110,7 @@ static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 }
 
 int Moe::route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
-               cudaStream_t stream, bool skip_topk, float* route_partial)
+               cudaStream_t stream, bool skip_topk, float* route_partial, int* counts)
 {
     const size_t smem = size_t(kRouteTokens) * opt.hidden * sizeof(float);
     if (smem > kMaxDynamicSmem - 2048) return fail(GARNET_B200_NOT_SUPPORTED, "moe_route: hidden too large");
@@ -1139,9 +1143,11 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
             static_cast<const __nv_bfloat16*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens,
             opt.hidden, opt.experts, per_cta);
     }
-    if (!skip_topk)
+    if (!skip_topk) {
+        if (counts) GB_CUDA(cudaMemsetAsync(counts, 0, size_t(opt.experts) * sizeof(int), stream));
         moe_topk_kernel<<<(tokens * 32 + 255) / 256, 256, 0, stream>>>(logits, selected, probs, tokens, opt.experts,
-                                                                     opt.top_k);
+                                                                     opt.top_k, counts, shard());
+    }
     GB_CUDA(cudaGetLastError());
     return GARNET_B200_OK;
 }
@@ -1230,13 +1236,14 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     const MoeShard sh = shard();
     const bool small = tokens <= 8 && opt.experts <= 256;
     const int tile_rows = use_mx(slots) ? moe_mx_plan(opt, tokens, slots).nt : 0;
-    if (int rc = route(x, w.logits, w.selected, w.probs, w.xh, w.xshift, tokens, stream, small, w.route_partial)) return rc;
+    if (int rc = route(x, w.logits, w.selected, w.probs, w.xh, w.xshift, tokens, stream, small, w.route_partial, w.counts))
+        return rc;
     if (small) {
         GB_CUDA(launch_pdl(moe_small_meta_kernel, dim3(1), dim3(256), 0, stream, true, w.logits, w.selected, w.probs,
                            w.counts, w.offsets, w.sorted, w.tasks, w.ntasks, tokens, opt.experts, opt.top_k, kMoeRows,
                            sh, tile_rows, w.mx_tp));
     } else {
-        moe_count_kernel<<<opt.experts, 256, 0, stream>>>(w.selected, slots, w.counts, sh);
+        // the counts come from the top-k kernel
         moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(w.selected, slots, w.counts, w.offsets, w.sorted, w.tasks,
                                                          w.ntasks, opt.experts, kMoeRows, sh, tile_rows, w.mx_tp);
     }

@@ -101,7 +101,7 @@ struct Moe {
     int local_experts() const;
     int prepare(const void* const* weights, cudaStream_t stream);
     int route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
-              cudaStream_t stream, bool skip_topk = false, float* route_partial = nullptr);
+              cudaStream_t stream, bool skip_topk = false, float* route_partial = nullptr, int* counts = nullptr);
     int launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream, int topk = -1);
     int run_rows(const void* x_rows, const int* row_expert, int rows, float* vals, void* ws, size_t ws_bytes,
                  cudaStream_t stream);

@@ -71,22 +71,47 @@ moe_route_mma_kernel(const XT* __restrict__ x, const __nv_bfloat16* __restrict__
 
     const int slabs = hidden / kRmSlab;
     const int k_begin = int(blockIdx.z) * slabs / kRmSplit * kRmSlab, k_end = int(blockIdx.z + 1) * slabs / kRmSplit * kRmSlab;
-    for (int k0 = k_begin; k0 < k_end; k0 += kRmSlab) {
-        __syncthreads();
-        // stage 64 tokens x 64 columns of x (as bf16) and 3 x 64 experts x 64 columns of the split weight
-        for (int i = threadIdx.x; i < kRmTokens * (kRmSlab / 2); i += 128) {
+    // The next slab's global loads are issued into registers before the current slab's
+    // MMAs, so that their latency is covered by the math.
+    constexpr int kXPer = kRmTokens * (kRmSlab / 2) / 128;          // 16 words of x per thread
+    constexpr int kWPer = 3 * kRmExperts * (kRmSlab / 8) / 128;     // 12 x 16 bytes of W per thread
+    uint32_t xr[kXPer];
+    uint4 wr[kWPer];
+    auto load_slab = [&](int k0) {
+#pragma unroll
+        for (int j = 0; j < kXPer; ++j) {
+            const int i = threadIdx.x + j * 128;
             const int r = i / (kRmSlab / 2), c = (i % (kRmSlab / 2)) * 2;
-            uint32_t v = 0;
-            if (t0 + r < tokens) v = rm_pack2<XT>(x + size_t(t0 + r) * hidden + k0 + c);
-            *reinterpret_cast<uint32_t*>(&xs[r * kRmStride + c]) = v;
+            xr[j] = (t0 + r < tokens) ? rm_pack2<XT>(x + size_t(t0 + r) * hidden + k0 + c) : 0u;
         }
-        for (int i = threadIdx.x; i < 3 * kRmExperts * (kRmSlab / 8); i += 128) {
+#pragma unroll
+        for (int j = 0; j < kWPer; ++j) {
+            const int i = threadIdx.x + j * 128;
             const int c = (i % (kRmSlab / 8)) * 8, r = (i / (kRmSlab / 8)) % kRmExperts, s = i / ((kRmSlab / 8) * kRmExperts);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (e0 + r < experts) v = *reinterpret_cast<const uint4*>(w3 + s * wcount + size_t(e0 + r) * hidden + k0 + c);
-            *reinterpret_cast<uint4*>(&ws[(s * kRmExperts + r) * kRmStride + c]) = v;
+            wr[j] = (e0 + r < experts) ? *reinterpret_cast<const uint4*>(w3 + s * wcount + size_t(e0 + r) * hidden + k0 + c)
+                                       : make_uint4(0, 0, 0, 0);
         }
+    };
+    auto store_slab = [&]() {
+#pragma unroll
+        for (int j = 0; j < kXPer; ++j) {
+            const int i = threadIdx.x + j * 128;
+            const int r = i / (kRmSlab / 2), c = (i % (kRmSlab / 2)) * 2;
+            *reinterpret_cast<uint32_t*>(&xs[r * kRmStride + c]) = xr[j];
+        }
+#pragma unroll
+        for (int j = 0; j < kWPer; ++j) {
+            const int i = threadIdx.x + j * 128;
+            const int c = (i % (kRmSlab / 8)) * 8, r = (i / (kRmSlab / 8)) % kRmExperts, s = i / ((kRmSlab / 8) * kRmExperts);
+            *reinterpret_cast<uint4*>(&ws[(s * kRmExperts + r) * kRmStride + c]) = wr[j];
+        }
+    };
+    if (k_begin < k_end) load_slab(k_begin);
+    for (int k0 = k_begin; k0 < k_end; k0 += kRmSlab) {
+        __syncthreads();      // the previous slab's MMAs have read the staging buffers
+        store_slab();
         __syncthreads();
+        if (k0 + kRmSlab < k_end) load_slab(k0 + kRmSlab);
 #pragma unroll
         for (int kk = 0; kk < kRmSlab; kk += 16) {
             const __nv_bfloat16* xa = xs + (warp * 16 + g) * kRmStride + kk + 2 * t;
