@@ -40,6 +40,11 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_w4a16_run.argtypes = [vp, vp, vp, i, vp, sz, u, vp]
     L.garnet_b200_w4a16_run_group.argtypes = [vp, i, vp, vp, i, u, vp]
     L.garnet_b200_w4a16_run_host.argtypes = [vp, vp, vp, i, vp]
+    L.garnet_b200_w4a16_run_host_async.argtypes = [vp, vp, vp, i, vp]
+    L.garnet_b200_w4a16_batch_create.argtypes = [vp, vp, vp, vp, i, vp]
+    L.garnet_b200_w4a16_batch_run.argtypes = [vp, vp]
+    L.garnet_b200_w4a16_batch_destroy.argtypes = [vp]
+    L.garnet_b200_w4a16_batch_destroy.restype = None
     L.garnet_b200_w4a16_dequant.argtypes = [vp, vp, vp]
     L.garnet_b200_w4a16_fault.argtypes = [vp]
     L.garnet_b200_w4a16_destroy.argtypes = [vp]

@@ -7,6 +7,8 @@
 // group scale is applied to that partial sum in fp32, so no product is rounded
 // before the final bf16 store.
 #include <algorithm>
+#include <memory>
+#include <vector>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -637,6 +639,60 @@ int w4a16_repack_device(const uint8_t* d_nibbles, const uint16_t* d_scales, cons
     return GARNET_B200_OK;
 }
 
+// ---------------------------------------------------------- host-buffer batches
+
+struct ScatterEntry {
+    const uint8_t* src;   // device staging of one linear's output
+    uint8_t* dst;         // device alias of the caller's pinned host buffer
+    size_t bytes;
+};
+
+// Copies every entry's output to its host buffer: one launch at the end of a batch
+// instead of one copy (or one flush of host-memory writes) per linear.
+__global__ void w4_scatter_outputs_kernel(const ScatterEntry* __restrict__ table, int count)
+{
+    pdl_wait();
+    for (int e = blockIdx.y; e < count; e += gridDim.y) {
+        const ScatterEntry t = table[e];
+        const size_t start = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * 16, step = size_t(gridDim.x) * blockDim.x * 16;
+        if (((reinterpret_cast<uintptr_t>(t.src) | reinterpret_cast<uintptr_t>(t.dst)) & 15) == 0) {
+            for (size_t o = start; o + 16 <= t.bytes; o += step)
+                *reinterpret_cast<uint4*>(t.dst + o) = *reinterpret_cast<const uint4*>(t.src + o);
+            if (blockIdx.x == 0 && threadIdx.x < (t.bytes & 15)) t.dst[(t.bytes & ~size_t(15)) + threadIdx.x] = t.src[(t.bytes & ~size_t(15)) + threadIdx.x];
+        } else {
+            for (size_t o = start / 16; o < t.bytes; o += step / 16) t.dst[o] = t.src[o];
+        }
+    }
+}
+
+struct HostBatch {
+    struct Call {
+        W4A16* h;
+        const void* h_x;
+        void* h_y;
+        int m;
+        int x_slot;          // index into xs
+        size_t y_off;        // offset of this call's output in y_stage
+        void* y_alias;       // device alias of h_y, or nullptr (pageable: copied with cudaMemcpyAsync)
+    };
+    struct X {
+        const void* host;
+        size_t bytes, off;
+    };
+    std::vector<Call> calls;
+    std::vector<X> xs;
+    uint8_t* x_stage = nullptr;
+    uint8_t* y_stage = nullptr;
+    ScatterEntry* table = nullptr;
+    int table_count = 0;
+    ~HostBatch()
+    {
+        if (x_stage) cudaFree(x_stage);
+        if (y_stage) cudaFree(y_stage);
+        if (table) cudaFree(table);
+    }
+};
+
 }  // namespace gb200
 
 using namespace gb200;
@@ -830,11 +886,21 @@ int garnet_b200_w4a16_run_group(const garnet_b200_w4a16_t* handles, int count, c
     return W4A16::launch_stream_group(hs, count, static_cast<const __nv_bfloat16*>(d_x), ys, ldys, m, flags, s);
 }
 
-int garnet_b200_w4a16_run_host(garnet_b200_w4a16_t hh, const void* h_x, void* h_y, int m, void* stream)
+// Device-visible alias of a host pointer (pinned and mapped memory), or nullptr.
+static void* device_alias_of(const void* host_ptr)
 {
-    W4A16* h = reinterpret_cast<W4A16*>(hh);
-    if (!h || !h_x || !h_y || m <= 0) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run_host: bad argument");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host_ptr) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+}
+
+// One linear with host buffers, enqueued on `s`.  `d_x_shared`: a device copy of h_x made
+// by an earlier call of the same batch (then no copy is enqueued), or nullptr.
+static int run_host_one(W4A16* h, const void* h_x, const void* d_x_shared, void* h_y, int m, cudaStream_t s)
+{
     const size_t xb = size_t(m) * h->geo.cols * 2, yb = size_t(m) * h->geo.rows * 2, wb = h->workspace_bytes(m);
     if (m > h->stage_rows) {
         if (h->stage_x) cudaFree(h->stage_x);
@@ -847,10 +913,100 @@ int garnet_b200_w4a16_run_host(garnet_b200_w4a16_t hh, const void* h_x, void* h_
         if (wb) GB_CUDA(cudaMalloc(&h->stage_ws, wb));
         h->stage_rows = m;
     }
-    GB_CUDA(cudaMemcpyAsync(h->stage_x, h_x, xb, cudaMemcpyHostToDevice, s));
-    if (int rc = h->run(h->stage_x, h->stage_y, m, h->stage_ws, wb, 0, s)) return rc;
-    GB_CUDA(cudaMemcpyAsync(h_y, h->stage_y, yb, cudaMemcpyDeviceToHost, s));
-    GB_CUDA(cudaStreamSynchronize(s));
+    // y in pinned, mapped host memory is written by the kernel itself (one posted write per
+    // output over the host link, no copy to enqueue); any other y goes through a staged copy.
+    if (h_y != h->last_host_y) {
+        h->last_host_y = h_y;
+        h->last_host_y_alias = device_alias_of(h_y);
+    }
+    if (!d_x_shared) GB_CUDA(cudaMemcpyAsync(h->stage_x, h_x, xb, cudaMemcpyHostToDevice, s));
+    void* y_dev = h->last_host_y_alias ? h->last_host_y_alias : h->stage_y;
+    if (int rc = h->run(d_x_shared ? d_x_shared : h->stage_x, y_dev, m, h->stage_ws, wb, 0, s)) return rc;
+    if (!h->last_host_y_alias) GB_CUDA(cudaMemcpyAsync(h_y, h->stage_y, yb, cudaMemcpyDeviceToHost, s));
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_run_host_async(garnet_b200_w4a16_t hh, const void* h_x, void* h_y, int m, void* stream)
+{
+    W4A16* h = reinterpret_cast<W4A16*>(hh);
+    if (!h || !h_x || !h_y || m <= 0) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run_host: bad argument");
+    return run_host_one(h, h_x, nullptr, h_y, m, static_cast<cudaStream_t>(stream));
+}
+
+int garnet_b200_w4a16_batch_create(const garnet_b200_w4a16_t* handles, const void* const* h_xs, void* const* h_ys,
+                                   const int* ms, int count, garnet_b200_w4a16_batch_t* out)
+{
+    if (!handles || !h_xs || !h_ys || !ms || !out || count <= 0)
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_batch_create: bad argument");
+    std::unique_ptr<HostBatch> b(new HostBatch);
+    size_t x_total = 0, y_total = 0;
+    for (int i = 0; i < count; ++i) {
+        W4A16* h = reinterpret_cast<W4A16*>(handles[i]);
+        if (!h || !h_xs[i] || !h_ys[i] || ms[i] <= 0)
+            return fail(GARNET_B200_INVALID_VALUE, "w4a16_batch_create: bad argument at index %d", i);
+        if (h->workspace_bytes(ms[i])) return fail(GARNET_B200_NOT_SUPPORTED, "w4a16_batch_create: linear needs a workspace");
+        const size_t xb = size_t(ms[i]) * h->geo.cols * 2, yb = size_t(ms[i]) * h->geo.rows * 2;
+        // inputs are read-only during a run: every distinct host buffer is copied once
+        int slot = -1;
+        for (size_t q = 0; q < b->xs.size(); ++q)
+            if (b->xs[q].host == h_xs[i] && b->xs[q].bytes == xb) slot = int(q);
+        if (slot < 0) {
+            slot = int(b->xs.size());
+            b->xs.push_back({h_xs[i], xb, x_total});
+            x_total += (xb + 255) & ~size_t(255);
+        }
+        b->calls.push_back({h, h_xs[i], h_ys[i], ms[i], slot, y_total, device_alias_of(h_ys[i])});
+        y_total += (yb + 255) & ~size_t(255);
+    }
+    GB_CUDA(cudaMalloc(&b->x_stage, x_total));
+    GB_CUDA(cudaMalloc(&b->y_stage, y_total));
+    std::vector<ScatterEntry> table;
+    for (const HostBatch::Call& c : b->calls)
+        if (c.y_alias)
+            table.push_back({b->y_stage + c.y_off, static_cast<uint8_t*>(c.y_alias), size_t(c.m) * c.h->geo.rows * 2});
+    b->table_count = int(table.size());
+    if (b->table_count) {
+        GB_CUDA(cudaMalloc(&b->table, table.size() * sizeof(ScatterEntry)));
+        GB_CUDA(cudaMemcpy(b->table, table.data(), table.size() * sizeof(ScatterEntry), cudaMemcpyHostToDevice));
+    }
+    *out = reinterpret_cast<garnet_b200_w4a16_batch_t>(b.release());
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_batch_run(garnet_b200_w4a16_batch_t bb, void* stream)
+{
+    HostBatch* b = reinterpret_cast<HostBatch*>(bb);
+    if (!b) return fail(GARNET_B200_INVALID_VALUE, "w4a16_batch_run: null batch");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    for (const HostBatch::X& x : b->xs)
+        GB_CUDA(cudaMemcpyAsync(b->x_stage + x.off, x.host, x.bytes, cudaMemcpyHostToDevice, s));
+    for (const HostBatch::Call& c : b->calls)
+        if (int rc = c.h->run(b->x_stage + b->xs[c.x_slot].off, b->y_stage + c.y_off, c.m, nullptr, 0, 1, s)) return rc;
+    if (b->table_count) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(8, unsigned(std::min(b->table_count, 1024)));
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        GB_CUDA(cudaLaunchKernelEx(&cfg, w4_scatter_outputs_kernel, (const ScatterEntry*)b->table, b->table_count));
+    }
+    for (const HostBatch::Call& c : b->calls)
+        if (!c.y_alias)
+            GB_CUDA(cudaMemcpyAsync(c.h_y, b->y_stage + c.y_off, size_t(c.m) * c.h->geo.rows * 2, cudaMemcpyDeviceToHost, s));
+    return GARNET_B200_OK;
+}
+
+void garnet_b200_w4a16_batch_destroy(garnet_b200_w4a16_batch_t bb) { delete reinterpret_cast<HostBatch*>(bb); }
+
+int garnet_b200_w4a16_run_host(garnet_b200_w4a16_t hh, const void* h_x, void* h_y, int m, void* stream)
+{
+    if (int rc = garnet_b200_w4a16_run_host_async(hh, h_x, h_y, m, stream)) return rc;
+    W4A16* h = reinterpret_cast<W4A16*>(hh);
+    GB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
     if (*h->fault_host) return fail(GARNET_B200_DEVICE_FAULT, "w4a16: device wait gave up (code %d)", *h->fault_host);
     return GARNET_B200_OK;
 }

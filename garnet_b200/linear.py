@@ -66,6 +66,35 @@ def forward_group(linears, x: torch.Tensor, outs=None, pdl: bool = True):
     return outs
 
 
+class HostBatch:
+    """A prepared list of (linear, host x, host y) calls (garnet_b200_w4a16_batch_*); after
+    `run` the outputs are complete once the current stream has been synchronised."""
+
+    def __init__(self, calls):
+        self._keep = list(calls)
+        n = len(self._keep)
+        hs = (ctypes.c_void_p * n)(*[lin._h for lin, _, _ in self._keep])
+        xs = (ctypes.c_void_p * n)(*[x.data_ptr() for _, x, _ in self._keep])
+        ys = (ctypes.c_void_p * n)(*[y.data_ptr() for _, _, y in self._keep])
+        ms = (ctypes.c_int * n)(*[x.numel() // lin.k for lin, x, _ in self._keep])
+        self._b = ctypes.c_void_p(None)
+        check(lib().garnet_b200_w4a16_batch_create(hs, xs, ys, ms, n, ctypes.byref(self._b)))
+
+    def run(self) -> None:
+        check(lib().garnet_b200_w4a16_batch_run(self._b, _stream_ptr()))
+
+    def close(self) -> None:
+        if self._b:
+            lib().garnet_b200_w4a16_batch_destroy(self._b)
+            self._b = ctypes.c_void_p(None)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class W4A16Linear:
     """y[M, N] = x[M, K] W^T, W int4 with one scale per (row, `group` columns)."""
 
@@ -129,6 +158,13 @@ class W4A16Linear:
         """Host buffers in, host buffers out (copies inside the call)."""
         m = x_host.numel() // self.k
         check(lib().garnet_b200_w4a16_run_host(self._h, x_host.data_ptr(), y_host.data_ptr(), m, _stream_ptr()))
+        return y_host
+
+    def forward_host_async(self, x_host: torch.Tensor, y_host: torch.Tensor) -> torch.Tensor:
+        """`forward_host` without the final synchronisation: y_host is complete once the
+        current stream has been synchronised."""
+        m = x_host.numel() // self.k
+        check(lib().garnet_b200_w4a16_run_host_async(self._h, x_host.data_ptr(), y_host.data_ptr(), m, _stream_ptr()))
         return y_host
 
     def dequantized(self) -> torch.Tensor:

@@ -123,6 +123,26 @@ int garnet_b200_w4a16_run_group(const garnet_b200_w4a16_t* handles, int count, c
  * copy, kernel, device -> host copy on `stream`, then a stream synchronise).
  * Staging buffers belong to the handle and grow on first use. */
 int garnet_b200_w4a16_run_host(garnet_b200_w4a16_t h, const void* h_x, void* h_y, int m, void* stream);
+/* The same call without the final synchronisation: x is copied in and the kernel is
+ * enqueued on `stream`; y is complete once the stream has been synchronised.  When
+ * h_y is pinned, mapped host memory the kernel writes it directly, otherwise a copy
+ * is enqueued behind the kernel.  (Q4Q8Linear::Forward, q4q8_linear.cpp:315-389, is
+ * synchronous; a caller that issues a whole decode pass synchronises once.) */
+int garnet_b200_w4a16_run_host_async(garnet_b200_w4a16_t h, const void* h_x, void* h_y, int m, void* stream);
+/* A prepared list of host-buffer calls (a whole decode pass, say): linear i reads
+ * h_xs[i] ([ms[i], K_i] bf16) and writes h_ys[i].  `batch_run` copies every distinct
+ * input buffer to the device once, launches the linears back to back (programmatic
+ * dependent launches), and writes all outputs to their host buffers with one kernel
+ * (pinned, mapped buffers) or one copy each (pageable buffers); the outputs are
+ * complete once `stream` has been synchronised.  The reference's CPU backend calls
+ * Q4Q8Linear::Forward once per operator (q4q8_linear.cpp:315-389); this is the same
+ * list of calls handed over at once.  create/destroy allocate and free device memory;
+ * run does not. */
+typedef struct garnet_b200_w4a16_batch_s* garnet_b200_w4a16_batch_t;
+int garnet_b200_w4a16_batch_create(const garnet_b200_w4a16_t* handles, const void* const* h_xs, void* const* h_ys,
+                                   const int* ms, int count, garnet_b200_w4a16_batch_t* out);
+int garnet_b200_w4a16_batch_run(garnet_b200_w4a16_batch_t batch, void* stream);
+void garnet_b200_w4a16_batch_destroy(garnet_b200_w4a16_batch_t batch);
 
 /* Writes the dequantised weights q*s as fp32 [n_local, k], reading the packed
  * tiles with the same device decode the GEMM kernels use (bit-exactness check;

@@ -191,7 +191,31 @@ def test_host_buffer_entry_point():
     xh = torch.from_numpy(case["x_bits"].view(np.int16)).view(torch.bfloat16).reshape(m, k).pin_memory()
     yh = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
     lin.forward_host(xh, yh)
-    assert torch.equal(yh, lin.forward(xh.cuda()).cpu())
+    expected = lin.forward(xh.cuda()).cpu()
+    assert torch.equal(yh, expected)
+    # pageable (not pinned) output: the staged-copy route
+    y_pageable = torch.empty(m, n, dtype=torch.bfloat16)
+    lin.forward_host(xh, y_pageable)
+    assert torch.equal(y_pageable, expected)
+    # asynchronous form: complete after the stream is synchronised; batch above 16 (tile kernel)
+    m2 = 40
+    case2 = synth.int4_linear(n, k, m2, seed=22)
+    xh2 = torch.from_numpy(case2["x_bits"].view(np.int16)).view(torch.bfloat16).reshape(m2, k).pin_memory()
+    yh2 = torch.zeros(m2, n, dtype=torch.bfloat16).pin_memory()
+    lin.forward_host_async(xh2, yh2)
+    torch.cuda.synchronize()
+    assert torch.equal(yh2, lin.forward(xh2.cuda()).cpu())
+    # batched form: two linears reading the same host buffer, then one reading another
+    case3 = synth.int4_linear(1024, k, m, seed=23)
+    lin3 = make_linear(case3, 1024, k)
+    ya = torch.zeros(m, n, dtype=torch.bfloat16).pin_memory()
+    yb = torch.zeros(m, 1024, dtype=torch.bfloat16).pin_memory()
+    yc = torch.zeros(m2, n, dtype=torch.bfloat16).pin_memory()
+    garnet_b200.HostBatch([(lin, xh, ya), (lin3, xh, yb), (lin, xh2, yc)]).run()
+    torch.cuda.synchronize()
+    assert torch.equal(ya, expected)
+    assert torch.equal(yb, lin3.forward(xh.cuda()).cpu())
+    assert torch.equal(yc, yh2)
 
 
 def test_run_rejects_bad_arguments():
