@@ -176,7 +176,15 @@ moe_mxr_kernel(const RxParams p, const __grid_constant__ CUtensorMap w_map, cons
         // ---------------------------------------------------------- MMA issuer
         if (lane == 0) {
             uint32_t n = 0, it_n = 0;
+            // The issuing thread shares its scheduler with two epilogue warps, so its loop is
+            // kept to a few instructions per MMA: every descriptor is the stage-0 descriptor
+            // plus a stage offset and a K-block offset in the start-address field (16-byte
+            // units), and the four instruction descriptors differ only in the scale selectors.
             const uint32_t ring_addr = smem_u32(ring);
+            const uint64_t hi_d0 = umma_desc_k_sw128(ring_addr), lo_d0 = umma_desc_k_sw128(ring_addr + kRxATile),
+                           w_d0 = umma_desc_k_sw128(ring_addr + 2 * kRxATile);
+            const uint64_t sfx_d0 = umma_desc_k_plain(ring_addr + 2 * kRxATile + kRxBTile, 128);
+            constexpr uint32_t kStageUnits = kRxStageBytes >> 4, kAtomUnits = kMxAtom >> 4;
             // A = e4m3 pieces (rows), B = e2m1 weights
             const uint32_t idesc0 = mx_idesc_fmt(kMxFmtE4M3, kMxFmtE2M1, kRxRows, kRxN, 0);
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
@@ -195,13 +203,11 @@ moe_mxr_kernel(const RxParams p, const __grid_constant__ CUtensorMap w_map, cons
                         *abort_flag = 1;
                         break;
                     }
-                    const uint32_t st = ring_addr + s * kRxStageBytes;
-                    const uint64_t hi_d = umma_desc_k_sw128(st), lo_d = umma_desc_k_sw128(st + kRxATile),
-                                   w_d = umma_desc_k_sw128(st + 2 * kRxATile);
-                    const uint32_t sf_addr = st + 2 * kRxATile + kRxBTile;
-                    tmem_cp_32x128b_warpx4(tmem_sfx, umma_desc_k_plain(sf_addr, 128));
-                    tmem_cp_32x128b_warpx4(tmem_sfw, umma_desc_k_plain(sf_addr + kMxAtom, 128));
-                    tmem_cp_32x128b_warpx4(tmem_sfw + 4, umma_desc_k_plain(sf_addr + 2 * kMxAtom, 128));
+                    const uint64_t off = uint64_t(s * kStageUnits);
+                    const uint64_t hi_d = hi_d0 + off, lo_d = lo_d0 + off, w_d = w_d0 + off, sf_d = sfx_d0 + off;
+                    tmem_cp_32x128b_warpx4(tmem_sfx, sf_d);
+                    tmem_cp_32x128b_warpx4(tmem_sfw, sf_d + kAtomUnits);
+                    tmem_cp_32x128b_warpx4(tmem_sfw + 4, sf_d + 2 * kAtomUnits);
 #pragma unroll
                     for (uint32_t kb = 0; kb < 4; ++kb) {
                         const uint32_t idesc = idesc0 + kb * ((1u << 4) | (1u << 29));
