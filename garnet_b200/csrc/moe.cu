@@ -917,7 +917,7 @@ MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens)
     const int mx_world = o.ep_world > 1 ? o.ep_world : 1;
     const int mx_local = mx_world <= 1 ? o.experts   // the same count as Moe::local_experts()
                          : o.ep_interleaved ? (o.experts - o.ep_rank + mx_world - 1) / mx_world : o.experts / mx_world;
-    const bool mx = moe_mx_enabled() && (moe_mx_forced() || slots > size_t(8) * mx_local);
+    const bool mx = moe_mx_enabled() && (moe_mx_forced() || slots > size_t(6) * mx_local);
     const MoeMxPlan mxp = moe_mx_plan(o, tokens, int(slots));
     w.mx_tp = take(mx ? size_t(o.experts + 1) * 4 : 0);
     w.mx_q = take(mx ? mxp.q_bytes : 0);

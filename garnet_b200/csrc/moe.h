@@ -118,9 +118,9 @@ struct Moe {
     int launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_sorted, int tokens, int slots, int topk,
                   cudaStream_t stream);
     // The block-scaled path pays off once experts get several rows each (measured
-    // crossover on the gpt-oss-120b layer: about 8 rows per expert); below that the
+    // crossover on the gpt-oss-120b layer: about 6 rows per expert); below that the
     // streaming kernel moves the weights faster.
-    bool use_mx(int slots) const { return mx_ok && moe_mx_enabled() && (moe_mx_forced() || slots > 8 * local_experts()); }
+    bool use_mx(int slots) const { return mx_ok && moe_mx_enabled() && (moe_mx_forced() || slots > 6 * local_experts()); }
     int init_route_mma(cudaStream_t stream);
     int route_mma(const void* x, float* logits, float* partial, int tokens, cudaStream_t stream);
     int combine(const float* vals, const float* probs, void* y, int tokens, cudaStream_t stream);
