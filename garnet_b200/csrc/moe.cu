@@ -1326,7 +1326,9 @@ int Moe::run_rows(const void* x_rows, const int* row_expert, int rows, float* va
     MoeWorkspacePtrs w = bind_workspace(ws, plan);
     w.vals = vals;
     const unsigned blocks = unsigned((size_t(rows) * 32 + 255) / 256);
-    if (opt.io_dtype == GARNET_B200_FP32)
+    if (use_mx(rows)) {
+        // the block-scaled path quantises the rows itself and does not read the fp16 copies
+    } else if (opt.io_dtype == GARNET_B200_FP32)
         moe_prep_rows_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x_rows), w.xh, w.xshift, rows, opt.hidden);
     else
         moe_prep_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x_rows), w.xh, w.xshift, rows, opt.hidden);
