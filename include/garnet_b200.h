@@ -199,8 +199,12 @@ int garnet_b200_moe_workspace(const garnet_b200_moe_options* options, int tokens
  * gate_up blocks u8 [E,2I,H/32,16], gate_up scales u8 [E,2I,H/32], gate_up bias
  * [E,2I] f32, down blocks [E,H,I/32,16], down scales [E,H,I/32], down bias [E,H]
  * f32.  Expert blocks and scales are repacked into handle-owned memory (one
- * stream synchronise); router weights and biases are borrowed and must outlive
- * the handle.  GptOssMarlin constructor + first-run prepare
+ * stream synchronise), once in the layout of the streaming kernels (few rows per
+ * expert) and once as the blocks and scale atoms of the block-scaled tensor-core
+ * kernels (many rows per expert), so a handle holds about twice the size of the
+ * expert tensors; router weights and biases are borrowed and must outlive the
+ * handle (the router weight is also kept as three bf16 terms for the tensor-core
+ * router).  GptOssMarlin constructor + first-run prepare
  * (plugins/gpt_oss/cuda/gpt_oss_marlin.cu:415-499). */
 int garnet_b200_moe_create(const garnet_b200_moe_options* options, const void* const* weights, void* stream,
                            garnet_b200_moe_t* out);
