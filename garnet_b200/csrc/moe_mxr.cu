@@ -135,8 +135,17 @@ moe_mxr_kernel(const RxParams p, const __grid_constant__ CUtensorMap w_map, cons
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            uint32_t n = 0, pf_n = 0;
+            // One thread feeds the whole pipeline, so its loop carries no divisions: the stage
+            // index, its parity and the prefetch cursor advance by increments.
+            uint32_t s = 0, round = 0;          // stage and how many times the ring has wrapped
+            uint32_t issued = 0, prefetched = 0;
             int cur = 0, pf_cur = 0;
+            int pf_item = blockIdx.x, pf_ks = 0;
+            const uint8_t* pf_base = nullptr;
+            if (pf_item < items) {
+                const RxItem pi = rx_decode(p, tile_prefix, pf_item, pf_cur);
+                pf_base = p.w + (size_t((pi.expert - p.expert_base) / p.expert_div) * p.ntiles + pi.ntile) * p.kslabs * kRxPkBytes;
+            }
             constexpr uint32_t tx = kRxPkBytes + 2 * kRxATile + 3 * kMxAtom;   // the 4-bit TMA counts packed bytes
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
                 const RxItem it = rx_decode(p, tile_prefix, item, cur);
@@ -144,19 +153,25 @@ moe_mxr_kernel(const RxParams p, const __grid_constant__ CUtensorMap w_map, cons
                 const size_t wblock = (size_t(se) * p.ntiles + it.ntile) * p.kslabs;
                 const uint8_t* sfw = p.sfw + wblock * (2 * kMxAtom);
                 const uint8_t* sfx = p.sfx + size_t(it.tile) * p.kslabs * kMxAtom;
-                for (int ks = 0; ks < p.kslabs; ++ks, ++n) {
+                int wrow = int(wblock * kRxN);
+                const int arow = it.tile * kRxRows;
+                for (int ks = 0; ks < p.kslabs; ++ks, ++issued) {
                     // ask L2 for the weight blocks a few stages ahead (also across the item boundary)
-                    while (pf_n < n + kRxPrefetch) {
-                        const int pf_item = blockIdx.x + int(pf_n / uint32_t(p.kslabs)) * gridDim.x;
-                        if (pf_item >= items) break;
-                        const RxItem pi = rx_decode(p, tile_prefix, pf_item, pf_cur);
-                        const int pse = (pi.expert - p.expert_base) / p.expert_div;
-                        bulk_prefetch_l2(p.w + ((size_t(pse) * p.ntiles + pi.ntile) * p.kslabs + pf_n % uint32_t(p.kslabs)) * kRxPkBytes,
-                                         kRxPkBytes);
-                        ++pf_n;
+                    while (pf_base && prefetched < issued + kRxPrefetch) {
+                        bulk_prefetch_l2(pf_base + size_t(pf_ks) * kRxPkBytes, kRxPkBytes);
+                        ++prefetched;
+                        if (++pf_ks == p.kslabs) {
+                            pf_ks = 0;
+                            pf_item += gridDim.x;
+                            pf_base = nullptr;
+                            if (pf_item < items) {
+                                const RxItem pi = rx_decode(p, tile_prefix, pf_item, pf_cur);
+                                pf_base = p.w + (size_t((pi.expert - p.expert_base) / p.expert_div) * p.ntiles + pi.ntile) *
+                                                    p.kslabs * kRxPkBytes;
+                            }
+                        }
                     }
-                    const uint32_t s = n % kRxStages;
-                    if (n >= kRxStages && !mbar_wait_bounded(&empty[s], ((n / kRxStages) - 1) & 1)) {
+                    if (round > 0 && !mbar_wait_bounded(&empty[s], (round - 1) & 1)) {
                         atomicExch(p.fault, 41);
                         *abort_flag = 1;
                         break;
@@ -164,18 +179,25 @@ moe_mxr_kernel(const RxParams p, const __grid_constant__ CUtensorMap w_map, cons
                     uint8_t* st = ring + s * kRxStageBytes;
                     uint8_t* sf_s = st + 2 * kRxATile + kRxBTile;
                     mbar_expect_tx(&full[s], tx);
-                    tma_load_2d(st + 2 * kRxATile, &w_map, 0, int((wblock + ks) * kRxN), &full[s]);
-                    tma_load_2d(st, &q_map, ks * kMxSlab, it.tile * kRxRows, &full[s]);
-                    tma_load_2d(st + kRxATile, &q_map, ks * kMxSlab, q_rows + it.tile * kRxRows, &full[s]);
-                    bulk_g2s(sf_s, sfx + size_t(ks) * kMxAtom, kMxAtom, &full[s]);
-                    bulk_g2s(sf_s + kMxAtom, sfw + size_t(ks) * (2 * kMxAtom), 2 * kMxAtom, &full[s]);
+                    tma_load_2d(st + 2 * kRxATile, &w_map, 0, wrow, &full[s]);
+                    tma_load_2d(st, &q_map, ks * kMxSlab, arow, &full[s]);
+                    tma_load_2d(st + kRxATile, &q_map, ks * kMxSlab, q_rows + arow, &full[s]);
+                    bulk_g2s(sf_s, sfx, kMxAtom, &full[s]);
+                    bulk_g2s(sf_s + kMxAtom, sfw, 2 * kMxAtom, &full[s]);
+                    wrow += kRxN;
+                    sfx += kMxAtom;
+                    sfw += 2 * kMxAtom;
+                    if (++s == kRxStages) {
+                        s = 0;
+                        ++round;
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            uint32_t n = 0, it_n = 0;
+            uint32_t s = 0, phase = 0, it_n = 0;
             // The issuing thread shares its scheduler with two epilogue warps, so its loop is
             // kept to a few instructions per MMA: every descriptor is the stage-0 descriptor
             // plus a stage offset and a K-block offset in the start-address field (16-byte
@@ -196,9 +218,8 @@ moe_mxr_kernel(const RxParams p, const __grid_constant__ CUtensorMap w_map, cons
                 }
                 tc_fence_after();
                 const uint32_t d_addr = tmem_base + buf * kRxN;
-                for (int ks = 0; ks < p.kslabs; ++ks, ++n) {
-                    const uint32_t s = n % kRxStages;
-                    if (!mbar_wait_bounded(&full[s], (n / kRxStages) & 1)) {
+                for (int ks = 0; ks < p.kslabs; ++ks) {
+                    if (!mbar_wait_bounded(&full[s], phase)) {
                         atomicExch(p.fault, 43);
                         *abort_flag = 1;
                         break;
@@ -215,6 +236,10 @@ moe_mxr_kernel(const RxParams p, const __grid_constant__ CUtensorMap w_map, cons
                         umma_mx(d_addr, lo_d + 2 * kb, w_d + 2 * kb, idesc, tmem_sfx, tmem_sfw, true);
                     }
                     umma_commit(&empty[s]);
+                    if (++s == kRxStages) {
+                        s = 0;
+                        phase ^= 1;
+                    }
                 }
                 if (*abort_flag) break;
                 umma_commit(&acc_full[buf]);
