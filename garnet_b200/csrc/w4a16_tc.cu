@@ -165,21 +165,26 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
         // Weights are constants: this stream starts before the previous kernel in the
         // stream has finished, and runs as far ahead as its ring allows.
         if (lane == 0) {
-            uint32_t pk_n = 0, pf_n = 0;   // chunks issued to the ring / prefetched into L2, in this CTA's order
+            // One thread feeds the ring, so its loop carries no divisions: the stage index, the
+            // ring's wrap count and the prefetch cursor advance by increments.
+            uint32_t ps = 0, round = 0, issued = 0, prefetched = 0;
+            int pf_item = blockIdx.x, pf_c = 0;
+            int pf_strip0 = pf_item < items ? (pf_item / p.token_tiles) * kStripsPerPanel : 0;
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
                 const int panel = item / p.token_tiles;
                 const int strip0 = panel * kStripsPerPanel;
-                for (int c = 0; c < p.chunks; ++c) {
+                for (int c = 0; c < p.chunks; ++c, ++issued) {
                     // keep the L2 prefetch kTcPrefetchChunks ahead of the ring, across items
-                    while (pf_n < pk_n + kTcPrefetchChunks) {
-                        const int pf_item = blockIdx.x + int(pf_n / p.chunks) * gridDim.x;
-                        if (pf_item >= items) break;
-                        tma_prefetch_2d(&w_map, int(pf_n % p.chunks) * (kTcChunkBytes / 8),
-                                        (pf_item / p.token_tiles) * kStripsPerPanel);
-                        ++pf_n;
+                    while (pf_item < items && prefetched < issued + kTcPrefetchChunks) {
+                        tma_prefetch_2d(&w_map, pf_c * (kTcChunkBytes / 8), pf_strip0);
+                        ++prefetched;
+                        if (++pf_c == p.chunks) {
+                            pf_c = 0;
+                            pf_item += gridDim.x;
+                            if (pf_item < items) pf_strip0 = (pf_item / p.token_tiles) * kStripsPerPanel;
+                        }
                     }
-                    const uint32_t ps = pk_n % kTcPackStages;
-                    if (pk_n >= kTcPackStages && !mbar_wait_bounded(&pk_empty[ps], ((pk_n / kTcPackStages) - 1) & 1)) {
+                    if (round > 0 && !mbar_wait_bounded(&pk_empty[ps], (round - 1) & 1)) {
                         atomicExch(p.fault, 11);
                         *abort_flag = 1;
                         break;
@@ -188,7 +193,10 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                     // past the last strip are filled with zeros and count as bytes)
                     mbar_expect_tx(&pk_full[ps], kPackStageBytes);
                     tma_load_2d(pk_ring + ps * kPackStageBytes, &w_map, c * (kTcChunkBytes / 8), strip0, &pk_full[ps]);
-                    ++pk_n;
+                    if (++ps == kTcPackStages) {
+                        ps = 0;
+                        ++round;
+                    }
                 }
             }
         }
