@@ -30,6 +30,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_resolve.restype = vp
     L.garnet_b200_resolve.argtypes = [c.c_char_p]
     L.garnet_b200_binary_path.restype = c.c_char_p
+    L.garnet_b200_is_int4_linear_weight.argtypes = [c.c_char_p, c.c_char_p, i, c.POINTER(c.c_int64), i]
+    L.garnet_b200_selftest_bounded_wait.argtypes = [i, vp]
     L.garnet_b200_int4_quantize.argtypes = [vp, i, c.c_int64, c.c_int64, i, i, vp, vp, vp]
     L.garnet_b200_w4a16_packed_bytes.argtypes = [i, i, i, c.POINTER(sz)]
     L.garnet_b200_w4a16_pack_host.argtypes = [vp, vp, i, i, i, i, vp]
@@ -39,12 +41,18 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_w4a16_workspace.argtypes = [vp, i, c.POINTER(sz)]
     L.garnet_b200_w4a16_run.argtypes = [vp, vp, vp, i, vp, sz, u, vp]
     L.garnet_b200_w4a16_run_group.argtypes = [vp, i, vp, vp, i, u, vp]
+    L.garnet_b200_w4a16_reserve_host.argtypes = [vp, i]
     L.garnet_b200_w4a16_run_host.argtypes = [vp, vp, vp, i, vp]
     L.garnet_b200_w4a16_run_host_async.argtypes = [vp, vp, vp, i, vp]
     L.garnet_b200_w4a16_batch_create.argtypes = [vp, vp, vp, vp, i, vp]
     L.garnet_b200_w4a16_batch_run.argtypes = [vp, vp]
     L.garnet_b200_w4a16_batch_destroy.argtypes = [vp]
     L.garnet_b200_w4a16_batch_destroy.restype = None
+    L.garnet_b200_w4a16_list_create.argtypes = [vp, vp, vp, vp, i, i, vp]
+    L.garnet_b200_w4a16_list_run.argtypes = [vp, u, vp]
+    L.garnet_b200_w4a16_list_fault.argtypes = [vp]
+    L.garnet_b200_w4a16_list_destroy.argtypes = [vp]
+    L.garnet_b200_w4a16_list_destroy.restype = None
     L.garnet_b200_w4a16_dequant.argtypes = [vp, vp, vp]
     L.garnet_b200_w4a16_fault.argtypes = [vp]
     L.garnet_b200_w4a16_destroy.argtypes = [vp]
@@ -67,9 +75,7 @@ def _declare(L: ctypes.CDLL) -> None:
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
-        path = _build.LIB_PATH
-        if not os.path.exists(path):
-            path = _build.build()
+        path = _build.build()      # does nothing when the binary is newer than its sources
         L = ctypes.CDLL(path)
         _declare(L)
         if L.garnet_b200_abi_version() != 1:

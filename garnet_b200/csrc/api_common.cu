@@ -28,6 +28,21 @@ int cuda_fail(cudaError_t e, const char* where)
     return fail(GARNET_B200_CUDA_ERROR, "%s: %s", where, cudaGetErrorString(e));
 }
 
+// One warp waits on a shared-memory barrier that nothing ever arrives on, with the
+// given limit, and reports through the status word the way every kernel of this
+// library reports a wait that ran out.
+__global__ void bounded_wait_probe_kernel(unsigned long long limit_ns, int* status)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    const bool completed = mbar_wait(&bar, 0, limit_ns);
+    if (threadIdx.x == 0) *status = completed ? 0 : 77;
+}
+
 }  // namespace gb200
 
 extern "C" {
@@ -59,6 +74,46 @@ void* garnet_b200_resolve(const char* symbol_name)
     void* sym = dlsym(self, symbol_name);
     dlclose(self);
     return sym;
+}
+
+int garnet_b200_is_int4_linear_weight(const char* name, const char* dtype, int rank, const int64_t* shape, int block)
+{
+    if (!name || !dtype || !shape || rank != 2) return 0;
+    if (shape[0] <= 0 || shape[1] <= 0 || block <= 0 || shape[1] % block != 0) return 0;
+    if (std::strcmp(dtype, "BF16") != 0 && std::strcmp(dtype, "F16") != 0 && std::strcmp(dtype, "F32") != 0) return 0;
+    static const char* const kEndings[] = {
+        ".self_attn.q_proj.weight",      ".self_attn.k_proj.weight",     ".self_attn.v_proj.weight",
+        ".self_attn.o_proj.weight",      ".linear_attn.in_proj_qkv.weight", ".linear_attn.in_proj_z.weight",
+        ".linear_attn.in_proj_b.weight", ".linear_attn.in_proj_a.weight", ".linear_attn.out_proj.weight",
+        ".mlp.gate_proj.weight",         ".mlp.up_proj.weight",          ".mlp.down_proj.weight",
+        "lm_head.weight"};
+    const size_t len = std::strlen(name);
+    for (const char* ending : kEndings) {
+        const size_t el = std::strlen(ending);
+        if (len >= el && std::memcmp(name + len - el, ending, el) == 0) return 1;
+    }
+    return 0;
+}
+
+int garnet_b200_selftest_bounded_wait(int limit_ms, void* stream)
+{
+    if (limit_ms <= 0 || limit_ms > 2000) return gb200::fail(GARNET_B200_INVALID_VALUE, "selftest_bounded_wait: limit must be 1..2000 ms");
+    int* status_host = nullptr;
+    int* status_dev = nullptr;
+    GB_CUDA(cudaHostAlloc(&status_host, sizeof(int), cudaHostAllocMapped));
+    *status_host = -1;
+    cudaError_t e = cudaHostGetDevicePointer(&status_dev, status_host, 0);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (e == cudaSuccess) {
+        gb200::bounded_wait_probe_kernel<<<1, 32, 0, s>>>((unsigned long long)limit_ms * 1000000ull, status_dev);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    const int status = *status_host;
+    cudaFreeHost(status_host);
+    if (e != cudaSuccess) return gb200::cuda_fail(e, "selftest_bounded_wait");
+    if (status == 77) return gb200::fail(GARNET_B200_DEVICE_FAULT, "device wait gave up (code %d)", status);
+    return status == 0 ? GARNET_B200_OK : gb200::fail(GARNET_B200_CUDA_ERROR, "selftest_bounded_wait: kernel did not report");
 }
 
 const char* garnet_b200_binary_path(void)

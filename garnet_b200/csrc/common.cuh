@@ -56,14 +56,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: returns false (and the caller records a fault) if the phase
-// never completes.  The bound is generous (seconds of SM clocks) so that it only
-// trips on a genuine protocol error, never on a slow copy.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+// Nanoseconds of the GPU's global timer (the same clock for every SM).
+__device__ __forceinline__ unsigned long long global_timer_ns()
 {
-    for (uint32_t spin = 0; spin < (1u << 28); ++spin)
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Default limit of every device-side wait: far longer than any copy or kernel of
+// this library takes, short enough that a protocol error ends in a fault word
+// and not in a hung GPU.
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+// Bounded wait: returns false (and the caller records a fault) if the phase does
+// not complete within `limit_ns` of the global timer.  The timer is read once
+// per 256 polls, so the fast path costs nothing extra.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns = kWaitLimitNs)
+{
+    for (int spin = 0; spin < 256; ++spin)
         if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+        for (int spin = 0; spin < 256; ++spin)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > limit_ns) return false;
+    }
 }
 __device__ __forceinline__ void fence_barrier_init()
 {

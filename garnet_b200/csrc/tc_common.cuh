@@ -25,14 +25,7 @@ int make_tensor_map_2d_bytes(CUtensorMap* map, const void* base, uint64_t rows, 
 
 #if defined(__CUDACC__)
 
-constexpr uint32_t kTcWaitSpins = 1u << 24;
-
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity)
-{
-    for (uint32_t spin = 0; spin < kTcWaitSpins; ++spin)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) { return mbar_wait(bar, parity); }
 
 __device__ __forceinline__ bool elect_one()
 {

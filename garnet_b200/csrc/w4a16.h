@@ -27,8 +27,6 @@ struct W4A16 {
     void* stage_y = nullptr;
     void* stage_ws = nullptr;
     int stage_rows = 0;
-    const void* last_host_y = nullptr;   // run_host: last host output buffer and its device alias (or null)
-    void* last_host_y_alias = nullptr;
 
     ~W4A16();
     int init_common();

@@ -66,6 +66,39 @@ def forward_group(linears, x: torch.Tensor, outs=None, pdl: bool = True):
     return outs
 
 
+class LinearList:
+    """A prepared list of linears run by one persistent launch (garnet_b200_w4a16_list_*).
+    `calls` is a sequence of (linear, x, y[, dep]) with device tensors; dep is the index of
+    an earlier call whose output x holds, or -1."""
+
+    def __init__(self, calls, m: int = 1):
+        self._keep = list(calls)
+        n = len(self._keep)
+        hs = (ctypes.c_void_p * n)(*[c[0]._h for c in self._keep])
+        xs = (ctypes.c_void_p * n)(*[c[1].data_ptr() for c in self._keep])
+        ys = (ctypes.c_void_p * n)(*[c[2].data_ptr() for c in self._keep])
+        deps = (ctypes.c_int * n)(*[(c[3] if len(c) > 3 else -1) for c in self._keep])
+        self._l = ctypes.c_void_p(None)
+        check(lib().garnet_b200_w4a16_list_create(hs, xs, ys, deps, n, m, ctypes.byref(self._l)))
+
+    def run(self, pdl: bool = False) -> None:
+        check(lib().garnet_b200_w4a16_list_run(self._l, 1 if pdl else 0, _stream_ptr()))
+
+    def fault(self) -> int:
+        return lib().garnet_b200_w4a16_list_fault(self._l)
+
+    def close(self) -> None:
+        if self._l:
+            lib().garnet_b200_w4a16_list_destroy(self._l)
+            self._l = ctypes.c_void_p(None)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class HostBatch:
     """A prepared list of (linear, host x, host y) calls (garnet_b200_w4a16_batch_*); after
     `run` the outputs are complete once the current stream has been synchronised."""
@@ -103,6 +136,13 @@ class W4A16Linear:
         self.n = self.k = self.group = 0
         self._keep = None
         self._ws = None
+        self._host_rows = 0
+
+    def reserve_host(self, max_m: int) -> None:
+        """Allocates the device staging of the host-buffer calls for up to max_m rows."""
+        if max_m > self._host_rows:
+            check(lib().garnet_b200_w4a16_reserve_host(self._h, max_m))
+            self._host_rows = max_m
 
     # Q4Q8Linear::Prepare (q4q8_linear.cpp:227-283)
     def prepare(self, nibbles: torch.Tensor, scales: torch.Tensor, n: int, k: int, group: int = 128,
@@ -157,6 +197,7 @@ class W4A16Linear:
     def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor) -> torch.Tensor:
         """Host buffers in, host buffers out (copies inside the call)."""
         m = x_host.numel() // self.k
+        self.reserve_host(m)
         check(lib().garnet_b200_w4a16_run_host(self._h, x_host.data_ptr(), y_host.data_ptr(), m, _stream_ptr()))
         return y_host
 
@@ -164,6 +205,7 @@ class W4A16Linear:
         """`forward_host` without the final synchronisation: y_host is complete once the
         current stream has been synchronised."""
         m = x_host.numel() // self.k
+        self.reserve_host(m)
         check(lib().garnet_b200_w4a16_run_host_async(self._h, x_host.data_ptr(), y_host.data_ptr(), m, _stream_ptr()))
         return y_host
 
@@ -181,6 +223,7 @@ class W4A16Linear:
             self._h = ctypes.c_void_p(None)
         self._keep = None
         self._ws = None
+        self._host_rows = 0
 
     def __del__(self):
         try:

@@ -56,6 +56,22 @@ const char* garnet_b200_manifest_json(void);
 void* garnet_b200_resolve(const char* symbol_name);
 const char* garnet_b200_binary_path(void);
 
+/* Which checkpoint tensors the int4 path quantizes: rank 2, positive extents, K a
+ * multiple of the block, dtype "BF16", "F16" or "F32", and a name that ends in one of
+ * the Qwen projection names (q/k/v/o_proj, the linear-attention projections,
+ * gate/up/down_proj, lm_head).  Returns 1 or 0.  Host only.  Replaces
+ * Garnet::IsQwenLinearWeightForINT4 (src/model/weight_quantization.cpp:146-186);
+ * `dtype`, `rank` and `shape` are the fields of SafeTensorMetadata it reads. */
+int garnet_b200_is_int4_linear_weight(const char* name, const char* dtype, int rank, const int64_t* shape, int block);
+
+/* Launches one warp that waits, with a limit of `limit_ms` (1..2000), on a barrier
+ * that nothing ever completes, synchronises `stream` and returns DEVICE_FAULT: the way
+ * every bounded device-side wait of this library ends when its partner never shows
+ * up, without hanging or faulting the GPU.  The context stays usable.  For tests of
+ * the fault reporting; the reference reports such waits through a fault word as well
+ * (plugins/gpt_oss/cuda/tp_peer_owner.cuh:40-46,308-315). */
+int garnet_b200_selftest_bounded_wait(int limit_ms, void* stream);
+
 /* ---- int4 quantizer ---------------------------------------------------------
  * Replaces Garnet::QuantizeSymmetricINT4 (src/model/weight_quantization.cpp:188-270)
  * for a device-resident weight: per (row, K-group) scale = max(-min/8, max/7),
@@ -119,9 +135,36 @@ int garnet_b200_w4a16_run(garnet_b200_w4a16_t h, const void* d_x, void* d_y, int
 int garnet_b200_w4a16_run_group(const garnet_b200_w4a16_t* handles, int count, const void* d_x, void* const* d_ys,
                                 int m, unsigned flags, void* stream);
 
+/* A prepared list of linears that one persistent launch runs back to back: linear i
+ * computes d_ys[i][m, n_i] = d_xs[i][m, k_i] W_i^T, every linear with the same batch m
+ * (at most 16, less for very large K).  deps[i] is -1, or the index of an EARLIER
+ * linear whose output d_xs[i] holds (directly, or through work of the caller's that
+ * the list does not see is not supported: the list only orders its own linears);
+ * linear i then reads its x only after that linear has completed on every SM.
+ * deps may be NULL (no dependencies).  The weights of later linears stream into
+ * shared memory while earlier ones finish, so a decode step pays one launch and no
+ * gaps between its projections.  This is the device form of the engine running the
+ * captured sequence of isLinear operators of one decode step
+ * (src/backends/tensorrt/trt_builder.cpp:7268-7423) with one enqueue.
+ * create allocates a small device table and counters; run allocates nothing and does
+ * not synchronise (flags as for garnet_b200_w4a16_run).  Pointers are captured at
+ * create time.  A list with dependencies needs all of the GPU's SMs for its CTAs to
+ * wait on one another: run it on a GPU that no other long-running kernel occupies,
+ * one run at a time.  garnet_b200_w4a16_list_fault is non-zero after a bounded
+ * device-side wait gave up (as garnet_b200_w4a16_fault). */
+typedef struct garnet_b200_w4a16_list_s* garnet_b200_w4a16_list_t;
+int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void* const* d_xs, void* const* d_ys,
+                                  const int* deps, int count, int m, garnet_b200_w4a16_list_t* out);
+int garnet_b200_w4a16_list_run(garnet_b200_w4a16_list_t list, unsigned flags, void* stream);
+int garnet_b200_w4a16_list_fault(garnet_b200_w4a16_list_t list);
+void garnet_b200_w4a16_list_destroy(garnet_b200_w4a16_list_t list);
+
 /* Same call for host-resident x and y (the plugin-facing form: host -> device
  * copy, kernel, device -> host copy on `stream`, then a stream synchronise).
- * Staging buffers belong to the handle and grow on first use. */
+ * The device staging behind it belongs to the handle and is allocated by
+ * garnet_b200_w4a16_reserve_host(h, max_m), once, outside the hot loop; run_host
+ * itself allocates nothing and rejects more rows than were reserved. */
+int garnet_b200_w4a16_reserve_host(garnet_b200_w4a16_t h, int max_m);
 int garnet_b200_w4a16_run_host(garnet_b200_w4a16_t h, const void* h_x, void* h_y, int m, void* stream);
 /* The same call without the final synchronisation: x is copied in and the kernel is
  * enqueued on `stream`; y is complete once the stream has been synchronised.  When
@@ -134,7 +177,10 @@ int garnet_b200_w4a16_run_host_async(garnet_b200_w4a16_t h, const void* h_x, voi
  * input buffer to the device once, launches the linears back to back (programmatic
  * dependent launches), and writes all outputs to their host buffers with one kernel
  * (pinned, mapped buffers) or one copy each (pageable buffers); the outputs are
- * complete once `stream` has been synchronised.  The reference's CPU backend calls
+ * complete once `stream` has been synchronised.  When every call has the same batch of
+ * at most 16 rows the linears run as one garnet_b200_w4a16_list launch.  Every h_xs[i]
+ * and h_ys[i] must stay allocated, with unchanged pinning, until batch_destroy: the
+ * device aliases of pinned outputs are taken at create time.  The reference's CPU backend calls
  * Q4Q8Linear::Forward once per operator (q4q8_linear.cpp:315-389); this is the same
  * list of calls handed over at once.  create/destroy allocate and free device memory;
  * run does not. */

@@ -108,3 +108,31 @@ def test_host_packer_layout(n, k, group):
     if n % 128:
         byte, _ = expected_position(strips_padded * 16 - 1, 0, chunks)
         assert words[byte // 4] == 0
+
+
+def test_int4_weight_predicate_follows_the_reference_rule():
+    """Garnet::IsQwenLinearWeightForINT4 (src/model/weight_quantization.cpp:146-186): rank 2,
+    K a multiple of the block, a float dtype and one of the Qwen projection endings."""
+    L = garnet_b200.lib()
+
+    def ok(name, dtype="BF16", shape=(2048, 2048), block=128):
+        arr = (ctypes.c_int64 * len(shape))(*shape)
+        return L.garnet_b200_is_int4_linear_weight(name.encode(), dtype.encode(), len(shape), arr, block)
+
+    for ending in ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj", "mlp.gate_proj",
+                   "mlp.up_proj", "mlp.down_proj", "linear_attn.in_proj_qkv", "linear_attn.in_proj_z",
+                   "linear_attn.in_proj_b", "linear_attn.in_proj_a", "linear_attn.out_proj"):
+        assert ok(f"model.layers.3.{ending}.weight") == 1
+    assert ok("lm_head.weight", shape=(151936, 2048)) == 1
+    assert ok("model.lm_head.weight") == 1                       # ending match, as in the reference
+    assert ok("model.layers.0.self_attn.q_proj.weight", dtype="F16") == 1
+    assert ok("model.layers.0.self_attn.q_proj.weight", dtype="F32") == 1
+    assert ok("model.layers.0.self_attn.q_proj.weight", dtype="I8") == 0
+    assert ok("model.layers.0.self_attn.q_proj.bias") == 0
+    assert ok("model.embed_tokens.weight") == 0
+    assert ok("model.layers.0.input_layernorm.weight", shape=(2048,)) == 0
+    assert ok("model.layers.0.self_attn.q_norm.weight", shape=(128,)) == 0
+    assert ok("model.layers.0.mlp.down_proj.weight", shape=(2048, 6100)) == 0    # K not a multiple of the block
+    assert ok("model.layers.0.mlp.down_proj.weight", shape=(2048, 6144), block=0) == 0
+    assert ok("model.layers.0.mlp.down_proj.weight", shape=(0, 6144)) == 0
+    assert ok("model.layers.0.mlp.experts.0.down_proj.weight") == 0              # not the dense MLP ending

@@ -39,9 +39,9 @@ def check_close(y_dev, y64, tol=TOL, rounded_weights=False):
     assert np.isfinite(y).all()
     assert (err <= tol * (1 + np.abs(y64))).all(), float((err / (1 + np.abs(y64))).max())
     # in practice the result is the correctly rounded bf16 of the exact sum, give or
-    # take one ulp, plus an absolute term far below the row's output scale (the
-    # int4 bias is removed once per 128 columns in fp32, which leaves a few 1e-6 of
-    # the typical output magnitude on results that nearly cancel)
+    # take one ulp, plus an absolute term far below the row's output scale (up to 16
+    # rows the activations enter as 15-bit block fixed point per 128 columns: exact
+    # for values within 2^-6 of the block's maximum, 2^-15 of that maximum otherwise)
     ref = oracle.bf16_round(y64.astype(np.float32)).astype(np.float64)
     ulp = np.maximum(np.abs(ref), 2.0 ** -120) * 2.0 ** -7
     rms = np.sqrt((y64 ** 2).mean(axis=1, keepdims=True))
@@ -49,7 +49,7 @@ def check_close(y_dev, y64, tol=TOL, rounded_weights=False):
     # weight carries one bf16 rounding (up to 2^-9 relative), which shows as up to
     # ~1e-2 of the row's output scale on individual outputs (the kernel reproduces
     # x . bf16(q*s) to the last bit; checked below where that model is passed in).
-    slack = 2.5e-2 if rounded_weights else 2e-5
+    slack = 2.5e-2 if rounded_weights else 2e-4
     assert (np.abs(y - ref) <= 1.01 * ulp + slack * rms + 1e-30).all()
 
 
@@ -238,12 +238,84 @@ def test_grouped_launch_equals_separate_launches(m):
     x = bf16_tensor(cases[0]["x_bits"]).reshape(m, k)
     separate = [lin.forward(x) for lin in lins]
     grouped = garnet_b200.forward_group(lins, x)
-    # The group runs as one wider launch, whose CTAs may split K over a different
-    # number of warps than the separate launches do: the fp32 partial sums associate
-    # differently, so the bf16 results may differ by one rounding step.
+    # Up to 16 rows the fp32 sum over K follows one fixed tree however the launch splits
+    # K among warps, so a group gives the bits of the separate launches; above 16 rows
+    # the group is separate launches of the tile kernel anyway.
     for a, b in zip(separate, grouped):
-        a32, b32 = a.float(), b.float()
-        step = torch.maximum(a32.abs(), b32.abs()) * 2.0 ** -7 + 1e-4 * a32.pow(2).mean().sqrt()
-        assert bool(((a32 - b32).abs() <= step).all())
-        assert float((a32 != b32).float().mean()) < 0.02
+        assert torch.equal(a, b)
     assert all(lin.fault() == 0 for lin in lins)
+
+
+def test_linear_list_equals_separate_runs_and_honours_dependencies():
+    """One persistent launch over a list: independent linears give the bits of their own
+    runs; a chain in which each linear reads the previous output gives the bits of
+    running them one after the other (garnet_b200_w4a16_list_*)."""
+    k = 2048
+    shapes = [2048, 1024, 1024, 2048]
+    cases = [synth.int4_linear(n, k, 1, seed=300 + i) for i, n in enumerate(shapes)]
+    lins = [make_linear(c, n, k) for c, n in zip(cases, shapes)]
+    for m in (1, 3, 8, 16):
+        x = bf16_tensor(synth.int4_linear(16, k, m, seed=41)["x_bits"]).reshape(m, k)
+        outs = [torch.zeros(m, n, dtype=torch.bfloat16, device="cuda") for n in shapes]
+        lst = garnet_b200.LinearList([(lin, x, y) for lin, y in zip(lins, outs)], m=m)
+        for _ in range(2):
+            for y in outs:
+                y.zero_()
+            lst.run()
+            torch.cuda.synchronize()
+            assert lst.fault() == 0
+            for lin, y in zip(lins, outs):
+                assert torch.equal(y, lin.forward(x))
+    # a chain of square linears and a gate -> down pair: true data dependencies
+    sq = [make_linear(synth.int4_linear(k, k, 1, seed=400 + i), k, k) for i in range(5)]
+    gate = make_linear(synth.int4_linear(6144, k, 1, seed=410), 6144, k)
+    down = make_linear(synth.int4_linear(k, 6144, 1, seed=411), k, 6144)
+    chain = sq + [gate, down]
+    for m in (1, 4):
+        bufs = [bf16_tensor(synth.int4_linear(16, k, m, seed=42)["x_bits"]).reshape(m, k) * 8]
+        for lin in chain:
+            bufs.append(torch.zeros(m, lin.n, dtype=torch.bfloat16, device="cuda"))
+        lst = garnet_b200.LinearList([(lin, bufs[i], bufs[i + 1], i - 1) for i, lin in enumerate(chain)], m=m)
+        for rep in range(3):                  # the run tag changes from run to run
+            for b in bufs[1:]:
+                b.zero_()
+            lst.run()
+            torch.cuda.synchronize()
+            assert lst.fault() == 0
+            cur = bufs[0]
+            for i, lin in enumerate(chain):
+                cur = lin.forward(cur)
+                assert torch.equal(cur, bufs[i + 1]), (m, rep, i)
+
+
+def test_linear_list_rejects_bad_dependencies():
+    k = 256
+    a = make_linear(synth.int4_linear(256, k, 1, seed=1), 256, k)
+    b = make_linear(synth.int4_linear(128, k, 1, seed=2), 128, k)
+    x = torch.zeros(1, k, dtype=torch.bfloat16, device="cuda")
+    y1 = torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda")
+    y2 = torch.zeros(1, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(garnet_b200.GarnetB200Error):       # depends on a later linear
+        garnet_b200.LinearList([(a, x, y1, 1), (b, y1, y2, -1)])
+    with pytest.raises(garnet_b200.GarnetB200Error):       # x is not the output it claims to depend on
+        garnet_b200.LinearList([(a, x, y1, -1), (b, x, y2, 0)])
+    with pytest.raises(garnet_b200.GarnetB200Error):       # batch too large for a list
+        garnet_b200.LinearList([(a, x, y1, -1)], m=64)
+    garnet_b200.LinearList([(a, x, y1, -1), (b, y1, y2, 0)]).run()
+    torch.cuda.synchronize()
+
+
+def test_bounded_device_wait_reports_a_fault_and_leaves_the_context_usable():
+    """A wait whose partner never arrives ends after its limit with DEVICE_FAULT (no
+    hang, no trap); the next ordinary call works."""
+    from garnet_b200 import _lib
+    L = garnet_b200.lib()
+    rc = L.garnet_b200_selftest_bounded_wait(20, None)
+    assert rc == _lib.DEVICE_FAULT
+    assert b"gave up" in L.garnet_b200_last_error()
+    case = synth.int4_linear(128, 128, 2, seed=77)
+    lin = make_linear(case, 128, 128)
+    y = lin.forward(bf16_tensor(case["x_bits"]).reshape(2, 128))
+    _, y64 = oracle.w4a16_exact(case["nibbles"], case["scales_f32"], 128, 128, 128, case["x_f32"])
+    check_close(y, y64)
+    assert lin.fault() == 0
