@@ -41,8 +41,7 @@ namespace {
 __device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                           uint32_t b1)
 {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -65,6 +64,7 @@ __device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefe
 struct Ctl {
     volatile int abort_flag;
     int warps_done;   // consumer warps that have finished the list
+    int next_slot;    // next slot of the CTA's sequence that no consumer warp has taken yet
 };
 
 // Waits on an mbarrier unless the CTA has been told to give up.
@@ -331,8 +331,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
     const int g = lane >> 2, t = lane & 3;
     const uint32_t run_tag = p.has_deps ? uint32_t(*reinterpret_cast<volatile int*>(p.epoch)) : 0u;
     int q_base = 0;
-    // this warp's next slot in the CTA's sequence, and where it sits in the ring and among the partial-sum slots
-    int next_q = warp, stage = warp, phase = 0, pslot = warp;
+    // Slots are handed out in order to whichever warp is free (a shared counter): a
+    // slow warp then never holds up the ring while others idle.  my_q = the slot this
+    // warp has taken and not yet processed, or -1.
+    int my_q = -1;
     const uint8_t* xcol[MBLK];
 #pragma unroll
     for (int mb = 0; mb < MBLK; ++mb) {
@@ -355,21 +357,25 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
         int s0, s1;
         op_share(op, s0, s1);
         const int ntask = (s1 - s0) * op.parts, q_end = q_base + ntask;
-        int sl = 0, part = 0;
-        if (next_q < q_end) {   // next_q - q_base < 16
-            sl = ((next_q - q_base) * op.inv_parts) >> 16;
-            part = (next_q - q_base) - sl * op.parts;
-        }
-        for (; next_q < q_end && ok;) {
+        while (ok) {
+            if (my_q < 0) {
+                if (lane == 0) my_q = atomicAdd(&ctl->next_slot, 1);
+                my_q = __shfl_sync(0xffffffffu, my_q, 0);
+            }
+            if (my_q >= q_end) break;   // a slot of a later linear: kept until this warp gets there
+            const int local = my_q - q_base;
+            const int sl = int((unsigned long long)(unsigned)local * op.inv_parts >> 40);
+            const int part = local - sl * op.parts;
+            const int round = int((unsigned long long)(unsigned)my_q * p.inv_ring >> 40), stage = my_q - round * NS;
+            const int phase = round & 1;
+            const int pslot = my_q - int((unsigned long long)(unsigned)my_q * p.inv_pslots >> 40) * PS;
             // A parity wait alone cannot tell this slot's phase from the phase two rounds
-            // earlier (a warp may get here before the stage's previous slot has even
-            // landed, and that slot belongs to another warp): the stage's tag says which
-            // slot the completed phase carried.
-            {
+            // earlier: the stage's tag says which slot the completed phase carried.
+            if (!mbar_try_wait(&full[stage], phase) || tags[stage] != my_q) {
                 const unsigned long long t0 = global_timer_ns();
                 while (ok) {
                     if (!wait_or_abort(&full[stage], phase, ctl, limit)) ok = false;
-                    else if (tags[stage] == next_q) break;
+                    else if (tags[stage] == my_q) break;
                     else if (global_timer_ns() - t0 > limit) ok = false;
                 }
                 if (!ok) {
@@ -520,20 +526,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);
-            next_q += kStreamConsumerWarps;
-            stage += kStreamConsumerWarps;
-            if (stage >= NS) {
-                stage -= NS;
-                phase ^= 1;
-            }
-            pslot += kStreamConsumerWarps;
-            if (pslot >= PS) pslot -= PS;
-            sl += op.step_sl;
-            part += op.step_part;
-            if (part >= op.parts) {
-                part -= op.parts;
-                ++sl;
-            }
+            my_q = -1;
         }
         q_base = q_end;
     }
@@ -595,9 +588,7 @@ static void finish_op(StreamOp& op, int grid)
 {
     op.base_strips = op.strips / grid;
     op.rem_strips = op.strips % grid;
-    op.step_sl = kStreamConsumerWarps / op.parts;
-    op.step_part = kStreamConsumerWarps % op.parts;
-    op.inv_parts = (65536 + op.parts - 1) / op.parts;
+    op.inv_parts = ((1ull << 40) + op.parts - 1) / op.parts;
 }
 
 static void choose_parts(StreamOp& op, int total_strips_hint)
@@ -609,8 +600,11 @@ static void choose_parts(StreamOp& op, int total_strips_hint)
     op.parts = (op.chunks + cpp - 1) / cpp;
 }
 
-static int launch_list(const StreamParams& p, int grid, unsigned flags, cudaStream_t stream)
+static int launch_list(StreamParams p, int grid, unsigned flags, cudaStream_t stream)
 {
+    const unsigned long long one = 1ull << 40;
+    p.inv_ring = (one + p.ring_slots - 1) / p.ring_slots;
+    p.inv_pslots = (one + (p.ring_slots + p.max_parts) - 1) / (p.ring_slots + p.max_parts);
     const size_t smem = size_t(stream_smem_plan(p.m, p.max_chunks, p.ring_slots, p.max_parts).total);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(grid));

@@ -45,11 +45,9 @@ struct StreamOp {
     int flags;
     int first_cta;                // CTA that owns the first strips (rotates from op to op to even out the shares)
     int in_strips;                // strips of the op behind xch_in
-    // precomputed for the launch grid, so that the device code divides nothing per op
+    // precomputed for the launch grid, so that the consumer warps divide nothing
     int base_strips, rem_strips;  // strips / grid, strips % grid: the first rem_strips CTAs (from first_cta) take one more
-    int step_sl, step_part;       // consumer warps / parts, consumer warps % parts
-    int inv_parts;                // ceil(65536 / parts): x / parts = (x * inv_parts) >> 16 for x < 1024
-    int pad;
+    unsigned long long inv_parts; // ceil(2^40 / parts): x / parts = (x * inv_parts) >> 40
 };
 
 struct StreamParams {
@@ -60,6 +58,8 @@ struct StreamParams {
     int max_chunks;               // largest chunks over the ops (sizes the activation buffers)
     int ring_slots;
     int max_parts;                // largest parts over the ops (sizes the partial-sum slots)
+    unsigned long long inv_ring;  // ceil(2^40 / ring_slots): q / ring_slots = (q * inv_ring) >> 40
+    unsigned long long inv_pslots; // the same for the partial-sum slots
     int has_deps;
     int* epoch;                   // tag of this run's exchange packets; bumped by the last CTA (only with has_deps)
     int* finish;                  // CTAs that finished the list (only with has_deps)
