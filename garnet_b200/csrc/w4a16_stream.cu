@@ -236,7 +236,7 @@ template <int MBLK>
 __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __grid_constant__ StreamParams p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    const StreamSmem plan = stream_smem_plan(p.m, p.max_chunks, p.ring_slots, p.max_parts);
+    const StreamSmem plan = stream_smem_plan(p.m, p.max_chunks, p.ring_slots, p.max_parts, p.table_in_smem ? p.count : 0);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + plan.bars);
     uint64_t* empty = full + kMaxRingSlots;
     Ctl* ctl = reinterpret_cast<Ctl*>(smem + plan.ctl);
@@ -252,6 +252,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
     const int NS = p.ring_slots, PS = plan.part_slots;
     const StreamOp* ops = p.ops ? p.ops : p.inline_ops;
     const unsigned long long limit = p.wait_limit_ns;
+    if (p.table_in_smem) {
+        // every warp reads every entry: a short table is served from shared memory
+        uint4* dst = reinterpret_cast<uint4*>(smem + plan.optable);
+        const uint4* src = reinterpret_cast<const uint4*>(ops);
+        for (int i = threadIdx.x; i < p.count * int(sizeof(StreamOp) / 16); i += blockDim.x) dst[i] = src[i];
+        ops = reinterpret_cast<const StreamOp*>(smem + plan.optable);
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -281,7 +288,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
         int q_base = 0;
         bool ok = true;
         for (int i = 0; i < p.count && ok; ++i) {
-            if (p.ops && i + 2 < p.count) {   // the table entry is needed the moment the previous op is issued
+            if (p.ops && !p.table_in_smem && i + 2 < p.count) {   // the table entry is needed the moment the previous op is issued
                 prefetch_l1(p.ops + i + 2);
                 prefetch_l1(reinterpret_cast<const char*>(p.ops + i + 3) - 4);
             }
@@ -572,10 +579,10 @@ int stream_max_rows(int chunks)
 }
 
 // Chooses buffers and ring depth for a list; returns false when it does not fit.
-static bool stream_fit(int m, int max_chunks, int max_parts, int* ring_slots)
+static bool stream_fit(int m, int max_chunks, int max_parts, int table_ops, int* ring_slots)
 {
     for (int slots = kMaxRingSlots; slots >= 20; --slots)
-        if (size_t(stream_smem_plan(m, max_chunks, slots, max_parts).total) <= kMaxDynamicSmem) {
+        if (size_t(stream_smem_plan(m, max_chunks, slots, max_parts, table_ops).total) <= kMaxDynamicSmem) {
             *ring_slots = slots;
             return true;
         }
@@ -605,7 +612,7 @@ static int launch_list(StreamParams p, int grid, unsigned flags, cudaStream_t st
     const unsigned long long one = 1ull << 40;
     p.inv_ring = (one + p.ring_slots - 1) / p.ring_slots;
     p.inv_pslots = (one + (p.ring_slots + p.max_parts) - 1) / (p.ring_slots + p.max_parts);
-    const size_t smem = size_t(stream_smem_plan(p.m, p.max_chunks, p.ring_slots, p.max_parts).total);
+    const size_t smem = size_t(stream_smem_plan(p.m, p.max_chunks, p.ring_slots, p.max_parts, p.table_in_smem ? p.count : 0).total);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(grid));
     cfg.blockDim = dim3(kStreamThreads);
@@ -671,7 +678,7 @@ int W4A16::launch_stream_group(W4A16* const* hs, int count, const __nv_bfloat16*
     p.fault = hs[0]->fault_dev;
     p.wait_limit_ns = stream_wait_limit_ns();
     for (int g = 0; g < count; ++g) p.max_parts = std::max(p.max_parts, p.inline_ops[g].parts);
-    if (!stream_fit(m, p.max_chunks, p.max_parts, &p.ring_slots))
+    if (!stream_fit(m, p.max_chunks, p.max_parts, 0, &p.ring_slots))
         return fail(GARNET_B200_NOT_SUPPORTED, "w4a16: batch %d with k=%d does not fit shared memory", m, hs[0]->geo.cols);
     const int grid = std::min(kSmCount, max_strips);
     for (int g = 0; g < count; ++g) {
@@ -773,7 +780,11 @@ int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void
     p.has_deps = has_deps ? 1 : 0;
     p.wait_limit_ns = stream_wait_limit_ns();
     for (int i = 0; i < count; ++i) p.max_parts = std::max(p.max_parts, ops[i].parts);
-    if (!stream_fit(m, max_chunks, p.max_parts, &p.ring_slots))
+    p.table_in_smem = count <= kMaxSmemOps ? 1 : 0;
+    if (!stream_fit(m, max_chunks, p.max_parts, p.table_in_smem ? count : 0, &p.ring_slots)) {
+        p.table_in_smem = 0;   // a long K leaves no room for the table: read it from global memory
+    }
+    if (!p.table_in_smem && !stream_fit(m, max_chunks, p.max_parts, 0, &p.ring_slots))
         return fail(GARNET_B200_NOT_SUPPORTED, "w4a16_list_create: batch %d with k=%d does not fit shared memory", m, max_chunks * 128);
     GB_CUDA(cudaMalloc(&l->d_counters, sizeof(int) * 2));
     const int counters_init[2] = {1, 0};   // first run tag 1 (the packets start as zeros), no CTA finished

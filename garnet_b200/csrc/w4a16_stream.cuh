@@ -17,6 +17,7 @@ constexpr int kSlotChunks = 4;               // chunks per ring slot = the large
 constexpr int kSlotBytes = kSlotChunks * kInt4ChunkBytes;
 constexpr int kMaxRingSlots = 64;
 constexpr int kMaxInlineOps = 4;
+constexpr int kMaxSmemOps = 256;             // lists up to this long keep their op table in shared memory
 
 enum : int {
     kOpSameX = 1,      // reads the same activation rows as the op before it: no restaging
@@ -61,6 +62,7 @@ struct StreamParams {
     unsigned long long inv_ring;  // ceil(2^40 / ring_slots): q / ring_slots = (q * inv_ring) >> 40
     unsigned long long inv_pslots; // the same for the partial-sum slots
     int has_deps;
+    int table_in_smem;            // the op table is copied to shared memory at the start (short lists)
     int* epoch;                   // tag of this run's exchange packets; bumped by the last CTA (only with has_deps)
     int* finish;                  // CTAs that finished the list (only with has_deps)
     int* fault;                   // mapped host word
@@ -69,13 +71,13 @@ struct StreamParams {
 
 // Shared-memory plan (byte offsets), the same on host and device.
 struct StreamSmem {
-    int bars, ctl, tags, sx, cneg, pcnt, partial, xq, ring, total;
+    int bars, ctl, tags, sx, cneg, pcnt, optable, partial, xq, ring, total;
     int xq_stride, xq_rows, xq_bytes, mblk, part_slots, ring_slots;
 };
 
 __host__ __device__ inline int stream_mblk(int m) { return m <= 4 ? 1 : m <= 8 ? 2 : 4; }
 
-__host__ __device__ inline StreamSmem stream_smem_plan(int m, int max_chunks, int ring_slots, int max_parts)
+__host__ __device__ inline StreamSmem stream_smem_plan(int m, int max_chunks, int ring_slots, int max_parts, int table_ops)
 {
     StreamSmem p;
     p.mblk = stream_mblk(m);
@@ -91,6 +93,8 @@ __host__ __device__ inline StreamSmem stream_smem_plan(int m, int max_chunks, in
     p.sx = off;     off += max_chunks * p.mblk * 4 * 4;       // [chunk][mblk][4] float
     p.cneg = off;   off += max_chunks * p.mblk * 8 * 4;       // [chunk][mblk][8] int
     p.pcnt = off;   off += p.part_slots * 4;
+    off = (off + 15) & ~15;
+    p.optable = off; off += table_ops * int(sizeof(StreamOp));       // copy of a short op table
     off = (off + 127) & ~127;
     p.partial = off; off += p.part_slots * p.mblk * 256;             // [slot][mblk][lane][2] float
     p.xq = off;     off += p.xq_bytes;
