@@ -6,13 +6,18 @@ Workload (N = 1): the W4A16 shape sweep over every Qwen3-1.7B projection.  One
 step = one decode pass (batch M = 1) over the full random-init weight set: 28
 layers x {q,k,v,o,gate,up,down}_proj + lm_head = 197 int4 linears, 887 MB of
 packed weights, i.e. several times the 126 MB L2, so every weight byte of a step
-comes from HBM.  `value` is algorithmic bytes / step time with activations
-resident in HBM; `e2e` is the same pass through the host-buffer entry point
-(pinned host x -> device, kernel, device -> host y, per linear).  `sweep` holds
-the per-shape, per-batch (M in 1,4,16,64,256) numbers measured on rotating weight
-copies larger than twice the L2.  With N > 1 the lm_head is sharded along N
-across the ranks and the logits are all-gathered over NVLink; the decoder
-layers are replicated (the configuration's definition), so scaling is strong.
+comes from HBM.  The pass is one persistent launch (garnet_b200_w4a16_list_*);
+its linears read fixed activation buffers, i.e. they do not wait for one
+another.  `value` is algorithmic bytes / step time with activations resident in
+HBM; `chained` repeats the pass with the data dependencies the shapes allow
+(q/k/v <- previous down, o <- q, gate/up <- o, down <- gate, lm_head <- last down),
+every dependent linear waiting on the device for its producer; `e2e` is the
+same pass through the host-buffer entry point (pinned host x -> device, one
+launch, device -> host y).  `sweep` holds the per-shape, per-batch (M in
+1,4,16,64,256) numbers measured on rotating weight copies larger than twice the
+L2.  With N > 1 the lm_head is sharded along N across the ranks and the logits
+are all-gathered over NVLink; the decoder layers are replicated (the
+configuration's definition), so scaling is strong.
 
 --impl reference times the reference's own CPU operator (Q4Q8Linear compiled
 from the reference sources when available, otherwise its restatement) on the
@@ -39,6 +44,12 @@ PROJ = [("q_proj", 2048, 2048), ("k_proj", 2048, 1024), ("v_proj", 2048, 1024), 
         ("gate_proj", 2048, 6144), ("up_proj", 2048, 6144), ("down_proj", 6144, 2048)]
 LM_HEAD = ("lm_head", 2048, 151936)
 SWEEP_M = [1, 4, 16, 64, 256]
+# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of a launch of
+# w4a16_list_kernel, from the ncu capture summarised in the file named below (a
+# four-layer list, 103.8 MB of weights, captured because the full pass is too large to
+# replay under ncu; traffic grows in proportion to the weights streamed)
+TRAFFIC_RATIO = 1.01
+TRAFFIC_SOURCE = "profiles/w4a16_list_kernel_4layers_m1.md"
 
 
 def weight_bytes(k, n):
@@ -169,23 +180,46 @@ def run_gpu(args):
     logits = torch.empty(world, m, hn_local, device="cuda", dtype=torch.bfloat16) if world > 1 else None
     ws_bytes = max([lin.workspace_bytes(m) for layer in layers for (lin, _, _) in layer] + [head.workspace_bytes(m)])
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
-    # q/k/v share their input, and so do gate/up: each group is one launch (the
-    # reference lowers them as packed projections for the same reason)
+    # the whole pass is one prepared list: one persistent launch per step
     y_k = torch.empty(m, 1024, device="cuda", dtype=torch.bfloat16)
     y_v = torch.empty(m, 1024, device="cuda", dtype=torch.bfloat16)
     y_up = torch.empty(m, 6144, device="cuda", dtype=torch.bfloat16)
-    launches_per_step = LAYERS * 4 + 1
+    y_o = torch.empty(m, 2048, device="cuda", dtype=torch.bfloat16)
+    y_d = torch.empty(m, 2048, device="cuda", dtype=torch.bfloat16)
+    calls = []
+    for layer in layers:
+        q, kk, v, o, gate, up, down = [lin for (lin, _, _) in layer]
+        calls += [(q, xs[2048], ys[2048]), (kk, xs[2048], y_k), (v, xs[2048], y_v), (o, xs[2048], y_o),
+                  (gate, xs[2048], ys[6144]), (up, xs[2048], y_up), (down, xs[6144], y_d)]
+    calls.append((head, xs[hk], y_head))
+    pass_list = gb.LinearList(calls, m=m)
+    launches_per_step = 1
 
     def decode_pass():
-        for layer in layers:
-            q, kk, v, o, gate, up, down = [lin for (lin, _, _) in layer]
-            gb.forward_group([q, kk, v], xs[2048], outs=[ys[2048], y_k, y_v])
-            o.forward(xs[2048], out=ys[2048], workspace=ws)
-            gb.forward_group([gate, up], xs[2048], outs=[ys[6144], y_up])
-            down.forward(xs[6144], out=ys[2048], workspace=ws)
-        head.forward(xs[hk], out=y_head, workspace=ws)
+        pass_list.run()
         if world > 1:
             dist.all_gather_into_tensor(logits.view(-1), y_head.view(-1))
+
+    # The same 197 linears with the data dependencies their shapes allow, each consumer
+    # waiting on the device for its producer (one launch as well).
+    def chained_list():
+        cc, prev_down = [], -1
+        x_in = xs[2048]
+        mk = lambda n: torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+        for layer in layers:
+            q, kk, v, o, gate, up, down = [lin for (lin, _, _) in layer]
+            yq, yk2, yv2, yo, yg, yu, yd = mk(2048), mk(1024), mk(1024), mk(2048), mk(6144), mk(6144), mk(2048)
+            iq = len(cc)
+            cc += [(q, x_in, yq, prev_down), (kk, x_in, yk2, prev_down), (v, x_in, yv2, prev_down)]
+            io = len(cc)
+            cc.append((o, yq, yo, iq))
+            ig = len(cc)
+            cc += [(gate, yo, yg, io), (up, yo, yu, io)]
+            prev_down = len(cc)
+            cc.append((down, yg, yd, ig))
+            x_in = yd
+        cc.append((head, x_in, y_head, prev_down))
+        return gb.LinearList(cc, m=m)
 
     step_bytes = LAYERS * sum(algo_bytes(k, n, m) for (_, k, n) in PROJ) + algo_bytes(hk, hn, m)
 
@@ -197,6 +231,11 @@ def run_gpu(args):
         sampler.start()
     ms = time_graph(torch, decode_pass, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
+    assert pass_list.fault() == 0, "a device-side wait gave up"
+    chain = chained_list()
+    chained_ms = time_graph(torch, chain.run, args.steps, args.warmup)
+    assert chain.fault() == 0, "a device-side wait gave up"
+    del chain
     if world > 1:
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -210,16 +249,16 @@ def run_gpu(args):
 
     # Every linear is called with HOST buffers (pinned) through the prepared-batch C entry
     # points: each distinct input buffer is copied to the device once per pass, the 197
-    # linears run back to back, one kernel writes their 197 outputs to the host buffers, and
+    # linears run as one launch, one kernel writes their 197 outputs to the host buffers, and
     # the pass synchronises once, when its results are read.  Two sets of seven output
     # buffers, alternating by layer.
     yh_all = [[torch.empty(m, n, dtype=torch.bfloat16).pin_memory() for (_, _, n) in PROJ] for _ in range(2)]
-    calls = []
+    host_calls = []
     for li, layer in enumerate(layers):
         for j, (lin, k, n) in enumerate(layer):
-            calls.append((lin, xh[k], yh_all[li & 1][j]))
-    calls.append((head, xh[hk], yh_head))
-    host_batch = gb.HostBatch(calls)
+            host_calls.append((lin, xh[k], yh_all[li & 1][j]))
+    host_calls.append((head, xh[hk], yh_head))
+    host_batch = gb.HostBatch(host_calls)
 
     def host_pass():
         host_batch.run()
@@ -254,22 +293,24 @@ def run_gpu(args):
         out = {
             "metric": "w4a16_weight_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16 x int4 -> fp32 accumulate",
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x int4 -> fp32 accumulate",
             "data": "synthetic",
             "config": {"workload": "qwen3_1p7b_w4a16_sweep: decode pass M=1 over 28x7 projections + lm_head (197 int4 group-128 linears)",
                        "bytes_per_step": step_bytes, "l2": "887 MB of weights per step > 126 MB L2; no flush needed",
                        "parallelism": f"lm_head N-sharded x{world} + all-gather" if world > 1 else "single GPU",
-                       "launch": "one CUDA graph of 113 programmatic-dependent launches (q/k/v and gate/up grouped, as the reference packs them)"},
+                       "launch": "one persistent launch per pass (a prepared list of the 197 linears reading fixed activation buffers; no linear waits for another)"},
+            "chained": {"ms_per_step": round(chained_ms, 5), "value": round(step_bytes / (chained_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                        "hbm_frac": round(step_bytes / (chained_ms * 1e-3) / 1e9 / peaks["hbm"], 4),
+                        "what": "same pass, one launch, with the data dependencies the shapes allow (113 dependent stages: q/k/v <- previous down, o <- q, gate/up <- o, down <- gate, lm_head <- last down); a dependent linear polls its producer's output packets on the device"},
             "clocks": clocks,
             "e2e": {"value": round(step_bytes / (e2e_ms * 1e-3) / 1e9, 3), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": round(value, 2), "peak": peaks["hbm"], "unit": "GB/s",
                          "frac": round(value / peaks["hbm"], 4), "peak_source": peaks["src"],
-                         # dram read+write per launch = 1.002 x algorithmic, from the ncu captures summarised in
-                         # profiles/ (gate_proj: 6,518,272 B for 6,504,448 B; lm_head: 164.4 MB for 160.75 MB)
-                         "traffic": round(step_bytes / launches_per_step * 1.002),
-                         "kernel": "w4a16_stream_kernel", "bytes_per_launch": round(step_bytes / launches_per_step),
+                         "traffic": round(step_bytes / launches_per_step * TRAFFIC_RATIO),
+                         "traffic_source": TRAFFIC_SOURCE,
+                         "kernel": "w4a16_list_kernel", "bytes_per_launch": round(step_bytes / launches_per_step),
                          "us_per_launch": round(ms * 1e3 / launches_per_step, 3)},
         }
 
@@ -288,9 +329,13 @@ def run_gpu(args):
                 y = torch.empty(mm, n, device="cuda", dtype=torch.bfloat16)
                 w = torch.empty(max(16, lins[0].workspace_bytes(mm)), dtype=torch.uint8, device="cuda")
 
-                def body():
-                    for lin in lins:
-                        lin.forward(x, out=y, workspace=w)
+                if mm <= 16 and mm <= (8 if k > 4096 else 16):
+                    rot = gb.LinearList([(lin, x, y) for lin in lins], m=mm)   # one launch over the rotating copies
+                    body = rot.run
+                else:
+                    def body():
+                        for lin in lins:
+                            lin.forward(x, out=y, workspace=w)
 
                 t_ms = time_graph(torch, body, max(3, args.steps // 4), 3) / copies
                 gbs = algo_bytes(k, n, mm) / (t_ms * 1e-3) / 1e9
@@ -314,7 +359,7 @@ def run_gpu(args):
 
     if rank == 0:
         if world == 1:
-            out["cpu_baseline"] = cpu_baseline(sample_seconds=12.0)
+            out["cpu_baseline"] = cpu_baseline(sample_seconds=10.0)
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
@@ -427,8 +472,8 @@ def bench_moe_ep(torch, dist, gb, args, rank, world, tokens_total=8192):
 # ------------------------------------------------------------- CPU baseline
 
 def cpu_linears():
-    """One layer's seven projections plus the lm_head, as CPU operators.  Uses the
-    reference's own compiled operator when oracle/_ref is present, else the
+    """The 197 linears of the decode pass as CPU operators, each with its own weights.
+    Uses the reference's own compiled operator when oracle/_ref is present, else the
     restatement in oracle/oracle.c."""
     import oracle
     import oracle.ref as ref
@@ -436,10 +481,11 @@ def cpu_linears():
     threads = min(16, os.cpu_count() or 1)      # the reference's pool is capped at 16 threads
     kind = "reference" if ref.available() else "port"
     ops = []
-    for name, k, n in PROJ + [LM_HEAD]:
+    xs = {k: rng.normal(0, 1, size=k).astype(np.float32) for k in (2048, 6144)}
+    for name, k, n in PROJ * LAYERS + [LM_HEAD]:
         nib = rng.integers(0, 256, size=n * k // 2, dtype=np.uint8)
         sc = (np.abs(rng.normal(0, 0.02, size=(n, k // GROUP))) / 7.0).astype(np.float32)
-        x = rng.normal(0, 1, size=k).astype(np.float32)
+        x = xs[k]
         if kind == "reference":
             op = ref.Q4Q8Linear(nib, sc, n, k, GROUP)
             y = np.empty(n, np.float32)
@@ -449,7 +495,7 @@ def cpu_linears():
     return ops, kind, threads
 
 
-def cpu_baseline(sample_seconds=12.0):
+def cpu_baseline(sample_seconds=10.0):
     ops, kind, threads = cpu_linears()
     bytes_pass = sum(algo_bytes(k, n, 1) for (_, k, n, _) in ops)
     for (_, _, _, fn) in ops:
@@ -462,7 +508,7 @@ def cpu_baseline(sample_seconds=12.0):
         passes += 1
     dt = time.perf_counter() - t0
     return {"value": round(bytes_pass * passes / dt / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": kind,
-            "sample": f"{passes} passes over one layer's 7 projections + lm_head at M=1 ({bytes_pass} B each), "
+            "sample": f"{passes} full decode passes (197 linears at M=1, {bytes_pass} B each), "
                       f"Q4Q8Linear::Forward (int8 activations), {dt:.1f} s"}
 
 
@@ -481,14 +527,14 @@ def run_reference(args):
             fn()
     dt = (time.perf_counter() - t0) / args.steps
     value = bytes_pass / dt / 1e9
-    sample = (f"each step = one layer's 7 projections + lm_head at M=1 ({bytes_pass} B of the 887 MB pass), "
-              f"Q4Q8Linear::Forward on host cores")
+    sample = (f"each step = the full decode pass, 197 linears at M=1 ({bytes_pass} B), Q4Q8Linear::Forward on host cores")
     print(json.dumps({
         "impl": "reference", "metric": "w4a16_weight_GBps", "value": round(value, 3), "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4 -> int32 (W4A8)",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4 -> int32 (W4A8)",
         "data": "synthetic",
-        "config": {"workload": "qwen3_1p7b_w4a16_sweep: decode pass M=1 (bounded sample: one layer + lm_head per step)"},
+        "config": {"workload": "qwen3_1p7b_w4a16_sweep: decode pass M=1 over 28x7 projections + lm_head (197 int4 group-128 linears)",
+                   "bytes_per_step": bytes_pass},
         "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)

@@ -61,6 +61,13 @@ __device__ __forceinline__ void st_relaxed_gpu_v2(void* p, uint32_t a, uint32_t 
 }
 __device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 
+#ifdef GB_STREAM_TRACE
+__device__ unsigned long long g_trace[4096];
+#define GB_TRACE(op, slot) do { if (blockIdx.x == 5 && (op) < 500) g_trace[(op) * 8 + (slot)] = global_timer_ns(); } while (0)
+#else
+#define GB_TRACE(op, slot) do {} while (0)
+#endif
+
 struct Ctl {
     volatile int abort_flag;
     int warps_done;   // consumer warps that have finished the list
@@ -236,7 +243,7 @@ template <int MBLK>
 __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __grid_constant__ StreamParams p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    const StreamSmem plan = stream_smem_plan(p.m, p.max_chunks, p.ring_slots, p.max_parts, p.table_in_smem ? p.count : 0);
+    const StreamSmem plan = stream_smem_plan(p.m, p.max_chunks, p.ring_slots, p.max_parts, p.table_in_smem ? p.count : 0, p.nbuf);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + plan.bars);
     uint64_t* empty = full + kMaxRingSlots;
     Ctl* ctl = reinterpret_cast<Ctl*>(smem + plan.ctl);
@@ -270,10 +277,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
     // control words, part counters, bias terms, the all-zero activation row
     for (int i = threadIdx.x; i < int(sizeof(Ctl) / 4); i += blockDim.x) reinterpret_cast<int*>(ctl)[i] = 0;
     for (int i = threadIdx.x; i < PS; i += blockDim.x) pcnt[i] = 0;
-    for (int i = threadIdx.x; i < p.max_chunks * MBLK * 8; i += blockDim.x) cneg[i] = 0;
-    for (int i = threadIdx.x; i < p.max_chunks * MBLK * 4; i += blockDim.x) sx[i] = 0.f;
-    for (int i = threadIdx.x; i < plan.xq_stride / 16; i += blockDim.x)
-        *reinterpret_cast<uint4*>(xq + size_t(2 * p.m) * plan.xq_stride + i * 16) = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < p.nbuf * p.max_chunks * MBLK * 8; i += blockDim.x) cneg[i] = 0;
+    for (int i = threadIdx.x; i < p.nbuf * p.max_chunks * MBLK * 4; i += blockDim.x) sx[i] = 0.f;
+    for (int b = 0; b < p.nbuf; ++b)
+        for (int i = threadIdx.x; i < plan.xq_stride / 16; i += blockDim.x)
+            *reinterpret_cast<uint4*>(xq + size_t(b) * plan.xq_bytes + size_t(2 * p.m) * plan.xq_stride + i * 16) = make_uint4(0, 0, 0, 0);
     __syncthreads();
     pdl_launch_dependents();
 
@@ -343,23 +351,32 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
     // warp has taken and not yet processed, or -1.
     int my_q = -1;
     const uint8_t* xcol[MBLK];
-#pragma unroll
-    for (int mb = 0; mb < MBLK; ++mb) {
-        const int r = mb * 8 + g;
-        xcol[mb] = xq + size_t(r < 2 * p.m ? r : 2 * p.m) * plan.xq_stride + t * 16;
-    }
+    const float* sxb = sx;
+    const int* cnb = cneg;
     bool ok = true;
     for (int i = 0; i < p.count; ++i) {
         const StreamOp op = ops[i];
-        if (i == 0 || !(op.flags & kOpSameX)) {
-            // Every warp has finished with the previous rows; then all stage the new ones.
-            // (A warp that gave up keeps meeting the others at these barriers.)
-            named_barrier_sync(1, kConsumerThreads);
-            if (ok && !ctl->abort_flag && !stage_rows<MBLK>(p, op, plan, ctl, xq, sx, cneg, run_tag, threadIdx.x, lane)) {
-                if ((lane & 15) == 0) give_up(p, ctl, 3);
+        {
+            const int buf = (op.flags & kOpBuffer1) ? 1 : 0;
+            uint8_t* xb = xq + size_t(buf) * plan.xq_bytes;
+            sxb = sx + size_t(buf) * p.max_chunks * MBLK * 4;
+            cnb = cneg + size_t(buf) * p.max_chunks * MBLK * 8;
+#pragma unroll
+            for (int mb = 0; mb < MBLK; ++mb) {
+                const int r = mb * 8 + g;
+                xcol[mb] = xb + size_t(r < 2 * p.m ? r : 2 * p.m) * plan.xq_stride + t * 16;
             }
-            named_barrier_sync(1, kConsumerThreads);
-            if (ctl->abort_flag) ok = false;
+            if (!(op.flags & kOpSameX)) {
+                // Every warp has finished with the rows this buffer held; then all stage the new
+                // ones.  (A warp that gave up keeps meeting the others at these barriers.)
+                named_barrier_sync(1, kConsumerThreads);
+                if (ok && !ctl->abort_flag &&
+                    !stage_rows<MBLK>(p, op, plan, ctl, xb, const_cast<float*>(sxb), const_cast<int*>(cnb), run_tag, threadIdx.x, lane)) {
+                    if ((lane & 15) == 0) give_up(p, ctl, 3);
+                }
+                named_barrier_sync(1, kConsumerThreads);
+                if (ctl->abort_flag) ok = false;
+            }
         }
         int s0, s1;
         op_share(op, s0, s1);
@@ -410,7 +427,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                 int acc_i[MBLK][4];
 #pragma unroll
                 for (int mb = 0; mb < MBLK; ++mb) {
-                    const int2 cn = *reinterpret_cast<const int2*>(cneg + (chunk * MBLK + mb) * 8 + 2 * t);
+                    const int2 cn = *reinterpret_cast<const int2*>(cnb + (chunk * MBLK + mb) * 8 + 2 * t);
                     acc_i[mb][0] = cn.x;
                     acc_i[mb][1] = cn.y;
                     acc_i[mb][2] = cn.x;
@@ -443,7 +460,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                 }
 #pragma unroll
                 for (int mb = 0; mb < MBLK; ++mb) {
-                    const float f = sx[(chunk * MBLK + mb) * 4 + t];
+                    const float f = sxb[(chunk * MBLK + mb) * 4 + t];
                     const int v0 = acc_i[mb][0] * 128 + acc_i[mb][1];   // hi and lo pieces of batch row 4*mb + t
                     const int v1 = acc_i[mb][2] * 128 + acc_i[mb][3];
                     // explicit roundings: no multiply-add contraction, so the bits do not depend on
@@ -460,6 +477,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                 acc[mb][1] = __fadd_rn(pr[mb][1][0], pr[mb][1][1]);
             }
 
+            if (lane == 0 && part == 0) GB_TRACE(i, 4);
             // ---- the parts of a strip meet in shared memory
             const int strip = s0 + sl;
             const int n_lo = strip * 16 + row_of_g(g), n_hi = n_lo + 8;
@@ -516,6 +534,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                     writer = true;
                 }
             }
+            if (writer && lane == 0) GB_TRACE(i, 5);
             if (writer) {
 #pragma unroll
                 for (int mb = 0; mb < MBLK; ++mb) {
@@ -533,6 +552,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);
+            if (writer && lane == 0) GB_TRACE(i, 6);
             my_q = -1;
         }
         q_base = q_end;
@@ -579,10 +599,10 @@ int stream_max_rows(int chunks)
 }
 
 // Chooses buffers and ring depth for a list; returns false when it does not fit.
-static bool stream_fit(int m, int max_chunks, int max_parts, int table_ops, int* ring_slots)
+static bool stream_fit(int m, int max_chunks, int max_parts, int table_ops, int nbuf, int* ring_slots)
 {
     for (int slots = kMaxRingSlots; slots >= 20; --slots)
-        if (size_t(stream_smem_plan(m, max_chunks, slots, max_parts, table_ops).total) <= kMaxDynamicSmem) {
+        if (size_t(stream_smem_plan(m, max_chunks, slots, max_parts, table_ops, nbuf).total) <= kMaxDynamicSmem) {
             *ring_slots = slots;
             return true;
         }
@@ -600,7 +620,11 @@ static void finish_op(StreamOp& op, int grid)
 
 static void choose_parts(StreamOp& op, int total_strips_hint)
 {
-    const int want_tasks = kSmCount * 8;
+    static const int per_sm = [] {
+        const char* e = getenv("GARNET_B200_STREAM_TASKS_PER_SM");   // A/B switch, read once
+        return e && atoi(e) > 0 ? atoi(e) : 8;
+    }();
+    const int want_tasks = kSmCount * per_sm;
     int cpp = kSlotChunks;
     while (cpp > 1 && (long long)total_strips_hint * ((op.chunks + cpp - 1) / cpp) < want_tasks) cpp >>= 1;
     op.cpp = cpp;
@@ -612,7 +636,7 @@ static int launch_list(StreamParams p, int grid, unsigned flags, cudaStream_t st
     const unsigned long long one = 1ull << 40;
     p.inv_ring = (one + p.ring_slots - 1) / p.ring_slots;
     p.inv_pslots = (one + (p.ring_slots + p.max_parts) - 1) / (p.ring_slots + p.max_parts);
-    const size_t smem = size_t(stream_smem_plan(p.m, p.max_chunks, p.ring_slots, p.max_parts, p.table_in_smem ? p.count : 0).total);
+    const size_t smem = size_t(stream_smem_plan(p.m, p.max_chunks, p.ring_slots, p.max_parts, p.table_in_smem ? p.count : 0, p.nbuf).total);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(grid));
     cfg.blockDim = dim3(kStreamThreads);
@@ -671,6 +695,7 @@ int W4A16::launch_stream_group(W4A16* const* hs, int count, const __nv_bfloat16*
         max_strips = std::max(max_strips, op.strips);
         p.inline_ops[g] = op;
     }
+    p.nbuf = 1;
     p.ops = nullptr;
     p.count = count;
     p.m = m;
@@ -678,7 +703,7 @@ int W4A16::launch_stream_group(W4A16* const* hs, int count, const __nv_bfloat16*
     p.fault = hs[0]->fault_dev;
     p.wait_limit_ns = stream_wait_limit_ns();
     for (int g = 0; g < count; ++g) p.max_parts = std::max(p.max_parts, p.inline_ops[g].parts);
-    if (!stream_fit(m, p.max_chunks, p.max_parts, 0, &p.ring_slots))
+    if (!stream_fit(m, p.max_chunks, p.max_parts, 0, 1, &p.ring_slots))
         return fail(GARNET_B200_NOT_SUPPORTED, "w4a16: batch %d with k=%d does not fit shared memory", m, hs[0]->geo.cols);
     const int grid = std::min(kSmCount, max_strips);
     for (int g = 0; g < count; ++g) {
@@ -728,7 +753,7 @@ int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void
     if (!handles || !d_xs || !d_ys || count <= 0 || m <= 0)
         return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: bad argument");
     std::vector<StreamOp> ops(static_cast<size_t>(count));
-    int max_chunks = 0, max_strips = 0;
+    int max_chunks = 0, max_strips = 0, l_nbuf = 1;
     bool has_deps = false;
     for (int i = 0; i < count; ++i) {
         const W4A16* h = reinterpret_cast<const W4A16*>(handles[i]);
@@ -752,10 +777,35 @@ int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void
             ops[dep].flags |= kOpSignal;
             has_deps = true;
         }
-        // Same rows as the op before (same buffer, same K): staged once.
-        if (i > 0 && d_xs[i] == d_xs[i - 1] && ops[i].chunks == ops[i - 1].chunks && dep == ops[i - 1].dep) ops[i].flags |= kOpSameX;
+        // (which activation buffer the rows go to, and whether they are already there, is decided below)
         max_chunks = std::max(max_chunks, ops[i].chunks);
         max_strips = std::max(max_strips, ops[i].strips);
+    }
+    // Two activation buffers (when they fit) hold the rows staged most recently: an op whose
+    // rows - same pointer, same K, no dependency of their own to wait for - are still
+    // in a buffer does not stage them again.  Rows that come from an earlier linear of
+    // the list are always staged: they change from run to run.
+    {
+        const size_t xq_bytes = size_t(2 * m + 1) * size_t(max_chunks * 128 + 64);
+        const int nbuf = 2 * xq_bytes <= 80 * 1024 ? 2 : 1;
+        const void* held[2] = {nullptr, nullptr};
+        int held_chunks[2] = {0, 0}, last_use[2] = {-1, -1};
+        for (int i = 0; i < count; ++i) {
+            int buf = -1;
+            if (ops[i].dep < 0 || (i > 0 && ops[i].dep == ops[i - 1].dep && d_xs[i] == d_xs[i - 1]))
+                for (int b = 0; b < nbuf; ++b)
+                    if (held[b] == d_xs[i] && held_chunks[b] == ops[i].chunks) buf = b;
+            if (buf >= 0) {
+                ops[i].flags |= kOpSameX;
+            } else {
+                buf = (nbuf == 2 && last_use[1] < last_use[0]) ? 1 : 0;   // the buffer used longest ago
+                held[buf] = d_xs[i];
+                held_chunks[buf] = ops[i].chunks;
+            }
+            last_use[buf] = i;
+            if (buf == 1) ops[i].flags |= kOpBuffer1;
+        }
+        l_nbuf = nbuf;
     }
     // ops that share their rows are one group for the purpose of splitting K
     for (int i = 0; i < count;) {
@@ -778,13 +828,14 @@ int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void
     p.m = m;
     p.max_chunks = max_chunks;
     p.has_deps = has_deps ? 1 : 0;
+    p.nbuf = l_nbuf;
     p.wait_limit_ns = stream_wait_limit_ns();
     for (int i = 0; i < count; ++i) p.max_parts = std::max(p.max_parts, ops[i].parts);
     p.table_in_smem = count <= kMaxSmemOps ? 1 : 0;
-    if (!stream_fit(m, max_chunks, p.max_parts, p.table_in_smem ? count : 0, &p.ring_slots)) {
+    if (!stream_fit(m, max_chunks, p.max_parts, p.table_in_smem ? count : 0, p.nbuf, &p.ring_slots)) {
         p.table_in_smem = 0;   // a long K leaves no room for the table: read it from global memory
     }
-    if (!p.table_in_smem && !stream_fit(m, max_chunks, p.max_parts, 0, &p.ring_slots))
+    if (!p.table_in_smem && !stream_fit(m, max_chunks, p.max_parts, 0, p.nbuf, &p.ring_slots))
         return fail(GARNET_B200_NOT_SUPPORTED, "w4a16_list_create: batch %d with k=%d does not fit shared memory", m, max_chunks * 128);
     GB_CUDA(cudaMalloc(&l->d_counters, sizeof(int) * 2));
     const int counters_init[2] = {1, 0};   // first run tag 1 (the packets start as zeros), no CTA finished
@@ -836,6 +887,14 @@ int garnet_b200_w4a16_list_fault(garnet_b200_w4a16_list_t ll)
     LinearList* l = reinterpret_cast<LinearList*>(ll);
     return l && l->fault_host ? *l->fault_host : -1;
 }
+
+#ifdef GB_STREAM_TRACE
+int garnet_b200_w4a16_trace(unsigned long long* out, int n)
+{
+    GB_CUDA(cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * size_t(n)));
+    return 0;
+}
+#endif
 
 void garnet_b200_w4a16_list_destroy(garnet_b200_w4a16_list_t ll) { delete reinterpret_cast<LinearList*>(ll); }
 

@@ -23,6 +23,7 @@ enum : int {
     kOpSameX = 1,      // reads the same activation rows as the op before it: no restaging
     kOpSignal = 2,     // a later op reads this one's output: publish it in exchange packets
     kOpScaleFp16 = 4,  // 16-bit scales are fp16 (else bf16)
+    kOpBuffer1 = 8,    // its activation rows live in the second buffer
 };
 
 // Outputs that a later op of the same list consumes also travel as 8-byte packets
@@ -58,6 +59,7 @@ struct StreamParams {
     int m;                        // batch rows of every op
     int max_chunks;               // largest chunks over the ops (sizes the activation buffers)
     int ring_slots;
+    int nbuf;                     // activation buffers: with two, rows staged earlier stay usable (gate/up x, then down x, then back)
     int max_parts;                // largest parts over the ops (sizes the partial-sum slots)
     unsigned long long inv_ring;  // ceil(2^40 / ring_slots): q / ring_slots = (q * inv_ring) >> 40
     unsigned long long inv_pslots; // the same for the partial-sum slots
@@ -77,7 +79,7 @@ struct StreamSmem {
 
 __host__ __device__ inline int stream_mblk(int m) { return m <= 4 ? 1 : m <= 8 ? 2 : 4; }
 
-__host__ __device__ inline StreamSmem stream_smem_plan(int m, int max_chunks, int ring_slots, int max_parts, int table_ops)
+__host__ __device__ inline StreamSmem stream_smem_plan(int m, int max_chunks, int ring_slots, int max_parts, int table_ops, int nbuf)
 {
     StreamSmem p;
     p.mblk = stream_mblk(m);
@@ -90,14 +92,14 @@ __host__ __device__ inline StreamSmem stream_smem_plan(int m, int max_chunks, in
     p.bars = off;   off += 2 * kMaxRingSlots * 8;
     p.ctl = off;    off += 128;                                      // abort flag, finished warps
     p.tags = off;   off += kMaxRingSlots * 4;                        // slot index each ring stage currently holds
-    p.sx = off;     off += max_chunks * p.mblk * 4 * 4;       // [chunk][mblk][4] float
-    p.cneg = off;   off += max_chunks * p.mblk * 8 * 4;       // [chunk][mblk][8] int
+    p.sx = off;     off += nbuf * max_chunks * p.mblk * 4 * 4;       // [buf][chunk][mblk][4] float
+    p.cneg = off;   off += nbuf * max_chunks * p.mblk * 8 * 4;       // [buf][chunk][mblk][8] int
     p.pcnt = off;   off += p.part_slots * 4;
     off = (off + 15) & ~15;
     p.optable = off; off += table_ops * int(sizeof(StreamOp));       // copy of a short op table
     off = (off + 127) & ~127;
     p.partial = off; off += p.part_slots * p.mblk * 256;             // [slot][mblk][lane][2] float
-    p.xq = off;     off += p.xq_bytes;
+    p.xq = off;     off += nbuf * p.xq_bytes;
     p.ring = off;   off += ring_slots * kSlotBytes;
     p.total = off;
     return p;
