@@ -63,10 +63,14 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_moe_run_static.argtypes = [vp, vp, vp, i, vp]
     L.garnet_b200_moe_rows_workspace.argtypes = [vp, i, c.POINTER(sz)]
     L.garnet_b200_moe_run_rows.argtypes = [vp, vp, vp, i, vp, vp, sz, vp]
+    L.garnet_b200_moe_run_rows_stage.argtypes = [vp, i, vp, vp, i, vp, vp, vp, sz, vp]
     L.garnet_b200_moe_combine.argtypes = [vp, vp, vp, vp, i, vp]
     L.garnet_b200_moe_route.argtypes = [vp, vp, vp, vp, vp, i, vp]
+    L.garnet_b200_moe_route_workspace.argtypes = [vp, i, c.POINTER(sz)]
+    L.garnet_b200_moe_route_ws.argtypes = [vp, vp, vp, vp, vp, i, vp, sz, vp]
     L.garnet_b200_mxfp4_decode.argtypes = [vp, vp, vp, i, vp]
     L.garnet_b200_moe_dequant.argtypes = [vp, i, i, vp, vp]
+    L.garnet_b200_mx_split_rows.argtypes = [vp, i, i, vp, vp, vp, vp]
     L.garnet_b200_moe_fault.argtypes = [vp]
     L.garnet_b200_moe_destroy.argtypes = [vp]
     L.garnet_b200_moe_destroy.restype = None

@@ -410,6 +410,30 @@ __global__ void moe_prep_rows_kernel(const XT* __restrict__ x, __half* __restric
     if (lane == 0) xshift[row] = shift;
 }
 
+// Activations of the routed rows between the two projections, exchanged with the
+// caller in row order as fp32 (bf16-valued).  The kernels keep them as fp16 at
+// the row's sorted position (block-scaled path) or at the row itself (streaming path).
+__global__ void moe_act_to_rows_kernel(const __half* __restrict__ act, const int* __restrict__ sorted,
+                                       const int* __restrict__ offsets, int experts, int inter, int by_position,
+                                       float* __restrict__ out)
+{
+    const int pos = blockIdx.x;
+    if (pos >= offsets[experts]) return;
+    const int row = sorted[pos];
+    const __half* src = act + size_t(by_position ? pos : row) * inter;
+    for (int i = threadIdx.x; i < inter; i += blockDim.x) out[size_t(row) * inter + i] = __half2float(src[i]);
+}
+__global__ void moe_rows_to_act_kernel(const float* __restrict__ in, const int* __restrict__ sorted,
+                                       const int* __restrict__ offsets, int experts, int inter, int by_position,
+                                       __half* __restrict__ act)
+{
+    const int pos = blockIdx.x;
+    if (pos >= offsets[experts]) return;
+    const int row = sorted[pos];
+    __half* dst = act + size_t(by_position ? pos : row) * inter;
+    for (int i = threadIdx.x; i < inter; i += blockDim.x) dst[i] = __float2half_rn(in[size_t(row) * inter + i]);
+}
+
 // ------------------------------------------------------------ slot bucketing
 
 
@@ -873,17 +897,6 @@ __global__ void moe_combine_kernel(const float* __restrict__ vals, const float* 
 
 // ------------------------------------------------------------------ handle
 
-__global__ void mx_scale_range_kernel(const uint8_t* __restrict__ scales, size_t count, int* lo, int* hi);   // moe_tc.cu
-
-bool Moe::use_tc(int slots) const
-{
-    // GARNET_B200_MOE_NO_TC=1 keeps every size on the streaming kernel (A/B switch).
-    static const bool enabled = [] {
-        const char* e = getenv("GARNET_B200_MOE_NO_TC");
-        return !(e && e[0] == '1');
-    }();
-    return enabled && tc_ok && (long long)slots >= 16LL * local_experts() && opt.experts <= 1024;
-}
 
 constexpr size_t kMaxDynamicSmem = 227 * 1024;
 
@@ -909,10 +922,6 @@ MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens)
     w.sorted = take(slots * 4);
     w.ntasks = take(4);
     w.tasks = take((slots / kMoeRows + o.experts + 1) * 16);
-    // rows gathered into expert order: only the tensor-core path uses them
-    const bool tc = moe_tc_eligible(o, tokens);
-    w.xg = take(tc ? slots * o.hidden * 2 : 0);
-    w.xshift_g = take(tc ? slots * 4 : 0);
     // the block-scaled path's buffers exist only at sizes that use it (see Moe::use_mx)
     const int mx_world = o.ep_world > 1 ? o.ep_world : 1;
     const int mx_local = mx_world <= 1 ? o.experts   // the same count as Moe::local_experts()
@@ -979,15 +988,12 @@ Moe::~Moe()
 {
     if (router_w3) cudaFree(router_w3);
     for (int i = 0; i < 2; ++i) {
-        if (mx_w[i]) cudaFree(mx_w[i]);
-        if (mx_sfa[i]) cudaFree(mx_sfa[i]);
         if (mxr_w[i]) cudaFree(mxr_w[i]);
         if (mxr_sf[i]) cudaFree(mxr_sf[i]);
     }
     if (packed_up) cudaFree(packed_up);
     if (packed_down) cudaFree(packed_down);
     if (flag_dev) cudaFree(flag_dev);
-    if (range_dev) cudaFree(range_dev);
     if (fault_host) cudaFreeHost(fault_host);
 }
 
@@ -1005,6 +1011,7 @@ static cudaError_t set_moe_attr()
 int Moe::prepare(const void* const* weights, cudaStream_t stream)
 {
     const int el = opt.expert_weights_sharded ? local_experts() : opt.experts;
+    GB_CUDA(cudaGetDevice(&device));
     geo_up = make_geom(kFormatMxfp4, 2 * opt.intermediate, opt.hidden, 32);
     geo_down = make_geom(kFormatMxfp4, opt.hidden, opt.intermediate, 32);
     stored_experts = local_experts();
@@ -1012,9 +1019,6 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
     GB_CUDA(cudaMalloc(&packed_down, geo_down.matrix_bytes() * stored_experts));
     GB_CUDA(cudaMalloc(&flag_dev, sizeof(int)));
     GB_CUDA(cudaMemsetAsync(flag_dev, 0, sizeof(int), stream));
-    GB_CUDA(cudaMalloc(&range_dev, 4 * sizeof(int)));
-    const int range_init[4] = {255, 0, 255, 0};   // {min, max} of the gate_up scales, then of the down scales
-    GB_CUDA(cudaMemcpyAsync(range_dev, range_init, sizeof(range_init), cudaMemcpyHostToDevice, stream));
     GB_CUDA(cudaHostAlloc(&fault_host, sizeof(int), cudaHostAllocMapped));
     *fault_host = 0;
     GB_CUDA(cudaHostGetDevicePointer(&fault_dev, fault_host, 0));
@@ -1047,8 +1051,6 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
             const size_t cnt = size_t(run) * sc_per_expert;
             mx_scan_scales_kernel<<<unsigned((cnt + 255) / 256), 256, 0, stream>>>(scales + e0 * sc_per_expert, cnt,
                                                                                  flag_dev);
-            mx_scale_range_kernel<<<256, 256, 0, stream>>>(scales + e0 * sc_per_expert, cnt, range_dev + 2 * pass,
-                                                          range_dev + 2 * pass + 1);
             if (moe_mx_enabled())
                 if (int rc = init_mx(pass, blocks + e0 * blk_per_expert, scales + e0 * sc_per_expert, s, run, stream))
                     return rc;
@@ -1056,12 +1058,10 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
         }
     }
     GB_CUDA(cudaGetLastError());
-    int flag = 0, range[4] = {255, 0, 255, 0};
+    int flag = 0;
     GB_CUDA(cudaMemcpyAsync(&flag, flag_dev, sizeof(int), cudaMemcpyDeviceToHost, stream));
-    GB_CUDA(cudaMemcpyAsync(range, range_dev, sizeof(range), cudaMemcpyDeviceToHost, stream));
     GB_CUDA(cudaStreamSynchronize(stream));
     careful_scales = flag != 0;
-    if (int rc = init_tc(range[0], range[1], range[2], range[3])) return rc;
     router_w_ptr = static_cast<const float*>(weights[0]);
     if (moe_mx_enabled()) {
         if (int rc = finish_mx()) return rc;
@@ -1204,10 +1204,23 @@ int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStrea
     return GARNET_B200_OK;
 }
 
+// The kernels read and write rows with 16-byte vector accesses.
+static bool misaligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
+// Row counts above this are rejected before any size arithmetic (2^24 rows of the
+// largest supported width still fit the 64-bit byte counts used below).
+constexpr int kMoeMaxRows = 1 << 24;
+
 int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cudaStream_t stream)
 {
-    if (tokens <= 0) return fail(GARNET_B200_INVALID_VALUE, "moe_run: tokens must be positive");
+    if (tokens <= 0 || tokens > kMoeMaxRows / opt.top_k)
+        return fail(GARNET_B200_INVALID_VALUE, "moe_run: tokens must be in 1..%d (got %d)", kMoeMaxRows / opt.top_k, tokens);
     if (!x || !y || !ws) return fail(GARNET_B200_INVALID_VALUE, "moe_run: null pointer");
+    if (misaligned16(x) || misaligned16(y)) return fail(GARNET_B200_INVALID_VALUE, "moe_run: x and y must be 16-byte aligned");
+    {
+        int dev = -1;
+        GB_CUDA(cudaGetDevice(&dev));
+        if (dev != device) return fail(GARNET_B200_INVALID_VALUE, "moe_run: the handle was created on device %d, the current device is %d", device, dev);
+    }
     const MoeWorkspace plan = moe_workspace_plan(opt, tokens);
     if (ws_bytes < plan.total) return fail(GARNET_B200_INVALID_VALUE, "moe_run: workspace too small (%zu < %zu)", ws_bytes, plan.total);
     if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(GARNET_B200_INVALID_VALUE, "moe_run: workspace must be 256-byte aligned");
@@ -1223,8 +1236,6 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     w.sorted = reinterpret_cast<int*>(b + plan.sorted);
     w.ntasks = reinterpret_cast<int*>(b + plan.ntasks);
     w.tasks = reinterpret_cast<int4*>(b + plan.tasks);
-    w.xg = reinterpret_cast<__half*>(b + plan.xg);
-    w.xshift_g = reinterpret_cast<int*>(b + plan.xshift_g);
     w.mx_tp = reinterpret_cast<int*>(b + plan.mx_tp);
     w.mx_q = b + plan.mx_q;
     w.mx_sf = b + plan.mx_sf;
@@ -1251,17 +1262,13 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     if (use_mx(slots)) {
         if (int rc = launch_mx(true, w, x, 0, tokens, slots, opt.top_k, stream)) return rc;
         if (int rc = launch_mx(false, w, x, 0, tokens, slots, opt.top_k, stream)) return rc;
-    } else if (use_tc(slots) && moe_tc_eligible(opt, tokens)) {
-        if (int rc = gather_rows(w, slots, opt.top_k, stream)) return rc;
-        if (int rc = launch_tc(true, w, slots, stream)) return rc;
-        if (int rc = launch_tc(false, w, slots, stream)) return rc;
     } else {
         if (int rc = launch_stream(true, w, tokens, stream)) return rc;
         if (int rc = launch_stream(false, w, tokens, stream)) return rc;
     }
     const size_t n = size_t(tokens) * opt.hidden;
     const int round_output = sh.world > 1 ? 0 : 1;
-    const bool streamed = use_mx(slots) || !(use_tc(slots) && moe_tc_eligible(opt, tokens));
+    const bool streamed = true;   // both expert paths end in kernels that support a programmatic dependent launch
     if (opt.io_dtype == GARNET_B200_FP32)
         GB_CUDA(launch_pdl(moe_combine_kernel<float>, dim3(unsigned((n + 255) / 256)), dim3(256), 0, stream, streamed,
                            (const float*)w.vals, (const float*)w.probs, (const int*)w.selected, static_cast<float*>(y),
@@ -1288,8 +1295,6 @@ static MoeWorkspacePtrs bind_workspace(void* ws, const MoeWorkspace& plan)
     w.sorted = reinterpret_cast<int*>(b + plan.sorted);
     w.ntasks = reinterpret_cast<int*>(b + plan.ntasks);
     w.tasks = reinterpret_cast<int4*>(b + plan.tasks);
-    w.xg = reinterpret_cast<__half*>(b + plan.xg);
-    w.xshift_g = reinterpret_cast<int*>(b + plan.xshift_g);
     w.mx_tp = reinterpret_cast<int*>(b + plan.mx_tp);
     w.mx_q = b + plan.mx_q;
     w.mx_sf = b + plan.mx_sf;
@@ -1315,18 +1320,24 @@ MoeWorkspace moe_rows_workspace_plan(const garnet_b200_moe_options& o, int rows)
 // run, already exchanged): row r goes through expert row_expert[r];
 // vals[r, :] = bf(bf(h . w_down) + bd), unweighted.  Rows of experts that this
 // handle does not hold are skipped (their vals are left untouched).
+// `stage`: 0 = both projections (x_rows -> vals); 1 = gate/up + SwiGLU only (x_rows ->
+// hidden_io [rows, intermediate] fp32); 2 = down projection only (hidden_io -> vals).
 int Moe::run_rows(const void* x_rows, const int* row_expert, int rows, float* vals, void* ws, size_t ws_bytes,
-                  cudaStream_t stream)
+                  cudaStream_t stream, int stage, float* hidden_io)
 {
-    if (rows <= 0) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: rows must be positive");
-    if (!x_rows || !row_expert || !vals || !ws) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: null pointer");
+    if (rows <= 0 || rows > kMoeMaxRows) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: rows must be in 1..%d (got %d)", kMoeMaxRows, rows);
+    if (!row_expert || !ws || (stage != 2 && !x_rows) || (stage != 1 && !vals) || (stage != 0 && !hidden_io))
+        return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: null pointer");
+    if (misaligned16(x_rows) || misaligned16(vals) || misaligned16(hidden_io) || (reinterpret_cast<uintptr_t>(row_expert) & 3))
+        return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: rows and values must be 16-byte aligned");
     const MoeWorkspace plan = moe_rows_workspace_plan(opt, rows);
     if (ws_bytes < plan.total) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: workspace too small (%zu < %zu)", ws_bytes, plan.total);
     if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows: workspace must be 256-byte aligned");
     MoeWorkspacePtrs w = bind_workspace(ws, plan);
     w.vals = vals;
+    const bool mx = use_mx(rows);
     const unsigned blocks = unsigned((size_t(rows) * 32 + 255) / 256);
-    if (use_mx(rows)) {
+    if (mx || stage == 2) {
         // the block-scaled path quantises the rows itself and does not read the fp16 copies
     } else if (opt.io_dtype == GARNET_B200_FP32)
         moe_prep_rows_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x_rows), w.xh, w.xshift, rows, opt.hidden);
@@ -1335,28 +1346,31 @@ int Moe::run_rows(const void* x_rows, const int* row_expert, int rows, float* va
     const MoeShard sh = shard();
     moe_count_kernel<<<opt.experts, 256, 0, stream>>>(row_expert, rows, w.counts, sh);
     moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(row_expert, rows, w.counts, w.offsets, w.sorted, w.tasks, w.ntasks,
-                                                     opt.experts, kMoeRows, sh,
-                                                     use_mx(rows) ? moe_mx_plan(opt, rows, rows).nt : 0, w.mx_tp);
+                                                     opt.experts, kMoeRows, sh, mx ? moe_mx_plan(opt, rows, rows).nt : 0, w.mx_tp);
     GB_CUDA(cudaGetLastError());
-    garnet_b200_moe_options one = opt;
-    one.top_k = 1;
-    if (use_mx(rows)) {
-        if (int rc = launch_mx(true, w, x_rows, 0, rows, rows, 1, stream)) return rc;
-        return launch_mx(false, w, x_rows, 0, rows, rows, 1, stream);
+    if (stage != 2) {
+        if (int rc = mx ? launch_mx(true, w, x_rows, 0, rows, rows, 1, stream) : launch_stream(true, w, rows, stream, 1)) return rc;
     }
-    if (use_tc(rows) && moe_tc_eligible(one, rows)) {
-        if (int rc = gather_rows(w, rows, 1, stream)) return rc;
-        if (int rc = launch_tc(true, w, rows, stream)) return rc;
-        return launch_tc(false, w, rows, stream);
+    if (stage == 1) {
+        moe_act_to_rows_kernel<<<rows, 128, 0, stream>>>(w.act, w.sorted, w.offsets, opt.experts, opt.intermediate, mx ? 1 : 0,
+                                                        hidden_io);
+        GB_CUDA(cudaGetLastError());
+        return GARNET_B200_OK;
     }
-    if (int rc = launch_stream(true, w, rows, stream, 1)) return rc;
-    return launch_stream(false, w, rows, stream, 1);
+    if (stage == 2) {
+        moe_rows_to_act_kernel<<<rows, 128, 0, stream>>>(hidden_io, w.sorted, w.offsets, opt.experts, opt.intermediate, mx ? 1 : 0,
+                                                        w.act);
+        GB_CUDA(cudaGetLastError());
+    }
+    return mx ? launch_mx(false, w, x_rows, 0, rows, rows, 1, stream) : launch_stream(false, w, rows, stream, 1);
 }
 
 // y[t, :] = bf(sum_j vals[t*k + j, :] * probs[t, j]) in router order, all slots.
 int Moe::combine(const float* vals, const float* probs, void* y, int tokens, cudaStream_t stream)
 {
-    if (tokens <= 0 || !vals || !probs || !y) return fail(GARNET_B200_INVALID_VALUE, "moe_combine: bad argument");
+    if (tokens <= 0 || tokens > kMoeMaxRows / opt.top_k || !vals || !probs || !y) return fail(GARNET_B200_INVALID_VALUE, "moe_combine: bad argument");
+    if (misaligned16(vals) || misaligned16(y) || (reinterpret_cast<uintptr_t>(probs) & 3))
+        return fail(GARNET_B200_INVALID_VALUE, "moe_combine: values and y must be 16-byte aligned");
     MoeShard all{};
     all.world = 1;
     const size_t n = size_t(tokens) * opt.hidden;
@@ -1382,8 +1396,9 @@ static __device__ __align__(256) unsigned char g_moe_static_scratch[kMoeStaticSc
 constexpr int kMaxDevices = 64;
 
 // Device address of the built-in scratch on the current device.  The first call
-// on a device performs the symbol lookup (with that device current).
-static int moe_static_scratch(void** out)
+// on a device performs the symbol lookup (with that device current); it is made from
+// garnet_b200_moe_create, so that garnet_b200_moe_run_static itself never does it.
+int moe_static_scratch(void** out)
 {
     static std::mutex mu;
     static void* address[kMaxDevices] = {};
@@ -1413,17 +1428,24 @@ int garnet_b200_moe_run_static(garnet_b200_moe_t hh, const void* d_x, void* d_y,
     Moe* h = reinterpret_cast<Moe*>(hh);
     if (!h) return fail(GARNET_B200_INVALID_VALUE, "moe_run_static: null handle");
     if (tokens <= 0) return fail(GARNET_B200_INVALID_VALUE, "moe_run_static: tokens must be positive");
+    if (tokens > kMoeMaxRows / h->opt.top_k)
+        return fail(GARNET_B200_INVALID_VALUE, "moe_run_static: %d tokens is far beyond what the built-in scratch holds", tokens);
     const size_t need = moe_workspace_plan(h->opt, tokens).total;
     if (need > kMoeStaticScratchBytes) {
-        int fit = tokens;
-        while (fit > 0 && moe_workspace_plan(h->opt, fit).total > kMoeStaticScratchBytes) --fit;
+        // the plan grows with the token count: bisect for the largest count that fits
+        int lo = 0, hi = tokens;   // fits(lo), !fits(hi)
+        while (hi - lo > 1) {
+            const int mid = lo + (hi - lo) / 2;
+            if (moe_workspace_plan(h->opt, mid).total <= kMoeStaticScratchBytes) lo = mid;
+            else hi = mid;
+        }
         return fail(GARNET_B200_INVALID_VALUE,
                     "moe_run_static: %d tokens need %zu bytes of scratch but the built-in array holds %zu "
                     "(at most %d tokens for this layer); use garnet_b200_moe_run with a caller workspace",
-                    tokens, need, kMoeStaticScratchBytes, fit);
+                    tokens, need, kMoeStaticScratchBytes, lo);
     }
-    void* scratch = nullptr;
-    if (int rc = moe_static_scratch(&scratch)) return rc;
+    void* scratch = h->static_scratch;   // looked up when the handle was created, on the handle's device
+    if (!scratch) return fail(GARNET_B200_CUDA_ERROR, "moe_run_static: the handle has no scratch address");
     // Nothing in the scratch has to start at zero: every region the kernels read
     // (logits, routing, counts, slot lists, activations, per-slot values) is fully
     // written earlier in the same call for the slots that are read.
@@ -1459,7 +1481,10 @@ int garnet_b200_moe_create(const garnet_b200_moe_options* o, const void* const* 
     Moe* h = new (std::nothrow) Moe();
     if (!h) return fail(GARNET_B200_OUT_OF_MEMORY, "moe_create: host allocation failed");
     h->opt = *o;
-    if (int rc = h->prepare(weights, static_cast<cudaStream_t>(stream))) {
+    int rc = h->prepare(weights, static_cast<cudaStream_t>(stream));
+    // the address of the built-in scratch of garnet_b200_moe_run_static, so that no run call looks it up
+    if (!rc) rc = moe_static_scratch(&h->static_scratch);
+    if (rc) {
         delete h;
         return rc;
     }
@@ -1491,6 +1516,16 @@ int garnet_b200_moe_run_rows(garnet_b200_moe_t hh, const void* d_rows, const int
     return h->run_rows(d_rows, d_row_expert, rows, d_vals, d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
+int garnet_b200_moe_run_rows_stage(garnet_b200_moe_t hh, int stage, const void* d_rows, const int* d_row_expert, int rows,
+                                   float* d_hidden, float* d_vals, void* d_workspace, size_t workspace_bytes, void* stream)
+{
+    Moe* h = reinterpret_cast<Moe*>(hh);
+    if (!h) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows_stage: null handle");
+    if (stage != 1 && stage != 2) return fail(GARNET_B200_INVALID_VALUE, "moe_run_rows_stage: stage must be 1 or 2");
+    return h->run_rows(d_rows, d_row_expert, rows, d_vals, d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream), stage,
+                       d_hidden);
+}
+
 int garnet_b200_moe_combine(garnet_b200_moe_t hh, const float* d_vals, const float* d_probs, void* d_y, int tokens,
                             void* stream)
 {
@@ -1504,16 +1539,44 @@ int garnet_b200_moe_route(garnet_b200_moe_t hh, const void* d_x, int* d_selected
 {
     Moe* h = reinterpret_cast<Moe*>(hh);
     if (!h) return fail(GARNET_B200_INVALID_VALUE, "moe_route: null handle");
-    if (!d_x || !d_selected || !d_probs || !d_logits || tokens <= 0)
+    if (!d_x || !d_selected || !d_probs || !d_logits || tokens <= 0 || tokens > kMoeMaxRows / h->opt.top_k)
         return fail(GARNET_B200_INVALID_VALUE, "moe_route: bad argument");
+    if (misaligned16(d_x) || ((reinterpret_cast<uintptr_t>(d_selected) | reinterpret_cast<uintptr_t>(d_probs) | reinterpret_cast<uintptr_t>(d_logits)) & 3))
+        return fail(GARNET_B200_INVALID_VALUE, "moe_route: x must be 16-byte aligned");
     return h->route(d_x, d_logits, d_selected, d_probs, nullptr, nullptr, tokens, static_cast<cudaStream_t>(stream));
+}
+
+int garnet_b200_moe_route_workspace(const garnet_b200_moe_options* o, int tokens, size_t* bytes)
+{
+    if (int rc = validate_options(o)) return rc;
+    if (!bytes || tokens <= 0 || tokens > kMoeMaxRows / o->top_k) return fail(GARNET_B200_INVALID_VALUE, "moe_route_workspace: bad argument");
+    *bytes = std::max<size_t>(256, moe_route_partial_bytes(tokens, o->experts));
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_moe_route_ws(garnet_b200_moe_t hh, const void* d_x, int* d_selected, float* d_probs, float* d_logits,
+                             int tokens, void* d_workspace, size_t workspace_bytes, void* stream)
+{
+    Moe* h = reinterpret_cast<Moe*>(hh);
+    if (!h) return fail(GARNET_B200_INVALID_VALUE, "moe_route_ws: null handle");
+    if (!d_x || !d_selected || !d_probs || !d_logits || !d_workspace || tokens <= 0 || tokens > kMoeMaxRows / h->opt.top_k)
+        return fail(GARNET_B200_INVALID_VALUE, "moe_route_ws: bad argument");
+    if (misaligned16(d_x) || (reinterpret_cast<uintptr_t>(d_workspace) & 255) ||
+        ((reinterpret_cast<uintptr_t>(d_selected) | reinterpret_cast<uintptr_t>(d_probs) | reinterpret_cast<uintptr_t>(d_logits)) & 3))
+        return fail(GARNET_B200_INVALID_VALUE, "moe_route_ws: x must be 16-byte and the workspace 256-byte aligned");
+    if (workspace_bytes < moe_route_partial_bytes(tokens, h->opt.experts))
+        return fail(GARNET_B200_INVALID_VALUE, "moe_route_ws: workspace too small");
+    // the same call the one-call operator makes: identical logits, selection and probabilities
+    return h->route(d_x, d_logits, d_selected, d_probs, nullptr, nullptr, tokens, static_cast<cudaStream_t>(stream), false,
+                    static_cast<float*>(d_workspace), nullptr);
 }
 
 int garnet_b200_moe_dequant(garnet_b200_moe_t hh, int which, int stored_expert, float* d_out, void* stream)
 {
     Moe* h = reinterpret_cast<Moe*>(hh);
-    if (!h || !d_out || stored_expert < 0 || stored_expert >= h->stored_experts || (which != 0 && which != 1))
+    if (!h || !d_out || stored_expert < 0 || stored_expert >= h->stored_experts || which < 0 || which > 3)
         return fail(GARNET_B200_INVALID_VALUE, "moe_dequant: bad argument");
+    if (which >= 2) return h->dequant_block_scaled(which - 2, stored_expert, d_out, static_cast<cudaStream_t>(stream));
     const PackGeom& geo = which == 0 ? h->geo_up : h->geo_down;
     const size_t total = size_t(geo.rows) * geo.cols / 2;
     mx_dequant_kernel<<<unsigned((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(

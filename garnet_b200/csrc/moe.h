@@ -22,7 +22,7 @@ struct MoeShard {
 
 // Byte offsets of the regions of the caller's workspace.
 struct MoeWorkspace {
-    size_t logits, selected, probs, xshift, xh, counts, offsets, sorted, ntasks, tasks, xg, xshift_g, mx_tp, mx_q, mx_sf, route_partial,
+    size_t logits, selected, probs, xshift, xh, counts, offsets, sorted, ntasks, tasks, mx_tp, mx_q, mx_sf, route_partial,
         act, vals, total;
 };
 
@@ -37,8 +37,6 @@ struct MoeWorkspacePtrs {
     int* sorted;
     int* ntasks;
     int4* tasks;
-    __half* xg;        // rows gathered into expert order (tensor-core path)
-    int* xshift_g;
     int* mx_tp;        // row tiles before each expert (block-scaled path)
     uint8_t* mx_q;     // e4m3 row pieces at tile-aligned positions: [2][q_rows][kp]
     uint8_t* mx_sf;    // their scale atoms: [tiles][kslabs][512]
@@ -60,10 +58,7 @@ struct MoeMxPlan {
 MoeMxPlan moe_mx_plan(const garnet_b200_moe_options& o, int tokens, int slots);
 bool moe_mx_enabled();
 bool moe_mx_forced();
-bool moe_mx_weights_as_m();   // the earlier orientation (GARNET_B200_MOE_MX=3), kept for comparison
 size_t moe_route_partial_bytes(int tokens, int experts);
-// True when the per-expert row counts are large enough for the tensor-core tile kernel.
-bool moe_tc_eligible(const garnet_b200_moe_options& o, int tokens);
 
 struct Moe {
     garnet_b200_moe_options opt{};
@@ -77,21 +72,22 @@ struct Moe {
     const float* down_bias_ptr = nullptr;
     bool careful_scales = false;       // some e8m0 byte is 0 or 255
     struct alignas(64) TensorMapStorage { unsigned char bytes[128]; };
-    TensorMapStorage tc_w_map[2];      // TMA views of the packed gate_up / down matrices
-    uint8_t* mx_w[2] = {nullptr, nullptr};     // block-scaled path: row-major e2m1, K padded to 128
-    uint8_t* mx_sfa[2] = {nullptr, nullptr};   // and the weights' scale atoms
-    TensorMapStorage mx_w_map[2];
-    int mx_kp[2] = {0, 0}, mx_mtiles[2] = {0, 0}, mx_kslabs[2] = {0, 0};
+    int mx_kp[2] = {0, 0}, mx_kslabs[2] = {0, 0};   // block-scaled path: K padded to 128, and in slabs of 128
     bool mx_ok = false;
+    struct QMapCache {                 // TMA view of the quantised rows of the last call
+        TensorMapStorage map;
+        const void* base = nullptr;
+        int kp = 0, q_rows = 0;
+    };
+    QMapCache q_map_cache[2];
     uint8_t* mxr_w[2] = {nullptr, nullptr};    // rows-as-M form: 15 KiB blocks of 240 weight rows
     uint8_t* mxr_sf[2] = {nullptr, nullptr};   // and their scale atoms
     int mxr_ntiles[2] = {0, 0};
     TensorMapStorage mxr_w_map[2];
     __nv_bfloat16* router_w3 = nullptr;        // router weight split into three bf16 terms (tensor-core router)
     bool route_mma_ok = false;
-    bool tc_ok = false;                // scale bytes fit the fp16 window of the tensor-core path
-    int ref_up = 0, ref_down = 0;      // exponent references of that path
-    int* range_dev = nullptr;
+    int device = 0;                    // device the handle was created on
+    void* static_scratch = nullptr;    // device address of the library's built-in scratch (run_static)
     int* flag_dev = nullptr;
     int* fault_host = nullptr;
     int* fault_dev = nullptr;
@@ -104,15 +100,12 @@ struct Moe {
               cudaStream_t stream, bool skip_topk = false, float* route_partial = nullptr, int* counts = nullptr);
     int launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream, int topk = -1);
     int run_rows(const void* x_rows, const int* row_expert, int rows, float* vals, void* ws, size_t ws_bytes,
-                 cudaStream_t stream);
-    int init_tc(int lo_up, int hi_up, int lo_dn, int hi_dn);
-    int gather_rows(const MoeWorkspacePtrs& w, int slots, int topk, cudaStream_t stream);
-    int launch_tc(bool up, const MoeWorkspacePtrs& w, int slots, cudaStream_t stream);
-    bool use_tc(int slots) const;
+                 cudaStream_t stream, int stage = 0, float* hidden_io = nullptr);
     int init_mx(int pass, const uint8_t* blocks, const uint8_t* scales, int first_stored, int count, cudaStream_t stream);
     int finish_mx();
     int init_mxr(int pass, const uint8_t* blocks, const uint8_t* scales, int first_stored, int count, cudaStream_t stream);
     int finish_mxr();
+    int dequant_block_scaled(int pass, int stored_expert, float* out, cudaStream_t stream);
     int launch_mxr_gemm(bool up, const MoeWorkspacePtrs& w, const void* q_map, int q_rows, int tiles_max,
                         cudaStream_t stream);
     int launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_sorted, int tokens, int slots, int topk,

@@ -382,7 +382,43 @@ __global__ void mxr_weight_atoms_kernel(const uint8_t* __restrict__ scales, uint
     dst[idx] = v;
 }
 
+// fp32 value of every element of one stored expert matrix, decoded from the 15 KiB
+// blocks and scale atoms above (the operands the tensor core reads), in the
+// original row order.  Subnormal (0) and NaN (255) scale bytes decode as in the
+// reference (gpt_oss_kernels.cu:55-56).
+__global__ void mxr_dequant_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sf, float* __restrict__ out,
+                                   int expert, int rows, int k, int ntiles, int kslabs)
+{
+    const size_t total = size_t(rows) * k / 2;
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int row = int(idx / (k / 2)), col = int(idx % (k / 2)) * 2;
+    const int nt = row / kRxN, r = row % kRxN, ks = col / kMxSlab, c = col % kMxSlab;
+    const size_t block = (size_t(expert) * ntiles + nt) * kslabs + ks;
+    // the conversion is fed from an aligned 32-bit word, as everywhere else
+    const size_t byte = block * kRxPkBytes + size_t(r) * (kMxSlab / 2) + c / 2;
+    const uint32_t word = *reinterpret_cast<const uint32_t*>(w + (byte & ~size_t(3)));
+    const uint32_t pair = e2m1x2_to_f16x2(word >> (8 * (byte & 3)), 0);
+    const int rr = r & 127;
+    const uint32_t e = sf[(block * 2 + (r >> 7)) * kMxAtom + (rr & 31) * 16 + (rr >> 5) * 4 + (c >> 5)];
+    const float s = e == 0 ? __uint_as_float(0x00400000u) : e == 255 ? __uint_as_float(0x7fc00000u) : __uint_as_float(e << 23);
+    const __half2 hv = *reinterpret_cast<const __half2*>(&pair);
+    out[size_t(row) * k + col] = __half2float(__low2half(hv)) * s;
+    out[size_t(row) * k + col + 1] = __half2float(__high2half(hv)) * s;
+}
+
 // ------------------------------------------------------------------ host side
+
+int Moe::dequant_block_scaled(int pass, int stored_expert, float* out, cudaStream_t stream)
+{
+    if (!mx_ok || !mxr_w[pass]) return fail(GARNET_B200_NOT_SUPPORTED, "moe_dequant: this handle holds no block-scaled weight copy");
+    const PackGeom& geo = pass == 0 ? geo_up : geo_down;
+    const size_t total = size_t(geo.rows) * geo.cols / 2;
+    mxr_dequant_kernel<<<unsigned((total + 255) / 256), 256, 0, stream>>>(mxr_w[pass], mxr_sf[pass], out, stored_expert, geo.rows,
+                                                                        geo.cols, mxr_ntiles[pass], mx_kslabs[pass]);
+    GB_CUDA(cudaGetLastError());
+    return GARNET_B200_OK;
+}
 
 int Moe::init_mxr(int pass, const uint8_t* blocks, const uint8_t* scales, int first_stored, int count, cudaStream_t stream)
 {

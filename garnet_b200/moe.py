@@ -97,6 +97,21 @@ class GptOssMoe:
         logits = torch.empty(tokens, self.opt.experts, dtype=torch.float32, device=x.device)
         selected = torch.empty(tokens, self.opt.top_k, dtype=torch.int32, device=x.device)
         probs = torch.empty(tokens, self.opt.top_k, dtype=torch.float32, device=x.device)
+        need = ctypes.c_size_t(0)
+        check(lib().garnet_b200_moe_route_workspace(ctypes.byref(self.opt), tokens, ctypes.byref(need)))
+        ws = torch.empty(need.value, dtype=torch.uint8, device=x.device)
+        # the router as `run` evaluates it for this token count
+        check(lib().garnet_b200_moe_route_ws(self._h, x2.data_ptr(), selected.data_ptr(), probs.data_ptr(),
+                                             logits.data_ptr(), tokens, ws.data_ptr(), ws.numel(), _stream_ptr()))
+        return logits, selected, probs
+
+    def route_fp32(self, x: torch.Tensor):
+        """Router on the fp32 pipe at every size (garnet_b200_moe_route)."""
+        x2 = x.reshape(-1, self.opt.hidden).contiguous()
+        tokens = x2.shape[0]
+        logits = torch.empty(tokens, self.opt.experts, dtype=torch.float32, device=x.device)
+        selected = torch.empty(tokens, self.opt.top_k, dtype=torch.int32, device=x.device)
+        probs = torch.empty(tokens, self.opt.top_k, dtype=torch.float32, device=x.device)
         check(lib().garnet_b200_moe_route(self._h, x2.data_ptr(), selected.data_ptr(), probs.data_ptr(),
                                           logits.data_ptr(), tokens, _stream_ptr()))
         return logits, selected, probs
@@ -120,6 +135,28 @@ class GptOssMoe:
                                              ws.data_ptr(), ws.numel(), _stream_ptr()))
         return vals
 
+    def run_rows_hidden(self, rows_x: torch.Tensor, row_expert: torch.Tensor) -> torch.Tensor:
+        """First half of run_rows: SwiGLU activations [rows, intermediate] fp32 (bf16-valued)."""
+        x2 = rows_x.reshape(-1, self.opt.hidden).contiguous()
+        rows = x2.shape[0]
+        hid = torch.zeros(rows, self.opt.intermediate, dtype=torch.float32, device=x2.device)
+        ws = torch.empty(self.rows_workspace_bytes(rows), dtype=torch.uint8, device=x2.device)
+        ex = row_expert.to(torch.int32).contiguous()
+        check(lib().garnet_b200_moe_run_rows_stage(self._h, 1, x2.data_ptr(), ex.data_ptr(), rows, hid.data_ptr(), None,
+                                                   ws.data_ptr(), ws.numel(), _stream_ptr()))
+        return hid
+
+    def run_rows_down(self, hidden: torch.Tensor, row_expert: torch.Tensor) -> torch.Tensor:
+        """Second half of run_rows: per-row values [rows, hidden] from given activations."""
+        h2 = hidden.reshape(-1, self.opt.intermediate).float().contiguous()
+        rows = h2.shape[0]
+        vals = torch.zeros(rows, self.opt.hidden, dtype=torch.float32, device=h2.device)
+        ws = torch.empty(self.rows_workspace_bytes(rows), dtype=torch.uint8, device=h2.device)
+        ex = row_expert.to(torch.int32).contiguous()
+        check(lib().garnet_b200_moe_run_rows_stage(self._h, 2, None, ex.data_ptr(), rows, h2.data_ptr(), vals.data_ptr(),
+                                                   ws.data_ptr(), ws.numel(), _stream_ptr()))
+        return vals
+
     def combine(self, vals: torch.Tensor, probs: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """y[t] = bf(sum_j vals[t*k+j] * probs[t, j]) in router order."""
         tokens = probs.shape[0]
@@ -129,7 +166,7 @@ class GptOssMoe:
         return y
 
     def dequantized(self, which: int, stored_expert: int) -> torch.Tensor:
-        rows, cols = (2 * self.opt.intermediate, self.opt.hidden) if which == 0 else (self.opt.hidden, self.opt.intermediate)
+        rows, cols = (2 * self.opt.intermediate, self.opt.hidden) if which in (0, 2) else (self.opt.hidden, self.opt.intermediate)
         out = torch.empty(rows, cols, dtype=torch.float32, device="cuda")
         check(lib().garnet_b200_moe_dequant(self._h, which, stored_expert, out.data_ptr(), _stream_ptr()))
         return out

@@ -255,8 +255,10 @@ int garnet_b200_moe_workspace(const garnet_b200_moe_options* options, int tokens
 int garnet_b200_moe_create(const garnet_b200_moe_options* options, const void* const* weights, void* stream,
                            garnet_b200_moe_t* out);
 
-/* y[tokens, hidden] = MoE(x[tokens, hidden]); x and y are of io_dtype.  No
- * allocation, no synchronisation.  RunGptOssMoe / GptOssMarlin::Run
+/* y[tokens, hidden] = MoE(x[tokens, hidden]); x and y are of io_dtype and 16-byte
+ * aligned (as are the row and value buffers of every entry point below; the
+ * kernels use 16-byte vector accesses, and a misaligned pointer is rejected with
+ * INVALID_VALUE before anything is launched).  No allocation, no synchronisation.  RunGptOssMoe / GptOssMarlin::Run
  * (gpt_oss_kernels.h:42-43, gpt_oss_marlin.h:28-29).  With ep_world > 1 the output
  * is this rank's unrounded partial sum (gpt_oss_kernels.cu:810). */
 int garnet_b200_moe_run(garnet_b200_moe_t h, const void* d_x, void* d_y, void* d_workspace, size_t workspace_bytes,
@@ -276,8 +278,11 @@ int garnet_b200_moe_run(garnet_b200_moe_t h, const void* d_x, void* d_y, void* d
  *     the gpt-oss-120b layer (hidden = intermediate = 2880, 128 experts, top-4).
  *     Larger requests are rejected with INVALID_VALUE and a message that names the
  *     largest token count that fits.
- *   - The first call on each device looks up the array's device address; make that
- *     first call before starting any stream capture on that device.
+ *   - The array's device address is looked up once per device by
+ *     garnet_b200_moe_create (with that device current), never by this call; create
+ *     the handle before starting any stream capture on that device.  The call must
+ *     be made with the device current on which the handle was created; any other
+ *     device is rejected with INVALID_VALUE.
  *   - All calls on a device share the one array, and it keeps the previous call's
  *     contents.  Nothing needs clearing between calls, but two calls whose kernels
  *     overlap on the GPU (different streams, or different handles at once) race on
@@ -306,6 +311,17 @@ int garnet_b200_moe_rows_workspace(const garnet_b200_moe_options* options, int r
 int garnet_b200_moe_run_rows(garnet_b200_moe_t h, const void* d_rows, const int* d_row_expert, int rows,
                              float* d_vals, void* d_workspace, size_t workspace_bytes, void* stream);
 
+/* The two halves of garnet_b200_moe_run_rows on their own, as the reference runs
+ * them (gate/up GEMM + activation, then the down GEMM:
+ * plugins/gpt_oss/cuda/gpt_oss_marlin.cu:632-644):
+ *   stage 1: d_hidden[r, :] (fp32 [rows, intermediate], bf16-valued) =
+ *            SwiGLU(d_rows[r, :] . w_gate_up[e] + b); d_vals is not used;
+ *   stage 2: d_vals[r, :] = bf(bf(d_hidden[r, :] . w_down[e]) + bd[e]); d_rows is not used.
+ * Same workspace as garnet_b200_moe_run_rows.  Lets each projection be checked
+ * against the reference arithmetic by itself. */
+int garnet_b200_moe_run_rows_stage(garnet_b200_moe_t h, int stage, const void* d_rows, const int* d_row_expert, int rows,
+                                   float* d_hidden, float* d_vals, void* d_workspace, size_t workspace_bytes, void* stream);
+
 /* y[t, :] = bf(sum_j d_vals[t * top_k + j, :] * d_probs[t, j]), j in router order
  * (combineExperts, gpt_oss_kernels.cu:907-921). */
 int garnet_b200_moe_combine(garnet_b200_moe_t h, const float* d_vals, const float* d_probs, void* d_y, int tokens,
@@ -317,13 +333,35 @@ int garnet_b200_moe_combine(garnet_b200_moe_t h, const float* d_vals, const floa
 int garnet_b200_moe_route(garnet_b200_moe_t h, const void* d_x, int* d_selected, float* d_probs, float* d_logits,
                           int tokens, void* stream);
 
+/* The router exactly as garnet_b200_moe_run evaluates it for the same token count (many
+ * tokens: scores on the tensor cores, the fp32 router weight as three bf16 terms with
+ * fp32 accumulation; garnet_b200_moe_route always uses the fp32 pipe, and its logits
+ * can differ from these in the last bf16 step).  The expert-parallel flow routes with
+ * this entry point.  Workspace size from garnet_b200_moe_route_workspace. */
+int garnet_b200_moe_route_workspace(const garnet_b200_moe_options* options, int tokens, size_t* bytes);
+int garnet_b200_moe_route_ws(garnet_b200_moe_t h, const void* d_x, int* d_selected, float* d_probs, float* d_logits,
+                             int tokens, void* d_workspace, size_t workspace_bytes, void* stream);
+
 /* Decodes rows x 32 MXFP4 values (16 bytes and one e8m0 byte per row) to fp32.
  * TestGptOssMxfp4Decode (gpt_oss_kernels.h:65). */
 int garnet_b200_mxfp4_decode(const uint8_t* d_blocks, const uint8_t* d_scales, float* d_out, int rows, void* stream);
 
 /* Writes one stored expert matrix (which = 0: gate_up [2I,H], 1: down [H,I]) as
- * fp32 in the original row order, decoded from the packed tiles. */
+ * fp32 in the original row order, decoded from the packed tiles of the streaming
+ * kernels; which = 2, 3: the same two matrices decoded from the second copy, the
+ * blocks and scale atoms that the block-scaled tensor-core kernels read
+ * (cf. the reference's packed-weight check, test2026/gpt_oss/marlin_weight_pack.cpp:54-78). */
 int garnet_b200_moe_dequant(garnet_b200_moe_t h, int which, int stored_expert, float* d_out, void* stream);
+
+/* The activation format of the block-scaled tensor-core path, on its own: every
+ * 32-block of a bf16 row [rows, k] becomes two e4m3 rows (d_hi, d_lo: [rows, k] bytes)
+ * that share one e8m0 scale byte (d_scales: [rows, k/32]): x = (hi + lo) * 2^(scale-127),
+ * exactly for elements within 2^-9 of the block's largest magnitude and to 2^-17 of it
+ * otherwise.  A block that holds an infinity or a NaN gets scale byte 255 (NaN).  For
+ * checks of the split; the reference keeps activations in bf16
+ * (plugins/gpt_oss/cuda/gpt_oss_marlin.cu:586-590). */
+int garnet_b200_mx_split_rows(const void* d_x_bf16, int rows, int k, uint8_t* d_hi, uint8_t* d_lo, uint8_t* d_scales,
+                              void* stream);
 
 /* Non-zero when a bounded device-side wait gave up (see garnet_b200_w4a16_fault). */
 int garnet_b200_moe_fault(garnet_b200_moe_t h);

@@ -234,6 +234,35 @@ def moe_experts(x, selected, probs, gu_blocks, gu_scales, gu_bias, dn_blocks, dn
     return (y, mass) if want_mass else y
 
 
+def moe_rows_hidden(x_rows, row_expert, gu_blocks, gu_scales, gu_bias, hidden, inter, limit=7.0):
+    """SwiGLU activations [rows, inter] of already routed rows (one expert per row)."""
+    x = _c(x_rows, np.float32).reshape(-1, hidden)
+    ex = _c(row_expert, np.int32).reshape(-1)
+    gb, gs, gbi = _c(gu_blocks, np.uint8), _c(gu_scales, np.uint8), _c(gu_bias, np.float32)
+    out = np.empty((x.shape[0], inter), dtype=np.float32)
+    L = lib()
+    L.orc_moe_rows_hidden.restype = None
+    L.orc_moe_rows_hidden.argtypes = [_f32p, _i32p, _u8p, _u8p, _f32p, ctypes.c_long, ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_float, _f32p]
+    L.orc_moe_rows_hidden(_p(x, _f32p), _p(ex, _i32p), _p(gb, _u8p), _p(gs, _u8p), _p(gbi, _f32p), x.shape[0], hidden,
+                          inter, limit, _p(out, _f32p))
+    return out
+
+
+def moe_rows_down(h_rows, row_expert, dn_blocks, dn_scales, dn_bias, hidden, inter):
+    """Per-row values bf(bf(h . w_down) + b) [rows, hidden] for given activations."""
+    h = _c(h_rows, np.float32).reshape(-1, inter)
+    ex = _c(row_expert, np.int32).reshape(-1)
+    db, ds, dbi = _c(dn_blocks, np.uint8), _c(dn_scales, np.uint8), _c(dn_bias, np.float32)
+    out = np.empty((h.shape[0], hidden), dtype=np.float32)
+    L = lib()
+    L.orc_moe_rows_down.restype = None
+    L.orc_moe_rows_down.argtypes = [_f32p, _i32p, _u8p, _u8p, _f32p, ctypes.c_long, ctypes.c_int, ctypes.c_int, _f32p]
+    L.orc_moe_rows_down(_p(h, _f32p), _p(ex, _i32p), _p(db, _u8p), _p(ds, _u8p), _p(dbi, _f32p), h.shape[0], hidden,
+                        inter, _p(out, _f32p))
+    return out
+
+
 def moe_forward(x, router_w, router_b, gu_blocks, gu_scales, gu_bias, dn_blocks, dn_scales, dn_bias,
                 hidden, inter, experts, topk, limit=7.0):
     """Route + experts; returns (y, logits, selected, probs)."""

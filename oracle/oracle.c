@@ -414,3 +414,52 @@ ORC_API void orc_moe_experts(const float* x, const int32_t* selected, const floa
         free(ms);
     }
 }
+
+/* The two halves of the expert computation on already routed rows, one expert per
+ * row (plugins/gpt_oss/cuda/gpt_oss_kernels.cu:762-811: gateUp, then down):
+ *   hidden[r, i] = bf( bf( g * bf(sigmoid(bf(1.702 g))) ) * bf(u + 1) ),
+ *                  g = min(bf(bf(x . w_gate_i) + b), limit), u = clamp(bf(bf(x . w_up_i) + b), +-limit);
+ *   vals[r, d]   = bf( bf(hidden[r, :] . w_down_d) + b_down_d ).
+ * Checking them separately keeps a one-step difference in a bf16 rounding of the
+ * first half (legitimate: it depends on the fp32 summation order) from being
+ * amplified by the second. */
+ORC_API void orc_moe_rows_hidden(const float* x, const int32_t* row_expert, const uint8_t* gu_blocks,
+                                 const uint8_t* gu_scales, const float* gu_bias, long rows, int hidden,
+                                 int inter, float limit, float* out)
+{
+#pragma omp parallel for schedule(dynamic, 1)
+    for (long r = 0; r < rows; ++r) {
+        const int e = row_expert[r];
+        const float* xt = x + r * hidden;
+        for (int i = 0; i < inter; ++i) {
+            const size_t row = (size_t)e * 2 * inter + 2 * (size_t)i;
+            float g = 0.f, u = 0.f;
+            for (int d = 0; d < hidden; ++d) {
+                g += xt[d] * mxfp4_at(gu_blocks, gu_scales, row, d, hidden);
+                u += xt[d] * mxfp4_at(gu_blocks, gu_scales, row + 1, d, hidden);
+            }
+            g = fminf(bf(bf(g) + gu_bias[row]), limit);
+            u = fminf(limit, fmaxf(-limit, bf(bf(u) + gu_bias[row + 1])));
+            const float glu = bf(g * bf(1.f / (1.f + expf(-bf(1.702f * g)))));
+            out[r * inter + i] = bf(glu * bf(u + 1.f));
+        }
+    }
+}
+
+ORC_API void orc_moe_rows_down(const float* h, const int32_t* row_expert, const uint8_t* dn_blocks,
+                               const uint8_t* dn_scales, const float* dn_bias, long rows, int hidden,
+                               int inter, float* out)
+{
+#pragma omp parallel for schedule(dynamic, 1)
+    for (long r = 0; r < rows; ++r) {
+        const int e = row_expert[r];
+        const float* hr = h + r * inter;
+        for (int d = 0; d < hidden; ++d) {
+            const size_t row = (size_t)e * hidden + (size_t)d;
+            float v = 0.f;
+            for (int i = 0; i < inter; ++i) v += hr[i] * mxfp4_at(dn_blocks, dn_scales, row, i, inter);
+            out[r * hidden + d] = bf(bf(v) + dn_bias[row]);
+        }
+    }
+}
+

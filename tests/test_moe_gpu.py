@@ -122,7 +122,7 @@ def test_mxfp4_decode_all_codes_and_scales_bit_exact():
     assert np.array_equal(got[:255].view(np.uint32), expect[:255].view(np.uint32))
 
 
-@pytest.mark.parametrize("h,inter", [(32, 32), (96, 64), (2880, 64), (64, 2880)])
+@pytest.mark.parametrize("h,inter", [(32, 32), (96, 64), (2880, 64), (64, 2880), (480, 256)])
 def test_packed_expert_matrices_decode_bit_exact(h, inter):
     case = synth.moe_layer(1, h, inter, experts=3, topk=2, seed=h + inter)
     case["gu_scales"][0, :5, 0] = [0, 1, 254, 255, 2]       # subnormal, NaN and extreme scales
@@ -134,6 +134,8 @@ def test_packed_expert_matrices_decode_bit_exact(h, inter):
         ed = oracle.mxfp4_dequant(case["dn_blocks"][e], case["dn_scales"][e], h, inter)
         same = lambda a, b: np.array_equal(a.view(np.uint32)[~np.isnan(b)], b.view(np.uint32)[~np.isnan(b)]) and np.array_equal(np.isnan(a), np.isnan(b))
         assert same(up, eu) and same(dn, ed)
+        # the second copy (15 KiB blocks of 240 rows + scale atoms of the block-scaled kernels)
+        assert same(moe.dequantized(2, e).cpu().numpy(), eu) and same(moe.dequantized(3, e).cpu().numpy(), ed)
 
 
 @pytest.mark.parametrize("tokens", [1, 3, 17, 65])
@@ -258,18 +260,211 @@ def test_rows_entry_point_and_combine_match_full_operator():
     assert torch.equal(vals.bfloat16().float(), vals)
 
 
+def check_rows_in_two_halves(moe, case, rows, row_expert_dev, pick, what, expert_base=0):
+    """Per-row values BEFORE the weighted sum, in the plain form |a - e| <= 1e-2 (1 + |e|), one
+    projection at a time: the SwiGLU activations against the oracle's, then the down
+    projection of the DEVICE's activations against the oracle's down projection of the
+    same activations (so that a one-step difference in a bf16 rounding of an activation,
+    which depends on the fp32 summation order, is not amplified 2880-fold); the two
+    halves together are bit-for-bit what the one-call form returns."""
+    hid = moe.run_rows_hidden(rows, row_expert_dev)
+    vals = moe.run_rows(rows, row_expert_dev)
+    torch.cuda.synchronize()
+    assert moe.fault() == 0
+    assert torch.equal(moe.run_rows_down(hid, row_expert_dev), vals)
+    sel = torch.from_numpy(pick).cuda()
+    experts = row_expert_dev[sel].cpu().numpy() - expert_base
+    x_rows = rows[sel].float().cpu().numpy()
+    h_dev = hid[sel].cpu().numpy()
+    h_ref = oracle.moe_rows_hidden(x_rows, experts, case["gu_blocks"], case["gu_scales"], case["gu_bias"].reshape(-1),
+                                   case["hidden"], case["inter"])
+    # An activation is the end of a chain of six bf16 roundings (g, u, 1.702 g, the sigmoid,
+    # the two products: gpt_oss_kernels.cu:786-789) fed by two 2880-term fp32 sums whose
+    # order differs between any two implementations.  A sum that lands on the other side
+    # of a rounding boundary moves g or u by one bf16 step (2^-8), and the chain can turn
+    # that into a few steps of the result (d ln(g sigmoid(1.702 g)) / d ln g <= 1.3, plus one
+    # step per later rounding that flips): the bound is 8 steps, nearly all values agree
+    # to two steps, and most are identical.
+    assert_close(h_dev, h_ref, 8 * 2.0 ** -8, what + ": activations")
+    assert (np.abs(h_dev - h_ref) <= 2.0 ** -7 * np.abs(h_ref) + 1e-6).mean() >= 0.999
+    assert (h_dev == h_ref).mean() >= 0.9
+    v_ref = oracle.moe_rows_down(h_dev, experts, case["dn_blocks"], case["dn_scales"], case["dn_bias"].reshape(-1),
+                                 case["hidden"], case["inter"])
+    assert_close(vals[sel].cpu().numpy(), v_ref, 1e-2, what + ": per-row values")
+    return vals
+
+
+def positions_in_expert(slots_expert):
+    """Position of every slot inside its expert's run of the stable slot order."""
+    order = np.argsort(slots_expert, kind="stable")
+    counts = np.bincount(slots_expert, minlength=slots_expert.max() + 1)
+    starts = np.concatenate([[0], np.cumsum(counts)[:-1]])
+    pos = np.empty_like(order)
+    pos[order] = np.arange(order.size) - starts[slots_expert[order]]
+    return pos, counts
+
+
+def test_gpt_oss_120b_layer_at_4096_tokens_per_slot_values_and_output():
+    """The configuration the MoE throughput is quoted on: 4096 tokens, 128 experts, top-4
+    (128 +- 11 rows per expert: many experts own a full 128-row tile and a nearly empty
+    second one).  Per-slot values BEFORE the weighted sum, in the plain form
+    |a - e| <= 1e-2 (1 + |e|), on slots that include second-tile rows; every output column
+    (hence every 240-row weight tile, the last one too) is compared.  Then sampled outputs."""
+    tokens = 4096
+    case = synth.moe_layer(tokens, seed=11, bias_scale=0.05)
+    moe = build(case, io_dtype=torch.bfloat16)
+    x = dev(case["x"]).bfloat16()
+    _, sel_t, pr_t = moe.route(x)
+    sel, pr = sel_t.cpu().numpy(), pr_t.cpu().numpy()
+    slots = sel.reshape(-1)
+    rows = x[torch.arange(slots.size, device="cuda") // 4]
+    pos, counts = positions_in_expert(slots)
+    assert counts.max() > 128 and counts.min() > 0
+    rng = np.random.default_rng(1)
+    second_tile = np.flatnonzero(pos >= 128)
+    last_of_expert = np.flatnonzero(pos == counts[slots] - 1)
+    pick = np.unique(np.concatenate([rng.choice(second_tile, min(32, second_tile.size), replace=False),
+                                     rng.choice(last_of_expert, 16, replace=False),
+                                     rng.choice(slots.size, 24, replace=False)]))
+    assert (pos[pick] >= 128).sum() >= 16
+    vals = check_rows_in_two_halves(moe, case, rows, sel_t.reshape(-1), pick, "4096 tokens")
+    # the one-call operator gives the combine of exactly these values
+    y = moe.run(x)
+    assert torch.equal(moe.combine(vals, pr_t), y)
+    tok = rng.choice(tokens, 16, replace=False)
+    exp_y, mass = oracle.moe_experts(case["x"][tok], sel[tok], pr[tok], *oracle_args(case), want_mass=True)
+    assert_close(y[torch.from_numpy(tok).cuda()].float().cpu().numpy(), exp_y, 1e-2, "outputs at 4096 tokens", mass)
+
+
+def test_zipf_routed_rows_on_the_busiest_of_eight_ranks():
+    """The expert-parallel configuration on one GPU: 8192 tokens routed with Zipf(1.1)
+    popularity; the rank that owns the most popular block of 16 experts receives several
+    times the mean load (experts with thousands of rows beside experts with none)."""
+    tokens, world = 8192, 8
+    case = synth.moe_layer(tokens, seed=12, zipf_s=1.1, bias_scale=0.05)
+    _, sel, _ = oracle.moe_route(case["x"], case["router_w"], case["router_b"], 128, 4)
+    slots = sel.reshape(-1)
+    per = 128 // world
+    load = np.bincount(slots // per, minlength=world)
+    rank = int(load.argmax())
+    assert load[rank] > 1.5 * load.mean()
+    local = dict(case)
+    for k in ("gu_blocks", "gu_scales", "gu_bias", "dn_blocks", "dn_scales", "dn_bias"):
+        local[k] = case[k][rank * per:(rank + 1) * per]
+    owner = build(local, ep_rank=rank, ep_world=world, expert_weights_sharded=True, io_dtype=torch.bfloat16)
+    mine = np.flatnonzero(slots // per == rank)
+    rng = np.random.default_rng(2)
+    mine = mine[rng.permutation(mine.size)]                         # arrival order of an exchange
+    rows = dev(case["x"][mine // 4]).bfloat16()
+    counts = np.bincount(slots[mine] - rank * per, minlength=per)
+    assert counts.max() > 1000
+    pos, _ = positions_in_expert(slots[mine])
+    pick = np.unique(np.concatenate([rng.choice(mine.size, 40, replace=False), np.flatnonzero(pos >= 1024)[:8],
+                                     np.flatnonzero(pos == 0)]))
+    check_rows_in_two_halves(owner, local, rows, dev(slots[mine].astype(np.int32)), pick, "zipf rows", expert_base=rank * per)
+
+
+def e4m3_decode(codes):
+    c = codes.astype(np.int32)
+    sign = np.where(c & 0x80, -1.0, 1.0)
+    e, m = (c >> 3) & 15, c & 7
+    mag = np.where(e == 0, m / 8.0 * 2.0 ** -6, (1 + m / 8.0) * 2.0 ** (e - 7.0))
+    return np.where((c & 0x7f) == 0x7f, np.nan, sign * mag)
+
+
+def test_activation_split_into_two_e4m3_pieces():
+    """x = (hi + lo) * 2^(s - 127): exact within 2^-9 of the block's largest magnitude, to
+    2^-17 of it otherwise; adversarial blocks: one huge value among tiny ones, all zeros,
+    bf16 subnormals, the largest finite bf16, signed zeros; an infinity or a NaN makes
+    the block's scale NaN (the reference, which keeps activations in bf16, produces an
+    infinity or a NaN from them as well)."""
+    rng = np.random.default_rng(3)
+    k = 32 * 12
+    x = oracle.bf16_round(rng.normal(0, 1, size=(64, k)).astype(np.float32))
+    x[0, :32] = 0.0
+    x[1, :32] = np.float32(2.0) ** -20 * rng.normal(size=32); x[1, 5] = 3.0e4        # one huge, many tiny
+    x[2, :32] = np.float32(2.0) ** -130 * np.arange(32)                               # bf16 subnormals
+    x[3, :32] = np.float32(3.3895314e38)                                              # largest finite bf16
+    x[4, :32] = -0.0
+    x[5, :64] = rng.normal(size=64) * np.float32(2.0) ** 60
+    x[6, 32:64] = rng.normal(size=32); x[6, 40] = np.inf
+    x[7, 64:96] = rng.normal(size=32); x[7, 70] = np.nan
+    x = oracle.bf16_round(x)
+    rows = x.shape[0]
+    xd = torch.from_numpy(oracle.bf16_bits(x).view(np.int16)).view(torch.bfloat16).reshape(rows, k).cuda()
+    hi = torch.empty(rows, k, dtype=torch.uint8, device="cuda")
+    lo = torch.empty_like(hi)
+    sc = torch.empty(rows, k // 32, dtype=torch.uint8, device="cuda")
+    from garnet_b200._lib import check
+    check(garnet_b200.lib().garnet_b200_mx_split_rows(xd.data_ptr(), rows, k, hi.data_ptr(), lo.data_ptr(), sc.data_ptr(), None))
+    torch.cuda.synchronize()
+    h, l, s = e4m3_decode(hi.cpu().numpy()), e4m3_decode(lo.cpu().numpy()), sc.cpu().numpy().astype(np.int32)
+    scale = np.repeat(np.where(s == 255, np.nan, 2.0 ** (s - 127.0)), 32, axis=1)
+    back = (h + l) * scale
+    blocks = x.astype(np.float64).reshape(rows, k // 32, 32)
+    amax = np.repeat(np.abs(blocks).max(axis=2), 32, axis=1)
+    finite = np.isfinite(amax)
+    assert (s[6, 1] == 255) and (s[7, 2] == 255) and np.isnan(back[6, 32:64]).all() and np.isnan(back[7, 64:96]).all()
+    assert np.isfinite(back[finite]).all()
+    err = np.abs(back - x.astype(np.float64))
+    # blocks whose scale byte was clamped at 1 (subnormal range) keep absolute accuracy 2^-126 * 2^-9
+    floor = 2.0 ** -140
+    assert (err[finite] <= amax[finite] * 2.0 ** -17 + floor).all()
+    near = finite & (np.abs(x) >= amax * 2.0 ** -9) & (amax >= 2.0 ** -100)
+    assert (back[near] == x[near]).all()
+    assert (back[0, :32] == 0).all() and (back[4, :32] == 0).all()
+
+
+def test_no_alloc_limit_and_argument_checks():
+    """Largest token count the built-in scratch holds at the gpt-oss-120b widths, and
+    misaligned pointers: rejected before any launch."""
+    import ctypes
+    case = synth.moe_layer(4, 64, 64, experts=8, topk=4, seed=1)
+    moe = build(case, io_dtype=torch.bfloat16)
+    L = garnet_b200.lib()
+    x = torch.zeros(8, 64, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty_like(x)
+    ws = torch.empty(moe.workspace_bytes(4), dtype=torch.uint8, device="cuda")
+    assert L.garnet_b200_moe_run(moe._h, x.data_ptr() + 2, y.data_ptr(), ws.data_ptr(), ws.numel(), 4, None) == 1
+    assert b"aligned" in L.garnet_b200_last_error()
+    assert L.garnet_b200_moe_run(moe._h, x.data_ptr(), y.data_ptr() + 8, ws.data_ptr(), ws.numel(), 4, None) == 1
+    assert L.garnet_b200_moe_run_static(moe._h, x.data_ptr() + 4, y.data_ptr(), 4, None) == 1
+    assert L.garnet_b200_moe_run_static(moe._h, x.data_ptr(), y.data_ptr(), 2 ** 31 - 1, None) == 1   # returns at once
+    vals = torch.empty(16, 64, dtype=torch.float32, device="cuda")
+    ex = torch.zeros(16, dtype=torch.int32, device="cuda")
+    assert L.garnet_b200_moe_run_rows(moe._h, x.data_ptr() + 2, ex.data_ptr(), 8, vals.data_ptr(), ws.data_ptr(), ws.numel(), None) == 1
+    assert L.garnet_b200_moe_combine(moe._h, vals.data_ptr() + 4, vals.data_ptr(), y.data_ptr(), 2, None) == 1
+    # the documented limit at the gpt-oss-120b layer widths
+    sz = ctypes.c_size_t(0)
+    opt = garnet_b200.MoeOptions(abi=1, struct_size=ctypes.sizeof(garnet_b200.MoeOptions), hidden=2880, intermediate=2880,
+                                 experts=128, top_k=4, io_dtype=1, limit=7.0)
+    fits = lambda t: L.garnet_b200_moe_workspace(ctypes.byref(opt), t, ctypes.byref(sz)) == 0 and sz.value <= (8 << 20)
+    assert fits(NO_ALLOC_TOKENS_120B) and not fits(NO_ALLOC_TOKENS_120B + 1)
+
+
+NO_ALLOC_TOKENS_120B = 111
+
+
+def _rerun_with_switch(value, selection):
+    import subprocess
+    import sys
+    if os.environ.get("GARNET_B200_MOE_MX") == value:
+        pytest.skip("already running with this switch")
+    env = dict(os.environ, GARNET_B200_MOE_MX=value)
+    here = os.path.dirname(os.path.abspath(__file__))
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_moe_gpu.py"), "-m", "gpu", "-q", "-x",
+                        "-k", selection], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
 def test_block_scaled_path_at_every_size():
     """Small batches normally take the streaming kernel; GARNET_B200_MOE_MX=2 sends every
     size through the block-scaled tensor-core path.  The switch is read once per process,
     so the fixture and golden parity tests are re-run in a child process with it set."""
-    import os
-    import subprocess
-    import sys
-    if os.environ.get("GARNET_B200_MOE_MX") == "2":
-        pytest.skip("already running with the block-scaled path forced")
-    env = dict(os.environ, GARNET_B200_MOE_MX="2")
-    here = os.path.dirname(os.path.abspath(__file__))
-    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_moe_gpu.py"), "-m", "gpu", "-q", "-x",
-                        "-k", "fixtures or golden or bf16_io or rows"], env=env, capture_output=True, text=True,
-                       timeout=900)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    _rerun_with_switch("2", "fixtures or golden or bf16_io or rows_entry")
+
+
+def test_streaming_path_at_every_size():
+    """GARNET_B200_MOE_MX=0 keeps every size on the streaming kernel: the path a handle
+    takes when the block-scaled copy cannot be built (no tensor-map encoder in the driver)."""
+    _rerun_with_switch("0", "fixtures or golden or bf16_io or rows_entry")

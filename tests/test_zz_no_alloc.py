@@ -51,6 +51,29 @@ def test_static_scratch_matches_workspace_entry_point_twice():
         assert torch.equal(got, expected)
 
 
+def test_static_scratch_allocates_nothing_and_survives_stale_block_scaled_scratch():
+    """Two calls large enough for the block-scaled kernels (more than six rows per expert),
+    the second with fewer tokens over the first one's leftovers; device memory in use does
+    not change across the calls (neither through torch's allocator nor through the driver)."""
+    case = synth.moe_layer(20, hidden=512, inter=512, experts=8, topk=4, seed=21, bias_scale=0.05)
+    moe = build(case)
+    x_first = dev(case["x"])
+    x_second = dev(synth.moe_layer(16, hidden=512, inter=512, experts=8, topk=4, seed=22)["x"])
+    expected = [moe.run(x) for x in (x_first, x_second)]
+    outs = [torch.empty_like(x) for x in (x_first, x_second)]
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    held_before = torch.cuda.memory_allocated()
+    for x, y in zip((x_first, x_second), outs):
+        moe.run_static(x, out=y)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == held_before
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert moe.fault() == 0
+    for y, e in zip(outs, expected):
+        assert torch.equal(y, e)
+
+
 def test_static_scratch_rejects_what_does_not_fit():
     case = synth.moe_layer(1, hidden=2880, inter=2880, experts=8, topk=4, seed=13)
     moe = build(case)
