@@ -366,7 +366,7 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
-def bench_moe(torch, gb, peaks, args, token_counts=(1, 32, 512, 4096)):
+def bench_moe(torch, gb, peaks, args, token_counts=(1, 32, 512, 4096), cpu_rows=True):
     """gpt-oss-120b MoE layer (hidden = intermediate = 2880, 128 experts, top-4, MXFP4), one GPU.
     tok/s per token count; a step = one call of the operator.  To keep weight reads
     out of L2 at small T, a graph holds several calls on different token sets
@@ -378,10 +378,11 @@ def bench_moe(torch, gb, peaks, args, token_counts=(1, 32, 512, 4096)):
     u8 = lambda *shape, lo=0, hi=256: torch.randint(lo, hi, shape, dtype=torch.uint8, device="cuda", generator=gen)
     router_w = (torch.randn(E, H, device="cuda", generator=gen) / H ** 0.5).to(torch.bfloat16).float()
     router_b = torch.zeros(E, device="cuda")
-    moe = gb.GptOssMoe(H, I, E, K, io_dtype=torch.bfloat16).prepare(
-        router_w, router_b, u8(E, 2 * I, H // 32, 16), u8(E, 2 * I, H // 32, lo=117, hi=124),
-        torch.zeros(E, 2 * I, device="cuda"), u8(E, H, I // 32, 16), u8(E, H, I // 32, lo=117, hi=124),
-        torch.zeros(E, H, device="cuda"))
+    tensors = [router_w, router_b, u8(E, 2 * I, H // 32, 16), u8(E, 2 * I, H // 32, lo=117, hi=124),
+               torch.zeros(E, 2 * I, device="cuda"), u8(E, H, I // 32, 16), u8(E, H, I // 32, lo=117, hi=124),
+               torch.zeros(E, H, device="cuda")]
+    moe = gb.GptOssMoe(H, I, E, K, io_dtype=torch.bfloat16).prepare(*tensors)
+    host = [t.cpu().numpy() for t in tensors] if cpu_rows else None      # the same layer for the CPU restatement
     per_expert = 5760 * 2880 // 2 + 5760 * 90 + 2880 * 2880 // 2 + 2880 * 90
     rows = []
     for T in token_counts:
@@ -397,16 +398,64 @@ def bench_moe(torch, gb, peaks, args, token_counts=(1, 32, 512, 4096)):
 
         steps = max(3, min(args.steps, 20 if T <= 512 else 5))
         ms = time_graph(torch, body, steps, 3) / rot
+        assert moe.fault() == 0, "a device-side wait gave up"
+        # end to end: pinned host tokens in, the layer, pinned host result out, one synchronisation per call
+        xh = [x.cpu().pin_memory() for x in xs]
+        yh = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+        xd = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+
+        def host_call(i):
+            xd.copy_(xh[i % rot], non_blocking=True)
+            moe.run(xd, out=y, workspace=ws)
+            yh.copy_(y, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return float(yh[0, 0])
+
+        for i in range(3):
+            host_call(i)
+        n_e2e = max(3, min(args.steps, 10))
+        t0 = time.perf_counter()
+        for i in range(n_e2e):
+            host_call(i)
+        e2e_ms = (time.perf_counter() - t0) / n_e2e * 1e3
         bytes_ = distinct * per_expert + T * H * 2 * 2
         flops = 199065600.0 * T
-        rows.append({"tokens": T, "ms": round(ms, 4), "tok_per_s": round(T / (ms * 1e-3), 1),
-                     "distinct_experts": round(distinct, 1), "GBps": round(bytes_ / (ms * 1e-3) / 1e9, 1),
-                     "hbm_frac": round(bytes_ / (ms * 1e-3) / 1e9 / peaks["hbm"], 4),
-                     "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 2),
-                     "tensor_frac": round(flops / (ms * 1e-3) / 1e12 / peaks["tf_sus"], 4), "calls_per_graph": rot})
+        row = {"tokens": T, "ms": round(ms, 4), "tok_per_s": round(T / (ms * 1e-3), 1),
+               "distinct_experts": round(distinct, 1), "GBps": round(bytes_ / (ms * 1e-3) / 1e9, 1),
+               "hbm_frac": round(bytes_ / (ms * 1e-3) / 1e9 / peaks["hbm"], 4),
+               "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 2),
+               "tensor_frac_burst": round(flops / (ms * 1e-3) / 1e12 / peaks["tf"], 4),
+               "tensor_frac_sustained": round(flops / (ms * 1e-3) / 1e12 / peaks["tf_sus"], 4), "calls_per_graph": rot,
+               "e2e": {"ms": round(e2e_ms, 4), "tok_per_s": round(T / (e2e_ms * 1e-3), 1), "h2d_bytes_per_step": T * H * 2,
+                       "d2h_bytes_per_step": T * H * 2}}
+        if cpu_rows:
+            row["cpu_baseline"] = moe_cpu_baseline(host, xs[0].float().cpu().numpy(), H, I, E, K)
+        rows.append(row)
     del moe
     torch.cuda.empty_cache()
     return rows
+
+
+def moe_cpu_baseline(host, x, H, I, E, K, budget_s=12.0):
+    """The reference has no production CPU MoE; this times the C/OpenMP restatement of its
+    arithmetic (oracle.moe_route + oracle.moe_experts) on the host cores, on all tokens
+    when that fits the time budget, else on a leading subset (stated)."""
+    import oracle
+    T = x.shape[0]
+    threads = os.cpu_count() or 1
+    # a token costs 4 experts x 24.9 M multiply-adds with on-the-fly MXFP4 decode: ~0.15 s on one core
+    est_per_token = 0.15 / max(1, min(threads, 16))
+    sample = int(max(1, min(T, budget_s / est_per_token)))
+    if sample < T:
+        sample = max(threads, sample // threads * threads)
+        sample = min(sample, T)
+    xs = np.ascontiguousarray(x[:sample])
+    t0 = time.perf_counter()
+    _, sel, pr = oracle.moe_route(xs, host[0], host[1], E, K)
+    oracle.moe_experts(xs, sel, pr, host[2], host[3], host[4].reshape(-1), host[5], host[6], host[7].reshape(-1), H, I, E, K)
+    dt = time.perf_counter() - t0
+    return {"value": round(sample / dt, 2), "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"{sample} of {T} tokens (route + experts, C restatement with OpenMP over tokens), {dt:.1f} s"}
 
 
 def bench_moe_ep(torch, dist, gb, args, rank, world, tokens_total=8192):
@@ -554,7 +603,7 @@ def run_profile_case(spec):
         # `moe:T`: the gpt-oss-120b MoE layer on T tokens, 2 warm-up calls + 2 timed calls
         class A:
             steps = 2
-        rows = bench_moe(torch, gb, measured_peaks(), A, token_counts=(int(spec.split(":")[1]),))
+        rows = bench_moe(torch, gb, measured_peaks(), A, token_counts=(int(spec.split(":")[1]),), cpu_rows=False)
         print(json.dumps({"case": spec, **rows[0]}))
         return
     if spec == "pass":

@@ -71,6 +71,25 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_mxfp4_decode.argtypes = [vp, vp, vp, i, vp]
     L.garnet_b200_moe_dequant.argtypes = [vp, i, i, vp, vp]
     L.garnet_b200_mx_split_rows.argtypes = [vp, i, i, vp, vp, vp, vp]
+    L.garnet_b200_comm_create.argtypes = [i, i, sz, c.POINTER(vp)]
+    L.garnet_b200_comm_export.argtypes = [vp, vp, sz]
+    L.garnet_b200_comm_connect.argtypes = [vp, vp]
+    L.garnet_b200_comm_fault.argtypes = [vp]
+    L.garnet_b200_comm_destroy.argtypes = [vp]
+    L.garnet_b200_comm_destroy.restype = None
+    L.garnet_b200_comm_channel_create.argtypes = [vp, sz, c.POINTER(vp)]
+    L.garnet_b200_comm_channel_destroy.argtypes = [vp]
+    L.garnet_b200_comm_channel_destroy.restype = None
+    L.garnet_b200_comm_all_gather.argtypes = [vp, vp, sz, vp, vp]
+    L.garnet_b200_comm_all_reduce.argtypes = [vp, vp, vp, sz, i, vp]
+    L.garnet_b200_comm_selftest_wait.argtypes = [vp, i, vp]
+    L.garnet_b200_moe_ep_arena_bytes.argtypes = [vp, i, i, c.POINTER(sz)]
+    L.garnet_b200_moe_ep_create.argtypes = [vp, vp, i, c.POINTER(vp)]
+    L.garnet_b200_moe_ep_run.argtypes = [vp, vp, vp, i, vp]
+    L.garnet_b200_moe_ep_rows_received.argtypes = [vp]
+    L.garnet_b200_moe_ep_destroy.argtypes = [vp]
+    L.garnet_b200_moe_ep_destroy.restype = None
+    L.garnet_b200_moe_ep_plan_host.argtypes = [vp, i, i, i, vp, vp]
     L.garnet_b200_moe_fault.argtypes = [vp]
     L.garnet_b200_moe_destroy.argtypes = [vp]
     L.garnet_b200_moe_destroy.restype = None

@@ -886,7 +886,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ vals, const float* 
     for (int j = 0; j < topk; ++j) {
         const int slot = token * topk + j;
         if (sh.world > 1 && !expert_is_local(selected[slot], sh)) continue;
-        r += vals[size_t(slot) * hidden + d] * probs[slot];
+        r = __fmaf_rn(vals[size_t(slot) * hidden + d], probs[slot], r);   // one rounding per term, here and in the exchange's combine
     }
     if (round_output) r = bf16_round_f(r);
     if constexpr (sizeof(YT) == 4)

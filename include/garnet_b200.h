@@ -366,6 +366,78 @@ int garnet_b200_mx_split_rows(const void* d_x_bf16, int rows, int k, uint8_t* d_
 /* Non-zero when a bounded device-side wait gave up (see garnet_b200_w4a16_fault). */
 int garnet_b200_moe_fault(garnet_b200_moe_t h);
 
+/* ---- collectives over NVLink (one node, up to 8 ranks) ---------------------------
+ * Replace the reference's two-rank collectives GptOssTpAllReduce, GptOssTpAllReduceBf16
+ * and GptOssTpAllGather (plugins/gpt_oss/cuda/tp_collective.cpp:77-148) and its
+ * peer-memory all-reduce with bounded waits and a fault word
+ * (plugins/gpt_oss/cuda/tp_peer_owner.cuh:30-106).  Every rank (one host thread or
+ * process per GPU, that device current: tp_collective.cpp:82-85) owns an arena of
+ * device memory which its peers map through CUDA IPC; contributions and flags are
+ * stored directly into the destination GPU's own memory, every wait polls local
+ * memory only and gives up after a time limit (status: garnet_b200_comm_fault; the
+ * kernel returns, the context stays usable).  No host synchronisation on the data
+ * path.  Set-up: create -> export a blob -> exchange the blobs of all ranks over any
+ * host channel -> connect.  Objects carved from an arena (channels, the
+ * expert-parallel exchange below) must be created in the same order on every rank. */
+typedef struct garnet_b200_comm* garnet_b200_comm_t;
+typedef struct garnet_b200_channel* garnet_b200_channel_t;
+#define GARNET_B200_COMM_BLOB_BYTES 128
+int garnet_b200_comm_create(int rank, int world, size_t arena_bytes, garnet_b200_comm_t* out);
+int garnet_b200_comm_export(garnet_b200_comm_t comm, void* blob, size_t blob_bytes);
+/* `blobs`: world consecutive blobs in rank order (this rank's own is ignored). */
+int garnet_b200_comm_connect(garnet_b200_comm_t comm, const void* blobs);
+int garnet_b200_comm_fault(garnet_b200_comm_t comm);
+void garnet_b200_comm_destroy(garnet_b200_comm_t comm);
+
+/* A channel carries collectives of up to slot_bytes per rank (two regions of
+ * world x slot_bytes in the arena, alternating from call to call). */
+int garnet_b200_comm_channel_create(garnet_b200_comm_t comm, size_t slot_bytes, garnet_b200_channel_t* out);
+void garnet_b200_comm_channel_destroy(garnet_b200_channel_t channel);
+
+/* d_dst[r] (r = 0..world-1, `bytes` each, contiguous) = d_src of rank r.  One kernel per
+ * rank; bytes a multiple of 16.  GptOssTpAllGather (tp_collective.cpp:124-148); the
+ * N-sharded lm_head gathers its logits with it. */
+int garnet_b200_comm_all_gather(garnet_b200_channel_t channel, const void* d_src, size_t bytes, void* d_dst, void* stream);
+
+/* d_dst[i] = sum over ranks of d_src[i], added in rank order on every rank (so all
+ * ranks hold the same bits).  wire_dtype GARNET_B200_FP32: GptOssTpAllReduce
+ * (tp_collective.cpp:77-98).  GARNET_B200_BF16: contributions travel as bf16 and the
+ * fp32 sum is rounded to bf16, which for two ranks is exactly bf16(a + b):
+ * GptOssTpAllReduceBf16 (tp_collective.cpp:100-122, tp_peer_math.cuh:10-14). */
+int garnet_b200_comm_all_reduce(garnet_b200_channel_t channel, const float* d_src, float* d_dst, size_t count,
+                                int wire_dtype, void* stream);
+
+/* ---- expert-parallel MoE with the exchange on the device ------------------------------
+ * Tokens are split over the ranks, experts live in contiguous blocks of experts/world
+ * (create the operator with ep_rank/ep_world of the communicator, ep_interleaved = 0,
+ * io_dtype bf16; rank-local expert tensors with expert_weights_sharded = 1).  One call
+ * routes this rank's tokens, stores every routed row into the receive buffer of the GPU
+ * that owns its expert (plain peer stores; fixed-capacity regions per source, so no
+ * count is needed before the data moves), runs the experts on what this rank
+ * received, stores the per-row values back the same way (as bf16: exact) and combines in
+ * router order: the output equals the single-GPU operator's.  No host synchronisation,
+ * no library collective; every wait is bounded (garnet_b200_comm_fault).  All ranks
+ * call it once per step.  The reference's form is two ranks with replicated tokens and
+ * an all-reduce (plugins/gpt_oss/cuda/gpt_oss_kernels.cu:771,818), which
+ * garnet_b200_moe_run with ep_world > 1 plus garnet_b200_comm_all_reduce reproduces. */
+typedef struct garnet_b200_moe_ep* garnet_b200_moe_ep_t;
+/* Arena bytes one exchange takes (add the channels' needs when sizing garnet_b200_comm_create). */
+int garnet_b200_moe_ep_arena_bytes(const garnet_b200_moe_options* options, int world, int tokens_local_max, size_t* bytes);
+int garnet_b200_moe_ep_create(garnet_b200_moe_t moe, garnet_b200_comm_t comm, int tokens_local_max, garnet_b200_moe_ep_t* out);
+int garnet_b200_moe_ep_run(garnet_b200_moe_ep_t ep, const void* d_x, void* d_y, int tokens_local, void* stream);
+/* Rows this rank's experts processed in the last completed call (read after a stream synchronise). */
+int garnet_b200_moe_ep_rows_received(garnet_b200_moe_ep_t ep);
+void garnet_b200_moe_ep_destroy(garnet_b200_moe_ep_t ep);
+/* The exchange's placement rule on the host: send_idx[s] = position of routed row s
+ * (expert selected[s], owner selected[s] / experts_per_rank) among the rows this rank
+ * sends to that owner, in slot order; dest_count[d] = rows bound for rank d. */
+int garnet_b200_moe_ep_plan_host(const int* selected, int slots, int experts_per_rank, int world, int* send_idx, int* dest_count);
+
+/* Launches a wait on a flag that no peer ever writes, with the given limit (1..2000
+ * ms), synchronises and returns DEVICE_FAULT: how every wait of the collectives ends
+ * when a peer never shows up. */
+int garnet_b200_comm_selftest_wait(garnet_b200_comm_t comm, int limit_ms, void* stream);
+
 void garnet_b200_moe_destroy(garnet_b200_moe_t h);
 
 #ifdef __cplusplus
