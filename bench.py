@@ -178,6 +178,11 @@ def run_gpu(args):
     ys = {n: torch.empty(m, n, device="cuda", dtype=torch.bfloat16) for n in (1024, 2048, 6144)}
     y_head = torch.empty(m, hn_local, device="cuda", dtype=torch.bfloat16)
     logits = torch.empty(world, m, hn_local, device="cuda", dtype=torch.bfloat16) if world > 1 else None
+    gather = None
+    if world > 1:
+        from garnet_b200.dist import Channel, Comm
+        comm = Comm(4 * world * m * hn_local * 2 + (1 << 20))
+        gather = Channel(comm, m * hn_local * 2)
     ws_bytes = max([lin.workspace_bytes(m) for layer in layers for (lin, _, _) in layer] + [head.workspace_bytes(m)])
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
     # the whole pass is one prepared list: one persistent launch per step
@@ -193,12 +198,12 @@ def run_gpu(args):
                   (gate, xs[2048], ys[6144]), (up, xs[2048], y_up), (down, xs[6144], y_d)]
     calls.append((head, xs[hk], y_head))
     pass_list = gb.LinearList(calls, m=m)
-    launches_per_step = 1
+    launches_per_step = 1 if world == 1 else 2
 
     def decode_pass():
         pass_list.run()
         if world > 1:
-            dist.all_gather_into_tensor(logits.view(-1), y_head.view(-1))
+            gather.all_gather(y_head, logits)     # peer stores over NVLink: one kernel per rank, no library collective
 
     # The same 197 linears with the data dependencies their shapes allow, each consumer
     # waiting on the device for its producer (one launch as well).
@@ -265,7 +270,7 @@ def run_gpu(args):
         if world > 1:
             torch.cuda.current_stream().synchronize()
             y_head.copy_(yh_head, non_blocking=True)
-            dist.all_gather_into_tensor(logits.view(-1), y_head.view(-1))
+            gather.all_gather(y_head, logits)
         torch.cuda.current_stream().synchronize()
         return float(yh_head[0, 0])   # the host reads the step's result
 
@@ -297,7 +302,7 @@ def run_gpu(args):
             "data": "synthetic",
             "config": {"workload": "qwen3_1p7b_w4a16_sweep: decode pass M=1 over 28x7 projections + lm_head (197 int4 group-128 linears)",
                        "bytes_per_step": step_bytes, "l2": "887 MB of weights per step > 126 MB L2; no flush needed",
-                       "parallelism": f"lm_head N-sharded x{world} + all-gather" if world > 1 else "single GPU",
+                       "parallelism": f"lm_head N-sharded x{world} + all-gather by peer stores (garnet_b200_comm_all_gather)" if world > 1 else "single GPU",
                        "launch": "one persistent launch per pass (a prepared list of the 197 linears reading fixed activation buffers; no linear waits for another)"},
             "chained": {"ms_per_step": round(chained_ms, 5), "value": round(step_bytes / (chained_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
                         "hbm_frac": round(step_bytes / (chained_ms * 1e-3) / 1e9 / peaks["hbm"], 4),
@@ -350,6 +355,7 @@ def run_gpu(args):
     if world == 1 and not args.no_moe:
         torch.cuda.empty_cache()
         out["moe"] = bench_moe(torch, gb, peaks, args)
+        out["moe_ep"] = bench_moe_ep(torch, dist, gb, args, 0, 1)
     if world > 1 and not args.no_moe:
         del layers, head
         torch.cuda.empty_cache()
@@ -459,11 +465,16 @@ def moe_cpu_baseline(host, x, H, I, E, K, budget_s=12.0):
 
 
 def bench_moe_ep(torch, dist, gb, args, rank, world, tokens_total=8192):
-    """gpt-oss-120b MoE layer, expert parallel over `world` GPUs: 128/world experts per
-    GPU (contiguous blocks), tokens_total tokens split evenly, Zipf(1.1)-skewed expert
-    popularity, NCCL all-to-all dispatch and combine.  tok/s = tokens_total / time
-    (device time, max over ranks)."""
-    from garnet_b200.dist import ExpertParallelMoe
+    """gpt-oss-120b MoE layer, expert parallel over `world` GPUs: 128/world experts per GPU,
+    tokens_total tokens split evenly over the ranks, Zipf(1.1)-skewed expert popularity; rows
+    and values travel by peer stores over NVLink (garnet_b200_moe_ep_run: no host
+    synchronisation, no library collective).  Experts are placed by popularity (most popular
+    first, dealt to the ranks in snake order) within the experts/world-per-GPU rule; the
+    imbalance of plain contiguous blocks is reported beside it.  tok/s = tokens_total / time
+    (device time, max over ranks).  With world = 1 the same call runs on one GPU (the anchor
+    of the scaling curve).  Every rank also holds the whole layer once, to check its slice
+    of the output against the single-GPU operator."""
+    from garnet_b200.dist import Comm, ExpertParallel, ep_arena_bytes
     H = I = 2880
     E, K = 128, 4
     gen = torch.Generator(device="cuda")
@@ -473,49 +484,72 @@ def bench_moe_ep(torch, dist, gb, args, rank, world, tokens_total=8192):
     perm = torch.randperm(E, device="cuda", generator=gen).float() + 1.0
     pop = perm ** -1.1
     router_b = torch.log(pop / pop.sum() * E).to(torch.bfloat16).float()
-    per = E // world
-    lo = rank * per
     gu_b, gu_s = u8(E, 2 * I, H // 32, 16), u8(E, 2 * I, H // 32, lo=117, hi=124)
     dn_b, dn_s = u8(E, H, I // 32, 16), u8(E, H, I // 32, lo=117, hi=124)
-    moe = gb.GptOssMoe(H, I, E, K, io_dtype=torch.bfloat16, ep_rank=rank, ep_world=world,
-                       expert_weights_sharded=True).prepare(
-        router_w, router_b, gu_b[lo:lo + per].contiguous(), gu_s[lo:lo + per].contiguous(),
-        torch.zeros(per, 2 * I, device="cuda"), dn_b[lo:lo + per].contiguous(), dn_s[lo:lo + per].contiguous(),
-        torch.zeros(per, H, device="cuda"))
-    del gu_b, gu_s, dn_b, dn_s
-    torch.cuda.empty_cache()
+    # placement: experts sorted by popularity, dealt to the ranks in snake order, then renumbered so
+    # that rank r owns the contiguous block [r * per, (r + 1) * per) of the new numbering
+    per = E // world
+    by_pop = torch.argsort(pop, descending=True).tolist()
+    owner_lists = [[] for _ in range(world)]
+    for i, e in enumerate(by_pop):
+        r = i % (2 * world)
+        owner_lists[r if r < world else 2 * world - 1 - r].append(e)
+    order = torch.tensor([e for lst in owner_lists for e in lst], device="cuda")
+    router_w, router_b = router_w[order].contiguous(), router_b[order].contiguous()
+    gu_b, gu_s, dn_b, dn_s = gu_b[order].contiguous(), gu_s[order].contiguous(), dn_b[order].contiguous(), dn_s[order].contiguous()
+    zeros_up, zeros_dn = torch.zeros(E, 2 * I, device="cuda"), torch.zeros(E, H, device="cuda")
+    full = gb.GptOssMoe(H, I, E, K, io_dtype=torch.bfloat16).prepare(router_w, router_b, gu_b, gu_s, zeros_up, dn_b, dn_s, zeros_dn)
+    lo = rank * per
+    if world > 1:
+        moe = gb.GptOssMoe(H, I, E, K, io_dtype=torch.bfloat16, ep_rank=rank, ep_world=world,
+                           expert_weights_sharded=True).prepare(
+            router_w, router_b, gu_b[lo:lo + per].contiguous(), gu_s[lo:lo + per].contiguous(),
+            zeros_up[:per].contiguous(), dn_b[lo:lo + per].contiguous(), dn_s[lo:lo + per].contiguous(), zeros_dn[:per].contiguous())
+    else:
+        moe = full
     t_local = tokens_total // world
     gx = torch.Generator(device="cuda")
     gx.manual_seed(1000 + rank)
     x = torch.randn(t_local, H, device="cuda", generator=gx).to(torch.bfloat16)
-
-    def route(a):
-        _, sel, pr = moe.route(a)
-        return sel, pr
-
-    ep = ExpertParallelMoe(route, moe.run_rows, moe.combine, E, K)
+    comm = Comm(ep_arena_bytes(moe, world, t_local) + (1 << 20))
+    ep = ExpertParallel(moe, comm, t_local)
+    y = torch.empty_like(x)
     for _ in range(3):
-        y = ep.forward(x)
-    dist.barrier()
+        ep.run(x, out=y)
+    torch.cuda.synchronize()
+    expected = full.run(x)
+    err = ((y.float() - expected.float()).abs() / (1 + expected.float().abs())).max()
+    if world > 1:
+        dist.barrier()
     torch.cuda.synchronize()
     steps = max(3, min(args.steps, 10))
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(steps):
-        y = ep.forward(x)
+        ep.run(x, out=y)
     b.record()
     torch.cuda.synchronize()
+    assert comm.fault() == 0 and moe.fault() == 0, "a device-side wait gave up"
     ms = a.elapsed_time(b) / steps
-    t = torch.tensor([ms, float(ep.last_recv_rows)], device="cuda")
-    tmax = t.clone()
-    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    tsum = t.clone()
-    dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+    # what contiguous blocks of the original numbering would have put on one GPU
+    _, sel, _ = full.route(x)
+    original = order[sel.reshape(-1).long()]
+    contiguous_rows = torch.bincount(torch.div(original, per, rounding_mode="floor"), minlength=world).float()
+    t = torch.tensor([ms, float(ep.rows_received()), float(err)], device="cuda")
+    tmax, tsum = t.clone(), t.clone()
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        dist.all_reduce(contiguous_rows, op=dist.ReduceOp.SUM)
     ms = float(tmax[0].item())
     return {"tokens": tokens_total, "ms": round(ms, 4), "tok_per_s": round(tokens_total / (ms * 1e-3), 1),
             "experts_per_gpu": per, "routing": "zipf(1.1) popularity over a seeded permutation",
+            "placement": "experts dealt to the ranks by popularity (snake order)",
+            "exchange": "peer stores over NVLink inside garnet_b200_moe_ep_run (no host synchronisation, no library collective)",
             "max_rows_on_one_gpu": int(tmax[1].item()), "mean_rows_per_gpu": round(float(tsum[1].item()) / world, 1),
-            "TFLOPs": round(199065600.0 * tokens_total / (ms * 1e-3) / 1e12, 2), "finite": bool(torch.isfinite(y).all().item())}
+            "max_rows_with_contiguous_blocks": int(contiguous_rows.max().item()),
+            "TFLOPs": round(199065600.0 * tokens_total / (ms * 1e-3) / 1e12, 2),
+            "parity_max_scaled_err_vs_single_gpu_operator": float(tmax[2].item())}
 
 
 # ------------------------------------------------------------- CPU baseline
