@@ -194,7 +194,8 @@ W4A16::~W4A16()
     if (stage_ws) cudaFree(stage_ws);
 }
 
-size_t W4A16::workspace_bytes(int) const { return 0; }
+// Only the tile kernel (more than 16 rows) uses a workspace: the partial sums of its K slices.
+size_t W4A16::workspace_bytes(int m) const { return m > 16 ? tc_plan(geo, m).workspace : 0; }
 
 int W4A16::run(const void* d_x, void* d_y, int m, void* ws, size_t ws_bytes, unsigned flags, cudaStream_t stream)
 {
@@ -202,13 +203,13 @@ int W4A16::run(const void* d_x, void* d_y, int m, void* ws, size_t ws_bytes, uns
     if (!d_x || !d_y) return fail(GARNET_B200_INVALID_VALUE, "w4a16_run: null x or y");
     if ((reinterpret_cast<uintptr_t>(d_x) & 15) || (reinterpret_cast<uintptr_t>(d_y) & 1))
         return fail(GARNET_B200_INVALID_VALUE, "w4a16_run: x must be 16-byte aligned");
-    if (ws_bytes < workspace_bytes(m) || (workspace_bytes(m) && !ws))
-        return fail(GARNET_B200_INVALID_VALUE, "w4a16_run: workspace too small (%zu < %zu)", ws_bytes,
-                    workspace_bytes(m));
+    // A workspace smaller than garnet_b200_w4a16_workspace asks for (or none) is allowed: the
+    // tile kernel then does not cut K into slices (slower on small matrices, same results
+    // up to the order of the fp32 sums).
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(d_x);
     __nv_bfloat16* y = static_cast<__nv_bfloat16*>(d_y);
     // Above 16 rows the weights are worth expanding once per 128 rows for the tensor core.
-    if (m > 16 && use_tensor_core_tiles()) return launch_tc(x, y, m, flags, stream);
+    if (m > 16 && use_tensor_core_tiles()) return launch_tc(x, y, m, ws, ws_bytes, flags, stream);
     for (int m0 = 0; m0 < m; m0 += max_rows_per_launch) {
         const int rows = std::min(max_rows_per_launch, m - m0);
         const int rc = launch_stream(x + size_t(m0) * geo.cols, y + size_t(m0) * geo.rows, rows, geo.rows, flags,
@@ -282,6 +283,8 @@ struct HostBatch {
     std::vector<X> xs;
     uint8_t* x_stage = nullptr;
     uint8_t* y_stage = nullptr;
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
     ScatterEntry* table = nullptr;
     int table_count = 0;
     garnet_b200_w4a16_list_t list = nullptr;   // the calls as one persistent launch, when they all share one small batch
@@ -290,6 +293,7 @@ struct HostBatch {
         if (list) garnet_b200_w4a16_list_destroy(list);
         if (x_stage) cudaFree(x_stage);
         if (y_stage) cudaFree(y_stage);
+        if (ws) cudaFree(ws);
         if (table) cudaFree(table);
     }
 };
@@ -557,12 +561,12 @@ int garnet_b200_w4a16_batch_create(const garnet_b200_w4a16_t* handles, const voi
     if (!handles || !h_xs || !h_ys || !ms || !out || count <= 0)
         return fail(GARNET_B200_INVALID_VALUE, "w4a16_batch_create: bad argument");
     std::unique_ptr<HostBatch> b(new HostBatch);
-    size_t x_total = 0, y_total = 0;
+    size_t x_total = 0, y_total = 0, ws_max = 0;
     for (int i = 0; i < count; ++i) {
         W4A16* h = reinterpret_cast<W4A16*>(handles[i]);
         if (!h || !h_xs[i] || !h_ys[i] || ms[i] <= 0)
             return fail(GARNET_B200_INVALID_VALUE, "w4a16_batch_create: bad argument at index %d", i);
-        if (h->workspace_bytes(ms[i])) return fail(GARNET_B200_NOT_SUPPORTED, "w4a16_batch_create: linear needs a workspace");
+        ws_max = std::max(ws_max, h->workspace_bytes(ms[i]));
         const size_t xb = size_t(ms[i]) * h->geo.cols * 2, yb = size_t(ms[i]) * h->geo.rows * 2;
         // inputs are read-only during a run: every distinct host buffer is copied once
         int slot = -1;
@@ -578,6 +582,8 @@ int garnet_b200_w4a16_batch_create(const garnet_b200_w4a16_t* handles, const voi
     }
     GB_CUDA(cudaMalloc(&b->x_stage, x_total));
     GB_CUDA(cudaMalloc(&b->y_stage, y_total));
+    if (ws_max) GB_CUDA(cudaMalloc(&b->ws, ws_max));   // the calls run one after the other: one workspace serves them all
+    b->ws_bytes = ws_max;
     std::vector<ScatterEntry> table;
     for (const HostBatch::Call& c : b->calls)
         if (c.y_alias)
@@ -618,7 +624,7 @@ int garnet_b200_w4a16_batch_run(garnet_b200_w4a16_batch_t bb, void* stream)
         if (int rc = garnet_b200_w4a16_list_run(b->list, 0, stream)) return rc;
     } else {
         for (const HostBatch::Call& c : b->calls)
-            if (int rc = c.h->run(b->x_stage + b->xs[c.x_slot].off, b->y_stage + c.y_off, c.m, nullptr, 0, 1, s)) return rc;
+            if (int rc = c.h->run(b->x_stage + b->xs[c.x_slot].off, b->y_stage + c.y_off, c.m, b->ws, b->ws_bytes, 1, s)) return rc;
     }
     if (b->table_count) {
         cudaLaunchConfig_t cfg = {};

@@ -36,9 +36,16 @@ struct W4A16 {
     static int launch_stream_group(W4A16* const* hs, int count, const __nv_bfloat16* x, __nv_bfloat16* const* ys,
                                    const int* ldys, int m, unsigned flags, cudaStream_t stream);
     int init_tc();
-    int launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, unsigned flags, cudaStream_t stream);
+    int launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, void* ws, size_t ws_bytes, unsigned flags, cudaStream_t stream);
     int run(const void* d_x, void* d_y, int m, void* ws, size_t ws_bytes, unsigned flags, cudaStream_t stream);
 };
+
+// Tiling of the tensor-core tile kernel for a batch of m rows.
+struct TcPlan {
+    int token_tiles, atiles, panels, kslices, chunks_per_slice;
+    size_t workspace;   // bytes of fp32 partial sums the K slices need (0 without slices)
+};
+TcPlan tc_plan(const PackGeom& geo, int m);
 
 int w4a16_repack_device(const uint8_t* d_nibbles, const uint16_t* d_scales, const PackGeom& geo, long long row0,
                         uint8_t* d_packed, cudaStream_t stream);

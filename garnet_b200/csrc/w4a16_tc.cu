@@ -57,8 +57,28 @@ struct TcParams {
     int ldy;
     int strips_padded, chunks;
     int panels, token_tiles;
+    int kslices, chunks_per_slice;   // the K dimension of a tile may be cut into slices handled by different CTAs
+    float* partial;                  // [kslices][m][n] fp32 partial sums (kslices > 1), else nullptr
     int scale_dtype;
 };
+
+// Work item -> (panel, batch tile, K slice) and the slice's chunk range.
+struct TcItem {
+    int panel, tt, c0, c1;
+    int slice;
+};
+__device__ __forceinline__ TcItem tc_decode(const TcParams& p, int item)
+{
+    TcItem it;
+    const int per_panel = p.token_tiles * p.kslices;
+    it.panel = item / per_panel;
+    const int rem = item - it.panel * per_panel;
+    it.tt = rem / p.kslices;
+    it.slice = rem - it.tt * p.kslices;
+    it.c0 = it.slice * p.chunks_per_slice;
+    it.c1 = min(p.chunks, it.c0 + p.chunks_per_slice);
+    return it;
+}
 
 template <int kATiles>
 struct TcSmem {
@@ -157,8 +177,7 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
 
-    const int items = p.panels * p.token_tiles;
-    const int ktiles = p.chunks * 2;
+    const int items = p.panels * p.token_tiles * p.kslices;
 
     if (warp == 0) {
         // ------------------------------------- producer of packed codes + scales
@@ -168,20 +187,23 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
             // One thread feeds the ring, so its loop carries no divisions: the stage index, the
             // ring's wrap count and the prefetch cursor advance by increments.
             uint32_t ps = 0, round = 0, issued = 0, prefetched = 0;
-            int pf_item = blockIdx.x, pf_c = 0;
-            int pf_strip0 = pf_item < items ? (pf_item / p.token_tiles) * kStripsPerPanel : 0;
+            int pf_item = blockIdx.x;
+            TcItem pf = pf_item < items ? tc_decode(p, pf_item) : TcItem{};
+            int pf_c = pf.c0;
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
-                const int panel = item / p.token_tiles;
-                const int strip0 = panel * kStripsPerPanel;
-                for (int c = 0; c < p.chunks; ++c, ++issued) {
+                const TcItem it = tc_decode(p, item);
+                const int strip0 = it.panel * kStripsPerPanel;
+                for (int c = it.c0; c < it.c1; ++c, ++issued) {
                     // keep the L2 prefetch kTcPrefetchChunks ahead of the ring, across items
                     while (pf_item < items && prefetched < issued + kTcPrefetchChunks) {
-                        tma_prefetch_2d(&w_map, pf_c * (kTcChunkBytes / 8), pf_strip0);
+                        tma_prefetch_2d(&w_map, pf_c * (kTcChunkBytes / 8), pf.panel * kStripsPerPanel);
                         ++prefetched;
-                        if (++pf_c == p.chunks) {
-                            pf_c = 0;
+                        if (++pf_c == pf.c1) {
                             pf_item += gridDim.x;
-                            if (pf_item < items) pf_strip0 = (pf_item / p.token_tiles) * kStripsPerPanel;
+                            if (pf_item < items) {
+                                pf = tc_decode(p, pf_item);
+                                pf_c = pf.c0;
+                            }
                         }
                     }
                     if (round > 0 && !mbar_wait_bounded(&pk_empty[ps], (round - 1) & 1)) {
@@ -206,8 +228,9 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
             uint32_t ab_n = 0;
             pdl_wait();   // activations come from the previous kernel in the stream
             for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
-                const int tt = item % p.token_tiles;
-                for (int kt = 0; kt < ktiles; ++kt) {
+                const TcItem it = tc_decode(p, item);
+                const int tt = it.tt;
+                for (int kt = 2 * it.c0; kt < 2 * it.c1; ++kt) {
                     const uint32_t s = ab_n % kBStages;
                     if (ab_n >= kBStages && !mbar_wait_bounded(&b_empty[s], ((ab_n / kBStages) - 1) & 1)) {
                         atomicExch(p.fault, 12);
@@ -234,6 +257,8 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                     break;
                 }
                 tc_fence_after();
+                const TcItem it = tc_decode(p, item);
+                const int ktiles = 2 * (it.c1 - it.c0);
                 for (int kt = 0; kt < ktiles; ++kt) {
                     const uint32_t s = ab_n % kAStages, sb = ab_n % kBStages;
                     if (!mbar_wait_bounded(&a_full[s], (ab_n / kAStages) & 1) ||
@@ -266,9 +291,10 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
         const int g = lane >> 2, t = lane & 3;
         uint32_t pk_n = 0, ab_n = 0;
         for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
-            const int panel = item / p.token_tiles;
+            const TcItem it = tc_decode(p, item);
+            const int panel = it.panel;
             const int valid = min(kStripsPerPanel, p.strips_padded - panel * kStripsPerPanel);
-            for (int c = 0; c < p.chunks && !*abort_flag; ++c) {
+            for (int c = it.c0; c < it.c1 && !*abort_flag; ++c) {
                 const uint32_t ps = pk_n % kTcPackStages;
                 if (!mbar_wait_bounded(&pk_full[ps], (pk_n / kTcPackStages) & 1)) {
                     atomicExch(p.fault, 15);
@@ -332,7 +358,8 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
         uint32_t it_n = 0;
         bool waited = false;
         for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++it_n) {
-            const int panel = item / p.token_tiles, tt = item % p.token_tiles;
+            const TcItem it = tc_decode(p, item);
+            const int panel = it.panel, tt = it.tt;
             const uint32_t buf = it_n & 1;
             if (!mbar_wait_bounded(&acc_full[buf], (it_n >> 1) & 1)) {
                 atomicExch(p.fault, 17);
@@ -356,6 +383,20 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                 tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * (kATiles * 128) + c0, r);
                 tmem_ld_wait();
                 if (m >= p.m) continue;
+                if (p.partial) {
+                    // a K slice: fp32 partial sums, added up in slice order by the reduction kernel
+                    float* prow = p.partial + (size_t(it.slice) * p.m + m) * p.n;
+                    if (n0 + 32 <= p.n && (p.n & 3) == 0) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            *reinterpret_cast<uint4*>(prow + n0 + 4 * q) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + j < p.n) prow[n0 + j] = __uint_as_float(r[j]);
+                    }
+                    continue;
+                }
                 if (vec_ok && n0 + 32 <= p.n) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
@@ -389,7 +430,60 @@ w4a16_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
     }
 }
 
+// y[m, n] = bf16(sum of the K slices' partial sums, in slice order).  Four outputs per thread.
+__global__ void w4a16_splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ y, int m, int n, int ldy,
+                                           int slices)
+{
+    pdl_wait();   // the partial sums come from the kernel before this one
+    const size_t total = size_t(m) * n;
+    const size_t idx = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (idx >= total) return;
+    if ((n & 3) == 0 && (ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 7) == 0) {
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < slices; ++s) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(partial + size_t(s) * total + idx));
+            sum.x += v.x;
+            sum.y += v.y;
+            sum.z += v.z;
+            sum.w += v.w;
+        }
+        const __nv_bfloat162 a = __floats2bfloat162_rn(sum.x, sum.y), b = __floats2bfloat162_rn(sum.z, sum.w);
+        *reinterpret_cast<uint2*>(y + (idx / n) * ldy + idx % n) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+    } else {
+        for (size_t j = idx; j < min(idx + 4, total); ++j) {
+            float sum = 0.f;
+            for (int s = 0; s < slices; ++s) sum += partial[size_t(s) * total + j];
+            y[(j / n) * ldy + j % n] = __float2bfloat16_rn(sum);
+        }
+    }
+}
+
 // ------------------------------------------------------------------ host side
+
+// How the tile kernel cuts the work for a batch of m rows: 256-row panels when they
+// already fill the machine, else 128-row panels, and K slices until there are about
+// as many work items as SMs.
+TcPlan tc_plan(const PackGeom& geo, int m)
+{
+    TcPlan t;
+    t.token_tiles = (m + kTcTokens - 1) / kTcTokens;
+    const int panels256 = (geo.strips_padded + 15) / 16;
+    t.atiles = panels256 * t.token_tiles >= 2 * kSmCount ? 2 : 1;
+    t.panels = t.atiles == 2 ? panels256 : geo.strips_padded / 8;
+    const int tiles = t.panels * t.token_tiles;
+    int want = tiles >= kSmCount ? 1 : (kSmCount + tiles - 1) / tiles;
+    want = std::min(want, std::min(geo.chunks, 16));
+    // every slice writes and the last one re-reads m x n fp32 partial sums: beyond a few MB per
+    // slice that costs more than the idle SMs it saves
+    const size_t plane = size_t(m) * geo.rows * sizeof(float);
+    want = int(std::max<size_t>(1, std::min<size_t>(size_t(want), (size_t(6) << 20) / std::max<size_t>(plane, 1))));
+
+    t.chunks_per_slice = (geo.chunks + want - 1) / want;
+    t.kslices = (geo.chunks + t.chunks_per_slice - 1) / t.chunks_per_slice;
+    t.workspace = t.kslices > 1 ? size_t(t.kslices) * m * geo.rows * sizeof(float) : 0;
+    return t;
+}
 
 TensorMapEncodeFn tensor_map_encoder()
 {
@@ -448,7 +542,7 @@ int W4A16::init_tc()
     return GARNET_B200_OK;
 }
 
-int W4A16::launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, unsigned flags, cudaStream_t stream)
+int W4A16::launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, void* ws, size_t ws_bytes, unsigned flags, cudaStream_t stream)
 {
     CUtensorMap map;
     if (int rc = make_tensor_map_2d_16bit(&map, x, uint64_t(m), uint64_t(geo.cols), kTcTokens)) return rc;
@@ -462,15 +556,18 @@ int W4A16::launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, unsigned f
     p.ldy = geo.rows;
     p.strips_padded = geo.strips_padded;
     p.chunks = geo.chunks;
-    p.token_tiles = (m + kTcTokens - 1) / kTcTokens;
+    const TcPlan plan = tc_plan(geo, m);
+    p.token_tiles = plan.token_tiles;
     p.scale_dtype = scale_dtype;
-    // 256-row CTA tiles halve the activation traffic per weight row; use them when
-    // there are enough tiles to fill the machine, else 128-row tiles.
-    const int panels256 = (geo.strips_padded + 15) / 16;
-    const int atiles = panels256 * p.token_tiles >= 2 * kSmCount ? 2 : 1;
-    p.panels = atiles == 2 ? panels256 : geo.strips_padded / 8;
+    const int atiles = plan.atiles;
+    p.panels = plan.panels;
+    // K slices need the caller's workspace for their partial sums; without one the tiles keep all of K
+    const bool sliced = plan.kslices > 1 && ws && ws_bytes >= plan.workspace && (reinterpret_cast<uintptr_t>(ws) & 15) == 0;
+    p.kslices = sliced ? plan.kslices : 1;
+    p.chunks_per_slice = sliced ? plan.chunks_per_slice : geo.chunks;
+    p.partial = sliced ? static_cast<float*>(ws) : nullptr;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(unsigned(std::min(p.panels * p.token_tiles, kSmCount)));
+    cfg.gridDim = dim3(unsigned(std::min(p.panels * p.token_tiles * p.kslices, kSmCount)));
     cfg.blockDim = dim3(tc_threads(atiles));
     cfg.dynamicSmemBytes = atiles == 2 ? TcSmem<2>::total : TcSmem<1>::total;
     cfg.stream = stream;
@@ -483,6 +580,16 @@ int W4A16::launch_tc(const __nv_bfloat16* x, __nv_bfloat16* y, int m, unsigned f
         GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<2>, p, map, *reinterpret_cast<const CUtensorMap*>(&tc_packed_map[1])));
     else
         GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<1>, p, map, *reinterpret_cast<const CUtensorMap*>(&tc_packed_map[0])));
+    if (sliced) {
+        const size_t quads = (size_t(m) * geo.rows + 3) / 4;
+        cudaLaunchConfig_t rc = {};
+        rc.gridDim = dim3(unsigned((quads + 255) / 256));
+        rc.blockDim = dim3(256);
+        rc.stream = stream;
+        rc.attrs = attr;
+        rc.numAttrs = 1;   // starts while the tile kernel drains; waits for its results on the device
+        GB_CUDA(cudaLaunchKernelEx(&rc, w4a16_splitk_reduce_kernel, (const float*)p.partial, y, m, geo.rows, geo.rows, p.kslices));
+    }
     return GARNET_B200_OK;
 }
 
