@@ -195,7 +195,7 @@ W4A16::~W4A16()
 }
 
 // Only the tile kernel (more than 16 rows) uses a workspace: the partial sums of its K slices.
-size_t W4A16::workspace_bytes(int m) const { return m > 16 ? tc_plan(geo, m).workspace : 0; }
+size_t W4A16::workspace_bytes(int m) const { return (m > 16 || m > max_rows_per_launch) ? tc_plan(geo, m).workspace : 0; }
 
 int W4A16::run(const void* d_x, void* d_y, int m, void* ws, size_t ws_bytes, unsigned flags, cudaStream_t stream)
 {
@@ -209,7 +209,8 @@ int W4A16::run(const void* d_x, void* d_y, int m, void* ws, size_t ws_bytes, uns
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(d_x);
     __nv_bfloat16* y = static_cast<__nv_bfloat16*>(d_y);
     // Above 16 rows the weights are worth expanding once per 128 rows for the tensor core.
-    if (m > 16 && use_tensor_core_tiles()) return launch_tc(x, y, m, ws, ws_bytes, flags, stream);
+    // (also when the rows do not fit one launch of the streaming kernel: a very long K)
+    if ((m > 16 || m > max_rows_per_launch) && use_tensor_core_tiles()) return launch_tc(x, y, m, ws, ws_bytes, flags, stream);
     for (int m0 = 0; m0 < m; m0 += max_rows_per_launch) {
         const int rows = std::min(max_rows_per_launch, m - m0);
         const int rc = launch_stream(x + size_t(m0) * geo.cols, y + size_t(m0) * geo.rows, rows, geo.rows, flags,

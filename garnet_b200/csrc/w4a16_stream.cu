@@ -4,10 +4,10 @@
 // Arithmetic.  Every 128-column group of an activation row becomes a 15-bit block
 // fixed-point number: V = round(x * 2^(14-e)) with 2^e just above the group's largest
 // magnitude, split into two signed bytes V = 128*hi + lo.  The int4 codes are widened
-// to unsigned bytes (q + 8) with three logic operations per eight codes and multiplied
-// on the tensor cores in integers (mma.sync m16n8k32 u8 x s8 -> s32; the batch rows'
-// hi and lo pieces are neighbouring MMA columns), so each group's sum
-// sum_k q_k V_k is exact.  It is scaled by 2^(e-14) and the weight's group scale in
+// to signed bytes 16 q with three logic operations per eight codes (a nibble moved to
+// the top of its byte) and multiplied on the tensor cores in integers (mma.sync
+// m16n8k32 s8 x s8 -> s32; the batch rows' hi and lo pieces are neighbouring MMA
+// columns), so each group's sum sum_k q_k V_k is exact.  It is scaled by 2^(e-14) and the weight's group scale in
 // fp32 and accumulated over the groups in fp32.  A bf16 activation within 2^-6 of its
 // group's maximum is represented exactly; smaller ones carry an absolute error of at
 // most 2^-15 of that maximum.
@@ -38,16 +38,18 @@ namespace gb200 {
 
 namespace {
 
-__device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+__device__ __forceinline__ void imma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                           uint32_t b1)
 {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Four int4 codes in the even nibbles of `w` -> four unsigned bytes q + 8.
-__device__ __forceinline__ uint32_t nib_to_u8(uint32_t w) { return lop3_and_xor(w, 0x0F0F0F0Fu, 0x08080808u); }
+// Four two's-complement int4 codes in the HIGH nibbles of the bytes of `w` -> four signed
+// bytes 16 q (a nibble moved to the top of its byte is the code times 16, sign and
+// all); the factor 16 is taken out of the activation scale.
+__device__ __forceinline__ uint32_t nib_to_s8x16(uint32_t w) { return w & 0xF0F0F0F0u; }
 
 __device__ __forceinline__ uint4 ld_relaxed_gpu_v4(const void* p)
 {
@@ -107,24 +109,25 @@ constexpr int kConsumerThreads = kStreamConsumerWarps * 32;
 constexpr int kHalves = kStreamConsumerWarps * 2;   // half-warps that stage activation rows
 
 // The consumer threads turn the activation rows of `op` into the int8 pieces, scale
-// factors and bias terms that the MMAs read.  One half-warp per (batch row, chunk of
+// factors that the MMAs read.  One half-warp per (batch row, chunk of
 // 128 activations); each lane quantises eight of them against the chunk's largest
 // magnitude.  Rows come from memory, or - when an earlier linear of the list
 // produces them - from that linear's exchange packets, polled until they carry this
 // run's tag.  Returns false if a poll ran out of time.
 template <int MBLK>
 __device__ __forceinline__ bool stage_rows(const StreamParams& p, const StreamOp& op, const StreamSmem& plan, Ctl* ctl,
-                                           uint8_t* xb, float* sxb, int* cnb, uint32_t run_tag, int tid, int lane)
+                                           uint8_t* xb, float* sxb, uint32_t run_tag, int tid, int lane)
 {
     const int half = tid >> 4, hl = tid & 15;
     const uint32_t hmask = 0xffffu << (lane & 16);   // the lanes of this half-warp
     const int k = op.chunks * 128;
     const int items = p.m * op.chunks;
-    for (int item0 = half; item0 < items; item0 += 2 * kHalves) {
-        uint4 pre[2], pre2[2];
+    constexpr int kAhead = MBLK == 1 ? 2 : 4;   // items whose loads are in flight together (registers permitting)
+    for (int item0 = half; item0 < items; item0 += kAhead * kHalves) {
+        uint4 pre[kAhead], pre2[kAhead];
         if (!op.xch_in) {
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {   // both loads are in flight together
+            for (int u = 0; u < kAhead; ++u) {
                 const int item = item0 + u * kHalves;
                 if (item < items) {
                     const int m = item / op.chunks, chunk = item - m * op.chunks;
@@ -139,7 +142,7 @@ __device__ __forceinline__ bool stage_rows(const StreamParams& p, const StreamOp
             bool good = true;
             for (;;) {
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
+                for (int u = 0; u < kAhead; ++u) {
                     const int item = item0 + u * kHalves;
                     if (item < items && !(valid & (1u << u))) {
                         const int m = item / op.chunks, chunk = item - m * op.chunks;
@@ -149,18 +152,18 @@ __device__ __forceinline__ bool stage_rows(const StreamParams& p, const StreamOp
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
+                for (int u = 0; u < kAhead; ++u) {
                     const int item = item0 + u * kHalves;
                     if (item >= items || (pre[u].y == run_tag && pre[u].w == run_tag && pre2[u].y == run_tag && pre2[u].w == run_tag))
                         valid |= 1u << u;
                 }
-                if (__all_sync(hmask, valid == 0x3u)) break;
+                if (__all_sync(hmask, valid == (1u << kAhead) - 1u)) break;
                 if (ctl->abort_flag || global_timer_ns() - t0 > p.wait_limit_ns) good = false;
                 if (!__all_sync(hmask, good)) return false;
             }
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kAhead; ++u) {
             const int item = item0 + u * kHalves;
             if (item < items) {
                 const int m = item / op.chunks, chunk = item - m * op.chunks;
@@ -200,24 +203,16 @@ __device__ __forceinline__ bool stage_rows(const StreamParams& p, const StreamOp
                 const int ef = int(amax >> 23);                   // biased exponent of the largest magnitude
                 const int e = max(ef - 126, -100);                // 2^e > max |x|
                 const float up = __uint_as_float(uint32_t(127 + 14 - e) << 23);      // 2^(14-e)
-                float down = __uint_as_float(uint32_t(127 + e - 14) << 23);          // 2^(e-14)
+                float down = __uint_as_float(uint32_t(127 + e - 18) << 23);          // 2^(e-14) / 16: the codes enter the MMA as 16 q
                 if (ef == 255) down = __uint_as_float(0x7fc00000u);                  // inf or NaN in the group: NaN out
                 uint32_t hi_b[2] = {0, 0}, lo_b[2] = {0, 0};
-                int hsum = 0, lsum = 0;
 #pragma unroll
                 for (int el = 0; el < 8; ++el) {
                     const float f = ef == 255 ? 0.f : __uint_as_float(bits[el]);
                     const int V = __float2int_rn(f * up);
                     const int hi = V >> 7, lo = V & 127;
-                    hsum += hi;
-                    lsum += lo;
                     hi_b[el >> 2] |= uint32_t(hi & 0xff) << (8 * (el & 3));
                     lo_b[el >> 2] |= uint32_t(lo) << (8 * (el & 3));
-                }
-#pragma unroll
-                for (int off = 8; off; off >>= 1) {
-                    hsum += __shfl_xor_sync(hmask, hsum, off, 16);
-                    lsum += __shfl_xor_sync(hmask, lsum, off, 16);
                 }
                 uint8_t* row_hi = xb + size_t(2 * m) * plan.xq_stride;
                 uint8_t* row_lo = row_hi + plan.xq_stride;
@@ -228,8 +223,6 @@ __device__ __forceinline__ bool stage_rows(const StreamParams& p, const StreamOp
                 if (hl == 0) {
                     const int mb = m >> 2, j = m & 3;
                     sxb[(chunk * MBLK + mb) * 4 + j] = down;
-                    cnb[(chunk * MBLK + mb) * 8 + 2 * j] = -8 * hsum;
-                    cnb[(chunk * MBLK + mb) * 8 + 2 * j + 1] = -8 * lsum;
                 }
             }
         }
@@ -249,7 +242,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
     Ctl* ctl = reinterpret_cast<Ctl*>(smem + plan.ctl);
     volatile int* tags = reinterpret_cast<volatile int*>(smem + plan.tags);
     float* sx = reinterpret_cast<float*>(smem + plan.sx);
-    int* cneg = reinterpret_cast<int*>(smem + plan.cneg);
     int* pcnt = reinterpret_cast<int*>(smem + plan.pcnt);
     float* partial = reinterpret_cast<float*>(smem + plan.partial);
     uint8_t* xq = smem + plan.xq;
@@ -267,18 +259,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
         ops = reinterpret_cast<const StreamOp*>(smem + plan.optable);
     }
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < NS; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
-        }
+    if (int(threadIdx.x) < NS) {   // one thread per ring stage
+        mbar_init(&full[threadIdx.x], 1);
+        mbar_init(&empty[threadIdx.x], 1);
         fence_barrier_init();
     }
-    // control words, part counters, bias terms, the all-zero activation row
+    // control words, part counters, the all-zero activation row (the scale factors and bias
+    // terms need no clearing: every entry that is read has been staged)
     for (int i = threadIdx.x; i < int(sizeof(Ctl) / 4); i += blockDim.x) reinterpret_cast<int*>(ctl)[i] = 0;
     for (int i = threadIdx.x; i < PS; i += blockDim.x) pcnt[i] = 0;
-    for (int i = threadIdx.x; i < p.nbuf * p.max_chunks * MBLK * 8; i += blockDim.x) cneg[i] = 0;
-    for (int i = threadIdx.x; i < p.nbuf * p.max_chunks * MBLK * 4; i += blockDim.x) sx[i] = 0.f;
     for (int b = 0; b < p.nbuf; ++b)
         for (int i = threadIdx.x; i < plan.xq_stride / 16; i += blockDim.x)
             *reinterpret_cast<uint4*>(xq + size_t(b) * plan.xq_bytes + size_t(2 * p.m) * plan.xq_stride + i * 16) = make_uint4(0, 0, 0, 0);
@@ -352,7 +341,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
     int my_q = -1;
     const uint8_t* xcol[MBLK];
     const float* sxb = sx;
-    const int* cnb = cneg;
     bool ok = true;
     for (int i = 0; i < p.count; ++i) {
         const StreamOp op = ops[i];
@@ -360,7 +348,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
             const int buf = (op.flags & kOpBuffer1) ? 1 : 0;
             uint8_t* xb = xq + size_t(buf) * plan.xq_bytes;
             sxb = sx + size_t(buf) * p.max_chunks * MBLK * 4;
-            cnb = cneg + size_t(buf) * p.max_chunks * MBLK * 8;
 #pragma unroll
             for (int mb = 0; mb < MBLK; ++mb) {
                 const int r = mb * 8 + g;
@@ -371,7 +358,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                 // ones.  (A warp that gave up keeps meeting the others at these barriers.)
                 named_barrier_sync(1, kConsumerThreads);
                 if (ok && !ctl->abort_flag &&
-                    !stage_rows<MBLK>(p, op, plan, ctl, xb, const_cast<float*>(sxb), const_cast<int*>(cnb), run_tag, threadIdx.x, lane)) {
+                    !stage_rows<MBLK>(p, op, plan, ctl, xb, const_cast<float*>(sxb), run_tag, threadIdx.x, lane)) {
                     if ((lane & 15) == 0) give_up(p, ctl, 3);
                 }
                 named_barrier_sync(1, kConsumerThreads);
@@ -426,13 +413,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                 const uint32_t sc = *reinterpret_cast<const uint32_t*>(ck + 1024 + g * 4);
                 int acc_i[MBLK][4];
 #pragma unroll
-                for (int mb = 0; mb < MBLK; ++mb) {
-                    const int2 cn = *reinterpret_cast<const int2*>(cnb + (chunk * MBLK + mb) * 8 + 2 * t);
-                    acc_i[mb][0] = cn.x;
-                    acc_i[mb][1] = cn.y;
-                    acc_i[mb][2] = cn.x;
-                    acc_i[mb][3] = cn.y;
-                }
+                for (int mb = 0; mb < MBLK; ++mb) acc_i[mb][0] = acc_i[mb][1] = acc_i[mb][2] = acc_i[mb][3] = 0;
 #pragma unroll
                 for (int tile = 0; tile < 2; ++tile) {
                     const uint4 u = tile ? u1 : u0;
@@ -443,11 +424,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
 #pragma unroll
                     for (int jj = 0; jj < 2; ++jj) {
                         const uint32_t w_lo = jj ? u.z : u.x, w_hi = jj ? u.w : u.y;
-                        const uint32_t a0 = nib_to_u8(w_lo), a1 = nib_to_u8(w_hi);
-                        const uint32_t a2 = nib_to_u8(w_lo >> 4), a3 = nib_to_u8(w_hi >> 4);
+                        const uint32_t a0 = nib_to_s8x16(w_lo << 4), a1 = nib_to_s8x16(w_hi << 4);
+                        const uint32_t a2 = nib_to_s8x16(w_lo), a3 = nib_to_s8x16(w_hi);
 #pragma unroll
                         for (int mb = 0; mb < MBLK; ++mb)
-                            imma_u8s8(acc_i[mb], a0, a1, a2, a3, jj ? xv[mb].z : xv[mb].x, jj ? xv[mb].w : xv[mb].y);
+                            imma_s8s8(acc_i[mb], a0, a1, a2, a3, jj ? xv[mb].z : xv[mb].x, jj ? xv[mb].w : xv[mb].y);
                     }
                 }
                 float s_lo, s_hi;
