@@ -640,34 +640,38 @@ def run_profile_case(spec):
         rows = bench_moe(torch, gb, measured_peaks(), A, token_counts=(int(spec.split(":")[1]),), cpu_rows=False)
         print(json.dumps({"case": spec, **rows[0]}))
         return
-    if spec == "pass":
-        # the headline decode pass (28 layers + lm_head, M = 1): 2 warm-up + 2 timed passes, no graph
+    if spec.startswith("list:"):
+        # `list:L[:head]`: the headline's launch on L layers (7 projections each, M = 1), with
+        # the lm_head when `head` is given; 3 warm-up launches + 3 timed ones, no graph.
+        # `list:4` holds 0.2 GB of weights, more than the L2.
+        f = spec.split(":")
+        nl, with_head = int(f[1]), len(f) > 2 and f[2] == "head"
         gen = torch.Generator(device="cuda")
         gen.manual_seed(1234)
-        layers = [[make_linear(torch, gb, k, n, gen) for (_, k, n) in PROJ] for _ in range(LAYERS)]
-        head = make_linear(torch, gb, LM_HEAD[1], LM_HEAD[2], gen)
         xs = {k: torch.randn(1, k, device="cuda", generator=gen).to(torch.bfloat16) for k in (2048, 6144)}
-        mk = lambda n: torch.empty(1, n, device="cuda", dtype=torch.bfloat16)
-        yq, yk, yv, yo, yg, yu, yd, yh = mk(2048), mk(1024), mk(1024), mk(2048), mk(6144), mk(6144), mk(2048), mk(LM_HEAD[2])
-
-        def decode_pass():
-            for q, kk, v, o, gate, up, down in layers:
-                gb.forward_group([q, kk, v], xs[2048], outs=[yq, yk, yv])
-                o.forward(xs[2048], out=yo)
-                gb.forward_group([gate, up], xs[2048], outs=[yg, yu])
-                down.forward(xs[6144], out=yd)
-            head.forward(xs[2048], out=yh)
-
-        for _ in range(2):
-            decode_pass()
+        calls, nbytes = [], 0
+        for _ in range(nl):
+            for (_, k, n) in PROJ:
+                calls.append((make_linear(torch, gb, k, n, gen), xs[k], torch.empty(1, n, device="cuda", dtype=torch.bfloat16)))
+                nbytes += algo_bytes(k, n, 1)
+        if with_head:
+            _, k, n = LM_HEAD
+            calls.append((make_linear(torch, gb, k, n, gen), xs[k], torch.empty(1, n, device="cuda", dtype=torch.bfloat16)))
+            nbytes += algo_bytes(k, n, 1)
+        lst = gb.LinearList(calls, m=1)
+        for _ in range(3):
+            lst.run()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(2):
-            decode_pass()
+        for _ in range(3):
+            lst.run()
         b.record()
         torch.cuda.synchronize()
-        print(json.dumps({"case": spec, "ms_per_pass_no_graph": round(a.elapsed_time(b) / 2, 4)}))
+        assert lst.fault() == 0
+        us = a.elapsed_time(b) / 3 * 1e3
+        print(json.dumps({"case": spec, "linears": len(calls), "algorithmic_bytes": nbytes,
+                          "us_per_launch_no_graph": round(us, 3), "GBps": round(nbytes / us / 1e3, 1)}))
         return
     parts = spec.split(":")
     kind, k, n, m = parts[0], int(parts[1]), int(parts[2]), int(parts[3])
@@ -702,7 +706,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-moe", action="store_true")
     ap.add_argument("--profile", default=None,
-                    help="w4a16:K:N:M[:copies] | moe:T | pass - run one small case for a profiler capture")
+                    help="w4a16:K:N:M[:copies] | moe:T | list:L[:head] - run one small case for a profiler capture")
     args = ap.parse_args()
     if args.profile:
         run_profile_case(args.profile)

@@ -123,7 +123,10 @@ int garnet_b200_w4a16_workspace(garnet_b200_w4a16_t h, int m, size_t* bytes);
 /* y[m, n_local] = x[m, k] W^T.  x, y bf16 device pointers, row-major, 16-byte
  * aligned.  Q4Q8Linear::Forward (q4q8_linear.cpp:315-389).  `flags`: bit 0 asks
  * for a programmatic dependent launch, so that this kernel's weight prefetch
- * overlaps the tail of the previous kernel in the stream. */
+ * overlaps the tail of the previous kernel in the stream.  Up to 16 rows (8 when
+ * K > 4096) take the streaming kernel: exact integer sums per group of 15-bit block
+ * fixed-point activations; more rows take the tensor-core tile kernel, which multiplies
+ * by the weights rounded once to bf16. */
 int garnet_b200_w4a16_run(garnet_b200_w4a16_t h, const void* d_x, void* d_y, int m, void* d_workspace,
                           size_t workspace_bytes, unsigned flags, void* stream);
 

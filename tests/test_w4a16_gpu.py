@@ -79,7 +79,10 @@ def test_linear_matches_exact_oracle(n, k, m):
     torch.cuda.synchronize()
     assert lin.fault() == 0
     _, y64 = oracle.w4a16_exact(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"])
-    check_close(y, y64, rounded_weights=m > 16)
+    # the tile kernel (weights rounded once to bf16) takes more than 16 rows, and more than 8
+    # rows of a K above 4096: that many quantised rows do not fit the streaming kernel's
+    # shared memory beside its ring
+    check_close(y, y64, rounded_weights=m > 16 or (m > 8 and k > 4096))
 
 
 @pytest.mark.parametrize("m", [33, 64, 130, 256, 300])
