@@ -63,13 +63,6 @@ __device__ __forceinline__ void st_relaxed_gpu_v2(void* p, uint32_t a, uint32_t 
 }
 __device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 
-#ifdef GB_STREAM_TRACE
-__device__ unsigned long long g_trace[4096];
-#define GB_TRACE(op, slot) do { if (blockIdx.x == 5 && (op) < 500) g_trace[(op) * 8 + (slot)] = global_timer_ns(); } while (0)
-#else
-#define GB_TRACE(op, slot) do {} while (0)
-#endif
-
 struct Ctl {
     volatile int abort_flag;
     int warps_done;   // consumer warps that have finished the list
@@ -243,6 +236,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
     volatile int* tags = reinterpret_cast<volatile int*>(smem + plan.tags);
     float* sx = reinterpret_cast<float*>(smem + plan.sx);
     int* pcnt = reinterpret_cast<int*>(smem + plan.pcnt);
+    volatile int* pgen = reinterpret_cast<volatile int*>(smem + plan.pgen);
     float* partial = reinterpret_cast<float*>(smem + plan.partial);
     uint8_t* xq = smem + plan.xq;
     uint8_t* ring = smem + plan.ring;
@@ -267,7 +261,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
     // control words, part counters, the all-zero activation row (the scale factors and bias
     // terms need no clearing: every entry that is read has been staged)
     for (int i = threadIdx.x; i < int(sizeof(Ctl) / 4); i += blockDim.x) reinterpret_cast<int*>(ctl)[i] = 0;
-    for (int i = threadIdx.x; i < PS; i += blockDim.x) pcnt[i] = 0;
+    for (int i = threadIdx.x; i < PS; i += blockDim.x) {
+        pcnt[i] = 0;
+        pgen[i] = 0;
+    }
     for (int b = 0; b < p.nbuf; ++b)
         for (int i = threadIdx.x; i < plan.xq_stride / 16; i += blockDim.x)
             *reinterpret_cast<uint4*>(xq + size_t(b) * plan.xq_bytes + size_t(2 * p.m) * plan.xq_stride + i * 16) = make_uint4(0, 0, 0, 0);
@@ -379,7 +376,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
             const int part = local - sl * op.parts;
             const int round = int((unsigned long long)(unsigned)my_q * p.inv_ring >> 40), stage = my_q - round * NS;
             const int phase = round & 1;
-            const int pslot = my_q - int((unsigned long long)(unsigned)my_q * p.inv_pslots >> 40) * PS;
+            const int pround = int((unsigned long long)(unsigned)my_q * p.inv_pslots >> 40);
+            const int pslot = my_q - pround * PS;
             // A parity wait alone cannot tell this slot's phase from the phase two rounds
             // earlier: the stage's tag says which slot the completed phase carried.
             if (!mbar_try_wait(&full[stage], phase) || tags[stage] != my_q) {
@@ -458,14 +456,35 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                 acc[mb][1] = __fadd_rn(pr[mb][1][0], pr[mb][1][1]);
             }
 
-            if (lane == 0 && part == 0) GB_TRACE(i, 4);
             // ---- the parts of a strip meet in shared memory
             const int strip = s0 + sl;
             const int n_lo = strip * 16 + row_of_g(g), n_hi = n_lo + 8;
             bool writer = op.parts == 1;
             if (op.parts > 1) {
                 int pbase = pslot - part;             // slot of the strip's first part
-                if (pbase < 0) pbase += PS;
+                int bround = pround;
+                if (pbase < 0) {
+                    pbase += PS;
+                    --bround;
+                }
+                // A partial-sum slot (and the strip's counter) is taken again PS slots later.  The
+                // ring's depth makes that far away in time, but only this generation count makes
+                // it certain that the strip which used them before has been added up.
+                if (!__all_sync(0xffffffffu, pgen[pslot] == pround && pgen[pbase] == bround)) {
+                    const unsigned long long t0 = global_timer_ns();
+                    for (;;) {
+                        if (__all_sync(0xffffffffu, pgen[pslot] == pround && pgen[pbase] == bround)) break;
+                        if (__any_sync(0xffffffffu, ctl->abort_flag || global_timer_ns() - t0 > limit)) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) {
+                        if (lane == 0) give_up(p, ctl, 4);
+                        break;
+                    }
+                }
+                __threadfence_block();
                 float* mine = partial + size_t(pslot) * (MBLK * 64);
 #pragma unroll
                 for (int mb = 0; mb < MBLK; ++mb)
@@ -512,10 +531,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                         }
                     }
                     if (lane == 0) pcnt[pbase] = 0;
+                    __threadfence_block();
+                    __syncwarp();
+                    for (int j = lane; j < op.parts; j += 32) {   // the strip's slots and counter may be taken again
+                        int idx = pbase + j;
+                        if (idx >= PS) idx -= PS;
+                        pgen[idx] = pgen[idx] + 1;
+                    }
                     writer = true;
                 }
             }
-            if (writer && lane == 0) GB_TRACE(i, 5);
             if (writer) {
 #pragma unroll
                 for (int mb = 0; mb < MBLK; ++mb) {
@@ -533,7 +558,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);
-            if (writer && lane == 0) GB_TRACE(i, 6);
             my_q = -1;
         }
         q_base = q_end;
@@ -868,14 +892,6 @@ int garnet_b200_w4a16_list_fault(garnet_b200_w4a16_list_t ll)
     LinearList* l = reinterpret_cast<LinearList*>(ll);
     return l && l->fault_host ? *l->fault_host : -1;
 }
-
-#ifdef GB_STREAM_TRACE
-int garnet_b200_w4a16_trace(unsigned long long* out, int n)
-{
-    GB_CUDA(cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * size_t(n)));
-    return 0;
-}
-#endif
 
 void garnet_b200_w4a16_list_destroy(garnet_b200_w4a16_list_t ll) { delete reinterpret_cast<LinearList*>(ll); }
 

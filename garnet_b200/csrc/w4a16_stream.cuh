@@ -73,7 +73,7 @@ struct StreamParams {
 
 // Shared-memory plan (byte offsets), the same on host and device.
 struct StreamSmem {
-    int bars, ctl, tags, sx, pcnt, optable, partial, xq, ring, total;
+    int bars, ctl, tags, sx, pcnt, pgen, optable, partial, xq, ring, total;
     int xq_stride, xq_rows, xq_bytes, mblk, part_slots, ring_slots;
 };
 
@@ -93,7 +93,8 @@ __host__ __device__ inline StreamSmem stream_smem_plan(int m, int max_chunks, in
     p.ctl = off;    off += 128;                                      // abort flag, finished warps
     p.tags = off;   off += kMaxRingSlots * 4;                        // slot index each ring stage currently holds
     p.sx = off;     off += nbuf * max_chunks * p.mblk * 4 * 4;       // [buf][chunk][mblk][4] float
-    p.pcnt = off;   off += p.part_slots * 4;
+    p.pcnt = off;   off += p.part_slots * 4;                         // parts of a strip that have arrived
+    p.pgen = off;   off += p.part_slots * 4;                         // times a partial-sum slot has been released
     off = (off + 15) & ~15;
     p.optable = off; off += table_ops * int(sizeof(StreamOp));       // copy of a short op table
     off = (off + 127) & ~127;
