@@ -45,11 +45,11 @@ PROJ = [("q_proj", 2048, 2048), ("k_proj", 2048, 1024), ("v_proj", 2048, 1024), 
 LM_HEAD = ("lm_head", 2048, 151936)
 SWEEP_M = [1, 4, 16, 64, 256]
 # dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of a launch of
-# w4a16_list_kernel, from the ncu capture summarised in the file named below (a
-# four-layer list, 103.8 MB of weights, captured because the full pass is too large to
-# replay under ncu; traffic grows in proportion to the weights streamed)
-TRAFFIC_RATIO = 1.01
-TRAFFIC_SOURCE = "profiles/w4a16_list_kernel_4layers_m1.md"
+# w4a16_list_kernel, from the ncu capture summarised in the file named below (an
+# eight-layer list, 208 MB of weights, captured instead of the full 890 MB pass to keep the
+# replay short; traffic grows in proportion to the weights streamed)
+TRAFFIC_RATIO = 1.017
+TRAFFIC_SOURCE = "profiles/w4a16_list_kernel_8layers_m1.md"
 
 
 def weight_bytes(k, n):

@@ -36,6 +36,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_w4a16_packed_bytes.argtypes = [i, i, i, c.POINTER(sz)]
     L.garnet_b200_w4a16_pack_host.argtypes = [vp, vp, i, i, i, i, vp]
     L.garnet_b200_w4a16_create.argtypes = [vp, vp, i, i, i, i, i, i, vp, c.POINTER(vp)]
+    L.garnet_b200_w4a16_create_k_shard.argtypes = [vp, vp, i, i, i, i, i, i, vp, c.POINTER(vp)]
     L.garnet_b200_w4a16_create_prepacked.argtypes = [vp, i, i, i, i, c.POINTER(vp)]
     L.garnet_b200_w4a16_shape.argtypes = [vp, c.POINTER(i), c.POINTER(i)]
     L.garnet_b200_w4a16_workspace.argtypes = [vp, i, c.POINTER(sz)]
@@ -71,6 +72,11 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_mxfp4_decode.argtypes = [vp, vp, vp, i, vp]
     L.garnet_b200_moe_dequant.argtypes = [vp, i, i, vp, vp]
     L.garnet_b200_mx_split_rows.argtypes = [vp, i, i, vp, vp, vp, vp]
+    L.garnet_b200_moe_packed_bytes.argtypes = [vp, i, i, i, c.POINTER(sz)]
+    L.garnet_b200_moe_pack_host.argtypes = [vp, i, i, vp, vp, i, vp]
+    L.garnet_b200_moe_packed_view.argtypes = [vp, i, i, c.POINTER(vp), c.POINTER(sz)]
+    L.garnet_b200_moe_create_prepacked.argtypes = [vp, vp, vp, vp, c.POINTER(vp)]
+    L.garnet_b200_moe_gather_intermediate_shard.argtypes = [vp, sz, c.POINTER(c.c_longlong), i, sz, i, i, i, vp]
     L.garnet_b200_comm_create.argtypes = [i, i, sz, c.POINTER(vp)]
     L.garnet_b200_comm_export.argtypes = [vp, vp, sz]
     L.garnet_b200_comm_connect.argtypes = [vp, vp]
@@ -82,6 +88,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_comm_channel_destroy.restype = None
     L.garnet_b200_comm_all_gather.argtypes = [vp, vp, sz, vp, vp]
     L.garnet_b200_comm_all_reduce.argtypes = [vp, vp, vp, sz, i, vp]
+    L.garnet_b200_comm_all_reduce_bf16.argtypes = [vp, vp, vp, sz, vp]
     L.garnet_b200_comm_selftest_wait.argtypes = [vp, i, vp]
     L.garnet_b200_moe_ep_arena_bytes.argtypes = [vp, i, i, c.POINTER(sz)]
     L.garnet_b200_moe_ep_create.argtypes = [vp, vp, i, c.POINTER(vp)]

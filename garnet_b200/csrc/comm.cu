@@ -77,7 +77,7 @@ struct ChannelDev {
 // mode 0: gather (the result is the local region); 1: sum of fp32 contributions;
 // 2: contributions travel as bf16, are summed in fp32 in rank order and rounded to bf16
 // (for two ranks: exactly bf16(a + b), the reference's wire format,
-// plugins/gpt_oss/cuda/tp_peer_math.cuh:10-14).
+// plugins/gpt_oss/cuda/tp_peer_math.cuh:10-14); 3: the same with bf16 source and result.
 __global__ void comm_exchange_kernel(const ChannelDev ch, const void* __restrict__ src, size_t bytes, int mode,
                                      void* __restrict__ dst_any, size_t count)
 {
@@ -135,6 +135,15 @@ __global__ void comm_exchange_kernel(const ChannelDev ch, const void* __restrict
         for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs * ch.world; i += size_t(gridDim.x) * blockDim.x) {
             const size_t s = i / vecs, v = i - s * vecs;
             *reinterpret_cast<uint4*>(dst + s * bytes + v * 16) = ld_cg_v4(region + s * ch.slot_bytes + v * 16);
+        }
+    } else if (mode == 3) {
+        const uint8_t* region = ch.peer_base[ch.rank] + ch.region_off + size_t(parity) * ch.world * ch.slot_bytes;
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(dst_any);
+        for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x) {
+            float sum = 0.f;
+            for (int s = 0; s < ch.world; ++s)
+                sum += __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(region + size_t(s) * ch.slot_bytes) + i)));
+            dst[i] = __float2bfloat16_rn(sum);
         }
     } else {
         const uint8_t* region = ch.peer_base[ch.rank] + ch.region_off + size_t(parity) * ch.world * ch.slot_bytes;
@@ -351,6 +360,17 @@ int garnet_b200_comm_all_reduce(garnet_b200_channel_t hh, const float* d_src, fl
     if (bytes > ch->slot_bytes) return fail(GARNET_B200_INVALID_VALUE, "comm_all_reduce: %zu bytes exceed the channel's slot of %zu", bytes, ch->slot_bytes);
     if (reinterpret_cast<uintptr_t>(d_src) & 15) return fail(GARNET_B200_INVALID_VALUE, "comm_all_reduce: source must be 16-byte aligned");
     return channel_launch(ch, d_src, bytes, wire_dtype == GARNET_B200_FP32 ? 1 : 2, d_dst, count, static_cast<cudaStream_t>(stream));
+}
+
+int garnet_b200_comm_all_reduce_bf16(garnet_b200_channel_t hh, const void* d_src, void* d_dst, size_t count, void* stream)
+{
+    Channel* ch = reinterpret_cast<Channel*>(hh);
+    if (!ch || !d_src || !d_dst || count == 0) return fail(GARNET_B200_INVALID_VALUE, "comm_all_reduce_bf16: bad argument");
+    const size_t bytes = count * 2;
+    if (bytes > ch->slot_bytes) return fail(GARNET_B200_INVALID_VALUE, "comm_all_reduce_bf16: %zu bytes exceed the channel's slot of %zu", bytes, ch->slot_bytes);
+    if ((reinterpret_cast<uintptr_t>(d_src) & 15) || (reinterpret_cast<uintptr_t>(d_dst) & 1))
+        return fail(GARNET_B200_INVALID_VALUE, "comm_all_reduce_bf16: source must be 16-byte aligned");
+    return channel_launch(ch, d_src, bytes, 3, d_dst, count, static_cast<cudaStream_t>(stream));
 }
 
 int garnet_b200_comm_selftest_wait(garnet_b200_comm_t cc, int limit_ms, void* stream)

@@ -25,6 +25,7 @@
 #include "common.cuh"
 #include "layout.h"
 #include "moe.h"
+#include "moe_pack.h"
 
 namespace gb200 {
 
@@ -32,36 +33,18 @@ constexpr int kMxChunkBytes = 512 + 32;
 
 // ------------------------------------------------------------------ repack
 
-// One thread per packed 32-bit word.  `interleaved` = 1 for the gate/up matrix:
-// original row 2i is gate_i and row 2i+1 is up_i (gpt_oss_kernels.cu:776); the
-// packed matrix stores gate_i at strip row r and up_i at strip row r + 8
-// (i = 8*strip + r), so that one MMA accumulator lane holds the gate and the up
-// value of the same intermediate channel.
+// One thread per packed 32-bit word (moe_pack.h says where each comes from).
 __global__ void mx_repack_codes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, PackGeom geo,
                                        int interleaved)
 {
     const int expert = blockIdx.y;
-    const size_t words_per_chunk = geo.chunk_data / 4;
-    const size_t total = size_t(geo.strips_padded) * geo.chunks * words_per_chunk;
     const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const size_t chunk_lin = idx / words_per_chunk;
-    const int w = int(idx % words_per_chunk);
-    const int strip = int(chunk_lin / geo.chunks), chunk = int(chunk_lin % geo.chunks);
-    const int unit = (w >> 2) & 31, word = w & 3;          // one 512-byte tile per chunk
-    const int g = unit >> 2, t = unit & 3, h = word & 1, j = word >> 1;
-    const int r16 = row_of_g(g) + 8 * h;
-    const int n = strip * 16 + r16;                          // packed row
-    const int k0 = chunk * 64 + (t + 4 * j) * 8;
+    if (idx >= mx_stream_words(geo)) return;
+    size_t db, sb;
     uint32_t out = 0;
-    if (n < geo.rows && k0 < geo.cols) {
-        const int src_row = interleaved ? 2 * (strip * 8 + (r16 & 7)) + (r16 >> 3) : n;
-        const size_t sb = (size_t(expert) * geo.rows + src_row) * size_t(geo.cols / 2) + k0 / 2;
-        out = *reinterpret_cast<const uint32_t*>(src + sb);
-    }
-    const size_t ob = size_t(expert) * geo.matrix_bytes() + (size_t(strip) * geo.chunks + chunk) * geo.chunk_bytes +
-                      size_t(w) * 4;
-    *reinterpret_cast<uint32_t*>(dst + ob) = out;
+    if (mx_stream_word(geo, idx, interleaved, &db, &sb))
+        out = *reinterpret_cast<const uint32_t*>(src + size_t(expert) * geo.rows * size_t(geo.cols / 2) + sb);
+    *reinterpret_cast<uint32_t*>(dst + size_t(expert) * geo.matrix_bytes() + db) = out;
 }
 
 // One thread per (packed row, 32-column group).  Padding gets scale 127 (1.0).
@@ -69,18 +52,12 @@ __global__ void mx_repack_scales_kernel(const uint8_t* __restrict__ src, uint8_t
                                         int interleaved)
 {
     const int expert = blockIdx.y;
-    const int groups = geo.chunks * 2;
-    const size_t total = size_t(geo.strips_padded) * 16 * groups;
     const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const int n = int(idx / groups), grp = int(idx % groups);
+    if (idx >= mx_stream_scale_count(geo)) return;
+    size_t db, sb;
     uint8_t e = 127;
-    if (n < geo.rows && grp * 32 < geo.cols) {
-        const int strip = n >> 4, r16 = n & 15;
-        const int src_row = interleaved ? 2 * (strip * 8 + (r16 & 7)) + (r16 >> 3) : n;
-        e = src[(size_t(expert) * geo.rows + src_row) * size_t(geo.cols / 32) + grp];
-    }
-    dst[size_t(expert) * geo.matrix_bytes() + locate_scale(geo, n, grp * 32)] = e;
+    if (mx_stream_scale(geo, idx, interleaved, &db, &sb)) e = src[size_t(expert) * geo.rows * size_t(geo.cols / 32) + sb];
+    dst[size_t(expert) * geo.matrix_bytes() + db] = e;
 }
 
 // Flags e8m0 bytes 0 (2^-127, an fp32 subnormal) and 255 (NaN), which need the
@@ -926,7 +903,8 @@ MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens)
     const int mx_world = o.ep_world > 1 ? o.ep_world : 1;
     const int mx_local = mx_world <= 1 ? o.experts   // the same count as Moe::local_experts()
                          : o.ep_interleaved ? (o.experts - o.ep_rank + mx_world - 1) / mx_world : o.experts / mx_world;
-    const bool mx = moe_mx_enabled() && (moe_mx_forced() || slots > size_t(6) * mx_local);
+    const int mx_mode = moe_mx_mode_of(o);
+    const bool mx = mx_mode == 2 || (mx_mode == 1 && slots > size_t(6) * mx_local);
     const MoeMxPlan mxp = moe_mx_plan(o, tokens, int(slots));
     w.mx_tp = take(mx ? size_t(o.experts + 1) * 4 : 0);
     w.mx_q = take(mx ? mxp.q_bytes : 0);
@@ -938,30 +916,50 @@ MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens)
     return w;
 }
 
-static int validate_options(const garnet_b200_moe_options* o)
+int moe_resolve_options(const garnet_b200_moe_options* in, garnet_b200_moe_options* eff)
 {
-    if (!o) return fail(GARNET_B200_INVALID_VALUE, "moe: null options");
-    if (o->abi != GARNET_B200_ABI || o->struct_size != int(sizeof(garnet_b200_moe_options)))
-        return fail(GARNET_B200_INVALID_VALUE, "moe: options abi/size mismatch (abi %d, size %d)", o->abi, o->struct_size);
-    if (o->hidden <= 0 || o->intermediate <= 0 || o->experts <= 0 || o->top_k <= 0)
+    if (!in) return fail(GARNET_B200_INVALID_VALUE, "moe: null options");
+    // the struct as first published ends after `limit`; later fields default to zero
+    const int first_size = int(offsetof(garnet_b200_moe_options, layouts));
+    if (in->abi != GARNET_B200_ABI || (in->struct_size != first_size && in->struct_size != int(sizeof(garnet_b200_moe_options))))
+        return fail(GARNET_B200_INVALID_VALUE, "moe: options abi/size mismatch (abi %d, size %d)", in->abi, in->struct_size);
+    garnet_b200_moe_options o{};
+    std::memcpy(&o, in, size_t(in->struct_size));
+    o.struct_size = int(sizeof(garnet_b200_moe_options));
+    if (o.hidden <= 0 || o.intermediate <= 0 || o.experts <= 0 || o.top_k <= 0)
         return fail(GARNET_B200_INVALID_VALUE, "moe: hidden, intermediate, experts, top_k must be positive");
-    if (o->hidden % 32 || o->intermediate % 32)
+    if (o.hidden % 32 || o.intermediate % 32)
         return fail(GARNET_B200_INVALID_VALUE, "moe: hidden and intermediate must be multiples of 32");
-    if (o->top_k > 8 || o->top_k > o->experts)
+    if (o.top_k > 8 || o.top_k > o.experts)
         return fail(GARNET_B200_INVALID_VALUE, "moe: top_k must be <= 8 and <= experts");
-    if (o->experts > 1024) return fail(GARNET_B200_NOT_SUPPORTED, "moe: more than 1024 experts");
-    if (o->io_dtype != GARNET_B200_FP32 && o->io_dtype != GARNET_B200_BF16)
+    if (o.experts > 1024) return fail(GARNET_B200_NOT_SUPPORTED, "moe: more than 1024 experts");
+    if (o.io_dtype != GARNET_B200_FP32 && o.io_dtype != GARNET_B200_BF16)
         return fail(GARNET_B200_INVALID_VALUE, "moe: io dtype must be fp32 or bf16");
-    if (!(o->limit > 0.f) || o->limit * (o->limit + 1.f) > 60000.f)
-        return fail(GARNET_B200_NOT_SUPPORTED, "moe: swiglu limit %g is outside the fp16 activation range", o->limit);
-    if (o->ep_world > 1) {
-        if (o->ep_rank < 0 || o->ep_rank >= o->ep_world)
-            return fail(GARNET_B200_INVALID_VALUE, "moe: ep_rank %d outside ep_world %d", o->ep_rank, o->ep_world);
-        if (!o->ep_interleaved && o->experts % o->ep_world)
+    if (!(o.limit > 0.f) || o.limit * (o.limit + 1.f) > 60000.f)
+        return fail(GARNET_B200_NOT_SUPPORTED, "moe: swiglu limit %g is outside the fp16 activation range", o.limit);
+    if (o.ep_world > 1) {
+        if (o.ep_rank < 0 || o.ep_rank >= o.ep_world)
+            return fail(GARNET_B200_INVALID_VALUE, "moe: ep_rank %d outside ep_world %d", o.ep_rank, o.ep_world);
+        if (!o.ep_interleaved && o.experts % o.ep_world)
             return fail(GARNET_B200_INVALID_VALUE, "moe: experts not divisible by ep_world");
     }
-    if (size_t(moe_smem_plan(std::max(o->hidden, o->intermediate)).total) > kMaxDynamicSmem)
+    if (o.layouts < 0 || o.layouts > GARNET_B200_MOE_LAYOUT_BLOCK)
+        return fail(GARNET_B200_INVALID_VALUE, "moe: layouts must be 0 (both), 1 (stream) or 2 (block)");
+    if (o.tp_world > 1) {
+        if (o.tp_rank < 0 || o.tp_rank >= o.tp_world)
+            return fail(GARNET_B200_INVALID_VALUE, "moe: tp_rank %d outside tp_world %d", o.tp_rank, o.tp_world);
+        if (o.intermediate % (32 * o.tp_world))
+            return fail(GARNET_B200_INVALID_VALUE, "moe: intermediate %d does not split into %d parts of whole 32-column groups",
+                        o.intermediate, o.tp_world);
+        o.intermediate /= o.tp_world;   // from here on: this rank's share
+    } else {
+        o.tp_world = 0;
+        o.tp_rank = 0;
+        o.tp_weights_sharded = 0;
+    }
+    if (size_t(moe_smem_plan(std::max(o.hidden, o.intermediate)).total) > kMaxDynamicSmem)
         return fail(GARNET_B200_NOT_SUPPORTED, "moe: hidden/intermediate too large for the streaming kernel");
+    *eff = o;
     return GARNET_B200_OK;
 }
 
@@ -987,12 +985,14 @@ int Moe::local_experts() const
 Moe::~Moe()
 {
     if (router_w3) cudaFree(router_w3);
-    for (int i = 0; i < 2; ++i) {
-        if (mxr_w[i]) cudaFree(mxr_w[i]);
-        if (mxr_sf[i]) cudaFree(mxr_sf[i]);
+    if (owns_packed) {
+        for (int i = 0; i < 2; ++i)
+            if (mxr_w[i]) cudaFree(mxr_w[i]);   // blocks and scale atoms are one allocation
+        if (packed_up) cudaFree(packed_up);
+        if (packed_down) cudaFree(packed_down);
     }
-    if (packed_up) cudaFree(packed_up);
-    if (packed_down) cudaFree(packed_down);
+    if (own_up_bias) cudaFree(own_up_bias);
+    if (zero_down_bias) cudaFree(zero_down_bias);
     if (flag_dev) cudaFree(flag_dev);
     if (fault_host) cudaFreeHost(fault_host);
 }
@@ -1008,35 +1008,106 @@ static cudaError_t set_moe_attr()
 // router W, router b, gate_up blocks, gate_up scales, gate_up bias, down blocks,
 // down scales, down bias.  Expert tensors hold all experts, or only this rank's
 // when expert_weights_sharded is set (gpt_oss_weight_shard.h:76-92).
-int Moe::prepare(const void* const* weights, cudaStream_t stream)
+// Scale bytes 0 and 255 in a packed blob (either layout): see mx_scan_scales_kernel.
+__global__ void mx_scan_packed_kernel(const uint8_t* __restrict__ blob, size_t count, int stream_layout, int chunk_bytes,
+                                      int* flag)
 {
-    const int el = opt.expert_weights_sharded ? local_experts() : opt.experts;
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= count) return;
+    // streaming layout: the last 32 bytes of every chunk are scales; block layout: `blob` is the atom region
+    const size_t at = stream_layout ? (idx / kScaleBytesPerChunk) * chunk_bytes + (chunk_bytes - kScaleBytesPerChunk) +
+                                          idx % kScaleBytesPerChunk
+                                    : idx;
+    if (blob[at] == 0 || blob[at] == 255) atomicOr(flag, 1);
+}
+
+int Moe::setup_common(cudaStream_t stream)
+{
     GB_CUDA(cudaGetDevice(&device));
+    mx_mode = moe_mx_mode_of(opt);
     geo_up = make_geom(kFormatMxfp4, 2 * opt.intermediate, opt.hidden, 32);
     geo_down = make_geom(kFormatMxfp4, opt.hidden, opt.intermediate, 32);
     stored_experts = local_experts();
-    GB_CUDA(cudaMalloc(&packed_up, geo_up.matrix_bytes() * stored_experts));
-    GB_CUDA(cudaMalloc(&packed_down, geo_down.matrix_bytes() * stored_experts));
     GB_CUDA(cudaMalloc(&flag_dev, sizeof(int)));
     GB_CUDA(cudaMemsetAsync(flag_dev, 0, sizeof(int), stream));
     GB_CUDA(cudaHostAlloc(&fault_host, sizeof(int), cudaHostAllocMapped));
     *fault_host = 0;
     GB_CUDA(cudaHostGetDevicePointer(&fault_dev, fault_host, 0));
+    for (int pass = 0; pass < 2; ++pass) {
+        const PackGeom& geo = pass == 0 ? geo_up : geo_down;
+        mx_kp[pass] = (geo.cols + kMxBlockCols - 1) / kMxBlockCols * kMxBlockCols;
+        mx_kslabs[pass] = mx_kp[pass] / kMxBlockCols;
+    }
+    return GARNET_B200_OK;
+}
 
+int Moe::prepare(const void* const* weights, cudaStream_t stream)
+{
+    if (int rc = setup_common(stream)) return rc;
+    const bool want_stream = opt.layouts != GARNET_B200_MOE_LAYOUT_BLOCK;
+    const bool want_block = mx_mode != 0;
+    if (want_stream) {
+        GB_CUDA(cudaMalloc(&packed_up, geo_up.matrix_bytes() * stored_experts));
+        GB_CUDA(cudaMalloc(&packed_down, geo_down.matrix_bytes() * stored_experts));
+    }
     const MoeShard sh = shard();
     // source expert index of stored expert s
     auto src_expert = [&](int s) {
         if (opt.expert_weights_sharded || sh.world <= 1) return s;
         return sh.interleaved ? s * sh.world + sh.rank : sh.lo + s;
     };
-    (void)el;
+    const int src_experts = opt.expert_weights_sharded ? stored_experts : opt.experts;
+    const uint8_t* src_blocks[2] = {static_cast<const uint8_t*>(weights[2]), static_cast<const uint8_t*>(weights[5])};
+    const uint8_t* src_scales[2] = {static_cast<const uint8_t*>(weights[3]), static_cast<const uint8_t*>(weights[6])};
+    up_bias_ptr = static_cast<const float*>(weights[4]);
+    down_bias_ptr = static_cast<const float*>(weights[7]);
+    // Intermediate-axis split over full tensors: gather this rank's gate/up row pairs and
+    // down-projection K groups first (GatherGptOssIntermediateShard modes 1 and 2,
+    // gpt_oss_weight_shard.h:48-57), into temporaries that are released after the repack.
+    uint8_t* gathered[4] = {nullptr, nullptr, nullptr, nullptr};
+    auto free_gathered = [&] {
+        for (uint8_t*& g : gathered)
+            if (g) cudaFree(g), g = nullptr;
+    };
+    if (opt.tp_world > 1 && !opt.tp_weights_sharded) {
+        const size_t il = size_t(opt.intermediate), w = size_t(opt.tp_world), r = size_t(opt.tp_rank), hd = size_t(opt.hidden);
+        struct Cut { const void* src; size_t width, height; void** dst; };   // rows of `width` bytes out of rows w times as long
+        void* up_bias_tmp = nullptr;
+        const Cut cuts[5] = {
+            {src_blocks[0], 2 * il * hd / 2, size_t(src_experts), reinterpret_cast<void**>(&gathered[0])},
+            {src_scales[0], 2 * il * hd / 32, size_t(src_experts), reinterpret_cast<void**>(&gathered[1])},
+            {src_blocks[1], il / 2, size_t(src_experts) * hd, reinterpret_cast<void**>(&gathered[2])},
+            {src_scales[1], il / 32, size_t(src_experts) * hd, reinterpret_cast<void**>(&gathered[3])},
+            {up_bias_ptr, 2 * il * 4, size_t(src_experts), &up_bias_tmp},
+        };
+        for (const Cut& c : cuts) {
+            cudaError_t e = cudaMalloc(c.dst, c.width * c.height);
+            if (e == cudaSuccess)
+                e = cudaMemcpy2DAsync(*c.dst, c.width, static_cast<const uint8_t*>(c.src) + r * c.width, c.width * w, c.width,
+                                      c.height, cudaMemcpyDeviceToDevice, stream);
+            if (e != cudaSuccess) {
+                free_gathered();
+                if (up_bias_tmp) cudaFree(up_bias_tmp);
+                return fail(GARNET_B200_CUDA_ERROR, "moe_create: gathering the intermediate shard failed: %s", cudaGetErrorString(e));
+            }
+        }
+        own_up_bias = static_cast<float*>(up_bias_tmp);
+        up_bias_ptr = own_up_bias;
+        src_blocks[0] = gathered[0], src_scales[0] = gathered[1], src_blocks[1] = gathered[2], src_scales[1] = gathered[3];
+    }
+    if (opt.tp_world > 1 && opt.tp_rank != 0) {
+        // the down bias is added once, by rank 0 (mode 3 of the reference's gather, :42-47)
+        const size_t n = size_t(src_experts) * opt.hidden * sizeof(float);
+        GB_CUDA(cudaMalloc(&zero_down_bias, n));
+        GB_CUDA(cudaMemsetAsync(zero_down_bias, 0, n, stream));
+        down_bias_ptr = zero_down_bias;
+    }
     for (int pass = 0; pass < 2; ++pass) {
         const PackGeom& geo = pass == 0 ? geo_up : geo_down;
-        const uint8_t* blocks = static_cast<const uint8_t*>(weights[pass == 0 ? 2 : 5]);
-        const uint8_t* scales = static_cast<const uint8_t*>(weights[pass == 0 ? 3 : 6]);
+        const uint8_t* blocks = src_blocks[pass];
+        const uint8_t* scales = src_scales[pass];
         uint8_t* dst = pass == 0 ? packed_up : packed_down;
-        const size_t words = size_t(geo.strips_padded) * geo.chunks * (geo.chunk_data / 4);
-        const size_t nsc = size_t(geo.strips_padded) * 16 * geo.chunks * 2;
+        const size_t words = mx_stream_words(geo), nsc = mx_stream_scale_count(geo);
         const size_t blk_per_expert = size_t(geo.rows) * geo.cols / 2, sc_per_expert = size_t(geo.rows) * geo.cols / 32;
         // contiguous runs of source experts are repacked with one launch each
         int s = 0;
@@ -1044,35 +1115,92 @@ int Moe::prepare(const void* const* weights, cudaStream_t stream)
             int run = 1;
             while (s + run < stored_experts && src_expert(s + run) == src_expert(s) + run) ++run;
             const size_t e0 = size_t(src_expert(s));
-            mx_repack_codes_kernel<<<dim3(unsigned((words + 255) / 256), run), 256, 0, stream>>>(
-                blocks + e0 * blk_per_expert, dst + size_t(s) * geo.matrix_bytes(), geo, pass == 0);
-            mx_repack_scales_kernel<<<dim3(unsigned((nsc + 255) / 256), run), 256, 0, stream>>>(
-                scales + e0 * sc_per_expert, dst + size_t(s) * geo.matrix_bytes(), geo, pass == 0);
+            if (want_stream) {
+                mx_repack_codes_kernel<<<dim3(unsigned((words + 255) / 256), run), 256, 0, stream>>>(
+                    blocks + e0 * blk_per_expert, dst + size_t(s) * geo.matrix_bytes(), geo, pass == 0);
+                mx_repack_scales_kernel<<<dim3(unsigned((nsc + 255) / 256), run), 256, 0, stream>>>(
+                    scales + e0 * sc_per_expert, dst + size_t(s) * geo.matrix_bytes(), geo, pass == 0);
+            }
             const size_t cnt = size_t(run) * sc_per_expert;
             mx_scan_scales_kernel<<<unsigned((cnt + 255) / 256), 256, 0, stream>>>(scales + e0 * sc_per_expert, cnt,
                                                                                  flag_dev);
-            if (moe_mx_enabled())
-                if (int rc = init_mx(pass, blocks + e0 * blk_per_expert, scales + e0 * sc_per_expert, s, run, stream))
+            if (want_block)
+                if (int rc = init_mxr(pass, blocks + e0 * blk_per_expert, scales + e0 * sc_per_expert, s, run, stream)) {
+                    free_gathered();
                     return rc;
+                }
             s += run;
         }
     }
+    const cudaError_t launched = cudaGetLastError();
+    const cudaError_t synced = cudaStreamSynchronize(stream);
+    free_gathered();
+    GB_CUDA(launched);
+    GB_CUDA(synced);
+    router_w_ptr = static_cast<const float*>(weights[0]);
+    router_b_ptr = static_cast<const float*>(weights[1]);
+    return finish_prepare(stream);
+}
+
+// The operator over packed blobs that the caller owns: nothing is copied or repacked.
+int Moe::prepare_prepacked(const void* const* small, const void* const* packed, cudaStream_t stream)
+{
+    owns_packed = false;
+    if (int rc = setup_common(stream)) return rc;
+    const bool want_stream = opt.layouts != GARNET_B200_MOE_LAYOUT_BLOCK;
+    const bool want_block = opt.layouts != GARNET_B200_MOE_LAYOUT_STREAM;
+    for (int i = 0; i < 4; ++i) {
+        const bool needed = i < 2 ? want_stream : want_block;
+        if (needed && !packed[i]) return fail(GARNET_B200_INVALID_VALUE, "moe_create_prepacked: packed blob %d is null", i);
+        if (needed && (reinterpret_cast<uintptr_t>(packed[i]) & 255))
+            return fail(GARNET_B200_INVALID_VALUE, "moe_create_prepacked: packed blob %d must be 256-byte aligned", i);
+    }
+    if (want_stream) {
+        packed_up = static_cast<uint8_t*>(const_cast<void*>(packed[0]));
+        packed_down = static_cast<uint8_t*>(const_cast<void*>(packed[1]));
+    }
+    for (int pass = 0; pass < 2; ++pass) {
+        const PackGeom& geo = pass == 0 ? geo_up : geo_down;
+        const MxBlockGeom g = make_block_geom(geo.rows, geo.cols);
+        if (want_block) {
+            mxr_w[pass] = static_cast<uint8_t*>(const_cast<void*>(packed[2 + pass]));
+            mxr_sf[pass] = mxr_w[pass] + size_t(stored_experts) * g.code_bytes();
+            mxr_ntiles[pass] = g.ntiles;
+        }
+        // the streaming kernels decode scale bytes 0 and 255 on a slower path: find out whether there are any
+        if (want_stream) {
+            const size_t cnt = size_t(stored_experts) * geo.strips_padded * geo.chunks * kScaleBytesPerChunk;
+            mx_scan_packed_kernel<<<unsigned((cnt + 255) / 256), 256, 0, stream>>>(pass == 0 ? packed_up : packed_down, cnt, 1,
+                                                                                  geo.chunk_bytes, flag_dev);
+        }
+    }
     GB_CUDA(cudaGetLastError());
+    router_w_ptr = static_cast<const float*>(small[0]);
+    router_b_ptr = static_cast<const float*>(small[1]);
+    up_bias_ptr = static_cast<const float*>(small[2]);
+    down_bias_ptr = static_cast<const float*>(small[3]);
+    if (opt.tp_world > 1 && opt.tp_rank != 0) {
+        const size_t n = size_t(stored_experts) * opt.hidden * sizeof(float);
+        GB_CUDA(cudaMalloc(&zero_down_bias, n));
+        GB_CUDA(cudaMemsetAsync(zero_down_bias, 0, n, stream));
+        down_bias_ptr = zero_down_bias;
+    }
+    return finish_prepare(stream);
+}
+
+int Moe::finish_prepare(cudaStream_t stream)
+{
     int flag = 0;
     GB_CUDA(cudaMemcpyAsync(&flag, flag_dev, sizeof(int), cudaMemcpyDeviceToHost, stream));
     GB_CUDA(cudaStreamSynchronize(stream));
     careful_scales = flag != 0;
-    router_w_ptr = static_cast<const float*>(weights[0]);
-    if (moe_mx_enabled()) {
+    if (mxr_w[0]) {
         if (int rc = finish_mx()) return rc;
         if (int rc = init_route_mma(stream)) return rc;
         GB_CUDA(cudaStreamSynchronize(stream));
     }
-    // router and biases are borrowed from the caller (engine-owned constants)
-    router_w_ptr = static_cast<const float*>(weights[0]);
-    router_b_ptr = static_cast<const float*>(weights[1]);
-    up_bias_ptr = static_cast<const float*>(weights[4]);
-    down_bias_ptr = static_cast<const float*>(weights[7]);
+    if (!packed_up && !mx_ok)
+        return fail(GARNET_B200_NOT_SUPPORTED, "moe: the block-scaled layout alone was asked for, but this shape or driver does not support it");
     // the router kernels also have a little static shared memory: leave room for it
     GB_CUDA(cudaFuncSetAttribute(moe_route_small_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  int(kMaxDynamicSmem - 2048)));
@@ -1267,7 +1395,7 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
         if (int rc = launch_stream(false, w, tokens, stream)) return rc;
     }
     const size_t n = size_t(tokens) * opt.hidden;
-    const int round_output = sh.world > 1 ? 0 : 1;
+    const int round_output = partial_output() ? 0 : 1;
     const bool streamed = true;   // both expert paths end in kernels that support a programmatic dependent launch
     if (opt.io_dtype == GARNET_B200_FP32)
         GB_CUDA(launch_pdl(moe_combine_kernel<float>, dim3(unsigned((n + 255) / 256)), dim3(256), 0, stream, streamed,
@@ -1463,9 +1591,10 @@ int garnet_b200_mxfp4_decode(const uint8_t* d_blocks, const uint8_t* d_scales, f
 
 int garnet_b200_moe_workspace(const garnet_b200_moe_options* o, int tokens, size_t* bytes)
 {
-    if (int rc = validate_options(o)) return rc;
+    garnet_b200_moe_options eff;
+    if (int rc = moe_resolve_options(o, &eff)) return rc;
     if (!bytes || tokens <= 0) return fail(GARNET_B200_INVALID_VALUE, "moe_workspace: bad argument");
-    *bytes = moe_workspace_plan(*o, tokens).total;
+    *bytes = moe_workspace_plan(eff, tokens).total;
     return GARNET_B200_OK;
 }
 
@@ -1474,13 +1603,14 @@ int garnet_b200_moe_create(const garnet_b200_moe_options* o, const void* const* 
 {
     if (!out) return fail(GARNET_B200_INVALID_VALUE, "moe_create: null output handle");
     *out = nullptr;
-    if (int rc = validate_options(o)) return rc;
+    garnet_b200_moe_options eff;
+    if (int rc = moe_resolve_options(o, &eff)) return rc;
     if (!weights) return fail(GARNET_B200_INVALID_VALUE, "moe_create: null weight list");
     for (int i = 0; i < 8; ++i)
         if (!weights[i]) return fail(GARNET_B200_INVALID_VALUE, "moe_create: weight operand %d is null", i + 1);
     Moe* h = new (std::nothrow) Moe();
     if (!h) return fail(GARNET_B200_OUT_OF_MEMORY, "moe_create: host allocation failed");
-    h->opt = *o;
+    h->opt = eff;
     int rc = h->prepare(weights, static_cast<cudaStream_t>(stream));
     // the address of the built-in scratch of garnet_b200_moe_run_static, so that no run call looks it up
     if (!rc) rc = moe_static_scratch(&h->static_scratch);
@@ -1490,6 +1620,52 @@ int garnet_b200_moe_create(const garnet_b200_moe_options* o, const void* const* 
     }
     *out = reinterpret_cast<garnet_b200_moe_t>(h);
     return GARNET_B200_OK;
+}
+
+int garnet_b200_moe_create_prepacked(const garnet_b200_moe_options* o, const void* const* small, const void* const* packed,
+                                     void* stream, garnet_b200_moe_t* out)
+{
+    if (!out) return fail(GARNET_B200_INVALID_VALUE, "moe_create_prepacked: null output handle");
+    *out = nullptr;
+    garnet_b200_moe_options eff;
+    if (int rc = moe_resolve_options(o, &eff)) return rc;
+    if (!small || !packed) return fail(GARNET_B200_INVALID_VALUE, "moe_create_prepacked: null operand list");
+    for (int i = 0; i < 4; ++i)
+        if (!small[i]) return fail(GARNET_B200_INVALID_VALUE, "moe_create_prepacked: small operand %d is null", i);
+    Moe* h = new (std::nothrow) Moe();
+    if (!h) return fail(GARNET_B200_OUT_OF_MEMORY, "moe_create_prepacked: host allocation failed");
+    h->opt = eff;
+    int rc = h->prepare_prepacked(small, packed, static_cast<cudaStream_t>(stream));
+    if (!rc) rc = moe_static_scratch(&h->static_scratch);
+    if (rc) {
+        delete h;
+        return rc;
+    }
+    *out = reinterpret_cast<garnet_b200_moe_t>(h);
+    return GARNET_B200_OK;
+}
+
+int garnet_b200_moe_packed_view(garnet_b200_moe_t hh, int which, int layout, const void** d_blob, size_t* bytes)
+{
+    Moe* h = reinterpret_cast<Moe*>(hh);
+    if (!h || !d_blob || !bytes || which < 0 || which > 1)
+        return fail(GARNET_B200_INVALID_VALUE, "moe_packed_view: bad argument");
+    const PackGeom& geo = which == 0 ? h->geo_up : h->geo_down;
+    if (layout == GARNET_B200_MOE_LAYOUT_STREAM) {
+        const uint8_t* p = which == 0 ? h->packed_up : h->packed_down;
+        if (!p) return fail(GARNET_B200_NOT_SUPPORTED, "moe_packed_view: this handle does not hold the streaming layout");
+        *d_blob = p;
+        *bytes = geo.matrix_bytes() * size_t(h->stored_experts);
+        return GARNET_B200_OK;
+    }
+    if (layout == GARNET_B200_MOE_LAYOUT_BLOCK) {
+        if (!h->mxr_w[which]) return fail(GARNET_B200_NOT_SUPPORTED, "moe_packed_view: this handle does not hold the block layout");
+        const MxBlockGeom g = make_block_geom(geo.rows, geo.cols);
+        *d_blob = h->mxr_w[which];
+        *bytes = size_t(h->stored_experts) * (g.code_bytes() + g.atom_bytes());
+        return GARNET_B200_OK;
+    }
+    return fail(GARNET_B200_INVALID_VALUE, "moe_packed_view: layout must be 1 (stream) or 2 (block)");
 }
 
 int garnet_b200_moe_run(garnet_b200_moe_t hh, const void* d_x, void* d_y, void* d_workspace, size_t workspace_bytes,
@@ -1502,9 +1678,10 @@ int garnet_b200_moe_run(garnet_b200_moe_t hh, const void* d_x, void* d_y, void* 
 
 int garnet_b200_moe_rows_workspace(const garnet_b200_moe_options* o, int rows, size_t* bytes)
 {
-    if (int rc = validate_options(o)) return rc;
+    garnet_b200_moe_options eff;
+    if (int rc = moe_resolve_options(o, &eff)) return rc;
     if (!bytes || rows <= 0) return fail(GARNET_B200_INVALID_VALUE, "moe_rows_workspace: bad argument");
-    *bytes = moe_rows_workspace_plan(*o, rows).total;
+    *bytes = moe_rows_workspace_plan(eff, rows).total;
     return GARNET_B200_OK;
 }
 
@@ -1548,7 +1725,8 @@ int garnet_b200_moe_route(garnet_b200_moe_t hh, const void* d_x, int* d_selected
 
 int garnet_b200_moe_route_workspace(const garnet_b200_moe_options* o, int tokens, size_t* bytes)
 {
-    if (int rc = validate_options(o)) return rc;
+    garnet_b200_moe_options eff;
+    if (int rc = moe_resolve_options(o, &eff)) return rc;
     if (!bytes || tokens <= 0 || tokens > kMoeMaxRows / o->top_k) return fail(GARNET_B200_INVALID_VALUE, "moe_route_workspace: bad argument");
     *bytes = std::max<size_t>(256, moe_route_partial_bytes(tokens, o->experts));
     return GARNET_B200_OK;
@@ -1577,6 +1755,7 @@ int garnet_b200_moe_dequant(garnet_b200_moe_t hh, int which, int stored_expert, 
     if (!h || !d_out || stored_expert < 0 || stored_expert >= h->stored_experts || which < 0 || which > 3)
         return fail(GARNET_B200_INVALID_VALUE, "moe_dequant: bad argument");
     if (which >= 2) return h->dequant_block_scaled(which - 2, stored_expert, d_out, static_cast<cudaStream_t>(stream));
+    if (!h->packed_up) return fail(GARNET_B200_NOT_SUPPORTED, "moe_dequant: this handle does not hold the streaming layout");
     const PackGeom& geo = which == 0 ? h->geo_up : h->geo_down;
     const size_t total = size_t(geo.rows) * geo.cols / 2;
     mx_dequant_kernel<<<unsigned((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(

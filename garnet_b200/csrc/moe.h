@@ -56,12 +56,20 @@ struct MoeMxPlan {
     size_t q_bytes, sf_bytes;
 };
 MoeMxPlan moe_mx_plan(const garnet_b200_moe_options& o, int tokens, int slots);
-bool moe_mx_enabled();
-bool moe_mx_forced();
+// Which expert kernels an operator with these options uses: 0 = the streaming kernels at
+// every size, 2 = the block-scaled tensor-core kernels at every size, 1 = by rows per expert.
+int moe_mx_mode_of(const garnet_b200_moe_options& o);
+// Checks caller options (either version of the struct) and writes the operator's own
+// view of them: later fields zero-filled, `intermediate` = this rank's share of it.
+int moe_resolve_options(const garnet_b200_moe_options* in, garnet_b200_moe_options* eff);
 size_t moe_route_partial_bytes(int tokens, int experts);
 
 struct Moe {
-    garnet_b200_moe_options opt{};
+    garnet_b200_moe_options opt{};     // resolved: `intermediate` is this rank's share
+    int mx_mode = 1;                   // moe_mx_mode_of(opt)
+    bool owns_packed = true;           // false: the packed blobs are the caller's (create_prepacked)
+    float* own_up_bias = nullptr;      // rank-local gate/up bias gathered at create time (intermediate-axis split)
+    float* zero_down_bias = nullptr;   // down bias of the ranks that do not add it
     PackGeom geo_up{}, geo_down{};
     int stored_experts = 0;            // experts whose packed weights this handle holds
     uint8_t* packed_up = nullptr;      // [stored_experts][geo_up.matrix_bytes()]
@@ -96,12 +104,15 @@ struct Moe {
     MoeShard shard() const;
     int local_experts() const;
     int prepare(const void* const* weights, cudaStream_t stream);
+    int prepare_prepacked(const void* const* small, const void* const* packed, cudaStream_t stream);
+    int setup_common(cudaStream_t stream);
+    int finish_prepare(cudaStream_t stream);
+    bool partial_output() const { return shard().world > 1 || opt.tp_world > 1; }
     int route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
               cudaStream_t stream, bool skip_topk = false, float* route_partial = nullptr, int* counts = nullptr);
     int launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream, int topk = -1);
     int run_rows(const void* x_rows, const int* row_expert, int rows, float* vals, void* ws, size_t ws_bytes,
                  cudaStream_t stream, int stage = 0, float* hidden_io = nullptr);
-    int init_mx(int pass, const uint8_t* blocks, const uint8_t* scales, int first_stored, int count, cudaStream_t stream);
     int finish_mx();
     int init_mxr(int pass, const uint8_t* blocks, const uint8_t* scales, int first_stored, int count, cudaStream_t stream);
     int finish_mxr();
@@ -113,7 +124,12 @@ struct Moe {
     // The block-scaled path pays off once experts get several rows each (measured
     // crossover on the gpt-oss-120b layer: about 6 rows per expert); below that the
     // streaming kernel moves the weights faster.
-    bool use_mx(int slots) const { return mx_ok && moe_mx_enabled() && (moe_mx_forced() || slots > 6 * local_experts()); }
+    // A handle that holds one layout only runs every size on it.
+    bool use_mx(int slots) const
+    {
+        if (!mx_ok || !mxr_w[0]) return false;
+        return mx_mode == 2 || !packed_up || (mx_mode == 1 && slots > 6 * local_experts());
+    }
     int init_route_mma(cudaStream_t stream);
     int route_mma(const void* x, float* logits, float* partial, int tokens, cudaStream_t stream);
     int combine(const float* vals, const float* probs, void* y, int tokens, cudaStream_t stream);

@@ -213,8 +213,12 @@ static int moe_mx_mode()
     }();
     return mode;
 }
-bool moe_mx_enabled() { return moe_mx_mode() != 0; }
-bool moe_mx_forced() { return moe_mx_mode() == 2; }
+int moe_mx_mode_of(const garnet_b200_moe_options& o)
+{
+    if (o.layouts == GARNET_B200_MOE_LAYOUT_STREAM) return 0;
+    if (o.layouts == GARNET_B200_MOE_LAYOUT_BLOCK) return 2;
+    return moe_mx_mode();
+}
 
 MoeMxPlan moe_mx_plan(const garnet_b200_moe_options& o, int tokens, int slots)
 {
@@ -245,15 +249,6 @@ int mx_encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank
 
 // Second copy of the expert weights in the block-scaled path's layout.  `blocks` and
 // `scales` are the tensors of the stored experts, in stored order.
-int Moe::init_mx(int pass, const uint8_t* blocks, const uint8_t* scales, int first_stored, int count, cudaStream_t stream)
-{
-    const PackGeom& geo = pass == 0 ? geo_up : geo_down;
-    const int kp = (geo.cols + kMxSlab - 1) / kMxSlab * kMxSlab;
-    mx_kp[pass] = kp;
-    mx_kslabs[pass] = kp / kMxSlab;
-    return init_mxr(pass, blocks, scales, first_stored, count, stream);
-}
-
 int Moe::finish_mx()
 {
     mx_ok = false;

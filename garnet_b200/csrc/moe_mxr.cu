@@ -29,16 +29,17 @@
 
 #include "layout.h"
 #include "moe.h"
+#include "moe_pack.h"
 #include "mx_common.cuh"
 
 namespace gb200 {
 
 constexpr int kRxRows = 128;          // routed rows per tile (UMMA M)
-constexpr int kRxN = 240;             // weight rows per tile (UMMA N)
+constexpr int kRxN = kMxBlockRows;    // weight rows per tile (UMMA N): 240
 constexpr int kRxEpiWarps = 8;
 constexpr int kRxFirstEpi = 3;                          // warp 0: producer, warp 1: MMA issuer, warp 2: spare
 constexpr int kRxThreads = (kRxFirstEpi + kRxEpiWarps) * 32;
-constexpr int kRxPkBytes = kRxN * kMxSlab / 2;          // 15360: packed weight block of a stage
+constexpr int kRxPkBytes = kMxBlockBytes;               // 15360: packed weight block of a stage
 constexpr int kRxPrefetch = 8;                          // weight blocks requested into L2 ahead of the ring
 constexpr int kRxMaxExperts = 1024;                     // tile prefix kept in shared memory
 constexpr int kRxATile = kRxRows * 128;                 // one e4m3 piece of a stage
@@ -342,43 +343,30 @@ moe_mxr_kernel(const RxParams p, const __grid_constant__ CUtensorMap w_map, cons
 // ------------------------------------------------------------ create-time kernels
 
 // Weight blocks: dst[e][ntile][kslab][240 rows][64 bytes]; rows and columns beyond the
-// matrix hold zero codes.
-__global__ void mxr_tile_weights_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int experts, int rows,
-                                        int k, int ntiles, int kslabs)
+// matrix hold zero codes (moe_pack.h says where each 16-byte piece comes from).
+__global__ void mxr_tile_weights_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int experts, MxBlockGeom g)
 {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one 16-byte piece of the output
-    const long long total = (long long)experts * ntiles * kslabs * (kRxPkBytes / 16);
-    if (idx >= total) return;
-    const int piece = int(idx % 4);
-    const int r = int((idx / 4) % kRxN);
-    const long long tile = idx / (4 * kRxN);
-    const int ks = int(tile % kslabs);
-    const int nt = int((tile / kslabs) % ntiles);
-    const int e = int(tile / ((long long)kslabs * ntiles));
-    const int row = nt * kRxN + r, col = ks * kMxSlab + piece * 32;
+    const size_t per_expert = g.code_bytes() / 16;
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;   // one 16-byte piece of the output
+    if (idx >= per_expert * experts) return;
+    const size_t e = idx / per_expert;
+    size_t sb;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < rows && col < k) v = *reinterpret_cast<const uint4*>(src + (size_t(e) * rows + row) * (k / 2) + col / 2);
+    if (mx_block_piece(g, idx % per_expert, &sb))
+        v = *reinterpret_cast<const uint4*>(src + e * g.rows * size_t(g.k / 2) + sb);
     *reinterpret_cast<uint4*>(dst + idx * 16) = v;
 }
 
-// Weight scale atoms: dst[e][ntile][kslab][2][512]; atom a covers rows 128 a .. of the
-// tile; byte (r % 32) * 16 + (r / 32) * 4 + kb; rows and blocks beyond the matrix get 127.
-__global__ void mxr_weight_atoms_kernel(const uint8_t* __restrict__ scales, uint8_t* __restrict__ dst, int experts, int rows,
-                                        int blocks, int ntiles, int kslabs)
+// Weight scale atoms: dst[e][ntile][kslab][2][512]; rows and groups beyond the matrix get 127.
+__global__ void mxr_weight_atoms_kernel(const uint8_t* __restrict__ scales, uint8_t* __restrict__ dst, int experts, MxBlockGeom g)
 {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long total = (long long)experts * ntiles * kslabs * (2 * kMxAtom);
-    if (idx >= total) return;
-    const int byte = int(idx % kMxAtom);
-    const int atom = int((idx / kMxAtom) % 2);
-    const long long tile = idx / (2 * kMxAtom);
-    const int ks = int(tile % kslabs);
-    const int nt = int((tile / kslabs) % ntiles);
-    const int e = int(tile / ((long long)kslabs * ntiles));
-    const int r = atom * 128 + (byte >> 4) + 32 * ((byte >> 2) & 3), kb = byte & 3;
-    const int row = nt * kRxN + r, blk = ks * 4 + kb;
+    const size_t per_expert = g.atom_bytes();
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= per_expert * experts) return;
+    const size_t e = idx / per_expert;
+    size_t sb;
     uint8_t v = 127;
-    if (r < kRxN && row < rows && blk < blocks) v = scales[(size_t(e) * rows + row) * blocks + blk];
+    if (mx_block_atom(g, idx % per_expert, &sb)) v = scales[e * g.rows * size_t(g.k / 32) + sb];
     dst[idx] = v;
 }
 
@@ -423,20 +411,19 @@ int Moe::dequant_block_scaled(int pass, int stored_expert, float* out, cudaStrea
 int Moe::init_mxr(int pass, const uint8_t* blocks, const uint8_t* scales, int first_stored, int count, cudaStream_t stream)
 {
     const PackGeom& geo = pass == 0 ? geo_up : geo_down;
-    const int k = geo.cols, rows = geo.rows;
-    const int kp = (k + kMxSlab - 1) / kMxSlab * kMxSlab;
-    const int ntiles = (rows + kRxN - 1) / kRxN, kslabs = kp / kMxSlab;
+    const MxBlockGeom g = make_block_geom(geo.rows, geo.cols);
     if (!mxr_w[pass]) {
-        GB_CUDA(cudaMalloc(&mxr_w[pass], size_t(stored_experts) * ntiles * kslabs * kRxPkBytes));
-        GB_CUDA(cudaMalloc(&mxr_sf[pass], size_t(stored_experts) * ntiles * kslabs * 2 * kMxAtom));
-        mxr_ntiles[pass] = ntiles;
+        // one allocation: all blocks, then all scale atoms (the form garnet_b200_moe_pack_host writes)
+        GB_CUDA(cudaMalloc(&mxr_w[pass], size_t(stored_experts) * (g.code_bytes() + g.atom_bytes())));
+        mxr_sf[pass] = mxr_w[pass] + size_t(stored_experts) * g.code_bytes();
+        mxr_ntiles[pass] = g.ntiles;
     }
-    const long long pieces = (long long)count * ntiles * kslabs * (kRxPkBytes / 16);
+    const size_t pieces = size_t(count) * (g.code_bytes() / 16);
     mxr_tile_weights_kernel<<<unsigned((pieces + 255) / 256), 256, 0, stream>>>(
-        blocks, mxr_w[pass] + size_t(first_stored) * ntiles * kslabs * kRxPkBytes, count, rows, k, ntiles, kslabs);
-    const long long bytes = (long long)count * ntiles * kslabs * 2 * kMxAtom;
+        blocks, mxr_w[pass] + size_t(first_stored) * g.code_bytes(), count, g);
+    const size_t bytes = size_t(count) * g.atom_bytes();
     mxr_weight_atoms_kernel<<<unsigned((bytes + 255) / 256), 256, 0, stream>>>(
-        scales, mxr_sf[pass] + size_t(first_stored) * ntiles * kslabs * 2 * kMxAtom, count, rows, k / 32, ntiles, kslabs);
+        scales, mxr_sf[pass] + size_t(first_stored) * g.atom_bytes(), count, g);
     GB_CUDA(cudaGetLastError());
     return GARNET_B200_OK;
 }

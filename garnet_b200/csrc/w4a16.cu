@@ -24,7 +24,7 @@ namespace gb200 {
 
 // One thread per packed 32-bit word (8 codes of one row).
 __global__ void w4_repack_codes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, PackGeom geo,
-                                       long long src_row0)
+                                       long long src_row0, int src_cols, int src_col0)
 {
     const size_t words_per_chunk = geo.chunk_data / 4;
     const size_t total = size_t(geo.strips_padded) * geo.chunks * words_per_chunk;
@@ -41,7 +41,7 @@ __global__ void w4_repack_codes_kernel(const uint8_t* __restrict__ src, uint8_t*
     uint32_t out = 0;
     if (n < geo.rows && k0 < geo.cols) {
         // K is a multiple of 8, so the 8 codes are 4 aligned source bytes.
-        const size_t sb = ((size_t(src_row0) + n) * size_t(geo.cols) + k0) / 2;
+        const size_t sb = ((size_t(src_row0) + n) * size_t(src_cols) + size_t(src_col0) + k0) / 2;
         const uint32_t in = *reinterpret_cast<const uint32_t*>(src + sb);
         if (geo.format == kFormatInt4) {
 #pragma unroll
@@ -58,7 +58,7 @@ __global__ void w4_repack_codes_kernel(const uint8_t* __restrict__ src, uint8_t*
 // they are (fp16 or bf16); the kernels widen them to fp32 according to the
 // handle's scale_dtype.
 __global__ void w4_repack_scales_int4_kernel(const uint16_t* __restrict__ src, uint8_t* __restrict__ dst,
-                                             PackGeom geo, long long src_row0)
+                                             PackGeom geo, long long src_row0, int src_cols, int src_col0)
 {
     const size_t total = size_t(geo.strips_padded) * 16 * geo.chunks;
     const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -66,8 +66,8 @@ __global__ void w4_repack_scales_int4_kernel(const uint16_t* __restrict__ src, u
     const int n = int(idx / geo.chunks), chunk = int(idx % geo.chunks);
     uint16_t bits = 0;
     if (n < geo.rows) {
-        const int groups = geo.cols / geo.group;
-        bits = src[(size_t(src_row0) + n) * groups + (chunk * geo.chunk_k) / geo.group];
+        const int groups = src_cols / geo.group;
+        bits = src[(size_t(src_row0) + n) * groups + (src_col0 + chunk * geo.chunk_k) / geo.group];
     }
     *reinterpret_cast<uint16_t*>(dst + locate_scale(geo, n, chunk * geo.chunk_k)) = bits;
 }
@@ -229,13 +229,15 @@ static int validate_shape(int n, int k, int group)
     return GARNET_B200_OK;
 }
 
+// Rows [row0, row0 + geo.rows) and columns [col0, col0 + geo.cols) of a canonical [*, src_cols] matrix.
 int w4a16_repack_device(const uint8_t* d_nibbles, const uint16_t* d_scales, const PackGeom& geo, long long row0,
-                        uint8_t* d_packed, cudaStream_t stream)
+                        uint8_t* d_packed, cudaStream_t stream, int src_cols, int col0)
 {
+    if (src_cols <= 0) src_cols = geo.cols;
     const size_t words = size_t(geo.strips_padded) * geo.chunks * (geo.chunk_data / 4);
-    w4_repack_codes_kernel<<<unsigned((words + 255) / 256), 256, 0, stream>>>(d_nibbles, d_packed, geo, row0);
+    w4_repack_codes_kernel<<<unsigned((words + 255) / 256), 256, 0, stream>>>(d_nibbles, d_packed, geo, row0, src_cols, col0);
     const size_t sc = size_t(geo.strips_padded) * 16 * geo.chunks;
-    w4_repack_scales_int4_kernel<<<unsigned((sc + 255) / 256), 256, 0, stream>>>(d_scales, d_packed, geo, row0);
+    w4_repack_scales_int4_kernel<<<unsigned((sc + 255) / 256), 256, 0, stream>>>(d_scales, d_packed, geo, row0, src_cols, col0);
     GB_CUDA(cudaGetLastError());
     return GARNET_B200_OK;
 }
@@ -372,9 +374,10 @@ int garnet_b200_w4a16_pack_host(const uint8_t* nibbles, const uint16_t* scales, 
     return GARNET_B200_OK;
 }
 
-int garnet_b200_w4a16_create(const uint8_t* d_nibbles, const void* d_scales, int scale_dtype, int n, int k,
-                             int group, int shard_rank, int shard_world, void* stream,
-                             garnet_b200_w4a16_t* out)
+// shard_axis 0: rows [rank n / world, ...) (N-sharded, "vocab" / "qkv"); 1: columns
+// [rank k / world, ...) (K-sharded, "row").
+static int create_sharded(const uint8_t* d_nibbles, const void* d_scales, int scale_dtype, int n, int k, int group,
+                          int shard_axis, int shard_rank, int shard_world, void* stream, garnet_b200_w4a16_t* out)
 {
     if (!out) return fail(GARNET_B200_INVALID_VALUE, "w4a16_create: null output handle");
     *out = nullptr;
@@ -383,12 +386,18 @@ int garnet_b200_w4a16_create(const uint8_t* d_nibbles, const void* d_scales, int
     if (scale_dtype != GARNET_B200_FP16 && scale_dtype != GARNET_B200_BF16)
         return fail(GARNET_B200_INVALID_VALUE, "w4a16_create: scale dtype must be fp16 or bf16");
     if (shard_world < 1) shard_world = 1;
-    if (shard_rank < 0 || shard_rank >= shard_world || n % shard_world)
+    if (shard_rank < 0 || shard_rank >= shard_world)
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_create: bad shard %d of %d", shard_rank, shard_world);
+    if (shard_axis == 0 && n % shard_world)
         return fail(GARNET_B200_INVALID_VALUE, "w4a16_create: bad shard %d of %d for n=%d", shard_rank, shard_world, n);
-    const int n_local = n / shard_world;
+    if (shard_axis == 1 && k % (shard_world * group))
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_create: k=%d does not split into %d parts of whole groups of %d", k,
+                    shard_world, group);
+    const int n_local = shard_axis == 0 ? n / shard_world : n;
+    const int k_local = shard_axis == 1 ? k / shard_world : k;
     W4A16* h = new (std::nothrow) W4A16();
     if (!h) return fail(GARNET_B200_OUT_OF_MEMORY, "w4a16_create: host allocation failed");
-    h->geo = make_geom(kFormatInt4, n_local, k, group);
+    h->geo = make_geom(kFormatInt4, n_local, k_local, group);
     h->scale_dtype = scale_dtype;
     h->owns_packed = true;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -400,7 +409,8 @@ int garnet_b200_w4a16_create(const uint8_t* d_nibbles, const void* d_scales, int
             break;
         }
         if ((rc = w4a16_repack_device(d_nibbles, static_cast<const uint16_t*>(d_scales), h->geo,
-                                      (long long)shard_rank * n_local, h->packed, s)))
+                                      shard_axis == 0 ? (long long)shard_rank * n_local : 0, h->packed, s, k,
+                                      shard_axis == 1 ? shard_rank * k_local : 0)))
             break;
         if ((rc = h->init_common())) break;
         if (cudaStreamSynchronize(s) != cudaSuccess) {
@@ -414,6 +424,20 @@ int garnet_b200_w4a16_create(const uint8_t* d_nibbles, const void* d_scales, int
     }
     *out = reinterpret_cast<garnet_b200_w4a16_t>(h);
     return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_create(const uint8_t* d_nibbles, const void* d_scales, int scale_dtype, int n, int k,
+                             int group, int shard_rank, int shard_world, void* stream,
+                             garnet_b200_w4a16_t* out)
+{
+    return create_sharded(d_nibbles, d_scales, scale_dtype, n, k, group, 0, shard_rank, shard_world, stream, out);
+}
+
+int garnet_b200_w4a16_create_k_shard(const uint8_t* d_nibbles, const void* d_scales, int scale_dtype, int n, int k,
+                                     int group, int shard_rank, int shard_world, void* stream,
+                                     garnet_b200_w4a16_t* out)
+{
+    return create_sharded(d_nibbles, d_scales, scale_dtype, n, k, group, 1, shard_rank, shard_world, stream, out);
 }
 
 int garnet_b200_w4a16_create_prepacked(const uint8_t* d_packed, int scale_dtype, int n, int k, int group,

@@ -48,6 +48,6 @@ struct TcPlan {
 TcPlan tc_plan(const PackGeom& geo, int m);
 
 int w4a16_repack_device(const uint8_t* d_nibbles, const uint16_t* d_scales, const PackGeom& geo, long long row0,
-                        uint8_t* d_packed, cudaStream_t stream);
+                        uint8_t* d_packed, cudaStream_t stream, int src_cols = 0, int col0 = 0);
 
 }  // namespace gb200

@@ -86,6 +86,12 @@ class Channel:
         return dst
 
 
+    def all_reduce_bf16(self, src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+        """dst = bf16(sum over ranks of src), bf16 tensors; for two ranks exactly bf16(a + b)."""
+        check(lib().garnet_b200_comm_all_reduce_bf16(self._h, src.data_ptr(), dst.data_ptr(), src.numel(), _stream_ptr()))
+        return dst
+
+
 def ep_arena_bytes(moe, world: int, tokens_local_max: int) -> int:
     out = ctypes.c_size_t(0)
     check(lib().garnet_b200_moe_ep_arena_bytes(ctypes.byref(moe.opt), world, tokens_local_max, ctypes.byref(out)))

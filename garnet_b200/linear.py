@@ -146,15 +146,20 @@ class W4A16Linear:
 
     # Q4Q8Linear::Prepare (q4q8_linear.cpp:227-283)
     def prepare(self, nibbles: torch.Tensor, scales: torch.Tensor, n: int, k: int, group: int = 128,
-                shard_rank: int = 0, shard_world: int = 1) -> "W4A16Linear":
+                shard_rank: int = 0, shard_world: int = 1, shard_axis: int = 0) -> "W4A16Linear":
+        """shard_axis 0 splits the rows (N: tp_mode "vocab" / "qkv"), 1 the columns (K: tp_mode "row",
+        whose partial sums are then added over the ranks)."""
         self.close()
         if not nibbles.is_cuda or not scales.is_cuda:
             raise ValueError("prepare needs device-resident canonical weights")
         nb, sc = nibbles.contiguous(), scales.contiguous()
         h = ctypes.c_void_p(None)
-        check(lib().garnet_b200_w4a16_create(nb.data_ptr(), sc.data_ptr(), _SCALE_KIND[sc.dtype], n, k, group,
-                                             shard_rank, shard_world, _stream_ptr(), ctypes.byref(h)))
-        self._h, self.n, self.k, self.group = h, n // shard_world, k, group
+        create = lib().garnet_b200_w4a16_create if shard_axis == 0 else lib().garnet_b200_w4a16_create_k_shard
+        check(create(nb.data_ptr(), sc.data_ptr(), _SCALE_KIND[sc.dtype], n, k, group, shard_rank, shard_world,
+                     _stream_ptr(), ctypes.byref(h)))
+        self._h, self.group = h, group
+        self.n = n // shard_world if shard_axis == 0 else n
+        self.k = k // shard_world if shard_axis == 1 else k
         return self
 
     # Q4Q8Linear::BindPackedView (q4q8_linear.cpp:285-313): borrows packed bytes

@@ -109,6 +109,16 @@ int garnet_b200_w4a16_create(const uint8_t* d_nibbles, const void* d_scales, int
                              int group, int shard_rank, int shard_world, void* stream,
                              garnet_b200_w4a16_t* out);
 
+/* The same with the split along K: the handle keeps columns [rank*K/world, (rank+1)*K/world)
+ * of every row (K/world a multiple of `group`), `run` takes x[m, K/world] - this rank's
+ * columns of the activations - and returns the rank's partial sums y[m, N] in bf16, to be
+ * added over the ranks (garnet_b200_comm_all_reduce_bf16).  The reference's row-parallel
+ * projections (tp_mode "row": the weight sliced along axis 1,
+ * src/backends/tensorrt/trt_builder.cpp:7347-7359, followed by GptOssTpAllReduceBf16). */
+int garnet_b200_w4a16_create_k_shard(const uint8_t* d_nibbles, const void* d_scales, int scale_dtype, int n, int k,
+                                     int group, int shard_rank, int shard_world, void* stream,
+                                     garnet_b200_w4a16_t* out);
+
 /* Creates the operator over already packed device bytes, which are borrowed, not
  * copied (Q4Q8Linear::BindPackedView, q4q8_linear.cpp:285-313). */
 int garnet_b200_w4a16_create_prepacked(const uint8_t* d_packed, int scale_dtype, int n, int k, int group,
@@ -234,7 +244,25 @@ typedef struct garnet_b200_moe_options {
     int expert_weights_sharded; /* expert tensors (and biases) hold only this rank's experts */
     int io_dtype;               /* GARNET_B200_FP32 (reference carrier: fp32 holding bf16 values) or GARNET_B200_BF16 */
     float limit;                /* swiglu clamp, 7 for gpt-oss */
+    /* Fields below were added after the first version of the struct: a caller that
+     * passes the earlier struct_size (up to and including `limit`) gets zeros here. */
+    int layouts;                /* which packed copies of the experts the handle holds:
+                                   0 both (any token count at full speed), GARNET_B200_MOE_LAYOUT_STREAM
+                                   (decode: few rows per expert), GARNET_B200_MOE_LAYOUT_BLOCK
+                                   (prefill: block-scaled tensor-core tiles).  With one copy the
+                                   handle holds the experts once and every token count runs on it. */
+    int tp_rank;                /* intermediate-axis split (the reference's "inner" 2-way tensor */
+    int tp_world;               /* parallelism, gpt_oss_weight_shard.h:9-11): rank r computes
+                                   intermediate channels [r I/world, (r+1) I/world): gate/up row pairs
+                                   and down-projection K groups; the down bias is added on rank 0
+                                   only; the output is this rank's unrounded partial sum, to be
+                                   all-reduced.  0 or 1 = not split.  `intermediate` is always the
+                                   full width. */
+    int tp_weights_sharded;     /* the expert tensors and the gate/up bias already hold only this
+                                   rank's part (GatherGptOssIntermediateShard modes 1 and 2) */
 } garnet_b200_moe_options;
+
+enum { GARNET_B200_MOE_LAYOUT_BOTH = 0, GARNET_B200_MOE_LAYOUT_STREAM = 1, GARNET_B200_MOE_LAYOUT_BLOCK = 2 };
 
 typedef struct garnet_b200_moe* garnet_b200_moe_t;
 
@@ -248,10 +276,11 @@ int garnet_b200_moe_workspace(const garnet_b200_moe_options* options, int tokens
  * gate_up blocks u8 [E,2I,H/32,16], gate_up scales u8 [E,2I,H/32], gate_up bias
  * [E,2I] f32, down blocks [E,H,I/32,16], down scales [E,H,I/32], down bias [E,H]
  * f32.  Expert blocks and scales are repacked into handle-owned memory (one
- * stream synchronise), once in the layout of the streaming kernels (few rows per
- * expert) and once as the blocks and scale atoms of the block-scaled tensor-core
- * kernels (many rows per expert), so a handle holds about twice the size of the
- * expert tensors; router weights and biases are borrowed and must outlive the
+ * stream synchronise): in the layout of the streaming kernels (few rows per
+ * expert) and as the blocks and scale atoms of the block-scaled tensor-core
+ * kernels (many rows per expert) - both when options->layouts is 0, so that a
+ * handle then holds about twice the size of the expert tensors, or only the one
+ * that options->layouts names; router weights and biases are borrowed and must outlive the
  * handle (the router weight is also kept as three bf16 terms for the tensor-core
  * router).  GptOssMarlin constructor + first-run prepare
  * (plugins/gpt_oss/cuda/gpt_oss_marlin.cu:415-499). */
@@ -356,6 +385,51 @@ int garnet_b200_mxfp4_decode(const uint8_t* d_blocks, const uint8_t* d_scales, f
  * (cf. the reference's packed-weight check, test2026/gpt_oss/marlin_weight_pack.cpp:54-78). */
 int garnet_b200_moe_dequant(garnet_b200_moe_t h, int which, int stored_expert, float* d_out, void* stream);
 
+/* ---- packed expert constants (host packer, borrowed prepacked form) ---------
+ * The reference lets an engine hold the experts as derived constants that were packed
+ * on the host, and hands them to the operator with marlinPrepacked = true
+ * (PackGptOssMarlinWeight, plugins/gpt_oss/include/gpt_oss_marlin_pack.h:74-193;
+ * gpt_oss_kernels.h:18; the test that host and device bytes agree:
+ * test2026/gpt_oss/marlin_weight_pack.cpp:33-111, kernel_parity.cpp:576-586).
+ *
+ * A packed blob holds one projection (`which` = 0 gate_up, 1 down) of `experts`
+ * experts in one layout: GARNET_B200_MOE_LAYOUT_STREAM = strips of 16 rows in 544-byte
+ * chunks (codes + scale bytes), GARNET_B200_MOE_LAYOUT_BLOCK = 15 KiB blocks of 240 rows
+ * x 128 columns followed by all their scale atoms.  With tp_world > 1 in `options` the
+ * sizes are those of the rank's part (intermediate / tp_world). */
+int garnet_b200_moe_packed_bytes(const garnet_b200_moe_options* options, int which, int layout, int experts, size_t* bytes);
+
+/* Packs `experts` experts of one projection on the host: blocks [experts, rows, K/32, 16]
+ * and scales [experts, rows, K/32] in the checkpoint layout (rows = 2I and K = H for
+ * gate_up, rows = H and K = I for down; rank-local I when tp_world > 1), into `out`
+ * (garnet_b200_moe_packed_bytes bytes).  Byte for byte what garnet_b200_moe_create
+ * builds on the device.  Uses up to 16 host threads, as the reference's packer does. */
+int garnet_b200_moe_pack_host(const garnet_b200_moe_options* options, int which, int layout, const uint8_t* blocks,
+                              const uint8_t* scales, int experts, uint8_t* out);
+
+/* The handle's own packed blob of a projection in a layout (device pointer and size),
+ * or NOT_SUPPORTED when the handle does not hold that layout. */
+int garnet_b200_moe_packed_view(garnet_b200_moe_t h, int which, int layout, const void** d_blob, size_t* bytes);
+
+/* Creates the operator over packed blobs that the caller owns and keeps alive (device
+ * memory, 256-byte aligned): nothing is repacked and the experts are not copied.
+ * small[0..3] = router W [E,H] f32, router b [E] f32, gate_up bias [E_local, 2 I_local] f32,
+ * down bias [E_local, H] f32; packed[0..3] = gate_up stream, down stream, gate_up block,
+ * down block - those that options->layouts asks for (both pairs when it is 0), each
+ * holding this rank's experts only.  GptOssMarlin with marlinPrepacked
+ * (plugins/gpt_oss/cuda/gpt_oss_marlin.cu:427-433,487-499). */
+int garnet_b200_moe_create_prepacked(const garnet_b200_moe_options* options, const void* const* small,
+                                     const void* const* packed, void* stream, garnet_b200_moe_t* out);
+
+/* Rank-local part of a checkpoint tensor for the intermediate-axis split, on the host:
+ * GatherGptOssIntermediateShard (src/backends/tensorrt/gpt_oss_weight_shard.h:25-60)
+ * for any world size.  mode 1: the rank's slice of axis 1 (gate_up blocks, scales, bias);
+ * mode 2: of axis 2 (down blocks, scales); mode 3: the whole tensor on rank 0, zeros on the
+ * others (down bias).  `shape` has `rank_dims` extents (2..4); `out` takes bytes / world
+ * bytes (modes 1, 2) or bytes (mode 3). */
+int garnet_b200_moe_gather_intermediate_shard(const void* source, size_t bytes, const long long* shape, int rank_dims,
+                                              size_t element_bytes, int rank, int world, int mode, void* out);
+
 /* The activation format of the block-scaled tensor-core path, on its own: every
  * 32-block of a bf16 row [rows, k] becomes two e4m3 rows (d_hi, d_lo: [rows, k] bytes)
  * that share one e8m0 scale byte (d_scales: [rows, k/32]): x = (hi + lo) * 2^(scale-127),
@@ -409,6 +483,12 @@ int garnet_b200_comm_all_gather(garnet_b200_channel_t channel, const void* d_src
  * GptOssTpAllReduceBf16 (tp_collective.cpp:100-122, tp_peer_math.cuh:10-14). */
 int garnet_b200_comm_all_reduce(garnet_b200_channel_t channel, const float* d_src, float* d_dst, size_t count,
                                 int wire_dtype, void* stream);
+
+/* The same sum for bf16 tensors: d_src and d_dst hold `count` bf16 values; the contributions
+ * travel as they are, are added in fp32 in rank order and rounded once - for two ranks
+ * exactly the reference's wire rule bf16(a + b) (plugins/gpt_oss/cuda/tp_peer_math.cuh:10-14).
+ * This is the reduction behind K-sharded ("row"-parallel) linears. */
+int garnet_b200_comm_all_reduce_bf16(garnet_b200_channel_t channel, const void* d_src, void* d_dst, size_t count, void* stream);
 
 /* ---- expert-parallel MoE with the exchange on the device ------------------------------
  * Tokens are split over the ranks, experts live in contiguous blocks of experts/world

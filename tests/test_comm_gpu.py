@@ -44,6 +44,9 @@ def test_single_rank_collectives_and_bounded_wait():
         assert torch.equal(red, x)
         ch.all_reduce(x, red, wire=torch.bfloat16)
         assert torch.equal(red, x.bfloat16().float())
+        xb, rb = x.bfloat16(), torch.zeros(1000, device="cuda", dtype=torch.bfloat16)
+        ch.all_reduce_bf16(xb, rb)
+        assert torch.equal(rb, xb)
     torch.cuda.synchronize()
     assert comm.fault() == 0
     # a flag that nobody writes: the wait gives up after its limit and says so; the context lives on
@@ -108,7 +111,29 @@ def _two_gpu_worker(rank, world, port, results):
             for r in range(1, world):
                 tb = tb + everyone[r].bfloat16().float()
             ok &= torch.equal(red, tb.bfloat16().float())
+            # bf16 in, bf16 out: for two ranks exactly bf16(a + b) (tp_peer_math.cuh:10-14)
+            rb = torch.zeros(50000, device="cuda", dtype=torch.bfloat16)
+            ch.all_reduce_bf16(x.bfloat16(), rb)
+            torch.cuda.synchronize()
+            ok &= torch.equal(rb, tb.bfloat16())
         ok &= comm.fault() == 0
+        # ---- a K-sharded (row-parallel) int4 linear: partial sums added over the ranks by the
+        # library's bf16 all-reduce equal the sum of the ranks' own partial results
+        n, k, m = 512, 1024, 3
+        lc = synth.int4_linear(n, k, m, seed=5)
+        nib = dev(lc["nibbles"])
+        sc = torch.from_numpy(lc["scales_bits"].view(np.int16)).view(torch.bfloat16).reshape(n, k // 128).cuda()
+        xl = torch.from_numpy(lc["x_bits"].view(np.int16)).view(torch.bfloat16).reshape(m, k).cuda()
+        kl = k // world
+        parts = [garnet_b200.W4A16Linear().prepare(nib, sc, n, k, 128, r, world, shard_axis=1).forward(
+            xl[:, r * kl:(r + 1) * kl].contiguous()) for r in range(world)]
+        want = parts[0].float()
+        for r in range(1, world):
+            want = want + parts[r].float()
+        got = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+        ch.all_reduce_bf16(parts[rank], got)
+        torch.cuda.synchronize()
+        ok &= torch.equal(got, want.bfloat16())
         # ---- expert-parallel exchange against the single-GPU operator
         E, K, H, I, T = 8, 4, 96, 64, 48
         case = synth.moe_layer(T * world, H, I, experts=E, topk=K, seed=77, zipf_s=1.1, bias_scale=0.1)

@@ -12,6 +12,7 @@ import pytest
 import torch
 
 import garnet_b200
+from garnet_b200 import moe as moe_mod
 import oracle
 from garnet_b200 import synth
 
@@ -215,6 +216,86 @@ def test_expert_parallel_partials():
     _, sel, pr = oracle.moe_route(wide["x"], wide["router_w"], wide["router_b"], 8, 4)
     o = oracle.moe_experts(wide["x"], sel, pr, *oracle_args(wide), expert_lo=2, expert_hi=4, round_output=False)
     assert_close(parts[1], o, 0.002, "rank-1 partial vs oracle")
+
+
+def test_host_packer_bytes_equal_device_bytes_and_prepacked_handle_is_the_same_operator():
+    """The reference checks that its host packer and its GPU repacker write the same bytes
+    (kernel_parity.cpp:576-586, marlin_weight_pack.cpp:33-111).  Here: both layouts of both
+    projections, then a handle that borrows the host-packed blobs gives bit-identical
+    results, with few rows per expert and with many."""
+    case = synth.moe_layer(96, hidden=160, inter=288, experts=6, topk=2, seed=5, bias_scale=0.1)   # 576 gate/up rows: 3 blocks of 240
+    moe = build(case)
+    blobs = []
+    for layout in (moe_mod.LAYOUT_STREAM, moe_mod.LAYOUT_BLOCK):
+        for which, (bk, sk) in enumerate((("gu_blocks", "gu_scales"), ("dn_blocks", "dn_scales"))):
+            host = moe.pack_host(which, layout, case[bk], case[sk])
+            device = moe.packed_view(which, layout).cpu().numpy()
+            assert host.shape == device.shape and np.array_equal(host, device), (layout, which)
+            blobs.append(dev(host))
+    small = [dev(case[k]) for k in ("router_w", "router_b", "gu_bias", "dn_bias")]
+    pre = garnet_b200.GptOssMoe(case["hidden"], case["inter"], case["experts"], case["topk"]).prepare_prepacked(*small, blobs)
+    for tokens in (3, 96):
+        x = dev(case["x"][:tokens])
+        assert torch.equal(pre.run(x), moe.run(x))
+    assert pre.fault() == 0
+    for which in range(4):
+        assert torch.equal(pre.dequantized(which, 5), moe.dequantized(which, 5))
+
+
+def test_handles_that_hold_one_layout():
+    """layouts = stream / block: one copy of the experts, every token count runs on it."""
+    case = synth.moe_layer(80, hidden=128, inter=256, experts=4, topk=2, seed=6, bias_scale=0.1)
+    for layout, missing in ((moe_mod.LAYOUT_STREAM, moe_mod.LAYOUT_BLOCK), (moe_mod.LAYOUT_BLOCK, moe_mod.LAYOUT_STREAM)):
+        moe = build(case, layouts=layout)
+        with pytest.raises(garnet_b200.GarnetB200Error):
+            moe.packed_view(0, missing)
+        for tokens in (2, 80):
+            sub = dict(case, x=case["x"][:tokens])
+            x = dev(sub["x"])
+            y = moe.run(x).cpu().numpy()
+            _, sel, pr = [t.cpu().numpy() for t in moe.route(x)]
+            expect, mass = oracle.moe_experts(sub["x"], sel, pr, *oracle_args(sub), want_mass=True)
+            # .004: the reference's bound for its tensor-core path (kernel_parity.cpp:714)
+            assert_close(y, expect, 0.004, f"layout {layout}, {tokens} tokens", mass)
+        assert moe.fault() == 0
+    # the prepacked form with one layout takes only that layout's blobs
+    moe = build(case, layouts=moe_mod.LAYOUT_BLOCK)
+    blobs = [None, None] + [moe.packed_view(w, moe_mod.LAYOUT_BLOCK) for w in (0, 1)]
+    small = [dev(case[k]) for k in ("router_w", "router_b", "gu_bias", "dn_bias")]
+    pre = garnet_b200.GptOssMoe(case["hidden"], case["inter"], case["experts"], case["topk"],
+                                layouts=moe_mod.LAYOUT_BLOCK).prepare_prepacked(*small, blobs)
+    x = dev(case["x"])
+    assert torch.equal(pre.run(x), moe.run(x))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_intermediate_axis_split(world):
+    """The reference's inner tensor parallelism (gpt_oss_weight_shard.h:9-11; its test
+    kernel_parity.cpp:674-709, tolerance .025): every rank keeps all experts and
+    1/world of the intermediate channels, adds the down bias on rank 0 only and returns
+    an unrounded partial sum.  A handle given the full tensors and one given the
+    rank-local tensors (gathered on the host) are the same operator."""
+    case = synth.moe_layer(70, hidden=96, inter=256, experts=5, topk=2, seed=9, bias_scale=0.1)
+    x = dev(case["x"])
+    full = build(case)
+    y_full = full.run(x).cpu().numpy()
+    _, sel, pr = [t.cpu().numpy() for t in full.route(x)]
+    expect = oracle.moe_experts(case["x"], sel, pr, *oracle_args(case))
+    for tokens in (2, 70):
+        xs = x[:tokens]
+        parts = []
+        for r in range(world):
+            moe = build(case, tp_rank=r, tp_world=world)
+            parts.append(moe.run(xs).cpu().numpy())
+            local = dict(case)
+            for key, mode in (("gu_blocks", 1), ("gu_scales", 1), ("gu_bias", 1), ("dn_blocks", 2), ("dn_scales", 2), ("dn_bias", 3)):
+                local[key] = moe_mod.gather_intermediate_shard(case[key], r, world, mode)
+            pre = build(local, tp_rank=r, tp_world=world, tp_weights_sharded=True)
+            assert np.array_equal(pre.run(xs).cpu().numpy(), parts[r])
+            assert moe.fault() == 0
+        total = oracle.bf16_round(np.sum(parts, axis=0, dtype=np.float32))
+        assert_close(total, expect[:tokens], 0.025, f"sum of {world} partial sums, {tokens} tokens")
+        assert_close(total, y_full[:tokens], 0.025, "against the unsplit operator")
 
 
 def test_rejects_bad_arguments():

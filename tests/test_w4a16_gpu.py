@@ -350,3 +350,36 @@ def test_bounded_device_wait_reports_a_fault_and_leaves_the_context_usable():
     _, y64 = oracle.w4a16_exact(case["nibbles"], case["scales_f32"], 128, 128, 128, case["x_f32"])
     check_close(y, y64)
     assert lin.fault() == 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("m", [1, 5, 40])
+def test_k_sharded_linear_partial_sums(world, m):
+    """Row-parallel split (the reference slices the weight along axis 1,
+    trt_builder.cpp:7347-7359): every rank holds K / world columns and returns bf16 partial
+    sums; each rank's weights are exactly its columns of the full matrix, and the partial sums,
+    added in fp32 in rank order and rounded once (the wire rule of the all-reduce), meet the
+    exact result within the operator's tolerance plus the roundings of the partial sums."""
+    n, k = 384, 2048
+    case = synth.int4_linear(n, k, m, seed=m + world)
+    full = make_linear(case, n, k)
+    deq = full.dequantized()
+    x = bf16_tensor(case["x_bits"]).reshape(m, k)
+    kl = k // world
+    total = torch.zeros(m, n, device="cuda")
+    for r in range(world):
+        lin = garnet_b200.W4A16Linear().prepare(dev(case["nibbles"]), bf16_tensor(case["scales_bits"]).reshape(n, k // 128),
+                                                n, k, 128, r, world, shard_axis=1)
+        assert torch.equal(lin.dequantized(), deq[:, r * kl:(r + 1) * kl])
+        part = lin.forward(x[:, r * kl:(r + 1) * kl].contiguous())
+        assert lin.fault() == 0 and part.shape == (m, n)
+        total += part.float()
+    y = total.bfloat16()
+    _, y64 = oracle.w4a16_exact(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"])
+    err = np.abs(y.float().cpu().numpy().astype(np.float64) - y64)
+    rms = np.sqrt((y64 ** 2).mean(axis=1, keepdims=True))
+    # every partial sum carries one bf16 rounding of a value of the size of the row's output scale
+    assert (err <= TOL * (1 + np.abs(y64)) + world * 2.0 ** -8 * 4 * rms).all()
+    with pytest.raises(garnet_b200.GarnetB200Error):
+        garnet_b200.W4A16Linear().prepare(dev(case["nibbles"]), bf16_tensor(case["scales_bits"]).reshape(n, k // 128),
+                                          n, k, 128, 0, 3, shard_axis=1)          # 2048 / 3 is not a whole number of groups
