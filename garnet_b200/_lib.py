@@ -58,6 +58,11 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_w4a16_fault.argtypes = [vp]
     L.garnet_b200_w4a16_destroy.argtypes = [vp]
     L.garnet_b200_w4a16_destroy.restype = None
+    L.garnet_b200_w4a16_list_create_ex.argtypes = [vp, i, i, c.POINTER(vp)]
+    L.garnet_b200_attention_decode_workspace.argtypes = [vp, i, c.POINTER(sz)]
+    L.garnet_b200_attention_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i, c.c_uint, vp]
+    L.garnet_b200_embedding_gather.argtypes = [vp, vp, vp, i, i, i, c.c_uint, vp]
+    L.garnet_b200_argmax_bf16.argtypes = [vp, vp, i, i, c.c_uint, vp]
     L.garnet_b200_moe_workspace.argtypes = [vp, i, c.POINTER(sz)]
     L.garnet_b200_moe_create.argtypes = [vp, vp, vp, c.POINTER(vp)]
     L.garnet_b200_moe_run.argtypes = [vp, vp, vp, vp, sz, i, vp]

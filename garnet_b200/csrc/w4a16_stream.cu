@@ -57,6 +57,12 @@ __device__ __forceinline__ uint4 ld_relaxed_gpu_v4(const void* p)
     asm volatile("ld.relaxed.gpu.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ uint2 ld_relaxed_gpu_v2(const void* p)
+{
+    uint2 v;
+    asm volatile("ld.relaxed.gpu.global.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void st_relaxed_gpu_v2(void* p, uint32_t a, uint32_t b)
 {
     asm volatile("st.relaxed.gpu.global.v2.b32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
@@ -67,7 +73,9 @@ struct Ctl {
     volatile int abort_flag;
     int warps_done;   // consumer warps that have finished the list
     int next_slot;    // next slot of the CTA's sequence that no consumer warp has taken yet
+    float row_sq[16]; // sum of squares of every batch row (RMS-normalised inputs)
 };
+static_assert(sizeof(Ctl) <= 128, "the control block has 128 bytes of shared memory");
 
 // Waits on an mbarrier unless the CTA has been told to give up.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ctl* ctl, unsigned long long limit)
@@ -100,6 +108,44 @@ __device__ __forceinline__ void op_share(const StreamOp& op, int& s0, int& s1)
 
 constexpr int kConsumerThreads = kStreamConsumerWarps * 32;
 constexpr int kHalves = kStreamConsumerWarps * 2;   // half-warps that stage activation rows
+
+// The 128 activations of one (batch row, chunk), eight per lane of a half-warp as fp32 bit
+// patterns of bf16 values in `bits` (in the order of the MMA operand bytes), become the two
+// int8 pieces and the scale factor of the group.
+template <int MBLK>
+__device__ __forceinline__ void quantise_group(const uint32_t (&bits)[8], uint32_t hmask, int at0, int at1, int m, int chunk, int hl,
+                                               uint8_t* xb, float* sxb, const StreamSmem& plan)
+{
+    uint32_t amax = 0;
+#pragma unroll
+    for (int el = 0; el < 8; ++el) amax = max(amax, bits[el] & 0x7fffffffu);
+#pragma unroll
+    for (int off = 8; off; off >>= 1) amax = max(amax, __shfl_xor_sync(hmask, amax, off, 16));
+    const int ef = int(amax >> 23);                   // biased exponent of the largest magnitude
+    const int e = max(ef - 126, -100);                // 2^e > max |x|
+    const float up = __uint_as_float(uint32_t(127 + 14 - e) << 23);      // 2^(14-e)
+    float down = __uint_as_float(uint32_t(127 + e - 18) << 23);          // 2^(e-14) / 16: the codes enter the MMA as 16 q
+    if (ef == 255) down = __uint_as_float(0x7fc00000u);                  // inf or NaN in the group: NaN out
+    uint32_t hi_b[2] = {0, 0}, lo_b[2] = {0, 0};
+#pragma unroll
+    for (int el = 0; el < 8; ++el) {
+        const float f = ef == 255 ? 0.f : __uint_as_float(bits[el]);
+        const int V = __float2int_rn(f * up);
+        const int hi = V >> 7, lo = V & 127;
+        hi_b[el >> 2] |= uint32_t(hi & 0xff) << (8 * (el & 3));
+        lo_b[el >> 2] |= uint32_t(lo) << (8 * (el & 3));
+    }
+    uint8_t* row_hi = xb + size_t(2 * m) * plan.xq_stride;
+    uint8_t* row_lo = row_hi + plan.xq_stride;
+    *reinterpret_cast<uint32_t*>(row_hi + at0) = hi_b[0];
+    *reinterpret_cast<uint32_t*>(row_hi + at1) = hi_b[1];
+    *reinterpret_cast<uint32_t*>(row_lo + at0) = lo_b[0];
+    *reinterpret_cast<uint32_t*>(row_lo + at1) = lo_b[1];
+    if (hl == 0) {
+        const int mb = m >> 2, j = m & 3;
+        sxb[(chunk * MBLK + mb) * 4 + j] = down;
+    }
+}
 
 // The consumer threads turn the activation rows of `op` into the int8 pieces, scale
 // factors that the MMAs read.  One half-warp per (batch row, chunk of
@@ -188,44 +234,162 @@ __device__ __forceinline__ bool stage_rows(const StreamParams& p, const StreamOp
                     at0 = chunk * 128 + (oa >> 3) * 64 + (oa & 3) * 16 + ((oa & 7) >> 2) * 8 + gh * 4;
                     at1 = chunk * 128 + (ob >> 3) * 64 + (ob & 3) * 16 + ((ob & 7) >> 2) * 8 + gh * 4;
                 }
-                uint32_t amax = 0;
-#pragma unroll
-                for (int el = 0; el < 8; ++el) amax = max(amax, bits[el] & 0x7fffffffu);
-#pragma unroll
-                for (int off = 8; off; off >>= 1) amax = max(amax, __shfl_xor_sync(hmask, amax, off, 16));
-                const int ef = int(amax >> 23);                   // biased exponent of the largest magnitude
-                const int e = max(ef - 126, -100);                // 2^e > max |x|
-                const float up = __uint_as_float(uint32_t(127 + 14 - e) << 23);      // 2^(14-e)
-                float down = __uint_as_float(uint32_t(127 + e - 18) << 23);          // 2^(e-14) / 16: the codes enter the MMA as 16 q
-                if (ef == 255) down = __uint_as_float(0x7fc00000u);                  // inf or NaN in the group: NaN out
-                uint32_t hi_b[2] = {0, 0}, lo_b[2] = {0, 0};
-#pragma unroll
-                for (int el = 0; el < 8; ++el) {
-                    const float f = ef == 255 ? 0.f : __uint_as_float(bits[el]);
-                    const int V = __float2int_rn(f * up);
-                    const int hi = V >> 7, lo = V & 127;
-                    hi_b[el >> 2] |= uint32_t(hi & 0xff) << (8 * (el & 3));
-                    lo_b[el >> 2] |= uint32_t(lo) << (8 * (el & 3));
-                }
-                uint8_t* row_hi = xb + size_t(2 * m) * plan.xq_stride;
-                uint8_t* row_lo = row_hi + plan.xq_stride;
-                *reinterpret_cast<uint32_t*>(row_hi + at0) = hi_b[0];
-                *reinterpret_cast<uint32_t*>(row_hi + at1) = hi_b[1];
-                *reinterpret_cast<uint32_t*>(row_lo + at0) = lo_b[0];
-                *reinterpret_cast<uint32_t*>(row_lo + at1) = lo_b[1];
-                if (hl == 0) {
-                    const int mb = m >> 2, j = m & 3;
-                    sxb[(chunk * MBLK + mb) * 4 + j] = down;
-                }
+                quantise_group<MBLK>(bits, hmask, at0, at1, m, chunk, hl, xb, sxb, plan);
             }
         }
     }
     return true;
 }
 
+// ---- inputs that are computed on the way in (the glue between the linears of a decoder layer)
+
+// The eight activations a lane holds of item (m, chunk), as fp32, with the columns they
+// belong to.  From memory a lane has eight consecutive columns; from exchange packets it
+// has rows R(4 gh .. 4 gh + 3) of two neighbouring octets (see stage_rows).  `col_shift`
+// moves the source columns (the second half of a [m, 2k] source).  Packets are polled
+// until they carry the run's tag; returns false when that ran out of time.
+__device__ __forceinline__ bool load_lane_values(const StreamParams& p, const StreamOp& op, Ctl* ctl, uint32_t run_tag, uint32_t hmask,
+                                                 int m, int chunk, int hl, int src_cols, int col_shift, float (&v)[8], int (&col)[8])
+{
+    if (!op.xch_in) {
+        const uint4 w = __ldcg(reinterpret_cast<const uint4*>(op.x + size_t(m) * src_cols + col_shift + chunk * 128 + hl * 8));
+        const uint32_t w4[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int el = 0; el < 8; ++el) {
+            const int pos = (el & 3) * 2 + (el >> 2);
+            v[pos] = __uint_as_float((el & 1) ? (w4[el >> 1] & 0xffff0000u) : (w4[el >> 1] << 16));
+            col[pos] = chunk * 128 + hl * 8 + el;
+        }
+        return true;
+    }
+    const int sidx = hl >> 1, gh = hl & 1;
+    const uint2* src = op.xch_in + (size_t(m) * op.in_strips + size_t(col_shift >> 4) + size_t(chunk) * 8 + sidx) * 8 + gh * 4;
+    const unsigned long long t0 = global_timer_ns();
+    uint4 a, b;
+    for (;;) {
+        a = ld_relaxed_gpu_v4(src);
+        b = ld_relaxed_gpu_v4(src + 2);
+        const bool have = a.y == run_tag && a.w == run_tag && b.y == run_tag && b.w == run_tag;
+        if (__all_sync(hmask, have)) break;
+        const bool stop = ctl->abort_flag || global_timer_ns() - t0 > p.wait_limit_ns;
+        if (__any_sync(hmask, stop)) return false;
+    }
+    const uint32_t d[4] = {a.x, a.z, b.x, b.z};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int g = 4 * gh + j;
+        v[j] = __uint_as_float(d[j] << 16);              // row R(g) of the strip
+        v[4 + j] = __uint_as_float(d[j] & 0xffff0000u);  // row R(g) + 8
+        col[j] = chunk * 128 + sidx * 16 + row_of_g(g);
+        col[4 + j] = col[j] + 8;
+    }
+    return true;
+}
+
+// Where a lane's two 4-byte groups go in an activation row (see stage_rows).
+__device__ __forceinline__ void lane_positions(bool from_packets, int chunk, int hl, int& at0, int& at1)
+{
+    if (!from_packets) {
+        const int tile = hl >> 3, o = hl & 7;
+        at0 = chunk * 128 + tile * 64 + (o & 3) * 16 + (o >> 2) * 8;
+        at1 = at0 + 4;
+    } else {
+        const int sidx = hl >> 1, gh = hl & 1;
+        const int oa = 2 * sidx, ob = oa + 1;
+        at0 = chunk * 128 + (oa >> 3) * 64 + (oa & 3) * 16 + ((oa & 7) >> 2) * 8 + gh * 4;
+        at1 = chunk * 128 + (ob >> 3) * 64 + (ob & 3) * 16 + ((ob & 7) >> 2) * 8 + gh * 4;
+    }
+}
+
+__device__ __forceinline__ float bf16_round_dev(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+
+// One item's input values after the op's own activation: plain, or
+// bf16(silu(gate) * up) with gate = source[:, c] and up = source[:, k + c].
+__device__ __forceinline__ bool load_item_values(const StreamParams& p, const StreamOp& op, Ctl* ctl, uint32_t run_tag, uint32_t hmask,
+                                                 int m, int chunk, int hl, float (&v)[8], int (&col)[8])
+{
+    const int k = op.chunks * 128;
+    if (!(op.flags & kOpSwiGLU)) return load_lane_values(p, op, ctl, run_tag, hmask, m, chunk, hl, k, 0, v, col);
+    float up[8];
+    int col_up[8];
+    if (!load_lane_values(p, op, ctl, run_tag, hmask, m, chunk, hl, 2 * k, 0, v, col)) return false;
+    if (!load_lane_values(p, op, ctl, run_tag, hmask, m, chunk, hl, 2 * k, k, up, col_up)) return false;
+#pragma unroll
+    for (int el = 0; el < 8; ++el) {
+        const float g = v[el];
+        const float s = __fdividef(g, 1.f + __expf(-g));
+        v[el] = bf16_round_dev(__fmul_rn(s, up[el]));
+    }
+    return true;
+}
+
+// stage_rows for ops whose input is computed on the way in: an RMS norm over the whole
+// row (x * 1/sqrt(mean(x^2) + eps) * w, rounded to bf16) and/or the SwiGLU product.
+// All consumer threads call it together: the norm needs two CTA-wide meetings.
+template <int MBLK>
+__device__ __forceinline__ bool stage_rows_glue(const StreamParams& p, const StreamOp& op, const StreamSmem& plan, Ctl* ctl,
+                                                uint8_t* xb, float* sxb, uint32_t run_tag, int tid, int lane)
+{
+    const int half = tid >> 4, hl = tid & 15;
+    const uint32_t hmask = 0xffffu << (lane & 16);
+    const int k = op.chunks * 128;
+    const int items = p.m * op.chunks;
+    const bool norm = (op.flags & kOpNorm) != 0, from_packets = op.xch_in != nullptr;
+    const bool single = items <= kHalves;   // every half-warp has at most one item: its values stay in registers
+    bool good = true;
+    float v[8];
+    int col[8];
+    if (norm) {
+        // ---- first pass: the sum of squares of every row, added in a fixed order
+        for (int item = half; item < items; item += kHalves) {
+            const int m = item / op.chunks, chunk = item - m * op.chunks;
+            if (good && !load_item_values(p, op, ctl, run_tag, hmask, m, chunk, hl, v, col)) good = false;
+            float sq = 0.f;
+            if (good) {
+#pragma unroll
+                for (int el = 0; el < 8; ++el) sq = __fmaf_rn(v[el], v[el], sq);
+            }
+#pragma unroll
+            for (int off = 8; off; off >>= 1) sq += __shfl_xor_sync(hmask, sq, off, 16);
+            if (hl == 0) sxb[(chunk * MBLK + (m >> 2)) * 4 + (m & 3)] = sq;   // the group's slot holds its share for now
+        }
+        named_barrier_sync(1, kConsumerThreads);
+        if (half < p.m) {
+            float total = 0.f;
+            for (int c = hl; c < op.chunks; c += 16) total += sxb[(c * MBLK + (half >> 2)) * 4 + (half & 3)];
+#pragma unroll
+            for (int off = 8; off; off >>= 1) total += __shfl_xor_sync(hmask, total, off, 16);
+            if (hl == 0) ctl->row_sq[half] = total;
+        }
+        named_barrier_sync(1, kConsumerThreads);
+    }
+    for (int item = half; item < items; item += kHalves) {
+        const int m = item / op.chunks, chunk = item - m * op.chunks;
+        if (good && !(norm && single) && !load_item_values(p, op, ctl, run_tag, hmask, m, chunk, hl, v, col)) good = false;
+        if (!good) continue;
+        uint32_t bits[8];
+        if (norm) {
+            const float rs = 1.f / sqrtf(ctl->row_sq[m] / float(k) + op.norm_eps);
+#pragma unroll
+            for (int el = 0; el < 8; ++el) {
+                const float w = __bfloat162float(op.norm_w[col[el]]);
+                bits[el] = __float_as_uint(bf16_round_dev(__fmul_rn(__fmul_rn(v[el], rs), w)));
+            }
+        } else {
+#pragma unroll
+            for (int el = 0; el < 8; ++el) bits[el] = __float_as_uint(v[el]);
+        }
+        int at0, at1;
+        lane_positions(from_packets, chunk, hl, at0, at1);
+        quantise_group<MBLK>(bits, hmask, at0, at1, m, chunk, hl, xb, sxb, plan);
+    }
+    return good;
+}
+
 }  // namespace
 
-template <int MBLK>
+// kGlue: the list holds ops with computed inputs or residuals (the plain instantiation carries none of that code).
+template <int MBLK, bool kGlue>
 __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __grid_constant__ StreamParams p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -354,8 +518,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                 // Every warp has finished with the rows this buffer held; then all stage the new
                 // ones.  (A warp that gave up keeps meeting the others at these barriers.)
                 named_barrier_sync(1, kConsumerThreads);
-                if (ok && !ctl->abort_flag &&
-                    !stage_rows<MBLK>(p, op, plan, ctl, xb, const_cast<float*>(sxb), run_tag, threadIdx.x, lane)) {
+                if (kGlue && (op.flags & (kOpNorm | kOpSwiGLU))) {
+                    // every thread takes part (the norm meets twice); one that has given up only keeps the meetings
+                    if (!stage_rows_glue<MBLK>(p, op, plan, ctl, xb, const_cast<float*>(sxb), run_tag, threadIdx.x, lane) &&
+                        (lane & 15) == 0)
+                        give_up(p, ctl, 3);
+                } else if (ok && !ctl->abort_flag &&
+                           !stage_rows<MBLK>(p, op, plan, ctl, xb, const_cast<float*>(sxb), run_tag, threadIdx.x, lane)) {
                     if ((lane & 15) == 0) give_up(p, ctl, 3);
                 }
                 named_barrier_sync(1, kConsumerThreads);
@@ -546,6 +715,21 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                 for (int mb = 0; mb < MBLK; ++mb) {
                     const int m = mb * 4 + t;
                     if (m < p.m) {
+                        if (kGlue && (op.flags & kOpResidual)) {
+                            if (n_lo < op.n) acc[mb][0] = __fadd_rn(acc[mb][0], __bfloat162float(op.res[size_t(m) * op.ldy + n_lo]));
+                            if (n_hi < op.n) acc[mb][1] = __fadd_rn(acc[mb][1], __bfloat162float(op.res[size_t(m) * op.ldy + n_hi]));
+                        } else if (kGlue && (op.flags & kOpResidualXch)) {
+                            // the packet of (m, strip, g) holds exactly this lane's two columns
+                            const uint2* src = op.res_xch + (size_t(m) * op.strips + strip) * 8 + g;
+                            uint2 pk = ld_relaxed_gpu_v2(src);
+                            if (pk.y != run_tag) {
+                                const unsigned long long t0 = global_timer_ns();
+                                while (pk.y != run_tag && !ctl->abort_flag && global_timer_ns() - t0 <= limit) pk = ld_relaxed_gpu_v2(src);
+                                if (pk.y != run_tag) give_up(p, ctl, 5);
+                            }
+                            acc[mb][0] = __fadd_rn(acc[mb][0], __uint_as_float(pk.x << 16));
+                            acc[mb][1] = __fadd_rn(acc[mb][1], __uint_as_float(pk.x & 0xffff0000u));
+                        }
                         const __nv_bfloat16 y_lo = __float2bfloat16_rn(acc[mb][0]), y_hi = __float2bfloat16_rn(acc[mb][1]);
                         if (n_lo < op.n) op.y[size_t(m) * op.ldy + n_lo] = y_lo;
                         if (n_hi < op.n) op.y[size_t(m) * op.ldy + n_hi] = y_hi;
@@ -652,19 +836,27 @@ static int launch_list(StreamParams p, int grid, unsigned flags, cudaStream_t st
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (flags & 1u) ? 1 : 0;
-    switch (stream_mblk(p.m)) {
-        case 1: GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_list_kernel<1>, p)); break;
-        case 2: GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_list_kernel<2>, p)); break;
-        default: GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_list_kernel<4>, p)); break;
+    const int mblk = stream_mblk(p.m);
+    if (p.has_glue) {
+        if (mblk == 1) GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_list_kernel<1, true>, p));
+        else if (mblk == 2) GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_list_kernel<2, true>, p));
+        else GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_list_kernel<4, true>, p));
+    } else {
+        if (mblk == 1) GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_list_kernel<1, false>, p));
+        else if (mblk == 2) GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_list_kernel<2, false>, p));
+        else GB_CUDA(cudaLaunchKernelEx(&cfg, w4a16_list_kernel<4, false>, p));
     }
     return GARNET_B200_OK;
 }
 
 int stream_set_attributes()
 {
-    GB_CUDA(cudaFuncSetAttribute(w4a16_list_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxDynamicSmem)));
-    GB_CUDA(cudaFuncSetAttribute(w4a16_list_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxDynamicSmem)));
-    GB_CUDA(cudaFuncSetAttribute(w4a16_list_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxDynamicSmem)));
+    GB_CUDA(cudaFuncSetAttribute(w4a16_list_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxDynamicSmem)));
+    GB_CUDA(cudaFuncSetAttribute(w4a16_list_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxDynamicSmem)));
+    GB_CUDA(cudaFuncSetAttribute(w4a16_list_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxDynamicSmem)));
+    GB_CUDA(cudaFuncSetAttribute(w4a16_list_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxDynamicSmem)));
+    GB_CUDA(cudaFuncSetAttribute(w4a16_list_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxDynamicSmem)));
+    GB_CUDA(cudaFuncSetAttribute(w4a16_list_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMaxDynamicSmem)));
     return GARNET_B200_OK;
 }
 
@@ -750,38 +942,66 @@ using namespace gb200;
 
 extern "C" {
 
-int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void* const* d_xs, void* const* d_ys,
-                                  const int* deps, int count, int m, garnet_b200_w4a16_list_t* out)
+static int list_create_impl(const garnet_b200_w4a16_list_item* items, int count, int m, garnet_b200_w4a16_list_t* out)
 {
     if (!out) return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: null output");
     *out = nullptr;
-    if (!handles || !d_xs || !d_ys || count <= 0 || m <= 0)
-        return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: bad argument");
+    if (!items || count <= 0 || m <= 0) return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: bad argument");
     std::vector<StreamOp> ops(static_cast<size_t>(count));
+    std::vector<const void*> d_xs(static_cast<size_t>(count));
     int max_chunks = 0, max_strips = 0, l_nbuf = 1;
-    bool has_deps = false;
+    bool has_deps = false, has_glue = false;
     for (int i = 0; i < count; ++i) {
-        const W4A16* h = reinterpret_cast<const W4A16*>(handles[i]);
-        if (!h || !d_xs[i] || !d_ys[i])
+        const garnet_b200_w4a16_list_item& it = items[i];
+        const W4A16* h = reinterpret_cast<const W4A16*>(it.linear);
+        if (!h || !it.d_x || !it.d_y)
             return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: null handle, x or y at index %d", i);
-        if (reinterpret_cast<uintptr_t>(d_xs[i]) & 15)
+        if (reinterpret_cast<uintptr_t>(it.d_x) & 15)
             return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: x of linear %d must be 16-byte aligned", i);
-        const int dep = deps ? deps[i] : -1;
+        const int dep = it.dep;
         if (dep >= i || dep < -1)
             return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: linear %d may only depend on an earlier linear (got %d)", i, dep);
         if (m > stream_max_rows(h->geo.chunks))
             return fail(GARNET_B200_NOT_SUPPORTED, "w4a16_list_create: batch %d is too large for k=%d in a list (at most %d)", m,
                         h->geo.cols, stream_max_rows(h->geo.chunks));
-        ops[i] = make_op(h, static_cast<const __nv_bfloat16*>(d_xs[i]), static_cast<__nv_bfloat16*>(d_ys[i]), h->geo.rows);
+        if (it.activation != 0 && it.activation != 1)
+            return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: activation of linear %d must be 0 or 1", i);
+        if (it.activation && it.d_norm_weight)
+            return fail(GARNET_B200_NOT_SUPPORTED, "w4a16_list_create: linear %d asks for a norm and an activation on the same input", i);
+        d_xs[i] = it.d_x;
+        ops[i] = make_op(h, static_cast<const __nv_bfloat16*>(it.d_x), static_cast<__nv_bfloat16*>(it.d_y), h->geo.rows);
         ops[i].dep = dep;
+        const int in_cols = it.activation ? 2 * h->geo.cols : h->geo.cols;   // columns of the source rows
         if (dep >= 0) {
-            if (d_xs[i] != d_ys[dep] || ops[dep].n != h->geo.cols)
+            if (it.d_x != items[dep].d_y || ops[dep].n != in_cols)
                 return fail(GARNET_B200_INVALID_VALUE,
-                            "w4a16_list_create: linear %d depends on linear %d, so its x must be that linear's y (n=%d, k=%d)", i,
-                            dep, ops[dep].n, h->geo.cols);
+                            "w4a16_list_create: linear %d depends on linear %d, so its x must be that linear's y (n=%d, needs %d)", i,
+                            dep, ops[dep].n, in_cols);
             ops[dep].flags |= kOpSignal;
             has_deps = true;
         }
+        if (it.activation) ops[i].flags |= kOpSwiGLU;
+        if (it.d_norm_weight) {
+            if (!(it.norm_eps > 0.f)) return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: norm_eps of linear %d must be positive", i);
+            ops[i].flags |= kOpNorm;
+            ops[i].norm_w = static_cast<const __nv_bfloat16*>(it.d_norm_weight);
+            ops[i].norm_eps = it.norm_eps;
+        }
+        if (it.d_residual && it.residual_dep >= 0)
+            return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: linear %d names two residuals", i);
+        if (it.d_residual) {
+            ops[i].flags |= kOpResidual;
+            ops[i].res = static_cast<const __nv_bfloat16*>(it.d_residual);
+        } else if (it.residual_dep >= 0) {
+            if (it.residual_dep >= i || ops[it.residual_dep].n != ops[i].n)
+                return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: the residual of linear %d must be an earlier linear with the same n", i);
+            ops[i].flags |= kOpResidualXch;
+            ops[it.residual_dep].flags |= kOpSignal;
+            has_deps = true;
+        } else if (it.residual_dep < -1) {
+            return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: residual_dep of linear %d must be -1 or an earlier index", i);
+        }
+        if (ops[i].flags & (kOpSwiGLU | kOpNorm | kOpResidual | kOpResidualXch)) has_glue = true;
         // (which activation buffer the rows go to, and whether they are already there, is decided below)
         max_chunks = std::max(max_chunks, ops[i].chunks);
         max_strips = std::max(max_strips, ops[i].strips);
@@ -793,19 +1013,22 @@ int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void
     {
         const size_t xq_bytes = size_t(2 * m + 1) * size_t(max_chunks * 128 + 64);
         const int nbuf = 2 * xq_bytes <= 80 * 1024 ? 2 : 1;
-        const void* held[2] = {nullptr, nullptr};
-        int held_chunks[2] = {0, 0}, last_use[2] = {-1, -1};
+        // what a buffer holds: the source rows, their width, and how they were transformed on the way in
+        struct Held { const void* x; int chunks; const void* norm_w; int act; };
+        Held held[2] = {{nullptr, 0, nullptr, 0}, {nullptr, 0, nullptr, 0}};
+        int last_use[2] = {-1, -1};
         for (int i = 0; i < count; ++i) {
             int buf = -1;
+            const Held want = {d_xs[i], ops[i].chunks, ops[i].norm_w, ops[i].flags & kOpSwiGLU};
             if (ops[i].dep < 0 || (i > 0 && ops[i].dep == ops[i - 1].dep && d_xs[i] == d_xs[i - 1]))
                 for (int b = 0; b < nbuf; ++b)
-                    if (held[b] == d_xs[i] && held_chunks[b] == ops[i].chunks) buf = b;
+                    if (held[b].x == want.x && held[b].chunks == want.chunks && held[b].norm_w == want.norm_w && held[b].act == want.act)
+                        buf = b;
             if (buf >= 0) {
                 ops[i].flags |= kOpSameX;
             } else {
                 buf = (nbuf == 2 && last_use[1] < last_use[0]) ? 1 : 0;   // the buffer used longest ago
-                held[buf] = d_xs[i];
-                held_chunks[buf] = ops[i].chunks;
+                held[buf] = want;
             }
             last_use[buf] = i;
             if (buf == 1) ops[i].flags |= kOpBuffer1;
@@ -833,6 +1056,7 @@ int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void
     p.m = m;
     p.max_chunks = max_chunks;
     p.has_deps = has_deps ? 1 : 0;
+    p.has_glue = has_glue ? 1 : 0;
     p.nbuf = l_nbuf;
     p.wait_limit_ns = stream_wait_limit_ns();
     for (int i = 0; i < count; ++i) p.max_parts = std::max(p.max_parts, ops[i].parts);
@@ -861,6 +1085,7 @@ int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void
                 ops[i].xch_in = l->d_exchange + at[ops[i].dep];
                 ops[i].in_strips = ops[ops[i].dep].strips;
             }
+            if (ops[i].flags & kOpResidualXch) ops[i].res_xch = l->d_exchange + at[items[i].residual_dep];
         }
     }
     GB_CUDA(cudaMalloc(&l->d_ops, sizeof(StreamOp) * size_t(count + 2)));   // two entries of slack for the table prefetch
@@ -875,6 +1100,30 @@ int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void
     if (int rc = stream_set_attributes()) return rc;
     *out = reinterpret_cast<garnet_b200_w4a16_list_t>(l.release());
     return GARNET_B200_OK;
+}
+
+int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void* const* d_xs, void* const* d_ys,
+                                  const int* deps, int count, int m, garnet_b200_w4a16_list_t* out)
+{
+    if (!out) return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: null output");
+    *out = nullptr;
+    if (!handles || !d_xs || !d_ys || count <= 0 || m <= 0)
+        return fail(GARNET_B200_INVALID_VALUE, "w4a16_list_create: bad argument");
+    std::vector<garnet_b200_w4a16_list_item> items(static_cast<size_t>(count));
+    for (int i = 0; i < count; ++i) {
+        items[i] = garnet_b200_w4a16_list_item{};
+        items[i].linear = handles[i];
+        items[i].d_x = d_xs[i];
+        items[i].d_y = d_ys[i];
+        items[i].dep = deps ? deps[i] : -1;
+        items[i].residual_dep = -1;
+    }
+    return list_create_impl(items.data(), count, m, out);
+}
+
+int garnet_b200_w4a16_list_create_ex(const garnet_b200_w4a16_list_item* items, int count, int m, garnet_b200_w4a16_list_t* out)
+{
+    return list_create_impl(items, count, m, out);
 }
 
 int garnet_b200_w4a16_list_run(garnet_b200_w4a16_list_t ll, unsigned flags, void* stream)

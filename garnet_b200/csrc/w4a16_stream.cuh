@@ -24,6 +24,10 @@ enum : int {
     kOpSignal = 2,     // a later op reads this one's output: publish it in exchange packets
     kOpScaleFp16 = 4,  // 16-bit scales are fp16 (else bf16)
     kOpBuffer1 = 8,    // its activation rows live in the second buffer
+    kOpNorm = 16,      // the input rows are RMS-normalised (and scaled by norm_w) before they are multiplied
+    kOpSwiGLU = 32,    // the source rows are [m, 2k]: the input is silu(source[:, :k]) * source[:, k:]
+    kOpResidual = 64,  // a bf16 matrix [m, ldy] in memory is added to the output before its rounding
+    kOpResidualXch = 128,   // the same, taken from the exchange packets of an earlier op of the list
 };
 
 // Outputs that a later op of the same list consumes also travel as 8-byte packets
@@ -50,7 +54,13 @@ struct StreamOp {
     // precomputed for the launch grid, so that the consumer warps divide nothing
     int base_strips, rem_strips;  // strips / grid, strips % grid: the first rem_strips CTAs (from first_cta) take one more
     unsigned long long inv_parts; // ceil(2^40 / parts): x / parts = (x * inv_parts) >> 40
+    const __nv_bfloat16* norm_w;  // kOpNorm: weight of the RMS norm, [k]
+    const __nv_bfloat16* res;     // kOpResidual: [m, ldy]
+    const uint2* res_xch;         // kOpResidualXch: packets of an op with the same n
+    float norm_eps;
+    int pad_;
 };
+static_assert(sizeof(StreamOp) % 16 == 0, "the op table is copied in 16-byte pieces");
 
 struct StreamParams {
     const StreamOp* ops;          // device table; nullptr = use inline_ops
@@ -64,6 +74,7 @@ struct StreamParams {
     unsigned long long inv_ring;  // ceil(2^40 / ring_slots): q / ring_slots = (q * inv_ring) >> 40
     unsigned long long inv_pslots; // the same for the partial-sum slots
     int has_deps;
+    int has_glue;                 // some op computes its input on the way in or adds a residual
     int table_in_smem;            // the op table is copied to shared memory at the start (short lists)
     int* epoch;                   // tag of this run's exchange packets; bumped by the last CTA (only with has_deps)
     int* finish;                  // CTAs that finished the list (only with has_deps)

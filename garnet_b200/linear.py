@@ -99,6 +99,37 @@ class LinearList:
             pass
 
 
+class ListItem(ctypes.Structure):
+    """garnet_b200_w4a16_list_item."""
+    _fields_ = [("linear", ctypes.c_void_p), ("d_x", ctypes.c_void_p), ("d_y", ctypes.c_void_p), ("dep", ctypes.c_int),
+                ("activation", ctypes.c_int), ("d_norm_weight", ctypes.c_void_p), ("norm_eps", ctypes.c_float),
+                ("residual_dep", ctypes.c_int), ("d_residual", ctypes.c_void_p)]
+
+
+class GlueList(LinearList):
+    """A list whose linears carry the glue of a decoder layer (garnet_b200_w4a16_list_create_ex).
+    `calls` is a sequence of dicts: linear, x, y, and optionally dep, activation (1 = the input is
+    silu(x[:, :K]) * x[:, K:]), norm_weight with norm_eps, residual (a tensor) or residual_dep."""
+
+    def __init__(self, calls, m: int = 1):
+        self._keep = list(calls)
+        n = len(self._keep)
+        items = (ListItem * n)()
+        for it, c in zip(items, self._keep):
+            it.linear = c["linear"]._h
+            it.d_x, it.d_y = c["x"].data_ptr(), c["y"].data_ptr()
+            it.dep = c.get("dep", -1)
+            it.activation = c.get("activation", 0)
+            nw = c.get("norm_weight")
+            it.d_norm_weight = nw.data_ptr() if nw is not None else None
+            it.norm_eps = c.get("norm_eps", 0.0)
+            it.residual_dep = c.get("residual_dep", -1)
+            res = c.get("residual")
+            it.d_residual = res.data_ptr() if res is not None else None
+        self._l = ctypes.c_void_p(None)
+        check(lib().garnet_b200_w4a16_list_create_ex(items, n, m, ctypes.byref(self._l)))
+
+
 class HostBatch:
     """A prepared list of (linear, host x, host y) calls (garnet_b200_w4a16_batch_*); after
     `run` the outputs are complete once the current stream has been synchronised."""

@@ -168,6 +168,31 @@ int garnet_b200_w4a16_run_group(const garnet_b200_w4a16_t* handles, int count, c
 typedef struct garnet_b200_w4a16_list_s* garnet_b200_w4a16_list_t;
 int garnet_b200_w4a16_list_create(const garnet_b200_w4a16_t* handles, const void* const* d_xs, void* const* d_ys,
                                   const int* deps, int count, int m, garnet_b200_w4a16_list_t* out);
+/* The same list with the glue between the linears of a decoder layer folded into them, so that
+ * a layer's o_proj, gate/up, down and the next layer's q/k/v are one launch (the reference
+ * lowers these as separate TensorRT layers around its linears: RMS norm and packed q/k/v,
+ * src/backends/tensorrt/trt_builder.cpp:7565-7726; packed gate/up with SiLU and multiply,
+ * :7727-7800; the residual additions of the decoder layer):
+ *   d_norm_weight  bf16 [K]: the input rows are first RMS-normalised,
+ *                  x' = bf16(x / sqrt(mean(x^2) + norm_eps) * w);
+ *   activation 1:  the source rows are [m, 2K] (a packed gate/up output) and the input is
+ *                  bf16(silu(source[:, :K]) * source[:, K:]);
+ *   d_residual     bf16 [m, N] in memory, or residual_dep = an earlier item of the list whose
+ *                  output it is: y = bf16(x' W^T + residual), one rounding.
+ * Items are zero-initialised apart from `dep` and `residual_dep`, which are -1 when unused. */
+typedef struct garnet_b200_w4a16_list_item {
+    garnet_b200_w4a16_t linear;
+    const void* d_x;            /* source rows: bf16 [m, K], or [m, 2K] with activation 1 */
+    void* d_y;                  /* bf16 [m, N] */
+    int dep;                    /* -1, or the earlier item whose d_y is this d_x */
+    int activation;             /* 0 or 1 */
+    const void* d_norm_weight;  /* NULL or bf16 [K] */
+    float norm_eps;
+    int residual_dep;           /* -1, or the earlier item whose output is added */
+    const void* d_residual;     /* NULL or bf16 [m, N] */
+} garnet_b200_w4a16_list_item;
+int garnet_b200_w4a16_list_create_ex(const garnet_b200_w4a16_list_item* items, int count, int m,
+                                     garnet_b200_w4a16_list_t* out);
 int garnet_b200_w4a16_list_run(garnet_b200_w4a16_list_t list, unsigned flags, void* stream);
 int garnet_b200_w4a16_list_fault(garnet_b200_w4a16_list_t list);
 void garnet_b200_w4a16_list_destroy(garnet_b200_w4a16_list_t list);
@@ -215,6 +240,52 @@ int garnet_b200_w4a16_dequant(garnet_b200_w4a16_t h, float* d_out, void* stream)
 int garnet_b200_w4a16_fault(garnet_b200_w4a16_t h);
 
 void garnet_b200_w4a16_destroy(garnet_b200_w4a16_t h);
+
+/* ---- the rest of a Qwen3 decode step ------------------------------------------
+ * What sits between the int4 linears of a decoder layer and is not folded into a
+ * garnet_b200_w4a16_list: attention of one new token per sequence over the paged bf16 KV
+ * cache, the embedding row and the greedy token.  The reference runs these as separate
+ * engines and kernels: the packed q/k/v lowering with per-head q/k RMS norm and rotate-half
+ * RoPE (src/backends/tensorrt/trt_builder.cpp:7565-7726, :1815-1870), the cache append and
+ * the split decode attention over page tables (src/cuda/text_kv_attention_kernel.cu:640-840)
+ * and the greedy sampler (src/cuda/logits_sampler_kernel.cu). */
+typedef struct garnet_b200_attention_options {
+    int abi;                /* GARNET_B200_ABI */
+    int struct_size;        /* sizeof(garnet_b200_attention_options) */
+    int q_heads;            /* 16 for Qwen3-1.7B */
+    int kv_heads;           /* 8; q head h reads kv head h / (q_heads / kv_heads) */
+    int head_dim;           /* 128 (the only supported value) */
+    int page_size;          /* positions per cache page (16 in the reference) */
+    int max_logical_pages;  /* columns of the page table */
+    int max_context;        /* largest context a call may see (sizes the grid and the workspace) */
+    int rope_positions;     /* rows of the cos / sin tables */
+    float norm_eps;         /* of the q / k head norms */
+} garnet_b200_attention_options;
+
+/* Workspace bytes for `batch` sequences.  The caller zero-fills the workspace once
+ * (cudaMemset) before the first call; the kernel leaves its counters zero. */
+int garnet_b200_attention_decode_workspace(const garnet_b200_attention_options* options, int batch, size_t* bytes);
+
+/* d_qkv [batch, (q_heads + 2 kv_heads) * 128] bf16: the output row q | k | v of the packed
+ * q/k/v linear.  Per sequence b with slot = d_positions[b] (its context is slots 0 .. slot):
+ *   q_h  = rope(bf16(rmsnorm(q_h) * q_norm_weight), slot) for every q head, k likewise with
+ *          k_norm_weight; rope uses rows `slot` of d_rope_cos / d_rope_sin (fp32 [rope_positions, 64],
+ *          rotate-half: out[d] = x[d] cos[d] - x[d+64] sin[d], out[d+64] = x[d+64] cos[d] + x[d] sin[d]);
+ *   k, v are written to the cache at ((page_table[b][slot / page_size] * page_size + slot % page_size)
+ *          * kv_heads + kv_head) * 128 (the reference's layout, text_kv_attention_kernel.cu:668-673);
+ *   out[b, h*128 ..] = softmax(q_h . K^T / sqrt(128)) V over the context, fp32 arithmetic, bf16 result.
+ * flags bit 0: programmatic dependent launch.  No allocation, no synchronisation. */
+int garnet_b200_attention_decode(const garnet_b200_attention_options* options, const void* d_qkv, const void* d_q_norm_weight,
+                                 const void* d_k_norm_weight, const float* d_rope_cos, const float* d_rope_sin, void* d_key_pages,
+                                 void* d_value_pages, const int* d_page_tables, const int* d_positions, void* d_out,
+                                 void* d_workspace, size_t workspace_bytes, int batch, unsigned flags, void* stream);
+
+/* out[b, :] = table[ids[b], :] (bf16 [vocab, hidden]; ids outside the table are clamped). */
+int garnet_b200_embedding_gather(const void* d_table, const int* d_ids, void* d_out, int batch, int hidden, int vocab,
+                                 unsigned flags, void* stream);
+
+/* out[b] = index of the largest of logits[b, :vocab] (bf16), the lowest index among equals. */
+int garnet_b200_argmax_bf16(const void* d_logits, int* d_out, int batch, int vocab, unsigned flags, void* stream);
 
 /* ---- gpt-oss MXFP4 mixture of experts (`gpt_oss_moe_mxfp4`) -------------------
  * Replaces the free functions below the TensorRT plugin:
