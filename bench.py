@@ -323,6 +323,8 @@ def run_gpu(args):
     if world == 1 and not args.no_sweep:
         del layers, head
         torch.cuda.empty_cache()
+        out["decode_step"] = bench_decode_step(torch, peaks, args)
+        torch.cuda.empty_cache()
         sweep = []
         shapes = [("q_proj/o_proj", 2048, 2048), ("k_proj/v_proj", 2048, 1024), ("gate_proj/up_proj", 2048, 6144),
                   ("down_proj", 6144, 2048), ("lm_head", 2048, 151936)]
@@ -370,6 +372,39 @@ def run_gpu(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def bench_decode_step(torch, peaks, args, context=2048):
+    """BASELINE's config 3 as a real step: one token through the 28 Qwen3-1.7B layers at a context
+    of 2048 positions (embedding, norms, packed q/k/v, head norms + RoPE, paged-KV attention,
+    o_proj, packed gate/up with SiLU, down, residuals, final norm, lm_head, arg-max) as one CUDA
+    graph of 2 launches per layer.  Synthetic weights and a random bf16 KV cache."""
+    from garnet_b200 import decode as dec
+    cfg = dec.DecoderConfig()
+    w = dec.synthetic_decoder(cfg, seed=7)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(11)
+    pages = context // cfg.page_size
+    kps = [torch.randn(pages, cfg.page_size, cfg.kv_heads, 128, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(cfg.layers)]
+    vps = [torch.randn(pages, cfg.page_size, cfg.kv_heads, 128, device="cuda", generator=gen).to(torch.bfloat16) for _ in range(cfg.layers)]
+    tables = torch.randperm(pages, generator=torch.Generator().manual_seed(2)).reshape(1, pages).to(torch.int32).cuda()
+    step = dec.DecodeStep(cfg, w, 1, max_context=context, key_pages=kps, value_pages=vps, page_tables=tables)
+    step.token_in.fill_(1234)
+    step.positions.fill_(context - 1)            # the new token is the context's last position
+    ms = time_graph(torch, step.enqueue, args.steps, args.warmup)
+    assert step.fault() == 0, "a device-side wait gave up"
+    H, I = cfg.hidden, cfg.intermediate
+    weights = cfg.layers * sum(weight_bytes(k, n) for (k, n) in ((H, cfg.qkv_width), (cfg.q_heads * 128, H), (H, 2 * I), (I, H))) \
+        + weight_bytes(H, cfg.vocab)
+    kv = cfg.layers * context * cfg.kv_heads * 128 * 2 * 2
+    nbytes = weights + kv
+    return {"ms_per_step": round(ms, 5), "tok_per_s": round(1e3 / ms, 1), "context": context, "batch": 1,
+            "bytes_per_step": nbytes, "weight_bytes": weights, "kv_bytes": kv,
+            "GBps": round(nbytes / (ms * 1e-3) / 1e9, 1), "hbm_frac": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm"], 4),
+            "launches_per_step": step.launches,
+            "what": "whole decode step in one CUDA graph: per layer one attention launch (head norms, RoPE, cache append, "
+                    "split softmax and merge) and one list launch (o_proj + residual, norm + gate/up, SwiGLU + down + residual, "
+                    "norm + next q/k/v); greedy token by arg-max"}
 
 
 def bench_moe(torch, gb, peaks, args, token_counts=(1, 32, 512, 4096), cpu_rows=True):

@@ -27,7 +27,8 @@ namespace {
 
 constexpr int kAttnHeadDim = 128;
 constexpr int kAttnWarps = 8;
-constexpr int kAttnSplitPositions = 128;   // positions per split
+constexpr int kAttnSplitPositions = 128;   // positions per split: 16 per warp, all loaded at once (one wave of CTAs at 2048 positions)
+constexpr int kAttnMaxSplits = 1024;       // contexts up to 65536 positions
 
 struct AttnParams {
     const __nv_bfloat16* qkv;       // [batch, (q_heads + 2 kv_heads) * 128]: q | k | v
@@ -98,6 +99,28 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const
     const float* sn = p.rope_sin + size_t(valid ? slot : 0) * (kAttnHeadDim / 2);
     const bool holds_new = valid && slot >= start && slot < end;
 
+    // A warp owns positions start + warp, + 8, ...: one per cache page of 16 when the pages are that size.  All
+    // their rows are requested before the first is used, so the walk costs one trip to memory.
+    constexpr int kPer = kAttnSplitPositions / kAttnWarps;
+    uint2 kr[kPer], vr[kPer];
+    if (valid) {
+        size_t at[kPer];
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int pos = start + warp + u * kAttnWarps;
+            at[u] = (pos < end && pos != slot)
+                        ? ((size_t(__ldg(&table[pos / p.page_size])) * p.page_size + pos % p.page_size) * p.kv_heads + kv_head) * kAttnHeadDim
+                        : ~size_t(0);
+        }
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            if (at[u] != ~size_t(0)) {
+                kr[u] = __ldcg(reinterpret_cast<const uint2*>(p.key_pages + at[u]) + lane);
+                vr[u] = __ldcg(reinterpret_cast<const uint2*>(p.value_pages + at[u]) + lane);
+            }
+        }
+    }
+
     if (warp == 0) {
         float o[4];
         norm_rope_head(row + q_head * kAttnHeadDim, p.q_norm_w, cs, sn, p.eps, lane, o);
@@ -127,21 +150,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const
     for (int i = 0; i < 4; ++i) qv[i] = q_s[4 * lane + i];
     const float scale = 0.08838834764831845f;   // 1 / sqrt(128)
     float run_max = -FLT_MAX, run_sum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-    constexpr int kUnroll = 4;
-    for (int pos0 = start + warp; valid && pos0 < end; pos0 += kAttnWarps * kUnroll) {
-        uint2 kr[kUnroll], vr[kUnroll];
+    if (valid) {
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const int pos = pos0 + u * kAttnWarps;
-            if (pos < end && pos != slot) {
-                const size_t at = ((size_t(table[pos / p.page_size]) * p.page_size + pos % p.page_size) * p.kv_heads + kv_head) * kAttnHeadDim;
-                kr[u] = __ldcg(reinterpret_cast<const uint2*>(p.key_pages + at) + lane);
-                vr[u] = __ldcg(reinterpret_cast<const uint2*>(p.value_pages + at) + lane);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const int pos = pos0 + u * kAttnWarps;
+        for (int u = 0; u < kPer; ++u) {
+            const int pos = start + warp + u * kAttnWarps;
             if (pos >= end) break;
             float kf[4], vf[4];
             if (pos == slot) {   // the new token's row is not read back from the cache
@@ -192,20 +204,33 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // ---- merge of the splits, in split order.  The statistics are fetched by one thread per split and the
+    // partial outputs without a condition on them, so that the loads overlap instead of queueing behind one another.
+    __shared__ float m_max[kAttnMaxSplits], m_sum[kAttnMaxSplits];
+    for (int s = threadIdx.x; s < p.splits; s += blockDim.x) {
+        m_max[s] = __ldcg(&p.part_stats[(head_index * p.splits + s) * 2]);
+        m_sum[s] = __ldcg(&p.part_stats[(head_index * p.splits + s) * 2 + 1]);
+    }
+    __syncthreads();
     if (threadIdx.x < kAttnHeadDim) {
         const int d = threadIdx.x;
         float t_max = -FLT_MAX;
         for (int s = 0; s < p.splits; ++s)
-            if (__ldcg(&p.part_stats[(head_index * p.splits + s) * 2 + 1]) > 0.f)
-                t_max = fmaxf(t_max, __ldcg(&p.part_stats[(head_index * p.splits + s) * 2]));
+            if (m_sum[s] > 0.f) t_max = fmaxf(t_max, m_max[s]);
         float t_sum = 0.f, t_out = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-            const size_t si = head_index * p.splits + s;
-            const float sum = __ldcg(&p.part_stats[si * 2 + 1]);
-            if (sum <= 0.f) continue;
-            const float m = __expf(__ldcg(&p.part_stats[si * 2]) - t_max);
-            t_sum += m * sum;
-            t_out += m * __ldcg(&p.part_out[si * kAttnHeadDim + d]);
+        const float* po = p.part_out + head_index * p.splits * kAttnHeadDim + d;
+        for (int s0 = 0; s0 < p.splits; s0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = s0 + u < p.splits ? __ldcg(po + size_t(s0 + u) * kAttnHeadDim) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int s = s0 + u;
+                if (s >= p.splits || m_sum[s] <= 0.f) continue;
+                const float m = __expf(m_max[s] - t_max);
+                t_sum += m * m_sum[s];
+                t_out += m * v[u];
+            }
         }
         p.out[size_t(b) * q_width + q_head * kAttnHeadDim + d] = __float2bfloat16_rn(t_sum > 0.f ? t_out / t_sum : 0.f);
     }
@@ -267,6 +292,8 @@ int validate_attention(const garnet_b200_attention_options* o)
         return fail(GARNET_B200_INVALID_VALUE, "attention: q_heads must be a positive multiple of kv_heads");
     if (o->page_size <= 0 || o->max_logical_pages <= 0 || o->max_context <= 0 || o->rope_positions <= 0 || !(o->norm_eps > 0.f))
         return fail(GARNET_B200_INVALID_VALUE, "attention: page_size, max_logical_pages, max_context, rope_positions and norm_eps must be positive");
+    if (o->max_context > kAttnMaxSplits * kAttnSplitPositions)
+        return fail(GARNET_B200_NOT_SUPPORTED, "attention: max_context above %d", kAttnMaxSplits * kAttnSplitPositions);
     if (o->max_context > o->max_logical_pages * o->page_size || o->max_context > o->rope_positions)
         return fail(GARNET_B200_INVALID_VALUE, "attention: max_context exceeds the page table or the rope tables");
     return GARNET_B200_OK;

@@ -153,7 +153,7 @@ class DecodeStep:
         self.launches = 2 + 2 * cfg.layers + 1
         self._graph = None
 
-    def _enqueue(self) -> None:
+    def enqueue(self) -> None:
         L = self.w["layers"]
         embedding_gather(self.w["embedding"], self.token_in, self.x[0])
         self.lists[0].run(pdl=True)
@@ -165,11 +165,11 @@ class DecodeStep:
 
     def capture(self) -> None:
         """Records the step as one CUDA graph (after one eager run to settle allocations)."""
-        self._enqueue()
+        self.enqueue()
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self._enqueue()
+            self.enqueue()
         self._graph = g
 
     def run(self) -> None:
@@ -178,7 +178,7 @@ class DecodeStep:
         if self._graph is not None:
             self._graph.replay()
         else:
-            self._enqueue()
+            self.enqueue()
 
     def fault(self) -> int:
         return max(l.fault() for l in self.lists)
