@@ -383,3 +383,19 @@ def test_k_sharded_linear_partial_sums(world, m):
     with pytest.raises(garnet_b200.GarnetB200Error):
         garnet_b200.W4A16Linear().prepare(dev(case["nibbles"]), bf16_tensor(case["scales_bits"]).reshape(n, k // 128),
                                           n, k, 128, 0, 3, shard_axis=1)          # 2048 / 3 is not a whole number of groups
+
+
+def test_full_lm_head_at_the_benchmark_batches():
+    """The whole lm_head of BASELINE's config 2 (151936 x 2048: 9496 strips, a vocabulary that is
+    not a multiple of 128) at M = 1, 64 and 256, i.e. through the list kernel, the tile kernel with
+    one batch tile and with two: every output column of sampled batch rows against the exact oracle."""
+    n, k = 151936, 2048
+    case = synth.int4_linear(n, k, 256, seed=77)
+    lin = make_linear(case, n, k)
+    x_all = bf16_tensor(case["x_bits"]).reshape(256, k)
+    for m, rows in ((1, [0]), (64, [0, 31, 63]), (256, [0, 127, 128, 255])):
+        y = lin.forward(x_all[:m].contiguous())
+        torch.cuda.synchronize()
+        assert lin.fault() == 0 and y.shape == (m, n)
+        _, y64 = oracle.w4a16_exact(case["nibbles"], case["scales_f32"], n, k, 128, case["x_f32"][rows])
+        check_close(y[torch.tensor(rows, device="cuda")], y64, rounded_weights=m > 16)
