@@ -842,8 +842,10 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
             }
         }
     }
+    // after a give-up the copies already issued may still land: give each stage a short moment (the fault is
+    // recorded already, nothing is read any more) before the CTA's shared memory is released
     if (!ok)
-        for (int i = 0; i < kMoeStages; ++i) (void)mbar_wait(&full[i], 0);
+        for (int i = 0; i < kMoeStages; ++i) (void)mbar_wait(&full[i], 0, 2000000ull);
 }
 
 // y[t,d] = bf(sum_j vals[t*k+j, d] * p[t,j]) over the local experts in router order

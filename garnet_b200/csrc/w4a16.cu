@@ -175,16 +175,6 @@ int W4A16::init_common()
     return init_tc();
 }
 
-static bool use_tensor_core_tiles()
-{
-    // GARNET_B200_W4_NO_TC=1 keeps every batch size on the streaming kernel (A/B switch).
-    static const bool on = [] {
-        const char* e = getenv("GARNET_B200_W4_NO_TC");
-        return !(e && e[0] == '1');
-    }();
-    return on;
-}
-
 W4A16::~W4A16()
 {
     if (owns_packed && packed) cudaFree(packed);
@@ -210,7 +200,7 @@ int W4A16::run(const void* d_x, void* d_y, int m, void* ws, size_t ws_bytes, uns
     __nv_bfloat16* y = static_cast<__nv_bfloat16*>(d_y);
     // Above 16 rows the weights are worth expanding once per 128 rows for the tensor core.
     // (also when the rows do not fit one launch of the streaming kernel: a very long K)
-    if ((m > 16 || m > max_rows_per_launch) && use_tensor_core_tiles()) return launch_tc(x, y, m, ws, ws_bytes, flags, stream);
+    if ((m > 16 || m > max_rows_per_launch)) return launch_tc(x, y, m, ws, ws_bytes, flags, stream);
     for (int m0 = 0; m0 < m; m0 += max_rows_per_launch) {
         const int rows = std::min(max_rows_per_launch, m - m0);
         const int rc = launch_stream(x + size_t(m0) * geo.cols, y + size_t(m0) * geo.rows, rows, geo.rows, flags,
