@@ -630,6 +630,63 @@ def cpu_baseline(sample_seconds=10.0):
                       f"Q4Q8Linear::Forward (int8 activations), {dt:.1f} s"}
 
 
+def reference_gpu_moe(token_counts=(1, 8, 32, 512, 4096)):
+    """The reference's own GPU MoE on this box (oracle/_ref/libgarnet_ref_gpu.so, compiled unchanged from
+    its sources): the gpt-oss-120b layer of bench_moe (same seed, same tensors), through RunGptOssMoe (the
+    scalar path below 16 tokens, the grouped WMMA path from 16) and through GptOssMarlin::Run, the
+    production GEMM.  Marlin takes 8 tokens at most in its default configuration; for the larger counts
+    the reference's documented opt-in is set (GARNET_GPT_OSS_MARLIN_MAX_TOKENS=4096 with
+    GARNET_GPT_OSS_MARLIN_PREFILL_BLOCK=32) and the rows say so.  CUDA events around repeated calls on
+    rotating inputs; None when the library or a GPU is absent."""
+    try:
+        import torch
+        from oracle import ref_gpu
+    except Exception:
+        return None
+    if not ref_gpu.available() or not torch.cuda.is_available():
+        return None
+    os.environ.setdefault("GARNET_GPT_OSS_MARLIN_MAX_TOKENS", "4096")
+    os.environ.setdefault("GARNET_GPT_OSS_MARLIN_PREFILL_BLOCK", "32")
+    H = I = 2880
+    E, K = 128, 4
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(99)
+    u8 = lambda *shape, lo=0, hi=256: torch.randint(lo, hi, shape, dtype=torch.uint8, device="cuda", generator=gen)   # noqa: E731
+    router_w = (torch.randn(E, H, device="cuda", generator=gen) / H ** 0.5).to(torch.bfloat16).float()
+    tensors = [router_w, torch.zeros(E, device="cuda"), u8(E, 2 * I, H // 32, 16), u8(E, 2 * I, H // 32, lo=117, hi=124),
+               torch.zeros(E, 2 * I, device="cuda"), u8(E, H, I // 32, 16), u8(E, H, I // 32, lo=117, hi=124),
+               torch.zeros(E, H, device="cuda")]
+    rows = []
+    for T in token_counts:
+        prefill = 1 if T > 8 else 0
+        ref = ref_gpu.RefMoe(H, I, E, K, tensors, prefill=prefill)
+        rot = 16 if T == 1 else (4 if T <= 32 else 1)
+        xs = [torch.randn(T, H, device="cuda", generator=gen).to(torch.bfloat16).float() for _ in range(rot)]
+        y = torch.empty(T, H, device="cuda")
+        row = {"tokens": T}
+        for name, fn in (("RunGptOssMoe", ref.run), ("GptOssMarlin", ref.run_marlin)):
+            rc, _ = fn(xs[0], out=y)
+            torch.cuda.synchronize()
+            if rc != 0:
+                row[name] = {"status": int(rc), "note": "cudaErrorNotSupported: the reference falls back" if rc == 801 else "error"}
+                continue
+            reps = 3 if T > 512 and name == "RunGptOssMoe" else 10
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for r in range(reps):
+                for x in xs:
+                    fn(x, out=y)
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / (reps * rot)
+            row[name] = {"ms": round(ms, 4), "tok_per_s": round(T / (ms * 1e-3), 1)}
+            if name == "GptOssMarlin" and T > 8:
+                row[name]["config"] = "GARNET_GPT_OSS_MARLIN_MAX_TOKENS=4096 GARNET_GPT_OSS_MARLIN_PREFILL_BLOCK=32, prefill=1"
+        ref.close()
+        rows.append(row)
+    return rows
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -646,6 +703,7 @@ def run_reference(args):
     dt = (time.perf_counter() - t0) / args.steps
     value = bytes_pass / dt / 1e9
     sample = (f"each step = the full decode pass, 197 linears at M=1 ({bytes_pass} B), Q4Q8Linear::Forward on host cores")
+    moe_gpu = None if args.no_moe else reference_gpu_moe()
     print(json.dumps({
         "impl": "reference", "metric": "w4a16_weight_GBps", "value": round(value, 3), "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3),
@@ -655,6 +713,7 @@ def run_reference(args):
                    "bytes_per_step": bytes_pass},
         "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "moe_reference_gpu": moe_gpu,
     }), flush=True)
 
 

@@ -549,3 +549,66 @@ def test_streaming_path_at_every_size():
     """GARNET_B200_MOE_MX=0 keeps every size on the streaming kernel: the path a handle
     takes when the block-scaled copy cannot be built (no tensor-map encoder in the driver)."""
     _rerun_with_switch("0", "fixtures or golden or bf16_io or rows_entry")
+
+
+# ---------------------------------------------------- against the reference's own GPU kernels
+
+def _ref_gpu():
+    from oracle import ref_gpu
+    if not ref_gpu.available():
+        pytest.skip("oracle/_ref/libgarnet_ref_gpu.so has not been built (make -C oracle ref_gpu REF=...)")
+    return ref_gpu
+
+
+@pytest.mark.parametrize("tokens", [1, 3, 17, 65])
+def test_against_the_reference_gpu_moe_on_its_own_fixtures(tokens):
+    """The reference's GPU kernels (compiled unchanged from its sources) on the closed-form inputs of
+    its own parity test (kernel_parity.cpp:610-652): RunGptOssMoe - the scalar path below 16 tokens,
+    the grouped WMMA path from 16 - against this operator and against the CPU oracle, each within the
+    reference's bound .002; and the production Marlin GEMM (8 tokens at most by default) within its .004."""
+    ref_gpu = _ref_gpu()
+    case = reference_fixture(tokens, 96, 64)
+    ops = [dev(case[k]) for k in ("router_w", "router_b", "gu_blocks", "gu_scales", "gu_bias", "dn_blocks", "dn_scales", "dn_bias")]
+    ref = ref_gpu.RefMoe(case["hidden"], case["inter"], case["experts"], case["topk"], ops)
+    x = dev(case["x"])
+    rc, y_ref = ref.run(x)
+    torch.cuda.synchronize()
+    assert rc == 0
+    mine = build(case).run(x).cpu().numpy()
+    y_ref = y_ref.cpu().numpy()
+    expect = oracle.moe_forward(case["x"], case["router_w"], case["router_b"], *oracle_args(case))[0]
+    assert_close(y_ref, expect, 0.002, "reference GPU vs oracle")
+    assert_close(mine, y_ref, 0.002, "this operator vs reference GPU")
+    if tokens <= 8:
+        rc, y_m = ref.run_marlin(x)
+        torch.cuda.synchronize()
+        assert rc == 0
+        assert_close(mine, y_m.cpu().numpy(), 0.004, "this operator vs reference Marlin")
+    ref.close()
+
+
+def test_against_the_reference_gpu_moe_at_the_gpt_oss_120b_shape():
+    """Decode-sized batches of the benchmark's layer (2880 x 2880, 128 experts, top-4): this operator
+    against the reference's scalar kernels and its Marlin GEMM on the same synthetic tensors, for the
+    tokens whose routing agrees (a router logit may round the other way on either side), at the
+    benchmark's bound 1e-2 judged against the scale of the summands."""
+    ref_gpu = _ref_gpu()
+    case = synth.moe_layer(8, seed=41)
+    ops = [dev(case[k]) for k in ("router_w", "router_b", "gu_blocks", "gu_scales", "gu_bias", "dn_blocks", "dn_scales", "dn_bias")]
+    ref = ref_gpu.RefMoe(2880, 2880, 128, 4, ops)
+    x = dev(case["x"])
+    moe = build(case)
+    mine = moe.run(x).cpu().numpy()
+    _, sel, pr = [t.cpu().numpy() for t in moe.route(x)]
+    expect, mass = oracle.moe_experts(case["x"], sel, pr, *oracle_args(case), want_mass=True)
+    _, o_sel, _ = oracle.moe_route(case["x"], case["router_w"], case["router_b"], 128, 4)
+    same = (sel == o_sel).all(axis=1)
+    assert same.sum() >= 6
+    for name, fn, tol in (("RunGptOssMoe", ref.run, 1e-2), ("GptOssMarlin", ref.run_marlin, 1e-2)):
+        rc, y = fn(x)
+        torch.cuda.synchronize()
+        assert rc == 0, name
+        y = y.cpu().numpy()
+        assert_close(y[same], expect[same], tol, f"{name} vs oracle", mass[same])
+        assert_close(mine[same], y[same], tol, f"this operator vs {name}", mass[same])
+    ref.close()
