@@ -63,6 +63,18 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_attention_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i, c.c_uint, vp]
     L.garnet_b200_embedding_gather.argtypes = [vp, vp, vp, i, i, i, c.c_uint, vp]
     L.garnet_b200_argmax_bf16.argtypes = [vp, vp, i, i, c.c_uint, vp]
+    L.garnet_b200_safetensors_open.argtypes = [c.c_char_p, c.POINTER(vp)]
+    L.garnet_b200_safetensors_count.argtypes = [vp]
+    L.garnet_b200_safetensors_entry.argtypes = [vp, i, c.c_char_p, c.POINTER(c.c_char_p), c.POINTER(c.c_char_p), c.POINTER(i),
+                                                c.POINTER(c.c_longlong), c.POINTER(vp), c.POINTER(sz)]
+    L.garnet_b200_safetensors_close.argtypes = [vp]
+    L.garnet_b200_safetensors_close.restype = None
+    L.garnet_b200_safetensors_write.argtypes = [c.c_char_p, vp, vp, vp, vp, vp, vp, i]
+    L.garnet_b200_int4_quantize_host.argtypes = [vp, i, i, i, i, i, vp, vp, c.POINTER(c.c_double)]
+    L.garnet_b200_packed_tensor_name.argtypes = [c.c_char_p, i, i, i, i, c.c_char_p, sz]
+    L.garnet_b200_packed_tensor_name_parse.argtypes = [c.c_char_p, c.POINTER(i), c.POINTER(i), c.POINTER(i), c.POINTER(i),
+                                                       c.POINTER(c.c_char_p)]
+    L.garnet_b200_checkpoint_build_cache.argtypes = [vp, c.c_char_p, i, i, i, i, i]
     L.garnet_b200_moe_workspace.argtypes = [vp, i, c.POINTER(sz)]
     L.garnet_b200_moe_create.argtypes = [vp, vp, vp, c.POINTER(vp)]
     L.garnet_b200_moe_run.argtypes = [vp, vp, vp, vp, sz, i, vp]

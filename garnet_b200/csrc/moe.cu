@@ -227,6 +227,133 @@ moe_route_scores_kernel(const XT* __restrict__ x, const float* __restrict__ rw, 
     }
 }
 
+__device__ __forceinline__ bool expert_is_local(int e, const MoeShard& sh)
+{
+    if (sh.world <= 1) return true;
+    return sh.interleaved ? (e % sh.world) == sh.rank : (e >= sh.lo && e < sh.hi);
+}
+
+// Decode-sized batches (at most 8 tokens, at most 256 experts): top-k, counts, stable slot
+// order, the task list and the row-tile prefix by one CTA of 256 threads - the last CTA of
+// the router kernel to finish (same results as moe_topk_kernel + moe_count_kernel +
+// moe_fill_kernel).
+struct SmallMeta {
+    int* selected;
+    float* probs;
+    int* counts;
+    int* offsets;
+    int* sorted;
+    int4* tasks;
+    int* ntasks;
+    int* tile_prefix;
+    unsigned* done;       // CTAs of the router kernel that have written their logits; nullptr: no bookkeeping here
+    int topk, rows_per_task, tile_rows;
+    MoeShard sh;
+};
+
+__device__ __forceinline__ void small_meta_body(const float* logits, const SmallMeta& mt, int tokens, int experts)
+{
+    __shared__ int s_sel[8 * 8];
+    __shared__ int s_count[256], s_offset[257], s_task[257], s_tile[257];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int topk = mt.topk;
+    // ---- top-k: one warp per token (8 warps); the logits were written by other CTAs: read them from L2
+    if (warp < tokens) {
+        const float* l = logits + size_t(warp) * experts;
+        float top[8];
+        int chosen[8];
+        for (int j = 0; j < topk; ++j) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int e = lane; e < experts; e += 32) {
+                bool used = false;
+                for (int q = 0; q < j; ++q) used |= chosen[q] == e;
+                const float v = __ldcg(&l[e]);
+                if (!used && (arg == 0x7fffffff || v > best || (v == best && e < arg))) {
+                    best = v;
+                    arg = e;
+                }
+            }
+#pragma unroll
+            for (int off = 16; off; off >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
+                if (oa != 0x7fffffff && (arg == 0x7fffffff || ov > best || (ov == best && oa < arg))) {
+                    best = ov;
+                    arg = oa;
+                }
+            }
+            chosen[j] = arg;
+            top[j] = best;
+        }
+        if (lane == 0) {
+            float total = 0.f;
+            for (int j = 0; j < topk; ++j) total += expf(top[j] - top[0]);
+            for (int j = 0; j < topk; ++j) {
+                mt.selected[warp * topk + j] = chosen[j];
+                s_sel[warp * topk + j] = chosen[j];
+                mt.probs[warp * topk + j] = bf16_round_f(expf(top[j] - top[0]) / total);
+            }
+        }
+    }
+    __syncthreads();
+    // ---- rows per expert (thread e)
+    const int slots = tokens * topk;
+    const int e = threadIdx.x;
+    int mine = 0;
+    if (e < experts && expert_is_local(e, mt.sh))
+        for (int i = 0; i < slots; ++i) mine += s_sel[i] == e;
+    s_count[e] = e < experts ? mine : 0;
+    if (e < experts) mt.counts[e] = mine;
+    __syncthreads();
+    // ---- exclusive prefix sums of rows, tasks and row tiles: warp 0, eight experts per lane
+    if (warp == 0) {
+        int off = 0, tk = 0, tp = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int c = s_count[lane * 8 + q];
+            off += c;
+            tk += (c + mt.rows_per_task - 1) / mt.rows_per_task;
+            if (mt.tile_rows) tp += (c + mt.tile_rows - 1) / mt.tile_rows;
+        }
+        int xo = off, xt = tk, xp = tp;   // inclusive scan over the lanes
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int a = __shfl_up_sync(0xffffffffu, xo, d), b = __shfl_up_sync(0xffffffffu, xt, d),
+                      c = __shfl_up_sync(0xffffffffu, xp, d);
+            if (lane >= d) xo += a, xt += b, xp += c;
+        }
+        off = xo - off, tk = xt - tk, tp = xp - tp;   // exclusive start of this lane's eight experts
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int idx = lane * 8 + q, c = s_count[idx];
+            s_offset[idx] = off, s_task[idx] = tk, s_tile[idx] = tp;
+            off += c;
+            tk += (c + mt.rows_per_task - 1) / mt.rows_per_task;
+            if (mt.tile_rows) tp += (c + mt.tile_rows - 1) / mt.tile_rows;
+        }
+        if (lane == 31) s_offset[256] = off, s_task[256] = tk, s_tile[256] = tp;
+    }
+    __syncthreads();
+    if (e < experts) {
+        mt.offsets[e] = s_offset[e];
+        if (mt.tile_rows) mt.tile_prefix[e] = s_tile[e];
+    }
+    if (e == 0) {
+        // experts beyond `experts` have no rows, so entry `experts` already holds the totals
+        mt.offsets[experts] = s_offset[experts];
+        *mt.ntasks = s_task[experts];
+        if (mt.tile_rows) mt.tile_prefix[experts] = s_tile[experts];
+    }
+    if (e < experts && mine) {
+        int n = 0;
+        for (int i = 0; i < slots; ++i)
+            if (s_sel[i] == e) mt.sorted[s_offset[e] + n++] = i;   // slot order kept: stable
+        for (int b = 0; b * mt.rows_per_task < mine; ++b)
+            mt.tasks[s_task[e] + b] = make_int4(e, s_offset[e] + b * mt.rows_per_task, min(mt.rows_per_task, mine - b * mt.rows_per_task), 0);
+    }
+}
+
 // Router for at most 8 tokens (decode): latency matters, so the hidden dimension is
 // split over the 8 warps of a CTA and a CTA owns only 4 experts (E/4 CTAs); the
 // warps' partial sums meet in shared memory.  Same results contract as
@@ -236,11 +363,12 @@ template <typename XT>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, const float* __restrict__ rb,
                        float* __restrict__ logits, __half* __restrict__ xh, int* __restrict__ xshift, int tokens,
-                       int hidden, int experts)
+                       int hidden, int experts, const SmallMeta mt)
 {
     extern __shared__ float xs[];   // [kRouteTokens][hidden]; rows >= tokens are not used
     __shared__ float part[kRouteWarps][4][kRouteTokens];
     __shared__ float s_amax[kRouteWarps];
+    __shared__ int s_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     pdl_wait();   // x comes from the kernel before this one
@@ -286,9 +414,8 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
             logits[size_t(t) * experts + e0 + q] = bf16_round_f(v + rb[e0 + q]);
         }
     }
-    if (!xh) return;
     // fp16 copy of token t by CTA t (mod the grid)
-    for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
+    for (int t = blockIdx.x; xh && t < tokens; t += gridDim.x) {
         float amax = 0.f;
         for (int d = threadIdx.x; d < hidden; d += kRouteWarps * 32)
             amax = fmaxf(amax, fabsf(bf16_round_f(xs[t * hidden + d])));
@@ -307,12 +434,16 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
             xh[size_t(t) * hidden + d] = __float2half_rn(bf16_round_f(xs[t * hidden + d]) * scale);
         if (threadIdx.x == 0) xshift[t] = shift;
     }
-}
-
-__device__ __forceinline__ bool expert_is_local(int e, const MoeShard& sh)
-{
-    if (sh.world <= 1) return true;
-    return sh.interleaved ? (e % sh.world) == sh.rank : (e >= sh.lo && e < sh.hi);
+    if (!mt.done) return;
+    // the CTA that finishes last has every logit in reach and does the call's bookkeeping
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(mt.done, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    small_meta_body(logits, mt, tokens, experts);
+    if (threadIdx.x == 0) *mt.done = 0;   // for the next call
 }
 
 // k rounds of arg-max (ties to the lowest expert index), then the softmax over the
@@ -485,95 +616,6 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
             s_running += total;
         }
         __syncthreads();
-    }
-}
-
-// Decode-sized batches (at most 8 tokens, at most 256 experts): top-k, counts,
-// stable slot order and the task list in ONE single-CTA launch instead of three.
-// Same results as moe_topk_kernel + moe_count_kernel + moe_fill_kernel.
-__global__ void __launch_bounds__(256)
-moe_small_meta_kernel(const float* __restrict__ logits, int* __restrict__ selected, float* __restrict__ probs,
-                      int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ sorted,
-                      int4* __restrict__ tasks, int* __restrict__ ntasks, int tokens, int experts, int topk,
-                      int rows_per_task, MoeShard sh, int tile_rows, int* __restrict__ tile_prefix)
-{
-    __shared__ int s_sel[8 * 8];
-    __shared__ int s_count[256], s_offset[257], s_task[257];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    pdl_launch_dependents();
-    pdl_wait();   // the logits come from the kernel before this one
-    // ---- top-k: one warp per token (8 warps)
-    if (warp < tokens) {
-        const float* l = logits + size_t(warp) * experts;
-        float top[8];
-        int chosen[8];
-        for (int j = 0; j < topk; ++j) {
-            float best = -INFINITY;
-            int arg = 0x7fffffff;
-            for (int e = lane; e < experts; e += 32) {
-                bool used = false;
-                for (int q = 0; q < j; ++q) used |= chosen[q] == e;
-                const float v = l[e];
-                if (!used && (arg == 0x7fffffff || v > best || (v == best && e < arg))) {
-                    best = v;
-                    arg = e;
-                }
-            }
-#pragma unroll
-            for (int off = 16; off; off >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, best, off);
-                const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
-                if (oa != 0x7fffffff && (arg == 0x7fffffff || ov > best || (ov == best && oa < arg))) {
-                    best = ov;
-                    arg = oa;
-                }
-            }
-            chosen[j] = arg;
-            top[j] = best;
-        }
-        if (lane == 0) {
-            float total = 0.f;
-            for (int j = 0; j < topk; ++j) total += expf(top[j] - top[0]);
-            for (int j = 0; j < topk; ++j) {
-                selected[warp * topk + j] = chosen[j];
-                s_sel[warp * topk + j] = chosen[j];
-                probs[warp * topk + j] = bf16_round_f(expf(top[j] - top[0]) / total);
-            }
-        }
-    }
-    __syncthreads();
-    // ---- counts per expert (thread e), then prefix sums by thread 0
-    const int slots = tokens * topk;
-    const int e = threadIdx.x;
-    int mine = 0;
-    if (e < experts && expert_is_local(e, sh))
-        for (int i = 0; i < slots; ++i) mine += s_sel[i] == e;
-    s_count[e] = e < experts ? mine : 0;
-    if (e < experts) counts[e] = mine;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int off = 0, tk = 0, tp = 0;
-        for (int q = 0; q < experts; ++q) {
-            s_offset[q] = off;
-            s_task[q] = tk;
-            if (tile_rows) tile_prefix[q] = tp;
-            off += s_count[q];
-            tk += (s_count[q] + rows_per_task - 1) / rows_per_task;
-            if (tile_rows) tp += (s_count[q] + tile_rows - 1) / tile_rows;
-        }
-        s_offset[experts] = off;
-        *ntasks = tk;
-        if (tile_rows) tile_prefix[experts] = tp;
-    }
-    __syncthreads();
-    if (e < experts) offsets[e] = s_offset[e];
-    if (e == 0) offsets[experts] = s_offset[experts];
-    if (e < experts && mine) {
-        int n = 0;
-        for (int i = 0; i < slots; ++i)
-            if (s_sel[i] == e) sorted[s_offset[e] + n++] = i;   // slot order kept: stable
-        for (int b = 0; b * rows_per_task < mine; ++b)
-            tasks[s_task[e] + b] = make_int4(e, s_offset[e] + b * rows_per_task, min(rows_per_task, mine - b * rows_per_task), 0);
     }
 }
 
@@ -1030,8 +1072,8 @@ int Moe::setup_common(cudaStream_t stream)
     geo_up = make_geom(kFormatMxfp4, 2 * opt.intermediate, opt.hidden, 32);
     geo_down = make_geom(kFormatMxfp4, opt.hidden, opt.intermediate, 32);
     stored_experts = local_experts();
-    GB_CUDA(cudaMalloc(&flag_dev, sizeof(int)));
-    GB_CUDA(cudaMemsetAsync(flag_dev, 0, sizeof(int), stream));
+    GB_CUDA(cudaMalloc(&flag_dev, 2 * sizeof(int)));   // [0]: scale bytes that need the careful decode; [1]: router CTAs done
+    GB_CUDA(cudaMemsetAsync(flag_dev, 0, 2 * sizeof(int), stream));
     GB_CUDA(cudaHostAlloc(&fault_host, sizeof(int), cudaHostAllocMapped));
     *fault_host = 0;
     GB_CUDA(cudaHostGetDevicePointer(&fault_dev, fault_host, 0));
@@ -1205,9 +1247,9 @@ int Moe::finish_prepare(cudaStream_t stream)
         return fail(GARNET_B200_NOT_SUPPORTED, "moe: the block-scaled layout alone was asked for, but this shape or driver does not support it");
     // the router kernels also have a little static shared memory: leave room for it
     GB_CUDA(cudaFuncSetAttribute(moe_route_small_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(kMaxDynamicSmem - 2048)));
+                                 int(kMaxDynamicSmem - 8192)));
     GB_CUDA(cudaFuncSetAttribute(moe_route_small_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(kMaxDynamicSmem - 2048)));
+                                 int(kMaxDynamicSmem - 8192)));
     GB_CUDA(cudaFuncSetAttribute(moe_route_scores_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  int(kMaxDynamicSmem - 1024)));
     GB_CUDA(cudaFuncSetAttribute(moe_route_scores_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1240,10 +1282,12 @@ static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 }
 
 int Moe::route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
-               cudaStream_t stream, bool skip_topk, float* route_partial, int* counts)
+               cudaStream_t stream, bool skip_topk, float* route_partial, int* counts, const void* small_meta)
 {
+    SmallMeta mt{};   // no bookkeeping unless the caller (run, at most 8 tokens) hands its lists over
+    if (small_meta) mt = *static_cast<const SmallMeta*>(small_meta);
     const size_t smem = size_t(kRouteTokens) * opt.hidden * sizeof(float);
-    if (smem > kMaxDynamicSmem - 2048) return fail(GARNET_B200_NOT_SUPPORTED, "moe_route: hidden too large");
+    if (smem > kMaxDynamicSmem - 8192) return fail(GARNET_B200_NOT_SUPPORTED, "moe_route: hidden too large");
     // spread the experts over enough CTAs to fill the machine at small token counts
     const int token_ctas = (tokens + kRouteTokens - 1) / kRouteTokens;
     int per_cta = opt.experts;
@@ -1259,11 +1303,11 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
         if (opt.io_dtype == GARNET_B200_FP32)
             GB_CUDA(launch_pdl(moe_route_small_kernel<float>, dim3(ctas), dim3(kRouteWarps * 32), small_smem, stream, true,
                                static_cast<const float*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens,
-                               opt.hidden, opt.experts));
+                               opt.hidden, opt.experts, mt));
         else
             GB_CUDA(launch_pdl(moe_route_small_kernel<__nv_bfloat16>, dim3(ctas), dim3(kRouteWarps * 32), small_smem, stream,
                                true, static_cast<const __nv_bfloat16*>(x), router_w_ptr, router_b_ptr, logits, xh,
-                               xshift, tokens, opt.hidden, opt.experts));
+                               xshift, tokens, opt.hidden, opt.experts, mt));
     } else if (opt.io_dtype == GARNET_B200_FP32) {
         moe_route_scores_kernel<float><<<grid, kRouteWarps * 32, smem, stream>>>(
             static_cast<const float*>(x), router_w_ptr, router_b_ptr, logits, xh, xshift, tokens, opt.hidden,
@@ -1377,13 +1421,18 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     const MoeShard sh = shard();
     const bool small = tokens <= 8 && opt.experts <= 256;
     const int tile_rows = use_mx(slots) ? moe_mx_plan(opt, tokens, slots).nt : 0;
-    if (int rc = route(x, w.logits, w.selected, w.probs, w.xh, w.xshift, tokens, stream, small, w.route_partial, w.counts))
-        return rc;
+    SmallMeta mt{};
     if (small) {
-        GB_CUDA(launch_pdl(moe_small_meta_kernel, dim3(1), dim3(256), 0, stream, true, w.logits, w.selected, w.probs,
-                           w.counts, w.offsets, w.sorted, w.tasks, w.ntasks, tokens, opt.experts, opt.top_k, kMoeRows,
-                           sh, tile_rows, w.mx_tp));
-    } else {
+        // at most 8 tokens: the router kernel's last CTA also selects, counts and builds the lists
+        mt.selected = w.selected, mt.probs = w.probs, mt.counts = w.counts, mt.offsets = w.offsets, mt.sorted = w.sorted;
+        mt.tasks = w.tasks, mt.ntasks = w.ntasks, mt.tile_prefix = w.mx_tp;
+        mt.done = reinterpret_cast<unsigned*>(flag_dev + 1);
+        mt.topk = opt.top_k, mt.rows_per_task = kMoeRows, mt.tile_rows = tile_rows, mt.sh = sh;
+    }
+    if (int rc = route(x, w.logits, w.selected, w.probs, w.xh, w.xshift, tokens, stream, small, w.route_partial, w.counts,
+                       small ? &mt : nullptr))
+        return rc;
+    if (!small) {
         // the counts come from the top-k kernel
         moe_fill_kernel<<<opt.experts, 1024, 0, stream>>>(w.selected, slots, w.counts, w.offsets, w.sorted, w.tasks,
                                                          w.ntasks, opt.experts, kMoeRows, sh, tile_rows, w.mx_tp);

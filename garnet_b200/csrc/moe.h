@@ -109,7 +109,8 @@ struct Moe {
     int finish_prepare(cudaStream_t stream);
     bool partial_output() const { return shard().world > 1 || opt.tp_world > 1; }
     int route(const void* x, float* logits, int* selected, float* probs, __half* xh, int* xshift, int tokens,
-              cudaStream_t stream, bool skip_topk = false, float* route_partial = nullptr, int* counts = nullptr);
+              cudaStream_t stream, bool skip_topk = false, float* route_partial = nullptr, int* counts = nullptr,
+              const void* small_meta = nullptr);
     int launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStream_t stream, int topk = -1);
     int run_rows(const void* x_rows, const int* row_expert, int rows, float* vals, void* ws, size_t ws_bytes,
                  cudaStream_t stream, int stage = 0, float* hidden_io = nullptr);

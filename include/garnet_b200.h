@@ -241,6 +241,49 @@ int garnet_b200_w4a16_fault(garnet_b200_w4a16_t h);
 
 void garnet_b200_w4a16_destroy(garnet_b200_w4a16_t h);
 
+/* ---- checkpoints and the packed-constant cache (host only) ---------------------
+ * The reference reads weights through SafeTensorsIndex (src/model/safetensors_index.h:42-60:
+ * a single .safetensors file, a Hugging Face model.safetensors.index.json, or a directory
+ * holding either; tensors are views into memory-mapped files), quantizes Qwen linears with
+ * QuantizeSymmetricINT4 (src/model/weight_quantization.cpp:188-270) and names the packed
+ * constants it derives so that a stripped engine can regenerate them
+ * (plugins/gpt_oss/include/gpt_oss_marlin_pack.h:29-44). */
+typedef struct garnet_b200_safetensors* garnet_b200_safetensors_t;
+int garnet_b200_safetensors_open(const char* path, garnet_b200_safetensors_t* out);
+int garnet_b200_safetensors_count(garnet_b200_safetensors_t st);
+/* One tensor, by `name` or (name == NULL) by `index` in file order: its name, dtype string
+ * ("BF16", "U8", ...), rank, shape (up to 8 extents), a pointer into the mapped file (valid
+ * until close) and its byte count.  Any output pointer may be NULL. */
+int garnet_b200_safetensors_entry(garnet_b200_safetensors_t st, int index, const char* name, const char** name_out,
+                                  const char** dtype, int* rank, long long* shape8, const void** data, size_t* bytes);
+void garnet_b200_safetensors_close(garnet_b200_safetensors_t st);
+/* Writes `count` tensors as one .safetensors file (data 256-byte aligned in the file). */
+int garnet_b200_safetensors_write(const char* path, const char* const* names, const char* const* dtypes, const int* ranks,
+                                  const long long* const* shapes, const void* const* datas, const size_t* bytes, int count);
+
+/* QuantizeSymmetricINT4 on the host: w [n, k] of fp32 / fp16 / bf16 -> canonical nibbles and
+ * fp16 (the reference's artifact) or bf16 scales; the same bits as garnet_b200_int4_quantize
+ * writes on the device.  max_abs_error may be NULL. */
+int garnet_b200_int4_quantize_host(const void* w, int w_dtype, int n, int k, int group, int scale_dtype, uint8_t* nibbles,
+                                   uint16_t* scales, double* max_abs_error);
+
+/* Names of derived constants: kind 0 = packed int4 linear ("__garnet_b200_w4a16_v1_g<a>_s<b>__:" +
+ * source; a = group, b = scale dtype), kind 1 / 2 = MoE projection in the streaming / block
+ * layout ("__garnet_b200_mxs|mxb_v1_u<a>_t<b>of<c>__:" + source; a = 0 gate_up, 1 down;
+ * b of c = the intermediate-axis part, 0 of 1 when unsplit).  `parse` is the inverse. */
+int garnet_b200_packed_tensor_name(const char* source, int kind, int a, int b, int c, char* out, size_t out_bytes);
+int garnet_b200_packed_tensor_name_parse(const char* name, int* kind, int* a, int* b, int* c, const char** source);
+
+/* Builds the packed-constant cache of a checkpoint as one .safetensors file: every tensor
+ * that garnet_b200_is_int4_linear_weight accepts is quantized and packed
+ * (garnet_b200_w4a16_create_prepacked takes the bytes as they are), every gpt-oss expert pair
+ * <prefix>.mlp.mlp1_weight.{blocks,scales} / mlp2_weight.{blocks,scales}
+ * (xModel/gpt_oss/120b/gpt_oss_llm.py:110-115) is packed in the layouts `moe_layouts` asks for
+ * (0 both; for tp_world > 1 this rank's part of the intermediate axis), all under their derived
+ * names; every other tensor is copied as it is.  One tensor at a time is held in memory. */
+int garnet_b200_checkpoint_build_cache(garnet_b200_safetensors_t st, const char* out_path, int group, int scale_dtype,
+                                       int moe_layouts, int tp_rank, int tp_world);
+
 /* ---- the rest of a Qwen3 decode step ------------------------------------------
  * What sits between the int4 linears of a decoder layer and is not folded into a
  * garnet_b200_w4a16_list: attention of one new token per sequence over the paged bf16 KV
