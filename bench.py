@@ -407,7 +407,7 @@ def bench_decode_step(torch, peaks, args, context=2048):
                     "norm + next q/k/v); greedy token by arg-max"}
 
 
-def bench_moe(torch, gb, peaks, args, token_counts=(1, 32, 512, 4096), cpu_rows=True):
+def bench_moe(torch, gb, peaks, args, token_counts=(1, 8, 32, 512, 4096), cpu_rows=True):
     """gpt-oss-120b MoE layer (hidden = intermediate = 2880, 128 experts, top-4, MXFP4), one GPU.
     tok/s per token count; a step = one call of the operator.  To keep weight reads
     out of L2 at small T, a graph holds several calls on different token sets
