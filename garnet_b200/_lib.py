@@ -75,6 +75,12 @@ def _declare(L: ctypes.CDLL) -> None:
     L.garnet_b200_packed_tensor_name_parse.argtypes = [c.c_char_p, c.POINTER(i), c.POINTER(i), c.POINTER(i), c.POINTER(i),
                                                        c.POINTER(c.c_char_p)]
     L.garnet_b200_checkpoint_build_cache.argtypes = [vp, c.c_char_p, i, i, i, i, i]
+    L.garnet_b200_gpt_oss_rms_norm.argtypes = [vp, vp, vp, i, i, c.c_float, vp]
+    L.garnet_b200_gpt_oss_rope.argtypes = [vp, vp, vp, vp, i, vp]
+    L.garnet_b200_gpt_oss_attention_workspace.argtypes = [vp, i, i, c.POINTER(sz)]
+    L.garnet_b200_gpt_oss_attention.argtypes = [vp, vp, vp, vp, sz, i, i, i, i, vp]
+    L.garnet_b200_gpt_oss_vocab_top1.argtypes = [vp, vp, i, i, i, vp]
+    L.garnet_b200_gpt_oss_decode_gemv.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, i, vp]
     L.garnet_b200_moe_workspace.argtypes = [vp, i, c.POINTER(sz)]
     L.garnet_b200_moe_create.argtypes = [vp, vp, vp, c.POINTER(vp)]
     L.garnet_b200_moe_run.argtypes = [vp, vp, vp, vp, sz, i, vp]

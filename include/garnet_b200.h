@@ -330,6 +330,48 @@ int garnet_b200_embedding_gather(const void* d_table, const int* d_ids, void* d_
 /* out[b] = index of the largest of logits[b, :vocab] (bf16), the lowest index among equals. */
 int garnet_b200_argmax_bf16(const void* d_logits, int* d_out, int batch, int vocab, unsigned flags, void* stream);
 
+/* ---- the rest of a gpt-oss decoder layer -----------------------------------------
+ * The operators around the MoE that the reference's plugin also carries (GptOssOptions kinds 0, 1,
+ * 5, 6, 7; plugins/gpt_oss/include/gpt_oss_kernels.h:8-46): RunGptOssRmsNorm, RunGptOssRope (YaRN),
+ * RunGptOssAttention (paged bf16 KV cache, learned sinks, sliding window), RunGptOssDecodeGemv and
+ * RunGptOssVocabTop1.  x and y are the reference's fp32 carrier (fp32 tensors holding bf16 values)
+ * unless stated. */
+typedef struct garnet_b200_gpt_oss_options {
+    int abi;               /* GARNET_B200_ABI */
+    int struct_size;       /* sizeof(garnet_b200_gpt_oss_options) */
+    int q_heads, kv_heads, head_dim;      /* gpt-oss-120b: 64, 8, 64 */
+    int layer;             /* selects the layer's slab of the KV cache */
+    int page_size;         /* positions per cache page (16) */
+    int window;            /* sliding window in positions, 0 = full attention */
+    int prefill;           /* 1: row t attends positions up to starts[b] + t; 0: up to lengths[b] */
+    float theta, factor, initial_context, beta_fast, beta_slow;   /* YaRN: 150000, 32, 4096, 32, 1 */
+} garnet_b200_gpt_oss_options;
+
+/* y = bf((bf(x) * rsqrt(mean(bf(x)^2) + epsilon)) * weight), rows of `hidden` (RunGptOssRmsNorm). */
+int garnet_b200_gpt_oss_rms_norm(const float* d_x, const float* d_weight, float* d_y, int rows, int hidden, float epsilon,
+                                 void* stream);
+/* YaRN rotary embedding of the q and k heads of packed rows [tokens, (q + 2 kv) * d]; the v part
+ * is copied (RunGptOssRope, gpt_oss_kernels.cu:78-99).  d_positions: int64 [tokens]. */
+int garnet_b200_gpt_oss_rope(const garnet_b200_gpt_oss_options* options, const float* d_x, const long long* d_positions, float* d_y,
+                             int tokens, void* stream);
+/* in[0..7] = qkv f32 [batch * tokens, (q + 2 kv) * d] (rotated), key cache, value cache (bf16
+ * [layers][physical pages][page size][kv heads][d]), page table int32 [batch, logical pages],
+ * lengths int32 [batch], starts int32 [batch], active int32 [batch], sinks f32 [q heads]: appends the
+ * rows' k and v at positions starts[b] + t, then y[row, head] = softmax over the visible window, with
+ * the head's sink in the denominator only (RunGptOssAttention, gpt_oss_kernels.cu:1012-1210).
+ * The workspace (zero-filled once by the caller) is needed at decode (tokens == 1, prefill == 0). */
+int garnet_b200_gpt_oss_attention_workspace(const garnet_b200_gpt_oss_options* options, int batch, int logical_pages, size_t* bytes);
+int garnet_b200_gpt_oss_attention(const garnet_b200_gpt_oss_options* options, const void* const* in, float* d_y, void* d_workspace,
+                                  size_t workspace_bytes, int batch, int tokens, int logical_pages, int physical_pages, void* stream);
+/* pairs[row] = (largest logit, float(rank * width + its index)), the lowest index among equals
+ * (RunGptOssVocabTop1: the 8-byte message of the sharded vocabulary). */
+int garnet_b200_gpt_oss_vocab_top1(const float* d_logits, float* d_pairs, int rows, int width, int rank, void* stream);
+/* y[row] = bf16(sum_c W[row', column_offset + c] * x[c]) for bf16 x, W, y; with q_heads > 0 row' walks
+ * this rank's half of the q, k and v rows of a packed q/k/v weight (RunGptOssDecodeGemv,
+ * plugins/gpt_oss/cuda/gpt_oss_gemv.cu:7-60). */
+int garnet_b200_gpt_oss_decode_gemv(const void* d_x, const void* d_weight, void* d_y, int rows, int columns, int weight_stride,
+                                    int column_offset, int q_heads, int kv_heads, int head_dim, int rank, void* stream);
+
 /* ---- gpt-oss MXFP4 mixture of experts (`gpt_oss_moe_mxfp4`) -------------------
  * Replaces the free functions below the TensorRT plugin:
  *   size_t GptOssMoeWorkspace(int tokens, const GptOssOptions&) and

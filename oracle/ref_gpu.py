@@ -31,6 +31,11 @@ def lib() -> ctypes.CDLL:
         L.ref_gpu_marlin_run.argtypes = [vp, vp, vp, vp, i, vp]
         L.ref_gpu_marlin_destroy.restype = None
         L.ref_gpu_marlin_destroy.argtypes = [vp]
+        L.ref_gpu_rms_norm.argtypes = [vp, vp, vp, i, i, f, i, vp]
+        L.ref_gpu_rope.argtypes = [vp, vp, vp, i, i, i, i, f, f, f, f, f, vp]
+        L.ref_gpu_attention.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, i, i, i, i, vp]
+        L.ref_gpu_vocab_top1.argtypes = [vp, vp, i, i, i, vp]
+        L.ref_gpu_decode_gemv.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, i, vp]
         _lib = L
     return _lib
 

@@ -60,4 +60,53 @@ int ref_gpu_marlin_run(void* handle, const void* const* in, float* y, void* work
 
 void ref_gpu_marlin_destroy(void* handle) { delete static_cast<Garnet::GptOssMarlin*>(handle); }
 
+// ---- the rest of the gpt-oss layer (gpt_oss_kernels.h:24-40)
+
+int ref_gpu_rms_norm(const float* x, const float* weight, float* y, int rows, int hidden, float epsilon, int threads, void* stream)
+{
+    return int(Garnet::RunGptOssRmsNorm(x, weight, y, rows, hidden, epsilon, threads, static_cast<cudaStream_t>(stream)));
+}
+
+static Garnet::GptOssOptions attention_options(int kind, int q_heads, int kv_heads, int head_dim, int layer, int page_size, int window,
+                                               int prefill, float theta, float factor, float initial_context, float beta_fast,
+                                               float beta_slow)
+{
+    Garnet::GptOssOptions o;
+    o.kind = kind;
+    o.qHeads = q_heads, o.kvHeads = kv_heads, o.headDim = head_dim;
+    o.layer = layer, o.pageSize = page_size, o.window = window, o.prefill = prefill;
+    o.theta = theta, o.factor = factor, o.initialContext = initial_context, o.betaFast = beta_fast, o.betaSlow = beta_slow;
+    return o;
+}
+
+int ref_gpu_rope(const float* x, const long long* positions, float* y, int tokens, int q_heads, int kv_heads, int head_dim, float theta,
+                 float factor, float initial_context, float beta_fast, float beta_slow, void* stream)
+{
+    const Garnet::GptOssOptions o = attention_options(0, q_heads, kv_heads, head_dim, 0, 16, 0, 0, theta, factor, initial_context,
+                                                      beta_fast, beta_slow);
+    return int(Garnet::RunGptOssRope(x, reinterpret_cast<const std::int64_t*>(positions), y, tokens, o, static_cast<cudaStream_t>(stream)));
+}
+
+// in[0..7] as RunGptOssAttention takes them; the workspace holds batch * q_heads * 64 * (2 + head_dim) floats at least.
+int ref_gpu_attention(const void* const* in, float* y, void* workspace, int batch, int tokens, int logical_pages, int physical_pages,
+                      int q_heads, int kv_heads, int head_dim, int layer, int page_size, int window, int prefill, void* stream)
+{
+    const Garnet::GptOssOptions o = attention_options(1, q_heads, kv_heads, head_dim, layer, page_size, window, prefill, 150000, 32, 4096,
+                                                      32, 1);
+    return int(Garnet::RunGptOssAttention(in, y, workspace, batch, tokens, logical_pages, physical_pages, o,
+                                          static_cast<cudaStream_t>(stream)));
+}
+
+int ref_gpu_vocab_top1(const float* logits, float* pairs, int rows, int width, int rank, void* stream)
+{
+    return int(Garnet::RunGptOssVocabTop1(logits, pairs, rows, width, rank, static_cast<cudaStream_t>(stream)));
+}
+
+int ref_gpu_decode_gemv(const void* x, const void* weight, void* y, int rows, int columns, int weight_stride, int column_offset,
+                        int q_heads, int kv_heads, int head_dim, int rank, void* stream)
+{
+    return int(Garnet::RunGptOssDecodeGemv(x, weight, y, rows, columns, weight_stride, column_offset, q_heads, kv_heads, head_dim, rank,
+                                           static_cast<cudaStream_t>(stream)));
+}
+
 }  // extern "C"
