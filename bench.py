@@ -357,6 +357,7 @@ def run_gpu(args):
     if world == 1 and not args.no_moe:
         torch.cuda.empty_cache()
         out["moe"] = bench_moe(torch, gb, peaks, args)
+        out["gpt_oss_layer_ops"] = bench_gpt_oss_layer_ops(torch, args)
         out["moe_ep"] = bench_moe_ep(torch, dist, gb, args, 0, 1)
     if world > 1 and not args.no_moe:
         del layers, head
@@ -405,6 +406,101 @@ def bench_decode_step(torch, peaks, args, context=2048):
             "what": "whole decode step in one CUDA graph: per layer one attention launch (head norms, RoPE, cache append, "
                     "split softmax and merge) and one list launch (o_proj + residual, norm + gate/up, SwiGLU + down + residual, "
                     "norm + next q/k/v); greedy token by arg-max"}
+
+
+def gpt_oss_layer_case(torch, context=2048, layers=4):
+    """Operands of the gpt-oss-120b attention block at decode (64 q heads, 8 kv heads of 64, pages of 16),
+    one sequence with `context` positions, caches of `layers` layers filled with random bf16."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(5)
+    logical = context // 16
+    keys = torch.randn(layers, logical, 16, 8, 64, device="cuda", generator=gen).to(torch.bfloat16)
+    values = torch.randn(layers, logical, 16, 8, 64, device="cuda", generator=gen).to(torch.bfloat16)
+    table = torch.randperm(logical, generator=torch.Generator().manual_seed(1)).reshape(1, logical).to(torch.int32).cuda()
+    qkv = torch.randn(1, 80 * 64, device="cuda", generator=gen).to(torch.bfloat16).float()
+    lens = torch.tensor([context], dtype=torch.int32, device="cuda")
+    starts = torch.tensor([context - 1], dtype=torch.int32, device="cuda")
+    active = torch.ones(1, dtype=torch.int32, device="cuda")
+    sinks = torch.randn(64, device="cuda", generator=gen)
+    w_qkv = (torch.randn(80 * 64, 2880, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    w_o = (torch.randn(2880, 4096, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    x = torch.randn(2880, device="cuda", generator=gen).to(torch.bfloat16)
+    a = torch.randn(4096, device="cuda", generator=gen).to(torch.bfloat16)
+    return dict(keys=keys, values=values, table=table, qkv=qkv, lens=lens, starts=starts, active=active, sinks=sinks, w_qkv=w_qkv,
+                w_o=w_o, x=x, a=a, logical=logical, layers=layers)
+
+
+def bench_gpt_oss_layer_ops(torch, args):
+    import garnet_b200 as gb
+    """The gpt-oss attention block at decode, one launch sequence per layer over `layers` different cache slabs
+    (so the KV rows come from HBM): attention with the cache append (full and with a 128-position window), and
+    the q/k/v and output GEMVs."""
+    from garnet_b200 import gpt_oss as go
+    c = gpt_oss_layer_case(torch)
+    out = {}
+    for name, window in (("attention_full_2048", 0), ("attention_window_128", 128)):
+        opts = [go.options(layer=l, window=window) for l in range(c["layers"])]
+        import ctypes
+        need = ctypes.c_size_t(0)
+        gb._lib.check(gb.lib().garnet_b200_gpt_oss_attention_workspace(ctypes.byref(opts[0]), 1, c["logical"], ctypes.byref(need)))
+        ws = torch.zeros(need.value, dtype=torch.uint8, device="cuda")
+
+        def body():
+            for o in opts:
+                go.attention(o, c["qkv"], c["keys"], c["values"], c["table"], c["lens"], c["starts"], c["active"], c["sinks"], 1, 1,
+                             c["logical"], workspace=ws)
+        out[name + "_us"] = round(time_graph(torch, body, args.steps, 3) * 1e3 / c["layers"], 2)
+
+    def gemvs():
+        go.decode_gemv(c["x"], c["w_qkv"], 80 * 64, 2880)
+        go.decode_gemv(c["a"], c["w_o"], 2880, 4096)
+    out["qkv_and_o_gemv_us"] = round(time_graph(torch, gemvs, args.steps, 3) * 1e3, 2)
+    return out
+
+
+def reference_gpu_layer_ops():
+    """The same operators through the reference's own kernels (RunGptOssAttention, RunGptOssDecodeGemv)."""
+    try:
+        import ctypes
+        import torch
+        from oracle import ref_gpu
+    except Exception:
+        return None
+    if not ref_gpu.available() or not torch.cuda.is_available():
+        return None
+    R = ref_gpu.lib()
+    c = gpt_oss_layer_case(torch)
+    s = torch.cuda.current_stream().cuda_stream
+    y = torch.empty(1, 4096, device="cuda")
+    ws = torch.zeros(64 * 64 * 66 * 4, dtype=torch.uint8, device="cuda")
+    ops = (ctypes.c_void_p * 8)(*[c[k].data_ptr() for k in ("qkv", "keys", "values", "table", "lens", "starts", "active", "sinks")])
+    out = {}
+
+    def timed(fn, per):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(20):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return round(a.elapsed_time(b) / 20 / per * 1e3, 2)
+
+    for name, window in (("attention_full_2048", 0), ("attention_window_128", 128)):
+        def body():
+            for l in range(c["layers"]):
+                R.ref_gpu_attention(ops, y.data_ptr(), ws.data_ptr(), 1, 1, c["logical"], c["logical"], 64, 8, 64, l, 16, window, 0, s)
+        out[name + "_us"] = timed(body, c["layers"])
+    yq = torch.empty(80 * 64, dtype=torch.bfloat16, device="cuda")
+    yo = torch.empty(2880, dtype=torch.bfloat16, device="cuda")
+
+    def gemvs():
+        R.ref_gpu_decode_gemv(c["x"].data_ptr(), c["w_qkv"].data_ptr(), yq.data_ptr(), 80 * 64, 2880, 2880, 0, 0, 0, 0, 0, s)
+        R.ref_gpu_decode_gemv(c["a"].data_ptr(), c["w_o"].data_ptr(), yo.data_ptr(), 2880, 4096, 4096, 0, 0, 0, 0, 0, s)
+    out["qkv_and_o_gemv_us"] = timed(gemvs, 1)
+    return out
 
 
 def bench_moe(torch, gb, peaks, args, token_counts=(1, 8, 32, 512, 4096), cpu_rows=True):
@@ -714,6 +810,7 @@ def run_reference(args):
         "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "moe_reference_gpu": moe_gpu,
+        "gpt_oss_layer_ops_reference_gpu": None if args.no_moe else reference_gpu_layer_ops(),
     }), flush=True)
 
 

@@ -167,7 +167,7 @@ __global__ void oss_attention_generic_kernel(const OssAttn p)
 
 constexpr int kOssSplit = 64;      // positions per split
 constexpr int kOssDim = 64;        // head dimension of the grouped decode kernel
-constexpr int kOssRowStride = 68;  // halves per staged row: 136 bytes, 16-byte aligned, two-way bank conflicts at most
+constexpr int kOssRowStride = 68;  // halves per staged row: 136 bytes (8-byte aligned), two-way bank conflicts at most
 
 // Decode (one new token per sequence), head_dim 64: CTA (kv head, split, sequence); warp g serves q head kv * group + g.
 __global__ void __launch_bounds__(512) oss_attention_decode_kernel(const OssAttn p)
@@ -190,7 +190,10 @@ __global__ void __launch_bounds__(512) oss_attention_decode_kernel(const OssAttn
         const size_t off = oss_cache_offset(p, b, s0 + r, kv);
         uint4 v = make_uint4(0, 0, 0, 0);
         if (off != SIZE_MAX) v = __ldcg(reinterpret_cast<const uint4*>((is_v ? p.values : p.keys) + off) + piece);
-        *reinterpret_cast<uint4*>((is_v ? vs : ks) + r * kOssRowStride + piece * 8) = v;
+        // a staged row starts on an 8-byte boundary (136-byte rows): two 8-byte stores
+        uint2* dst = reinterpret_cast<uint2*>((is_v ? vs : ks) + r * kOssRowStride + piece * 8);
+        dst[0] = make_uint2(v.x, v.y);
+        dst[1] = make_uint2(v.z, v.w);
     }
     {
         const float* qg = p.qkv + size_t(b) * packed + head * kOssDim;
