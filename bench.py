@@ -298,7 +298,7 @@ def run_gpu(args):
         out = {
             "metric": "w4a16_weight_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x int4 -> fp32 accumulate",
+            "scaling": "strong", "vs_baseline": None, "dtype": "int4 x bf16 (as 15-bit block fixed point) -> int32 per 128-group, fp32 across groups, bf16 out",
             "data": "synthetic",
             "config": {"workload": "qwen3_1p7b_w4a16_sweep: decode pass M=1 over 28x7 projections + lm_head (197 int4 group-128 linears)",
                        "bytes_per_step": step_bytes, "l2": "887 MB of weights per step > 126 MB L2; no flush needed",

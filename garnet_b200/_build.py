@@ -67,7 +67,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(pair):
         src, obj = pair
-        cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", src, "-o", obj]
+        extra = os.environ.get("GARNET_B200_NVCC_FLAGS", "").split()   # e.g. -DGB_STREAM_TRACE for a timing build
+        cmd = [nvcc, *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if verbose else []), "-c", src, "-o", obj]
         subprocess.check_call(cmd, env=env)
 
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(todo)))) as pool:

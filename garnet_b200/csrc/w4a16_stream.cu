@@ -69,6 +69,18 @@ __device__ __forceinline__ void st_relaxed_gpu_v2(void* p, uint32_t a, uint32_t 
 }
 __device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 
+// Timing build (-DGB_STREAM_TRACE, see GARNET_B200_NVCC_FLAGS in _build.py): CTA 7 records when each op of a
+// list reaches its stages (slots 0..6: arrive, rows free, staged, first and last weights ready, last part, last
+// strip written), read back with garnet_b200_w4a16_trace.  Absent from the normal build.
+#ifdef GB_STREAM_TRACE
+__device__ unsigned long long g_trace[512];
+#define GB_TRACE(op, slot) do { if (blockIdx.x == 7 && (op) < 63) g_trace[(op) * 8 + (slot)] = global_timer_ns(); } while (0)
+#define GB_TRACE_MAX(op, slot) do { if (blockIdx.x == 7 && (op) < 63) atomicMax(&g_trace[(op) * 8 + (slot)], global_timer_ns()); } while (0)
+#else
+#define GB_TRACE(op, slot) do {} while (0)
+#define GB_TRACE_MAX(op, slot) do {} while (0)
+#endif
+
 struct Ctl {
     volatile int abort_flag;
     int warps_done;   // consumer warps that have finished the list
@@ -304,16 +316,46 @@ __device__ __forceinline__ void lane_positions(bool from_packets, int chunk, int
 __device__ __forceinline__ float bf16_round_dev(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
 
 // One item's input values after the op's own activation: plain, or
-// bf16(silu(gate) * up) with gate = source[:, c] and up = source[:, k + c].
+// bf16(silu(gate) * up) with gate = source[:, c] and up = source[:, k + c].  The gate and up
+// values are requested together, so that an item costs one trip to L2 and not two.
 __device__ __forceinline__ bool load_item_values(const StreamParams& p, const StreamOp& op, Ctl* ctl, uint32_t run_tag, uint32_t hmask,
                                                  int m, int chunk, int hl, float (&v)[8], int (&col)[8])
 {
     const int k = op.chunks * 128;
     if (!(op.flags & kOpSwiGLU)) return load_lane_values(p, op, ctl, run_tag, hmask, m, chunk, hl, k, 0, v, col);
     float up[8];
-    int col_up[8];
-    if (!load_lane_values(p, op, ctl, run_tag, hmask, m, chunk, hl, 2 * k, 0, v, col)) return false;
-    if (!load_lane_values(p, op, ctl, run_tag, hmask, m, chunk, hl, 2 * k, k, up, col_up)) return false;
+    if (!op.xch_in) {
+        int col_up[8];
+        if (!load_lane_values(p, op, ctl, run_tag, hmask, m, chunk, hl, 2 * k, 0, v, col)) return false;
+        if (!load_lane_values(p, op, ctl, run_tag, hmask, m, chunk, hl, 2 * k, k, up, col_up)) return false;
+    } else {
+        const int sidx = hl >> 1, gh = hl & 1;
+        const uint2* gate_src = op.xch_in + (size_t(m) * op.in_strips + size_t(chunk) * 8 + sidx) * 8 + gh * 4;
+        const uint2* up_src = gate_src + size_t(k >> 4) * 8;
+        const unsigned long long t0 = global_timer_ns();
+        uint4 a, b, c, d;
+        for (;;) {
+            a = ld_relaxed_gpu_v4(gate_src);
+            b = ld_relaxed_gpu_v4(gate_src + 2);
+            c = ld_relaxed_gpu_v4(up_src);
+            d = ld_relaxed_gpu_v4(up_src + 2);
+            const bool have = a.y == run_tag && a.w == run_tag && b.y == run_tag && b.w == run_tag && c.y == run_tag &&
+                              c.w == run_tag && d.y == run_tag && d.w == run_tag;
+            if (__all_sync(hmask, have)) break;
+            const bool stop = ctl->abort_flag || global_timer_ns() - t0 > p.wait_limit_ns;
+            if (__any_sync(hmask, stop)) return false;
+        }
+        const uint32_t g4[4] = {a.x, a.z, b.x, b.z}, u4[4] = {c.x, c.z, d.x, d.z};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[j] = __uint_as_float(g4[j] << 16);
+            v[4 + j] = __uint_as_float(g4[j] & 0xffff0000u);
+            up[j] = __uint_as_float(u4[j] << 16);
+            up[4 + j] = __uint_as_float(u4[j] & 0xffff0000u);
+            col[j] = chunk * 128 + sidx * 16 + row_of_g(4 * gh + j);
+            col[4 + j] = col[j] + 8;
+        }
+    }
 #pragma unroll
     for (int el = 0; el < 8; ++el) {
         const float g = v[el];
@@ -504,7 +546,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
     const float* sxb = sx;
     bool ok = true;
     for (int i = 0; i < p.count; ++i) {
-        const StreamOp op = ops[i];
+        const StreamOp& op = ops[i];   // read where it lies (shared memory or the parameter bank): no registers held
         {
             const int buf = (op.flags & kOpBuffer1) ? 1 : 0;
             uint8_t* xb = xq + size_t(buf) * plan.xq_bytes;
@@ -517,7 +559,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
             if (!(op.flags & kOpSameX)) {
                 // Every warp has finished with the rows this buffer held; then all stage the new
                 // ones.  (A warp that gave up keeps meeting the others at these barriers.)
+                if (threadIdx.x == 0) GB_TRACE(i, 0);
                 named_barrier_sync(1, kConsumerThreads);
+                if (threadIdx.x == 0) GB_TRACE(i, 1);
                 if (kGlue && (op.flags & (kOpNorm | kOpSwiGLU))) {
                     // every thread takes part (the norm meets twice); one that has given up only keeps the meetings
                     if (!stage_rows_glue<MBLK>(p, op, plan, ctl, xb, const_cast<float*>(sxb), run_tag, threadIdx.x, lane) &&
@@ -528,6 +572,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                     if ((lane & 15) == 0) give_up(p, ctl, 3);
                 }
                 named_barrier_sync(1, kConsumerThreads);
+                if (threadIdx.x == 0) GB_TRACE(i, 2);
                 if (ctl->abort_flag) ok = false;
             }
         }
@@ -561,9 +606,31 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                     break;
                 }
             }
+            if (lane == 0 && local == 0) GB_TRACE(i, 3);
+            if (lane == 0 && local == ntask - 1) GB_TRACE(i, 6);
             const uint8_t* slot = ring + size_t(stage) * kSlotBytes;
             const int c_first = part * op.cpp;
             const int nch = min(op.cpp, op.chunks - c_first);
+            // The residual that the strip's writer will add is requested now: by the time the
+            // sums are complete it has arrived (only the warp that delivers the last part uses it).
+            const int strip = s0 + sl;
+            const int n_lo = strip * 16 + row_of_g(g), n_hi = n_lo + 8;
+            float res_lo[MBLK], res_hi[MBLK];
+            uint2 res_pk[MBLK];
+            if (kGlue && (op.flags & kOpResidual)) {
+#pragma unroll
+                for (int mb = 0; mb < MBLK; ++mb) {
+                    const int m = mb * 4 + t;
+                    res_lo[mb] = (m < p.m && n_lo < op.n) ? __bfloat162float(op.res[size_t(m) * op.ldy + n_lo]) : 0.f;
+                    res_hi[mb] = (m < p.m && n_hi < op.n) ? __bfloat162float(op.res[size_t(m) * op.ldy + n_hi]) : 0.f;
+                }
+            } else if (kGlue && (op.flags & kOpResidualXch)) {
+#pragma unroll
+                for (int mb = 0; mb < MBLK; ++mb) {
+                    const int m = mb * 4 + t;
+                    res_pk[mb] = m < p.m ? ld_relaxed_gpu_v2(op.res_xch + (size_t(m) * op.strips + strip) * 8 + g) : make_uint2(0, run_tag);
+                }
+            }
             // The fp32 sum over the chunks follows one fixed tree whatever the split into
             // parts: groups of four chunks G = (s0 + s1) + (s2 + s3), then the groups in
             // order.  pr[..][0] collects s0 + s1, pr[..][1] collects s2 + s3 of this part.
@@ -626,8 +693,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
             }
 
             // ---- the parts of a strip meet in shared memory
-            const int strip = s0 + sl;
-            const int n_lo = strip * 16 + row_of_g(g), n_hi = n_lo + 8;
             bool writer = op.parts == 1;
             if (op.parts > 1) {
                 int pbase = pslot - part;             // slot of the strip's first part
@@ -716,13 +781,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                     const int m = mb * 4 + t;
                     if (m < p.m) {
                         if (kGlue && (op.flags & kOpResidual)) {
-                            if (n_lo < op.n) acc[mb][0] = __fadd_rn(acc[mb][0], __bfloat162float(op.res[size_t(m) * op.ldy + n_lo]));
-                            if (n_hi < op.n) acc[mb][1] = __fadd_rn(acc[mb][1], __bfloat162float(op.res[size_t(m) * op.ldy + n_hi]));
+                            acc[mb][0] = __fadd_rn(acc[mb][0], res_lo[mb]);
+                            acc[mb][1] = __fadd_rn(acc[mb][1], res_hi[mb]);
                         } else if (kGlue && (op.flags & kOpResidualXch)) {
                             // the packet of (m, strip, g) holds exactly this lane's two columns
-                            const uint2* src = op.res_xch + (size_t(m) * op.strips + strip) * 8 + g;
-                            uint2 pk = ld_relaxed_gpu_v2(src);
+                            uint2 pk = res_pk[mb];
                             if (pk.y != run_tag) {
+                                const uint2* src = op.res_xch + (size_t(m) * op.strips + strip) * 8 + g;
                                 const unsigned long long t0 = global_timer_ns();
                                 while (pk.y != run_tag && !ctl->abort_flag && global_timer_ns() - t0 <= limit) pk = ld_relaxed_gpu_v2(src);
                                 if (pk.y != run_tag) give_up(p, ctl, 5);
@@ -741,6 +806,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                 }
             }
             __syncwarp();
+            if (lane == 0) GB_TRACE_MAX(i, writer ? 5 : 4);
             if (lane == 0) mbar_arrive(&empty[stage]);
             my_q = -1;
         }
@@ -1141,6 +1207,16 @@ int garnet_b200_w4a16_list_fault(garnet_b200_w4a16_list_t ll)
     LinearList* l = reinterpret_cast<LinearList*>(ll);
     return l && l->fault_host ? *l->fault_host : -1;
 }
+
+#ifdef GB_STREAM_TRACE
+int garnet_b200_w4a16_trace(unsigned long long* out, int n)
+{
+    GB_CUDA(cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * size_t(n)));
+    static unsigned long long zeros[512];
+    GB_CUDA(cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros)));
+    return 0;
+}
+#endif
 
 void garnet_b200_w4a16_list_destroy(garnet_b200_w4a16_list_t ll) { delete reinterpret_cast<LinearList*>(ll); }
 
