@@ -645,26 +645,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                 const uint4 u0 = *reinterpret_cast<const uint4*>(ck + lane * 16);
                 const uint4 u1 = *reinterpret_cast<const uint4*>(ck + 512 + lane * 16);
                 const uint32_t sc = *reinterpret_cast<const uint32_t*>(ck + 1024 + g * 4);
-                int acc_i[MBLK][4];
-#pragma unroll
-                for (int mb = 0; mb < MBLK; ++mb) acc_i[mb][0] = acc_i[mb][1] = acc_i[mb][2] = acc_i[mb][3] = 0;
-#pragma unroll
-                for (int tile = 0; tile < 2; ++tile) {
-                    const uint4 u = tile ? u1 : u0;
-                    uint4 xv[MBLK];
-#pragma unroll
-                    for (int mb = 0; mb < MBLK; ++mb)
-                        xv[mb] = *reinterpret_cast<const uint4*>(xcol[mb] + chunk * 128 + tile * 64);
-#pragma unroll
-                    for (int jj = 0; jj < 2; ++jj) {
-                        const uint32_t w_lo = jj ? u.z : u.x, w_hi = jj ? u.w : u.y;
-                        const uint32_t a0 = nib_to_s8x16(w_lo << 4), a1 = nib_to_s8x16(w_hi << 4);
-                        const uint32_t a2 = nib_to_s8x16(w_lo), a3 = nib_to_s8x16(w_hi);
-#pragma unroll
-                        for (int mb = 0; mb < MBLK; ++mb)
-                            imma_s8s8(acc_i[mb], a0, a1, a2, a3, jj ? xv[mb].z : xv[mb].x, jj ? xv[mb].w : xv[mb].y);
-                    }
-                }
                 float s_lo, s_hi;
                 if (op.flags & kOpScaleFp16) {
                     s_lo = __half2float(__ushort_as_half(uint16_t(sc & 0xffffu)));
@@ -673,11 +653,31 @@ __global__ void __launch_bounds__(kStreamThreads, 1) w4a16_list_kernel(const __g
                     s_lo = __uint_as_float(sc << 16);
                     s_hi = __uint_as_float(sc & 0xffff0000u);
                 }
+                // the chunk's 128 codes as signed bytes, once; then one block of four batch rows after the
+                // other (few registers live at a time: with several blocks in flight the kernel spilled)
+                uint32_t a[2][2][4];
+#pragma unroll
+                for (int tile = 0; tile < 2; ++tile) {
+                    const uint4 u = tile ? u1 : u0;
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {
+                        const uint32_t w_lo = jj ? u.z : u.x, w_hi = jj ? u.w : u.y;
+                        a[tile][jj][0] = nib_to_s8x16(w_lo << 4), a[tile][jj][1] = nib_to_s8x16(w_hi << 4);
+                        a[tile][jj][2] = nib_to_s8x16(w_lo), a[tile][jj][3] = nib_to_s8x16(w_hi);
+                    }
+                }
 #pragma unroll
                 for (int mb = 0; mb < MBLK; ++mb) {
+                    int acc_i[4] = {0, 0, 0, 0};
+#pragma unroll
+                    for (int tile = 0; tile < 2; ++tile) {
+                        const uint4 xv = *reinterpret_cast<const uint4*>(xcol[mb] + chunk * 128 + tile * 64);
+                        imma_s8s8(acc_i, a[tile][0][0], a[tile][0][1], a[tile][0][2], a[tile][0][3], xv.x, xv.y);
+                        imma_s8s8(acc_i, a[tile][1][0], a[tile][1][1], a[tile][1][2], a[tile][1][3], xv.z, xv.w);
+                    }
                     const float f = sxb[(chunk * MBLK + mb) * 4 + t];
-                    const int v0 = acc_i[mb][0] * 128 + acc_i[mb][1];   // hi and lo pieces of batch row 4*mb + t
-                    const int v1 = acc_i[mb][2] * 128 + acc_i[mb][3];
+                    const int v0 = acc_i[0] * 128 + acc_i[1];   // hi and lo pieces of batch row 4*mb + t
+                    const int v1 = acc_i[2] * 128 + acc_i[3];
                     // explicit roundings: no multiply-add contraction, so the bits do not depend on
                     // how the compiler arranges this loop
                     const float c_lo = __fmul_rn(__fmul_rn(float(v0), f), s_lo), c_hi = __fmul_rn(__fmul_rn(float(v1), f), s_hi);
