@@ -257,20 +257,26 @@ __device__ __forceinline__ void small_meta_body(const float* logits, const Small
     __shared__ int s_count[256], s_offset[257], s_task[257], s_tile[257];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int topk = mt.topk;
-    // ---- top-k: one warp per token (8 warps); the logits were written by other CTAs: read them from L2
+    // ---- top-k: one warp per token (8 warps); the logits were written by other CTAs: read them from L2,
+    // once (a lane keeps its up to eight logits in registers over the k rounds)
     if (warp < tokens) {
         const float* l = logits + size_t(warp) * experts;
+        float mine_v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) mine_v[u] = lane + 32 * u < experts ? __ldcg(&l[lane + 32 * u]) : -INFINITY;
+        unsigned taken = 0;   // bit u: this lane's u-th logit has been selected
         float top[8];
         int chosen[8];
-        for (int j = 0; j < topk; ++j) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (j >= topk) break;
             float best = -INFINITY;
             int arg = 0x7fffffff;
-            for (int e = lane; e < experts; e += 32) {
-                bool used = false;
-                for (int q = 0; q < j; ++q) used |= chosen[q] == e;
-                const float v = __ldcg(&l[e]);
-                if (!used && (arg == 0x7fffffff || v > best || (v == best && e < arg))) {
-                    best = v;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e = lane + 32 * u;
+                if (e < experts && !(taken & (1u << u)) && (arg == 0x7fffffff || mine_v[u] > best)) {   // ascending e: ties keep the lower
+                    best = mine_v[u];
                     arg = e;
                 }
             }
@@ -283,6 +289,7 @@ __device__ __forceinline__ void small_meta_body(const float* logits, const Small
                     arg = oa;
                 }
             }
+            if ((arg & 31) == lane) taken |= 1u << (arg >> 5);
             chosen[j] = arg;
             top[j] = best;
         }
@@ -382,10 +389,13 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
     for (int q = 0; q < 4; ++q)
 #pragma unroll
         for (int t = 0; t < kRouteTokens; ++t) acc[q][t] = 0.f;
+    // four steps of the hidden dimension at a time: their sixteen weight loads are in flight together (the
+    // loop is latency-bound: a thread has only a dozen steps)
+#pragma unroll 4
     for (int d = threadIdx.x; d < hidden; d += kRouteWarps * 32) {
         float wv[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) wv[q] = rw[size_t(min(e0 + q, experts - 1)) * hidden + d];
+        for (int q = 0; q < 4; ++q) wv[q] = __ldg(&rw[size_t(min(e0 + q, experts - 1)) * hidden + d]);
 #pragma unroll
         for (int t = 0; t < kRouteTokens; ++t) {
             if (t < tokens) {
