@@ -33,6 +33,18 @@ constexpr int kMxChunkBytes = 512 + 32;
 
 // ------------------------------------------------------------------ repack
 
+// Timing build (-DGB_MOE_TRACE): CTA 7 of each small-batch launch records global-timer stamps (router: slots
+// 0..15, gate/up: 16..47, down: 48..79, combine: 80..83), read back with garnet_b200_moe_trace.  Absent from the
+// normal build.
+#ifdef GB_MOE_TRACE
+__device__ unsigned long long g_moe_trace[96];
+#define GB_MTRACE(slot) do { if (blockIdx.x == 7) g_moe_trace[(slot)] = global_timer_ns(); } while (0)
+#define GB_MTRACE_ANY(slot) do { g_moe_trace[(slot)] = global_timer_ns(); } while (0)
+#else
+#define GB_MTRACE(slot) do {} while (0)
+#define GB_MTRACE_ANY(slot) do {} while (0)
+#endif
+
 // One thread per packed 32-bit word (moe_pack.h says where each comes from).
 __global__ void mx_repack_codes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, PackGeom geo,
                                        int interleaved)
@@ -254,7 +266,7 @@ struct SmallMeta {
 __device__ __forceinline__ void small_meta_body(const float* logits, const SmallMeta& mt, int tokens, int experts)
 {
     __shared__ int s_sel[8 * 8];
-    __shared__ int s_count[256], s_offset[257], s_task[257], s_tile[257];
+    __shared__ int s_count[256], s_ntask[256], s_ntile[256], s_offset[257], s_task[257], s_tile[257];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int topk = mt.topk;
     // ---- top-k: one warp per token (8 warps); the logits were written by other CTAs: read them from L2,
@@ -293,14 +305,21 @@ __device__ __forceinline__ void small_meta_body(const float* logits, const Small
             chosen[j] = arg;
             top[j] = best;
         }
-        if (lane == 0) {
-            float total = 0.f;
-            for (int j = 0; j < topk; ++j) total += expf(top[j] - top[0]);
-            for (int j = 0; j < topk; ++j) {
-                mt.selected[warp * topk + j] = chosen[j];
-                s_sel[warp * topk + j] = chosen[j];
-                mt.probs[warp * topk + j] = bf16_round_f(expf(top[j] - top[0]) / total);
-            }
+        // lane j holds the j-th pick; the sum runs over j = 0, 1, ... in that order
+        float my_top = -INFINITY;
+        int my_pick = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j < topk && lane == j) my_top = top[j], my_pick = chosen[j];
+        const float ex = lane < topk ? expf(my_top - top[0]) : 0.f;
+        float total = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j < topk) total += __shfl_sync(0xffffffffu, ex, j);
+        if (lane < topk) {
+            mt.selected[warp * topk + lane] = my_pick;
+            s_sel[warp * topk + lane] = my_pick;
+            mt.probs[warp * topk + lane] = bf16_round_f(ex / total);
         }
     }
     __syncthreads();
@@ -311,6 +330,9 @@ __device__ __forceinline__ void small_meta_body(const float* logits, const Small
     if (e < experts && expert_is_local(e, mt.sh))
         for (int i = 0; i < slots; ++i) mine += s_sel[i] == e;
     s_count[e] = e < experts ? mine : 0;
+    // tasks and row tiles of this expert: the divisions run once per thread, side by side, not in the scan below
+    s_ntask[e] = e < experts ? (mine + mt.rows_per_task - 1) / mt.rows_per_task : 0;
+    s_ntile[e] = (e < experts && mt.tile_rows) ? (mine + mt.tile_rows - 1) / mt.tile_rows : 0;
     if (e < experts) mt.counts[e] = mine;
     __syncthreads();
     // ---- exclusive prefix sums of rows, tasks and row tiles: warp 0, eight experts per lane
@@ -318,10 +340,9 @@ __device__ __forceinline__ void small_meta_body(const float* logits, const Small
         int off = 0, tk = 0, tp = 0;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-            const int c = s_count[lane * 8 + q];
-            off += c;
-            tk += (c + mt.rows_per_task - 1) / mt.rows_per_task;
-            if (mt.tile_rows) tp += (c + mt.tile_rows - 1) / mt.tile_rows;
+            off += s_count[lane * 8 + q];
+            tk += s_ntask[lane * 8 + q];
+            tp += s_ntile[lane * 8 + q];
         }
         int xo = off, xt = tk, xp = tp;   // inclusive scan over the lanes
 #pragma unroll
@@ -333,11 +354,11 @@ __device__ __forceinline__ void small_meta_body(const float* logits, const Small
         off = xo - off, tk = xt - tk, tp = xp - tp;   // exclusive start of this lane's eight experts
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-            const int idx = lane * 8 + q, c = s_count[idx];
+            const int idx = lane * 8 + q;
             s_offset[idx] = off, s_task[idx] = tk, s_tile[idx] = tp;
-            off += c;
-            tk += (c + mt.rows_per_task - 1) / mt.rows_per_task;
-            if (mt.tile_rows) tp += (c + mt.tile_rows - 1) / mt.tile_rows;
+            off += s_count[idx];
+            tk += s_ntask[idx];
+            tp += s_ntile[idx];
         }
         if (lane == 31) s_offset[256] = off, s_task[256] = tk, s_tile[256] = tp;
     }
@@ -361,98 +382,135 @@ __device__ __forceinline__ void small_meta_body(const float* logits, const Small
     }
 }
 
-// Router for at most 8 tokens (decode): latency matters, so the hidden dimension is
-// split over the 8 warps of a CTA and a CTA owns only 4 experts (E/4 CTAs); the
-// warps' partial sums meet in shared memory.  Same results contract as
-// moe_route_scores_kernel (fp32 accumulation, bf16-rounded logits); CTA 0 also
-// writes the fp16 copy of x.
+// Router for at most 8 tokens (decode).  Latency is everything here, so: one expert per CTA with the
+// hidden dimension split over the CTA's 256 threads (a thread's first twelve weights are requested
+// before the wait on the preceding kernel: the router weights are constants); x arrives with 16-byte
+// loads, all in flight together; the fp16 copy of x is written in slices by all CTAs.  Same results
+// contract as moe_route_scores_kernel (fp32 accumulation, bf16-rounded logits).
+constexpr int kSmallRouteSteps = 12;   // weights per thread held in registers (hidden <= 3072; a loop covers the rest)
 template <typename XT>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, const float* __restrict__ rb,
                        float* __restrict__ logits, __half* __restrict__ xh, int* __restrict__ xshift, int tokens,
                        int hidden, int experts, const SmallMeta mt)
 {
-    extern __shared__ float xs[];   // [kRouteTokens][hidden]; rows >= tokens are not used
-    __shared__ float part[kRouteWarps][4][kRouteTokens];
+    extern __shared__ __align__(16) float xs[];   // [tokens][hidden]
+    __shared__ float part[kRouteWarps][kRouteTokens];
     __shared__ float s_amax[kRouteWarps];
     __shared__ int s_last;
+    constexpr int kThreads = kRouteWarps * 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) GB_MTRACE(0);
+    const int e = blockIdx.x;
+    const float* wrow = rw + size_t(e) * hidden;
+    float wv[kSmallRouteSteps];
+#pragma unroll
+    for (int i = 0; i < kSmallRouteSteps; ++i) {
+        const int d = threadIdx.x + i * kThreads;
+        wv[i] = d < hidden ? __ldg(&wrow[d]) : 0.f;
+    }
+    const float bias = __ldg(&rb[e]);
     pdl_launch_dependents();
     pdl_wait();   // x comes from the kernel before this one
-    for (int t = 0; t < tokens; ++t)
-        for (int d = threadIdx.x; d < hidden; d += kRouteWarps * 32)
-            xs[t * hidden + d] = to_float(x[size_t(t) * hidden + d]);
-    __syncthreads();
-    const int e0 = blockIdx.x * 4;
-    float acc[4][kRouteTokens];
+    if (threadIdx.x == 0) GB_MTRACE(1);
+    {
+        constexpr int kPer = 16 / int(sizeof(XT));   // elements per 16-byte load
+        const int total = tokens * hidden;
+        if (hidden % kPer == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            const uint4* xv = reinterpret_cast<const uint4*>(x);
+            const int nvec = total / kPer;
+#pragma unroll 6
+            for (int v = threadIdx.x; v < nvec; v += kThreads) {
+                const uint4 u = __ldcg(&xv[v]);
+                float* dst = xs + size_t(v) * kPer;
+                if constexpr (sizeof(XT) == 4) {
+                    *reinterpret_cast<uint4*>(dst) = u;
+                } else {
+                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-    for (int q = 0; q < 4; ++q)
-#pragma unroll
-        for (int t = 0; t < kRouteTokens; ++t) acc[q][t] = 0.f;
-    // four steps of the hidden dimension at a time: their sixteen weight loads are in flight together (the
-    // loop is latency-bound: a thread has only a dozen steps)
-#pragma unroll 4
-    for (int d = threadIdx.x; d < hidden; d += kRouteWarps * 32) {
-        float wv[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) wv[q] = __ldg(&rw[size_t(min(e0 + q, experts - 1)) * hidden + d]);
-#pragma unroll
-        for (int t = 0; t < kRouteTokens; ++t) {
-            if (t < tokens) {
-                const float xv = xs[t * hidden + d];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) acc[q][t] = fmaf(xv, wv[q], acc[q][t]);
+                    for (int q = 0; q < 4; ++q) {
+                        dst[2 * q] = __uint_as_float(w[q] << 16);
+                        dst[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u);
+                    }
+                }
             }
+        } else {
+            for (int i = threadIdx.x; i < total; i += kThreads) xs[i] = to_float(x[i]);
         }
     }
-#pragma unroll
-    for (int q = 0; q < 4; ++q)
-#pragma unroll
-        for (int t = 0; t < kRouteTokens; ++t) {
-            if (t < tokens) {
-                const float v = warp_sum(acc[q][t]);
-                if (lane == 0) part[warp][q][t] = v;
-            }
-        }
     __syncthreads();
-    if (threadIdx.x < 4 * kRouteTokens) {
-        const int q = threadIdx.x / kRouteTokens, t = threadIdx.x % kRouteTokens;
-        if (e0 + q < experts && t < tokens) {
-            float v = 0.f;
+    if (threadIdx.x == 0) GB_MTRACE(2);
+    float acc[kRouteTokens];
 #pragma unroll
-            for (int w = 0; w < kRouteWarps; ++w) v += part[w][q][t];
-            logits[size_t(t) * experts + e0 + q] = bf16_round_f(v + rb[e0 + q]);
+    for (int t = 0; t < kRouteTokens; ++t) acc[t] = 0.f;
+#pragma unroll
+    for (int i = 0; i < kSmallRouteSteps; ++i) {
+        const int d = threadIdx.x + i * kThreads;
+        if (d < hidden) {
+#pragma unroll
+            for (int t = 0; t < kRouteTokens; ++t)
+                if (t < tokens) acc[t] = fmaf(xs[t * hidden + d], wv[i], acc[t]);
         }
     }
-    // fp16 copy of token t by CTA t (mod the grid)
-    for (int t = blockIdx.x; xh && t < tokens; t += gridDim.x) {
-        float amax = 0.f;
-        for (int d = threadIdx.x; d < hidden; d += kRouteWarps * 32)
-            amax = fmaxf(amax, fabsf(bf16_round_f(xs[t * hidden + d])));
+    for (int d = threadIdx.x + kSmallRouteSteps * kThreads; d < hidden; d += kThreads) {
+        const float w = __ldg(&wrow[d]);
 #pragma unroll
-        for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        __syncthreads();
-        if (lane == 0) s_amax[warp] = amax;
-        __syncthreads();
+        for (int t = 0; t < kRouteTokens; ++t)
+            if (t < tokens) acc[t] = fmaf(xs[t * hidden + d], w, acc[t]);
+    }
 #pragma unroll
-        for (int w = 0; w < kRouteWarps; ++w) amax = fmaxf(amax, s_amax[w]);
-        int shift = 0;
-        if (amax > 0.f && isfinite(amax)) shift = int((__float_as_uint(amax) >> 23) & 0xff) - 127 - 13;
-        shift = max(-100, min(100, shift));
-        const float scale = __uint_as_float(uint32_t(127 - shift) << 23);
-        for (int d = threadIdx.x; d < hidden; d += kRouteWarps * 32)
-            xh[size_t(t) * hidden + d] = __float2half_rn(bf16_round_f(xs[t * hidden + d]) * scale);
-        if (threadIdx.x == 0) xshift[t] = shift;
+    for (int t = 0; t < kRouteTokens; ++t) {
+        if (t < tokens) {
+            const float v = warp_sum(acc[t]);
+            if (lane == 0) part[warp][t] = v;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) GB_MTRACE(3);
+    if (threadIdx.x < tokens) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kRouteWarps; ++w) v += part[w][threadIdx.x];
+        logits[size_t(threadIdx.x) * experts + e] = bf16_round_f(v + bias);
+    }
+    // fp16 copy of x: token t's row in `slices` pieces, piece (t, s) by CTA t * slices + s (mod the grid)
+    if (xh) {
+        const int slices = max(1, int(gridDim.x) / tokens);
+        const int len = ((hidden + slices - 1) / slices + 7) & ~7;
+        for (int u = blockIdx.x; u < tokens * slices; u += gridDim.x) {
+            const int t = u / slices, sl = u % slices;
+            float amax = 0.f;
+            for (int d = threadIdx.x; d < hidden; d += kThreads) amax = fmaxf(amax, fabsf(bf16_round_f(xs[t * hidden + d])));
+#pragma unroll
+            for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            __syncthreads();
+            if (lane == 0) s_amax[warp] = amax;
+            __syncthreads();
+#pragma unroll
+            for (int w = 0; w < kRouteWarps; ++w) amax = fmaxf(amax, s_amax[w]);
+            int shift = 0;
+            if (amax > 0.f && isfinite(amax)) shift = int((__float_as_uint(amax) >> 23) & 0xff) - 127 - 13;
+            shift = max(-100, min(100, shift));
+            const float scale = __uint_as_float(uint32_t(127 - shift) << 23);
+            const int d1 = min(hidden, (sl + 1) * len);
+            for (int d = sl * len + threadIdx.x; d < d1; d += kThreads)
+                xh[size_t(t) * hidden + d] = __float2half_rn(bf16_round_f(xs[t * hidden + d]) * scale);
+            if (sl == 0 && threadIdx.x == 0) xshift[t] = shift;
+        }
     }
     if (!mt.done) return;
+    if (threadIdx.x == 0) GB_MTRACE(4);
     // the CTA that finishes last has every logit in reach and does the call's bookkeeping
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) s_last = atomicAdd(mt.done, 1u) == gridDim.x - 1;
     __syncthreads();
+    if (threadIdx.x == 0) GB_MTRACE(5);
     if (!s_last) return;
     __threadfence();
+    if (threadIdx.x == 0) GB_MTRACE_ANY(6);
     small_meta_body(logits, mt, tokens, experts);
+    if (threadIdx.x == 0) GB_MTRACE_ANY(7);
     if (threadIdx.x == 0) *mt.done = 0;   // for the next call
 }
 
@@ -631,11 +689,16 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
 
 // ------------------------------------------------- streaming expert kernel
 
+
 constexpr int kMoeWarps = 8;                       // consumer warps; one extra warp produces
-constexpr int kMoeStages = 4;
+#ifndef GB_MOE_STAGES
+#define GB_MOE_STAGES 5
+#endif
+constexpr int kMoeStages = GB_MOE_STAGES;
 constexpr int kMoeSegChunks = 2 * kMoeWarps;       // 16 chunks = 1024 columns per segment
 constexpr int kMoeSegBytes = kMoeSegChunks * kMxChunkBytes;
 constexpr int kMoeRows = 8;                        // slots per task (one MMA N-tile)
+constexpr int kMoeListCache = 32;                  // leading task and slot-order entries a CTA keeps in shared memory
 
 struct MoeStreamParams {
     const uint8_t* packed;      // [experts_local][matrix]
@@ -654,6 +717,8 @@ struct MoeStreamParams {
     int expert_base, expert_div;   // stored expert = (e - expert_base) / expert_div
     int bias_by_global;            // bias rows are indexed by the global expert id
     int tasks_early;               // the task list was complete before this grid could start (see kernel)
+    int slots;                     // entries of `sorted` (tokens * topk)
+    int tasks_cap;                 // entries the task list has room for
     float limit;
     size_t matrix_bytes;
 };
@@ -697,7 +762,9 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
 
     uint64_t* xbar = empty + kMoeStages;   // completion of a task's row copies
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    [[maybe_unused]] constexpr int kTr = kUp ? 16 : 48;   // first trace slot of this launch (timing build)
     if (threadIdx.x == 0) {
+        GB_MTRACE(kTr + 0);
         for (int s = 0; s < kMoeStages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kMoeWarps);
@@ -713,32 +780,62 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
     // Only its consumers, which read gate/up's activations, wait.
     if (!p.tasks_early) pdl_wait();
     pdl_launch_dependents();
+    if (threadIdx.x == 0) GB_MTRACE(kTr + 1);
 
-    const int ntasks = __ldcg(p.ntasks);
+    // The first entries of the task list and of the slot order, and the task count, in one round trip to L2
+    // (three warps load side by side); a decode-sized call never needs more than these.
+    __shared__ int4 s_tasks[kMoeListCache];
+    __shared__ int s_sorted[kMoeListCache];
+    __shared__ int s_ntasks;
+    if (threadIdx.x < kMoeListCache) {
+        if (int(threadIdx.x) < p.tasks_cap) s_tasks[threadIdx.x] = __ldcg(&p.tasks[threadIdx.x]);
+    } else if (threadIdx.x < 2 * kMoeListCache) {
+        const int i = threadIdx.x - kMoeListCache;
+        if (i < p.slots) s_sorted[i] = __ldcg(&p.sorted[i]);
+    } else if (threadIdx.x == 2 * kMoeListCache) {
+        s_ntasks = __ldcg(p.ntasks);
+    }
+    __syncthreads();
+    const int ntasks = s_ntasks;
     const long long total = (long long)ntasks * p.strips;
     const long long i0 = total * blockIdx.x / gridDim.x, i1 = total * (blockIdx.x + 1) / gridDim.x;
     const int nseg = (p.chunks + kMoeSegChunks - 1) / kMoeSegChunks;
     const size_t strip_bytes = size_t(p.chunks) * kMxChunkBytes;
+    const int task0 = int(i0 / p.strips), strip0 = int(i0 % p.strips);
 
     if (warp == kMoeWarps) {
         if (lane == 0) {
             long long n = 0;
+            int task = task0, strip = strip0, s = 0, round = 0, cur = -1;
+            const uint8_t* matrix = p.packed;
             for (long long it = i0; it < i1; ++it) {
-                const int task = int(it / p.strips), strip = int(it % p.strips);
-                const int e = (__ldcg(&p.tasks[task]).x - p.expert_base) / p.expert_div;
-                const uint8_t* src = p.packed + size_t(e) * p.matrix_bytes + size_t(strip) * strip_bytes;
+                if (task != cur) {
+                    const int ex = task < kMoeListCache ? s_tasks[task].x : __ldcg(&p.tasks[task]).x;
+                    matrix = p.packed + size_t((ex - p.expert_base) / p.expert_div) * p.matrix_bytes;
+                    cur = task;
+                }
+                const uint8_t* src = matrix + size_t(strip) * strip_bytes;
+                if (++strip == p.strips) strip = 0, ++task;
                 for (int seg = 0; seg < nseg; ++seg, ++n) {
-                    const int s = int(n % kMoeStages);
-                    if (n >= kMoeStages && !mbar_wait(&empty[s], uint32_t((n / kMoeStages) - 1) & 1)) {
+#ifdef GB_MOE_TRACE
+                    const long long tw0 = clock64();
+#endif
+                    if (round && !mbar_wait(&empty[s], uint32_t(round - 1) & 1)) {
                         atomicExch(p.fault, 1);
                         return;
                     }
+#ifdef GB_MOE_TRACE
+                    if (blockIdx.x == 7) g_moe_trace[kUp ? 85 : 87] += (unsigned long long)(clock64() - tw0);
+#endif
                     const int nch = min(kMoeSegChunks, p.chunks - seg * kMoeSegChunks);
                     const uint32_t bytes = uint32_t(nch) * kMxChunkBytes;
                     mbar_expect_tx(&full[s], bytes);
                     bulk_g2s(ring + size_t(s) * kMoeSegBytes, src + size_t(seg) * kMoeSegBytes, bytes, &full[s]);
+                    if (n == 0) GB_MTRACE(kTr + 2);
+                    if (++s == kMoeStages) s = 0, ++round;
                 }
             }
+            GB_MTRACE(kTr + 3);
         }
         return;
     }
@@ -747,7 +844,9 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
     // row copies never write the padding behind column K.
     for (int i = threadIdx.x; i < (kMoeRows + 1) * (plan.x_stride / 16); i += kMoeWarps * 32)
         *reinterpret_cast<uint4*>(xs + size_t(i) * 16) = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) GB_MTRACE(kTr + 4);
     if (p.tasks_early) pdl_wait();   // the activations come from the launch before this one
+    if (threadIdx.x == 0) GB_MTRACE(kTr + 5);
 
     const int g = lane >> 2, t = lane & 3;
     const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -757,21 +856,23 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
     bool ok = true;
     int s = 0, phase = 0, parity = 0, xphase = 0;
 
+    int task = task0, strip = strip0 - 1;
     for (long long it = i0; it < i1; ++it) {
-        const int task = int(it / p.strips), strip = int(it % p.strips);
+        if (++strip == p.strips) strip = 0, ++task;
         if (task != cur_task) {
             // ---- new task: stage its rows, one bulk copy per row (one round trip to L2
             // however long the rows are).  All consumers have left the previous x tile.
             fence_proxy_async_smem();
             named_barrier_sync(1, kMoeWarps * 32);
-            const int4 tk = __ldcg(&p.tasks[task]);
+            const int4 tk = task < kMoeListCache ? s_tasks[task] : __ldcg(&p.tasks[task]);
             task_expert = tk.x;
             task_rows = tk.z;
             if (threadIdx.x == 0) mbar_expect_tx(xbar, uint32_t(task_rows) * uint32_t(p.k) * 2u);
             if (threadIdx.x < kMoeRows) {
                 int slot = -1, shift = 0;
                 if (int(threadIdx.x) < task_rows) {
-                    slot = __ldcg(&p.sorted[tk.y + threadIdx.x]);
+                    const int at = tk.y + int(threadIdx.x);
+                    slot = at < kMoeListCache ? s_sorted[at] : __ldcg(&p.sorted[at]);
                     const size_t src_row = kUp ? size_t(slot / p.topk) : size_t(slot);
                     bulk_g2s(xs + size_t(threadIdx.x) * plan.x_stride, p.act_in + src_row * p.k, uint32_t(p.k) * 2u,
                              xbar);
@@ -786,15 +887,38 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
             }
             xphase ^= 1;
             named_barrier_sync(1, kMoeWarps * 32);
+            if (threadIdx.x == 0 && it == i0) GB_MTRACE(kTr + 6);
             cur_task = task;
             xrow = xs + size_t(g < task_rows ? g : kMoeRows) * plan.x_stride + t * 16;
         }
+        // this strip's bias values are requested now and used in the epilogue
+        const int ebias = p.bias_by_global ? task_expert : (task_expert - p.expert_base) / p.expert_div;
+        float bias0 = 0.f, bias1 = 0.f;
+        if (kUp) {
+            if (threadIdx.x < 64) {
+                const int i = strip * 8 + row_of_g((threadIdx.x & 31) >> 2);
+                if (2 * i + 1 < p.rows) {
+                    const float* b = p.bias + size_t(ebias) * p.rows + 2 * i;
+                    bias0 = __ldg(b), bias1 = __ldg(b + 1);
+                }
+            }
+        } else if (threadIdx.x < 128) {
+            const int d = strip * 16 + row_of_g((threadIdx.x & 31) >> 2) + 8 * (threadIdx.x >> 6);
+            if (d < p.rows) bias0 = __ldg(&p.bias[size_t(ebias) * p.rows + d]);
+        }
         for (int seg = 0; seg < nseg; ++seg) {
+#ifdef GB_MOE_TRACE
+            const long long tw0 = clock64();
+#endif
             if (ok && !mbar_wait(&full[s], phase)) {
                 atomicExch(p.fault, 2);
                 ok = false;
             }
+#ifdef GB_MOE_TRACE
+            if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 84 : 86] += (unsigned long long)(clock64() - tw0);
+#endif
             const int nch = min(kMoeSegChunks, p.chunks - seg * kMoeSegChunks);
+            if (threadIdx.x == 0 && it == i0 && seg == 0) GB_MTRACE(kTr + 7);
             if (ok) {
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
@@ -857,7 +981,6 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
             acc[q] = 0.f;
         }
         named_barrier_sync(2, kMoeWarps * 32);
-        const int ebias = p.bias_by_global ? task_expert : (task_expert - p.expert_base) / p.expert_div;
         if (kUp) {
             // 64 outputs: (lane l, slot parity): gate from q = par, up from q = par + 2
             if (threadIdx.x < 64) {
@@ -872,9 +995,8 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
                 const int i = strip * 8 + row_of_g(l >> 2);          // intermediate channel
                 if (m < task_rows && 2 * i + 1 < p.rows) {
                     const float sc2 = __uint_as_float(uint32_t(127 + row_shift[m]) << 23);   // 2^shift
-                    const float* b = p.bias + size_t(ebias) * p.rows + 2 * i;
-                    gate = fminf(bf16_round_f(bf16_round_f(gate * sc2) + b[0]), p.limit);
-                    up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(up * sc2) + b[1])));
+                    gate = fminf(bf16_round_f(bf16_round_f(gate * sc2) + bias0), p.limit);
+                    up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(up * sc2) + bias1)));
                     const float sig = bf16_round_f(1.f / (1.f + expf(-bf16_round_f(1.702f * gate))));
                     const float glu = bf16_round_f(gate * sig);
                     p.act_out[size_t(row_slot[m]) * (p.rows / 2) + i] = __float2half_rn(bf16_round_f(glu * bf16_round_f(up + 1.f)));
@@ -889,11 +1011,12 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
                 const int m = 2 * (l & 3) + (q & 1);
                 const int d = strip * 16 + row_of_g(l >> 2) + 8 * (q >> 1);
                 if (m < task_rows && d < p.rows)
-                    p.vals_out[size_t(row_slot[m]) * p.rows + d] =
-                        bf16_round_f(bf16_round_f(v) + p.bias[size_t(ebias) * p.rows + d]);
+                    p.vals_out[size_t(row_slot[m]) * p.rows + d] = bf16_round_f(bf16_round_f(v) + bias0);
             }
         }
+        if (threadIdx.x == 0 && it - i0 < 20) GB_MTRACE(kTr + 8 + int(it - i0));
     }
+    if (threadIdx.x == 0) GB_MTRACE(kTr + 31);
     // after a give-up the copies already issued may still land: give each stage a short moment (the fault is
     // recorded already, nothing is read any more) before the CTA's shared memory is released
     if (!ok)
@@ -908,8 +1031,10 @@ __global__ void moe_combine_kernel(const float* __restrict__ vals, const float* 
                                    const int* __restrict__ selected, YT* __restrict__ y, int tokens, int hidden,
                                    int topk, MoeShard sh, int round_output)
 {
+    if (threadIdx.x == 0) GB_MTRACE(80);
     pdl_launch_dependents();
     pdl_wait();   // the per-slot values come from the kernel before this one
+    if (threadIdx.x == 0) GB_MTRACE(81);
     const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= size_t(tokens) * hidden) return;
     const int token = int(idx / hidden), d = int(idx % hidden);
@@ -924,6 +1049,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ vals, const float* 
         y[idx] = r;
     else
         y[idx] = __float2bfloat16_rn(r);
+    if (threadIdx.x == 0) GB_MTRACE(82);
 }
 
 // ------------------------------------------------------------------ handle
@@ -1011,7 +1137,7 @@ int moe_resolve_options(const garnet_b200_moe_options* in, garnet_b200_moe_optio
         o.tp_rank = 0;
         o.tp_weights_sharded = 0;
     }
-    if (size_t(moe_smem_plan(std::max(o.hidden, o.intermediate)).total) > kMaxDynamicSmem)
+    if (size_t(moe_smem_plan(std::max(o.hidden, o.intermediate)).total) > kMaxDynamicSmem - 1024)
         return fail(GARNET_B200_NOT_SUPPORTED, "moe: hidden/intermediate too large for the streaming kernel");
     *eff = o;
     return GARNET_B200_OK;
@@ -1055,7 +1181,7 @@ template <bool U, bool C>
 static cudaError_t set_moe_attr()
 {
     return cudaFuncSetAttribute(moe_stream_kernel<U, C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                int(kMaxDynamicSmem));
+                                int(kMaxDynamicSmem - 1024));   // the kernel also has under 1 KB of static shared memory
 }
 
 // weights[0..7] = in[1..8] of the reference operand list (gpt_oss_lowering.cpp:309-312):
@@ -1308,7 +1434,7 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
         // many tokens, and no consumer of the fp16 row copies: tensor-core router
         if (int rc = route_mma(x, logits, route_partial, tokens, stream)) return rc;
     } else if (tokens <= kRouteTokens) {
-        const unsigned ctas = unsigned((opt.experts + 3) / 4);
+        const unsigned ctas = unsigned(opt.experts);   // one expert per CTA
         const size_t small_smem = size_t(tokens) * opt.hidden * sizeof(float);
         if (opt.io_dtype == GARNET_B200_FP32)
             GB_CUDA(launch_pdl(moe_route_small_kernel<float>, dim3(ctas), dim3(kRouteWarps * 32), small_smem, stream, true,
@@ -1366,9 +1492,11 @@ int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStrea
     p.bias_by_global = (!opt.expert_weights_sharded && sh.world > 1) ? 1 : 0;
     // The down launch always follows the gate/up launch of the same call directly.
     p.tasks_early = up ? 0 : 1;
+    p.slots = tokens * topk;
+    p.tasks_cap = p.slots / kMoeRows + opt.experts + 1;   // as sized in moe_workspace_plan
 
     const size_t smem = size_t(moe_smem_plan(geo.cols).total);
-    const int ctas_per_sm = std::max(1, std::min(2, int(kMaxDynamicSmem / (smem + 1024))));
+    const int ctas_per_sm = std::max(1, std::min(2, int(kMaxDynamicSmem / (smem + 2048))));
     // upper bound of (task, strip) items: every slot its own task
     const long long max_items = (long long)tokens * topk * geo.strips;
     cudaLaunchConfig_t cfg = {};
@@ -1452,8 +1580,19 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
         if (int rc = launch_mx(true, w, x, 0, tokens, slots, opt.top_k, stream)) return rc;
         if (int rc = launch_mx(false, w, x, 0, tokens, slots, opt.top_k, stream)) return rc;
     } else {
+#ifdef GB_MOE_PROBE
+        // timing build only: leave launches out (the results are then meaningless) to read each one's share of a call
+        static const int probe_skip = getenv("GB_MOE_SKIP") ? atoi(getenv("GB_MOE_SKIP")) : 0;
+        if (!(probe_skip & 2))
+#endif
         if (int rc = launch_stream(true, w, tokens, stream)) return rc;
+#ifdef GB_MOE_PROBE
+        if (!(probe_skip & 4))
+#endif
         if (int rc = launch_stream(false, w, tokens, stream)) return rc;
+#ifdef GB_MOE_PROBE
+        if (probe_skip & 8) return GARNET_B200_OK;
+#endif
     }
     const size_t n = size_t(tokens) * opt.hidden;
     const int round_output = partial_output() ? 0 : 1;
@@ -1832,5 +1971,15 @@ int garnet_b200_moe_fault(garnet_b200_moe_t hh)
 }
 
 void garnet_b200_moe_destroy(garnet_b200_moe_t hh) { delete reinterpret_cast<Moe*>(hh); }
+
+#ifdef GB_MOE_TRACE
+int garnet_b200_moe_trace(unsigned long long* out, int n)
+{
+    GB_CUDA(cudaMemcpyFromSymbol(out, g_moe_trace, sizeof(unsigned long long) * size_t(n)));
+    static unsigned long long zeros[96];
+    GB_CUDA(cudaMemcpyToSymbol(g_moe_trace, zeros, sizeof(zeros)));
+    return 0;
+}
+#endif
 
 }  // extern "C"
