@@ -690,12 +690,12 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
 // ------------------------------------------------- streaming expert kernel
 
 
-constexpr int kMoeWarps = 8;                       // consumer warps; one extra warp produces
+constexpr int kMoeWarps = 8;                       // warps per CTA; each streams its own strips through its own ring
 #ifndef GB_MOE_STAGES
-#define GB_MOE_STAGES 5
+#define GB_MOE_STAGES 4
 #endif
-constexpr int kMoeStages = GB_MOE_STAGES;
-constexpr int kMoeSegChunks = 2 * kMoeWarps;       // 16 chunks = 1024 columns per segment
+constexpr int kMoeStages = GB_MOE_STAGES;          // ring slots per warp
+constexpr int kMoeSegChunks = 5;                   // chunks per bulk copy (a gpt-oss strip is 45 chunks = 9 copies)
 constexpr int kMoeSegBytes = kMoeSegChunks * kMxChunkBytes;
 constexpr int kMoeRows = 8;                        // slots per task (one MMA N-tile)
 constexpr int kMoeListCache = 32;                  // leading task and slot-order entries a CTA keeps in shared memory
@@ -724,60 +724,83 @@ struct MoeStreamParams {
 };
 
 struct MoeSmem {
-    int ring, red, bars, meta, xs, total, x_stride;
+    int ring, bars, total;
 };
-__host__ __device__ inline MoeSmem moe_smem_plan(int k)
+__host__ __device__ inline MoeSmem moe_smem_plan()
 {
     MoeSmem p;
-    p.x_stride = k * 2 + 64 + ((k * 2) % 128 == 0 ? 0 : 64);   // keep (stride mod 128) == 64
     p.ring = 0;
-    p.red = p.ring + kMoeStages * kMoeSegBytes;
-    p.bars = p.red + 2 * kMoeWarps * 128 * 4;
-    p.meta = p.bars + 2 * kMoeStages * 8 + 8;        // row slot ids and shifts
-    p.xs = (p.meta + 2 * kMoeRows * 4 + 127) & ~127;
-    p.total = p.xs + (kMoeRows + 1) * p.x_stride;
+    p.bars = kMoeWarps * kMoeStages * kMoeSegBytes;
+    p.total = p.bars + kMoeWarps * kMoeStages * 8;
     return p;
 }
 
-// Persistent CTAs over the flattened list of (task, strip) items; a task is up to
-// 8 routed slots of one expert.  The producer warp streams each strip of that
-// expert's matrix (codes and scales together) in 16-chunk segments; the 8
-// consumer warps split a segment along K, convert e2m1 pairs to fp16 pairs with
-// one instruction each, and run m16n8k16 fp16 MMAs whose N dimension is the
-// task's slots.  Each 32-column group's fp32 partial sum is scaled by its e8m0
-// factor.  kUp: epilogue = bias + clamped SwiGLU -> activation (bf16-valued,
-// stored as fp16); else bias -> per-slot values for the combine.
+// m16n8k16 fp16 MMA, fp32 accumulation, as a plain (not volatile) statement: the compiler may interleave the
+// independent MMAs of neighbouring column groups and chunks.
+__device__ __forceinline__ void moe_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1, const float (&c)[4])
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+// One chunk (16 rows x 64 columns: 512 bytes of codes, 32 scale bytes) times the task's slots.  xa/xb: this lane's
+// activations of column groups 0 and 1.  acc[0..1]: strip row R(g), slots 2t and 2t+1; acc[2..3]: strip row R(g)+8.
+template <bool kCareful>
+__device__ __forceinline__ void moe_chunk_math(const uint8_t* st, int lane, int g, const uint4& xa, const uint4& xb,
+                                               float (&acc)[4])
+{
+    const uint4 u = *reinterpret_cast<const uint4*>(st + lane * 16);
+    const uint32_t sc = *reinterpret_cast<const uint32_t*>(st + 512 + g * 4);
+    const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+    float t0[4], t1[4];
+    // group 0: octets 0..3 (words x = row R, y = row R+8); group 1: octets 4..7 (words z, w)
+    moe_mma(t0, e2m1x2_to_f16x2(u.x, 0), e2m1x2_to_f16x2(u.y, 0), e2m1x2_to_f16x2(u.x, 1), e2m1x2_to_f16x2(u.y, 1), xa.x, xa.y, zero4);
+    moe_mma(t1, e2m1x2_to_f16x2(u.z, 0), e2m1x2_to_f16x2(u.w, 0), e2m1x2_to_f16x2(u.z, 1), e2m1x2_to_f16x2(u.w, 1), xb.x, xb.y, zero4);
+    moe_mma(t0, e2m1x2_to_f16x2(u.x, 2), e2m1x2_to_f16x2(u.y, 2), e2m1x2_to_f16x2(u.x, 3), e2m1x2_to_f16x2(u.y, 3), xa.z, xa.w, t0);
+    moe_mma(t1, e2m1x2_to_f16x2(u.z, 2), e2m1x2_to_f16x2(u.w, 2), e2m1x2_to_f16x2(u.z, 3), e2m1x2_to_f16x2(u.w, 3), xb.z, xb.w, t1);
+    const float f0_lo = e8m0_to_float<kCareful>(sc & 0xff), f0_hi = e8m0_to_float<kCareful>((sc >> 8) & 0xff);
+    const float f1_lo = e8m0_to_float<kCareful>((sc >> 16) & 0xff), f1_hi = e8m0_to_float<kCareful>(sc >> 24);
+    acc[0] = fmaf(t0[0], f0_lo, acc[0]);
+    acc[1] = fmaf(t0[1], f0_lo, acc[1]);
+    acc[2] = fmaf(t0[2], f0_hi, acc[2]);
+    acc[3] = fmaf(t0[3], f0_hi, acc[3]);
+    acc[0] = fmaf(t1[0], f1_lo, acc[0]);
+    acc[1] = fmaf(t1[1], f1_lo, acc[1]);
+    acc[2] = fmaf(t1[2], f1_hi, acc[2]);
+    acc[3] = fmaf(t1[3], f1_hi, acc[3]);
+}
+
+// Persistent CTAs over the flattened list of (task, strip) items; a task is up to 8 routed slots of
+// one expert, a strip 16 rows of that expert's matrix (codes and scales together, contiguous).  A CTA
+// owns a contiguous range of items and its warps take them in turn; every warp works alone: lane 0
+// requests the strip in 5-chunk bulk copies into the warp's own ring, the warp converts e2m1 pairs to
+// fp16 pairs with one instruction each and runs m16n8k16 fp16 MMAs whose N dimension is the task's
+// slots (the slots' activations come straight from global memory: a few rows that stay in L1), scales
+// each 32-column group's fp32 partial sum by its e8m0 factor, and finishes the strip from its own
+// registers.  No warp waits for another one (the kernel is bound by instruction issue, and barriers
+// between warps were a third of its stalls).  kUp: epilogue = bias + clamped SwiGLU -> activation
+// (bf16-valued, stored as fp16); else bias -> per-slot values for the combine.
 template <bool kUp, bool kCareful>
-__global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const MoeStreamParams p)
+__global__ void __launch_bounds__(kMoeWarps * 32, 2) moe_stream_kernel(const MoeStreamParams p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    const MoeSmem plan = moe_smem_plan(p.k);
-    uint8_t* ring = smem + plan.ring;
-    float* red = reinterpret_cast<float*>(smem + plan.red);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + plan.bars);
-    uint64_t* empty = full + kMoeStages;
-    int* row_slot = reinterpret_cast<int*>(smem + plan.meta);
-    int* row_shift = row_slot + kMoeRows;
-    uint8_t* xs = smem + plan.xs;
-
-    uint64_t* xbar = empty + kMoeStages;   // completion of a task's row copies
+    const MoeSmem plan = moe_smem_plan();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* ring = smem + plan.ring + warp * (kMoeStages * kMoeSegBytes);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + plan.bars) + warp * kMoeStages;
     [[maybe_unused]] constexpr int kTr = kUp ? 16 : 48;   // first trace slot of this launch (timing build)
-    if (threadIdx.x == 0) {
-        GB_MTRACE(kTr + 0);
-        for (int s = 0; s < kMoeStages; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kMoeWarps);
-        }
-        mbar_init(xbar, 1);
+    if (threadIdx.x == 0) GB_MTRACE(kTr + 0);
+    if (lane == 0) {
+        for (int s = 0; s < kMoeStages; ++s) mbar_init(&full[s], 1);
         fence_barrier_init();
     }
-    __syncthreads();
     // Programmatic dependent launch.  The gate/up launch lets its dependent (the down
     // launch) start only after its own wait has returned, i.e. once the kernels that
     // wrote the task list have completed: the down launch can therefore read the task
-    // list and stream its expert weights before its own wait, while gate/up still runs.
-    // Only its consumers, which read gate/up's activations, wait.
+    // list and request its expert weights before its own wait, while gate/up still runs.
+    // It waits before it reads gate/up's activations.
     if (!p.tasks_early) pdl_wait();
     pdl_launch_dependents();
     if (threadIdx.x == 0) GB_MTRACE(kTr + 1);
@@ -797,230 +820,193 @@ __global__ void __launch_bounds__((kMoeWarps + 1) * 32) moe_stream_kernel(const 
     }
     __syncthreads();
     const int ntasks = s_ntasks;
-    const long long total = (long long)ntasks * p.strips;
-    const long long i0 = total * blockIdx.x / gridDim.x, i1 = total * (blockIdx.x + 1) / gridDim.x;
+    // this CTA's items [i0, i1): an even split of ntasks * strips
+    const unsigned long long total = (unsigned long long)ntasks * unsigned(p.strips);
+    unsigned long long i0, i1;
+    if (total < (1ull << 31)) {
+        const unsigned per = unsigned(total) / gridDim.x, rem = unsigned(total) % gridDim.x;
+        i0 = (unsigned long long)blockIdx.x * per + min(blockIdx.x, rem);
+        i1 = i0 + per + (blockIdx.x < rem ? 1u : 0u);
+    } else {
+        i0 = total * blockIdx.x / gridDim.x, i1 = total * (blockIdx.x + 1) / gridDim.x;
+    }
+    if (i0 + warp >= i1) return;   // nothing for this warp (it holds no copies and no barrier another warp uses)
+    const int my_items = int((i1 - i0 - warp + kMoeWarps - 1) / kMoeWarps);
     const int nseg = (p.chunks + kMoeSegChunks - 1) / kMoeSegChunks;
     const size_t strip_bytes = size_t(p.chunks) * kMxChunkBytes;
-    const int task0 = int(i0 / p.strips), strip0 = int(i0 % p.strips);
+    const int last_bytes = (p.chunks - (nseg - 1) * kMoeSegChunks) * kMxChunkBytes;
+    const int total_segs = my_items * nseg;
 
-    if (warp == kMoeWarps) {
-        if (lane == 0) {
-            long long n = 0;
-            int task = task0, strip = strip0, s = 0, round = 0, cur = -1;
-            const uint8_t* matrix = p.packed;
-            for (long long it = i0; it < i1; ++it) {
-                if (task != cur) {
-                    const int ex = task < kMoeListCache ? s_tasks[task].x : __ldcg(&p.tasks[task]).x;
-                    matrix = p.packed + size_t((ex - p.expert_base) / p.expert_div) * p.matrix_bytes;
-                    cur = task;
-                }
-                const uint8_t* src = matrix + size_t(strip) * strip_bytes;
-                if (++strip == p.strips) strip = 0, ++task;
-                for (int seg = 0; seg < nseg; ++seg, ++n) {
-#ifdef GB_MOE_TRACE
-                    const long long tw0 = clock64();
-#endif
-                    if (round && !mbar_wait(&empty[s], uint32_t(round - 1) & 1)) {
-                        atomicExch(p.fault, 1);
-                        return;
-                    }
-#ifdef GB_MOE_TRACE
-                    if (blockIdx.x == 7) g_moe_trace[kUp ? 85 : 87] += (unsigned long long)(clock64() - tw0);
-#endif
-                    const int nch = min(kMoeSegChunks, p.chunks - seg * kMoeSegChunks);
-                    const uint32_t bytes = uint32_t(nch) * kMxChunkBytes;
-                    mbar_expect_tx(&full[s], bytes);
-                    bulk_g2s(ring + size_t(s) * kMoeSegBytes, src + size_t(seg) * kMoeSegBytes, bytes, &full[s]);
-                    if (n == 0) GB_MTRACE(kTr + 2);
-                    if (++s == kMoeStages) s = 0, ++round;
-                }
-            }
-            GB_MTRACE(kTr + 3);
-        }
-        return;
+    auto expert_of = [&](int task) { return task < kMoeListCache ? s_tasks[task].x : __ldcg(&p.tasks[task]).x; };
+    auto advance = [&](int& task, int& strip) {   // the warp's next item: kMoeWarps strips further
+        strip += kMoeWarps;
+        while (strip >= p.strips) strip -= p.strips, ++task;
+    };
+
+    // ---- requests run kMoeStages copies ahead of the arithmetic; their state lives in every lane, lane 0 acts
+    int iss = 0, iss_seg = 0, iss_stage = 0;
+    int iss_task, iss_strip;
+    {
+        const unsigned long long first = i0 + warp;
+        iss_task = int(first / unsigned(p.strips)), iss_strip = int(first % unsigned(p.strips));
     }
-
-    // The row tile starts all-zero: row kMoeRows stays zero for the padded slots, and the
-    // row copies never write the padding behind column K.
-    for (int i = threadIdx.x; i < (kMoeRows + 1) * (plan.x_stride / 16); i += kMoeWarps * 32)
-        *reinterpret_cast<uint4*>(xs + size_t(i) * 16) = make_uint4(0, 0, 0, 0);
-    if (threadIdx.x == 0) GB_MTRACE(kTr + 4);
+    int task = iss_task, strip = iss_strip;   // the item the arithmetic is at
+    const uint8_t* iss_src = p.packed + size_t((expert_of(iss_task) - p.expert_base) / p.expert_div) * p.matrix_bytes +
+                             size_t(iss_strip) * strip_bytes;
+    auto request = [&]() {
+        const int bytes = iss_seg == nseg - 1 ? last_bytes : kMoeSegBytes;
+        if (lane == 0) {
+            mbar_expect_tx(&full[iss_stage], uint32_t(bytes));
+            bulk_g2s(ring + iss_stage * kMoeSegBytes, iss_src + size_t(iss_seg) * kMoeSegBytes, uint32_t(bytes), &full[iss_stage]);
+        }
+        ++iss;
+        if (++iss_stage == kMoeStages) iss_stage = 0;
+        if (++iss_seg == nseg && iss < total_segs) {
+            iss_seg = 0;
+            advance(iss_task, iss_strip);
+            iss_src = p.packed + size_t((expert_of(iss_task) - p.expert_base) / p.expert_div) * p.matrix_bytes +
+                      size_t(iss_strip) * strip_bytes;
+        }
+    };
+    for (int n = 0; n < kMoeStages && n < total_segs; ++n) request();
+    if (threadIdx.x == 0) GB_MTRACE(kTr + 2);
     if (p.tasks_early) pdl_wait();   // the activations come from the launch before this one
     if (threadIdx.x == 0) GB_MTRACE(kTr + 5);
 
     const int g = lane >> 2, t = lane & 3;
-    const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    int cur_task = -1, task_rows = 0, task_expert = 0;
-    const uint8_t* xrow = xs;
+    const int row_bytes = p.k * 2;
     bool ok = true;
-    int s = 0, phase = 0, parity = 0, xphase = 0;
-
-    int task = task0, strip = strip0 - 1;
-    for (long long it = i0; it < i1; ++it) {
-        if (++strip == p.strips) strip = 0, ++task;
+    int stage = 0, phase = 0, con = 0;
+    int cur_task = -1, task_rows = 0, task_expert = 0;
+    int slot0 = 0, slot1 = 0, shift0 = 0, shift1 = 0;   // the two slots (2t, 2t + 1) this lane finishes
+    const uint8_t* xg = nullptr;                          // this lane's activation row (row g of the task), at column 8t
+    for (int item = 0; item < my_items && ok; ++item) {
         if (task != cur_task) {
-            // ---- new task: stage its rows, one bulk copy per row (one round trip to L2
-            // however long the rows are).  All consumers have left the previous x tile.
-            fence_proxy_async_smem();
-            named_barrier_sync(1, kMoeWarps * 32);
             const int4 tk = task < kMoeListCache ? s_tasks[task] : __ldcg(&p.tasks[task]);
             task_expert = tk.x;
             task_rows = tk.z;
-            if (threadIdx.x == 0) mbar_expect_tx(xbar, uint32_t(task_rows) * uint32_t(p.k) * 2u);
-            if (threadIdx.x < kMoeRows) {
-                int slot = -1, shift = 0;
-                if (int(threadIdx.x) < task_rows) {
-                    const int at = tk.y + int(threadIdx.x);
-                    slot = at < kMoeListCache ? s_sorted[at] : __ldcg(&p.sorted[at]);
-                    const size_t src_row = kUp ? size_t(slot / p.topk) : size_t(slot);
-                    bulk_g2s(xs + size_t(threadIdx.x) * plan.x_stride, p.act_in + src_row * p.k, uint32_t(p.k) * 2u,
-                             xbar);
-                    if (kUp) shift = p.xshift[slot / p.topk];
-                }
-                row_slot[threadIdx.x] = slot;
-                row_shift[threadIdx.x] = shift;
+            auto slot_at = [&](int m) {
+                const int at = tk.y + m;
+                return at < kMoeListCache ? s_sorted[at] : __ldcg(&p.sorted[at]);
+            };
+            {
+                // a lane whose slot g is beyond the task's rows reads the first row: the MMA column it feeds is
+                // never stored, and the loop needs no test
+                const int sg = slot_at(g < task_rows ? g : 0);
+                const size_t src_row = kUp ? size_t(sg / p.topk) : size_t(sg);
+                xg = reinterpret_cast<const uint8_t*>(p.act_in + src_row * p.k) + t * 16;
             }
-            if (ok && !mbar_wait(xbar, xphase)) {
-                atomicExch(p.fault, 3);
-                ok = false;
+            slot0 = 2 * t < task_rows ? slot_at(2 * t) : -1;
+            slot1 = 2 * t + 1 < task_rows ? slot_at(2 * t + 1) : -1;
+            if (kUp) {
+                shift0 = slot0 >= 0 ? __ldg(&p.xshift[slot0 / p.topk]) : 0;
+                shift1 = slot1 >= 0 ? __ldg(&p.xshift[slot1 / p.topk]) : 0;
             }
-            xphase ^= 1;
-            named_barrier_sync(1, kMoeWarps * 32);
-            if (threadIdx.x == 0 && it == i0) GB_MTRACE(kTr + 6);
             cur_task = task;
-            xrow = xs + size_t(g < task_rows ? g : kMoeRows) * plan.x_stride + t * 16;
         }
         // this strip's bias values are requested now and used in the epilogue
         const int ebias = p.bias_by_global ? task_expert : (task_expert - p.expert_base) / p.expert_div;
         float bias0 = 0.f, bias1 = 0.f;
         if (kUp) {
-            if (threadIdx.x < 64) {
-                const int i = strip * 8 + row_of_g((threadIdx.x & 31) >> 2);
-                if (2 * i + 1 < p.rows) {
-                    const float* b = p.bias + size_t(ebias) * p.rows + 2 * i;
-                    bias0 = __ldg(b), bias1 = __ldg(b + 1);
+            const int i = strip * 8 + row_of_g(g);
+            if (2 * i + 1 < p.rows) {
+                const float* b = p.bias + size_t(ebias) * p.rows + 2 * i;
+                bias0 = __ldg(b), bias1 = __ldg(b + 1);
+            }
+        } else {
+            const int d = strip * 16 + row_of_g(g);
+            if (d < p.rows) bias0 = __ldg(&p.bias[size_t(ebias) * p.rows + d]);
+            if (d + 8 < p.rows) bias1 = __ldg(&p.bias[size_t(ebias) * p.rows + d + 8]);
+        }
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int seg = 0; seg < nseg; ++seg, ++con) {
+            const int nch = min(kMoeSegChunks, p.chunks - seg * kMoeSegChunks);
+            // the activations of this copy's columns first: they do not depend on the weights
+            // Plain loads (cached in L1): the rows were written by the kernel before this one, which may still
+            // have been running when this one started.
+            uint4 xa[kMoeSegChunks], xb[kMoeSegChunks];
+            const uint8_t* xseg = xg + size_t(seg) * (kMoeSegChunks * 128);   // 64 columns = 128 bytes of x
+            if (nch == kMoeSegChunks && (seg + 1) * (kMoeSegChunks * 128) <= row_bytes) {
+#pragma unroll
+                for (int c = 0; c < kMoeSegChunks; ++c) {
+                    xa[c] = *reinterpret_cast<const uint4*>(xseg + c * 128);
+                    xb[c] = *reinterpret_cast<const uint4*>(xseg + c * 128 + 64);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < kMoeSegChunks; ++c) {
+                    xa[c] = xb[c] = make_uint4(0, 0, 0, 0);
+                    const int off = (seg * kMoeSegChunks + c) * 128 + t * 16;
+                    if (c < nch) {
+                        if (off + 16 <= row_bytes) xa[c] = *reinterpret_cast<const uint4*>(xseg + c * 128);
+                        if (off + 80 <= row_bytes) xb[c] = *reinterpret_cast<const uint4*>(xseg + c * 128 + 64);
+                    }
                 }
             }
-        } else if (threadIdx.x < 128) {
-            const int d = strip * 16 + row_of_g((threadIdx.x & 31) >> 2) + 8 * (threadIdx.x >> 6);
-            if (d < p.rows) bias0 = __ldg(&p.bias[size_t(ebias) * p.rows + d]);
-        }
-        for (int seg = 0; seg < nseg; ++seg) {
-#ifdef GB_MOE_TRACE
-            const long long tw0 = clock64();
-#endif
-            if (ok && !mbar_wait(&full[s], phase)) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&full[stage], phase))) {   // the whole warp gives up, or no lane
                 atomicExch(p.fault, 2);
                 ok = false;
+                break;
             }
-#ifdef GB_MOE_TRACE
-            if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 84 : 86] += (unsigned long long)(clock64() - tw0);
-#endif
-            const int nch = min(kMoeSegChunks, p.chunks - seg * kMoeSegChunks);
-            if (threadIdx.x == 0 && it == i0 && seg == 0) GB_MTRACE(kTr + 7);
-            if (ok) {
+            if (threadIdx.x == 0 && con == 0) GB_MTRACE(kTr + 7);
+            const uint8_t* sbase = ring + stage * kMoeSegBytes;
+            if (nch == kMoeSegChunks) {   // the common case as one straight run of instructions
 #pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    const int c = 2 * warp + cc;
-                    if (c >= nch) break;
-                    const uint8_t* st = ring + s * kMoeSegBytes + c * kMxChunkBytes;
-                    const uint4 u = *reinterpret_cast<const uint4*>(st + lane * 16);
-                    const uint32_t sc = *reinterpret_cast<const uint32_t*>(st + 512 + g * 4);
-                    const int kbyte = (seg * kMoeSegChunks + c) * 128;      // 64 columns = 128 bytes of x
-                    const uint4 xa = *reinterpret_cast<const uint4*>(xrow + kbyte);
-                    const uint4 xb = *reinterpret_cast<const uint4*>(xrow + kbyte + 64);
-                    float tmp[4];
-                    // group 0: octets 0..3 (words x = row R, y = row R+8)
-                    {
-                        const uint32_t a0[4] = {e2m1x2_to_f16x2(u.x, 0), e2m1x2_to_f16x2(u.y, 0),
-                                                e2m1x2_to_f16x2(u.x, 1), e2m1x2_to_f16x2(u.y, 1)};
-                        const uint32_t a1[4] = {e2m1x2_to_f16x2(u.x, 2), e2m1x2_to_f16x2(u.y, 2),
-                                                e2m1x2_to_f16x2(u.x, 3), e2m1x2_to_f16x2(u.y, 3)};
-                        mma_f16_16816(tmp, a0, xa.x, xa.y, zero4);
-                        mma_f16_16816(tmp, a1, xa.z, xa.w, tmp);
-                        const float f_lo = e8m0_to_float<kCareful>(sc & 0xff);
-                        const float f_hi = e8m0_to_float<kCareful>((sc >> 8) & 0xff);
-                        acc[0] = fmaf(tmp[0], f_lo, acc[0]);
-                        acc[1] = fmaf(tmp[1], f_lo, acc[1]);
-                        acc[2] = fmaf(tmp[2], f_hi, acc[2]);
-                        acc[3] = fmaf(tmp[3], f_hi, acc[3]);
-                    }
-                    // group 1: octets 4..7 (words z = row R, w = row R+8)
-                    {
-                        const uint32_t a0[4] = {e2m1x2_to_f16x2(u.z, 0), e2m1x2_to_f16x2(u.w, 0),
-                                                e2m1x2_to_f16x2(u.z, 1), e2m1x2_to_f16x2(u.w, 1)};
-                        const uint32_t a1[4] = {e2m1x2_to_f16x2(u.z, 2), e2m1x2_to_f16x2(u.w, 2),
-                                                e2m1x2_to_f16x2(u.z, 3), e2m1x2_to_f16x2(u.w, 3)};
-                        mma_f16_16816(tmp, a0, xb.x, xb.y, zero4);
-                        mma_f16_16816(tmp, a1, xb.z, xb.w, tmp);
-                        const float f_lo = e8m0_to_float<kCareful>((sc >> 16) & 0xff);
-                        const float f_hi = e8m0_to_float<kCareful>(sc >> 24);
-                        acc[0] = fmaf(tmp[0], f_lo, acc[0]);
-                        acc[1] = fmaf(tmp[1], f_lo, acc[1]);
-                        acc[2] = fmaf(tmp[2], f_hi, acc[2]);
-                        acc[3] = fmaf(tmp[3], f_hi, acc[3]);
-                    }
-                }
+                for (int c = 0; c < kMoeSegChunks; ++c)
+                    moe_chunk_math<kCareful>(sbase + c * kMxChunkBytes, lane, g, xa[c], xb[c], acc);
+            } else {
+#pragma unroll
+                for (int c = 0; c < kMoeSegChunks; ++c)
+                    if (c < nch) moe_chunk_math<kCareful>(sbase + c * kMxChunkBytes, lane, g, xa[c], xb[c], acc);
             }
+            // every lane has read this ring slot: lane 0 asks for the copy that reuses it
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-            if (++s == kMoeStages) {
-                s = 0;
-                phase ^= 1;
+            if (iss < total_segs) {
+                if (lane == 0) fence_proxy_async_smem();
+                request();
             }
+            if (++stage == kMoeStages) stage = 0, phase ^= 1;
         }
+        if (!ok) break;
 
-        // ---- end of a strip: reduce the warps' partial sums, then the epilogue.
-        // acc[0..1]: strip row R(g), slots 2t, 2t+1; acc[2..3]: strip row R(g)+8.
-        float* slotbuf = red + parity * (kMoeWarps * 128);
-        parity ^= 1;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            slotbuf[(warp * 4 + q) * 32 + lane] = acc[q];
-            acc[q] = 0.f;
-        }
-        named_barrier_sync(2, kMoeWarps * 32);
+        // ---- end of a strip.  acc[0..1]: strip row R(g), slots 2t, 2t+1; acc[2..3]: strip row R(g)+8.
         if (kUp) {
-            // 64 outputs: (lane l, slot parity): gate from q = par, up from q = par + 2
-            if (threadIdx.x < 64) {
-                const int l = threadIdx.x & 31, par = threadIdx.x >> 5;
-                float gate = 0.f, up = 0.f;
+            // rows R(g) and R(g)+8 are the gate and the up value of one intermediate channel
+            const int i = strip * 8 + row_of_g(g);
+            if (2 * i + 1 < p.rows) {
 #pragma unroll
-                for (int w = 0; w < kMoeWarps; ++w) {
-                    gate += slotbuf[(w * 4 + par) * 32 + l];
-                    up += slotbuf[(w * 4 + par + 2) * 32 + l];
-                }
-                const int m = 2 * (l & 3) + par;
-                const int i = strip * 8 + row_of_g(l >> 2);          // intermediate channel
-                if (m < task_rows && 2 * i + 1 < p.rows) {
-                    const float sc2 = __uint_as_float(uint32_t(127 + row_shift[m]) << 23);   // 2^shift
-                    gate = fminf(bf16_round_f(bf16_round_f(gate * sc2) + bias0), p.limit);
-                    up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(up * sc2) + bias1)));
+                for (int par = 0; par < 2; ++par) {
+                    const int slot = par ? slot1 : slot0;
+                    if (slot < 0) continue;
+                    const float sc2 = __uint_as_float(uint32_t(127 + (par ? shift1 : shift0)) << 23);   // 2^shift
+                    float gate = fminf(bf16_round_f(bf16_round_f(acc[par] * sc2) + bias0), p.limit);
+                    const float up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(acc[par + 2] * sc2) + bias1)));
                     const float sig = bf16_round_f(1.f / (1.f + expf(-bf16_round_f(1.702f * gate))));
                     const float glu = bf16_round_f(gate * sig);
-                    p.act_out[size_t(row_slot[m]) * (p.rows / 2) + i] = __float2half_rn(bf16_round_f(glu * bf16_round_f(up + 1.f)));
+                    p.act_out[size_t(slot) * (p.rows / 2) + i] = __float2half_rn(bf16_round_f(glu * bf16_round_f(up + 1.f)));
                 }
             }
         } else {
-            if (threadIdx.x < 128) {
-                const int l = threadIdx.x & 31, q = threadIdx.x >> 5;
-                float v = 0.f;
 #pragma unroll
-                for (int w = 0; w < kMoeWarps; ++w) v += slotbuf[(w * 4 + q) * 32 + l];
-                const int m = 2 * (l & 3) + (q & 1);
-                const int d = strip * 16 + row_of_g(l >> 2) + 8 * (q >> 1);
-                if (m < task_rows && d < p.rows)
-                    p.vals_out[size_t(row_slot[m]) * p.rows + d] = bf16_round_f(bf16_round_f(v) + bias0);
+            for (int q = 0; q < 4; ++q) {
+                const int slot = (q & 1) ? slot1 : slot0;
+                const int d = strip * 16 + row_of_g(g) + 8 * (q >> 1);
+                if (slot >= 0 && d < p.rows)
+                    p.vals_out[size_t(slot) * p.rows + d] = bf16_round_f(bf16_round_f(acc[q]) + ((q >> 1) ? bias1 : bias0));
             }
         }
-        if (threadIdx.x == 0 && it - i0 < 20) GB_MTRACE(kTr + 8 + int(it - i0));
+        if (threadIdx.x == 0 && item < 20) GB_MTRACE(kTr + 8 + item);
+        advance(task, strip);
     }
     if (threadIdx.x == 0) GB_MTRACE(kTr + 31);
-    // after a give-up the copies already issued may still land: give each stage a short moment (the fault is
+    // after a give-up the copies already requested may still land: give each a short moment (the fault is
     // recorded already, nothing is read any more) before the CTA's shared memory is released
-    if (!ok)
-        for (int i = 0; i < kMoeStages; ++i) (void)mbar_wait(&full[i], 0, 2000000ull);
+    if (!ok) {
+        for (int n = con; n < iss; ++n) {
+            (void)mbar_wait(&full[stage], phase, 2000000ull);
+            if (++stage == kMoeStages) stage = 0, phase ^= 1;
+        }
+    }
 }
 
 // y[t,d] = bf(sum_j vals[t*k+j, d] * p[t,j]) over the local experts in router order
@@ -1137,8 +1123,6 @@ int moe_resolve_options(const garnet_b200_moe_options* in, garnet_b200_moe_optio
         o.tp_rank = 0;
         o.tp_weights_sharded = 0;
     }
-    if (size_t(moe_smem_plan(std::max(o.hidden, o.intermediate)).total) > kMaxDynamicSmem - 1024)
-        return fail(GARNET_B200_NOT_SUPPORTED, "moe: hidden/intermediate too large for the streaming kernel");
     *eff = o;
     return GARNET_B200_OK;
 }
@@ -1495,13 +1479,13 @@ int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStrea
     p.slots = tokens * topk;
     p.tasks_cap = p.slots / kMoeRows + opt.experts + 1;   // as sized in moe_workspace_plan
 
-    const size_t smem = size_t(moe_smem_plan(geo.cols).total);
-    const int ctas_per_sm = std::max(1, std::min(2, int(kMaxDynamicSmem / (smem + 2048))));
+    const size_t smem = size_t(moe_smem_plan().total);
+    const int ctas_per_sm = 2;   // as the kernel's launch bounds say
     // upper bound of (task, strip) items: every slot its own task
     const long long max_items = (long long)tokens * topk * geo.strips;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(std::max<long long>(1, std::min<long long>(max_items, (long long)kSmCount * ctas_per_sm))));
-    cfg.blockDim = dim3((kMoeWarps + 1) * 32);
+    cfg.blockDim = dim3(kMoeWarps * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
