@@ -692,9 +692,13 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
 
 constexpr int kMoeWarps = 8;                       // warps per CTA; each streams its own strips through its own ring
 #ifndef GB_MOE_STAGES
-#define GB_MOE_STAGES 4
+#define GB_MOE_STAGES 3
 #endif
 constexpr int kMoeStages = GB_MOE_STAGES;          // ring slots per warp
+#ifndef GB_MOE_CTAS
+#define GB_MOE_CTAS 2
+#endif
+constexpr int kMoeCtasPerSm = GB_MOE_CTAS;
 constexpr int kMoeSegChunks = 5;                   // chunks per bulk copy (a gpt-oss strip is 45 chunks = 9 copies)
 constexpr int kMoeSegBytes = kMoeSegChunks * kMxChunkBytes;
 constexpr int kMoeRows = 8;                        // slots per task (one MMA N-tile)
@@ -783,7 +787,7 @@ __device__ __forceinline__ void moe_chunk_math(const uint8_t* st, int lane, int 
 // between warps were a third of its stalls).  kUp: epilogue = bias + clamped SwiGLU -> activation
 // (bf16-valued, stored as fp16); else bias -> per-slot values for the combine.
 template <bool kUp, bool kCareful>
-__global__ void __launch_bounds__(kMoeWarps * 32, 2) moe_stream_kernel(const MoeStreamParams p)
+__global__ void __launch_bounds__(kMoeWarps * 32, kMoeCtasPerSm) moe_stream_kernel(const MoeStreamParams p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     const MoeSmem plan = moe_smem_plan();
@@ -881,6 +885,9 @@ __global__ void __launch_bounds__(kMoeWarps * 32, 2) moe_stream_kernel(const Moe
     int slot0 = 0, slot1 = 0, shift0 = 0, shift1 = 0;   // the two slots (2t, 2t + 1) this lane finishes
     const uint8_t* xg = nullptr;                          // this lane's activation row (row g of the task), at column 8t
     for (int item = 0; item < my_items && ok; ++item) {
+#ifdef GB_MOE_TRACE
+        const long long ti0 = clock64();
+#endif
         if (task != cur_task) {
             const int4 tk = task < kMoeListCache ? s_tasks[task] : __ldcg(&p.tasks[task]);
             task_expert = tk.x;
@@ -919,7 +926,13 @@ __global__ void __launch_bounds__(kMoeWarps * 32, 2) moe_stream_kernel(const Moe
             if (d + 8 < p.rows) bias1 = __ldg(&p.bias[size_t(ebias) * p.rows + d + 8]);
         }
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#ifdef GB_MOE_TRACE
+        if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 88 : 91] += (unsigned long long)(clock64() - ti0);
+#endif
         for (int seg = 0; seg < nseg; ++seg, ++con) {
+#ifdef GB_MOE_TRACE
+            const long long ts0 = clock64();
+#endif
             const int nch = min(kMoeSegChunks, p.chunks - seg * kMoeSegChunks);
             // the activations of this copy's columns first: they do not depend on the weights
             // Plain loads (cached in L1): the rows were written by the kernel before this one, which may still
@@ -943,12 +956,20 @@ __global__ void __launch_bounds__(kMoeWarps * 32, 2) moe_stream_kernel(const Moe
                     }
                 }
             }
+#ifdef GB_MOE_TRACE
+            const long long tw0 = clock64();
+            if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 89 : 92] += (unsigned long long)(tw0 - ts0);
+#endif
             if (!__all_sync(0xffffffffu, mbar_wait(&full[stage], phase))) {   // the whole warp gives up, or no lane
                 atomicExch(p.fault, 2);
                 ok = false;
                 break;
             }
             if (threadIdx.x == 0 && con == 0) GB_MTRACE(kTr + 7);
+#ifdef GB_MOE_TRACE
+            const long long tw1 = clock64();
+            if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 84 : 86] += (unsigned long long)(tw1 - tw0);
+#endif
             const uint8_t* sbase = ring + stage * kMoeSegBytes;
             if (nch == kMoeSegChunks) {   // the common case as one straight run of instructions
 #pragma unroll
@@ -966,9 +987,15 @@ __global__ void __launch_bounds__(kMoeWarps * 32, 2) moe_stream_kernel(const Moe
                 request();
             }
             if (++stage == kMoeStages) stage = 0, phase ^= 1;
+#ifdef GB_MOE_TRACE
+            if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 85 : 87] += (unsigned long long)(clock64() - tw1);
+#endif
         }
         if (!ok) break;
 
+#ifdef GB_MOE_TRACE
+        const long long te0 = clock64();
+#endif
         // ---- end of a strip.  acc[0..1]: strip row R(g), slots 2t, 2t+1; acc[2..3]: strip row R(g)+8.
         if (kUp) {
             // rows R(g) and R(g)+8 are the gate and the up value of one intermediate channel
@@ -996,6 +1023,9 @@ __global__ void __launch_bounds__(kMoeWarps * 32, 2) moe_stream_kernel(const Moe
             }
         }
         if (threadIdx.x == 0 && item < 20) GB_MTRACE(kTr + 8 + item);
+#ifdef GB_MOE_TRACE
+        if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 90 : 93] += (unsigned long long)(clock64() - te0);
+#endif
         advance(task, strip);
     }
     if (threadIdx.x == 0) GB_MTRACE(kTr + 31);
@@ -1070,14 +1100,16 @@ MoeWorkspace moe_workspace_plan(const garnet_b200_moe_options& o, int tokens)
     const int mx_local = mx_world <= 1 ? o.experts   // the same count as Moe::local_experts()
                          : o.ep_interleaved ? (o.experts - o.ep_rank + mx_world - 1) / mx_world : o.experts / mx_world;
     const int mx_mode = moe_mx_mode_of(o);
-    const bool mx = mx_mode == 2 || (mx_mode == 1 && slots > size_t(6) * mx_local);
+    const bool mx = mx_mode == 2 || (mx_mode == 1 && slots > size_t(kMxMinRowsPerExpert) * mx_local);
     const MoeMxPlan mxp = moe_mx_plan(o, tokens, int(slots));
     w.mx_tp = take(mx ? size_t(o.experts + 1) * 4 : 0);
     w.mx_q = take(mx ? mxp.q_bytes : 0);
     w.mx_sf = take(mx ? mxp.sf_bytes : 0);
-    w.route_partial = take(mx ? moe_route_partial_bytes(tokens, o.experts) : 0);
     w.act = take(slots * o.intermediate * 2);
-    w.vals = take(slots * o.hidden * 4);
+    // The tensor-core router (more than a decode batch) leaves its partial sums where the per-slot values go
+    // later: the logits are final before any expert kernel writes.
+    w.vals = take(std::max(slots * o.hidden * 4, tokens > 8 ? moe_route_partial_bytes(tokens, o.experts) : size_t(0)));
+    w.route_partial = w.vals;
     w.total = off;
     return w;
 }
@@ -1358,11 +1390,10 @@ int Moe::finish_prepare(cudaStream_t stream)
     GB_CUDA(cudaMemcpyAsync(&flag, flag_dev, sizeof(int), cudaMemcpyDeviceToHost, stream));
     GB_CUDA(cudaStreamSynchronize(stream));
     careful_scales = flag != 0;
-    if (mxr_w[0]) {
+    if (mxr_w[0])
         if (int rc = finish_mx()) return rc;
-        if (int rc = init_route_mma(stream)) return rc;
-        GB_CUDA(cudaStreamSynchronize(stream));
-    }
+    if (int rc = init_route_mma(stream)) return rc;
+    GB_CUDA(cudaStreamSynchronize(stream));
     if (!packed_up && !mx_ok)
         return fail(GARNET_B200_NOT_SUPPORTED, "moe: the block-scaled layout alone was asked for, but this shape or driver does not support it");
     // the router kernels also have a little static shared memory: leave room for it
@@ -1414,9 +1445,18 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
     while (per_cta > 4 * kRouteWarps && token_ctas * ((opt.experts + per_cta - 1) / per_cta) < 2 * kSmCount) per_cta = (per_cta + 1) / 2;
     per_cta = std::max(per_cta, std::min(opt.experts, 4));
     const dim3 grid(token_ctas, (opt.experts + per_cta - 1) / per_cta);
-    if (route_partial && route_mma_ok && use_mx(tokens * opt.top_k) && tokens > 4 * kRouteTokens) {
-        // many tokens, and no consumer of the fp16 row copies: tensor-core router
+    if (route_partial && route_mma_ok && tokens > kRouteTokens) {
+        // more than a decode batch: tensor-core router; the streaming expert kernel (not the block-scaled one,
+        // which quantises the rows itself) also wants the fp16 row copies
         if (int rc = route_mma(x, logits, route_partial, tokens, stream)) return rc;
+        if (xh && !use_mx(tokens * opt.top_k)) {
+            const unsigned blocks = unsigned((size_t(tokens) * 32 + 255) / 256);
+            if (opt.io_dtype == GARNET_B200_FP32)
+                moe_prep_rows_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x), xh, xshift, tokens, opt.hidden);
+            else
+                moe_prep_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), xh, xshift,
+                                                                                tokens, opt.hidden);
+        }
     } else if (tokens <= kRouteTokens) {
         const unsigned ctas = unsigned(opt.experts);   // one expert per CTA
         const size_t small_smem = size_t(tokens) * opt.hidden * sizeof(float);
@@ -1480,7 +1520,7 @@ int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStrea
     p.tasks_cap = p.slots / kMoeRows + opt.experts + 1;   // as sized in moe_workspace_plan
 
     const size_t smem = size_t(moe_smem_plan().total);
-    const int ctas_per_sm = 2;   // as the kernel's launch bounds say
+    const int ctas_per_sm = kMoeCtasPerSm;   // as the kernel's launch bounds say
     // upper bound of (task, strip) items: every slot its own task
     const long long max_items = (long long)tokens * topk * geo.strips;
     cudaLaunchConfig_t cfg = {};

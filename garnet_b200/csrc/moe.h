@@ -63,6 +63,7 @@ int moe_mx_mode_of(const garnet_b200_moe_options& o);
 // view of them: later fields zero-filled, `intermediate` = this rank's share of it.
 int moe_resolve_options(const garnet_b200_moe_options* in, garnet_b200_moe_options* eff);
 size_t moe_route_partial_bytes(int tokens, int experts);
+constexpr int kMxMinRowsPerExpert = 8;   // routed rows per local expert above which the block-scaled path is used
 
 struct Moe {
     garnet_b200_moe_options opt{};     // resolved: `intermediate` is this rank's share
@@ -123,13 +124,13 @@ struct Moe {
     int launch_mx(bool up, const MoeWorkspacePtrs& w, const void* x, int x_is_sorted, int tokens, int slots, int topk,
                   cudaStream_t stream);
     // The block-scaled path pays off once experts get several rows each (measured
-    // crossover on the gpt-oss-120b layer: about 6 rows per expert); below that the
+    // crossover on the gpt-oss-120b layer: about 8 rows per expert); below that the
     // streaming kernel moves the weights faster.
     // A handle that holds one layout only runs every size on it.
     bool use_mx(int slots) const
     {
         if (!mx_ok || !mxr_w[0]) return false;
-        return mx_mode == 2 || !packed_up || (mx_mode == 1 && slots > 6 * local_experts());
+        return mx_mode == 2 || !packed_up || (mx_mode == 1 && slots > kMxMinRowsPerExpert * local_experts());
     }
     int init_route_mma(cudaStream_t stream);
     int route_mma(const void* x, float* logits, float* partial, int tokens, cudaStream_t stream);
