@@ -323,9 +323,34 @@ __device__ __forceinline__ void small_meta_body(const float* logits, const Small
         }
     }
     __syncthreads();
-    // ---- rows per expert (thread e)
     const int slots = tokens * topk;
     const int e = threadIdx.x;
+    if (tokens == 1 && !mt.tile_rows) {
+        // One token: its experts are distinct, so every local one of them is a task of one row, in ascending
+        // expert order - no scan, no second barrier.
+        if (e < experts) {
+            int before = 0, mine_slot = -1;
+            for (int j = 0; j < topk; ++j) {
+                const int c = s_sel[j];
+                if (!expert_is_local(c, mt.sh)) continue;
+                before += c < e;
+                if (c == e) mine_slot = j;
+            }
+            mt.counts[e] = mine_slot >= 0 ? 1 : 0;
+            mt.offsets[e] = before;
+            if (mine_slot >= 0) {
+                mt.sorted[before] = mine_slot;
+                mt.tasks[before] = make_int4(e, before, 1, 0);
+            }
+            if (e == experts - 1) {
+                const int total = before + (mine_slot >= 0 ? 1 : 0);
+                mt.offsets[experts] = total;
+                *mt.ntasks = total;
+            }
+        }
+        return;
+    }
+    // ---- rows per expert (thread e)
     int mine = 0;
     if (e < experts && expert_is_local(e, mt.sh))
         for (int i = 0; i < slots; ++i) mine += s_sel[i] == e;
@@ -852,7 +877,10 @@ __global__ void __launch_bounds__(kMoeWarps * 32, kMoeCtasPerSm) moe_stream_kern
     int iss_task, iss_strip;
     {
         const unsigned long long first = i0 + warp;
-        iss_task = int(first / unsigned(p.strips)), iss_strip = int(first % unsigned(p.strips));
+        if (first < (1ull << 31))   // 32-bit division: this sits in front of the first request
+            iss_task = int(unsigned(first) / unsigned(p.strips)), iss_strip = int(unsigned(first) % unsigned(p.strips));
+        else
+            iss_task = int(first / unsigned(p.strips)), iss_strip = int(first % unsigned(p.strips));
     }
     int task = iss_task, strip = iss_strip;   // the item the arithmetic is at
     const uint8_t* iss_src = p.packed + size_t((expert_of(iss_task) - p.expert_base) / p.expert_div) * p.matrix_bytes +

@@ -216,6 +216,18 @@ def test_expert_parallel_partials():
     _, sel, pr = oracle.moe_route(wide["x"], wide["router_w"], wide["router_b"], 8, 4)
     o = oracle.moe_experts(wide["x"], sel, pr, *oracle_args(wide), expert_lo=2, expert_hi=4, round_output=False)
     assert_close(parts[1], o, 0.002, "rank-1 partial vs oracle")
+    # decode-sized batches take the router kernel's own bookkeeping (one token: a shortcut of its own)
+    for tokens in (1, 2, 8):
+        small = dict(wide)
+        small["x"] = wide["x"][:tokens]
+        full = build(small).run(dev(small["x"])).cpu().numpy()
+        for world, inter in ((4, False), (2, True)):
+            parts = [build(small, ep_rank=r, ep_world=world, ep_interleaved=inter).run(dev(small["x"])).cpu().numpy()
+                     for r in range(world)]
+            assert_close(oracle.bf16_round(sum(parts)), full, 0.002, f"{tokens} token(s), {world} ranks")
+        _, sel, pr = oracle.moe_route(small["x"], small["router_w"], small["router_b"], 8, 4)
+        o = oracle.moe_experts(small["x"], sel, pr, *oracle_args(small), expert_lo=2, expert_hi=4, round_output=False)
+        assert_close(build(small, ep_rank=1, ep_world=4).run(dev(small["x"])).cpu().numpy(), o, 0.002, f"{tokens} token(s), rank-1 partial vs oracle")
 
 
 def test_host_packer_bytes_equal_device_bytes_and_prepacked_handle_is_the_same_operator():
