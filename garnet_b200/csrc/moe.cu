@@ -587,6 +587,146 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int* __restric
     }
 }
 
+// After the tensor-core router, one warp per token: adds the K ranges' partial sums in order (+ bias, bf16
+// rounding: the logits), picks the top k from registers (ties to the lowest expert index) with the softmax over
+// the picked logits only (gpt_oss_kernels.cu:681-726), counts the rows of the local experts, and - when the
+// streaming expert kernel follows - writes the token's fp16 row copy (same arithmetic as moe_prep_rows_kernel).
+// At most 256 experts (eight logits per lane) and top 8.
+template <typename XT>
+__global__ void __launch_bounds__(256)
+moe_route_finish_topk_kernel(const float* __restrict__ partial, int splits, const float* __restrict__ rb,
+                             float* __restrict__ logits, int* __restrict__ selected, float* __restrict__ probs,
+                             int* __restrict__ counts, MoeShard sh, const XT* __restrict__ x, __half* __restrict__ xh,
+                             int* __restrict__ xshift, int tokens, int hidden, int experts, int topk)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int token = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (token >= tokens) return;
+    const size_t plane = size_t(tokens) * experts;
+    const float* p0 = partial + size_t(token) * experts;
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = lane + 32 * u < experts ? p0[lane + 32 * u] : 0.f;
+#pragma unroll 2
+    for (int z = 1; z < splits; ++z) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (lane + 32 * u < experts) v[u] += p0[z * plane + lane + 32 * u];
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int e = lane + 32 * u;
+        if (e < experts) {
+            v[u] = bf16_round_f(v[u] + rb[e]);
+            logits[size_t(token) * experts + e] = v[u];
+        } else {
+            v[u] = -INFINITY;
+        }
+    }
+    unsigned taken = 0;   // bit u: this lane's u-th logit has been picked
+    float top[8];
+    int chosen[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (j >= topk) break;
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int e = lane + 32 * u;
+            if (e < experts && !(taken & (1u << u)) && (arg == 0x7fffffff || v[u] > best)) {   // ascending e: ties keep the lower
+                best = v[u];
+                arg = e;
+            }
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
+            if (oa != 0x7fffffff && (arg == 0x7fffffff || ov > best || (ov == best && oa < arg))) {
+                best = ov;
+                arg = oa;
+            }
+        }
+        if ((arg & 31) == lane) taken |= 1u << (arg >> 5);
+        chosen[j] = arg;
+        top[j] = best;
+    }
+    float my_top = -INFINITY;
+    int my_pick = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (j < topk && lane == j) my_top = top[j], my_pick = chosen[j];
+    const float ex = lane < topk ? expf(my_top - top[0]) : 0.f;
+    float total = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (j < topk) total += __shfl_sync(0xffffffffu, ex, j);
+    if (lane < topk) {
+        selected[token * topk + lane] = my_pick;
+        probs[token * topk + lane] = bf16_round_f(ex / total);
+        // rows per local expert (zeroed by the caller): integer adds, any order
+        if (counts && expert_is_local(my_pick, sh)) atomicAdd(&counts[my_pick], 1);
+    }
+    if (!xh) return;
+    const XT* src = x + size_t(token) * hidden;
+    __half* dst = xh + size_t(token) * hidden;
+    auto shift_of = [](float amax) {
+        int shift = 0;
+        if (amax > 0.f && isfinite(amax)) shift = int((__float_as_uint(amax) >> 23) & 0xff) - 127 - 13;
+        return max(-100, min(100, shift));
+    };
+    if constexpr (sizeof(XT) == 2) {
+        // a bf16 row of up to 3072 columns in one round trip: twelve 16-byte loads per lane, kept in registers
+        constexpr int kVec = 12;
+        if (hidden % 8 == 0 && hidden <= kVec * 32 * 8 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            const uint4* sv = reinterpret_cast<const uint4*>(src);
+            const int nvec = hidden / 8;
+            uint4 r[kVec];
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) r[i] = lane + 32 * i < nvec ? sv[lane + 32 * i] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) {
+                const uint32_t w[4] = {r[i].x, r[i].y, r[i].z, r[i].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w[q] << 16)), fabsf(__uint_as_float(w[q] & 0xffff0000u))));
+            }
+#pragma unroll
+            for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            const int shift = shift_of(amax);
+            const float scale = __uint_as_float(uint32_t(127 - shift) << 23);
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) {
+                if (lane + 32 * i < nvec) {
+                    const uint32_t w[4] = {r[i].x, r[i].y, r[i].z, r[i].w};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const __half2 h = __floats2half2_rn(__uint_as_float(w[q] << 16) * scale, __uint_as_float(w[q] & 0xffff0000u) * scale);
+                        o[q] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    *reinterpret_cast<uint4*>(dst + size_t(lane + 32 * i) * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            }
+            if (lane == 0) xshift[token] = shift;
+            return;
+        }
+    }
+    float amax = 0.f;
+#pragma unroll 8
+    for (int d = lane; d < hidden; d += 32) amax = fmaxf(amax, fabsf(bf16_round_f(to_float(src[d]))));
+#pragma unroll
+    for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const int shift = shift_of(amax);
+    const float scale = __uint_as_float(uint32_t(127 - shift) << 23);
+#pragma unroll 8
+    for (int d = lane; d < hidden; d += 32) dst[d] = __float2half_rn(bf16_round_f(to_float(src[d])) * scale);
+    if (lane == 0) xshift[token] = shift;
+}
+
 // fp16 copy of activation rows for the expert kernels, one warp per row: the row
 // is rounded to bf16 and scaled by an exact power of two so that its largest
 // magnitude lands in [2^13, 2^14); `xshift` keeps the exponent (x = xh * 2^shift).
@@ -1476,8 +1616,26 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
     if (route_partial && route_mma_ok && tokens > kRouteTokens) {
         // more than a decode batch: tensor-core router; the streaming expert kernel (not the block-scaled one,
         // which quantises the rows itself) also wants the fp16 row copies
+        const bool want_xh = xh && !use_mx(tokens * opt.top_k);
+        if (!skip_topk && opt.experts <= 256 && opt.top_k <= 8) {
+            // one more launch: the ranges' sum, the top k, the rows per expert and the fp16 row copies
+            if (int rc = route_mma(x, logits, route_partial, tokens, stream, false)) return rc;
+            if (counts) GB_CUDA(cudaMemsetAsync(counts, 0, size_t(opt.experts) * sizeof(int), stream));
+            const unsigned blocks = unsigned((size_t(tokens) * 32 + 255) / 256);
+            const int splits = moe_route_splits(tokens);
+            if (opt.io_dtype == GARNET_B200_FP32)
+                moe_route_finish_topk_kernel<float><<<blocks, 256, 0, stream>>>(
+                    route_partial, splits, router_b_ptr, logits, selected, probs, counts, shard(), static_cast<const float*>(x),
+                    want_xh ? xh : nullptr, xshift, tokens, opt.hidden, opt.experts, opt.top_k);
+            else
+                moe_route_finish_topk_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+                    route_partial, splits, router_b_ptr, logits, selected, probs, counts, shard(),
+                    static_cast<const __nv_bfloat16*>(x), want_xh ? xh : nullptr, xshift, tokens, opt.hidden, opt.experts, opt.top_k);
+            GB_CUDA(cudaGetLastError());
+            return GARNET_B200_OK;
+        }
         if (int rc = route_mma(x, logits, route_partial, tokens, stream)) return rc;
-        if (xh && !use_mx(tokens * opt.top_k)) {
+        if (want_xh) {
             const unsigned blocks = unsigned((size_t(tokens) * 32 + 255) / 256);
             if (opt.io_dtype == GARNET_B200_FP32)
                 moe_prep_rows_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x), xh, xshift, tokens, opt.hidden);

@@ -63,6 +63,7 @@ int moe_mx_mode_of(const garnet_b200_moe_options& o);
 // view of them: later fields zero-filled, `intermediate` = this rank's share of it.
 int moe_resolve_options(const garnet_b200_moe_options* in, garnet_b200_moe_options* eff);
 size_t moe_route_partial_bytes(int tokens, int experts);
+int moe_route_splits(int tokens);   // K ranges (partial-sum planes) of the tensor-core router
 constexpr int kMxMinRowsPerExpert = 8;   // routed rows per local expert above which the block-scaled path is used
 
 struct Moe {
@@ -133,7 +134,7 @@ struct Moe {
         return mx_mode == 2 || !packed_up || (mx_mode == 1 && slots > kMxMinRowsPerExpert * local_experts());
     }
     int init_route_mma(cudaStream_t stream);
-    int route_mma(const void* x, float* logits, float* partial, int tokens, cudaStream_t stream);
+    int route_mma(const void* x, float* logits, float* partial, int tokens, cudaStream_t stream, bool finish = true);
     int combine(const float* vals, const float* probs, void* y, int tokens, cudaStream_t stream);
     int run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cudaStream_t stream);
 };

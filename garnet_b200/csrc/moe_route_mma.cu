@@ -18,7 +18,9 @@ constexpr int kRmTokens = 64;     // tokens per CTA: 4 warps x 16 rows
 constexpr int kRmExperts = 64;    // experts per CTA: 8 MMA column tiles per warp
 constexpr int kRmSlab = 64;       // K per staging step
 constexpr int kRmStride = kRmSlab + 8;   // halves per staged row: bank-conflict-free fragment reads
-constexpr int kRmSplit = 3;       // K is cut in three: three times the CTAs, partial sums added in a fixed order
+// K is cut into moe_route_splits(tokens) ranges (grid z): that many times the CTAs, partial sums added in a
+// fixed order.  Few tokens make few token tiles, so they get more ranges.
+int moe_route_splits(int tokens) { return tokens <= 512 ? 9 : 3; }
 
 __global__ void moe_router_split_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ w3, size_t count)
 {
@@ -49,8 +51,8 @@ __device__ __forceinline__ uint32_t rm_pack2<__nv_bfloat16>(const __nv_bfloat16*
     return *reinterpret_cast<const uint32_t*>(p);
 }
 
-// grid = (token tiles, expert tiles, K thirds); 128 threads.  hidden % 64 == 0.
-// partial[z][t][e] = sum over the K range of third z.
+// grid = (token tiles, expert tiles, K ranges); 128 threads.  hidden % 64 == 0.
+// partial[z][t][e] = sum over K range z.
 template <typename XT>
 __global__ void __launch_bounds__(128)
 moe_route_mma_kernel(const XT* __restrict__ x, const __nv_bfloat16* __restrict__ w3, float* __restrict__ partial,
@@ -70,7 +72,7 @@ moe_route_mma_kernel(const XT* __restrict__ x, const __nv_bfloat16* __restrict__
         for (int q = 0; q < 4; ++q) acc[n][q] = 0.f;
 
     const int slabs = hidden / kRmSlab;
-    const int k_begin = int(blockIdx.z) * slabs / kRmSplit * kRmSlab, k_end = int(blockIdx.z + 1) * slabs / kRmSplit * kRmSlab;
+    const int k_begin = int(blockIdx.z) * slabs / int(gridDim.z) * kRmSlab, k_end = int(blockIdx.z + 1) * slabs / int(gridDim.z) * kRmSlab;
     // The next slab's global loads are issued into registers before the current slab's
     // MMAs, so that their latency is covered by the math.
     constexpr int kXPer = kRmTokens * (kRmSlab / 2) / 128;          // 16 words of x per thread
@@ -145,9 +147,9 @@ moe_route_mma_kernel(const XT* __restrict__ x, const __nv_bfloat16* __restrict__
     }
 }
 
-// logits = bf16(p0 + p1 + p2 + b), the thirds added in this order.
+// logits = bf16(p0 + p1 + ... + b), the ranges added in this order.
 __global__ void moe_route_finish_kernel(const float* __restrict__ partial, const float* __restrict__ rb,
-                                        float* __restrict__ logits, int tokens, int experts)
+                                        float* __restrict__ logits, int tokens, int experts, int splits)
 {
     pdl_launch_dependents();
     pdl_wait();
@@ -156,11 +158,11 @@ __global__ void moe_route_finish_kernel(const float* __restrict__ partial, const
     if (i >= n) return;
     float v = partial[i];
 #pragma unroll
-    for (int z = 1; z < kRmSplit; ++z) v += partial[z * n + i];
+    for (int z = 1; z < splits; ++z) v += partial[z * n + i];
     logits[i] = bf16_round_f(v + rb[i % experts]);
 }
 
-size_t moe_route_partial_bytes(int tokens, int experts) { return size_t(kRmSplit) * tokens * experts * sizeof(float); }
+size_t moe_route_partial_bytes(int tokens, int experts) { return size_t(moe_route_splits(tokens)) * tokens * experts * sizeof(float); }
 
 int Moe::init_route_mma(cudaStream_t stream)
 {
@@ -174,11 +176,12 @@ int Moe::init_route_mma(cudaStream_t stream)
     return GARNET_B200_OK;
 }
 
-int Moe::route_mma(const void* x, float* logits, float* partial, int tokens, cudaStream_t stream)
+int Moe::route_mma(const void* x, float* logits, float* partial, int tokens, cudaStream_t stream, bool finish)
 {
+    const int splits = moe_route_splits(tokens);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned((tokens + kRmTokens - 1) / kRmTokens), unsigned((opt.experts + kRmExperts - 1) / kRmExperts),
-                       kRmSplit);
+                       unsigned(splits));
     cfg.blockDim = dim3(128);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -192,11 +195,12 @@ int Moe::route_mma(const void* x, float* logits, float* partial, int tokens, cud
     else
         GB_CUDA(cudaLaunchKernelEx(&cfg, moe_route_mma_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x),
                                    (const __nv_bfloat16*)router_w3, partial, tokens, opt.hidden, opt.experts));
+    if (!finish) return GARNET_B200_OK;   // the caller's own kernel adds the ranges up
     const size_t n = size_t(tokens) * opt.experts;
     cfg.gridDim = dim3(unsigned((n + 255) / 256));
     cfg.blockDim = dim3(256);
     GB_CUDA(cudaLaunchKernelEx(&cfg, moe_route_finish_kernel, (const float*)partial, router_b_ptr, logits, tokens,
-                               opt.experts));
+                               opt.experts, splits));
     return GARNET_B200_OK;
 }
 
