@@ -1103,27 +1103,11 @@ __global__ void __launch_bounds__(kMoeWarps * 32, kMoeCtasPerSm) moe_stream_kern
 #endif
             const int nch = min(kMoeSegChunks, p.chunks - seg * kMoeSegChunks);
             // the activations of this copy's columns first: they do not depend on the weights
-            // Plain loads (cached in L1): the rows were written by the kernel before this one, which may still
-            // have been running when this one started.
-            uint4 xa[kMoeSegChunks], xb[kMoeSegChunks];
+            // The slots' activations are read where they are used, by plain loads (cached in L1; three CTAs per SM
+            // would leave an L1 too small for them): the rows were written by the kernel before this one, which
+            // may still have been running when this one started.
             const uint8_t* xseg = xg + size_t(seg) * (kMoeSegChunks * 128);   // 64 columns = 128 bytes of x
-            if (nch == kMoeSegChunks && (seg + 1) * (kMoeSegChunks * 128) <= row_bytes) {
-#pragma unroll
-                for (int c = 0; c < kMoeSegChunks; ++c) {
-                    xa[c] = *reinterpret_cast<const uint4*>(xseg + c * 128);
-                    xb[c] = *reinterpret_cast<const uint4*>(xseg + c * 128 + 64);
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < kMoeSegChunks; ++c) {
-                    xa[c] = xb[c] = make_uint4(0, 0, 0, 0);
-                    const int off = (seg * kMoeSegChunks + c) * 128 + t * 16;
-                    if (c < nch) {
-                        if (off + 16 <= row_bytes) xa[c] = *reinterpret_cast<const uint4*>(xseg + c * 128);
-                        if (off + 80 <= row_bytes) xb[c] = *reinterpret_cast<const uint4*>(xseg + c * 128 + 64);
-                    }
-                }
-            }
+            const bool xfast = nch == kMoeSegChunks && (seg + 1) * (kMoeSegChunks * 128) <= row_bytes;
 #ifdef GB_MOE_TRACE
             const long long tw0 = clock64();
             if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 89 : 92] += (unsigned long long)(tw0 - ts0);
@@ -1139,14 +1123,23 @@ __global__ void __launch_bounds__(kMoeWarps * 32, kMoeCtasPerSm) moe_stream_kern
             if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 84 : 86] += (unsigned long long)(tw1 - tw0);
 #endif
             const uint8_t* sbase = ring + stage * kMoeSegBytes;
-            if (nch == kMoeSegChunks) {   // the common case as one straight run of instructions
+            if (xfast) {   // the common case as one straight run of instructions
 #pragma unroll
-                for (int c = 0; c < kMoeSegChunks; ++c)
-                    moe_chunk_math<kCareful>(sbase + c * kMxChunkBytes, lane, g, xa[c], xb[c], acc);
+                for (int c = 0; c < kMoeSegChunks; ++c) {
+                    const uint4 xa = *reinterpret_cast<const uint4*>(xseg + c * 128);
+                    const uint4 xb = *reinterpret_cast<const uint4*>(xseg + c * 128 + 64);
+                    moe_chunk_math<kCareful>(sbase + c * kMxChunkBytes, lane, g, xa, xb, acc);
+                }
             } else {
 #pragma unroll
                 for (int c = 0; c < kMoeSegChunks; ++c)
-                    if (c < nch) moe_chunk_math<kCareful>(sbase + c * kMxChunkBytes, lane, g, xa[c], xb[c], acc);
+                    if (c < nch) {
+                        uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
+                        const int off = (seg * kMoeSegChunks + c) * 128 + t * 16;
+                        if (off + 16 <= row_bytes) xa = *reinterpret_cast<const uint4*>(xseg + c * 128);
+                        if (off + 80 <= row_bytes) xb = *reinterpret_cast<const uint4*>(xseg + c * 128 + 64);
+                        moe_chunk_math<kCareful>(sbase + c * kMxChunkBytes, lane, g, xa, xb, acc);
+                    }
             }
             // every lane has read this ring slot: lane 0 asks for the copy that reuses it
             __syncwarp();
