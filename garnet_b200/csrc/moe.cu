@@ -855,7 +855,10 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
 // ------------------------------------------------- streaming expert kernel
 
 
-constexpr int kMoeWarps = 8;                       // warps per CTA; each streams its own strips through its own ring
+#ifndef GB_MOE_WARPS
+#define GB_MOE_WARPS 8
+#endif
+constexpr int kMoeWarps = GB_MOE_WARPS;                       // warps per CTA; each streams its own strips through its own ring
 #ifndef GB_MOE_STAGES
 #define GB_MOE_STAGES 3
 #endif
