@@ -140,9 +140,25 @@ def test_packed_expert_matrices_decode_bit_exact(h, inter):
 
 
 @pytest.mark.parametrize("tokens", [1, 3, 17, 65])
-@pytest.mark.parametrize("h,inter", [(32, 32), (96, 64)])
+@pytest.mark.parametrize("h,inter", [(32, 32), (96, 64), (128, 64)])   # hidden 128: the tensor-core router's shapes
 def test_reference_fixtures(tokens, h, inter):
     run_and_compare(reference_fixture(tokens, h, inter), 0.002)
+
+
+@pytest.mark.parametrize("tokens", [9, 40, 200])
+def test_tensor_core_router_on_synthetic_layers(tokens):
+    """Above a decode batch the router runs on the tensor cores (hidden a multiple of 64) and one kernel adds its
+    K ranges, picks the top k, counts the rows and writes the fp16 row copies: random layers, both io types,
+    whole and expert-sharded."""
+    case = synth.moe_layer(tokens, 128, 96, experts=16, topk=4, seed=tokens, bias_scale=0.1)
+    tol = 0.002 if tokens * 4 <= 8 * 16 else 0.004   # more than 8 rows per expert: the block-scaled kernels' bound
+    run_and_compare(case, tol)
+    x = dev(case["x"])
+    y32 = build(case).run(x)
+    y16 = build(case, io_dtype=torch.bfloat16).run(x.bfloat16())
+    assert torch.equal(y32.bfloat16(), y16)
+    parts = [build(case, ep_rank=r, ep_world=4).run(x).cpu().numpy() for r in range(4)]
+    assert_close(oracle.bf16_round(sum(parts)), y32.cpu().numpy(), tol, "four-rank sum")
 
 
 @pytest.mark.parametrize("tokens,h,inter,tied", [(65, 96, 64, True), (513, 32, 32, True), (128, 96, 64, False),
