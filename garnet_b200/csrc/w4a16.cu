@@ -599,19 +599,23 @@ int garnet_b200_w4a16_batch_create(const garnet_b200_w4a16_t* handles, const voi
     GB_CUDA(cudaMalloc(&b->y_stage, y_total));
     if (ws_max) GB_CUDA(cudaMalloc(&b->ws, ws_max));   // the calls run one after the other: one workspace serves them all
     b->ws_bytes = ws_max;
+    // Calls that all have the same small batch run as one list (one launch for the lot).
+    bool one_list = true;
+    for (const HostBatch::Call& c : b->calls)
+        if (c.m != b->calls[0].m || c.m > c.h->max_rows_per_launch) one_list = false;
+    // The list kernel writes pinned, mapped output buffers itself, strip by strip while the pass runs (the
+    // writes cross PCIe under the rest of the pass); the other launches write device staging that one kernel
+    // copies out at the end.
+    const bool direct = one_list;
     std::vector<ScatterEntry> table;
     for (const HostBatch::Call& c : b->calls)
-        if (c.y_alias)
+        if (c.y_alias && !direct)
             table.push_back({b->y_stage + c.y_off, static_cast<uint8_t*>(c.y_alias), size_t(c.m) * c.h->geo.rows * 2});
     b->table_count = int(table.size());
     if (b->table_count) {
         GB_CUDA(cudaMalloc(&b->table, table.size() * sizeof(ScatterEntry)));
         GB_CUDA(cudaMemcpy(b->table, table.data(), table.size() * sizeof(ScatterEntry), cudaMemcpyHostToDevice));
     }
-    // Calls that all have the same small batch run as one list (one launch for the lot).
-    bool one_list = true;
-    for (const HostBatch::Call& c : b->calls)
-        if (c.m != b->calls[0].m || c.m > c.h->max_rows_per_launch) one_list = false;
     if (one_list) {
         std::vector<garnet_b200_w4a16_t> hs;
         std::vector<const void*> dxs;
@@ -619,7 +623,7 @@ int garnet_b200_w4a16_batch_create(const garnet_b200_w4a16_t* handles, const voi
         for (const HostBatch::Call& c : b->calls) {
             hs.push_back(reinterpret_cast<garnet_b200_w4a16_t>(c.h));
             dxs.push_back(b->x_stage + b->xs[c.x_slot].off);
-            dys.push_back(b->y_stage + c.y_off);
+            dys.push_back(c.y_alias ? c.y_alias : static_cast<void*>(b->y_stage + c.y_off));
         }
         if (int rc = garnet_b200_w4a16_list_create(hs.data(), dxs.data(), dys.data(), nullptr, count, b->calls[0].m, &b->list))
             return rc;
