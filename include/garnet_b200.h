@@ -216,7 +216,8 @@ int garnet_b200_w4a16_run_host_async(garnet_b200_w4a16_t h, const void* h_x, voi
  * dependent launches), and writes all outputs to their host buffers with one kernel
  * (pinned, mapped buffers) or one copy each (pageable buffers); the outputs are
  * complete once `stream` has been synchronised.  When every call has the same batch of
- * at most 16 rows the linears run as one garnet_b200_w4a16_list launch.  Every h_xs[i]
+ * at most 16 rows the linears run as one garnet_b200_w4a16_list launch, which writes
+ * pinned, mapped output buffers itself while the pass runs.  Every h_xs[i]
  * and h_ys[i] must stay allocated, with unchanged pinning, until batch_destroy: the
  * device aliases of pinned outputs are taken at create time.  The reference's CPU backend calls
  * Q4Q8Linear::Forward once per operator (q4q8_linear.cpp:315-389); this is the same
