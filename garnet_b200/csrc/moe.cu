@@ -807,13 +807,23 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
 {
     const int e = blockIdx.x;
     __shared__ int s_offset, s_warp[32], s_running;
-    if (threadIdx.x == 0) {
-        int off = 0, tk = 0, tp = 0;
-        for (int q = 0; q < e; ++q) {
-            off += counts[q];
-            tk += (counts[q] + rows_per_task - 1) / rows_per_task;
-            if (tile_rows) tp += (counts[q] + tile_rows - 1) / tile_rows;
+    // rows, tasks and row tiles of the experts before this one: warp 0 adds them up, a slice per lane
+    int off = 0, tk = 0, tp = 0;
+    if (threadIdx.x < 32) {
+        for (int q = threadIdx.x; q < e; q += 32) {
+            const int c = counts[q];
+            off += c;
+            tk += (c + rows_per_task - 1) / rows_per_task;
+            if (tile_rows) tp += (c + tile_rows - 1) / tile_rows;
         }
+#pragma unroll
+        for (int d = 16; d; d >>= 1) {
+            off += __shfl_xor_sync(0xffffffffu, off, d);
+            tk += __shfl_xor_sync(0xffffffffu, tk, d);
+            tp += __shfl_xor_sync(0xffffffffu, tp, d);
+        }
+    }
+    if (threadIdx.x == 0) {
         if (tile_rows) {
             // row tiles before each expert (block-scaled path)
             tile_prefix[e] = tp;
