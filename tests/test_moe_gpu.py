@@ -189,14 +189,14 @@ def test_bf16_io_matches_fp32_carrier():
     assert torch.equal(y32.bfloat16(), y16)
 
 
-@pytest.mark.parametrize("tokens", [1, 32])
+@pytest.mark.parametrize("tokens", [1, 8, 32])
 def test_gpt_oss_120b_layer_shape(tokens):
     case = synth.moe_layer(tokens, seed=tokens)
     run_and_compare(case, 1e-2, use_mass=True)
 
 
-def test_gpt_oss_120b_layer_shape_sampled_tokens():
-    tokens = 512
+@pytest.mark.parametrize("tokens", [96, 200, 512])   # streaming kernel, near the crossover, block-scaled kernel
+def test_gpt_oss_120b_layer_shape_sampled_tokens(tokens):
     case = synth.moe_layer(tokens, seed=7, bias_scale=0.05)
     moe = build(case)
     x = dev(case["x"])
