@@ -954,6 +954,120 @@ __device__ __forceinline__ void moe_chunk_math(const uint8_t* st, int lane, int 
     acc[3] = fmaf(t1[3], f1_hi, acc[3]);
 }
 
+// What a lane keeps about the task (up to 8 routed slots of one expert) it is working on.
+struct MoeTaskLane {
+    int expert = 0, rows = 0;
+    int slot0 = -1, slot1 = -1, shift0 = 0, shift1 = 0;   // the two slots (2t, 2t + 1) this lane finishes
+    const uint8_t* xg = nullptr;                           // this lane's activation row (row g of the task), at column 8t
+};
+
+template <bool kUp>
+__device__ __forceinline__ void moe_task_lane(const MoeStreamParams& p, const int4* s_tasks, const int* s_sorted, int task,
+                                              int g, int t, MoeTaskLane& tl)
+{
+    const int4 tk = task < kMoeListCache ? s_tasks[task] : __ldcg(&p.tasks[task]);
+    tl.expert = tk.x;
+    tl.rows = tk.z;
+    auto slot_at = [&](int m) {
+        const int at = tk.y + m;
+        return at < kMoeListCache ? s_sorted[at] : __ldcg(&p.sorted[at]);
+    };
+    // a lane whose slot g is beyond the task's rows reads the first row: the MMA column it feeds is never
+    // stored, and the loop needs no test
+    const int sg = slot_at(g < tl.rows ? g : 0);
+    const size_t src_row = kUp ? size_t(sg / p.topk) : size_t(sg);
+    tl.xg = reinterpret_cast<const uint8_t*>(p.act_in + src_row * p.k) + t * 16;
+    tl.slot0 = 2 * t < tl.rows ? slot_at(2 * t) : -1;
+    tl.slot1 = 2 * t + 1 < tl.rows ? slot_at(2 * t + 1) : -1;
+    tl.shift0 = tl.shift1 = 0;
+    if (kUp) {
+        if (tl.slot0 >= 0) tl.shift0 = __ldg(&p.xshift[tl.slot0 / p.topk]);
+        if (tl.slot1 >= 0) tl.shift1 = __ldg(&p.xshift[tl.slot1 / p.topk]);
+    }
+}
+
+// The two bias values a lane needs at the end of a strip (requested at its start).
+template <bool kUp>
+__device__ __forceinline__ void moe_strip_bias(const MoeStreamParams& p, const MoeTaskLane& tl, int strip, int g, float& bias0,
+                                               float& bias1)
+{
+    const int ebias = p.bias_by_global ? tl.expert : (tl.expert - p.expert_base) / p.expert_div;
+    bias0 = bias1 = 0.f;
+    if (kUp) {
+        const int i = strip * 8 + row_of_g(g);
+        if (2 * i + 1 < p.rows) {
+            const float* b = p.bias + size_t(ebias) * p.rows + 2 * i;
+            bias0 = __ldg(b), bias1 = __ldg(b + 1);
+        }
+    } else {
+        const int d = strip * 16 + row_of_g(g);
+        if (d < p.rows) bias0 = __ldg(&p.bias[size_t(ebias) * p.rows + d]);
+        if (d + 8 < p.rows) bias1 = __ldg(&p.bias[size_t(ebias) * p.rows + d + 8]);
+    }
+}
+
+// End of a strip.  acc[0..1]: strip row R(g), slots 2t, 2t+1; acc[2..3]: strip row R(g)+8.
+template <bool kUp>
+__device__ __forceinline__ void moe_strip_finish(const MoeStreamParams& p, const MoeTaskLane& tl, int strip, int g,
+                                                 const float (&acc)[4], float bias0, float bias1)
+{
+    if (kUp) {
+        // rows R(g) and R(g)+8 are the gate and the up value of one intermediate channel
+        const int i = strip * 8 + row_of_g(g);
+        if (2 * i + 1 < p.rows) {
+#pragma unroll
+            for (int par = 0; par < 2; ++par) {
+                const int slot = par ? tl.slot1 : tl.slot0;
+                if (slot < 0) continue;
+                const float sc2 = __uint_as_float(uint32_t(127 + (par ? tl.shift1 : tl.shift0)) << 23);   // 2^shift
+                float gate = fminf(bf16_round_f(bf16_round_f(acc[par] * sc2) + bias0), p.limit);
+                const float up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(acc[par + 2] * sc2) + bias1)));
+                const float sig = bf16_round_f(1.f / (1.f + expf(-bf16_round_f(1.702f * gate))));
+                const float glu = bf16_round_f(gate * sig);
+                p.act_out[size_t(slot) * (p.rows / 2) + i] = __float2half_rn(bf16_round_f(glu * bf16_round_f(up + 1.f)));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int slot = (q & 1) ? tl.slot1 : tl.slot0;
+            const int d = strip * 16 + row_of_g(g) + 8 * (q >> 1);
+            if (slot >= 0 && d < p.rows)
+                p.vals_out[size_t(slot) * p.rows + d] = bf16_round_f(bf16_round_f(acc[q]) + ((q >> 1) ? bias1 : bias0));
+        }
+    }
+}
+
+// The chunks of one ring slot (a copy of up to kMoeSegChunks chunks of a strip, starting at chunk seg * kMoeSegChunks)
+// times the task's slots, added to acc.  The slots' activations are read where they are used, by plain loads (cached
+// in L1; three CTAs per SM would leave an L1 too small for them): the rows were written by the kernel before this
+// one, which may still have been running when this one started.
+template <bool kCareful>
+__device__ __forceinline__ void moe_seg_math(const uint8_t* sbase, const uint8_t* xg, int seg, int nch, int row_bytes, int lane,
+                                             float (&acc)[4])
+{
+    const int g = lane >> 2, t = lane & 3;
+    const uint8_t* xseg = xg + size_t(seg) * (kMoeSegChunks * 128);   // 64 columns = 128 bytes of x
+    if (nch == kMoeSegChunks && (seg + 1) * (kMoeSegChunks * 128) <= row_bytes) {   // the common case as one straight run
+#pragma unroll
+        for (int c = 0; c < kMoeSegChunks; ++c) {
+            const uint4 xa = *reinterpret_cast<const uint4*>(xseg + c * 128);
+            const uint4 xb = *reinterpret_cast<const uint4*>(xseg + c * 128 + 64);
+            moe_chunk_math<kCareful>(sbase + c * kMxChunkBytes, lane, g, xa, xb, acc);
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < kMoeSegChunks; ++c)
+            if (c < nch) {
+                uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
+                const int off = (seg * kMoeSegChunks + c) * 128 + t * 16;
+                if (off + 16 <= row_bytes) xa = *reinterpret_cast<const uint4*>(xseg + c * 128);
+                if (off + 80 <= row_bytes) xb = *reinterpret_cast<const uint4*>(xseg + c * 128 + 64);
+                moe_chunk_math<kCareful>(sbase + c * kMxChunkBytes, lane, g, xa, xb, acc);
+            }
+    }
+}
+
 // Persistent CTAs over the flattened list of (task, strip) items; a task is up to 8 routed slots of
 // one expert, a strip 16 rows of that expert's matrix (codes and scales together, contiguous).  A CTA
 // owns a contiguous range of items and its warps take them in turn; every warp works alone: lane 0
@@ -1062,50 +1176,19 @@ __global__ void __launch_bounds__(kMoeWarps * 32, kMoeCtasPerSm) moe_stream_kern
     const int row_bytes = p.k * 2;
     bool ok = true;
     int stage = 0, phase = 0, con = 0;
-    int cur_task = -1, task_rows = 0, task_expert = 0;
-    int slot0 = 0, slot1 = 0, shift0 = 0, shift1 = 0;   // the two slots (2t, 2t + 1) this lane finishes
-    const uint8_t* xg = nullptr;                          // this lane's activation row (row g of the task), at column 8t
+    int cur_task = -1;
+    MoeTaskLane tl;
     for (int item = 0; item < my_items && ok; ++item) {
 #ifdef GB_MOE_TRACE
         const long long ti0 = clock64();
 #endif
         if (task != cur_task) {
-            const int4 tk = task < kMoeListCache ? s_tasks[task] : __ldcg(&p.tasks[task]);
-            task_expert = tk.x;
-            task_rows = tk.z;
-            auto slot_at = [&](int m) {
-                const int at = tk.y + m;
-                return at < kMoeListCache ? s_sorted[at] : __ldcg(&p.sorted[at]);
-            };
-            {
-                // a lane whose slot g is beyond the task's rows reads the first row: the MMA column it feeds is
-                // never stored, and the loop needs no test
-                const int sg = slot_at(g < task_rows ? g : 0);
-                const size_t src_row = kUp ? size_t(sg / p.topk) : size_t(sg);
-                xg = reinterpret_cast<const uint8_t*>(p.act_in + src_row * p.k) + t * 16;
-            }
-            slot0 = 2 * t < task_rows ? slot_at(2 * t) : -1;
-            slot1 = 2 * t + 1 < task_rows ? slot_at(2 * t + 1) : -1;
-            if (kUp) {
-                shift0 = slot0 >= 0 ? __ldg(&p.xshift[slot0 / p.topk]) : 0;
-                shift1 = slot1 >= 0 ? __ldg(&p.xshift[slot1 / p.topk]) : 0;
-            }
+            moe_task_lane<kUp>(p, s_tasks, s_sorted, task, g, t, tl);
             cur_task = task;
         }
         // this strip's bias values are requested now and used in the epilogue
-        const int ebias = p.bias_by_global ? task_expert : (task_expert - p.expert_base) / p.expert_div;
-        float bias0 = 0.f, bias1 = 0.f;
-        if (kUp) {
-            const int i = strip * 8 + row_of_g(g);
-            if (2 * i + 1 < p.rows) {
-                const float* b = p.bias + size_t(ebias) * p.rows + 2 * i;
-                bias0 = __ldg(b), bias1 = __ldg(b + 1);
-            }
-        } else {
-            const int d = strip * 16 + row_of_g(g);
-            if (d < p.rows) bias0 = __ldg(&p.bias[size_t(ebias) * p.rows + d]);
-            if (d + 8 < p.rows) bias1 = __ldg(&p.bias[size_t(ebias) * p.rows + d + 8]);
-        }
+        float bias0, bias1;
+        moe_strip_bias<kUp>(p, tl, strip, g, bias0, bias1);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #ifdef GB_MOE_TRACE
         if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 88 : 91] += (unsigned long long)(clock64() - ti0);
@@ -1115,12 +1198,6 @@ __global__ void __launch_bounds__(kMoeWarps * 32, kMoeCtasPerSm) moe_stream_kern
             const long long ts0 = clock64();
 #endif
             const int nch = min(kMoeSegChunks, p.chunks - seg * kMoeSegChunks);
-            // the activations of this copy's columns first: they do not depend on the weights
-            // The slots' activations are read where they are used, by plain loads (cached in L1; three CTAs per SM
-            // would leave an L1 too small for them): the rows were written by the kernel before this one, which
-            // may still have been running when this one started.
-            const uint8_t* xseg = xg + size_t(seg) * (kMoeSegChunks * 128);   // 64 columns = 128 bytes of x
-            const bool xfast = nch == kMoeSegChunks && (seg + 1) * (kMoeSegChunks * 128) <= row_bytes;
 #ifdef GB_MOE_TRACE
             const long long tw0 = clock64();
             if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 89 : 92] += (unsigned long long)(tw0 - ts0);
@@ -1135,25 +1212,7 @@ __global__ void __launch_bounds__(kMoeWarps * 32, kMoeCtasPerSm) moe_stream_kern
             const long long tw1 = clock64();
             if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 84 : 86] += (unsigned long long)(tw1 - tw0);
 #endif
-            const uint8_t* sbase = ring + stage * kMoeSegBytes;
-            if (xfast) {   // the common case as one straight run of instructions
-#pragma unroll
-                for (int c = 0; c < kMoeSegChunks; ++c) {
-                    const uint4 xa = *reinterpret_cast<const uint4*>(xseg + c * 128);
-                    const uint4 xb = *reinterpret_cast<const uint4*>(xseg + c * 128 + 64);
-                    moe_chunk_math<kCareful>(sbase + c * kMxChunkBytes, lane, g, xa, xb, acc);
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < kMoeSegChunks; ++c)
-                    if (c < nch) {
-                        uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
-                        const int off = (seg * kMoeSegChunks + c) * 128 + t * 16;
-                        if (off + 16 <= row_bytes) xa = *reinterpret_cast<const uint4*>(xseg + c * 128);
-                        if (off + 80 <= row_bytes) xb = *reinterpret_cast<const uint4*>(xseg + c * 128 + 64);
-                        moe_chunk_math<kCareful>(sbase + c * kMxChunkBytes, lane, g, xa, xb, acc);
-                    }
-            }
+            moe_seg_math<kCareful>(ring + stage * kMoeSegBytes, tl.xg, seg, nch, row_bytes, lane, acc);
             // every lane has read this ring slot: lane 0 asks for the copy that reuses it
             __syncwarp();
             if (iss < total_segs) {
@@ -1170,32 +1229,7 @@ __global__ void __launch_bounds__(kMoeWarps * 32, kMoeCtasPerSm) moe_stream_kern
 #ifdef GB_MOE_TRACE
         const long long te0 = clock64();
 #endif
-        // ---- end of a strip.  acc[0..1]: strip row R(g), slots 2t, 2t+1; acc[2..3]: strip row R(g)+8.
-        if (kUp) {
-            // rows R(g) and R(g)+8 are the gate and the up value of one intermediate channel
-            const int i = strip * 8 + row_of_g(g);
-            if (2 * i + 1 < p.rows) {
-#pragma unroll
-                for (int par = 0; par < 2; ++par) {
-                    const int slot = par ? slot1 : slot0;
-                    if (slot < 0) continue;
-                    const float sc2 = __uint_as_float(uint32_t(127 + (par ? shift1 : shift0)) << 23);   // 2^shift
-                    float gate = fminf(bf16_round_f(bf16_round_f(acc[par] * sc2) + bias0), p.limit);
-                    const float up = fminf(p.limit, fmaxf(-p.limit, bf16_round_f(bf16_round_f(acc[par + 2] * sc2) + bias1)));
-                    const float sig = bf16_round_f(1.f / (1.f + expf(-bf16_round_f(1.702f * gate))));
-                    const float glu = bf16_round_f(gate * sig);
-                    p.act_out[size_t(slot) * (p.rows / 2) + i] = __float2half_rn(bf16_round_f(glu * bf16_round_f(up + 1.f)));
-                }
-            }
-        } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int slot = (q & 1) ? slot1 : slot0;
-                const int d = strip * 16 + row_of_g(g) + 8 * (q >> 1);
-                if (slot >= 0 && d < p.rows)
-                    p.vals_out[size_t(slot) * p.rows + d] = bf16_round_f(bf16_round_f(acc[q]) + ((q >> 1) ? bias1 : bias0));
-            }
-        }
+        moe_strip_finish<kUp>(p, tl, strip, g, acc, bias0, bias1);
         if (threadIdx.x == 0 && item < 20) GB_MTRACE(kTr + 8 + item);
 #ifdef GB_MOE_TRACE
         if (threadIdx.x == 0 && blockIdx.x == 7) g_moe_trace[kUp ? 90 : 93] += (unsigned long long)(clock64() - te0);
@@ -1715,8 +1749,9 @@ int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStrea
     const int ctas_per_sm = kMoeCtasPerSm;   // as the kernel's launch bounds say
     // upper bound of (task, strip) items: every slot its own task
     const long long max_items = (long long)tokens * topk * geo.strips;
+    const long long grid = std::max<long long>(1, std::min<long long>(max_items, (long long)kSmCount * ctas_per_sm));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(unsigned(std::max<long long>(1, std::min<long long>(max_items, (long long)kSmCount * ctas_per_sm))));
+    cfg.gridDim = dim3(unsigned(grid));
     cfg.blockDim = dim3(kMoeWarps * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
