@@ -2193,7 +2193,7 @@ int garnet_b200_moe_route_ws(garnet_b200_moe_t hh, const void* d_x, int* d_selec
     if (misaligned16(d_x) || (reinterpret_cast<uintptr_t>(d_workspace) & 255) ||
         ((reinterpret_cast<uintptr_t>(d_selected) | reinterpret_cast<uintptr_t>(d_probs) | reinterpret_cast<uintptr_t>(d_logits)) & 3))
         return fail(GARNET_B200_INVALID_VALUE, "moe_route_ws: x must be 16-byte and the workspace 256-byte aligned");
-    if (workspace_bytes < moe_route_partial_bytes(tokens, h->opt.experts))
+    if (workspace_bytes < moe_route_partial_need(tokens, h->opt.experts))
         return fail(GARNET_B200_INVALID_VALUE, "moe_route_ws: workspace too small");
     // the same call the one-call operator makes: identical logits, selection and probabilities
     return h->route(d_x, d_logits, d_selected, d_probs, nullptr, nullptr, tokens, static_cast<cudaStream_t>(stream), false,

@@ -9,6 +9,8 @@
 // the only difference from a serial fp32 dot product is the order of the additions.
 // 3 GFLOP at 4096 tokens of gpt-oss-120b: 281 us on the fp32 pipe before, about a
 // tenth of that here.
+#include <algorithm>
+
 #include "moe.h"
 #include "common.cuh"
 
@@ -162,7 +164,14 @@ __global__ void moe_route_finish_kernel(const float* __restrict__ partial, const
     logits[i] = bf16_round_f(v + rb[i % experts]);
 }
 
-size_t moe_route_partial_bytes(int tokens, int experts) { return size_t(moe_route_splits(tokens)) * tokens * experts * sizeof(float); }
+// What a call with `tokens` tokens writes, and what a caller sizing for up to `tokens` tokens must provide (the
+// number of K ranges drops above 512 tokens, so the second is kept monotone).
+size_t moe_route_partial_need(int tokens, int experts) { return size_t(moe_route_splits(tokens)) * tokens * experts * sizeof(float); }
+size_t moe_route_partial_bytes(int tokens, int experts)
+{
+    const size_t need = moe_route_partial_need(tokens, experts);
+    return tokens > 512 ? std::max(need, moe_route_partial_need(512, experts)) : need;
+}
 
 int Moe::init_route_mma(cudaStream_t stream)
 {

@@ -268,3 +268,21 @@ def test_moe_options_of_the_first_struct_version_are_accepted():
     assert L.garnet_b200_moe_workspace(ctypes.byref(opt2), 8, ctypes.byref(n_new)) == 1
     opt2.tp_rank, opt2.intermediate = 0, 96       # 96 / 2 is not a whole number of 32-column groups
     assert L.garnet_b200_moe_workspace(ctypes.byref(opt2), 8, ctypes.byref(n_new)) == 1
+
+
+def test_moe_workspace_sizes_never_shrink_with_the_token_count():
+    """A caller sizes its workspaces once for its largest batch (garnet_b200_moe_ep_create does): a smaller batch
+    must fit in them, also across the token counts where the router changes its number of K ranges."""
+    from garnet_b200.moe import MoeOptions
+    opt = MoeOptions(abi=1, struct_size=ctypes.sizeof(MoeOptions), hidden=2880, intermediate=2880, experts=128, top_k=4,
+                     io_dtype=_lib.BF16, limit=7.0)
+    L = garnet_b200.lib()
+    n = ctypes.c_size_t(0)
+    last_route = last_run = 0
+    for tokens in list(range(1, 40)) + list(range(480, 560)) + [1000, 1024, 4096, 8192]:
+        assert L.garnet_b200_moe_route_workspace(ctypes.byref(opt), tokens, ctypes.byref(n)) == 0
+        assert n.value >= last_route, tokens
+        last_route = n.value
+        assert L.garnet_b200_moe_workspace(ctypes.byref(opt), tokens, ctypes.byref(n)) == 0
+        assert n.value >= last_run, tokens
+        last_run = n.value
