@@ -806,7 +806,7 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
                 int* __restrict__ tile_prefix)
 {
     const int e = blockIdx.x;
-    __shared__ int s_offset, s_warp[32], s_running;
+    __shared__ int s_offset, s_warp[32];
     // rows, tasks and row tiles of the experts before this one: warp 0 adds them up, a slice per lane
     int off = 0, tk = 0, tp = 0;
     if (threadIdx.x < 32) {
@@ -830,7 +830,6 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
             if (e == experts - 1) tile_prefix[experts] = tp + (counts[e] + tile_rows - 1) / tile_rows;
         }
         s_offset = off;
-        s_running = 0;
         offsets[e] = off;
         const int mine = counts[e];
         for (int b = 0; b * rows_per_task < mine; ++b)
@@ -842,24 +841,25 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
     }
     __syncthreads();
     if (counts[e] == 0) return;
+    // Stable order of this expert's slots: a thread counts its own run of consecutive slots, one scan over the
+    // threads gives every run its place, and the thread writes its run's hits in slot order.
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int base = 0; base < slots; base += blockDim.x) {
-        const int i = base + threadIdx.x;
-        const bool hit = i < slots && selected[i] == e;
-        const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0) s_warp[warp] = __popc(ballot);
-        __syncthreads();
-        int before = s_running;
-        for (int w = 0; w < warp; ++w) before += s_warp[w];
-        if (hit) sorted[s_offset + before + __popc(ballot & ((1u << lane) - 1u))] = i;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int total = 0;
-            for (int w = 0; w < int(blockDim.x >> 5); ++w) total += s_warp[w];
-            s_running += total;
-        }
-        __syncthreads();
+    const int per = (slots + int(blockDim.x) - 1) / int(blockDim.x);
+    const int i0 = min(slots, int(threadIdx.x) * per), i1 = min(slots, i0 + per);
+    int hits = 0;
+    for (int i = i0; i < i1; ++i) hits += selected[i] == e;
+    int incl = hits;   // inclusive scan over the warp's lanes
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += v;
     }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    int before = s_offset + incl - hits;
+    for (int w = 0; w < warp; ++w) before += s_warp[w];
+    for (int i = i0; i < i1; ++i)
+        if (selected[i] == e) sorted[before++] = i;
 }
 
 // ------------------------------------------------- streaming expert kernel
