@@ -901,6 +901,7 @@ struct MoeStreamParams {
     int tasks_early;               // the task list was complete before this grid could start (see kernel)
     int slots;                     // entries of `sorted` (tokens * topk)
     int tasks_cap;                 // entries the task list has room for
+    int vals_bf16;                 // vals_out holds bf16
     float limit;
     size_t matrix_bytes;
 };
@@ -1033,7 +1034,11 @@ __device__ __forceinline__ void moe_strip_finish(const MoeStreamParams& p, const
             const int slot = (q & 1) ? tl.slot1 : tl.slot0;
             const int d = strip * 16 + row_of_g(g) + 8 * (q >> 1);
             if (slot >= 0 && d < p.rows)
-                p.vals_out[size_t(slot) * p.rows + d] = bf16_round_f(bf16_round_f(acc[q]) + ((q >> 1) ? bias1 : bias0));
+            {
+                    const float v = bf16_round_f(bf16_round_f(acc[q]) + ((q >> 1) ? bias1 : bias0));
+                    if (p.vals_bf16) reinterpret_cast<__nv_bfloat16*>(p.vals_out)[size_t(slot) * p.rows + d] = __float2bfloat16_rn(v);
+                    else p.vals_out[size_t(slot) * p.rows + d] = v;
+                }
         }
     }
 }
@@ -1274,6 +1279,50 @@ __global__ void moe_combine_kernel(const float* __restrict__ vals, const float* 
     else
         y[idx] = __float2bfloat16_rn(r);
     if (threadIdx.x == 0) GB_MTRACE(82);
+}
+
+// The same combine for Moe::run's own bf16 per-slot values: a CTA row per token, eight columns per thread (16-byte
+// loads and stores, no division per element).  hidden is a multiple of 8.
+template <typename YT>
+__global__ void __launch_bounds__(256)
+moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ vals, const float* __restrict__ probs, const int* __restrict__ selected,
+                        YT* __restrict__ y, int hidden, int topk, MoeShard sh, int round_output)
+{
+    pdl_launch_dependents();
+    pdl_wait();   // the per-slot values come from the kernel before this one
+    const int token = blockIdx.x;
+    const int d0 = (blockIdx.y * 256 + threadIdx.x) * 8;
+    if (d0 >= hidden) return;
+    float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < topk; ++j) {
+        const int slot = token * topk + j;
+        if (sh.world > 1 && !expert_is_local(selected[slot], sh)) continue;
+        const float pj = probs[slot];
+        const uint4 v = *reinterpret_cast<const uint4*>(vals + size_t(slot) * hidden + d0);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {   // one rounding per term, in router order
+            r[2 * q] = __fmaf_rn(__uint_as_float(w[q] << 16), pj, r[2 * q]);
+            r[2 * q + 1] = __fmaf_rn(__uint_as_float(w[q] & 0xffff0000u), pj, r[2 * q + 1]);
+        }
+    }
+    if (round_output) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) r[k] = bf16_round_f(r[k]);
+    }
+    YT* out = y + size_t(token) * hidden + d0;
+    if constexpr (sizeof(YT) == 4) {
+        *reinterpret_cast<float4*>(out) = make_float4(r[0], r[1], r[2], r[3]);
+        *reinterpret_cast<float4*>(out + 4) = make_float4(r[4], r[5], r[6], r[7]);
+    } else {
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(r[2 * q], r[2 * q + 1]);
+            o[q] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(out) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
 }
 
 // ------------------------------------------------------------------ handle
@@ -1727,6 +1776,7 @@ int Moe::launch_stream(bool up, const MoeWorkspacePtrs& w, int tokens, cudaStrea
     p.bias = up ? up_bias_ptr : down_bias_ptr;
     p.act_out = w.act;
     p.vals_out = w.vals;
+    p.vals_bf16 = w.vals_bf16;
     p.fault = fault_dev;
     p.k = geo.cols;
     p.rows = geo.rows;
@@ -1805,6 +1855,7 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     w.route_partial = reinterpret_cast<float*>(b + plan.route_partial);
     w.act = reinterpret_cast<__half*>(b + plan.act);
     w.vals = reinterpret_cast<float*>(b + plan.vals);
+    w.vals_bf16 = 1;   // between this call's own kernels the per-slot values (bf16-valued) travel as bf16
 
     const int slots = tokens * opt.top_k;
     const MoeShard sh = shard();
@@ -1848,14 +1899,16 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
     const size_t n = size_t(tokens) * opt.hidden;
     const int round_output = partial_output() ? 0 : 1;
     const bool streamed = true;   // both expert paths end in kernels that support a programmatic dependent launch
+    const __nv_bfloat16* vals16 = reinterpret_cast<const __nv_bfloat16*>(w.vals);
+    const dim3 cgrid(unsigned(tokens), unsigned((opt.hidden + 2047) / 2048));
+    (void)n;
     if (opt.io_dtype == GARNET_B200_FP32)
-        GB_CUDA(launch_pdl(moe_combine_kernel<float>, dim3(unsigned((n + 255) / 256)), dim3(256), 0, stream, streamed,
-                           (const float*)w.vals, (const float*)w.probs, (const int*)w.selected, static_cast<float*>(y),
-                           tokens, opt.hidden, opt.top_k, sh, round_output));
+        GB_CUDA(launch_pdl(moe_combine_rows_kernel<float>, cgrid, dim3(256), 0, stream, streamed, vals16, (const float*)w.probs,
+                           (const int*)w.selected, static_cast<float*>(y), opt.hidden, opt.top_k, sh, round_output));
     else
-        GB_CUDA(launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(unsigned((n + 255) / 256)), dim3(256), 0, stream,
-                           streamed, (const float*)w.vals, (const float*)w.probs, (const int*)w.selected,
-                           static_cast<__nv_bfloat16*>(y), tokens, opt.hidden, opt.top_k, sh, round_output));
+        GB_CUDA(launch_pdl(moe_combine_rows_kernel<__nv_bfloat16>, cgrid, dim3(256), 0, stream, streamed, vals16,
+                           (const float*)w.probs, (const int*)w.selected, static_cast<__nv_bfloat16*>(y), opt.hidden, opt.top_k, sh,
+                           round_output));
     GB_CUDA(cudaGetLastError());
     return GARNET_B200_OK;
 }

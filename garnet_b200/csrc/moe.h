@@ -40,7 +40,8 @@ struct MoeWorkspacePtrs {
     int* mx_tp;        // row tiles before each expert (block-scaled path)
     uint8_t* mx_q;     // e4m3 row pieces at tile-aligned positions: [2][q_rows][kp]
     uint8_t* mx_sf;    // their scale atoms: [tiles][kslabs][512]
-    float* route_partial;   // [3][tokens][experts] partial router sums (tensor-core router)
+    float* route_partial;   // [K ranges][tokens][experts] partial router sums (tensor-core router)
+    int vals_bf16 = 0;      // `vals` holds bf16 (the per-slot values are bf16-valued; Moe::run keeps them so between its own kernels)
     __half* act;
     float* vals;
 };

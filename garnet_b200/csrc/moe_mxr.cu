@@ -61,6 +61,7 @@ struct RxParams {
     const uint8_t* sfx;        // [row tiles][kslabs][512] activation scale atoms
     __half* act_out;           // up: [sorted position, intermediate]
     float* vals_out;           // down: [slot id, hidden]
+    int vals_bf16;             // vals_out holds bf16
     int* fault;
     int experts, rows, ntiles, kslabs;
     int expert_base, expert_div, bias_by_global;
@@ -319,7 +320,16 @@ moe_mxr_kernel(const RxParams p, const __grid_constant__ CUtensorMap w_map, cons
                             const int d = n0 + c0 + 4 * q + j;
                             vp[j] = d < p.rows ? bf16_round_f(bf16_round_f(__uint_as_float(r[4 * q + j])) + bias[d]) : 0.f;
                         }
-                        if (n0 + c0 + 4 * q + 3 < p.rows) *reinterpret_cast<float4*>(vrow + c0 + 4 * q) = v;
+                        if (p.vals_bf16) {   // the values are bf16-valued: the conversions below are exact
+                            __nv_bfloat16* vb = reinterpret_cast<__nv_bfloat16*>(p.vals_out) + size_t(p.sorted[pos]) * p.rows + n0 + c0 + 4 * q;
+                            if (n0 + c0 + 4 * q + 3 < p.rows) {
+                                const __nv_bfloat162 lo = __floats2bfloat162_rn(vp[0], vp[1]), hi = __floats2bfloat162_rn(vp[2], vp[3]);
+                                *reinterpret_cast<uint2*>(vb) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                            } else {
+                                for (int j = 0; j < 4; ++j)
+                                    if (n0 + c0 + 4 * q + j < p.rows) vb[j] = __float2bfloat16_rn(vp[j]);
+                            }
+                        } else if (n0 + c0 + 4 * q + 3 < p.rows) *reinterpret_cast<float4*>(vrow + c0 + 4 * q) = v;
                         else
                             for (int j = 0; j < 4; ++j)
                                 if (n0 + c0 + 4 * q + j < p.rows) vrow[c0 + 4 * q + j] = vp[j];
@@ -467,6 +477,7 @@ int Moe::launch_mxr_gemm(bool up, const MoeWorkspacePtrs& w, const void* q_map_p
     p.sfx = w.mx_sf;
     p.act_out = w.act;
     p.vals_out = w.vals;
+    p.vals_bf16 = w.vals_bf16;
     p.fault = fault_dev;
     p.experts = opt.experts;
     p.rows = geo.rows;
