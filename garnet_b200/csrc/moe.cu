@@ -1264,9 +1264,10 @@ __global__ void moe_combine_kernel(const float* __restrict__ vals, const float* 
     pdl_launch_dependents();
     pdl_wait();   // the per-slot values come from the kernel before this one
     if (threadIdx.x == 0) GB_MTRACE(81);
-    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= size_t(tokens) * hidden) return;
-    const int token = int(idx / hidden), d = int(idx % hidden);
+    // grid = (tokens, column blocks): no division per element
+    const int token = blockIdx.x, d = blockIdx.y * blockDim.x + threadIdx.x;
+    if (token >= tokens || d >= hidden) return;
+    const size_t idx = size_t(token) * hidden + d;
     float r = 0.f;
     for (int j = 0; j < topk; ++j) {
         const int slot = token * topk + j;
@@ -1896,12 +1897,10 @@ int Moe::run(const void* x, void* y, void* ws, size_t ws_bytes, int tokens, cuda
         if (probe_skip & 8) return GARNET_B200_OK;
 #endif
     }
-    const size_t n = size_t(tokens) * opt.hidden;
     const int round_output = partial_output() ? 0 : 1;
     const bool streamed = true;   // both expert paths end in kernels that support a programmatic dependent launch
     const __nv_bfloat16* vals16 = reinterpret_cast<const __nv_bfloat16*>(w.vals);
     const dim3 cgrid(unsigned(tokens), unsigned((opt.hidden + 2047) / 2048));
-    (void)n;
     if (opt.io_dtype == GARNET_B200_FP32)
         GB_CUDA(launch_pdl(moe_combine_rows_kernel<float>, cgrid, dim3(256), 0, stream, streamed, vals16, (const float*)w.probs,
                            (const int*)w.selected, static_cast<float*>(y), opt.hidden, opt.top_k, sh, round_output));
@@ -2005,12 +2004,11 @@ int Moe::combine(const float* vals, const float* probs, void* y, int tokens, cud
         return fail(GARNET_B200_INVALID_VALUE, "moe_combine: values and y must be 16-byte aligned");
     MoeShard all{};
     all.world = 1;
-    const size_t n = size_t(tokens) * opt.hidden;
     if (opt.io_dtype == GARNET_B200_FP32)
-        moe_combine_kernel<float><<<unsigned((n + 255) / 256), 256, 0, stream>>>(vals, probs, nullptr, static_cast<float*>(y),
-                                                                               tokens, opt.hidden, opt.top_k, all, 1);
+        moe_combine_kernel<float><<<dim3(unsigned(tokens), unsigned((opt.hidden + 255) / 256)), 256, 0, stream>>>(
+            vals, probs, nullptr, static_cast<float*>(y), tokens, opt.hidden, opt.top_k, all, 1);
     else
-        moe_combine_kernel<__nv_bfloat16><<<unsigned((n + 255) / 256), 256, 0, stream>>>(
+        moe_combine_kernel<__nv_bfloat16><<<dim3(unsigned(tokens), unsigned((opt.hidden + 255) / 256)), 256, 0, stream>>>(
             vals, probs, nullptr, static_cast<__nv_bfloat16*>(y), tokens, opt.hidden, opt.top_k, all, 1);
     GB_CUDA(cudaGetLastError());
     return GARNET_B200_OK;
