@@ -211,10 +211,11 @@ template <typename YT>
 __global__ void ep_combine_kernel(const EpDev ep, const int* __restrict__ selected, const float* __restrict__ probs,
                                   YT* __restrict__ y, int tokens)
 {
-    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;   // a pair of columns
+    // grid = (tokens, blocks of column pairs): no division per element
     const int pairs = ep.hidden / 2;
-    if (idx >= size_t(tokens) * pairs) return;
-    const int token = int(idx / pairs), c = int(idx % pairs);
+    const int token = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;   // c: a pair of columns
+    if (token >= tokens || c >= pairs) return;
+    const size_t idx = size_t(token) * pairs + c;
     const uint8_t* ret = ep.peer_base[ep.rank] + ep.ret_off;
     float r0 = 0.f, r1 = 0.f;
     for (int j = 0; j < ep.topk; ++j) {
@@ -404,13 +405,11 @@ int garnet_b200_moe_ep_run(garnet_b200_moe_ep_t ee, const void* d_x, void* d_y, 
     if (int rc = moe->run_rows(rows, row_expert, d.world * d.cap, ep->vals, ep->rows_ws, ep->rows_ws_bytes, s)) return rc;
     ep_return_kernel<<<d.world * d.cap, 128, 0, s>>>(d, ep->vals);
     ep_wait_return_kernel<<<1, 32, 0, s>>>(d);
-    const size_t pairs = size_t(tokens_local) * d.hidden / 2;
+    const dim3 cgrid(unsigned(tokens_local), unsigned((d.hidden / 2 + 255) / 256));
     if (moe->opt.io_dtype == GARNET_B200_BF16)
-        ep_combine_kernel<__nv_bfloat16><<<unsigned((pairs + 255) / 256), 256, 0, s>>>(d, ep->selected, ep->probs,
-                                                                                      static_cast<__nv_bfloat16*>(d_y), tokens_local);
+        ep_combine_kernel<__nv_bfloat16><<<cgrid, 256, 0, s>>>(d, ep->selected, ep->probs, static_cast<__nv_bfloat16*>(d_y), tokens_local);
     else
-        ep_combine_kernel<float><<<unsigned((pairs + 255) / 256), 256, 0, s>>>(d, ep->selected, ep->probs, static_cast<float*>(d_y),
-                                                                               tokens_local);
+        ep_combine_kernel<float><<<cgrid, 256, 0, s>>>(d, ep->selected, ep->probs, static_cast<float*>(d_y), tokens_local);
     GB_CUDA(cudaGetLastError());
     return GARNET_B200_OK;
 }
