@@ -1712,7 +1712,7 @@ int Moe::route(const void* x, float* logits, int* selected, float* probs, __half
             if (int rc = route_mma(x, logits, route_partial, tokens, stream, false)) return rc;
             if (counts) GB_CUDA(cudaMemsetAsync(counts, 0, size_t(opt.experts) * sizeof(int), stream));
             const unsigned blocks = unsigned((size_t(tokens) * 32 + 255) / 256);
-            const int splits = moe_route_splits(tokens);
+            const int splits = moe_route_splits(tokens, opt.experts);
             if (opt.io_dtype == GARNET_B200_FP32)
                 moe_route_finish_topk_kernel<float><<<blocks, 256, 0, stream>>>(
                     route_partial, splits, router_b_ptr, logits, selected, probs, counts, shard(), static_cast<const float*>(x),

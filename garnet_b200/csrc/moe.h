@@ -65,7 +65,7 @@ int moe_mx_mode_of(const garnet_b200_moe_options& o);
 int moe_resolve_options(const garnet_b200_moe_options* in, garnet_b200_moe_options* eff);
 size_t moe_route_partial_bytes(int tokens, int experts);   // to provide for calls of up to `tokens` tokens
 size_t moe_route_partial_need(int tokens, int experts);    // written by a call of exactly `tokens` tokens
-int moe_route_splits(int tokens);   // K ranges (partial-sum planes) of the tensor-core router
+int moe_route_splits(int tokens, int experts);   // K ranges (partial-sum planes) of the tensor-core router
 constexpr int kMxMinRowsPerExpert = 8;   // routed rows per local expert above which the block-scaled path is used
 
 struct Moe {

@@ -20,9 +20,16 @@ constexpr int kRmTokens = 64;     // tokens per CTA: 4 warps x 16 rows
 constexpr int kRmExperts = 64;    // experts per CTA: 8 MMA column tiles per warp
 constexpr int kRmSlab = 64;       // K per staging step
 constexpr int kRmStride = kRmSlab + 8;   // halves per staged row: bank-conflict-free fragment reads
-// K is cut into moe_route_splits(tokens) ranges (grid z): that many times the CTAs, partial sums added in a
-// fixed order.  Few tokens make few token tiles, so they get more ranges.
-int moe_route_splits(int tokens) { return tokens <= 512 ? 9 : 3; }
+// K is cut into moe_route_splits(tokens, experts) ranges (grid z): that many times the CTAs, partial sums added
+// in a fixed order.  The ranges are chosen so that the CTAs about fill the GPU once (two CTAs of this kernel fit an
+// SM): few tokens make few tiles and get up to nine ranges, 4096 tokens of 128 experts get two (256 CTAs; three
+// ranges made 384 CTAs, a wave and a third).
+constexpr int kRmMaxSplits = 9;
+int moe_route_splits(int tokens, int experts)
+{
+    const long long tiles = (long long)((tokens + kRmTokens - 1) / kRmTokens) * ((experts + kRmExperts - 1) / kRmExperts);
+    return int(std::max<long long>(1, std::min<long long>(kRmMaxSplits, (2 * kSmCount) / tiles)));
+}
 
 __global__ void moe_router_split_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ w3, size_t count)
 {
@@ -166,12 +173,11 @@ __global__ void moe_route_finish_kernel(const float* __restrict__ partial, const
 
 // What a call with `tokens` tokens writes, and what a caller sizing for up to `tokens` tokens must provide (the
 // number of K ranges drops above 512 tokens, so the second is kept monotone).
-size_t moe_route_partial_need(int tokens, int experts) { return size_t(moe_route_splits(tokens)) * tokens * experts * sizeof(float); }
-size_t moe_route_partial_bytes(int tokens, int experts)
+size_t moe_route_partial_need(int tokens, int experts)
 {
-    const size_t need = moe_route_partial_need(tokens, experts);
-    return tokens > 512 ? std::max(need, moe_route_partial_need(512, experts)) : need;
+    return size_t(moe_route_splits(tokens, experts)) * tokens * experts * sizeof(float);
 }
+size_t moe_route_partial_bytes(int tokens, int experts) { return size_t(kRmMaxSplits) * tokens * experts * sizeof(float); }
 
 int Moe::init_route_mma(cudaStream_t stream)
 {
@@ -187,7 +193,7 @@ int Moe::init_route_mma(cudaStream_t stream)
 
 int Moe::route_mma(const void* x, float* logits, float* partial, int tokens, cudaStream_t stream, bool finish)
 {
-    const int splits = moe_route_splits(tokens);
+    const int splits = moe_route_splits(tokens, opt.experts);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned((tokens + kRmTokens - 1) / kRmTokens), unsigned((opt.experts + kRmExperts - 1) / kRmExperts),
                        unsigned(splits));
