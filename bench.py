@@ -43,7 +43,7 @@ LAYERS = 28
 PROJ = [("q_proj", 2048, 2048), ("k_proj", 2048, 1024), ("v_proj", 2048, 1024), ("o_proj", 2048, 2048),
         ("gate_proj", 2048, 6144), ("up_proj", 2048, 6144), ("down_proj", 6144, 2048)]
 LM_HEAD = ("lm_head", 2048, 151936)
-SWEEP_M = [1, 4, 16, 64, 256]
+SWEEP_M = [1, 4, 8, 16, 64, 256]   # the configured sweep plus 8 rows (two 4-row MMA column blocks)
 # dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of a launch of
 # w4a16_list_kernel, from the ncu capture summarised in the file named below (an
 # eight-layer list, 208 MB of weights, captured instead of the full 890 MB pass to keep the
