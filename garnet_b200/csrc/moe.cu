@@ -870,14 +870,18 @@ moe_fill_kernel(const int* __restrict__ selected, int slots, const int* __restri
 #endif
 constexpr int kMoeWarps = GB_MOE_WARPS;                       // warps per CTA; each streams its own strips through its own ring
 #ifndef GB_MOE_STAGES
-#define GB_MOE_STAGES 3
+#define GB_MOE_STAGES 2
 #endif
 constexpr int kMoeStages = GB_MOE_STAGES;          // ring slots per warp
 #ifndef GB_MOE_CTAS
 #define GB_MOE_CTAS 2
 #endif
 constexpr int kMoeCtasPerSm = GB_MOE_CTAS;
-constexpr int kMoeSegChunks = 5;                   // chunks per bulk copy (a gpt-oss strip is 45 chunks = 9 copies)
+#ifndef GB_MOE_SEG
+#define GB_MOE_SEG 9
+#endif
+constexpr int kMoeSegChunks = GB_MOE_SEG;          // chunks per bulk copy (a gpt-oss strip is 45 chunks = 5 copies; copies of 3 / 5 / 9
+                                                   // chunks measured 275 / 244 / 221 us per 32-token call: the work around a copy is per copy)
 constexpr int kMoeSegBytes = kMoeSegChunks * kMxChunkBytes;
 constexpr int kMoeRows = 8;                        // slots per task (one MMA N-tile)
 constexpr int kMoeListCache = 32;                  // leading task and slot-order entries a CTA keeps in shared memory
@@ -1076,7 +1080,7 @@ __device__ __forceinline__ void moe_seg_math(const uint8_t* sbase, const uint8_t
 // Persistent CTAs over the flattened list of (task, strip) items; a task is up to 8 routed slots of
 // one expert, a strip 16 rows of that expert's matrix (codes and scales together, contiguous).  A CTA
 // owns a contiguous range of items and its warps take them in turn; every warp works alone: lane 0
-// requests the strip in 5-chunk bulk copies into the warp's own ring, the warp converts e2m1 pairs to
+// requests the strip in 9-chunk bulk copies into the warp's own two-slot ring, the warp converts e2m1 pairs to
 // fp16 pairs with one instruction each and runs m16n8k16 fp16 MMAs whose N dimension is the task's
 // slots (the slots' activations come straight from global memory: a few rows that stay in L1), scales
 // each 32-column group's fp32 partial sum by its e8m0 factor, and finishes the strip from its own
