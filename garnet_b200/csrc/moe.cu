@@ -465,30 +465,21 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
     }
     __syncthreads();
     if (threadIdx.x == 0) GB_MTRACE(2);
-    float acc[kRouteTokens];
+    // One token after the other through the same few instructions: this code runs once per CTA, so every
+    // instruction of it is fetched cold, and unrolled over eight tokens it spent more time being fetched than
+    // running.
+#pragma unroll 1
+    for (int t = 0; t < tokens; ++t) {
+        const float* xt = xs + t * hidden;
+        float acc = 0.f;
 #pragma unroll
-    for (int t = 0; t < kRouteTokens; ++t) acc[t] = 0.f;
-#pragma unroll
-    for (int i = 0; i < kSmallRouteSteps; ++i) {
-        const int d = threadIdx.x + i * kThreads;
-        if (d < hidden) {
-#pragma unroll
-            for (int t = 0; t < kRouteTokens; ++t)
-                if (t < tokens) acc[t] = fmaf(xs[t * hidden + d], wv[i], acc[t]);
+        for (int i = 0; i < kSmallRouteSteps; ++i) {
+            const int d = threadIdx.x + i * kThreads;
+            if (d < hidden) acc = fmaf(xt[d], wv[i], acc);
         }
-    }
-    for (int d = threadIdx.x + kSmallRouteSteps * kThreads; d < hidden; d += kThreads) {
-        const float w = __ldg(&wrow[d]);
-#pragma unroll
-        for (int t = 0; t < kRouteTokens; ++t)
-            if (t < tokens) acc[t] = fmaf(xs[t * hidden + d], w, acc[t]);
-    }
-#pragma unroll
-    for (int t = 0; t < kRouteTokens; ++t) {
-        if (t < tokens) {
-            const float v = warp_sum(acc[t]);
-            if (lane == 0) part[warp][t] = v;
-        }
+        for (int d = threadIdx.x + kSmallRouteSteps * kThreads; d < hidden; d += kThreads) acc = fmaf(xt[d], __ldg(&wrow[d]), acc);
+        const float v = warp_sum(acc);
+        if (lane == 0) part[warp][t] = v;
     }
     __syncthreads();
     if (threadIdx.x == 0) GB_MTRACE(3);
