@@ -277,11 +277,12 @@ __device__ __forceinline__ void small_meta_body(const float* logits, const Small
 #pragma unroll
         for (int u = 0; u < 8; ++u) mine_v[u] = lane + 32 * u < experts ? __ldcg(&l[lane + 32 * u]) : -INFINITY;
         unsigned taken = 0;   // bit u: this lane's u-th logit has been selected
-        float top[8];
-        int chosen[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (j >= topk) break;
+        // The rounds run through one copy of the code (this body runs once per call, cold: see the router kernel);
+        // lane j keeps the j-th pick.
+        float my_top = -INFINITY, top0 = 0.f;
+        int my_pick = 0;
+#pragma unroll 1
+        for (int j = 0; j < topk; ++j) {
             float best = -INFINITY;
             int arg = 0x7fffffff;
 #pragma unroll
@@ -302,20 +303,14 @@ __device__ __forceinline__ void small_meta_body(const float* logits, const Small
                 }
             }
             if ((arg & 31) == lane) taken |= 1u << (arg >> 5);
-            chosen[j] = arg;
-            top[j] = best;
+            if (lane == j) my_top = best, my_pick = arg;
+            if (j == 0) top0 = best;
         }
-        // lane j holds the j-th pick; the sum runs over j = 0, 1, ... in that order
-        float my_top = -INFINITY;
-        int my_pick = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (j < topk && lane == j) my_top = top[j], my_pick = chosen[j];
-        const float ex = lane < topk ? expf(my_top - top[0]) : 0.f;
+        // the sum runs over j = 0, 1, ... in that order
+        const float ex = lane < topk ? expf(my_top - top0) : 0.f;
         float total = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (j < topk) total += __shfl_sync(0xffffffffu, ex, j);
+#pragma unroll 1
+        for (int j = 0; j < topk; ++j) total += __shfl_sync(0xffffffffu, ex, j);
         if (lane < topk) {
             mt.selected[warp * topk + lane] = my_pick;
             s_sel[warp * topk + lane] = my_pick;
@@ -419,7 +414,8 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
                        float* __restrict__ logits, __half* __restrict__ xh, int* __restrict__ xshift, int tokens,
                        int hidden, int experts, const SmallMeta mt)
 {
-    extern __shared__ __align__(16) float xs[];   // [tokens][hidden]
+    extern __shared__ __align__(16) uint8_t xs_raw[];
+    XT* xs = reinterpret_cast<XT*>(xs_raw);   // [tokens][hidden], as it comes (converted where it is used: less code here)
     __shared__ float part[kRouteWarps][kRouteTokens];
     __shared__ float s_amax[kRouteWarps];
     __shared__ int s_last;
@@ -445,22 +441,9 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
             const uint4* xv = reinterpret_cast<const uint4*>(x);
             const int nvec = total / kPer;
 #pragma unroll 6
-            for (int v = threadIdx.x; v < nvec; v += kThreads) {
-                const uint4 u = __ldcg(&xv[v]);
-                float* dst = xs + size_t(v) * kPer;
-                if constexpr (sizeof(XT) == 4) {
-                    *reinterpret_cast<uint4*>(dst) = u;
-                } else {
-                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        dst[2 * q] = __uint_as_float(w[q] << 16);
-                        dst[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u);
-                    }
-                }
-            }
+            for (int v = threadIdx.x; v < nvec; v += kThreads) reinterpret_cast<uint4*>(xs)[v] = __ldcg(&xv[v]);
         } else {
-            for (int i = threadIdx.x; i < total; i += kThreads) xs[i] = to_float(x[i]);
+            for (int i = threadIdx.x; i < total; i += kThreads) xs[i] = x[i];
         }
     }
     __syncthreads();
@@ -470,14 +453,15 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
     // running.
 #pragma unroll 1
     for (int t = 0; t < tokens; ++t) {
-        const float* xt = xs + t * hidden;
+        const XT* xt = xs + t * hidden;
         float acc = 0.f;
 #pragma unroll
         for (int i = 0; i < kSmallRouteSteps; ++i) {
             const int d = threadIdx.x + i * kThreads;
-            if (d < hidden) acc = fmaf(xt[d], wv[i], acc);
+            if (d < hidden) acc = fmaf(to_float(xt[d]), wv[i], acc);
         }
-        for (int d = threadIdx.x + kSmallRouteSteps * kThreads; d < hidden; d += kThreads) acc = fmaf(xt[d], __ldg(&wrow[d]), acc);
+        for (int d = threadIdx.x + kSmallRouteSteps * kThreads; d < hidden; d += kThreads)
+            acc = fmaf(to_float(xt[d]), __ldg(&wrow[d]), acc);
         const float v = warp_sum(acc);
         if (lane == 0) part[warp][t] = v;
     }
@@ -496,7 +480,7 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
         for (int u = blockIdx.x; u < tokens * slices; u += gridDim.x) {
             const int t = u / slices, sl = u % slices;
             float amax = 0.f;
-            for (int d = threadIdx.x; d < hidden; d += kThreads) amax = fmaxf(amax, fabsf(bf16_round_f(xs[t * hidden + d])));
+            for (int d = threadIdx.x; d < hidden; d += kThreads) amax = fmaxf(amax, fabsf(bf16_round_f(to_float(xs[t * hidden + d]))));
 #pragma unroll
             for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
             __syncthreads();
@@ -510,7 +494,7 @@ moe_route_small_kernel(const XT* __restrict__ x, const float* __restrict__ rw, c
             const float scale = __uint_as_float(uint32_t(127 - shift) << 23);
             const int d1 = min(hidden, (sl + 1) * len);
             for (int d = sl * len + threadIdx.x; d < d1; d += kThreads)
-                xh[size_t(t) * hidden + d] = __float2half_rn(bf16_round_f(xs[t * hidden + d]) * scale);
+                xh[size_t(t) * hidden + d] = __float2half_rn(bf16_round_f(to_float(xs[t * hidden + d])) * scale);
             if (sl == 0 && threadIdx.x == 0) xshift[t] = shift;
         }
     }
