@@ -57,6 +57,14 @@ __device__ __forceinline__ float warp_sum_f(float v)
 
 __device__ __forceinline__ float bf16r(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
 
+// 8-byte asynchronous copy global -> shared (no registers in between), and the wait for a thread's own copies.
+__device__ __forceinline__ void cp_async_8(void* dst_smem, const void* src)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(uint32_t(__cvta_generic_to_shared(dst_smem))), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // Per-head RMS norm (weight w) and rotate-half RoPE of one 128-wide head held as dims
 // lane, lane + 32, lane + 64, lane + 96; every step rounds to bf16 as a bf16 network does.
 __device__ __forceinline__ void norm_rope_head(const __nv_bfloat16* head, const __nv_bfloat16* w, const float* cs, const float* sn,
@@ -100,25 +108,32 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const
     const bool holds_new = valid && slot >= start && slot < end;
 
     // A warp owns positions start + warp, + 8, ...: one per cache page of 16 when the pages are that size.  All
-    // their rows are requested before the first is used, so the walk costs one trip to memory.
+    // their rows are requested before the first is used, so the walk costs one trip to memory - as asynchronous
+    // copies into shared memory issued from a loop, not as an unrolled run of loads into registers: this kernel
+    // runs once per CTA, every instruction of it is fetched cold, and the unrolled form (sixteen address
+    // computations, thirty-two loads, sixteen score steps) spent longer being fetched than running.
     constexpr int kPer = kAttnSplitPositions / kAttnWarps;
-    uint2 kr[kPer], vr[kPer];
+    extern __shared__ __align__(16) uint8_t kv_rows[];   // [warp][K, V][kPer][256 bytes]
+    uint8_t* my_k = kv_rows + size_t(warp) * (2 * kPer * kAttnHeadDim * 2);
+    uint8_t* my_v = my_k + kPer * kAttnHeadDim * 2;
     if (valid) {
-        size_t at[kPer];
-#pragma unroll
+        // the page of every position of this warp, one lane each, in one trip
+        int page = 0;
+        {
+            const int pos = start + warp + lane * kAttnWarps;
+            if (lane < kPer && pos < end) page = __ldg(&table[pos / p.page_size]);
+        }
+#pragma unroll 1
         for (int u = 0; u < kPer; ++u) {
             const int pos = start + warp + u * kAttnWarps;
-            at[u] = (pos < end && pos != slot)
-                        ? ((size_t(__ldg(&table[pos / p.page_size])) * p.page_size + pos % p.page_size) * p.kv_heads + kv_head) * kAttnHeadDim
-                        : ~size_t(0);
-        }
-#pragma unroll
-        for (int u = 0; u < kPer; ++u) {
-            if (at[u] != ~size_t(0)) {
-                kr[u] = __ldcg(reinterpret_cast<const uint2*>(p.key_pages + at[u]) + lane);
-                vr[u] = __ldcg(reinterpret_cast<const uint2*>(p.value_pages + at[u]) + lane);
+            const int pg = __shfl_sync(0xffffffffu, page, u);
+            if (pos < end && pos != slot) {
+                const size_t at = ((size_t(pg) * p.page_size + pos % p.page_size) * p.kv_heads + kv_head) * kAttnHeadDim;
+                cp_async_8(my_k + u * (kAttnHeadDim * 2) + lane * 8, reinterpret_cast<const uint2*>(p.key_pages + at) + lane);
+                cp_async_8(my_v + u * (kAttnHeadDim * 2) + lane * 8, reinterpret_cast<const uint2*>(p.value_pages + at) + lane);
             }
         }
+        cp_async_commit();
     }
 
     if (warp == 0) {
@@ -151,7 +166,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const
     const float scale = 0.08838834764831845f;   // 1 / sqrt(128)
     float run_max = -FLT_MAX, run_sum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
     if (valid) {
-#pragma unroll
+        cp_async_wait_all();   // a lane reads back only the bytes it copied itself
+#pragma unroll 1
         for (int u = 0; u < kPer; ++u) {
             const int pos = start + warp + u * kAttnWarps;
             if (pos >= end) break;
@@ -160,10 +176,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const
 #pragma unroll
                 for (int i = 0; i < 4; ++i) kf[i] = k_new[4 * lane + i], vf[i] = v_new[4 * lane + i];
             } else {
-                kf[0] = __uint_as_float(kr[u].x << 16), kf[1] = __uint_as_float(kr[u].x & 0xffff0000u);
-                kf[2] = __uint_as_float(kr[u].y << 16), kf[3] = __uint_as_float(kr[u].y & 0xffff0000u);
-                vf[0] = __uint_as_float(vr[u].x << 16), vf[1] = __uint_as_float(vr[u].x & 0xffff0000u);
-                vf[2] = __uint_as_float(vr[u].y << 16), vf[3] = __uint_as_float(vr[u].y & 0xffff0000u);
+                const uint2 kr = *reinterpret_cast<const uint2*>(my_k + u * (kAttnHeadDim * 2) + lane * 8);
+                const uint2 vr = *reinterpret_cast<const uint2*>(my_v + u * (kAttnHeadDim * 2) + lane * 8);
+                kf[0] = __uint_as_float(kr.x << 16), kf[1] = __uint_as_float(kr.x & 0xffff0000u);
+                kf[2] = __uint_as_float(kr.y << 16), kf[3] = __uint_as_float(kr.y & 0xffff0000u);
+                vf[0] = __uint_as_float(vr.x << 16), vf[1] = __uint_as_float(vr.x & 0xffff0000u);
+                vf[2] = __uint_as_float(vr.y << 16), vf[3] = __uint_as_float(vr.y & 0xffff0000u);
             }
             const float score = warp_sum_f(qv[0] * kf[0] + qv[1] * kf[1] + qv[2] * kf[2] + qv[3] * kf[3]) * scale;
             const float next_max = fmaxf(run_max, score);
@@ -374,8 +392,27 @@ int garnet_b200_attention_decode(const garnet_b200_attention_options* o, const v
     p.max_logical_pages = o->max_logical_pages;
     p.rope_positions = o->rope_positions;
     p.eps = o->norm_eps;
-    GB_CUDA(launch_with_pdl(attention_decode_kernel, dim3(unsigned(o->q_heads), unsigned(p.splits), unsigned(batch)),
-                            dim3(kAttnWarps * 32), static_cast<cudaStream_t>(stream), (flags & 1u) != 0, p));
+    {
+        constexpr int kRowsBytes = kAttnWarps * 2 * (kAttnSplitPositions / kAttnWarps) * kAttnHeadDim * 2;   // 64 KB
+        static bool attr_set[64] = {};
+        int dev = 0;
+        GB_CUDA(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+            GB_CUDA(cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRowsBytes));
+            attr_set[dev] = true;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(o->q_heads), unsigned(p.splits), unsigned(batch));
+        cfg.blockDim = dim3(kAttnWarps * 32);
+        cfg.dynamicSmemBytes = kRowsBytes;
+        cfg.stream = static_cast<cudaStream_t>(stream);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = (flags & 1u) ? 1 : 0;
+        GB_CUDA(cudaLaunchKernelEx(&cfg, attention_decode_kernel, p));
+    }
     return GARNET_B200_OK;
 }
 
