@@ -600,11 +600,12 @@ moe_route_finish_topk_kernel(const float* __restrict__ partial, int splits, cons
         }
     }
     unsigned taken = 0;   // bit u: this lane's u-th logit has been picked
-    float top[8];
-    int chosen[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        if (j >= topk) break;
+    // the rounds run through one copy of the code (a warp runs this once: every instruction is fetched cold);
+    // lane j keeps the j-th pick
+    float my_top = -INFINITY, top0 = 0.f;
+    int my_pick = 0;
+#pragma unroll 1
+    for (int j = 0; j < topk; ++j) {
         float best = -INFINITY;
         int arg = 0x7fffffff;
 #pragma unroll
@@ -625,19 +626,13 @@ moe_route_finish_topk_kernel(const float* __restrict__ partial, int splits, cons
             }
         }
         if ((arg & 31) == lane) taken |= 1u << (arg >> 5);
-        chosen[j] = arg;
-        top[j] = best;
+        if (lane == j) my_top = best, my_pick = arg;
+        if (j == 0) top0 = best;
     }
-    float my_top = -INFINITY;
-    int my_pick = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-        if (j < topk && lane == j) my_top = top[j], my_pick = chosen[j];
-    const float ex = lane < topk ? expf(my_top - top[0]) : 0.f;
+    const float ex = lane < topk ? expf(my_top - top0) : 0.f;
     float total = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-        if (j < topk) total += __shfl_sync(0xffffffffu, ex, j);
+#pragma unroll 1
+    for (int j = 0; j < topk; ++j) total += __shfl_sync(0xffffffffu, ex, j);
     if (lane < topk) {
         selected[token * topk + lane] = my_pick;
         probs[token * topk + lane] = bf16_round_f(ex / total);
