@@ -174,6 +174,7 @@ __global__ void __launch_bounds__(512) oss_attention_decode_kernel(const OssAttn
 {
     __shared__ __align__(16) __nv_bfloat16 ks[kOssSplit * kOssRowStride], vs[kOssSplit * kOssRowStride];
     __shared__ float qs[16][kOssDim];
+    __shared__ unsigned char row_ok[kOssSplit];   // the row's page exists (looked up once, while staging)
     __shared__ int s_last;
     const int kv = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group = p.q_heads / p.kv_heads;
@@ -190,6 +191,7 @@ __global__ void __launch_bounds__(512) oss_attention_decode_kernel(const OssAttn
         const size_t off = oss_cache_offset(p, b, s0 + r, kv);
         uint4 v = make_uint4(0, 0, 0, 0);
         if (off != SIZE_MAX) v = __ldcg(reinterpret_cast<const uint4*>((is_v ? p.values : p.keys) + off) + piece);
+        if ((i & 15) == 0) row_ok[r] = off != SIZE_MAX;
         // a staged row starts on an 8-byte boundary (136-byte rows): two 8-byte stores
         uint2* dst = reinterpret_cast<uint2*>((is_v ? vs : ks) + r * kOssRowStride + piece * 8);
         dst[0] = make_uint2(v.x, v.y);
@@ -209,7 +211,7 @@ __global__ void __launch_bounds__(512) oss_attention_decode_kernel(const OssAttn
     for (int u = 0; u < 2; ++u) {
         const int r = lane + 32 * u;
         float s = -FLT_MAX;
-        if (r < rows && oss_cache_offset(p, b, s0 + r, kv) != SIZE_MAX) {
+        if (r < rows && row_ok[r]) {
             float acc = 0.f;
             const __nv_bfloat162* kr = reinterpret_cast<const __nv_bfloat162*>(ks + r * kOssRowStride);
 #pragma unroll 8
@@ -249,18 +251,31 @@ __global__ void __launch_bounds__(512) oss_attention_decode_kernel(const OssAttn
     if (warp < group) {
         const size_t hb = (size_t(b) * p.q_heads + head) * p.splits * (2 + kOssDim);
         float mx = p.sinks[head];
-        for (int s = lane; s < p.splits; s += 32)
-            if (__ldcg(&p.part[hb + size_t(s) * (2 + kOssDim) + 1]) > 0.f) mx = fmaxf(mx, __ldcg(&p.part[hb + size_t(s) * (2 + kOssDim)]));
+        for (int s = lane; s < p.splits; s += 32) {   // both values requested at once
+            const float pmax = __ldcg(&p.part[hb + size_t(s) * (2 + kOssDim)]), psum = __ldcg(&p.part[hb + size_t(s) * (2 + kOssDim) + 1]);
+            if (psum > 0.f) mx = fmaxf(mx, pmax);
+        }
         mx = warp_max(mx);
         float sum = __expf(p.sinks[head] - mx), o0 = 0.f, o1 = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-            const float* ps = p.part + hb + size_t(s) * (2 + kOssDim);
-            const float ssum = __ldcg(ps + 1);
-            if (ssum <= 0.f) continue;
-            const float f = __expf(__ldcg(ps) - mx);
-            sum += f * ssum;
-            o0 += f * __ldcg(ps + 2 + 2 * lane);
-            o1 += f * __ldcg(ps + 3 + 2 * lane);
+        // eight splits' values are requested together, without a condition on them, so that the loads overlap
+        // instead of queueing behind one another (the order of the additions stays the order of the splits)
+        for (int sb = 0; sb < p.splits; sb += 8) {
+            float pm[8], psum[8], po0[8], po1[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool in = sb + u < p.splits;
+                const float* ps = p.part + hb + size_t(in ? sb + u : sb) * (2 + kOssDim);
+                pm[u] = __ldcg(ps), psum[u] = in ? __ldcg(ps + 1) : 0.f;
+                po0[u] = __ldcg(ps + 2 + 2 * lane), po1[u] = __ldcg(ps + 3 + 2 * lane);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (psum[u] <= 0.f) continue;
+                const float f = __expf(pm[u] - mx);
+                sum += f * psum[u];
+                o0 += f * po0[u];
+                o1 += f * po1[u];
+            }
         }
         float* o = p.out + size_t(b) * p.q_heads * kOssDim + head * kOssDim;
         o[2 * lane] = bfr(live ? o0 / sum : 0.f);
