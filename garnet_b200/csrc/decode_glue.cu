@@ -98,10 +98,18 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const
     pdl_launch_dependents();
     pdl_wait();   // q, k, v come from the linear before this kernel
     const __nv_bfloat16* row = p.qkv + size_t(b) * (q_width + 2 * kv_width);
+    const int* table = p.page_tables + size_t(b) * p.max_logical_pages;
+    // the page of every position of this warp, one lane each: asked for together with the sequence's position
+    // (it does not depend on it), so that the two look-ups cost one trip
+    constexpr int kPer = kAttnSplitPositions / kAttnWarps;
+    int page = 0;
+    {
+        const int pos = split * kAttnSplitPositions + warp + lane * kAttnWarps;
+        if (lane < kPer && pos / p.page_size < p.max_logical_pages) page = __ldg(&table[pos / p.page_size]);
+    }
     const int slot = p.positions[b];
     const int context = slot + 1;
     const int start = split * kAttnSplitPositions, end = min(context, start + kAttnSplitPositions);
-    const int* table = p.page_tables + size_t(b) * p.max_logical_pages;
     const bool valid = slot >= 0 && slot < p.rope_positions && slot / p.page_size < p.max_logical_pages;
     const float* cs = p.rope_cos + size_t(valid ? slot : 0) * (kAttnHeadDim / 2);
     const float* sn = p.rope_sin + size_t(valid ? slot : 0) * (kAttnHeadDim / 2);
@@ -112,17 +120,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_decode_kernel(const
     // copies into shared memory issued from a loop, not as an unrolled run of loads into registers: this kernel
     // runs once per CTA, every instruction of it is fetched cold, and the unrolled form (sixteen address
     // computations, thirty-two loads, sixteen score steps) spent longer being fetched than running.
-    constexpr int kPer = kAttnSplitPositions / kAttnWarps;
     extern __shared__ __align__(16) uint8_t kv_rows[];   // [warp][K, V][kPer][256 bytes]
     uint8_t* my_k = kv_rows + size_t(warp) * (2 * kPer * kAttnHeadDim * 2);
     uint8_t* my_v = my_k + kPer * kAttnHeadDim * 2;
     if (valid) {
-        // the page of every position of this warp, one lane each, in one trip
-        int page = 0;
-        {
-            const int pos = start + warp + lane * kAttnWarps;
-            if (lane < kPer && pos < end) page = __ldg(&table[pos / p.page_size]);
-        }
 #pragma unroll 1
         for (int u = 0; u < kPer; ++u) {
             const int pos = start + warp + u * kAttnWarps;
